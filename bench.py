@@ -1,0 +1,407 @@
+"""Benchmark of the sparse-dense grid query hot path (and the hash engine beside it) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload ("trilinear query microbench"): 500k active blocks, grid_dim 8, embedding_dim 16 fp32
+~ N(0, 0.01), 4M query points uniform inside the active blocks, linear interpolation; one step
+is forward + backward (gradient w.r.t. embeddings AND offsets, a fresh dense gradient tensor per
+step exactly as the reference's autograd contract demands).  Per GPU the table is 16.4 GB, far
+beyond L2, and the query batches rotate, so no step re-reads a warm cache.  With N > 1 every rank
+holds a replica of the grid and works on its own 4M-query shard (weak scaling, no collective
+on the data path; the cost of synchronising the dense gradient is reported separately).
+
+One JSON line on stdout (rank 0).  ``value`` is device-timed with inputs resident in HBM;
+``e2e`` goes through the public API (``ash.SparseDenseGrid.__call__`` + ``backward``) with the
+query positions starting in pinned host memory and the loss read back to the host.
+``--impl reference`` times the CPU restatement of the reference's kernels (the reference has no
+CPU implementation of its own and its CUDA sources cannot be built here) on a 1/16-scale sample.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path[:0] = [ROOT, os.path.join(ROOT, "torch-ash_b200")]
+
+import torch  # noqa: E402
+
+N_BLOCKS, GRID_DIM, EMB_DIM, N_QUERIES = 500_000, 8, 16, 4_000_000
+HASH_KEYS, HASH_CAPACITY = 50_000_000, 64_000_000
+CPU_SCALE = 16  # the CPU arms run a 1/16-scale sample
+FWD_BYTES = 12 + 32 * EMB_DIM + 4 * EMB_DIM + 1          # x, 8 corner rows, y, mask
+BWD_BYTES = 4 * EMB_DIM + 12 + 32 * EMB_DIM + 32 * EMB_DIM + 12  # z, x, corner rows, gradient rows, grad x
+FIND_BYTES = 12 + 16 + 8 + 1                              # key, one slot, index, mask
+
+
+def measured_peak_gbs():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc = index, None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            return
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if sm:
+            self.result = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons)}
+
+
+def event_ms(fn, stream=None):
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    fn()
+    b.record()
+    b.synchronize()
+    return a.elapsed_time(b)
+
+
+def build_grid(ash, bw, device, n_blocks):
+    grid = ash.SparseDenseGrid(3, n_blocks, EMB_DIM, GRID_DIM, device)
+    blocks = bw.block_coords_blob(n_blocks, device)
+    grid.engine.insert_keys(blocks)
+    with torch.no_grad():
+        grid.embeddings.normal_(0.0, 0.01, generator=torch.Generator(device=device).manual_seed(bw.SEED + 3))
+    grid.construct_grid_neighbor_lut_(radius=1, bidirectional=False)
+    return grid, blocks
+
+
+# ------------------------------------------------------------------------------ CPU arms
+def cpu_query_sample(bw, steps, warmup):
+    """Forward + backward of the CPU restatement on a 1/16-scale sample; M queries/s."""
+    import numpy as np
+
+    import oracle
+
+    cpu = torch.device("cpu")
+    n_blocks, n_q = N_BLOCKS // CPU_SCALE, N_QUERIES // CPU_SCALE
+    blocks = bw.block_coords_blob(n_blocks, cpu).numpy()
+    om = oracle.OracleHashMap(3, n_blocks)
+    om.insert_keys(blocks)
+    rng = np.random.default_rng(bw.SEED)
+    emb = (rng.standard_normal((n_blocks, GRID_DIM**3, EMB_DIM), dtype=np.float32) * np.float32(0.01))
+    # lookup tables exactly as the Python layer builds them (ash/grid.py:526-617)
+    idx_of, _ = om.find(blocks)
+    offs = np.array([[(c >> d) & 1 for d in range(3)] for c in range(8)], np.int32)
+    nb_idx, nb_ok = om.find((blocks[:, None, :] + offs[None]).reshape(-1, 3))
+    g2g = np.full((n_blocks, 8), -1, np.int64)
+    g2g[idx_of] = np.where(nb_ok, nb_idx, -1).reshape(-1, 8)
+    G = GRID_DIM
+    cells = np.arange(G**3)
+    cc = np.stack([cells % G, (cells // G) % G, cells // (G * G)], 1)
+    nb = cc[:, None, :] + offs[None]
+    c2c = ((nb % G) * np.array([1, G, G * G])).sum(-1).astype(np.int64)
+    c2g = ((nb // G) * np.array([1, 2, 4])).sum(-1).astype(np.int64)
+    batches = []
+    for s in range(2):
+        x = bw.points_in_blocks(torch.from_numpy(blocks), n_q, G, 1.0, cpu, seed=bw.SEED + 50 + s).numpy()
+        bl = np.floor(x / G)
+        local = x - bl * G
+        cell = np.floor(local)
+        gi, mk = om.find(bl.astype(np.int32))
+        ci = (cell.astype(np.int64) * np.array([1, G, G * G])).sum(-1)
+        z = np.ones((n_q, EMB_DIM), np.float32)
+        batches.append((local - cell, gi, ci, mk, z))
+    times = []
+    for it in range(warmup + steps):
+        off, gi, ci, mk, z = batches[it % len(batches)]
+        t0 = time.perf_counter()
+        oracle.query_forward(emb, off, gi, ci, mk, g2g, c2c, c2g, "linear")
+        oracle.query_backward_forward(z, emb, off, gi, ci, mk, g2g, c2c, c2g, "linear")
+        if it >= warmup:
+            times.append(time.perf_counter() - t0)
+    sec = sum(times) / len(times)
+    return n_q / sec / 1e6, sec, oracle.num_threads(), (
+        f"{n_q} queries over {n_blocks} blocks (1/{CPU_SCALE} of the workload), forward + backward with a fresh "
+        f"dense gradient, mean of {len(times)} steps")
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import bench_workloads as bw
+
+    value, sec, cores, sample = cpu_query_sample(bw, max(1, min(args.steps, 5)), max(1, min(args.warmup, 2)))
+    line = {
+        "impl": "reference", "metric": "M trilinear queries/s (fwd+bwd)", "value": round(value, 4), "unit": "M queries/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(), "gpu_launches": 0,
+        "cpu_baseline": {"value": round(value, 4), "unit": "M queries/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": round(value, 4), "unit": "M queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config():
+    return {
+        "workload": "trilinear query microbench: 500k active blocks, grid_dim 8, embedding_dim 16 fp32 ~N(0,0.01), "
+                    "4M query points uniform in active blocks per GPU, linear interpolation, forward + backward "
+                    "(grad w.r.t. embeddings and offsets, fresh dense gradient per step)",
+        "cache": "inputs larger than L2: 16.4 GB table per GPU, 4 rotating query batches",
+        "parallelism": "replicated grid, query batch sharded per rank",
+    }
+
+
+# ------------------------------------------------------------------------------ GPU arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-hash", action="store_true", help="skip the hash-engine side measurement")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        sys.exit("bench.py needs a CUDA device: there is no CPU fallback (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+
+    import __ash
+    import ash
+    import bench_workloads as bw
+
+    peak, peak_kind = measured_peak_gbs()
+    grid, blocks = build_grid(ash, bw, device, N_BLOCKS)
+    emb = grid.embeddings.detach()
+    luts = (grid.lut_grid_nb2grid_idx, grid.lut_cell_nb2cell_idx, grid.lut_cell_nb2grid_nb)
+    n_batches = 4
+    xs = [bw.points_in_blocks(blocks, N_QUERIES, GRID_DIM, 1.0, device, seed=bw.SEED + 100 * rank + s)
+          for s in range(n_batches)]
+    split = [grid.query(x) for x in xs]  # (grid_indices, cell_indices, offsets, masks), resident in HBM
+    z = torch.ones(N_QUERIES, EMB_DIM, device=device)
+    # share of queries answered with a zero row because a +x/+y/+z neighbour block is absent
+    y0 = __ash.query_forward(emb, split[0][2], split[0][0], split[0][1], split[0][3], *luts, GRID_DIM, "linear")
+    zero_rows = float(((y0 == 0).all(dim=1) & split[0][3]).float().mean())
+    del y0
+
+    fwd_ms, bwd_ms, bwd_persist_ms = [], [], []
+    marks = []  # (before fwd, between, after bwd) events of every timed step; read after the region
+
+    def step(i, record):
+        gi, ci, off, mk = split[i % n_batches]
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if record else None
+        if record:
+            ev[0].record()
+        y = __ash.query_forward(emb, off, gi, ci, mk, *luts, GRID_DIM, "linear")
+        if record:
+            ev[1].record()
+        grad_emb, grad_off = __ash.query_backward_forward(z, emb, off, gi, ci, mk, *luts, GRID_DIM, "linear")
+        if record:
+            ev[2].record()
+            marks.append(ev)
+        del y, grad_emb, grad_off
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i, False)
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(args.steps):
+            step(i, True)
+        end.record()
+        barrier()
+    total_ms = start.elapsed_time(end)
+    for ev in marks:
+        fwd_ms.append(ev[0].elapsed_time(ev[1]))
+        bwd_ms.append(ev[1].elapsed_time(ev[2]))
+    if dist is not None:
+        t = torch.tensor([total_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    value = world * N_QUERIES / (ms_per_step * 1e-3) / 1e6
+
+    # persistent-gradient variant: accumulate into one long-lived buffer, no per-step zero-fill
+    gacc = torch.zeros_like(emb)
+    for i in range(args.warmup + args.steps):
+        gi, ci, off, mk = split[i % n_batches]
+        t = event_ms(lambda: __ash.query_backward_forward(z, emb, off, gi, ci, mk, *luts, GRID_DIM, "linear",
+                                                           grad_embeddings_out=gacc))
+        if i >= args.warmup:
+            bwd_persist_ms.append(t)
+    barrier()
+
+    # gradient synchronisation cost (not on the timed data path): one dense all-reduce
+    allreduce_ms = None
+    if dist is not None:
+        dist.all_reduce(gacc)
+        torch.cuda.synchronize()
+        allreduce_ms = event_ms(lambda: dist.all_reduce(gacc))
+        t = torch.tensor([allreduce_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        allreduce_ms = float(t.item())
+    del gacc
+    torch.cuda.empty_cache()
+
+    # end to end through the public API: pinned host positions in, loss out
+    x_host = [x.cpu().pin_memory() for x in xs]
+    e2e_times = []
+    for i in range(args.warmup + args.steps):
+        grid.embeddings.grad = None
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        x = x_host[i % n_batches].to(device, non_blocking=True).requires_grad_(True)
+        y, masks = grid(x, interpolation="linear")
+        loss = y.sum()
+        loss.backward()
+        loss_value = loss.item()
+        torch.cuda.synchronize()
+        if i >= args.warmup:
+            e2e_times.append(time.perf_counter() - t0)
+    grid.embeddings.grad = None
+    e2e_sec = sum(e2e_times) / len(e2e_times)
+    if dist is not None:
+        t = torch.tensor([e2e_sec], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_sec = float(t.item())
+    e2e_value = world * N_QUERIES / e2e_sec / 1e6
+
+    line = {
+        "metric": "M trilinear queries/s (fwd+bwd)", "value": round(value, 2), "unit": "M queries/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(),
+        "clocks": clocks.result, "gpu_launches": 2 * args.steps,
+        "e2e": {"value": round(e2e_value, 2), "unit": "M queries/s", "h2d_bytes_per_step": N_QUERIES * 12,
+                "d2h_bytes_per_step": 4, "ms_per_step": round(e2e_sec * 1e3, 4)},
+    }
+    if rank == 0:
+        f_ms, b_ms, bp_ms = statistics.mean(fwd_ms), statistics.mean(bwd_ms), statistics.mean(bwd_persist_ms)
+        achieved = N_QUERIES * BWD_BYTES / (bp_ms * 1e-3) / 1e9
+        line["roofline"] = {
+            "kernel": "query_backward_forward_kernel<float,4>", "bound": "hbm", "achieved": round(achieved, 1),
+            "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4), "peak_kind": peak_kind,
+            "traffic": None, "ms_per_launch": round(bp_ms, 4),
+            "note": "dominant kernel of the library; timed alone on a persistent gradient buffer "
+                    "(the API-faithful step adds a 16.4 GB cudaMemsetAsync before it)",
+        }
+        fa = N_QUERIES * FWD_BYTES / (f_ms * 1e-3) / 1e9
+        table_bytes = N_BLOCKS * GRID_DIM**3 * EMB_DIM * 4
+        step_bytes = N_QUERIES * (FWD_BYTES + BWD_BYTES) + table_bytes
+        line["kernels"] = {
+            "query_forward": {"ms": round(f_ms, 4), "achieved_gbs": round(fa, 1), "frac": round(fa / peak, 4)},
+            "query_backward_dense(memset+kernel)": {"ms": round(b_ms, 4)},
+            "step_api_faithful": {"bytes": step_bytes, "achieved_gbs": round(step_bytes / (ms_per_step * 1e-3) / 1e9, 1),
+                                  "frac": round(step_bytes / (ms_per_step * 1e-3) / 1e9 / peak, 4)},
+            "frac_of_8TBs_nominal": round(achieved / 8000.0, 4),
+        }
+        line["persistent_grad"] = {
+            "value": round(world * N_QUERIES / ((f_ms + bp_ms) * 1e-3) / 1e6, 2), "unit": "M queries/s",
+            "ms_per_step": round(f_ms + bp_ms, 4),
+            "note": "same kernels, gradient accumulated into a long-lived buffer instead of a fresh zero-filled one"}
+        line["zero_row_fraction"] = round(zero_rows, 4)
+        if allreduce_ms is not None:
+            line["grad_allreduce_ms"] = round(allreduce_ms, 3)
+
+    # free the grid before the hash-engine measurement
+    del grid, emb, split, xs, x_host, z, luts
+    torch.cuda.empty_cache()
+
+    if rank == 0 and not args.no_hash:
+        uniq = bw.hash_keys_clustered(HASH_KEYS // 2, device)
+        g = torch.Generator(device=device).manual_seed(bw.SEED + 9)
+        keys = torch.cat([uniq, uniq])[torch.randperm(HASH_KEYS, generator=g, device=device)]
+        heap = torch.arange(HASH_CAPACITY, dtype=torch.int32, device=device)
+        hm = __ash.HashMap(3, HASH_CAPACITY, heap, device)
+        t_ins = event_ms(lambda: hm.insert_keys(keys))
+        fresh = bw.hash_keys_clustered(HASH_KEYS // 2, device, seed=bw.SEED + 77)
+        q = torch.cat([uniq, fresh])[torch.randperm(HASH_KEYS, generator=g, device=device)]
+        del keys, fresh
+        for _ in range(3):
+            hm.find(q)
+        t_find = statistics.mean(event_ms(lambda: hm.find(q)) for _ in range(10))
+        hit = float(hm.find(q)[1].float().mean())
+        t_er = event_ms(lambda: hm.erase(uniq[: HASH_KEYS // 8]))
+        t_items = event_ms(lambda: hm.items())
+        fa = HASH_KEYS * FIND_BYTES / (t_find * 1e-3) / 1e9
+        line["hash_find"] = {
+            "workload": "50M int32x3 keys from 1024 Gaussian clusters (50% duplicates) into capacity 64M; "
+                        "50M finds at 50% hit rate; erase 6.25M; items()",
+            "value": round(HASH_KEYS / (t_find * 1e-3) / 1e6, 1), "unit": "M finds/s", "ms": round(t_find, 4),
+            "hit_rate": round(hit, 4),
+            "roofline": {"bound": "hbm", "achieved": round(fa, 1), "peak": peak, "unit": "GB/s", "frac": round(fa / peak, 4),
+                         "peak_kind": peak_kind, "traffic": None},
+            "insert_M_per_s": round(HASH_KEYS / (t_ins * 1e-3) / 1e6, 1),
+            "erase_M_per_s": round(HASH_KEYS / 8 / (t_er * 1e-3) / 1e6, 1), "items_ms": round(t_items, 3),
+        }
+        del hm, heap, q, uniq
+        torch.cuda.empty_cache()
+
+    if rank == 0 and world == 1 and not args.no_cpu:
+        v, sec, cores, sample = cpu_query_sample(bw, 2, 1)
+        line["cpu_baseline"] = {"value": round(v, 4), "unit": "M queries/s", "cores": cores, "kind": "port", "sample": sample}
+
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,241 @@
+/*
+ * libashb200 -- C ABI of the B200 (sm_100a) implementation of torch-ash's
+ * native hot path: the collision-free spatial hash engine and the sparse-dense
+ * grid kernels.  It replaces the reference's pybind module `__ash`
+ * (ash/src/pybind.cpp:8-38) and its stdgpu dependency.
+ *
+ * Conventions
+ *   - every pointer named *_dev or documented "device" is a CUDA device
+ *     pointer owned by the caller and only borrowed for the call;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default
+ *     stream); all work is enqueued on it and, unless stated otherwise, the
+ *     call returns without synchronising;
+ *   - every function returns 0 on success or an ASHB_ERR_* code; a text for
+ *     the calling thread's last failure is available from
+ *     ashb_last_error_string();
+ *   - sizes and counts are int64_t; keys are int32 rows of `key_dim` columns.
+ *
+ * There is no CPU implementation behind this interface: without a CUDA device
+ * every compute entry point fails with ASHB_ERR_CUDA.
+ */
+#ifndef ASHB200_H_
+#define ASHB200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ASHB_OK 0
+#define ASHB_ERR_INVALID 1   /* bad argument (dimension, size, null pointer, dtype code) */
+#define ASHB_ERR_CUDA 2      /* a CUDA runtime call failed */
+#define ASHB_ERR_UNSUPPORTED 3
+
+/* Bits of the device-side status word returned by ashb_map_status(). */
+#define ASHB_STATUS_CAPACITY 1u   /* an insert needed more than `capacity` indices; the key was dropped */
+#define ASHB_STATUS_PROBE 2u      /* a probe sequence visited every slot without finishing */
+#define ASHB_STATUS_SPIN 4u       /* a bounded wait on a slot being written ran out */
+#define ASHB_STATUS_DUPLICATE 8u  /* load_states met a key twice */
+
+/* dtype / interpolation codes of the grid entry points */
+#define ASHB_F32 0
+#define ASHB_F64 1
+#define ASHB_LINEAR 0
+#define ASHB_SMOOTH_STEP 1
+
+typedef struct ashb_map ashb_map;
+
+const char* ashb_last_error_string(void);
+int ashb_version(void);
+
+/* ---------------------------------------------------------------- hash engine */
+
+/* Replaces HashMap::HashMap / HashMapGPUImpl ctor (ash/src/hashmap.cpp:8-18,
+ * ash/src/hashmap_gpu.cuh:119-137, ash/src/hashmap_impl.h:11-24).
+ * key_dim in 1..4.  heap_dev: caller-owned int32[capacity] free-index stack,
+ * aliased for the life of the map, mutated in place and NOT rewritten here.
+ * device: CUDA ordinal the map lives on. */
+int ashb_map_create(int key_dim, int64_t capacity, int32_t* heap_dev, int device, ashb_map** out);
+
+/* Replaces ~HashMapGPUImpl (ash/src/hashmap_gpu.cuh:127, :134-137). */
+int ashb_map_destroy(ashb_map* map);
+
+/* Replaces HashMapGPUImpl::clear + HashMapImpl::reset_heap
+ * (ash/src/hashmap_gpu.cuh:355-358, ash/src/hashmap_impl.h:26-33). */
+int ashb_map_clear(ashb_map* map, void* stream);
+
+/* Replaces HashMapGPUImpl::size (ash/src/hashmap_gpu.cuh:157).  Synchronises `stream`. */
+int ashb_map_size(ashb_map* map, void* stream, int64_t* size_out);
+
+/* Reads and clears the device status word (ASHB_STATUS_* bits).  Synchronises
+ * `stream`.  The reference has no counterpart: it prints from the device or
+ * has undefined behaviour (ash/src/hashmap_gpu.cuh:226-227, :420). */
+int ashb_map_status(ashb_map* map, void* stream, uint32_t* status_out);
+
+/* Replaces find_kernel + HashMapGPUImpl::find (ash/src/hashmap_gpu.cuh:164-208).
+ * keys_dev int32[n][key_dim]; indices_dev int64[n] (0 on a miss); masks_dev
+ * uint8[n] (1 hit / 0 miss).  Every output element is written. */
+int ashb_map_find(ashb_map* map, const int32_t* keys_dev, int64_t n, int64_t* indices_dev,
+                  uint8_t* masks_dev, void* stream);
+
+/* Replaces insert_kernel (keys) + insert_keys (ash/src/hashmap_gpu.cuh:212-247).
+ * Insert-if-absent; each new key takes heap[counter++]. */
+int ashb_map_insert_keys(ashb_map* map, const int32_t* keys_dev, int64_t n, void* stream);
+
+/* Replaces insert_kernel (values) + insert + ValueContext
+ * (ash/src/hashmap_gpu.cuh:23-114, :250-313).  For each NEW key i with index
+ * idx, row i of src_dev[j] (row_bytes[j] bytes) is copied to row idx of
+ * dst_dev[j], j < n_values <= 16.  src_dev/dst_dev/row_bytes are HOST arrays of
+ * device pointers / sizes. */
+int ashb_map_insert_values(ashb_map* map, const int32_t* keys_dev, int64_t n, int n_values,
+                           const void* const* src_dev, void* const* dst_dev,
+                           const int64_t* row_bytes, void* stream);
+
+/* Replaces erase_kernel + erase (ash/src/hashmap_gpu.cuh:317-351): each erased
+ * key pushes its index back, heap[--counter] = idx. */
+int ashb_map_erase(ashb_map* map, const int32_t* keys_dev, int64_t n, void* stream);
+
+/* Replaces HashMapGPUImpl::items (ash/src/hashmap_gpu.cuh:377-405).  Writes up
+ * to max_n active (key, index) pairs, order unspecified; *n_out (host) gets the
+ * number of active pairs found.  Synchronises `stream`. */
+int ashb_map_items(ashb_map* map, int32_t* keys_out_dev, int64_t* indices_out_dev, int64_t max_n,
+                   int64_t* n_out, void* stream);
+
+/* Replaces load_states_kernel + load_states (ash/src/hashmap_gpu.cuh:408-450):
+ * the table is emptied, counter = n, heap contents copied from heap_src_dev
+ * (may alias the map's heap), every (key, index) pair stored verbatim. */
+int ashb_map_load_states(ashb_map* map, const int32_t* keys_dev, const int64_t* indices_dev,
+                         int64_t n, const int32_t* heap_src_dev, void* stream);
+
+/* ---------------------------------------------------------------- grid query
+ * Layouts (ash/grid_query.py:40-55): embeddings [n_emb][cells_per_grid][D]
+ * (D <= 16), offsets float32 [n][3] (always float32, ash/src/grid.cu:71),
+ * grid_indices / cell_indices int64 [n], masks uint8 [n], lut_grid_nb2grid_idx
+ * int64 [n_emb][8] (-1 = absent block), lut_cell_nb2cell_idx and
+ * lut_cell_nb2grid_nb int64 [cells_per_grid][8].  dtype = ASHB_F32 | ASHB_F64
+ * is the type of embeddings and of every floating output/input except offsets.
+ */
+
+/* Replaces query_forward_kernel + query_forward (ash/src/grid.cu:69-175).
+ * out [n][D]; rows of masked-out queries and of queries with an absent
+ * neighbour block are written as zeros (the reference zero-fills first). */
+int ashb_query_forward(int dtype, int interp, const void* embeddings, const float* offsets,
+                       const int64_t* grid_indices, const int64_t* cell_indices,
+                       const uint8_t* masks, const int64_t* lut_grid_nb2grid_idx,
+                       const int64_t* lut_cell_nb2cell_idx, const int64_t* lut_cell_nb2grid_nb,
+                       void* out, int64_t n, int64_t n_emb, int64_t cells_per_grid, int64_t D,
+                       void* stream);
+
+/* Replaces query_backward_forward_kernel + host (ash/src/grid.cu:178-307).
+ * z [n][D].  grad_offsets [n][3] is fully written.  grad_embeddings
+ * [n_emb][cells][D] is ACCUMULATED into (atomic adds); pass zero_grad != 0 to
+ * have it zero-filled on `stream` first, which reproduces the reference's fresh
+ * dense gradient. */
+int ashb_query_backward_forward(int dtype, int interp, const void* z, const void* embeddings,
+                                const float* offsets, const int64_t* grid_indices,
+                                const int64_t* cell_indices, const uint8_t* masks,
+                                const int64_t* lut_grid_nb2grid_idx,
+                                const int64_t* lut_cell_nb2cell_idx,
+                                const int64_t* lut_cell_nb2grid_nb, void* grad_embeddings,
+                                void* grad_offsets, int zero_grad, int64_t n, int64_t n_emb,
+                                int64_t cells_per_grid, int64_t D, void* stream);
+
+/* Replaces query_backward_backward_kernel + host (ash/src/grid.cu:310-451).
+ * grad_grad_offsets [n][3], z [n][D]; grad_z [n][D] is fully written;
+ * grad_embeddings accumulated as above.  The reference's third output
+ * (grad_offsets) is identically zero (grid.cu:417-418) and its first input
+ * (grad_grad_embeddings) is unused (grid.cu:426); neither crosses this ABI. */
+int ashb_query_backward_backward(int dtype, int interp, const void* grad_grad_offsets,
+                                 const void* z, const void* embeddings, const float* offsets,
+                                 const int64_t* grid_indices, const int64_t* cell_indices,
+                                 const uint8_t* masks, const int64_t* lut_grid_nb2grid_idx,
+                                 const int64_t* lut_cell_nb2cell_idx,
+                                 const int64_t* lut_cell_nb2grid_nb, void* grad_z,
+                                 void* grad_embeddings, int zero_grad, int64_t n, int64_t n_emb,
+                                 int64_t cells_per_grid, int64_t D, void* stream);
+
+/* ---------------------------------------------------------------- neighbourhood convolution */
+
+/* Replaces convolution_forward_kernel + convolution_forward (ash/src/grid.cu:951-1043).
+ * inputs/outputs [n_emb][cells_per_grid][D]; weights [num_cell_nbs][D]; masks uint8
+ * [num_grids * cells_per_grid]; grid_indices int64 [num_grids]; cell_indices int64
+ * [cells_per_grid]; lut_grid_nb2grid_idx int64 [n_emb][num_grid_nbs] (<= 125, -1 = absent);
+ * the two per-cell tables int64 [cells_per_grid][num_cell_nbs].  Rows of the listed
+ * blocks are written; zero_output != 0 zero-fills the whole output first, as the
+ * reference does. */
+int ashb_conv_forward(int dtype, const void* inputs, const void* weights, const uint8_t* masks,
+                      const int64_t* grid_indices, const int64_t* cell_indices,
+                      const int64_t* lut_grid_nb2grid_idx, const int64_t* lut_cell_nb2cell_idx,
+                      const int64_t* lut_cell_nb2grid_nb, void* outputs, int zero_output,
+                      int64_t num_grids, int64_t n_emb, int64_t cells_per_grid, int64_t D,
+                      int64_t num_cell_nbs, int64_t num_grid_nbs, void* stream);
+
+/* ---------------------------------------------------------------- ray sampler
+ * All lengths in cell units; rays float32 [n][3]; bbox float32 [3] each; the map
+ * must have key_dim 3 (ash/src/sampler.cu:89-99).  Positions are fma(t, d, o) in
+ * float32 and the block of a position is floor(position * (float)(1.0 / grid2cell)). */
+
+/* Replaces ray_find_near_far_kernel + ray_find_near_far (ash/src/sampler.cu:7-121).
+ * nears[i] = -1 when the ray meets no active block.  t_step is accepted and unused,
+ * as in the reference. */
+int ashb_ray_find_near_far(ashb_map* map, const float* ray_origins, const float* ray_directions,
+                           const float* bbox_min, const float* bbox_max, float* nears, float* fars,
+                           float t_min, float t_max, float t_step, float grid2cell, int64_t n,
+                           void* stream);
+
+/* Replace the two launches of ray_sample_count_kernel inside ray_sample
+ * (ash/src/sampler.cu:123-294): pass 1 writes counts int64 [n]; the caller forms their
+ * inclusive prefix sum; pass 2 writes ray_indices int64, t_nears and t_fars float32
+ * at [prefix[i-1], prefix[i]). */
+int ashb_ray_sample_count(ashb_map* map, const float* ray_origins, const float* ray_directions,
+                          const float* ray_nears, const float* ray_fars, int64_t* counts,
+                          int64_t max_samples_per_ray, float grid2cell, int64_t n, void* stream);
+int ashb_ray_sample_fill(ashb_map* map, const float* ray_origins, const float* ray_directions,
+                         const float* ray_nears, const float* ray_fars, const int64_t* prefix_sum,
+                         int64_t* ray_indices, float* t_nears, float* t_fars,
+                         int64_t max_samples_per_ray, float grid2cell, int64_t n, void* stream);
+
+/* ---------------------------------------------------------------- RGB-D TSDF integration
+ * Two launches replace one TSDFFusion.fuse_frame call (demo/rgbd_fusion.py:199-254),
+ * which in the reference is ~40 torch operations, a temporary hash set
+ * (ash/grid.py:145-147) and a third-party depth unprojection (demo/rgbd_fusion.py:57-74).
+ * intrinsic: HOST float[9] row-major pinhole matrix without skew; cam_to_world /
+ * world_to_cam: HOST float[12], rows of [R | t]; origin: HOST float[3], the world
+ * position of cell (0,0,0) (zero for unbounded grids, bbox_min for bounded ones);
+ * depth float32 [H][W] in metres and color float32 [H][W][3] are device buffers. */
+
+/* Step 1, allocation (unprojection + SparseDenseGrid.spatial_init_ with
+ * bidirectional dilation): every block within `dilation` blocks of a valid depth point
+ * (0 < depth < depth_max) is inserted if absent; for each such block idx,
+ * grid_coords[idx] (int32 [n_emb][3]) receives its coordinate and touched[idx]
+ * (uint32 [n_emb]) receives `stamp` (non-zero, different per frame).  bound_lo/bound_hi:
+ * HOST int32[3] half-open range of admissible block coordinates, or NULL for none. */
+int ashb_tsdf_touch(ashb_map* map, const float* depth, int H, int W, const float* intrinsic,
+                    const float* cam_to_world, float depth_max, float cell_size, const float* origin,
+                    int G, int dilation, const int32_t* bound_lo, const int32_t* bound_hi,
+                    int32_t* grid_coords, uint32_t* touched, uint32_t stamp, void* stream);
+
+/* Step 2, fusion (project_points_to_rgbd + the running average,
+ * demo/rgbd_fusion.py:76-110, :236-254) over every cell of every block whose
+ * touched[idx] == stamp.  embeddings float32 [n_emb][G^3][D], 5 <= D <= 16, with sdf at
+ * sdf_channel, colour at rgb_channel..+2 and the weight at weight_channel (the demo uses
+ * 0, 1, 4).  n_integrated_dev: optional device counter incremented once per fused block. */
+int ashb_tsdf_integrate(void* embeddings, int64_t n_emb, int G, int64_t D, const int32_t* grid_coords,
+                        const uint32_t* touched, uint32_t stamp, const float* depth, const float* color,
+                        int H, int W, const float* intrinsic, const float* world_to_cam, float depth_max,
+                        float cell_size, const float* origin, float trunc, int sdf_channel,
+                        int rgb_channel, int weight_channel, unsigned long long* n_integrated_dev,
+                        void* stream);
+
+/* ---------------------------------------------------------------- runtime knobs */
+
+/* cudaLimitMaxL2FetchGranularity of the current context (32, 64 or 128 bytes); a
+ * performance hint that lasts as long as the process.  No counterpart in the reference. */
+int ashb_set_l2_fetch_granularity(int bytes);
+int ashb_get_l2_fetch_granularity(int* bytes_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ASHB200_H_ */

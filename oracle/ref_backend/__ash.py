@@ -17,6 +17,9 @@ import torch
 import oracle as _o
 
 
+STATUS_CAPACITY, STATUS_PROBE, STATUS_SPIN, STATUS_DUPLICATE = 1, 2, 4, 8
+
+
 def _np(t: torch.Tensor):
     return t.detach().contiguous().numpy()
 
@@ -29,20 +32,28 @@ class HashMap:
         self._device = torch.device(device)
         self._heap = heap  # aliased and mutated in place (ash/src/hashmap_impl.h:23)
         self._m = _o.OracleHashMap(key_dim, capacity, heap.numpy())
+        self._status = 0
 
     def find(self, keys):
         idx, msk = self._m.find(_np(keys))
         return torch.from_numpy(idx), torch.from_numpy(msk)
 
     def insert_keys(self, keys):
-        self._m.insert_keys(_np(keys))
+        if self._m.insert_keys(_np(keys)):
+            self._status |= STATUS_CAPACITY
+
+    def status(self):
+        """Read-and-clear status word of the product's native module (not in the reference)."""
+        st, self._status = self._status, 0
+        return st
 
     def insert(self, keys, values, external_values):
-        self._m.insert(
+        if self._m.insert(
             _np(keys),
             {k: _np(v) for k, v in values.items()},
             {k: external_values[k].numpy() for k in values},
-        )
+        ):
+            self._status |= STATUS_CAPACITY
 
     def erase(self, keys):
         self._m.erase(_np(keys.to(torch.int32)))

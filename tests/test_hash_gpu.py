@@ -1,0 +1,275 @@
+"""Hash engine parity on the GPU: the reference's unit tests (unittests/test_engine.py,
+test_hashset.py, test_hashmap.py, test_embedding.py) replayed on the CUDA library, plus
+key -> value / hit-mask comparisons against the CPU oracle.  Raw indices are never compared
+(their order is nondeterministic); index SETS and key -> value associations are."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+DEV = torch.device("cuda:0")
+CAP = 100000
+
+
+def _diag_keys(dim, num, device=DEV):
+    """Keys of unittests/test_engine.py:11-19: shuffled (i, i, ..., i)."""
+    keys = torch.arange(num, dtype=torch.int32, device=device).view(-1, 1).tile((1, dim))
+    return keys[torch.randperm(num, device=device)]
+
+
+def _rand_keys(n, dim, lo, hi, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(lo, hi, (n, dim), generator=g, dtype=torch.int32)
+
+
+@pytest.mark.parametrize("dim", [1, 2, 3, 4])
+def test_insert_find_index_set(dim):
+    """unittests/test_engine.py:21-36: capacity == num inserts, indices == arange(num)."""
+    from ash import ASHEngine
+
+    eng = ASHEngine(dim=dim, capacity=CAP, device=DEV)
+    keys = _diag_keys(dim, CAP)
+    eng.insert_keys(keys)
+    assert eng.size() == CAP
+    indices, masks = eng.find(keys)
+    assert masks.sum() == CAP
+    uniq = torch.unique(indices, sorted=True)
+    assert len(uniq) == CAP and uniq.eq(torch.arange(CAP, device=DEV)).all()
+
+
+@pytest.mark.parametrize("dim", [1, 2, 3, 4])
+def test_insert_erase(dim):
+    """unittests/test_engine.py:38-47 and unittests/test_hashset.py:28-41."""
+    from ash import HashSet
+
+    hs = HashSet(dim, CAP, DEV)
+    keys = _diag_keys(dim, CAP)
+    hs.insert(keys)
+    assert hs.size() == CAP
+    hs.erase(keys[: CAP // 2])
+    assert hs.find(keys).sum() == CAP // 2
+    assert hs.size() == CAP // 2
+    hs.erase(keys)  # half of these are already gone
+    assert hs.size() == 0
+    # the freed indices are reusable: fill up again and get arange back
+    hs.insert(keys)
+    idx, m = hs.engine.find(keys)
+    assert m.all() and torch.unique(idx).numel() == CAP
+
+
+@pytest.mark.parametrize("dim", [1, 2, 3, 4])
+def test_insert_duplicates(dim):
+    """unittests/test_engine.py:49-69: x3 duplicates in one batch, one winner each."""
+    from ash import ASHEngine
+
+    num = CAP
+    eng = ASHEngine(dim=dim, capacity=CAP, device=DEV)
+    keys = _diag_keys(dim, num).tile((3, 1))
+    keys = keys[torch.randperm(len(keys), device=DEV)]
+    eng.insert_keys(keys)
+    assert eng.size() == num
+    indices, masks = eng.find(keys)
+    assert masks.sum() == 3 * num
+    uniq = torch.unique(indices, sorted=True)
+    assert len(uniq) == num and uniq.eq(torch.arange(num, device=DEV)).all()
+    # duplicates of a key all see the same index
+    order = torch.argsort(keys[:, 0].long(), stable=True)
+    assert (indices[order].view(num, 3) == indices[order].view(num, 3)[:, :1]).all()
+
+
+@pytest.mark.parametrize("dim", [1, 2, 3, 4])
+@pytest.mark.parametrize("num", [0, CAP])
+def test_items_and_state_dict(dim, num, tmp_path):
+    """unittests/test_engine.py:71-106 incl. the empty map."""
+    import warnings
+
+    from ash import ASHEngine
+
+    eng = ASHEngine(dim=dim, capacity=CAP, device=DEV)
+    keys = _diag_keys(dim, num)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        eng.insert_keys(keys)
+    active, idx = eng.items()
+    assert active.shape == (num, dim) and idx.shape == (num,)
+    assert torch.sort(active, dim=0)[0].eq(torch.sort(keys, dim=0)[0]).all()
+
+    path = tmp_path / "sd.pt"
+    torch.save(eng.state_dict(), path)
+    del eng
+    eng2 = ASHEngine(dim=dim, capacity=CAP, device=DEV)
+    eng2.load_state_dict(torch.load(path, map_location=DEV))
+    active2, idx2 = eng2.items()
+    assert len(active2) == num
+    assert torch.sort(active2, dim=0)[0].eq(torch.sort(keys, dim=0)[0]).all()
+    if num:
+        # the key -> index association survives the round trip
+        f_idx, f_m = eng2.find(active)
+        assert f_m.all() and (f_idx == idx).all()
+        # and the restored heap keeps handing out fresh indices after an erase
+        eng2.erase(keys[:10])
+        eng2.insert_keys(keys[:10])
+        i3, m3 = eng2.find(keys)
+        assert m3.all() and torch.unique(i3).numel() == num
+
+
+@pytest.mark.parametrize("dim,num,new_cap", [(1, CAP // 2, CAP // 2), (1, CAP, 2 * CAP), (3, CAP // 2, CAP // 2), (3, CAP, 2 * CAP)])
+def test_multivalue_and_resize(dim, num, new_cap):
+    """unittests/test_engine.py:121-159: int64 + float32 payloads, retrievable by index, surviving resize."""
+    from ash import ASHEngine
+
+    eng = ASHEngine(dim=dim, capacity=CAP, device=DEV)
+    old = {"0": torch.zeros(CAP, dim, dtype=torch.int64, device=DEV), "1": torch.zeros(CAP, dim, device=DEV)}
+    keys = _diag_keys(dim, num)
+    vals = {"0": keys.long() * 2, "1": keys.float() * 4}
+    eng.insert(keys, vals, old)
+    idx, m = eng.find(keys)
+    assert m.sum() == num
+    assert torch.eq(old["0"][idx], keys.long() * 2).all() and torch.allclose(old["1"][idx], keys.float() * 4)
+    new = {"0": torch.zeros(new_cap, dim, dtype=torch.int64, device=DEV), "1": torch.zeros(new_cap, dim, device=DEV)}
+    eng.resize(new_cap, old, new)
+    idx, m = eng.find(keys)
+    assert m.sum() == num
+    assert torch.eq(new["0"][idx], keys.long() * 2).all() and torch.allclose(new["1"][idx], keys.float() * 4)
+
+
+@pytest.mark.parametrize("value_dims", [3, [1, 3], {"sdf": 1, "rgb": 3}])
+def test_hashmap_values(value_dims):
+    """unittests/test_hashmap.py: int / list / dict value_dims; find(return_values), items, resize."""
+    from ash import HashMap
+
+    hm = HashMap(3, value_dims, 2000, DEV)
+    keys = _diag_keys(3, 1000)
+
+    def make(d):
+        return keys[:, :1].float().tile((1, d)) + 0.5
+
+    if isinstance(value_dims, int):
+        vals = make(value_dims)
+    elif isinstance(value_dims, list):
+        vals = [make(d) for d in value_dims]
+    else:
+        vals = {k: make(d) for k, d in value_dims.items()}
+    hm.insert(keys, vals)
+    masks, indices, got = hm.find(keys, return_values=True)
+    assert masks.all()
+
+    def flat(v):
+        return [v] if torch.is_tensor(v) else (list(v.values()) if isinstance(v, dict) else list(v))
+
+    for a, b in zip(flat(got), flat(vals)):
+        assert torch.equal(a, b)
+    ikeys, iidx, ivals = hm.items(return_values=True)
+    for a in flat(ivals):
+        assert torch.equal(a[:, 0], ikeys[:, 0].float() + 0.5)
+    hm.resize(4000)
+    masks, got = hm.find(keys, return_indices=False, return_values=True)
+    assert masks.all()
+    for a, b in zip(flat(got), flat(vals)):
+        assert torch.equal(a, b)
+    sd = hm.state_dict()
+    hm2 = HashMap(3, value_dims, 4000, DEV)
+    hm2.load_state_dict(sd)
+    masks, got = hm2.find(keys, return_indices=False, return_values=True)
+    assert masks.all()
+    for a, b in zip(flat(got), flat(vals)):
+        assert torch.equal(a, b)
+    hm2.clear()
+    assert hm2.size() == 0 and not hm2.find(keys)[0].any()
+
+
+def test_embedding_zero_for_missing():
+    """unittests/test_embedding.py:29-39."""
+    from ash import HashEmbedding
+
+    emb = HashEmbedding(3, 1000, 8, DEV)
+    keys = _diag_keys(3, 2000)
+    emb.spatial_init_(keys[:1000])
+    out = emb(keys)
+    assert out.shape == (2000, 8)
+    assert torch.count_nonzero(out[1000:]) == 0
+    out.sum().backward()
+    assert emb.embedding.grad is not None and torch.allclose(emb.embedding.grad, torch.ones_like(emb.embedding.grad))
+
+
+@pytest.mark.parametrize("dim", [1, 2, 3, 4])
+def test_oracle_parity_random_ops(dim):
+    """insert (with values) / find / erase / re-insert / items against the CPU oracle on
+    negative and positive random keys with duplicates; compared through key -> value
+    association, hit masks, sizes and sorted items.  The capacity exceeds every key ever
+    inserted: which keys an overfull map drops is order dependent and not comparable."""
+    cap = 200000
+    import __ash
+
+    heap = torch.arange(cap, dtype=torch.int32, device=DEV)
+    m = __ash.HashMap(dim, cap, heap, DEV)
+    om = oracle.OracleHashMap(dim, cap)
+    span = {1: 40000, 2: 300, 3: 40, 4: 16}[dim]
+
+    def value_of(k):  # a pure function of the key, so any duplicate winner is equal
+        k = k.astype(np.int64)
+        return (k * np.arange(1, dim + 1)).sum(axis=1, keepdims=True).astype(np.float32) * np.array([[1.0, -2.0, 0.5]], np.float32)
+
+    ext = torch.zeros(cap, 3, device=DEV)
+    oext = np.zeros((cap, 3), np.float32)
+    for rnd in range(4):
+        k = _rand_keys(30000, dim, -span, span, seed=100 * dim + rnd).numpy()
+        v = value_of(k)
+        m.insert(torch.from_numpy(k).to(DEV), {"v": torch.from_numpy(v).to(DEV)}, {"v": ext})
+        om.insert(k, {"v": v}, {"v": oext})
+        assert m.size() == om.size()
+        q = _rand_keys(40000, dim, -span - 5, span + 5, seed=999 + 100 * dim + rnd).numpy()
+        gi, gm = m.find(torch.from_numpy(q).to(DEV))
+        oi, omk = om.find(q)
+        assert np.array_equal(gm.cpu().numpy(), omk)
+        hit = torch.from_numpy(omk).to(DEV)
+        assert torch.equal(ext[gi[hit]].cpu(), torch.from_numpy(oext[oi[omk]]))
+        assert (gi[~hit] == 0).all()
+        e = _rand_keys(10000, dim, -span, span, seed=5000 + 100 * dim + rnd).numpy()
+        m.erase(torch.from_numpy(e).to(DEV))
+        om.erase(e)
+        assert m.size() == om.size()
+        gk, gidx = m.items()
+        ok, _ = om.items()
+        gk = gk.cpu().numpy()
+        assert np.array_equal(gk[np.lexsort(gk.T[::-1])], ok[np.lexsort(ok.T[::-1])])
+        assert torch.unique(gidx).numel() == len(gk)
+        assert torch.equal(ext[gidx].cpu(), torch.from_numpy(value_of(gk)))
+    assert m.status() == 0
+
+
+def test_capacity_overflow_is_reported_not_undefined():
+    import __ash
+
+    cap = 1000
+    heap = torch.arange(cap, dtype=torch.int32, device=DEV)
+    m = __ash.HashMap(3, cap, heap, DEV)
+    m.insert_keys(_diag_keys(3, 1500))
+    assert m.size() == cap
+    assert m.status() & __ash.STATUS_CAPACITY
+    idx, masks = m.find(_diag_keys(3, 1500))
+    assert masks.sum() == cap and torch.unique(idx[masks]).numel() == cap
+
+
+def test_empty_batches_and_errors():
+    import warnings
+
+    import __ash
+    from ash import ASHEngine
+
+    eng = ASHEngine(3, 100, DEV)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        idx, m = eng.find(torch.empty((0, 3), dtype=torch.int32, device=DEV))
+        eng.insert_keys(torch.empty((0, 3), dtype=torch.int32, device=DEV))
+        eng.erase(torch.empty((0, 3), dtype=torch.int32, device=DEV))
+    assert idx.shape == (0,) and m.shape == (0,) and eng.size() == 0
+    k, i = eng.items()
+    assert k.shape == (0, 3) and i.shape == (0,)
+    with pytest.raises(RuntimeError):
+        __ash.HashMap(5, 10, torch.arange(10, dtype=torch.int32, device=DEV), DEV)
+    with pytest.raises(RuntimeError):
+        __ash.HashMap(3, 10, torch.arange(10, dtype=torch.int32), torch.device("cpu"))

@@ -1,0 +1,462 @@
+"""``__ash`` -- the native module of torch-ash, re-implemented for B200.
+
+The reference builds a pybind11 extension of this name from ash/src
+(ash/src/pybind.cpp:8-38) and its Python layer imports it through
+``ash.common._get_c_extension``.  This module exports the same names with the
+same arguments and return values, but every operation is a call into
+``libashb200.so`` (hand-written sm_100a CUDA behind a C ABI, see
+include/ashb200.h).  It is the only place where torch tensors meet the C ABI:
+it allocates outputs with torch (caching allocator, current stream), passes raw
+device pointers and turns non-zero status codes into ``RuntimeError``.
+
+There is no CPU path: tensors must live on a CUDA device and the shared library
+must have been built (``python torch-ash_b200/build.py``).
+"""
+import ctypes
+import os
+import warnings
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libashb200.so")
+
+if not os.path.exists(_LIB_PATH):
+    raise ImportError(
+        f"{_LIB_PATH} is missing: build it with `python {os.path.join(_HERE, 'build.py')}` "
+        "(needs nvcc; there is no CPU fallback)"
+    )
+
+_lib = ctypes.CDLL(_LIB_PATH)
+_c = ctypes
+_vp, _i64, _int = _c.c_void_p, _c.c_int64, _c.c_int
+
+_lib.ashb_last_error_string.restype = _c.c_char_p
+_lib.ashb_map_create.argtypes = [_int, _i64, _vp, _int, _c.POINTER(_vp)]
+_lib.ashb_map_destroy.argtypes = [_vp]
+_lib.ashb_map_clear.argtypes = [_vp, _vp]
+_lib.ashb_map_size.argtypes = [_vp, _vp, _c.POINTER(_i64)]
+_lib.ashb_map_status.argtypes = [_vp, _vp, _c.POINTER(_c.c_uint32)]
+_lib.ashb_map_find.argtypes = [_vp, _vp, _i64, _vp, _vp, _vp]
+_lib.ashb_map_insert_keys.argtypes = [_vp, _vp, _i64, _vp]
+_lib.ashb_map_insert_values.argtypes = [_vp, _vp, _i64, _int, _vp, _vp, _vp, _vp]
+_lib.ashb_map_erase.argtypes = [_vp, _vp, _i64, _vp]
+_lib.ashb_map_items.argtypes = [_vp, _vp, _vp, _i64, _c.POINTER(_i64), _vp]
+_lib.ashb_map_load_states.argtypes = [_vp, _vp, _vp, _i64, _vp, _vp]
+_lib.ashb_query_forward.argtypes = [_int, _int] + [_vp] * 9 + [_i64] * 4 + [_vp]
+_lib.ashb_query_backward_forward.argtypes = [_int, _int] + [_vp] * 11 + [_int] + [_i64] * 4 + [_vp]
+_lib.ashb_query_backward_backward.argtypes = [_int, _int] + [_vp] * 12 + [_int] + [_i64] * 4 + [_vp]
+_f32 = _c.c_float
+_lib.ashb_conv_forward.argtypes = [_int] + [_vp] * 9 + [_int] + [_i64] * 6 + [_vp]
+_lib.ashb_ray_find_near_far.argtypes = [_vp] * 7 + [_f32] * 4 + [_i64, _vp]
+_lib.ashb_ray_sample_count.argtypes = [_vp] * 6 + [_i64, _f32, _i64, _vp]
+_lib.ashb_ray_sample_fill.argtypes = [_vp] * 9 + [_i64, _f32, _i64, _vp]
+_lib.ashb_tsdf_touch.argtypes = [_vp, _vp, _int, _int, _vp, _vp, _f32, _f32, _vp, _int, _int, _vp, _vp, _vp, _vp,
+                                 _c.c_uint32, _vp]
+_lib.ashb_tsdf_integrate.argtypes = [_vp, _i64, _int, _i64, _vp, _vp, _c.c_uint32, _vp, _vp, _int, _int, _vp, _vp,
+                                     _f32, _f32, _vp, _f32, _int, _int, _int, _vp, _vp]
+
+STATUS_CAPACITY, STATUS_PROBE, STATUS_SPIN, STATUS_DUPLICATE = 1, 2, 4, 8
+_DTYPES = {torch.float32: 0, torch.float64: 1}
+_INTERP = {"linear": 0, "smooth_step": 1}
+
+
+def _check(rc: int):
+    if rc != 0:
+        raise RuntimeError(f"libashb200: {_lib.ashb_last_error_string().decode()} (status {rc})")
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _cuda(t: torch.Tensor, name: str, dtype=None) -> torch.Tensor:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor (there is no CPU implementation), got {t.device}")
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError(f"{name} must be {dtype}, got {t.dtype}")
+    return t.contiguous()
+
+
+def _interp_code(name: str) -> int:
+    try:
+        return _INTERP[name]
+    except KeyError:
+        raise RuntimeError(f"Unknown interpolation functor: {name}") from None  # ash/src/grid.cu:61
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise RuntimeError(f"embeddings must be float32 or float64, got {t.dtype}") from None
+
+
+class HashMap:
+    """Key (int32 x key_dim) -> index map; replaces ash/src/hashmap.h:18-61.
+
+    ``heap`` is the caller's int32 free-index stack; it is aliased and mutated
+    in place for the life of the map (it is part of the checkpoint,
+    ash/core.py:72-74).
+    """
+
+    def __init__(self, key_dim: int, capacity: int, heap: torch.Tensor, device):
+        device = torch.device(device)
+        if device.type != "cuda":
+            raise RuntimeError(f"HashMap needs a CUDA device (there is no CPU implementation), got {device}")
+        if device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        if heap.device != device or heap.dtype != torch.int32 or not heap.is_contiguous() or heap.numel() != capacity:
+            raise RuntimeError("heap must be a contiguous int32 tensor of `capacity` elements on the map's device")
+        self._device = device
+        self._key_dim = int(key_dim)
+        self._capacity = int(capacity)
+        self._heap = heap
+        handle = _vp()
+        # make sure the heap's initial contents are complete before the library touches it
+        torch.cuda.current_stream(device).synchronize()
+        _check(_lib.ashb_map_create(self._key_dim, self._capacity, heap.data_ptr(), device.index, _c.byref(handle)))
+        self._h = handle
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            self._h = None
+            try:
+                torch.cuda.synchronize(self._device)
+            except Exception:  # interpreter shutdown
+                pass
+            if _lib is not None:  # None once the interpreter is tearing modules down
+                _lib.ashb_map_destroy(h)
+
+    # -- helpers
+    def _keys(self, keys: torch.Tensor) -> torch.Tensor:
+        if keys.dim() != 2 or keys.shape[1] != self._key_dim:
+            raise RuntimeError(f"keys must be (N, {self._key_dim}), got {tuple(keys.shape)}")
+        # erase() receives unconverted keys from the reference's engine (ash/core.py:256)
+        return keys.to(self._device, torch.int32).contiguous()
+
+    def _raise_status(self, where: str):
+        st = _c.c_uint32()
+        _check(_lib.ashb_map_status(self._h, _stream(self._device), _c.byref(st)))
+        if st.value & STATUS_CAPACITY:
+            warnings.warn(
+                f"{where}: more distinct keys than the capacity {self._capacity}; the excess keys were dropped"
+            )
+        if st.value & (STATUS_PROBE | STATUS_SPIN | STATUS_DUPLICATE):
+            raise RuntimeError(f"{where}: hash table status 0x{st.value:x}")
+
+    # -- the reference's interface
+    def find(self, keys: torch.Tensor):
+        keys = self._keys(keys)
+        n = keys.shape[0]
+        indices = torch.empty(n, dtype=torch.int64, device=self._device)
+        masks = torch.empty(n, dtype=torch.bool, device=self._device)
+        _check(_lib.ashb_map_find(self._h, keys.data_ptr(), n, indices.data_ptr(), masks.data_ptr(), _stream(self._device)))
+        return indices, masks
+
+    def insert_keys(self, keys: torch.Tensor) -> None:
+        keys = self._keys(keys)
+        _check(_lib.ashb_map_insert_keys(self._h, keys.data_ptr(), keys.shape[0], _stream(self._device)))
+
+    def insert(self, keys: torch.Tensor, values: dict, external_values: dict) -> None:
+        keys = self._keys(keys)
+        names = list(values.keys())
+        k = len(names)
+        src = (_vp * max(k, 1))()
+        dst = (_vp * max(k, 1))()
+        row = (_i64 * max(k, 1))()
+        keep = []
+        for j, name in enumerate(names):
+            v = _cuda(values[name], f"values[{name!r}]")
+            e = external_values[name]
+            if not e.is_cuda or not e.is_contiguous() or e.dtype != v.dtype or e.shape[1:] != v.shape[1:]:
+                raise RuntimeError(f"external_values[{name!r}] must be a contiguous CUDA tensor matching values")
+            if v.shape[0] != keys.shape[0] or e.shape[0] != self._capacity:
+                raise RuntimeError(f"value {name!r}: row counts do not match keys / capacity")
+            keep.append(v)
+            src[j], dst[j] = v.data_ptr(), e.data_ptr()
+            row[j] = (v.numel() // max(v.shape[0], 1)) * v.element_size()
+        _check(
+            _lib.ashb_map_insert_values(self._h, keys.data_ptr(), keys.shape[0], k, src, dst, row, _stream(self._device))
+        )
+
+    def erase(self, keys: torch.Tensor) -> None:
+        keys = self._keys(keys)
+        _check(_lib.ashb_map_erase(self._h, keys.data_ptr(), keys.shape[0], _stream(self._device)))
+
+    def clear(self) -> None:
+        _check(_lib.ashb_map_clear(self._h, _stream(self._device)))
+
+    def load_states(self, states: dict) -> None:
+        keys = self._keys(states["active_keys"])
+        indices = states["active_indices"].to(self._device, torch.int64).contiguous()
+        heap = states["heap"].to(self._device, torch.int32).contiguous()
+        if heap.numel() != self._capacity or indices.numel() != keys.shape[0]:
+            raise RuntimeError("load_states: heap / indices sizes do not match the map")
+        _check(
+            _lib.ashb_map_load_states(
+                self._h, keys.data_ptr(), indices.data_ptr(), keys.shape[0], heap.data_ptr(), _stream(self._device)
+            )
+        )
+        self._raise_status("load_states")
+
+    def items(self):
+        n = self.size()
+        keys = torch.empty((n, self._key_dim), dtype=torch.int32, device=self._device)
+        indices = torch.empty(n, dtype=torch.int64, device=self._device)
+        got = _i64()
+        _check(
+            _lib.ashb_map_items(self._h, keys.data_ptr(), indices.data_ptr(), n, _c.byref(got), _stream(self._device))
+        )
+        if got.value != n:
+            raise RuntimeError(f"items(): enumerated {got.value} entries but size() is {n}")
+        return keys, indices
+
+    def size(self) -> int:
+        out = _i64()
+        _check(_lib.ashb_map_size(self._h, _stream(self._device), _c.byref(out)))
+        return int(out.value)
+
+    def device(self) -> torch.device:
+        return self._device
+
+    # -- additions (no counterpart in the reference)
+    def status(self) -> int:
+        """Read and clear the device status word (STATUS_* bits)."""
+        st = _c.c_uint32()
+        _check(_lib.ashb_map_status(self._h, _stream(self._device), _c.byref(st)))
+        return int(st.value)
+
+    @property
+    def handle(self) -> int:
+        return self._h.value
+
+
+def _query_args(embeddings, offsets, grid_indices, cell_indices, masks, g2g, c2c, c2g):
+    emb = _cuda(embeddings, "embeddings")
+    if emb.dim() != 3:
+        raise RuntimeError("embeddings must be (num_embeddings, cells_per_grid, embedding_dim)")
+    dev = emb.device
+    off = _cuda(offsets.to(dev), "offsets", torch.float32)  # ash/src/grid.cu:71: offsets are always float32
+    gi = _cuda(grid_indices.to(dev), "grid_indices", torch.int64).view(-1)
+    ci = _cuda(cell_indices.to(dev), "cell_indices", torch.int64).view(-1)
+    mk = _cuda(masks.to(dev), "masks", torch.bool).view(-1)
+    n = gi.shape[0]
+    if off.shape != (n, 3) or ci.shape[0] != n or mk.shape[0] != n:
+        raise RuntimeError("offsets / grid_indices / cell_indices / masks disagree on the number of queries")
+    g2g = _cuda(g2g, "lut_grid_nb2grid_idx", torch.int64)
+    c2c = _cuda(c2c, "lut_cell_nb2cell_idx", torch.int64)
+    c2g = _cuda(c2g, "lut_cell_nb2grid_nb", torch.int64)
+    if g2g.shape != (emb.shape[0], 8) or c2c.shape != (emb.shape[1], 8) or c2g.shape != (emb.shape[1], 8):
+        raise RuntimeError("neighbour lookup tables must be (num_embeddings, 8) and (cells_per_grid, 8)")
+    return emb, off, gi, ci, mk, g2g, c2c, c2g, n
+
+
+def query_forward(embeddings, offsets, grid_indices, cell_indices, masks, lut_grid_nb2grid_idx,
+                  lut_cell_nb2cell_idx, lut_cell_nb2grid_nb, grid_dim, interpolation):
+    """ash/src/grid.cu:134-175."""
+    emb, off, gi, ci, mk, g2g, c2c, c2g, n = _query_args(
+        embeddings, offsets, grid_indices, cell_indices, masks, lut_grid_nb2grid_idx, lut_cell_nb2cell_idx,
+        lut_cell_nb2grid_nb)
+    out = torch.empty((n, emb.shape[2]), dtype=emb.dtype, device=emb.device)
+    with torch.cuda.device(emb.device):
+        _check(_lib.ashb_query_forward(
+            _dtype_code(emb), _interp_code(interpolation), emb.data_ptr(), off.data_ptr(), gi.data_ptr(),
+            ci.data_ptr(), mk.data_ptr(), g2g.data_ptr(), c2c.data_ptr(), c2g.data_ptr(), out.data_ptr(), n,
+            emb.shape[0], emb.shape[1], emb.shape[2], _stream(emb.device)))
+    return out
+
+
+def query_backward_forward(z, embeddings, offsets, grid_indices, cell_indices, masks, lut_grid_nb2grid_idx,
+                           lut_cell_nb2cell_idx, lut_cell_nb2grid_nb, grid_dim, interpolation,
+                           grad_embeddings_out=None):
+    """ash/src/grid.cu:257-307.  Returns (grad_embeddings, grad_offsets).
+
+    ``grad_embeddings_out`` (an addition): accumulate into this existing tensor
+    instead of allocating and zero-filling a fresh table-sized gradient.
+    """
+    emb, off, gi, ci, mk, g2g, c2c, c2g, n = _query_args(
+        embeddings, offsets, grid_indices, cell_indices, masks, lut_grid_nb2grid_idx, lut_cell_nb2cell_idx,
+        lut_cell_nb2grid_nb)
+    z = _cuda(z, "z", emb.dtype)
+    if z.shape != (n, emb.shape[2]):
+        raise RuntimeError("z must be (num_queries, embedding_dim)")
+    if grad_embeddings_out is None:
+        grad_emb, zero = torch.empty_like(emb), 1
+    else:
+        grad_emb, zero = grad_embeddings_out, 0
+        if grad_emb.shape != emb.shape or grad_emb.dtype != emb.dtype or not grad_emb.is_contiguous():
+            raise RuntimeError("grad_embeddings_out must match embeddings")
+    grad_off = torch.empty((n, 3), dtype=emb.dtype, device=emb.device)  # ash/src/grid.cu:277
+    with torch.cuda.device(emb.device):
+        _check(_lib.ashb_query_backward_forward(
+            _dtype_code(emb), _interp_code(interpolation), z.data_ptr(), emb.data_ptr(), off.data_ptr(),
+            gi.data_ptr(), ci.data_ptr(), mk.data_ptr(), g2g.data_ptr(), c2c.data_ptr(), c2g.data_ptr(),
+            grad_emb.data_ptr(), grad_off.data_ptr(), zero, n, emb.shape[0], emb.shape[1], emb.shape[2],
+            _stream(emb.device)))
+    return grad_emb, grad_off
+
+
+def query_backward_backward(grad_grad_embeddings, grad_grad_offsets, z, embeddings, offsets, grid_indices,
+                            cell_indices, masks, lut_grid_nb2grid_idx, lut_cell_nb2cell_idx, lut_cell_nb2grid_nb,
+                            grid_dim, interpolation, grad_embeddings_out=None):
+    """ash/src/grid.cu:389-451.  Returns (grad_z, grad_embeddings, grad_offsets).
+
+    ``grad_grad_embeddings`` is accepted and unused, and the returned
+    grad_offsets is all zeros, exactly as in the reference (grid.cu:417-418, :426).
+    """
+    emb, off, gi, ci, mk, g2g, c2c, c2g, n = _query_args(
+        embeddings, offsets, grid_indices, cell_indices, masks, lut_grid_nb2grid_idx, lut_cell_nb2cell_idx,
+        lut_cell_nb2grid_nb)
+    z = _cuda(z, "z", emb.dtype)
+    ggo = _cuda(grad_grad_offsets, "grad_grad_offsets", emb.dtype)
+    if z.shape != (n, emb.shape[2]) or ggo.shape != (n, 3):
+        raise RuntimeError("z must be (num_queries, embedding_dim) and grad_grad_offsets (num_queries, 3)")
+    if grad_embeddings_out is None:
+        grad_emb, zero = torch.empty_like(emb), 1
+    else:
+        grad_emb, zero = grad_embeddings_out, 0
+    grad_z = torch.empty_like(z)
+    with torch.cuda.device(emb.device):
+        _check(_lib.ashb_query_backward_backward(
+            _dtype_code(emb), _interp_code(interpolation), ggo.data_ptr(), z.data_ptr(), emb.data_ptr(),
+            off.data_ptr(), gi.data_ptr(), ci.data_ptr(), mk.data_ptr(), g2g.data_ptr(), c2c.data_ptr(),
+            c2g.data_ptr(), grad_z.data_ptr(), grad_emb.data_ptr(), zero, n, emb.shape[0], emb.shape[1],
+            emb.shape[2], _stream(emb.device)))
+    grad_off = torch.zeros((n, 3), dtype=emb.dtype, device=emb.device)
+    return grad_z, grad_emb, grad_off
+
+
+def convolution_forward(inputs, weights, masks, grid_indices, cell_indices, lut_grid_nb2grid_idx,
+                        lut_cell_nb2cell_idx, lut_cell_nb2grid_nb, grid_dim):
+    """ash/src/grid.cu:1006-1043.  ``masks`` is indexed flat over (listed block, cell)."""
+    inp = _cuda(inputs, "inputs")
+    dev = inp.device
+    w = _cuda(weights, "weights", inp.dtype)
+    mk = _cuda(masks, "masks", torch.bool).view(-1)
+    gi = _cuda(grid_indices, "grid_indices", torch.int64).view(-1)
+    ci = _cuda(cell_indices, "cell_indices", torch.int64).view(-1)
+    g2g = _cuda(lut_grid_nb2grid_idx, "lut_grid_nb2grid_idx", torch.int64)
+    c2c = _cuda(lut_cell_nb2cell_idx, "lut_cell_nb2cell_idx", torch.int64)
+    c2g = _cuda(lut_cell_nb2grid_nb, "lut_cell_nb2grid_nb", torch.int64)
+    n_emb, cells, D = inp.shape
+    if ci.shape[0] != cells or c2c.shape != c2g.shape or c2c.shape[0] != cells or g2g.shape[0] != n_emb:
+        raise RuntimeError("convolution_forward: lookup table shapes do not match the inputs")
+    if w.shape != (c2c.shape[1], D) or mk.numel() < gi.shape[0] * cells:
+        raise RuntimeError("convolution_forward: weights must be (window taps, channels) and masks cover every cell")
+    out = torch.empty_like(inp)
+    with torch.cuda.device(dev):
+        _check(_lib.ashb_conv_forward(
+            _dtype_code(inp), inp.data_ptr(), w.data_ptr(), mk.data_ptr(), gi.data_ptr(), ci.data_ptr(),
+            g2g.data_ptr(), c2c.data_ptr(), c2g.data_ptr(), out.data_ptr(), 1, gi.shape[0], n_emb, cells, D,
+            c2c.shape[1], g2g.shape[1], _stream(dev)))
+    return out
+
+
+def _rays(hashmap, ray_origins, ray_directions):
+    if not isinstance(hashmap, HashMap):
+        raise RuntimeError("hashmap is not a GPU hashmap of type <int, 3>, ray sample not supported")
+    dev = hashmap.device()
+    o = _cuda(ray_origins.to(dev), "ray_origins", torch.float32)
+    d = _cuda(ray_directions.to(dev), "ray_directions", torch.float32)
+    if o.dim() != 2 or o.shape[1] != 3 or d.shape != o.shape:
+        raise RuntimeError("ray origins and directions must both be (N, 3)")
+    return dev, o, d
+
+
+def _per_ray(v, n, dev, name):
+    """A per-ray float32 tensor from a tensor or a scalar."""
+    if not torch.is_tensor(v):
+        return torch.full((n,), float(v), dtype=torch.float32, device=dev)
+    v = v.to(dev, torch.float32)
+    return (v.expand(n) if v.dim() == 0 else v.reshape(-1)).contiguous()
+
+
+def ray_find_near_far(hashmap, ray_origins, ray_directions, bbox_min, bbox_max, t_min, t_max, t_step,
+                      grid2cell_multiplier):
+    """ash/src/sampler.cu:73-121.  Returns (ray_nears, ray_fars) float32 (N,)."""
+    dev, o, d = _rays(hashmap, ray_origins, ray_directions)
+    n = o.shape[0]
+    lo = _cuda(bbox_min.to(dev, torch.float32), "bbox_min").view(-1)
+    hi = _cuda(bbox_max.to(dev, torch.float32), "bbox_max").view(-1)
+    nears = torch.empty(n, dtype=torch.float32, device=dev)
+    fars = torch.empty(n, dtype=torch.float32, device=dev)
+    _check(_lib.ashb_ray_find_near_far(
+        hashmap._h, o.data_ptr(), d.data_ptr(), lo.data_ptr(), hi.data_ptr(), nears.data_ptr(), fars.data_ptr(),
+        float(t_min), float(t_max), float(t_step), float(grid2cell_multiplier), n, _stream(dev)))
+    return nears, fars
+
+
+def ray_sample(hashmap, ray_origins, ray_directions, ray_nears, ray_fars, bbox_min, bbox_max,
+               max_samples_per_ray, grid2cell_multiplier):
+    """ash/src/sampler.cu:217-294.  Returns (ray_indices int64 (M,), t_nears (M,), t_fars (M,),
+    inclusive prefix sum of samples per ray int64 (N,)).  The bbox is unused, as in the reference."""
+    dev, o, d = _rays(hashmap, ray_origins, ray_directions)
+    n = o.shape[0]
+    nears = _per_ray(ray_nears, n, dev, "ray_nears")
+    fars = _per_ray(ray_fars, n, dev, "ray_fars")
+    counts = torch.empty(n, dtype=torch.int64, device=dev)
+    st = _stream(dev)
+    g2c = float(grid2cell_multiplier)
+    _check(_lib.ashb_ray_sample_count(
+        hashmap._h, o.data_ptr(), d.data_ptr(), nears.data_ptr(), fars.data_ptr(), counts.data_ptr(),
+        int(max_samples_per_ray), g2c, n, st))
+    prefix = torch.cumsum(counts, 0)
+    total = int(prefix[-1].item()) if n else 0
+    ray_indices = torch.empty(total, dtype=torch.int64, device=dev)
+    t_nears = torch.empty(total, dtype=torch.float32, device=dev)
+    t_fars = torch.empty(total, dtype=torch.float32, device=dev)
+    if total:
+        _check(_lib.ashb_ray_sample_fill(
+            hashmap._h, o.data_ptr(), d.data_ptr(), nears.data_ptr(), fars.data_ptr(), prefix.data_ptr(),
+            ray_indices.data_ptr(), t_nears.data_ptr(), t_fars.data_ptr(), int(max_samples_per_ray), g2c, n, st))
+    return ray_indices, t_nears, t_fars, prefix
+
+
+def _host_floats(values, n):
+    arr = (_f32 * n)(*[float(v) for v in values])
+    return arr
+
+
+def tsdf_touch(hashmap, depth, intrinsic, cam_to_world, depth_max, cell_size, origin, grid_dim, dilation,
+               grid_coords, touched, stamp, bound_lo=None, bound_hi=None):
+    """Allocate and stamp the blocks seen by a depth frame (no counterpart in the reference's
+    native module; replaces the allocation half of demo/rgbd_fusion.py:199-224).
+    ``intrinsic`` (3,3), ``cam_to_world`` (>=3,4) and ``origin`` (3,) are host values."""
+    dev = hashmap.device()
+    depth = _cuda(depth, "depth", torch.float32)
+    if depth.dim() != 2 or grid_coords.dtype != torch.int32 or touched.dtype != torch.int32:
+        raise RuntimeError("depth must be (H, W); grid_coords and touched must be int32")
+    H, W = depth.shape
+    K = _host_floats([intrinsic[i][j] for i in range(3) for j in range(3)], 9)
+    Ei = _host_floats([cam_to_world[i][j] for i in range(3) for j in range(4)], 12)
+    org = _host_floats(origin, 3)
+    lo = (_c.c_int32 * 3)(*bound_lo) if bound_lo is not None else None
+    hi = (_c.c_int32 * 3)(*bound_hi) if bound_hi is not None else None
+    _check(_lib.ashb_tsdf_touch(
+        hashmap._h, depth.data_ptr(), H, W, K, Ei, float(depth_max), float(cell_size), org, int(grid_dim),
+        int(dilation), lo, hi, grid_coords.data_ptr(), touched.data_ptr(), int(stamp), _stream(dev)))
+
+
+def tsdf_integrate(embeddings, grid_dim, grid_coords, touched, stamp, depth, color, intrinsic, world_to_cam,
+                   depth_max, cell_size, origin, trunc, sdf_channel=0, rgb_channel=1, weight_channel=4,
+                   counter=None):
+    """Fuse a frame into every stamped block in place (replaces demo/rgbd_fusion.py:226-254)."""
+    emb = embeddings
+    if not emb.is_cuda or emb.dtype != torch.float32 or not emb.is_contiguous() or emb.dim() != 3:
+        raise RuntimeError("embeddings must be a contiguous float32 CUDA tensor (blocks, cells, channels)")
+    depth = _cuda(depth, "depth", torch.float32)
+    color = _cuda(color, "color", torch.float32)
+    H, W = depth.shape
+    if color.shape != (H, W, 3):
+        raise RuntimeError("color must be (H, W, 3)")
+    K = _host_floats([intrinsic[i][j] for i in range(3) for j in range(3)], 9)
+    E = _host_floats([world_to_cam[i][j] for i in range(3) for j in range(4)], 12)
+    org = _host_floats(origin, 3)
+    with torch.cuda.device(emb.device):
+        _check(_lib.ashb_tsdf_integrate(
+            emb.data_ptr(), emb.shape[0], int(grid_dim), emb.shape[2], grid_coords.data_ptr(), touched.data_ptr(),
+            int(stamp), depth.data_ptr(), color.data_ptr(), H, W, K, E, float(depth_max), float(cell_size), org,
+            float(trunc), int(sdf_channel), int(rgb_channel), int(weight_channel),
+            counter.data_ptr() if counter is not None else None, _stream(emb.device)))

@@ -1,0 +1,66 @@
+"""RGB-D TSDF fusion into a sparse-dense grid (API of the reference demo's TSDFFusion).
+
+The reference implements one frame of fusion in Python (demo/rgbd_fusion.py:199-254):
+unproject the depth image, ``spatial_init_`` the blocks around the points (temporary hash
+set, insert, find), build every cell position of the touched blocks, project them back into
+the frame, gather depth and colour, and update the running weighted averages -- about forty
+torch launches and several multi-megabyte temporaries per frame.  Here a frame is two CUDA
+launches (``tsdf_touch`` + ``tsdf_integrate``) with no temporaries and no host round trip.
+
+Embedding layout as in the demo (:239-241): channel 0 sdf, 1..3 rgb, 4 weight.
+"""
+from typing import Union
+
+import torch
+
+from .common import _get_c_extension
+from .grid import BoundedSparseDenseGrid, UnBoundedSparseDenseGrid
+
+backend = _get_c_extension()
+
+
+class TSDFFusion:
+    def __init__(self, grid: Union[UnBoundedSparseDenseGrid, BoundedSparseDenseGrid], dilation: int):
+        assert grid.embedding_dim >= 5, "embeddings must hold sdf(1) + rgb(3) + weight(1)"
+        self.grid = grid
+        self.voxel_size = grid.cell_size
+        self.dilation = dilation
+        self.trunc = dilation * self.voxel_size * grid.grid_dim  # demo/rgbd_fusion.py:44
+        dev = grid.device
+        # per-block scratch kept across frames: coordinate of each block and the last frame
+        # (stamp) that touched it
+        self._coords = torch.zeros((grid.num_embeddings, 3), dtype=torch.int32, device=dev)
+        self._touched = torch.zeros(grid.num_embeddings, dtype=torch.int32, device=dev)
+        self._stamp = 0
+        if isinstance(grid, BoundedSparseDenseGrid):
+            self._origin = [float(v) for v in grid.bbox_min.tolist()]
+            self._bounds = ([0, 0, 0], [grid.sparse_grid_dim] * 3)
+        else:
+            self._origin = [0.0, 0.0, 0.0]
+            self._bounds = (None, None)
+
+    @torch.no_grad()
+    def fuse_frame(self, datum) -> None:
+        """``datum``: depth (H, W) raw, depth_scale, depth_max, intrinsic (3, 3), extrinsic (4, 4)
+        world -> camera, rgb (H, W, 3); as demo/rgbd_fusion.py:199-254 (``datum.depth`` is scaled to
+        metres in place there too)."""
+        datum.depth *= datum.depth_scale
+        depth = datum.depth
+        K = torch.as_tensor(datum.intrinsic).double().cpu()
+        E = torch.as_tensor(datum.extrinsic).double().cpu()
+        Ei = torch.linalg.inv(E)
+        self._stamp = self._stamp % 0x7FFFFFFF + 1
+        g = self.grid
+        backend.tsdf_touch(
+            g.engine.backend, depth, K.tolist(), Ei.tolist(), datum.depth_max, g.cell_size, self._origin,
+            g.grid_dim, self.dilation, self._coords, self._touched, self._stamp, *self._bounds)
+        backend.tsdf_integrate(
+            g.embeddings.data, g.grid_dim, self._coords, self._touched, self._stamp, depth, datum.rgb, K.tolist(),
+            E.tolist(), datum.depth_max, g.cell_size, self._origin, self.trunc)
+        # the engine's host-side size bound is stale after native insertions
+        g.engine._size_bound = g.engine.capacity
+
+    @torch.no_grad()
+    def fuse_dataset(self, frames) -> None:
+        for datum in frames:
+            self.fuse_frame(datum)

@@ -1,0 +1,337 @@
+"""Sparse-dense grids: hashed blocks of G^3 dense cells (API of ash/grid.py).
+
+``embeddings`` is a ``(num_embeddings, G**3, embedding_dim)`` parameter; block
+``b`` of it belongs to the integer block coordinate the hash engine maps to
+``b``.  A position ``x`` (in cell units) lives in block ``floor(x / G)``, cell
+``x - G * block`` (linearised x fastest) at fractional ``offset``.  Class,
+method and argument names follow ash/grid.py:28-863.
+"""
+from typing import Literal, Optional, Tuple, Union
+
+import torch
+import torch.nn as nn
+
+from .common import _get_c_extension
+from .core import ASHEngine, ASHModule, _as_device
+from .grid_nns import enumerate_neighbor_coord_offsets
+from .grid_query import SparseDenseGridQuery
+from .hashmap import HashSet
+
+backend = _get_c_extension()
+
+
+class SparseDenseGrid(ASHModule):
+    """Sparse grid of dense ``grid_dim``^3 blocks, positions measured in cells."""
+
+    def __init__(self, in_dim: int, num_embeddings: int, embedding_dim: int, grid_dim: int,
+                 device: Optional[Union[str, torch.device]] = torch.device("cpu")):
+        assert in_dim == 3, "Only 3D sparse-dense grid is supported for now."
+        assert embedding_dim <= 16, "Embedding dim must be <= 16 for now."
+        super().__init__()
+        self.in_dim = in_dim
+        self.num_embeddings = num_embeddings
+        self.embedding_dim = embedding_dim
+        self.grid_dim = grid_dim
+        self.device = _as_device(device)
+        self.num_cells_per_grid = grid_dim**in_dim
+
+        self.transform_world_to_cell = lambda x: x
+        self.transform_cell_to_world = lambda x: x
+
+        self.engine = ASHEngine(in_dim, num_embeddings, self.device)
+        self.embeddings = nn.Parameter(
+            torch.zeros(num_embeddings, self.num_cells_per_grid, embedding_dim, device=self.device))
+
+        # Dense (per-cell) structure is fixed by grid_dim and built once.
+        self.cell_indices = torch.arange(self.num_cells_per_grid, dtype=torch.long, device=self.device)
+        self.cell_coords = self._delinearize_cell_indices(self.cell_indices)
+        self.lut_cell_nb2grid_nb, self.lut_cell_nb2cell_idx = self.construct_cell_neighbor_lut(
+            radius=1, bidirectional=False)
+
+        # Sparse (per-block) structure depends on the active set; built on demand.
+        self.grid_indices = None
+        self.grid_coords = None
+        self.lut_grid_nb2grid_idx = None
+
+    # ------------------------------------------------------------------ allocation
+    def spatial_init_(self, points: torch.Tensor, dilation: int = 1, bidirectional: bool = False):
+        """Activate the blocks around ``points`` (world units), ash/grid.py:121-159.
+
+        Returns ``(grid_coords (n,1,3) int32, cell_coords (1,G^3,3) int32, grid_indices (n,1)
+        int64, cell_indices (1,G^3) int64)`` of the touched blocks, new or not.
+        """
+        points = self.transform_world_to_cell(points)
+        block = self.grids_in_bound(torch.floor(points / self.grid_dim).int())
+        offsets, _ = enumerate_neighbor_coord_offsets(self.in_dim, dilation, bidirectional, self.device)
+        candidates = (block.view(-1, 1, self.in_dim) + offsets.int().view(1, -1, self.in_dim)).view(-1, self.in_dim)
+        candidates = self.grids_in_bound(candidates)
+
+        # Deduplicate through a scratch hash set sized for the worst case (every
+        # candidate distinct); the reference sizes it by the point count and leans
+        # on duplicates (ash/grid.py:145), which can overflow.
+        if candidates.shape[0] == 0:
+            unique = candidates
+            grid_indices = torch.empty(0, dtype=torch.long, device=self.device)
+        else:
+            scratch = HashSet(key_dim=self.in_dim, capacity=candidates.shape[0], device=self.device)
+            scratch.insert(candidates)
+            unique = scratch.keys()
+            self.engine.insert_keys(unique)
+            grid_indices, masks = self.engine.find(unique)
+            assert masks.all(), "grid capacity exhausted during spatial_init_"
+        return (
+            unique.view(-1, 1, self.in_dim),
+            self.cell_coords.view(1, -1, self.in_dim),
+            grid_indices.view(-1, 1),
+            self.cell_indices.view(1, -1),
+        )
+
+    def ray_init_(self, ray_o, rays_d, rays_near, rays_far, dilation: int = 3) -> None:
+        raise NotImplementedError("Ray-tracing initialization not implemented yet")
+
+    # ------------------------------------------------------------------ query
+    def query(self, x: torch.Tensor):
+        """Split cell-unit positions into ``(grid_indices, cell_indices, offsets, masks)``
+        (ash/grid.py:183-199)."""
+        G = self.grid_dim
+        block = (x / G).floor()
+        local = x - block * G
+        cell = local.floor()
+        offsets = local - cell
+        grid_indices, masks = self.engine.find(block.int())
+        # `local` can round up to exactly G for tiny negative x; keep the cell in range.
+        cell_indices = self._linearize_cell_coords(cell.int().clamp_(0, G - 1))
+        return grid_indices, cell_indices, offsets, masks
+
+    def forward(self, x: torch.Tensor, interpolation: Literal["nearest", "linear", "smooth_step"] = "smooth_step"):
+        """Differentiable query at world positions ``x`` (N, 3): returns
+        ``(features (N, embedding_dim), masks (N,))``; ash/grid.py:201-238."""
+        x = self.transform_world_to_cell(x)
+        grid_indices, cell_indices, offsets, masks = self.query(x)
+
+        if interpolation == "nearest":
+            return self.embeddings[grid_indices, cell_indices], masks
+        if interpolation not in ("linear", "smooth_step"):
+            raise ValueError(f"Unknown interpolation: {interpolation}")
+
+        if self.grid_coords is None or self.lut_grid_nb2grid_idx is None:
+            self.construct_grid_neighbor_lut_(radius=1, bidirectional=False)
+        features = SparseDenseGridQuery.apply(
+            self.embeddings, offsets, grid_indices, cell_indices, masks, self.lut_grid_nb2grid_idx,
+            self.lut_cell_nb2cell_idx, self.lut_cell_nb2grid_nb, self.grid_dim, interpolation)
+        return features, masks
+
+    def items(self):
+        """Active blocks in broadcastable form: ``(grid_coords (n,1,3), cell_coords (1,G^3,3),
+        grid_indices (n,1), cell_indices (1,G^3))``; cell position = grid_coords * G + cell_coords,
+        features = embeddings[grid_indices, cell_indices] (ash/grid.py:240-266)."""
+        grid_coords, grid_indices = self.engine.items()
+        return (
+            grid_coords.view(-1, 1, self.in_dim),
+            self.cell_coords.view(1, -1, self.in_dim),
+            grid_indices.view(-1, 1),
+            self.cell_indices.view(1, -1),
+        )
+
+    # ------------------------------------------------------------------ geometry
+    @torch.no_grad()
+    def get_bbox(self):
+        return self.bbox_min, self.bbox_max
+
+    def cell_to_world(self, grid_coords: torch.Tensor, cell_coords: torch.Tensor) -> torch.Tensor:
+        """World positions (n * G^3, 3) of every cell of the given blocks."""
+        cells = grid_coords.view(-1, 1, self.in_dim) * self.grid_dim + cell_coords.view(1, -1, self.in_dim)
+        return self.transform_cell_to_world(cells).view(-1, self.in_dim)
+
+    def grids_in_bound(self, grid_coords: torch.Tensor) -> torch.Tensor:
+        return grid_coords
+
+    @torch.no_grad()
+    def _linearize_cell_coords(self, cell_coords: torch.Tensor) -> torch.Tensor:
+        """(N, 3) cell coordinates -> linear cell index, x fastest."""
+        assert cell_coords.dim() == 2 and cell_coords.shape[1] == self.in_dim
+        strides = torch.tensor([self.grid_dim**d for d in range(self.in_dim)], dtype=torch.long,
+                               device=cell_coords.device)
+        return (cell_coords.long() * strides).sum(dim=1)
+
+    @torch.no_grad()
+    def _delinearize_cell_indices(self, cell_indices: torch.Tensor) -> torch.Tensor:
+        """Linear cell index -> (…, 3) int32 cell coordinates."""
+        digits = [
+            torch.div(cell_indices, self.grid_dim**d, rounding_mode="floor") % self.grid_dim
+            for d in range(self.in_dim)
+        ]
+        return torch.stack(digits, dim=1).int()
+
+    # ------------------------------------------------------------------ sampling
+    @torch.no_grad()
+    def ray_sample(self, rays_o, rays_d, rays_near, rays_far, max_samples_per_ray: int):
+        """Sample intervals inside active blocks along rays (ash/grid.py:322-377): returns
+        ``(ray_indices (M,), t_near (M,), t_far (M,), prefix_sum (N,))``, lengths in world units."""
+        bbox_min, bbox_max = self.get_bbox()
+        ray_indices, t_nears, t_fars, prefix_sum = backend.ray_sample(
+            self.engine.backend, self.transform_world_to_cell(rays_o), rays_d, rays_near / self.cell_size,
+            rays_far / self.cell_size, self.transform_world_to_cell(bbox_min),
+            self.transform_world_to_cell(bbox_max), max_samples_per_ray, float(self.grid_dim))
+        return ray_indices, t_nears * self.cell_size, t_fars * self.cell_size, prefix_sum
+
+    @torch.no_grad()
+    def ray_find_near_far(self, rays_o, rays_d, t_min: float, t_max: float, t_step: float):
+        """First / last occupied stretch along each ray (ash/grid.py:379-403)."""
+        bbox_min, bbox_max = self.get_bbox()
+        nears, fars = backend.ray_find_near_far(
+            self.engine.backend, self.transform_world_to_cell(rays_o), rays_d,
+            self.transform_world_to_cell(bbox_min), self.transform_world_to_cell(bbox_max),
+            t_min / self.cell_size, t_max / self.cell_size, t_step / self.cell_size, float(self.grid_dim))
+        return nears * self.cell_size, fars * self.cell_size
+
+    def uniform_sample(self, num_samples: int, space: Literal["occupied", "empty"] = "occupied") -> torch.Tensor:
+        """Uniform world positions inside randomly chosen active blocks (ash/grid.py:405-430)."""
+        if space != "occupied":
+            raise NotImplementedError("empty space sampling not implemented")
+        active, _ = self.engine.items()
+        pick = torch.randint(len(active), (num_samples,), device=self.device)
+        inside = torch.rand(num_samples, self.in_dim, device=self.device)
+        return self.transform_cell_to_world((active[pick].float() + inside) * self.grid_dim)
+
+    # ------------------------------------------------------------------ filtering
+    @staticmethod
+    def _gaussian_weights(size: int, sigma: float) -> torch.Tensor:
+        """Separable kernel of ash/grid.py:449-462: bin masses of a standard normal over
+        ``size`` equal bins of [-sigma, sigma], outer-multiplied and normalised."""
+        import numpy as np
+        import scipy.stats as st
+
+        edges = np.linspace(-sigma, sigma, size + 1)
+        k1 = np.diff(st.norm.cdf(edges))
+        k3 = np.outer(k1, np.outer(k1, k1)).reshape(size, size, size)
+        return torch.from_numpy(k3 / k3.sum()).float()
+
+    @torch.no_grad()
+    def gaussian_filter_(self, size: int, sigma: float) -> None:
+        """In-place ``size``^3 Gaussian smoothing of every embedding channel."""
+        assert size % 2 == 1, "size must be odd"
+        channels = self.embeddings.shape[-1]
+        weights = self._gaussian_weights(size, sigma).view(size, size, size, 1).repeat(1, 1, 1, channels)
+        self.embeddings.copy_(self.convolution(self.embeddings, weights.to(self.embeddings.device)))
+
+    def convolution(self, inputs: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+        """Depth-wise (2R+1)^3 convolution over the sparse-dense structure (ash/grid.py:476-520).
+        ``inputs`` (num_embeddings, G^3, C); ``weights`` (2R+1, 2R+1, 2R+1, C)."""
+        assert inputs.is_contiguous() and inputs.shape[:2] == self.embeddings.shape[:2]
+        assert weights.is_contiguous() and weights.dim() == 4 and weights.shape[0] % 2 == 1
+        radius = weights.shape[0] // 2
+        assert weights.shape[:3] == (2 * radius + 1,) * 3
+        assert weights.shape[3] == inputs.shape[-1] and weights.device == inputs.device
+
+        lut_c2g, lut_c2c = self.construct_cell_neighbor_lut(radius, bidirectional=True)
+        grid_radius = (radius + self.grid_dim - 1) // self.grid_dim
+        _, lut_g2g = self.construct_grid_neighbor_lut(grid_radius, bidirectional=True)
+        _, _, grid_indices, cell_indices = self.items()
+        return backend.convolution_forward(
+            inputs, weights.view(lut_c2g.shape[1], weights.shape[-1]), torch.ones_like(inputs, dtype=torch.bool),
+            grid_indices, cell_indices, lut_g2g, lut_c2c, lut_c2g, self.grid_dim)
+
+    # ------------------------------------------------------------------ lookup tables
+    @torch.no_grad()
+    def construct_cell_neighbor_lut(self, radius: int, bidirectional: bool):
+        """Per-cell neighbour tables ``(lut_cell_nb2grid_nb, lut_cell_nb2cell_idx)``, both
+        (G^3, K) int64: for cell c and window offset k, which neighbouring block (numbered in the
+        block-level window) and which cell inside it (ash/grid.py:525-564)."""
+        G = self.grid_dim
+        cell_offsets, _ = enumerate_neighbor_coord_offsets(self.in_dim, radius, bidirectional, self.device)
+        _, block_offset2idx = enumerate_neighbor_coord_offsets(
+            self.in_dim, (radius + G - 1) // G, bidirectional, self.device)
+        nb = (self.cell_coords.view(-1, 1, self.in_dim) + cell_offsets.view(1, -1, self.in_dim)).view(-1, self.in_dim)
+        block_shift = torch.div(nb, G, rounding_mode="floor").long()
+        nb_cell = self._linearize_cell_coords(torch.remainder(nb, G))
+        return (
+            block_offset2idx(block_shift).view(self.num_cells_per_grid, -1),
+            nb_cell.view(self.num_cells_per_grid, -1),
+        )
+
+    @torch.no_grad()
+    def construct_grid_neighbor_lut(self, radius: int, bidirectional: bool):
+        """Per-block tables ``(grid_coords (num_embeddings, 3) int32, lut_grid_nb2grid_idx
+        (num_embeddings, K) int64)``; rows of inactive blocks and absent neighbours hold -1
+        (ash/grid.py:566-617)."""
+        coords, indices = self.engine.items()
+        offsets, _ = enumerate_neighbor_coord_offsets(self.in_dim, radius, bidirectional, self.device)
+        K = offsets.shape[0]
+        grid_coords = torch.full((self.num_embeddings, self.in_dim), -1, dtype=torch.int32, device=self.device)
+        lut = torch.full((self.num_embeddings, K), -1, dtype=torch.int64, device=self.device)
+        if coords.shape[0] > 0:
+            nb = (coords.view(-1, 1, self.in_dim) + offsets.int().view(1, -1, self.in_dim)).view(-1, self.in_dim)
+            nb_indices, nb_masks = self.engine.find(nb)
+            nb_indices = torch.where(nb_masks, nb_indices, torch.full_like(nb_indices, -1))
+            grid_coords[indices] = coords
+            lut[indices] = nb_indices.view(-1, K)
+        return grid_coords, lut
+
+    @torch.no_grad()
+    def construct_grid_neighbor_lut_(self, radius: int, bidirectional: bool) -> None:
+        self.grid_coords, self.lut_grid_nb2grid_idx = self.construct_grid_neighbor_lut(radius, bidirectional)
+
+    # ------------------------------------------------------------------ surface extraction
+    def marching_cubes(self, tsdfs, weights, color_fn=None, normal_fn=None, iso_value: float = 0.0,
+                       weight_thr: float = 1.0, vertices_only=False):
+        raise NotImplementedError(
+            "mesh extraction (ash/grid.py:628-711, ash/src/grid.cu:453-946) is outside the hot path "
+            "this library implements")
+
+
+class UnBoundedSparseDenseGrid(SparseDenseGrid):
+    """Grid with a fixed metric ``cell_size`` and no fixed extent (ash/grid.py:714-776)."""
+
+    def __init__(self, in_dim: int, num_embeddings: int, embedding_dim: int, grid_dim: int,
+                 cell_size: float = 0.01, device: Optional[Union[str, torch.device]] = torch.device("cpu")):
+        super().__init__(in_dim, num_embeddings, embedding_dim, grid_dim, device)
+        self.cell_size = cell_size
+        self.transform_world_to_cell = lambda x: x / self.cell_size
+        self.transform_cell_to_world = lambda x: x * self.cell_size
+        self.bbox_min = None
+        self.bbox_max = None
+
+    @torch.no_grad()
+    def compute_bbox_(self):
+        coords, _ = self.engine.items()
+        lo = coords.min(dim=0)[0]
+        hi = coords.max(dim=0)[0] + 1
+        self.bbox_min = self.transform_cell_to_world(lo * self.grid_dim)
+        self.bbox_max = self.transform_cell_to_world(hi * self.grid_dim)
+
+    @torch.no_grad()
+    def get_bbox(self, force_recompute: bool = False):
+        if self.bbox_min is None or self.bbox_max is None or force_recompute:
+            self.compute_bbox_()
+        return self.bbox_min, self.bbox_max
+
+
+# The spelling used by callers that write "Unbounded".
+UnboundedSparseDenseGrid = UnBoundedSparseDenseGrid
+
+
+class BoundedSparseDenseGrid(SparseDenseGrid):
+    """Grid over a fixed box split into ``sparse_grid_dim``^3 blocks (ash/grid.py:779-863)."""
+
+    def __init__(self, in_dim: int, num_embeddings: int, embedding_dim: int, grid_dim: int = 8,
+                 sparse_grid_dim: int = 128, bbox_min: torch.Tensor = None, bbox_max: torch.Tensor = None,
+                 device: Optional[Union[str, torch.device]] = None):
+        assert in_dim == 3, "Only 3D is supported now"
+        super().__init__(in_dim, num_embeddings, embedding_dim, grid_dim, device)
+        self.sparse_grid_dim = sparse_grid_dim
+        self.bbox_min = (-torch.ones(in_dim, device=self.device)) if bbox_min is None else bbox_min.to(self.device)
+        self.bbox_max = torch.ones(in_dim, device=self.device) if bbox_max is None else bbox_max.to(self.device)
+        self.cell_size = ((self.bbox_max - self.bbox_min) / (sparse_grid_dim * grid_dim - 1)).min().item()
+        self.transform_world_to_cell = lambda x: (x - self.bbox_min) / self.cell_size
+        self.transform_cell_to_world = lambda x: x * self.cell_size + self.bbox_min
+
+    def grids_in_bound(self, grid_coords: torch.Tensor) -> torch.Tensor:
+        inside = ((grid_coords >= 0) & (grid_coords < self.sparse_grid_dim)).all(dim=-1)
+        return grid_coords[inside]
+
+    def dense_init_(self):
+        """Activate every block of the box."""
+        r = torch.arange(self.sparse_grid_dim, device=self.device)
+        coords = torch.stack(torch.meshgrid(r, r, r, indexing="ij")).reshape(self.in_dim, -1).T
+        self.engine.insert_keys(coords.int().contiguous())

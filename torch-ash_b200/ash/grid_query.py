@@ -1,0 +1,74 @@
+"""Autograd wiring of the sparse-dense grid query (API of ash/grid_query.py).
+
+``SparseDenseGridQuery``          y = sum_c w_c(offset) * embeddings[corner_c]
+``SparseDenseGridQueryBackward``  (dL/d embeddings, dL/d offsets) given z = dL/dy, itself
+                                  differentiable w.r.t. z and embeddings so that
+                                  gradient-of-gradient losses (eikonal) train.
+
+Argument order, which inputs receive ``None`` gradients, and the choice to drop
+the double-backward gradient w.r.t. offsets all follow ash/grid_query.py:10-283.
+The three native calls go to the sm_100a kernels behind ``__ash``.
+"""
+from typing import Literal
+
+import torch
+
+from .common import _get_c_extension
+
+backend = _get_c_extension()
+
+_N_FWD_INPUTS = 10   # embeddings, offsets, 3 index tensors, 3 lookup tables, grid_dim, interpolation
+_N_BWD_INPUTS = 11   # z + the above
+
+
+class SparseDenseGridQuery(torch.autograd.Function):
+    """Interpolate embeddings at (grid_indices, cell_indices, offsets); differentiable
+    w.r.t. ``embeddings`` and ``offsets``."""
+
+    @staticmethod
+    def forward(ctx, embeddings, offsets, grid_indices, cell_indices, masks, lut_grid_nb2grid_idx,
+                lut_cell_nb2cell_idx, lut_cell_nb2grid_nb, grid_dim: int,
+                interpolation: Literal["linear", "smooth_step"] = "smooth_step"):
+        ctx.save_for_backward(embeddings, offsets, grid_indices, cell_indices, masks, lut_grid_nb2grid_idx,
+                              lut_cell_nb2cell_idx, lut_cell_nb2grid_nb)
+        ctx.grid_dim = grid_dim
+        ctx.interpolation = interpolation
+        return backend.query_forward(embeddings, offsets, grid_indices, cell_indices, masks, lut_grid_nb2grid_idx,
+                                     lut_cell_nb2cell_idx, lut_cell_nb2grid_nb, grid_dim, interpolation)
+
+    @staticmethod
+    def backward(ctx, z):
+        grad_embeddings, grad_offsets = SparseDenseGridQueryBackward.apply(
+            z.contiguous(), *ctx.saved_tensors, ctx.grid_dim, ctx.interpolation)
+        return (grad_embeddings, grad_offsets) + (None,) * (_N_FWD_INPUTS - 2)
+
+
+class SparseDenseGridQueryBackward(torch.autograd.Function):
+    """The backward pass of the query as a differentiable function of (z, embeddings)."""
+
+    @staticmethod
+    def forward(ctx, z, embeddings, offsets, grid_indices, cell_indices, masks, lut_grid_nb2grid_idx,
+                lut_cell_nb2cell_idx, lut_cell_nb2grid_nb, grid_dim, interpolation):
+        ctx.save_for_backward(z, embeddings, offsets, grid_indices, cell_indices, masks, lut_grid_nb2grid_idx,
+                              lut_cell_nb2cell_idx, lut_cell_nb2grid_nb)
+        ctx.grid_dim = grid_dim
+        ctx.interpolation = interpolation
+        # An unused grad_grad_embeddings would otherwise be materialised as a
+        # table-sized zero tensor only to be ignored by the kernel.
+        ctx.set_materialize_grads(False)
+        return backend.query_backward_forward(z, embeddings, offsets, grid_indices, cell_indices, masks,
+                                              lut_grid_nb2grid_idx, lut_cell_nb2cell_idx, lut_cell_nb2grid_nb,
+                                              grid_dim, interpolation)
+
+    @staticmethod
+    def backward(ctx, grad_grad_embeddings, grad_grad_offsets):
+        """Only the path through grad_offsets is propagated (to z and embeddings); the path
+        through grad_embeddings and the gradient w.r.t. offsets are dropped as in
+        ash/grid_query.py:224-283."""
+        if grad_grad_offsets is None:
+            return (None,) * _N_BWD_INPUTS
+        z, embeddings, *rest = ctx.saved_tensors
+        grad_z, grad_embeddings, _ = backend.query_backward_backward(
+            grad_grad_embeddings, grad_grad_offsets.contiguous(), z, embeddings, *rest, ctx.grid_dim,
+            ctx.interpolation)
+        return (grad_z, grad_embeddings) + (None,) * (_N_BWD_INPUTS - 2)

@@ -1,0 +1,479 @@
+// Collision-free spatial hash engine for sm_100a: a lock-free open-addressing
+// table over packed int32 keys.
+//
+// Layout in HBM
+//   key_dim 1..3 : one 16-byte slot {k0, k1, k2, value}; a probe is one 128-bit
+//                  load and an insert claims a slot with one 128-bit CAS, so no
+//                  reader ever waits for a half-written key.
+//   key_dim 4    : one 32-byte slot {k0..k3, value, pad}; the value word is
+//                  claimed with a 32-bit CAS (LOCKED), the key written, then the
+//                  value released; readers that meet LOCKED wait with a bound.
+//   value        : >= 0 index into the caller's value/embedding rows,
+//                  EMPTY (-1), TOMB (-2, erased), PENDING (-3, index not yet
+//                  assigned; only inside an insert launch), LOCKED (-4).
+//   n_slots      : power of two >= 2 * capacity (load factor <= 0.5), linear
+//                  probing: consecutive probes stay inside one 128-byte line.
+//   heap         : the caller's int32[capacity] free-index stack; counter is a
+//                  device int32 (= number of live keys).  Pops and pushes are
+//                  warp-aggregated: one atomic per warp, not per key.
+//
+// Semantics follow ash/src/hashmap_gpu.cuh (find :164-178, insert-if-absent +
+// heap pop :212-232, value copy by the winner :250-283, erase + heap push
+// :317-336, clear :355-358, items :377-405, load_states :408-450).
+#include <cstring>
+#include <new>
+
+#include "hashmap.cuh"
+
+namespace ashb {
+
+// ---- find ----------------------------------------------------------------------
+template <class Table, int DIM>
+__global__ void __launch_bounds__(256) find_kernel(Table t, const int32_t* __restrict__ keys, int64_t n,
+                                                   int64_t* __restrict__ indices,
+                                                   uint8_t* __restrict__ masks) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int k0, k1, k2, k3;
+    load_key<DIM>(keys, i, k0, k1, k2, k3);
+    uint32_t s = hash_key(k0, k1, k2, k3) & t.mask;
+    int found = -1;
+    for (uint32_t probe = 0; probe <= t.mask; ++probe) {
+        const Entry e = t.read_const(s);
+        if (e.val == kEmpty) break;
+        if (e.val >= 0 && key_match(e, k0, k1, k2, k3)) {
+            found = e.val;
+            break;
+        }
+        s = (s + 1) & t.mask;
+    }
+    indices[i] = found >= 0 ? (int64_t)found : 0;
+    masks[i] = (uint8_t)(found >= 0);
+}
+
+// ---- insert ----------------------------------------------------------------------
+struct ValueCtx {
+    int n;
+    const char* src[kMaxValues];
+    char* dst[kMaxValues];
+    long long row_bytes[kMaxValues];
+    int word[kMaxValues];  // widest power-of-two copy word (<= 16) both sides allow
+};
+
+__device__ __forceinline__ void copy_row(const char* __restrict__ src, char* __restrict__ dst,
+                                         long long bytes, int word) {
+    switch (word) {
+        case 16:
+            for (long long b = 0; b < bytes; b += 16)
+                *reinterpret_cast<int4*>(dst + b) = *reinterpret_cast<const int4*>(src + b);
+            break;
+        case 8:
+            for (long long b = 0; b < bytes; b += 8)
+                *reinterpret_cast<int2*>(dst + b) = *reinterpret_cast<const int2*>(src + b);
+            break;
+        case 4:
+            for (long long b = 0; b < bytes; b += 4)
+                *reinterpret_cast<int*>(dst + b) = *reinterpret_cast<const int*>(src + b);
+            break;
+        case 2:
+            for (long long b = 0; b < bytes; b += 2)
+                *reinterpret_cast<short*>(dst + b) = *reinterpret_cast<const short*>(src + b);
+            break;
+        default:
+            for (long long b = 0; b < bytes; ++b) dst[b] = src[b];
+    }
+}
+
+template <class Table, int DIM>
+__global__ void __launch_bounds__(256) insert_kernel(Table t, const int32_t* __restrict__ keys, int64_t n,
+                                                     int32_t* __restrict__ heap, int32_t* counter,
+                                                     int32_t capacity, ValueCtx vctx) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t slot = -1;
+    if (i < n) {
+        int k0, k1, k2, k3;
+        load_key<DIM>(keys, i, k0, k1, k2, k3);
+        bool present = false;
+        slot = emplace(t, k0, k1, k2, k3, kPending, &present);
+    }
+    // Warp-aggregated pop of the free-index stack: one atomic per warp.
+    const bool won = slot >= 0;
+    const unsigned ballot = __ballot_sync(0xffffffffu, won);
+    if (ballot == 0) return;
+    const int leader = __ffs(ballot) - 1;
+    int base = 0;
+    if ((int)(threadIdx.x & 31) == leader) base = atomicAdd(counter, __popc(ballot));
+    base = __shfl_sync(0xffffffffu, base, leader);
+    if (!won) return;
+    const int top = base + __popc(ballot & lanemask_lt());
+    if (top >= capacity) {
+        // No free index left: undo the pop, give the slot back, record it.
+        atomicSub(counter, 1);
+        *reinterpret_cast<volatile int*>(t.val_ptr((uint32_t)slot)) = kTomb;
+        atomicOr(t.status, ASHB_STATUS_CAPACITY);
+        return;
+    }
+    const int idx = heap[top];
+    for (int j = 0; j < vctx.n; ++j)
+        copy_row(vctx.src[j] + i * vctx.row_bytes[j], vctx.dst[j] + (long long)idx * vctx.row_bytes[j],
+                 vctx.row_bytes[j], vctx.word[j]);
+    *reinterpret_cast<volatile int*>(t.val_ptr((uint32_t)slot)) = idx;
+}
+
+// ---- erase -----------------------------------------------------------------------
+template <class Table, int DIM>
+__global__ void __launch_bounds__(256) erase_kernel(Table t, const int32_t* __restrict__ keys, int64_t n,
+                                                    int32_t* __restrict__ heap, int32_t* counter) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int idx = -1;
+    if (i < n) {
+        int k0, k1, k2, k3;
+        load_key<DIM>(keys, i, k0, k1, k2, k3);
+        uint32_t s = hash_key(k0, k1, k2, k3) & t.mask;
+        for (uint32_t probe = 0; probe <= t.mask; ++probe) {
+            const Entry e = t.read_fresh(s);
+            if (e.val == kEmpty) break;
+            if (e.val >= 0 && key_match(e, k0, k1, k2, k3)) {
+                // In-batch duplicates race here; exactly one CAS succeeds.
+                if (atomicCAS(t.val_ptr(s), e.val, kTomb) == e.val) idx = e.val;
+                break;
+            }
+            s = (s + 1) & t.mask;
+        }
+    }
+    const bool won = idx >= 0;
+    const unsigned ballot = __ballot_sync(0xffffffffu, won);
+    if (ballot == 0) return;
+    const int leader = __ffs(ballot) - 1;
+    int base = 0;
+    if ((int)(threadIdx.x & 31) == leader) base = atomicSub(counter, __popc(ballot));
+    base = __shfl_sync(0xffffffffu, base, leader);
+    if (!won) return;
+    const int top = base - __popc(ballot & lanemask_lt());
+    if (top >= 1) heap[top - 1] = idx;
+}
+
+// ---- load_states -----------------------------------------------------------------
+template <class Table, int DIM>
+__global__ void __launch_bounds__(256) load_states_kernel(Table t, const int32_t* __restrict__ keys,
+                                                          const int64_t* __restrict__ indices, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int k0, k1, k2, k3;
+    load_key<DIM>(keys, i, k0, k1, k2, k3);
+    bool present = false;
+    emplace(t, k0, k1, k2, k3, (int)indices[i], &present);
+    if (present) atomicOr(t.status, ASHB_STATUS_DUPLICATE);
+}
+
+__global__ void set_counter_kernel(int32_t* counter, int32_t v) { *counter = v; }
+
+__global__ void reset_heap_kernel(int32_t* __restrict__ heap, int64_t capacity) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < capacity;
+         i += (int64_t)gridDim.x * blockDim.x)
+        heap[i] = (int32_t)i;
+}
+
+// ---- items -----------------------------------------------------------------------
+// Compacted enumeration.  A CTA scans a tile of 256 x 4 slots per round, ranks its
+// live slots with a block-wide prefix sum and reserves its output range with ONE
+// atomic, so the shared cursor sees n_slots / 1024 atomics instead of one per warp.
+template <class Table, int DIM>
+__global__ void __launch_bounds__(256) items_kernel(Table t, int32_t* __restrict__ keys_out,
+                                                    int64_t* __restrict__ indices_out, int64_t max_n,
+                                                    unsigned long long* cursor) {
+    constexpr int kPerThread = 4;
+    __shared__ unsigned warp_totals[8];
+    __shared__ unsigned long long tile_base;
+    const uint64_t n_slots = (uint64_t)t.mask + 1;
+    const uint64_t tile = 256ull * kPerThread;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (uint64_t start = (uint64_t)blockIdx.x * tile; start < n_slots; start += (uint64_t)gridDim.x * tile) {
+        Entry e[kPerThread];
+        unsigned mine = 0;
+#pragma unroll
+        for (int j = 0; j < kPerThread; ++j) {
+            const uint64_t s = start + (uint64_t)j * 256 + threadIdx.x;
+            e[j] = Entry{0, 0, 0, 0, kEmpty};
+            if (s < n_slots) e[j] = t.read_const((uint32_t)s);
+            mine += e[j].val >= 0;
+        }
+        // exclusive prefix of `mine` over the CTA
+        unsigned incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
+        }
+        if (lane == 31) warp_totals[warp] = incl;
+        __syncthreads();
+        unsigned before = 0, total = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            const unsigned v = warp_totals[w];
+            if (w < warp) before += v;
+            total += v;
+        }
+        if (threadIdx.x == 0) tile_base = total ? atomicAdd(cursor, (unsigned long long)total) : 0ull;
+        __syncthreads();
+        int64_t o = (int64_t)tile_base + before + (incl - mine);
+#pragma unroll
+        for (int j = 0; j < kPerThread; ++j) {
+            if (e[j].val < 0) continue;
+            if (o < max_n) {
+                int32_t* k = keys_out + o * DIM;
+                k[0] = e[j].k0;
+                if (DIM > 1) k[1] = e[j].k1;
+                if (DIM > 2) k[2] = e[j].k2;
+                if (DIM > 3) k[3] = e[j].k3;
+                indices_out[o] = e[j].val;
+            }
+            ++o;
+        }
+        __syncthreads();  // warp_totals / tile_base are reused next round
+    }
+}
+
+}  // namespace ashb
+
+using namespace ashb;
+
+namespace {
+
+template <class F16, class F32>
+int dispatch(ashb_map* m, F16&& f16, F32&& f32) {
+    if (m->key_dim == 4) {
+        Table32 t{static_cast<Slot32*>(m->slots), (uint32_t)(m->n_slots - 1), m->status};
+        return f32(t);
+    }
+    Table16 t{static_cast<uint4*>(m->slots), (uint32_t)(m->n_slots - 1), m->status};
+    return f16(t);
+}
+
+inline unsigned blocks_for(int64_t n, int threads) { return (unsigned)((n + threads - 1) / threads); }
+
+int check_map(ashb_map* m) {
+    ASHB_REQUIRE(m != nullptr && m->slots != nullptr, "null or destroyed map");
+    return ASHB_OK;
+}
+
+#define ASHB_MAP_PROLOGUE(m)                      \
+    if (int _rc = check_map(m)) return _rc;       \
+    DeviceGuard _guard((m)->device);              \
+    if (!_guard.ok) {                             \
+        set_error("cannot select device %d", (m)->device); \
+        return ASHB_ERR_CUDA;                     \
+    }
+
+#define ASHB_DIM_LAUNCH(KERNEL, m, grid, block, st, ...)                                   \
+    dispatch(                                                                              \
+            m,                                                                             \
+            [&](Table16 t) {                                                               \
+                switch ((m)->key_dim) {                                                    \
+                    case 1: KERNEL<Table16, 1><<<grid, block, 0, st>>>(t, __VA_ARGS__); break; \
+                    case 2: KERNEL<Table16, 2><<<grid, block, 0, st>>>(t, __VA_ARGS__); break; \
+                    default: KERNEL<Table16, 3><<<grid, block, 0, st>>>(t, __VA_ARGS__); break; \
+                }                                                                          \
+                return 0;                                                                  \
+            },                                                                             \
+            [&](Table32 t) {                                                               \
+                KERNEL<Table32, 4><<<grid, block, 0, st>>>(t, __VA_ARGS__);                \
+                return 0;                                                                  \
+            })
+
+}  // namespace
+
+extern "C" {
+
+int ashb_map_create(int key_dim, int64_t capacity, int32_t* heap_dev, int device, ashb_map** out) {
+    ASHB_REQUIRE(out != nullptr, "out is null");
+    *out = nullptr;
+    ASHB_REQUIRE(key_dim >= 1 && key_dim <= 4, "key_dim %d not in 1..4", key_dim);
+    ASHB_REQUIRE(capacity >= 1 && capacity <= (int64_t)1 << 30, "capacity %lld not in 1..2^30",
+                 (long long)capacity);
+    ASHB_REQUIRE(heap_dev != nullptr, "heap is null");
+    DeviceGuard guard(device);
+    if (!guard.ok) {
+        set_error("cannot select device %d", device);
+        return ASHB_ERR_CUDA;
+    }
+    ashb_map* m = new (std::nothrow) ashb_map();
+    ASHB_REQUIRE(m != nullptr, "out of host memory");
+    m->key_dim = key_dim;
+    m->capacity = capacity;
+    m->device = device;
+    m->heap = heap_dev;
+    uint64_t n = 32;
+    while (n < 2ull * (uint64_t)capacity) n <<= 1;
+    m->n_slots = n;
+    m->slot_bytes = key_dim == 4 ? sizeof(Slot32) : sizeof(uint4);
+    cudaError_t e = cudaMalloc(&m->slots, n * m->slot_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&m->small, 256);
+    if (e != cudaSuccess) {
+        set_error("cudaMalloc of %llu-slot table failed: %s", (unsigned long long)n, cudaGetErrorString(e));
+        if (m->slots) cudaFree(m->slots);
+        delete m;
+        return ASHB_ERR_CUDA;
+    }
+    m->counter = reinterpret_cast<int32_t*>(m->small);
+    m->status = reinterpret_cast<uint32_t*>(static_cast<char*>(m->small) + 64);
+    m->cursor = reinterpret_cast<unsigned long long*>(static_cast<char*>(m->small) + 128);
+    // 0xFF bytes: every key word -1 and every value word EMPTY (-1); for 32-byte
+    // slots the pad words too.  Ordered before any later work on any stream by
+    // the synchronising memset on the legacy stream.
+    e = cudaMemset(m->slots, 0xFF, n * m->slot_bytes);
+    if (e == cudaSuccess) e = cudaMemset(m->small, 0, 256);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        set_error("table initialisation failed: %s", cudaGetErrorString(e));
+        cudaFree(m->slots);
+        cudaFree(m->small);
+        delete m;
+        return ASHB_ERR_CUDA;
+    }
+    *out = m;
+    return ASHB_OK;
+}
+
+int ashb_map_destroy(ashb_map* m) {
+    if (m == nullptr) return ASHB_OK;
+    DeviceGuard guard(m->device);
+    if (m->slots) cudaFree(m->slots);
+    if (m->small) cudaFree(m->small);
+    m->slots = nullptr;
+    delete m;
+    return ASHB_OK;
+}
+
+int ashb_map_clear(ashb_map* m, void* stream) {
+    ASHB_MAP_PROLOGUE(m);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    ASHB_CUDA_TRY(cudaMemsetAsync(m->slots, 0xFF, m->n_slots * m->slot_bytes, st));
+    ASHB_CUDA_TRY(cudaMemsetAsync(m->counter, 0, sizeof(int32_t), st));
+    reset_heap_kernel<<<wave_grid(m->capacity, 256, 8), 256, 0, st>>>(m->heap, m->capacity);
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+int ashb_map_size(ashb_map* m, void* stream, int64_t* size_out) {
+    ASHB_MAP_PROLOGUE(m);
+    ASHB_REQUIRE(size_out != nullptr, "size_out is null");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int32_t v = 0;
+    ASHB_CUDA_TRY(cudaMemcpyAsync(&v, m->counter, sizeof(v), cudaMemcpyDeviceToHost, st));
+    ASHB_CUDA_TRY(cudaStreamSynchronize(st));
+    *size_out = v;
+    return ASHB_OK;
+}
+
+int ashb_map_status(ashb_map* m, void* stream, uint32_t* status_out) {
+    ASHB_MAP_PROLOGUE(m);
+    ASHB_REQUIRE(status_out != nullptr, "status_out is null");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint32_t v = 0;
+    ASHB_CUDA_TRY(cudaMemcpyAsync(&v, m->status, sizeof(v), cudaMemcpyDeviceToHost, st));
+    ASHB_CUDA_TRY(cudaMemsetAsync(m->status, 0, sizeof(v), st));
+    ASHB_CUDA_TRY(cudaStreamSynchronize(st));
+    *status_out = v;
+    return ASHB_OK;
+}
+
+int ashb_map_find(ashb_map* m, const int32_t* keys, int64_t n, int64_t* indices, uint8_t* masks,
+                  void* stream) {
+    ASHB_MAP_PROLOGUE(m);
+    ASHB_REQUIRE(n >= 0, "negative count");
+    if (n == 0) return ASHB_OK;
+    ASHB_REQUIRE(keys && indices && masks, "null buffer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    ASHB_DIM_LAUNCH(find_kernel, m, blocks_for(n, 256), 256, st, keys, n, indices, masks);
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+static int insert_impl(ashb_map* m, const int32_t* keys, int64_t n, const ValueCtx& vctx, void* stream) {
+    ASHB_MAP_PROLOGUE(m);
+    ASHB_REQUIRE(n >= 0, "negative count");
+    if (n == 0) return ASHB_OK;
+    ASHB_REQUIRE(keys != nullptr, "null keys");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    ASHB_DIM_LAUNCH(insert_kernel, m, blocks_for(n, 256), 256, st, keys, n, m->heap, m->counter,
+                    (int32_t)m->capacity, vctx);
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+int ashb_map_insert_keys(ashb_map* m, const int32_t* keys, int64_t n, void* stream) {
+    ValueCtx v;
+    std::memset(&v, 0, sizeof(v));
+    return insert_impl(m, keys, n, v, stream);
+}
+
+int ashb_map_insert_values(ashb_map* m, const int32_t* keys, int64_t n, int n_values,
+                           const void* const* src, void* const* dst, const int64_t* row_bytes,
+                           void* stream) {
+    ASHB_REQUIRE(n_values >= 0 && n_values <= kMaxValues, "n_values %d not in 0..%d", n_values, kMaxValues);
+    ASHB_REQUIRE(n_values == 0 || (src && dst && row_bytes), "null value tables");
+    ValueCtx v;
+    std::memset(&v, 0, sizeof(v));
+    v.n = n_values;
+    for (int j = 0; j < n_values; ++j) {
+        ASHB_REQUIRE(src[j] && dst[j] && row_bytes[j] > 0, "value %d: null pointer or empty row", j);
+        v.src[j] = static_cast<const char*>(src[j]);
+        v.dst[j] = static_cast<char*>(dst[j]);
+        v.row_bytes[j] = row_bytes[j];
+        int w = 16;
+        const uintptr_t bits = (uintptr_t)src[j] | (uintptr_t)dst[j] | (uintptr_t)row_bytes[j];
+        while (w > 1 && (bits & (uintptr_t)(w - 1))) w >>= 1;
+        v.word[j] = w;
+    }
+    return insert_impl(m, keys, n, v, stream);
+}
+
+int ashb_map_erase(ashb_map* m, const int32_t* keys, int64_t n, void* stream) {
+    ASHB_MAP_PROLOGUE(m);
+    ASHB_REQUIRE(n >= 0, "negative count");
+    if (n == 0) return ASHB_OK;
+    ASHB_REQUIRE(keys != nullptr, "null keys");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    ASHB_DIM_LAUNCH(erase_kernel, m, blocks_for(n, 256), 256, st, keys, n, m->heap, m->counter);
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+int ashb_map_items(ashb_map* m, int32_t* keys_out, int64_t* indices_out, int64_t max_n, int64_t* n_out,
+                   void* stream) {
+    ASHB_MAP_PROLOGUE(m);
+    ASHB_REQUIRE(max_n >= 0 && n_out != nullptr, "bad output arguments");
+    ASHB_REQUIRE(max_n == 0 || (keys_out && indices_out), "null output buffer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    ASHB_CUDA_TRY(cudaMemsetAsync(m->cursor, 0, sizeof(unsigned long long), st));
+    const unsigned grid = wave_grid((int64_t)(m->n_slots / 4 + 1), 256, 8);
+    ASHB_DIM_LAUNCH(items_kernel, m, grid, 256, st, keys_out, indices_out, max_n, m->cursor);
+    ASHB_LAUNCH_CHECK();
+    unsigned long long total = 0;
+    ASHB_CUDA_TRY(cudaMemcpyAsync(&total, m->cursor, sizeof(total), cudaMemcpyDeviceToHost, st));
+    ASHB_CUDA_TRY(cudaStreamSynchronize(st));
+    *n_out = (int64_t)total;
+    return ASHB_OK;
+}
+
+int ashb_map_load_states(ashb_map* m, const int32_t* keys, const int64_t* indices, int64_t n,
+                         const int32_t* heap_src, void* stream) {
+    ASHB_MAP_PROLOGUE(m);
+    ASHB_REQUIRE(n >= 0 && n <= m->capacity, "count %lld not in 0..capacity", (long long)n);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // Start from an empty table: loading on top of live entries would mix two states.
+    ASHB_CUDA_TRY(cudaMemsetAsync(m->slots, 0xFF, m->n_slots * m->slot_bytes, st));
+    set_counter_kernel<<<1, 1, 0, st>>>(m->counter, (int32_t)n);
+    ASHB_LAUNCH_CHECK();
+    if (heap_src != nullptr && heap_src != m->heap)
+        ASHB_CUDA_TRY(cudaMemcpyAsync(m->heap, heap_src, sizeof(int32_t) * m->capacity,
+                                      cudaMemcpyDeviceToDevice, st));
+    if (n == 0) return ASHB_OK;
+    ASHB_REQUIRE(keys && indices, "null buffer");
+    ASHB_DIM_LAUNCH(load_states_kernel, m, blocks_for(n, 256), 256, st, keys, indices, n);
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,226 @@
+// Device-side view of the hash table of libashb200, shared by every kernel that
+// probes it (hash engine, ray sampler, fused grid query, TSDF integration).
+//
+// Layout in HBM
+//   key_dim 1..3 : one 16-byte slot {k0, k1, k2, value}; a probe is one 128-bit
+//                  load and an insert claims a slot with one 128-bit CAS, so no
+//                  reader ever waits for a half-written key.
+//   key_dim 4    : one 32-byte slot {k0..k3, value, pad}; the value word is
+//                  claimed with a 32-bit CAS (LOCKED), the key written, then the
+//                  value released; readers that meet LOCKED wait with a bound.
+//   value        : >= 0 index into the caller's value/embedding rows,
+//                  EMPTY (-1), TOMB (-2, erased), PENDING (-3, index not yet
+//                  assigned; only inside an insert launch), LOCKED (-4).
+//   n_slots      : power of two >= 2 * capacity (load factor <= 0.5), linear
+//                  probing: consecutive probes stay inside one 128-byte line.
+#pragma once
+
+#include "common.cuh"
+
+namespace ashb {
+
+constexpr int kEmpty = -1;
+constexpr int kTomb = -2;
+constexpr int kPending = -3;
+constexpr int kLocked = -4;
+constexpr int kSpinLimit = 1 << 20;
+constexpr int kMaxValues = 16;
+
+struct Entry {
+    int k0, k1, k2, k3;
+    int val;
+};
+
+__device__ __forceinline__ bool key_match(const Entry& e, int k0, int k1, int k2, int k3) {
+    return e.k0 == k0 && e.k1 == k1 && e.k2 == k2 && e.k3 == k3;
+}
+
+union U128 {
+    unsigned __int128 q;
+    uint4 v;
+};
+
+// ---- 16-byte slots, key_dim <= 3 ---------------------------------------------
+struct Table16 {
+    uint4* slots;
+    uint32_t mask;
+    uint32_t* status;
+
+    __device__ __forceinline__ Entry unpack(uint4 r) const {
+        return Entry{(int)r.x, (int)r.y, (int)r.z, 0, (int)r.w};
+    }
+    // Read-only probe (find / items): table is constant for the launch.
+    __device__ __forceinline__ Entry read_const(uint32_t s) const { return unpack(__ldg(slots + s)); }
+    // Probe inside a mutating launch: read at L2, where the atomics resolve.
+    __device__ __forceinline__ Entry read_fresh(uint32_t s) const { return unpack(__ldcg(slots + s)); }
+    // Try to turn the free slot `s` (last seen as `expected`) into {key, PENDING}.
+    // On failure `observed` holds what is there now.
+    __device__ __forceinline__ bool claim(uint32_t s, const Entry& expected, int k0, int k1, int k2,
+                                          int k3, int new_val, Entry& observed) const {
+        (void)k3;
+        U128 cmp, val, old;
+        cmp.v = make_uint4((unsigned)expected.k0, (unsigned)expected.k1, (unsigned)expected.k2,
+                           (unsigned)expected.val);
+        val.v = make_uint4((unsigned)k0, (unsigned)k1, (unsigned)k2, (unsigned)new_val);
+        old.q = atomicCAS(reinterpret_cast<unsigned __int128*>(slots + s), cmp.q, val.q);
+        observed = unpack(old.v);
+        return old.q == cmp.q;
+    }
+    __device__ __forceinline__ int* val_ptr(uint32_t s) const {
+        return reinterpret_cast<int*>(slots + s) + 3;
+    }
+};
+
+// ---- 32-byte slots, key_dim == 4 -----------------------------------------------
+struct __align__(32) Slot32 {
+    int k[4];
+    int val;
+    int pad[3];
+};
+
+struct Table32 {
+    Slot32* slots;
+    uint32_t mask;
+    uint32_t* status;
+
+    __device__ __forceinline__ Entry read_const(uint32_t s) const {
+        const int4 k = __ldg(reinterpret_cast<const int4*>(slots[s].k));
+        const int v = __ldg(&slots[s].val);
+        return Entry{k.x, k.y, k.z, k.w, v};
+    }
+    // Waits (bounded) while another thread is between claiming the slot and
+    // publishing its key; on a timeout the slot is reported as an unrelated
+    // occupied one and the status word records it.
+    __device__ __forceinline__ Entry read_fresh(uint32_t s) const {
+        volatile int* vp = &slots[s].val;
+        int v = *vp;
+        for (int spin = 0; v == kLocked; ++spin) {
+            if (spin >= kSpinLimit) {
+                atomicOr(status, ASHB_STATUS_SPIN);
+                return Entry{0, 0, 0, 0, kLocked};
+            }
+            __nanosleep(32);
+            v = *vp;
+        }
+        __threadfence();
+        const int4 k = __ldcg(reinterpret_cast<const int4*>(slots[s].k));
+        return Entry{k.x, k.y, k.z, k.w, v};
+    }
+    __device__ __forceinline__ bool claim(uint32_t s, const Entry& expected, int k0, int k1, int k2,
+                                          int k3, int new_val, Entry& observed) const {
+        const int old = atomicCAS(&slots[s].val, expected.val, kLocked);
+        if (old != expected.val) {
+            observed = read_fresh(s);
+            return false;
+        }
+        __stcg(reinterpret_cast<int4*>(slots[s].k), make_int4(k0, k1, k2, k3));
+        __threadfence();
+        *reinterpret_cast<volatile int*>(&slots[s].val) = new_val;
+        observed = Entry{k0, k1, k2, k3, new_val};
+        return true;
+    }
+    __device__ __forceinline__ int* val_ptr(uint32_t s) const { return &slots[s].val; }
+};
+
+template <int DIM>
+__device__ __forceinline__ void load_key(const int32_t* __restrict__ keys, int64_t i, int& k0, int& k1,
+                                         int& k2, int& k3) {
+    const int32_t* p = keys + i * DIM;
+    k0 = p[0];
+    k1 = DIM > 1 ? p[1] : 0;
+    k2 = DIM > 2 ? p[2] : 0;
+    k3 = DIM > 3 ? p[3] : 0;
+}
+
+// Insert-if-absent of one key; returns the claimed slot or -1 (present, lost a
+// duplicate race, or table exhausted).  `new_val` is what the slot holds when
+// claimed: PENDING for inserts (index assigned afterwards) or a saved index.
+template <class Table>
+__device__ __forceinline__ int64_t emplace(const Table& t, int k0, int k1, int k2, int k3,
+                                           int new_val, bool* already_present) {
+    uint32_t s = hash_key(k0, k1, k2, k3) & t.mask;
+    int64_t free_slot = -1;
+    Entry free_entry{};
+    // A failed claim restarts the scan at the contested slot, so the bound is on
+    // total steps rather than on one pass.
+    for (uint64_t steps = 0; steps <= 4ull * t.mask + 8; ++steps) {
+        const Entry e = t.read_fresh(s);
+        if (e.val == kEmpty) {
+            const uint32_t target = free_slot >= 0 ? (uint32_t)free_slot : s;
+            const Entry expected = free_slot >= 0 ? free_entry : e;
+            Entry seen;
+            if (t.claim(target, expected, k0, k1, k2, k3, new_val, seen)) return (int64_t)target;
+            if (seen.val != kEmpty && seen.val != kTomb && seen.val != kLocked &&
+                key_match(seen, k0, k1, k2, k3)) {
+                *already_present = true;
+                return -1;
+            }
+            s = target;  // somebody else's key landed there: rescan from it
+            free_slot = -1;
+            continue;
+        }
+        if (e.val == kTomb) {
+            if (free_slot < 0) {
+                free_slot = s;
+                free_entry = e;
+            }
+        } else if (e.val != kLocked && key_match(e, k0, k1, k2, k3)) {
+            *already_present = true;
+            return -1;
+        }
+        s = (s + 1) & t.mask;
+    }
+    atomicOr(t.status, ASHB_STATUS_PROBE);
+    return -1;
+}
+
+// Read-only lookup: index of the key or -1.
+template <class Table>
+__device__ __forceinline__ int lookup(const Table& t, int k0, int k1, int k2, int k3) {
+    uint32_t s = hash_key(k0, k1, k2, k3) & t.mask;
+    for (uint32_t probe = 0; probe <= t.mask; ++probe) {
+        const Entry e = t.read_const(s);
+        if (e.val == kEmpty) return -1;
+        if (e.val >= 0 && key_match(e, k0, k1, k2, k3)) return e.val;
+        s = (s + 1) & t.mask;
+    }
+    return -1;
+}
+
+}  // namespace ashb
+
+// The host-side map object behind the opaque `ashb_map*` of the C ABI.
+struct ashb_map {
+    int key_dim;
+    int64_t capacity;
+    int device;
+    uint64_t n_slots;
+    void* slots;
+    size_t slot_bytes;
+    int32_t* heap;               // borrowed: the caller's free-index stack
+    int32_t* counter;            // device: live keys == popped indices
+    uint32_t* status;            // device: ASHB_STATUS_* bits
+    unsigned long long* cursor;  // device scratch for items()
+    void* small;                 // one allocation backing the three words above
+};
+
+namespace ashb {
+
+inline Table16 table16_of(const ashb_map* m) {
+    return Table16{static_cast<uint4*>(m->slots), (uint32_t)(m->n_slots - 1), m->status};
+}
+
+// Selects the map's device for the scope of a call.
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) ok = false;
+        if (ok && prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+}  // namespace ashb

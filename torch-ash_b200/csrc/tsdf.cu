@@ -1,0 +1,279 @@
+// Fused RGB-D TSDF integration for sm_100a: block allocation from a depth frame
+// and the running weighted average of sdf / colour / weight per cell.
+//
+// It replaces the ~40 torch launches per frame of TSDFFusion.fuse_frame
+// (demo/rgbd_fusion.py:199-254) and project_points_to_rgbd (:76-110), the temporary
+// hash set of SparseDenseGrid.spatial_init_ (ash/grid.py:121-159) and the
+// third-party depth unprojection (demo/rgbd_fusion.py:57-74) with two launches and
+// no host synchronisation:
+//
+//   touch     one thread per depth pixel: unproject with the pinhole model, take the
+//             block of the point, and for every block of the (2*dilation+1)^3
+//             neighbourhood insert-if-absent into the grid's hash table, record the
+//             block coordinate and stamp the block as touched by this frame.  A warp
+//             first elects one lane per distinct block among its 32 pixels, so the
+//             27 probes are issued once per block, not once per pixel.
+//   integrate one CTA per embedding row; CTAs of untouched rows exit at once.  The
+//             10 KB of a block (512 cells x 5 floats) is staged in shared memory with
+//             coalesced 16-byte accesses, every cell is projected into the frame and
+//             fused, and the block is written back the same way.
+#include "hashmap.cuh"
+
+namespace ashb {
+
+struct Camera {
+    float K[9];    // intrinsic, row major
+    float E[12];   // world -> camera, rows of [R | t]
+    float Ei[12];  // camera -> world, rows of [R' | c]
+};
+
+// Every product and sum below is individually rounded (no fused multiply-add), so the
+// block a point falls in and the pixel a cell projects to are bit-reproducible.
+__device__ __forceinline__ float affine3(const float* r, float x, float y, float z) {
+    return __fadd_rn(__fadd_rn(__fadd_rn(__fmul_rn(r[0], x), __fmul_rn(r[1], y)), __fmul_rn(r[2], z)), r[3]);
+}
+__device__ __forceinline__ float dot3(const float* r, float x, float y, float z) {
+    return __fadd_rn(__fadd_rn(__fmul_rn(r[0], x), __fmul_rn(r[1], y)), __fmul_rn(r[2], z));
+}
+
+// ---- touch -------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) tsdf_touch_kernel(Table16 t, int32_t* __restrict__ heap, int32_t* counter,
+                                                         int32_t capacity, const float* __restrict__ depth, int H,
+                                                         int W, Camera cam, float depth_max, float inv_cell,
+                                                         float3 origin, float inv_G, int dilation,
+                                                         int3 lo, int3 hi, int bounded,
+                                                         int32_t* __restrict__ grid_coords,
+                                                         uint32_t* __restrict__ touched, uint32_t stamp) {
+    const int64_t pix = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    bool valid = pix < (int64_t)H * W;
+    int bx = 0, by = 0, bz = 0;
+    if (valid) {
+        const float d = depth[pix];
+        valid = d > 0.f && d < depth_max;
+        if (valid) {
+            const int v = (int)(pix / W), u = (int)(pix - (int64_t)v * W);
+            // camera point of pixel (u, v) at depth d for K = [fx 0 cx; 0 fy cy; 0 0 1]
+            const float xc = __fdiv_rn(__fmul_rn(__fsub_rn((float)u, cam.K[2]), d), cam.K[0]);
+            const float yc = __fdiv_rn(__fmul_rn(__fsub_rn((float)v, cam.K[5]), d), cam.K[4]);
+            const float wx = affine3(cam.Ei, xc, yc, d);
+            const float wy = affine3(cam.Ei + 4, xc, yc, d);
+            const float wz = affine3(cam.Ei + 8, xc, yc, d);
+            // world -> cell -> block as the Python layer does on a CUDA tensor:
+            // multiply by the float reciprocals (ash/grid.py:132-134, :756, :846)
+            bx = (int)floorf(__fmul_rn(__fmul_rn(__fsub_rn(wx, origin.x), inv_cell), inv_G));
+            by = (int)floorf(__fmul_rn(__fmul_rn(__fsub_rn(wy, origin.y), inv_cell), inv_G));
+            bz = (int)floorf(__fmul_rn(__fmul_rn(__fsub_rn(wz, origin.z), inv_cell), inv_G));
+        }
+    }
+    // one lane per distinct block in the warp does the neighbourhood
+    const unsigned active = __ballot_sync(0xffffffffu, valid);
+    if (!valid) return;
+    const unsigned long long packed = ((unsigned long long)(unsigned)bx * 0x9E3779B97F4A7C15ull) ^
+                                      ((unsigned long long)(unsigned)by << 21) ^
+                                      ((unsigned long long)(unsigned)bz << 42) ^ (unsigned)bz;
+    const unsigned peers = __match_any_sync(active, packed);
+    // `packed` is not injective; lanes that collide without being equal just do their own work
+    const int leader = __ffs(peers) - 1;
+    const int lbx = __shfl_sync(peers, bx, leader), lby = __shfl_sync(peers, by, leader),
+              lbz = __shfl_sync(peers, bz, leader);
+    if ((int)(threadIdx.x & 31) != leader && lbx == bx && lby == by && lbz == bz) return;
+
+    for (int dz = -dilation; dz <= dilation; ++dz)
+        for (int dy = -dilation; dy <= dilation; ++dy)
+            for (int dx = -dilation; dx <= dilation; ++dx) {
+                const int kx = bx + dx, ky = by + dy, kz = bz + dz;
+                if (bounded && (kx < lo.x || ky < lo.y || kz < lo.z || kx >= hi.x || ky >= hi.y || kz >= hi.z))
+                    continue;
+                // fast path: the block exists already (probe at L2: this launch mutates the table)
+                int idx = -1;
+                {
+                    uint32_t s = hash_key(kx, ky, kz, 0) & t.mask;
+                    for (uint32_t probe = 0; probe <= t.mask; ++probe) {
+                        const Entry e = t.read_fresh(s);
+                        if (e.val == kEmpty) break;
+                        if (e.val >= 0 && key_match(e, kx, ky, kz, 0)) {
+                            idx = e.val;
+                            break;
+                        }
+                        s = (s + 1) & t.mask;
+                    }
+                }
+                if (idx < 0) {
+                    bool present = false;
+                    const int64_t slot = emplace(t, kx, ky, kz, 0, kPending, &present);
+                    if (slot < 0) continue;  // another thread of this launch owns it and stamps it
+                    const int top = atomicAdd(counter, 1);
+                    if (top >= capacity) {
+                        atomicSub(counter, 1);
+                        *reinterpret_cast<volatile int*>(t.val_ptr((uint32_t)slot)) = kTomb;
+                        atomicOr(t.status, ASHB_STATUS_CAPACITY);
+                        continue;
+                    }
+                    idx = heap[top];
+                    *reinterpret_cast<volatile int*>(t.val_ptr((uint32_t)slot)) = idx;
+                }
+                // the coordinate is recorded for blocks allocated by other means too
+                grid_coords[3 * idx] = kx;
+                grid_coords[3 * idx + 1] = ky;
+                grid_coords[3 * idx + 2] = kz;
+                touched[idx] = stamp;
+            }
+}
+
+// ---- integrate ---------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(256) tsdf_integrate_kernel(
+        float* __restrict__ emb, const int32_t* __restrict__ grid_coords, const uint32_t* __restrict__ touched,
+        uint32_t stamp, const float* __restrict__ depth, const float* __restrict__ color, int H, int W, Camera cam,
+        float depth_max, float cell_size, float3 origin, int G, int cells, float trunc, int sdf_ch, int rgb_ch,
+        int w_ch, unsigned long long* n_integrated) {
+    extern __shared__ float tile[];  // cells * D floats
+    const int64_t idx = blockIdx.x;
+    if (touched[idx] != stamp) return;
+    float* block = emb + idx * (int64_t)cells * D;
+    const int n_float = cells * D;
+    // rows are 16-byte aligned when cells * D * 4 is a multiple of 16
+    const bool vec_ok = (n_float & 3) == 0 && (((uintptr_t)block) & 15) == 0;
+    if (vec_ok) {
+        for (int i = threadIdx.x; i < n_float / 4; i += blockDim.x)
+            reinterpret_cast<float4*>(tile)[i] = reinterpret_cast<const float4*>(block)[i];
+    } else {
+        for (int i = threadIdx.x; i < n_float; i += blockDim.x) tile[i] = block[i];
+    }
+    __syncthreads();
+    const int gx = grid_coords[3 * idx], gy = grid_coords[3 * idx + 1], gz = grid_coords[3 * idx + 2];
+    for (int c = threadIdx.x; c < cells; c += blockDim.x) {
+        const int cx = c % G, cy = (c / G) % G, cz = c / (G * G);
+        // cell_to_world: (block * G + cell) * cell_size (+ origin for bounded grids)
+        const float px = __fadd_rn(__fmul_rn((float)(gx * G + cx), cell_size), origin.x);
+        const float py = __fadd_rn(__fmul_rn((float)(gy * G + cy), cell_size), origin.y);
+        const float pz = __fadd_rn(__fmul_rn((float)(gz * G + cz), cell_size), origin.z);
+        const float x = affine3(cam.E, px, py, pz);
+        const float y = affine3(cam.E + 4, px, py, pz);
+        const float z = affine3(cam.E + 8, px, py, pz);
+        const float un = dot3(cam.K, x, y, z);
+        const float vn = dot3(cam.K + 3, x, y, z);
+        const float d = dot3(cam.K + 6, x, y, z);
+        float w = 0.f, sdf = 0.f, r = 0.f, g = 0.f, b = 0.f;
+        if (d > 0.f) {
+            const float uf = rintf(__fdiv_rn(un, d)), vf = rintf(__fdiv_rn(vn, d));  // torch.round: half to even
+            if (uf >= 0.f && vf >= 0.f && uf < (float)W && vf < (float)H) {
+                const int u = (int)uf, v = (int)vf;
+                const float dr = __ldg(depth + (int64_t)v * W + u);
+                const float* col = color + ((int64_t)v * W + u) * 3;
+                r = __ldg(col), g = __ldg(col + 1), b = __ldg(col + 2);
+                sdf = __fsub_rn(dr, d);
+                if (dr > 0.f && dr < depth_max && sdf >= -trunc) w = 1.f;
+                if (sdf >= trunc) sdf = trunc;
+            }
+        }
+        // outside the image or behind the camera the observation has weight 0 and its
+        // value does not matter (demo/rgbd_fusion.py:93-108)
+        float* cell = tile + c * D;
+        const float w_sum = cell[w_ch];
+        // demo/rgbd_fusion.py:247-249: mean' = (mean * w_sum + obs * w) / (w_sum + w + 1e-6)
+        const float w_new = __fadd_rn(w_sum, w);
+        const float den = __fadd_rn(w_new, 1e-6f);
+        auto fuse = [&](float mean, float obs) {
+            return __fdiv_rn(__fadd_rn(__fmul_rn(mean, w_sum), __fmul_rn(obs, w)), den);
+        };
+        cell[sdf_ch] = fuse(cell[sdf_ch], sdf);
+        cell[rgb_ch] = fuse(cell[rgb_ch], r);
+        cell[rgb_ch + 1] = fuse(cell[rgb_ch + 1], g);
+        cell[rgb_ch + 2] = fuse(cell[rgb_ch + 2], b);
+        cell[w_ch] = w_new;
+    }
+    __syncthreads();
+    if (vec_ok) {
+        for (int i = threadIdx.x; i < n_float / 4; i += blockDim.x)
+            reinterpret_cast<float4*>(block)[i] = reinterpret_cast<const float4*>(tile)[i];
+    } else {
+        for (int i = threadIdx.x; i < n_float; i += blockDim.x) block[i] = tile[i];
+    }
+    if (threadIdx.x == 0 && n_integrated) atomicAdd(n_integrated, 1ull);
+}
+
+}  // namespace ashb
+
+using namespace ashb;
+
+extern "C" {
+
+int ashb_tsdf_touch(ashb_map* m, const float* depth, int H, int W, const float* intrinsic,
+                    const float* cam_to_world, float depth_max, float cell_size, const float* origin, int G,
+                    int dilation, const int32_t* bound_lo, const int32_t* bound_hi, int32_t* grid_coords,
+                    uint32_t* touched, uint32_t stamp, void* stream) {
+    ASHB_REQUIRE(m != nullptr && m->slots != nullptr, "null or destroyed map");
+    ASHB_REQUIRE(m->key_dim == 3, "TSDF integration needs a 3-D map");
+    ASHB_REQUIRE(depth && intrinsic && cam_to_world && origin && grid_coords && touched, "null buffer");
+    ASHB_REQUIRE(H > 0 && W > 0 && G > 0 && cell_size > 0.f && dilation >= 0 && dilation <= 4, "bad frame or grid geometry");
+    ASHB_REQUIRE(stamp != 0, "stamp 0 is reserved for 'never touched'");
+    DeviceGuard guard(m->device);
+    Camera cam{};
+    for (int i = 0; i < 9; ++i) cam.K[i] = intrinsic[i];
+    for (int i = 0; i < 12; ++i) cam.Ei[i] = cam_to_world[i];
+    ASHB_REQUIRE(cam.K[0] != 0.f && cam.K[4] != 0.f && cam.K[1] == 0.f && cam.K[3] == 0.f,
+                 "intrinsic must be a skew-free pinhole matrix");
+    const int bounded = bound_lo != nullptr && bound_hi != nullptr;
+    const int3 lo = bounded ? make_int3(bound_lo[0], bound_lo[1], bound_lo[2]) : make_int3(0, 0, 0);
+    const int3 hi = bounded ? make_int3(bound_hi[0], bound_hi[1], bound_hi[2]) : make_int3(0, 0, 0);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t n = (int64_t)H * W;
+    tsdf_touch_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
+            table16_of(m), m->heap, m->counter, (int32_t)m->capacity, depth, H, W, cam, depth_max,
+            1.0f / cell_size, make_float3(origin[0], origin[1], origin[2]), 1.0f / (float)G, dilation, lo, hi,
+            bounded, grid_coords, touched, stamp);
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+int ashb_tsdf_integrate(void* embeddings, int64_t n_emb, int G, int64_t D, const int32_t* grid_coords,
+                        const uint32_t* touched, uint32_t stamp, const float* depth, const float* color, int H,
+                        int W, const float* intrinsic, const float* world_to_cam, float depth_max,
+                        float cell_size, const float* origin, float trunc, int sdf_channel, int rgb_channel,
+                        int weight_channel, unsigned long long* n_integrated_dev, void* stream) {
+    ASHB_REQUIRE(embeddings && grid_coords && touched && depth && color && intrinsic && world_to_cam && origin,
+                 "null buffer");
+    ASHB_REQUIRE(n_emb >= 1 && G >= 1 && G <= 16 && H > 0 && W > 0, "bad sizes");
+    ASHB_REQUIRE(D >= 5 && D <= 16, "embedding_dim %lld cannot hold sdf + rgb + weight", (long long)D);
+    ASHB_REQUIRE(sdf_channel >= 0 && sdf_channel < D && weight_channel >= 0 && weight_channel < D &&
+                         rgb_channel >= 0 && rgb_channel + 2 < D,
+                 "channel layout out of range");
+    Camera cam{};
+    for (int i = 0; i < 9; ++i) cam.K[i] = intrinsic[i];
+    for (int i = 0; i < 12; ++i) cam.E[i] = world_to_cam[i];
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int cells = G * G * G;
+    const size_t smem = (size_t)cells * D * sizeof(float);
+    ASHB_REQUIRE(smem <= 200 * 1024, "block of %zu bytes does not fit in shared memory", smem);
+    const float3 org = make_float3(origin[0], origin[1], origin[2]);
+#define ASHB_TSDF_LAUNCH(DD)                                                                               \
+    case DD: {                                                                                             \
+        if (smem > 48 * 1024)                                                                              \
+            ASHB_CUDA_TRY(cudaFuncSetAttribute(tsdf_integrate_kernel<DD>,                                  \
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));  \
+        tsdf_integrate_kernel<DD><<<(unsigned)n_emb, 256, smem, st>>>(                                     \
+                static_cast<float*>(embeddings), grid_coords, touched, stamp, depth, color, H, W, cam,     \
+                depth_max, cell_size, org, G, cells, trunc, sdf_channel, rgb_channel, weight_channel,      \
+                n_integrated_dev);                                                                         \
+    } break;
+    switch ((int)D) {
+        ASHB_TSDF_LAUNCH(5)
+        ASHB_TSDF_LAUNCH(6)
+        ASHB_TSDF_LAUNCH(7)
+        ASHB_TSDF_LAUNCH(8)
+        ASHB_TSDF_LAUNCH(9)
+        ASHB_TSDF_LAUNCH(10)
+        ASHB_TSDF_LAUNCH(11)
+        ASHB_TSDF_LAUNCH(12)
+        ASHB_TSDF_LAUNCH(13)
+        ASHB_TSDF_LAUNCH(14)
+        ASHB_TSDF_LAUNCH(15)
+        ASHB_TSDF_LAUNCH(16)
+    }
+#undef ASHB_TSDF_LAUNCH
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+}  // extern "C"
