@@ -228,6 +228,28 @@ int ashb_tsdf_integrate(void* embeddings, int64_t n_emb, int G, int64_t D, const
                         int rgb_channel, int weight_channel, unsigned long long* n_integrated_dev,
                         void* stream);
 
+/* One whole fusion step (allocation + fusion, as the two calls above) that allocates nothing.
+ * It has no counterpart in the reference.  It exists for callers that must not allocate device
+ * memory while they run: a capture or playback loop that reserved all of its memory up front, a
+ * host application whose allocator the library may not touch, or code running where a
+ * cudaMalloc would stall every stream of the device.  The per-block scratch (a stamp word and a
+ * block coordinate) sits in a fixed array inside the library image instead of being passed in,
+ * which limits the grid to ashb_tsdf_static_max_blocks() = 262144 blocks (n_emb beyond that is
+ * rejected with ASHB_ERR_INVALID) and costs 4 MiB on every GPU that loads the library, until
+ * the process exits.  The caller still owns and passes the map, the embeddings and the frame.
+ * The first call on a device looks up the array's device address; make that first call before
+ * any stream capture.  All calls share the one array (it is cleared at the start of each call),
+ * so two calls whose work overlaps on the GPU race with each other: issue them on one stream
+ * or order them yourself.  No cudaMalloc, cudaFree or other allocating routine is called. */
+int ashb_tsdf_static_max_blocks(void);
+int ashb_tsdf_fuse_frame_static(ashb_map* map, void* embeddings, int64_t n_emb, int G, int64_t D,
+                                const float* depth, const float* color, int H, int W,
+                                const float* intrinsic, const float* world_to_cam,
+                                const float* cam_to_world, float depth_max, float cell_size,
+                                const float* origin, int dilation, const int32_t* bound_lo,
+                                const int32_t* bound_hi, float trunc, int sdf_channel, int rgb_channel,
+                                int weight_channel, void* stream);
+
 /* ---------------------------------------------------------------- runtime knobs */
 
 /* cudaLimitMaxL2FetchGranularity of the current context (32, 64 or 128 bytes); a

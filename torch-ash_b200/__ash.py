@@ -55,6 +55,8 @@ _lib.ashb_tsdf_touch.argtypes = [_vp, _vp, _int, _int, _vp, _vp, _f32, _f32, _vp
                                  _c.c_uint32, _vp]
 _lib.ashb_tsdf_integrate.argtypes = [_vp, _i64, _int, _i64, _vp, _vp, _c.c_uint32, _vp, _vp, _int, _int, _vp, _vp,
                                      _f32, _f32, _vp, _f32, _int, _int, _int, _vp, _vp]
+_lib.ashb_tsdf_fuse_frame_static.argtypes = [_vp, _vp, _i64, _int, _i64, _vp, _vp, _int, _int, _vp, _vp, _vp, _f32, _f32,
+                                             _vp, _int, _vp, _vp, _f32, _int, _int, _int, _vp]
 
 STATUS_CAPACITY, STATUS_PROBE, STATUS_SPIN, STATUS_DUPLICATE = 1, 2, 4, 8
 _DTYPES = {torch.float32: 0, torch.float64: 1}
@@ -460,3 +462,37 @@ def tsdf_integrate(embeddings, grid_dim, grid_coords, touched, stamp, depth, col
             int(stamp), depth.data_ptr(), color.data_ptr(), H, W, K, E, float(depth_max), float(cell_size), org,
             float(trunc), int(sdf_channel), int(rgb_channel), int(weight_channel),
             counter.data_ptr() if counter is not None else None, _stream(emb.device)))
+
+
+def tsdf_fuse_frame_static(hashmap, embeddings, grid_dim, depth, color, intrinsic, world_to_cam, cam_to_world,
+                           depth_max, cell_size, origin, dilation, trunc, bound_lo=None, bound_hi=None,
+                           sdf_channel=0, rgb_channel=1, weight_channel=4):
+    """One fusion step without any allocation, on this side or in the library.
+
+    For callers that cannot allocate device memory while running (all memory reserved up
+    front, or an allocation would stall the device): the per-block scratch that
+    ``tsdf_touch`` / ``tsdf_integrate`` take as tensors lives in a fixed array inside the
+    library instead, so grids are limited to ``_lib.ashb_tsdf_static_max_blocks()`` blocks.
+    ``depth`` (H, W) and ``color`` (H, W, 3) must already be contiguous float32 CUDA tensors:
+    nothing is copied or converted here.  Calls share the library's array; do not let two of
+    them overlap on the GPU.  Make the first call on a device outside stream capture.
+    """
+    emb = embeddings
+    if not (emb.is_cuda and emb.dtype == torch.float32 and emb.is_contiguous() and emb.dim() == 3):
+        raise RuntimeError("embeddings must be a contiguous float32 CUDA tensor (blocks, cells, channels)")
+    for name, t in (("depth", depth), ("color", color)):
+        if not (t.is_cuda and t.dtype == torch.float32 and t.is_contiguous()):
+            raise RuntimeError(f"{name} must be a contiguous float32 CUDA tensor (nothing is converted here)")
+    H, W = depth.shape
+    if color.shape != (H, W, 3):
+        raise RuntimeError("color must be (H, W, 3)")
+    K = _host_floats([intrinsic[i][j] for i in range(3) for j in range(3)], 9)
+    E = _host_floats([world_to_cam[i][j] for i in range(3) for j in range(4)], 12)
+    Ei = _host_floats([cam_to_world[i][j] for i in range(3) for j in range(4)], 12)
+    org = _host_floats(origin, 3)
+    lo = (_c.c_int32 * 3)(*bound_lo) if bound_lo is not None else None
+    hi = (_c.c_int32 * 3)(*bound_hi) if bound_hi is not None else None
+    _check(_lib.ashb_tsdf_fuse_frame_static(
+        hashmap._h, emb.data_ptr(), emb.shape[0], int(grid_dim), emb.shape[2], depth.data_ptr(), color.data_ptr(),
+        H, W, K, E, Ei, float(depth_max), float(cell_size), org, int(dilation), lo, hi, float(trunc),
+        int(sdf_channel), int(rgb_channel), int(weight_channel), _stream(hashmap.device())))

@@ -17,7 +17,15 @@
 //             10 KB of a block (512 cells x 5 floats) is staged in shared memory with
 //             coalesced 16-byte accesses, every cell is projected into the frame and
 //             fused, and the block is written back the same way.
+#include <mutex>
+
 #include "hashmap.cuh"
+
+// Scratch of ashb_tsdf_fuse_frame_static: per block one stamp word and one int32x3
+// coordinate.  It lives in the library image, so no allocation is ever made for it; every
+// GPU that loads the library holds these bytes until the process exits.
+#define ASHB_TSDF_STATIC_MAX_BLOCKS 262144
+static __device__ __align__(256) unsigned char g_tsdf_static_scratch[ASHB_TSDF_STATIC_MAX_BLOCKS * 16];
 
 namespace ashb {
 
@@ -274,6 +282,58 @@ int ashb_tsdf_integrate(void* embeddings, int64_t n_emb, int G, int64_t D, const
 #undef ASHB_TSDF_LAUNCH
     ASHB_LAUNCH_CHECK();
     return ASHB_OK;
+}
+
+// Device address of g_tsdf_static_scratch on the current device.  In host code the array's
+// name is only a handle; the address the kernels need comes from cudaGetSymbolAddress, looked
+// up once per device with that device current.
+static int static_scratch_for_current_device(unsigned char** out) {
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static unsigned char* cached[kMaxDevices] = {};
+    int dev = -1;
+    ASHB_CUDA_TRY(cudaGetDevice(&dev));
+    ASHB_REQUIRE(dev >= 0 && dev < kMaxDevices, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == nullptr) {
+        void* p = nullptr;
+        ASHB_CUDA_TRY(cudaGetSymbolAddress(&p, g_tsdf_static_scratch));
+        ASHB_REQUIRE(p != nullptr, "static scratch has no device address");
+        cached[dev] = static_cast<unsigned char*>(p);
+    }
+    *out = cached[dev];
+    return ASHB_OK;
+}
+
+int ashb_tsdf_static_max_blocks(void) { return ASHB_TSDF_STATIC_MAX_BLOCKS; }
+
+int ashb_tsdf_fuse_frame_static(ashb_map* m, void* embeddings, int64_t n_emb, int G, int64_t D,
+                                const float* depth, const float* color, int H, int W, const float* intrinsic,
+                                const float* world_to_cam, const float* cam_to_world, float depth_max,
+                                float cell_size, const float* origin, int dilation, const int32_t* bound_lo,
+                                const int32_t* bound_hi, float trunc, int sdf_channel, int rgb_channel,
+                                int weight_channel, void* stream) {
+    ASHB_REQUIRE(m != nullptr && m->slots != nullptr, "null or destroyed map");
+    ASHB_REQUIRE(n_emb >= 1 && n_emb <= ASHB_TSDF_STATIC_MAX_BLOCKS,
+                 "ashb_tsdf_fuse_frame_static handles at most %d blocks (got %lld); use ashb_tsdf_touch + "
+                 "ashb_tsdf_integrate with caller-provided scratch for larger grids",
+                 ASHB_TSDF_STATIC_MAX_BLOCKS, (long long)n_emb);
+    ASHB_REQUIRE(n_emb == m->capacity, "n_emb must equal the map's capacity");
+    DeviceGuard guard(m->device);
+    unsigned char* scratch = nullptr;
+    if (int rc = static_scratch_for_current_device(&scratch)) return rc;
+    uint32_t* touched = reinterpret_cast<uint32_t*>(scratch);
+    int32_t* coords = reinterpret_cast<int32_t*>(scratch + (size_t)ASHB_TSDF_STATIC_MAX_BLOCKS * 4);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // The array is shared by every call and keeps the previous call's stamps: start from zero.
+    ASHB_CUDA_TRY(cudaMemsetAsync(touched, 0, (size_t)n_emb * sizeof(uint32_t), st));
+    const uint32_t stamp = 1;
+    if (int rc = ashb_tsdf_touch(m, depth, H, W, intrinsic, cam_to_world, depth_max, cell_size, origin, G, dilation,
+                                 bound_lo, bound_hi, coords, touched, stamp, stream))
+        return rc;
+    return ashb_tsdf_integrate(embeddings, n_emb, G, D, coords, touched, stamp, depth, color, H, W, intrinsic,
+                               world_to_cam, depth_max, cell_size, origin, trunc, sdf_channel, rgb_channel,
+                               weight_channel, nullptr, stream);
 }
 
 }  // extern "C"
