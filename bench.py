@@ -4,8 +4,9 @@
 
 Workload ("trilinear query microbench"): 500k active blocks, grid_dim 8, embedding_dim 16 fp32
 ~ N(0, 0.01), 4M query points uniform inside the active blocks, linear interpolation; one step
-is forward + backward (gradient w.r.t. embeddings AND offsets, a fresh dense gradient tensor per
-step exactly as the reference's autograd contract demands).  Per GPU the table is 16.4 GB, far
+is forward + backward from the query positions (split, hash find, gather, interpolation; gradient
+w.r.t. embeddings AND positions, a fresh dense gradient tensor per step exactly as the reference's
+autograd contract demands).  Per GPU the table is 16.4 GB, far
 beyond L2, and the query batches rotate, so no step re-reads a warm cache.  With N > 1 every rank
 holds a replica of the grid and works on its own 4M-query shard (weak scaling, no collective
 on the data path; the cost of synchronising the dense gradient is reported separately).
@@ -223,33 +224,33 @@ def main():
     peak, peak_kind = measured_peak_gbs()
     grid, blocks = build_grid(ash, bw, device, N_BLOCKS)
     emb = grid.embeddings.detach()
-    luts = (grid.lut_grid_nb2grid_idx, grid.lut_cell_nb2cell_idx, grid.lut_cell_nb2grid_nb)
+    hm, lut32 = grid.engine.backend, grid._neighbor_lut32()
+    origin, cell_size = grid._cell_frame()
     n_batches = 4
     xs = [bw.points_in_blocks(blocks, N_QUERIES, GRID_DIM, 1.0, device, seed=bw.SEED + 100 * rank + s)
-          for s in range(n_batches)]
-    split = [grid.query(x) for x in xs]  # (grid_indices, cell_indices, offsets, masks), resident in HBM
+          for s in range(n_batches)]  # positions, resident in HBM: the input of the path
     z = torch.ones(N_QUERIES, EMB_DIM, device=device)
     # share of queries answered with a zero row because a +x/+y/+z neighbour block is absent
-    y0 = __ash.query_forward(emb, split[0][2], split[0][0], split[0][1], split[0][3], *luts, GRID_DIM, "linear")
-    zero_rows = float(((y0 == 0).all(dim=1) & split[0][3]).float().mean())
-    del y0
+    y0, m0, _ = __ash.grid_query_forward(hm, emb, xs[0], cell_size, origin, GRID_DIM, lut32, "linear")
+    zero_rows = float(((y0 == 0).all(dim=1) & m0).float().mean())
+    del y0, m0
 
     fwd_ms, bwd_ms, bwd_persist_ms = [], [], []
     marks = []  # (before fwd, between, after bwd) events of every timed step; read after the region
 
     def step(i, record):
-        gi, ci, off, mk = split[i % n_batches]
+        x = xs[i % n_batches]
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if record else None
         if record:
             ev[0].record()
-        y = __ash.query_forward(emb, off, gi, ci, mk, *luts, GRID_DIM, "linear")
+        y, masks, bidx = __ash.grid_query_forward(hm, emb, x, cell_size, origin, GRID_DIM, lut32, "linear")
         if record:
             ev[1].record()
-        grad_emb, grad_off = __ash.query_backward_forward(z, emb, off, gi, ci, mk, *luts, GRID_DIM, "linear")
+        grad_emb, grad_x = __ash.grid_query_backward(hm, z, emb, x, cell_size, origin, GRID_DIM, lut32, bidx, "linear")
         if record:
             ev[2].record()
             marks.append(ev)
-        del y, grad_emb, grad_off
+        del y, masks, bidx, grad_emb, grad_x
 
     def barrier():
         if dist is not None:
@@ -280,9 +281,10 @@ def main():
     # persistent-gradient variant: accumulate into one long-lived buffer, no per-step zero-fill
     gacc = torch.zeros_like(emb)
     for i in range(args.warmup + args.steps):
-        gi, ci, off, mk = split[i % n_batches]
-        t = event_ms(lambda: __ash.query_backward_forward(z, emb, off, gi, ci, mk, *luts, GRID_DIM, "linear",
-                                                           grad_embeddings_out=gacc))
+        x = xs[i % n_batches]
+        _, _, bidx = __ash.grid_query_forward(hm, emb, x, cell_size, origin, GRID_DIM, lut32, "linear")
+        t = event_ms(lambda: __ash.grid_query_backward(hm, z, emb, x, cell_size, origin, GRID_DIM, lut32, bidx,
+                                                       "linear", grad_embeddings_out=gacc))
         if i >= args.warmup:
             bwd_persist_ms.append(t)
     barrier()
@@ -334,7 +336,7 @@ def main():
         f_ms, b_ms, bp_ms = statistics.mean(fwd_ms), statistics.mean(bwd_ms), statistics.mean(bwd_persist_ms)
         achieved = N_QUERIES * BWD_BYTES / (bp_ms * 1e-3) / 1e9
         line["roofline"] = {
-            "kernel": "query_backward_forward_kernel<float,4>", "bound": "hbm", "achieved": round(achieved, 1),
+            "kernel": "query_backward_forward_kernel<float,4,FusedSource>", "bound": "hbm", "achieved": round(achieved, 1),
             "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4), "peak_kind": peak_kind,
             "traffic": None, "ms_per_launch": round(bp_ms, 4),
             "note": "dominant kernel of the library; timed alone on a persistent gradient buffer "
@@ -359,7 +361,7 @@ def main():
             line["grad_allreduce_ms"] = round(allreduce_ms, 3)
 
     # free the grid before the hash-engine measurement
-    del grid, emb, split, xs, x_host, z, luts
+    del grid, emb, xs, x_host, z, lut32, hm
     torch.cuda.empty_cache()
 
     if rank == 0 and not args.no_hash:

@@ -155,6 +155,45 @@ int ashb_query_backward_backward(int dtype, int interp, const void* grad_grad_of
                                  void* grad_embeddings, int zero_grad, int64_t n, int64_t n_emb,
                                  int64_t cells_per_grid, int64_t D, void* stream);
 
+/* ---------------------------------------------------------------- fused grid query
+ * Positions in, features out: the work of SparseDenseGrid.forward (ash/grid.py:201-238) --
+ * world -> cell transform, block / cell / offset split (ash/grid.py:183-199), hash find of the
+ * block, neighbour resolution, gather and interpolation -- in one launch instead of ~15 torch
+ * launches + find + query_forward.  x float32 [n][3] world positions; cell = (x - origin) *
+ * (1 / cell_size) with origin a HOST float[3] (NULL = zero); nb_lut int32 [n_emb][8]: index of
+ * the block at offset (bit0, bit1, bit2) of the column, -1 absent (column 0 is the block
+ * itself); the map must have key_dim 3.  Results are identical to the split + pre-split entry
+ * points above. */
+
+/* Builds nb_lut (and optionally grid_coords int32 [n_emb][3], -1 rows for inactive indices)
+ * from the map; replaces SparseDenseGrid.construct_grid_neighbor_lut(radius=1,
+ * bidirectional=False) (ash/grid.py:566-617). */
+int ashb_grid_build_neighbor_lut(ashb_map* map, int32_t* nb_lut, int32_t* grid_coords, int64_t n_emb,
+                                 void* stream);
+
+/* out [n][D]; masks uint8 [n] = hash hit (a query whose neighbour block is absent keeps mask 1
+ * and gets a zero row, as ash/src/grid.cu:109-111); block_idx_out int32 [n] (optional) = block
+ * index per query, -1 on a miss, to be handed to the two backward entry points. */
+int ashb_grid_query_forward(ashb_map* map, int dtype, int interp, const void* embeddings, const float* x,
+                            float cell_size, const float* origin, int G, const int32_t* nb_lut, void* out,
+                            uint8_t* masks, int32_t* block_idx_out, int64_t n, int64_t n_emb, int64_t D,
+                            void* stream);
+
+/* grad_x [n][3] (type of embeddings) = d/d offsets * (1 / cell_size), fully written; pass NULL
+ * when the positions need no gradient and the eight embedding rows per query are not read at
+ * all.  grad_embeddings accumulated (zero_grad as above).  block_idx NULL = probe the map again. */
+int ashb_grid_query_backward(ashb_map* map, int dtype, int interp, const void* z, const void* embeddings,
+                             const float* x, float cell_size, const float* origin, int G,
+                             const int32_t* nb_lut, const int32_t* block_idx, void* grad_embeddings,
+                             void* grad_x, int zero_grad, int64_t n, int64_t n_emb, int64_t D, void* stream);
+
+/* grad_grad_x [n][3] (type of embeddings): gradient arriving at grad_x. */
+int ashb_grid_query_backward_backward(ashb_map* map, int dtype, int interp, const void* grad_grad_x,
+                                      const void* z, const void* embeddings, const float* x,
+                                      float cell_size, const float* origin, int G, const int32_t* nb_lut,
+                                      const int32_t* block_idx, void* grad_z, void* grad_embeddings,
+                                      int zero_grad, int64_t n, int64_t n_emb, int64_t D, void* stream);
+
 /* ---------------------------------------------------------------- neighbourhood convolution */
 
 /* Replaces convolution_forward_kernel + convolution_forward (ash/src/grid.cu:951-1043).

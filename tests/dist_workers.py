@@ -1,0 +1,103 @@
+"""Worker bodies of the multi-process tests (importable by spawned children)."""
+import os
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+
+def _keys(seed, n, dim=3, span=40):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(-span, span, (n, dim), generator=g, dtype=torch.int32)
+
+
+def partitioned_hash_worker(rank, world, port, backend, use_cuda):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    if use_cuda:
+        torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank) if use_cuda else torch.device("cpu")
+    dist.init_process_group(backend, rank=rank, world_size=world)
+    try:
+        import oracle
+        from ash.distributed import PartitionedHashMap, owner_of, shard_rows
+
+        pm = PartitionedHashMap(3, 20000, device)
+        # every rank inserts ITS OWN batch (different sizes, overlapping keys, duplicates)
+        batches = [_keys(100 + r, 3000 + 500 * r) for r in range(world)]
+        pm.insert_keys(batches[rank].to(device))
+        # the single-map oracle holding the union
+        om = oracle.OracleHashMap(3, 40000)
+        for b in batches:
+            om.insert_keys(b.numpy())
+        assert pm.size() == om.size()
+        # each rank asks about its own query batch
+        q = _keys(900 + rank, 4000 + 300 * rank, span=45)
+        gidx, masks = pm.find(q.to(device))
+        _, omask = om.find(q.numpy())
+        assert np.array_equal(masks.cpu().numpy(), omask)
+        assert (gidx[~masks] == 0).all()
+        # the same key has the same global index whoever asks, distinct keys have distinct ones
+        common = _keys(7, 2500, span=42)
+        cg, cm = pm.find(common.to(device))
+        gathered = [torch.empty_like(cg) for _ in range(world)]
+        dist.all_gather(gathered, cg)
+        for g in gathered:
+            assert torch.equal(g, gathered[0])
+        hit = cm.cpu().numpy()
+        uk = {tuple(k) for k in common.numpy()[hit]}
+        assert len(set(cg.cpu().numpy()[hit].tolist())) == len(uk)
+        owner, local = pm.split_global_index(cg[cm])
+        assert torch.equal(owner, owner_of(common.to(device)[cm], world))
+        # owners hold exactly their keys
+        lk, lg = pm.local_items()
+        assert (owner_of(lk, world) == rank).all() and (torch.remainder(lg, world) == rank).all()
+        # erase from one rank only (others pass an empty batch), then everybody sees it gone
+        gone = batches[0][:700]
+        pm.erase(gone.to(device) if rank == 0 else torch.empty((0, 3), dtype=torch.int32, device=device))
+        om.erase(gone.numpy())
+        assert pm.size() == om.size()
+        _, m2 = pm.find(q.to(device))
+        assert np.array_equal(m2.cpu().numpy(), om.find(q.numpy())[1])
+        # shard_rows partitions a batch without loss
+        x = torch.arange(1001).view(-1, 1)
+        parts = [shard_rows(x, r, world) for r in range(world)]
+        assert torch.equal(torch.cat(parts), x)
+    finally:
+        dist.destroy_process_group()
+
+
+def replicated_grid_worker(rank, world, port, backend, use_cuda):
+    """Sharded queries over a replicated grid + summed gradients == one process on the whole batch."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    if use_cuda:
+        torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank) if use_cuda else torch.device("cpu")
+    dist.init_process_group(backend, rank=rank, world_size=world)
+    try:
+        import ash
+        from ash.distributed import allreduce_gradients, shard_rows
+
+        torch.manual_seed(0)  # identical replicas
+        G, D = 4, 3
+        grid = ash.SparseDenseGrid(3, 64, D, G, device)
+        r = torch.arange(-1, 2, dtype=torch.int32)
+        blocks = torch.stack(torch.meshgrid(r, r, r, indexing="ij"), -1).view(-1, 3)
+        grid.engine.insert_keys(blocks.to(device))
+        idx, ok = grid.engine.find(blocks.to(device))
+        vals = torch.randn(27, G**3, D)
+        with torch.no_grad():
+            grid.embeddings[idx] = vals.to(device)
+        x = (torch.rand(600, 3) * 3 - 1.2) * G
+        y, _ = grid(shard_rows(x, rank, world).to(device), "linear")
+        (y * y).sum().backward()
+        allreduce_gradients(grid)
+        summed = grid.embeddings.grad[idx].cpu()
+        # one process, whole batch
+        grid.embeddings.grad = None
+        y_all, _ = grid(x.to(device), "linear")
+        (y_all * y_all).sum().backward()
+        torch.testing.assert_close(summed, grid.embeddings.grad[idx].cpu(), rtol=1e-4, atol=1e-5)
+    finally:
+        dist.destroy_process_group()

@@ -1,0 +1,24 @@
+"""The same multi-process checks on GPUs with NCCL; skipped unless two GPUs are visible."""
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+import dist_workers
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_partitioned_hash_map_nccl():
+    mp.spawn(dist_workers.partitioned_hash_worker, args=(2, _free_port(), "nccl", True), nprocs=2, join=True)
+
+
+def test_replicated_grid_gradient_sum_nccl():
+    mp.spawn(dist_workers.replicated_grid_worker, args=(2, _free_port(), "nccl", True), nprocs=2, join=True)

@@ -1,0 +1,117 @@
+"""The fused grid query (positions in, features out, one launch) against the reference's call
+sequence -- Python split + hash find + pre-split kernel -- which the other GPU tests pin against
+the oracle.  Values must agree exactly in the forward pass (same arithmetic, same order) and within
+the scatter-order tolerance in the gradients."""
+import numpy as np
+import pytest
+import torch
+
+import bench_workloads as bw
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+
+
+def _make(kind, G, D, seed):
+    import ash
+
+    n_blocks = 400
+    if kind == "plain":
+        grid = ash.SparseDenseGrid(3, 2 * n_blocks, D, G, DEV)
+        scale = 1.0
+    elif kind == "unbounded":
+        grid = ash.UnBoundedSparseDenseGrid(3, 2 * n_blocks, D, G, cell_size=0.037, device=DEV)
+        scale = 0.037
+    else:
+        grid = ash.BoundedSparseDenseGrid(3, 2 * n_blocks, D, grid_dim=G, sparse_grid_dim=12,
+                                          bbox_min=torch.tensor([-1.0, -0.5, 0.25]), bbox_max=torch.tensor([1.0, 1.5, 2.5]),
+                                          device=DEV)
+        scale = grid.cell_size
+    blocks = bw.block_coords_blob(n_blocks, DEV, n_blobs=3, seed=seed)
+    if kind == "bounded":
+        blocks = (blocks - blocks.min(dim=0)[0]).clamp_(0, 11)
+        blocks = torch.unique(blocks, dim=0)
+    grid.engine.insert_keys(blocks)
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    with torch.no_grad():
+        grid.embeddings.copy_(torch.randn(grid.embeddings.shape, generator=g, device=DEV))
+    grid.construct_grid_neighbor_lut_(1, False)
+    # positions around the active blocks, reaching outside them (misses) and across faces
+    pick = torch.randint(blocks.shape[0], (5000,), generator=g, device=DEV)
+    cell = (blocks[pick].float() + torch.rand(5000, 3, generator=g, device=DEV) * 1.6 - 0.3) * G
+    x = grid.transform_cell_to_world(cell).contiguous()
+    return grid, x
+
+
+@pytest.mark.parametrize("kind", ["plain", "unbounded", "bounded"])
+@pytest.mark.parametrize("G,D", [(8, 16), (8, 1), (4, 5), (2, 3), (1, 2)])
+@pytest.mark.parametrize("interp", ["linear", "smooth_step"])
+def test_fused_equals_split_sequence(kind, G, D, interp):
+    grid, x = _make(kind, G, D, seed=G * 7 + D)
+    gen = torch.Generator(device=DEV).manual_seed(1)
+
+    def run(fused):
+        grid.fused = fused
+        grid.embeddings.grad = None
+        xr = x.clone().requires_grad_(True)
+        y, m = grid(xr, interp)
+        w = torch.rand(y.shape, generator=torch.Generator(device=DEV).manual_seed(2), device=DEV) - 0.5
+        (gx,) = torch.autograd.grad((y * w).sum(), xr, create_graph=True)
+        (y * w).sum().backward(retain_graph=True)
+        ge = grid.embeddings.grad.clone()
+        grid.embeddings.grad = None
+        ((gx.norm(dim=-1) - 1) ** 2).mean().backward()
+        ge2 = grid.embeddings.grad.clone()
+        return y.detach(), m, gx.detach(), ge, ge2
+
+    y_f, m_f, gx_f, ge_f, ge2_f = run(True)
+    y_s, m_s, gx_s, ge_s, ge2_s = run(False)
+    assert torch.equal(m_f, m_s) and 0 < m_f.sum() < len(x)
+    assert torch.equal(y_f, y_s)
+    scale = max(1.0, float(gx_s.abs().max()))
+    torch.testing.assert_close(gx_f, gx_s, rtol=1e-5, atol=1e-6 * scale)
+    torch.testing.assert_close(ge_f, ge_s, rtol=4e-5, atol=4e-6)
+    torch.testing.assert_close(ge2_f, ge2_s, rtol=2e-4, atol=1e-5 * max(1.0, float(ge2_s.abs().max())))
+
+
+def test_native_neighbor_table_equals_python_construction():
+    grid, _ = _make("plain", 8, 2, seed=5)
+    coords_py, lut_py = grid.construct_grid_neighbor_lut(1, False)  # items + find(8n) + scatter, ash/grid.py:566-617
+    grid.construct_grid_neighbor_lut_(1, False)                      # native table scan
+    assert torch.equal(grid.lut_grid_nb2grid_idx, lut_py)
+    assert torch.equal(grid.grid_coords, coords_py)
+    assert grid.lut_grid_nb2grid_idx.dtype == torch.int64 and grid.grid_coords.dtype == torch.int32
+    # column 0 is the block itself for active rows
+    _, idx = grid.engine.items()
+    assert torch.equal(lut_py[idx, 0], idx)
+
+
+def test_fused_float64_and_tiny_negative_positions():
+    import ash
+
+    grid = ash.SparseDenseGrid(3, 64, 3, 4, DEV)
+    grid.engine.insert_keys(torch.tensor([[-1, -1, -1], [0, 0, 0], [-1, 0, 0], [0, -1, 0], [0, 0, -1], [-1, -1, 0],
+                                          [-1, 0, -1], [0, -1, -1]], dtype=torch.int32, device=DEV))
+    grid.embeddings = torch.nn.Parameter(torch.randn(64, 64, 3, device=DEV, dtype=torch.float64))
+    # -1e-9 / 4 floors to block -1, but -1e-9 - (-1 * 4) rounds to exactly 4.0 in float32: the cell is clamped
+    x = torch.tensor([[-1e-9, 0.5, 0.5], [1.5, -1e-9, 2.0], [0.0, 0.0, 0.0], [-0.25, -0.25, -0.25]], device=DEV)
+    for fused in (True, False):
+        grid.fused = fused
+        y, m = grid(x, "linear")
+        assert m.all() and torch.isfinite(y).all() and y.dtype == torch.float64
+        if fused:
+            y_fused = y.detach()
+    assert torch.equal(y_fused, y.detach())
+
+
+def test_scatter_only_backward_when_positions_need_no_gradient():
+    grid, x = _make("unbounded", 8, 16, seed=3)
+    grads = []
+    for needs in (True, False):
+        grid.embeddings.grad = None
+        xr = x.clone().requires_grad_(needs)
+        y, _ = grid(xr, "smooth_step")
+        (y * y).sum().backward()
+        grads.append(grid.embeddings.grad.clone())
+        assert (xr.grad is not None) == needs
+    torch.testing.assert_close(grads[0], grads[1], rtol=4e-5, atol=4e-6)

@@ -57,6 +57,12 @@ _lib.ashb_tsdf_integrate.argtypes = [_vp, _i64, _int, _i64, _vp, _vp, _c.c_uint3
                                      _f32, _f32, _vp, _f32, _int, _int, _int, _vp, _vp]
 _lib.ashb_tsdf_fuse_frame_static.argtypes = [_vp, _vp, _i64, _int, _i64, _vp, _vp, _int, _int, _vp, _vp, _vp, _f32, _f32,
                                              _vp, _int, _vp, _vp, _f32, _int, _int, _int, _vp]
+_lib.ashb_grid_build_neighbor_lut.argtypes = [_vp, _vp, _vp, _i64, _vp]
+_lib.ashb_grid_query_forward.argtypes = [_vp, _int, _int, _vp, _vp, _f32, _vp, _int, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]
+_lib.ashb_grid_query_backward.argtypes = [_vp, _int, _int, _vp, _vp, _vp, _f32, _vp, _int, _vp, _vp, _vp, _vp, _int,
+                                          _i64, _i64, _i64, _vp]
+_lib.ashb_grid_query_backward_backward.argtypes = [_vp, _int, _int, _vp, _vp, _vp, _vp, _f32, _vp, _int, _vp, _vp, _vp,
+                                                   _vp, _int, _i64, _i64, _i64, _vp]
 
 STATUS_CAPACITY, STATUS_PROBE, STATUS_SPIN, STATUS_DUPLICATE = 1, 2, 4, 8
 _DTYPES = {torch.float32: 0, torch.float64: 1}
@@ -496,3 +502,92 @@ def tsdf_fuse_frame_static(hashmap, embeddings, grid_dim, depth, color, intrinsi
         hashmap._h, emb.data_ptr(), emb.shape[0], int(grid_dim), emb.shape[2], depth.data_ptr(), color.data_ptr(),
         H, W, K, E, Ei, float(depth_max), float(cell_size), org, int(dilation), lo, hi, float(trunc),
         int(sdf_channel), int(rgb_channel), int(weight_channel), _stream(hashmap.device())))
+
+
+# ---------------------------------------------------------------------------------------------
+# Fused grid query: additions with no counterpart in the reference's native module.  They do in
+# one launch what SparseDenseGrid.forward does with ~15 torch launches + find + query_forward.
+
+def grid_build_neighbor_lut(hashmap, num_embeddings, with_coords=False):
+    """int32 (num_embeddings, 8) block-neighbour table (and optionally the (num_embeddings, 3)
+    block coordinates), -1 for absent; the content of ash/grid.py:566-617 for radius 1, one-sided."""
+    dev = hashmap.device()
+    lut = torch.empty((num_embeddings, 8), dtype=torch.int32, device=dev)
+    coords = torch.empty((num_embeddings, 3), dtype=torch.int32, device=dev) if with_coords else None
+    _check(_lib.ashb_grid_build_neighbor_lut(
+        hashmap._h, lut.data_ptr(), coords.data_ptr() if with_coords else None, num_embeddings, _stream(dev)))
+    return (lut, coords) if with_coords else lut
+
+
+def _fused_args(hashmap, embeddings, x, nb_lut):
+    emb = _cuda(embeddings, "embeddings")
+    if emb.dim() != 3 or emb.device != hashmap.device():
+        raise RuntimeError("embeddings must be (num_embeddings, cells_per_grid, embedding_dim) on the map's device")
+    x = _cuda(x, "x", torch.float32)
+    if x.dim() != 2 or x.shape[1] != 3:
+        raise RuntimeError("x must be (N, 3)")
+    nb_lut = _cuda(nb_lut, "nb_lut", torch.int32)
+    if nb_lut.shape != (emb.shape[0], 8):
+        raise RuntimeError("nb_lut must be int32 (num_embeddings, 8)")
+    return emb, x, nb_lut
+
+
+def grid_query_forward(hashmap, embeddings, x, cell_size, origin, grid_dim, nb_lut, interpolation):
+    """Returns (features (N, D), masks bool (N,), block_idx int32 (N,))."""
+    emb, x, nb_lut = _fused_args(hashmap, embeddings, x, nb_lut)
+    n, dev = x.shape[0], emb.device
+    out = torch.empty((n, emb.shape[2]), dtype=emb.dtype, device=dev)
+    masks = torch.empty(n, dtype=torch.bool, device=dev)
+    bidx = torch.empty(n, dtype=torch.int32, device=dev)
+    _check(_lib.ashb_grid_query_forward(
+        hashmap._h, _dtype_code(emb), _interp_code(interpolation), emb.data_ptr(), x.data_ptr(), float(cell_size),
+        _host_floats(origin, 3), int(grid_dim), nb_lut.data_ptr(), out.data_ptr(), masks.data_ptr(), bidx.data_ptr(),
+        n, emb.shape[0], emb.shape[2], _stream(dev)))
+    return out, masks, bidx
+
+
+def grid_query_backward(hashmap, z, embeddings, x, cell_size, origin, grid_dim, nb_lut, block_idx, interpolation,
+                        grad_embeddings_out=None, need_grad_x=True):
+    """Returns (grad_embeddings, grad_x (N, 3) in the embeddings' dtype, or None if not needed)."""
+    emb, x, nb_lut = _fused_args(hashmap, embeddings, x, nb_lut)
+    n, dev = x.shape[0], emb.device
+    z = _cuda(z, "z", emb.dtype)
+    if z.shape != (n, emb.shape[2]):
+        raise RuntimeError("z must be (num_queries, embedding_dim)")
+    if grad_embeddings_out is None:
+        grad_emb, zero = torch.empty_like(emb), 1
+    else:
+        grad_emb, zero = grad_embeddings_out, 0
+        if grad_emb.shape != emb.shape or grad_emb.dtype != emb.dtype or not grad_emb.is_contiguous():
+            raise RuntimeError("grad_embeddings_out must match embeddings")
+    grad_x = torch.empty((n, 3), dtype=emb.dtype, device=dev) if need_grad_x else None
+    bidx = _cuda(block_idx, "block_idx", torch.int32) if block_idx is not None else None
+    _check(_lib.ashb_grid_query_backward(
+        hashmap._h, _dtype_code(emb), _interp_code(interpolation), z.data_ptr(), emb.data_ptr(), x.data_ptr(),
+        float(cell_size), _host_floats(origin, 3), int(grid_dim), nb_lut.data_ptr(),
+        bidx.data_ptr() if bidx is not None else None, grad_emb.data_ptr(),
+        grad_x.data_ptr() if need_grad_x else None, zero, n, emb.shape[0], emb.shape[2], _stream(dev)))
+    return grad_emb, grad_x
+
+
+def grid_query_backward_backward(hashmap, grad_grad_x, z, embeddings, x, cell_size, origin, grid_dim, nb_lut,
+                                 block_idx, interpolation, grad_embeddings_out=None):
+    """Returns (grad_z, grad_embeddings); the gradient w.r.t. x is dropped as in the reference."""
+    emb, x, nb_lut = _fused_args(hashmap, embeddings, x, nb_lut)
+    n, dev = x.shape[0], emb.device
+    z = _cuda(z, "z", emb.dtype)
+    ggx = _cuda(grad_grad_x, "grad_grad_x", emb.dtype)
+    if z.shape != (n, emb.shape[2]) or ggx.shape != (n, 3):
+        raise RuntimeError("z must be (num_queries, embedding_dim) and grad_grad_x (num_queries, 3)")
+    if grad_embeddings_out is None:
+        grad_emb, zero = torch.empty_like(emb), 1
+    else:
+        grad_emb, zero = grad_embeddings_out, 0
+    grad_z = torch.empty_like(z)
+    bidx = _cuda(block_idx, "block_idx", torch.int32) if block_idx is not None else None
+    _check(_lib.ashb_grid_query_backward_backward(
+        hashmap._h, _dtype_code(emb), _interp_code(interpolation), ggx.data_ptr(), z.data_ptr(), emb.data_ptr(),
+        x.data_ptr(), float(cell_size), _host_floats(origin, 3), int(grid_dim), nb_lut.data_ptr(),
+        bidx.data_ptr() if bidx is not None else None, grad_z.data_ptr(), grad_emb.data_ptr(), zero, n, emb.shape[0],
+        emb.shape[2], _stream(dev)))
+    return grad_z, grad_emb

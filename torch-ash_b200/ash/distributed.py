@@ -1,0 +1,143 @@
+"""Multi-GPU scaling of the hash engine and the grid query (one process per GPU).
+
+The reference is single-process, single-GPU (no collective anywhere in its tree); this module
+is new.  Two schemes, both on ``torch.distributed`` (NCCL over NVLink/NVSwitch on GPUs; any
+backend works, which is how the host logic is tested with gloo on CPU):
+
+* ``PartitionedHashMap`` -- a hash map too large for one GPU, partitioned by a hash of the key.
+  Rank ``owner(key)`` holds the key in a local ``ASHEngine`` of ``ceil(capacity / P * slack)``
+  entries.  insert / find / erase route keys to their owners with one all-to-all of counts
+  and one all-to-all(v) of the packed int32 keys; find routes ``(index, mask)`` back the same
+  way.  Remote data always lands in local memory through the collective before a kernel reads
+  it.  A global index is ``local_index * P + owner``.
+* Replicated grid, sharded queries -- every rank holds the whole grid and queries its own shard
+  of the batch with no communication; ``allreduce_gradients`` sums the embedding gradients
+  afterwards (dense all-reduce: right for tables up to a few GB).
+"""
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .core import ASHEngine
+
+
+def owner_of(keys: torch.Tensor, world_size: int) -> torch.Tensor:
+    """Owner rank per key: a multiplicative mix of the columns, independent of the slot hash
+    the local tables use, reduced modulo the world size."""
+    k = keys.to(torch.int64)
+    primes = (73856093, 19349663, 83492791, 2654435761)
+    h = torch.zeros(k.shape[0], dtype=torch.int64, device=k.device)
+    for d in range(k.shape[1]):
+        h = h ^ (k[:, d] * primes[d % 4])
+    h = (h ^ (h >> 15)) * 0x2C1B3C6D
+    h = h ^ (h >> 12)
+    return torch.remainder(h, world_size)
+
+
+class _Route:
+    """One all-to-all(v) pattern: which rows go where, and how to bring answers back."""
+
+    def __init__(self, dest: torch.Tensor, group) -> None:
+        world = dist.get_world_size(group)
+        self.group = group
+        self.order = torch.argsort(dest, stable=True)          # rows grouped by destination
+        send = torch.bincount(dest, minlength=world)
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=group)        # how many rows every peer sends me
+        self.send_counts = send.tolist()
+        self.recv_counts = recv.tolist()
+        self.n_recv = int(sum(self.recv_counts))
+
+    def forward(self, rows: torch.Tensor) -> torch.Tensor:
+        """Send ``rows`` (N, C) to their destinations; returns what this rank received."""
+        out = torch.empty((self.n_recv,) + tuple(rows.shape[1:]), dtype=rows.dtype, device=rows.device)
+        dist.all_to_all_single(out, rows[self.order].contiguous(), self.recv_counts, self.send_counts, group=self.group)
+        return out
+
+    def backward(self, answers: torch.Tensor) -> torch.Tensor:
+        """Return per-received-row ``answers`` to the ranks that asked, in their original order."""
+        n_send = int(sum(self.send_counts))
+        back = torch.empty((n_send,) + tuple(answers.shape[1:]), dtype=answers.dtype, device=answers.device)
+        dist.all_to_all_single(back, answers.contiguous(), self.send_counts, self.recv_counts, group=self.group)
+        out = torch.empty_like(back)
+        out[self.order] = back
+        return out
+
+
+class PartitionedHashMap:
+    """Key-hash-partitioned hash map over the ranks of ``group``.
+
+    Every rank calls every method collectively with ITS OWN batch of keys (batches may differ in
+    size, including empty).  ``find`` answers in the caller's order.
+    """
+
+    def __init__(self, key_dim: int, capacity: int, device, group=None, slack: float = 1.25):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.key_dim = key_dim
+        self.capacity = capacity
+        self.local_capacity = int(-(-capacity // self.world) * slack) + 64
+        self.engine = ASHEngine(key_dim, self.local_capacity, device)
+        self.device = self.engine.device
+
+    def _route(self, keys: torch.Tensor) -> Tuple[_Route, torch.Tensor]:
+        keys = keys.to(self.device, torch.int32).contiguous()
+        assert keys.dim() == 2 and keys.shape[1] == self.key_dim, "keys shape mismatch"
+        route = _Route(owner_of(keys, self.world), self.group)
+        return route, route.forward(keys)
+
+    def insert_keys(self, keys: torch.Tensor) -> None:
+        _, mine = self._route(keys)
+        if mine.shape[0]:
+            self.engine.insert_keys(mine)
+
+    def erase(self, keys: torch.Tensor) -> None:
+        _, mine = self._route(keys)
+        if mine.shape[0]:
+            self.engine.erase(mine)
+
+    def find(self, keys: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """(global indices int64 (N,), masks bool (N,)); a miss has index 0 and mask False."""
+        route, mine = self._route(keys)
+        if mine.shape[0]:
+            idx, masks = self.engine.find(mine)
+        else:
+            idx = torch.empty(0, dtype=torch.int64, device=self.device)
+            masks = torch.empty(0, dtype=torch.bool, device=self.device)
+        global_idx = torch.where(masks, idx * self.world + self.rank, torch.zeros_like(idx))
+        packed = torch.stack([global_idx, masks.to(torch.int64)], dim=1)
+        back = route.backward(packed)
+        return back[:, 0].contiguous(), back[:, 1].to(torch.bool)
+
+    def local_items(self) -> Tuple[torch.Tensor, torch.Tensor]:
+        """This rank's (keys, GLOBAL indices)."""
+        keys, idx = self.engine.items()
+        return keys, idx * self.world + self.rank
+
+    def size(self) -> int:
+        """Total number of live keys over all ranks."""
+        n = torch.tensor([self.engine.size()], dtype=torch.int64, device=self.device)
+        dist.all_reduce(n, group=self.group)
+        return int(n.item())
+
+    def split_global_index(self, global_idx: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """global index -> (owner rank, local row)."""
+        return torch.remainder(global_idx, self.world), torch.div(global_idx, self.world, rounding_mode="floor")
+
+
+def shard_rows(x: torch.Tensor, rank: Optional[int] = None, world: Optional[int] = None) -> torch.Tensor:
+    """Contiguous shard of a query / ray batch for this rank (sizes differ by at most one row)."""
+    rank = dist.get_rank() if rank is None else rank
+    world = dist.get_world_size() if world is None else world
+    n = x.shape[0]
+    lo, hi = n * rank // world, n * (rank + 1) // world
+    return x[lo:hi]
+
+
+def allreduce_gradients(module: torch.nn.Module, group=None) -> None:
+    """Sum the gradients of a replicated grid's parameters over the ranks (dense all-reduce)."""
+    for p in module.parameters():
+        if p.grad is not None:
+            dist.all_reduce(p.grad, group=group)

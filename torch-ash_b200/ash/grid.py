@@ -14,7 +14,7 @@ import torch.nn as nn
 from .common import _get_c_extension
 from .core import ASHEngine, ASHModule, _as_device
 from .grid_nns import enumerate_neighbor_coord_offsets
-from .grid_query import SparseDenseGridQuery
+from .grid_query import FusedGridQuery, SparseDenseGridQuery
 from .hashmap import HashSet
 
 backend = _get_c_extension()
@@ -52,6 +52,14 @@ class SparseDenseGrid(ASHModule):
         self.grid_indices = None
         self.grid_coords = None
         self.lut_grid_nb2grid_idx = None
+
+        # forward() runs as ONE fused launch when the world <-> cell transform is the class's own
+        # (it is described to the kernel by an origin and a cell size); set to False to force the
+        # reference's split + find + pre-split kernel sequence.
+        self.fused = True
+        self._lut32 = None
+        self._lut32_source = None
+        self._own_transform = self.transform_world_to_cell
 
     # ------------------------------------------------------------------ allocation
     def spatial_init_(self, points: torch.Tensor, dilation: int = 1, bidirectional: bool = False):
@@ -106,20 +114,39 @@ class SparseDenseGrid(ASHModule):
     def forward(self, x: torch.Tensor, interpolation: Literal["nearest", "linear", "smooth_step"] = "smooth_step"):
         """Differentiable query at world positions ``x`` (N, 3): returns
         ``(features (N, embedding_dim), masks (N,))``; ash/grid.py:201-238."""
+        if interpolation not in ("nearest", "linear", "smooth_step"):
+            raise ValueError(f"Unknown interpolation: {interpolation}")
+        if interpolation != "nearest" and (self.grid_coords is None or self.lut_grid_nb2grid_idx is None):
+            self.construct_grid_neighbor_lut_(radius=1, bidirectional=False)
+
+        if (interpolation != "nearest" and self.fused and x.is_cuda and x.dtype == torch.float32
+                and hasattr(backend, "grid_query_forward")
+                and self.transform_world_to_cell is self._own_transform):
+            origin, cell_size = self._cell_frame()
+            geom = (self.engine.backend, self._neighbor_lut32(), cell_size, origin, self.grid_dim, interpolation)
+            return FusedGridQuery.apply(self.embeddings, x, geom)
+
         x = self.transform_world_to_cell(x)
         grid_indices, cell_indices, offsets, masks = self.query(x)
 
         if interpolation == "nearest":
             return self.embeddings[grid_indices, cell_indices], masks
-        if interpolation not in ("linear", "smooth_step"):
-            raise ValueError(f"Unknown interpolation: {interpolation}")
-
-        if self.grid_coords is None or self.lut_grid_nb2grid_idx is None:
-            self.construct_grid_neighbor_lut_(radius=1, bidirectional=False)
         features = SparseDenseGridQuery.apply(
             self.embeddings, offsets, grid_indices, cell_indices, masks, self.lut_grid_nb2grid_idx,
             self.lut_cell_nb2cell_idx, self.lut_cell_nb2grid_nb, self.grid_dim, interpolation)
         return features, masks
+
+    def _cell_frame(self):
+        """(origin, cell_size) such that cell position = (world - origin) / cell_size."""
+        return [0.0, 0.0, 0.0], 1.0
+
+    def _neighbor_lut32(self) -> torch.Tensor:
+        """int32 copy of ``lut_grid_nb2grid_idx`` for the fused kernels, refreshed whenever that
+        table is replaced (it is as stale or as fresh as the table the reference would read)."""
+        if self._lut32 is None or self._lut32_source is not self.lut_grid_nb2grid_idx:
+            self._lut32 = self.lut_grid_nb2grid_idx.to(torch.int32).contiguous()
+            self._lut32_source = self.lut_grid_nb2grid_idx
+        return self._lut32
 
     def items(self):
         """Active blocks in broadcastable form: ``(grid_coords (n,1,3), cell_coords (1,G^3,3),
@@ -270,6 +297,13 @@ class SparseDenseGrid(ASHModule):
 
     @torch.no_grad()
     def construct_grid_neighbor_lut_(self, radius: int, bidirectional: bool) -> None:
+        if radius == 1 and not bidirectional and self.device.type == "cuda" and hasattr(backend, "grid_build_neighbor_lut"):
+            # one table scan + 8 probes per block instead of items() + find(8n) + two scatters
+            lut32, coords = backend.grid_build_neighbor_lut(self.engine.backend, self.num_embeddings, with_coords=True)
+            self.grid_coords = coords
+            self.lut_grid_nb2grid_idx = lut32.long()
+            self._lut32, self._lut32_source = lut32, self.lut_grid_nb2grid_idx
+            return
         self.grid_coords, self.lut_grid_nb2grid_idx = self.construct_grid_neighbor_lut(radius, bidirectional)
 
     # ------------------------------------------------------------------ surface extraction
@@ -289,8 +323,12 @@ class UnBoundedSparseDenseGrid(SparseDenseGrid):
         self.cell_size = cell_size
         self.transform_world_to_cell = lambda x: x / self.cell_size
         self.transform_cell_to_world = lambda x: x * self.cell_size
+        self._own_transform = self.transform_world_to_cell
         self.bbox_min = None
         self.bbox_max = None
+
+    def _cell_frame(self):
+        return [0.0, 0.0, 0.0], self.cell_size
 
     @torch.no_grad()
     def compute_bbox_(self):
@@ -325,6 +363,11 @@ class BoundedSparseDenseGrid(SparseDenseGrid):
         self.cell_size = ((self.bbox_max - self.bbox_min) / (sparse_grid_dim * grid_dim - 1)).min().item()
         self.transform_world_to_cell = lambda x: (x - self.bbox_min) / self.cell_size
         self.transform_cell_to_world = lambda x: x * self.cell_size + self.bbox_min
+        self._own_transform = self.transform_world_to_cell
+        self._origin = [float(v) for v in self.bbox_min.tolist()]
+
+    def _cell_frame(self):
+        return self._origin, self.cell_size
 
     def grids_in_bound(self, grid_coords: torch.Tensor) -> torch.Tensor:
         inside = ((grid_coords >= 0) & (grid_coords < self.sparse_grid_dim)).all(dim=-1)

@@ -72,3 +72,59 @@ class SparseDenseGridQueryBackward(torch.autograd.Function):
             grad_grad_embeddings, grad_grad_offsets.contiguous(), z, embeddings, *rest, ctx.grid_dim,
             ctx.interpolation)
         return (grad_z, grad_embeddings) + (None,) * (_N_BWD_INPUTS - 2)
+
+
+class FusedGridQuery(torch.autograd.Function):
+    """``SparseDenseGrid.forward`` as one launch: positions in, (features, masks) out.
+
+    Same values and the same gradient structure as ``SparseDenseGrid.query`` followed by
+    ``SparseDenseGridQuery``: differentiable w.r.t. ``embeddings`` and ``x`` (through the
+    offsets, d offset / d x = 1 / cell_size), twice differentiable w.r.t. ``embeddings`` and the
+    incoming gradient.  ``geom`` = (hashmap, nb_lut int32, cell_size, origin, grid_dim, interpolation).
+    """
+
+    @staticmethod
+    def forward(ctx, embeddings, x, geom):
+        hashmap, nb_lut, cell_size, origin, grid_dim, interpolation = geom
+        y, masks, block_idx = backend.grid_query_forward(
+            hashmap, embeddings, x, cell_size, origin, grid_dim, nb_lut, interpolation)
+        ctx.save_for_backward(embeddings, x, block_idx)
+        ctx.geom = geom
+        ctx.mark_non_differentiable(masks)
+        return y, masks
+
+    @staticmethod
+    def backward(ctx, z, _grad_masks):
+        embeddings, x, block_idx = ctx.saved_tensors
+        # positions that need no gradient spare the backward its eight embedding-row reads
+        need_grad_x = bool(ctx.needs_input_grad[1])
+        grad_embeddings, grad_x = FusedGridQueryBackward.apply(
+            z.contiguous(), embeddings, x, block_idx, ctx.geom, need_grad_x)
+        return grad_embeddings, grad_x, None
+
+
+class FusedGridQueryBackward(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, z, embeddings, x, block_idx, geom, need_grad_x=True):
+        hashmap, nb_lut, cell_size, origin, grid_dim, interpolation = geom
+        ctx.save_for_backward(z, embeddings, x, block_idx)
+        ctx.geom = geom
+        ctx.set_materialize_grads(False)
+        grad_embeddings, grad_x = backend.grid_query_backward(
+            hashmap, z, embeddings, x, cell_size, origin, grid_dim, nb_lut, block_idx, interpolation,
+            need_grad_x=need_grad_x)
+        if grad_x is None:
+            ctx.mark_non_differentiable(grad_embeddings)
+            return grad_embeddings, None
+        return grad_embeddings, grad_x.to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, grad_grad_embeddings, grad_grad_x):
+        if grad_grad_x is None:
+            return (None,) * 6
+        z, embeddings, x, block_idx = ctx.saved_tensors
+        hashmap, nb_lut, cell_size, origin, grid_dim, interpolation = ctx.geom
+        grad_z, grad_embeddings = backend.grid_query_backward_backward(
+            hashmap, grad_grad_x.to(embeddings.dtype).contiguous(), z, embeddings, x, cell_size, origin, grid_dim,
+            nb_lut, block_idx, interpolation)
+        return grad_z, grad_embeddings, None, None, None, None

@@ -10,7 +10,15 @@
 // lane.  All 8 corner loads of a lane are independent and issued back to back.
 // Row offsets are 64-bit (the reference's 32-bit `base_idx` overflows beyond
 // 2^31 table elements).
-#include "common.cuh"
+//
+// Two front ends feed the same gather / scatter bodies:
+//   LutSource    the reference's native interface: pre-split (grid index, cell index,
+//                offset, mask) per query and three int64 neighbour tables;
+//   FusedSource  positions in, everything else in-kernel: world -> cell transform,
+//                block / cell / offset split (ash/grid.py:183-199), hash probe of the
+//                block, corner cells by add-with-carry, and an int32 block-neighbour
+//                row read only by queries whose cell touches a +x/+y/+z block face.
+#include "hashmap.cuh"
 
 namespace ashb {
 
@@ -112,32 +120,98 @@ struct QueryLuts {
     int64_t cells_per_grid;
 };
 
-// Resolve the 8 corner rows of query q (element offsets into the table).
-// False when the query is masked out, its indices are out of range, or any
-// neighbour block is absent: the reference leaves such rows zero
-// (grid.cu:81-83, :109-111, :209-216).
-__device__ __forceinline__ bool resolve_corners(const QueryLuts& L, int64_t q, int64_t D, int64_t* base) {
-    if (!L.masks[q]) return false;
-    const int64_t gi = L.grid_indices[q];
-    const int64_t ci = L.cell_indices[q];
-    if (gi < 0 || gi >= L.n_emb || ci < 0 || ci >= L.cells_per_grid) return false;
-    const longlong2* nb_cg = reinterpret_cast<const longlong2*>(L.c2g + ci * 8);
-    const longlong2* nb_cc = reinterpret_cast<const longlong2*>(L.c2c + ci * 8);
-    const int64_t* nb_g = L.g2g + gi * 8;
-    bool ok = true;
+// Pre-split queries + lookup tables.  resolve() yields the 8 corner rows of query q
+// (element offsets into the table) and its offsets; false when the query is masked
+// out, its indices are out of range, or any neighbour block is absent: the
+// reference leaves such rows zero (grid.cu:81-83, :109-111, :209-216).
+struct LutSource {
+    const float* __restrict__ offsets;
+    QueryLuts L;
+
+    __device__ __forceinline__ bool resolve(int64_t q, int lane, int64_t D, int64_t* base, float* off) const {
+        (void)lane;
+        if (!L.masks[q]) return false;
+        const int64_t gi = L.grid_indices[q];
+        const int64_t ci = L.cell_indices[q];
+        if (gi < 0 || gi >= L.n_emb || ci < 0 || ci >= L.cells_per_grid) return false;
+        const longlong2* nb_cg = reinterpret_cast<const longlong2*>(L.c2g + ci * 8);
+        const longlong2* nb_cc = reinterpret_cast<const longlong2*>(L.c2c + ci * 8);
+        const int64_t* nb_g = L.g2g + gi * 8;
+        bool ok = true;
 #pragma unroll
-    for (int h = 0; h < 4; ++h) {
-        const longlong2 cg = __ldg(nb_cg + h);
-        const longlong2 cc = __ldg(nb_cc + h);
-        const int64_t g0 = __ldg(nb_g + (cg.x & 7));
-        const int64_t g1 = __ldg(nb_g + (cg.y & 7));
-        ok = ok && g0 >= 0 && g0 < L.n_emb && g1 >= 0 && g1 < L.n_emb && cc.x >= 0 &&
-             cc.x < L.cells_per_grid && cc.y >= 0 && cc.y < L.cells_per_grid;
-        base[2 * h] = (g0 * L.cells_per_grid + cc.x) * D;
-        base[2 * h + 1] = (g1 * L.cells_per_grid + cc.y) * D;
+        for (int h = 0; h < 4; ++h) {
+            const longlong2 cg = __ldg(nb_cg + h);
+            const longlong2 cc = __ldg(nb_cc + h);
+            const int64_t g0 = __ldg(nb_g + (cg.x & 7));
+            const int64_t g1 = __ldg(nb_g + (cg.y & 7));
+            ok = ok && g0 >= 0 && g0 < L.n_emb && g1 >= 0 && g1 < L.n_emb && cc.x >= 0 &&
+                 cc.x < L.cells_per_grid && cc.y >= 0 && cc.y < L.cells_per_grid;
+            base[2 * h] = (g0 * L.cells_per_grid + cc.x) * D;
+            base[2 * h + 1] = (g1 * L.cells_per_grid + cc.y) * D;
+        }
+        off[0] = offsets[3 * q];
+        off[1] = offsets[3 * q + 1];
+        off[2] = offsets[3 * q + 2];
+        return ok;
     }
-    return ok;
-}
+};
+
+// Positions in.  The split follows the Python layer operation by operation as it
+// evaluates on a CUDA tensor (ash/grid.py:192-197, :756, :846): divisions by the
+// cell size and by G are multiplications by float reciprocals, each rounded.
+struct FusedSource {
+    Table16 table;
+    const float* __restrict__ x;          // (n, 3) world positions
+    float org[3];                         // world position of cell (0,0,0)
+    float inv_cell;                       // 1 / cell_size (1 for plain grids)
+    float G_f, inv_G;
+    int G;
+    const int32_t* __restrict__ nb_lut;   // (n_emb, 8) block -> neighbour block, -1 absent
+    const int32_t* __restrict__ gi_in;    // saved block index per query (-1 = miss) or null: probe
+    int32_t* __restrict__ gi_out;         // forward only: block index per query for the backward passes
+    uint8_t* __restrict__ mask_out;       // forward only: hash hit mask
+    int64_t n_emb;
+    int64_t cells_per_grid;
+
+    __device__ __forceinline__ bool resolve(int64_t q, int lane, int64_t D, int64_t* base, float* off) const {
+        int blk[3], cell[3];
+#pragma unroll
+        for (int d = 0; d < 3; ++d) {
+            const float xc = __fmul_rn(__fsub_rn(x[3 * q + d], org[d]), inv_cell);
+            const float bf = floorf(__fmul_rn(xc, inv_G));
+            const float local = __fsub_rn(xc, __fmul_rn(bf, G_f));
+            const float cf = floorf(local);
+            off[d] = __fsub_rn(local, cf);
+            blk[d] = (int)bf;
+            // `local` can round up to exactly G for tiny negative positions
+            cell[d] = min(max((int)cf, 0), G - 1);
+        }
+        const int gi = gi_in ? gi_in[q] : lookup(table, blk[0], blk[1], blk[2], 0);
+        if (lane == 0) {
+            if (gi_out) gi_out[q] = gi;
+            if (mask_out) mask_out[q] = (uint8_t)(gi >= 0);
+        }
+        if (gi < 0 || gi >= n_emb) return false;
+        const int32_t* row = nb_lut + (int64_t)gi * 8;
+        bool ok = true;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            int cc[3], nb = 0;
+#pragma unroll
+            for (int d = 0; d < 3; ++d) {
+                cc[d] = cell[d] + ((c >> d) & 1);
+                if (cc[d] == G) {
+                    cc[d] = 0;
+                    nb |= 1 << d;
+                }
+            }
+            const int g = nb ? __ldg(row + nb) : gi;
+            ok = ok && g >= 0 && g < n_emb;
+            base[c] = ((int64_t)g * cells_per_grid + (cc[0] + (cc[1] + cc[2] * G) * G)) * D;
+        }
+        return ok;
+    }
+};
 
 template <typename T>
 __device__ __forceinline__ T group_sum(T v, int lanes) {
@@ -146,9 +220,8 @@ __device__ __forceinline__ T group_sum(T v, int lanes) {
 }
 
 // ---- forward -------------------------------------------------------------------
-template <typename T, int VEC>
-__global__ void __launch_bounds__(256) query_forward_kernel(const T* __restrict__ emb,
-                                                            const float* __restrict__ offsets, QueryLuts L,
+template <typename T, int VEC, class Src>
+__global__ void __launch_bounds__(256) query_forward_kernel(const T* __restrict__ emb, Src src,
                                                             T* __restrict__ out, int64_t n, int D,
                                                             int lane_shift, int interp) {
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -160,8 +233,8 @@ __global__ void __launch_bounds__(256) query_forward_kernel(const T* __restrict_
 #pragma unroll
     for (int k = 0; k < VEC; ++k) acc.v[k] = 0;
     int64_t base[8];
-    if (resolve_corners(L, q, D, base)) {
-        const float off[3] = {offsets[3 * q], offsets[3 * q + 1], offsets[3 * q + 2]};
+    float off[3];
+    if (src.resolve(q, lane, D, base, off)) {
         AxisWeights<T> aw;
         aw.init(interp, off);
         Pack<T, VEC> e[8];
@@ -178,30 +251,34 @@ __global__ void __launch_bounds__(256) query_forward_kernel(const T* __restrict_
 }
 
 // ---- backward: d/d embeddings (scatter) and d/d offsets -----------------------------
-template <typename T, int VEC>
+// grad_off receives d/d offset times `go_scale` (1 for the pre-split interface, 1 / cell_size
+// when the caller differentiates w.r.t. world positions).  With grad_off == nullptr only the
+// scatter runs: the eight embedding rows are not read at all.
+template <typename T, int VEC, class Src, bool NEED_GO>
 __global__ void __launch_bounds__(256) query_backward_forward_kernel(
-        const T* __restrict__ z, const T* __restrict__ emb, const float* __restrict__ offsets, QueryLuts L,
-        T* __restrict__ grad_emb, T* __restrict__ grad_off, int64_t n, int D, int lane_shift, int interp) {
+        const T* __restrict__ z, const T* __restrict__ emb, Src src, T* __restrict__ grad_emb,
+        T* __restrict__ grad_off, T go_scale, int64_t n, int D, int lane_shift, int interp) {
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t q = tid >> lane_shift;
     const int lanes = 1 << lane_shift;
     const int lane = (int)(tid & (lanes - 1));
     const int ch = lane * VEC;
-    // Whole groups stay together for the shuffles below; n is padded by the
-    // launch to a multiple of the groups per block.
+    // Whole groups stay together for the shuffles below (no early return).
     const bool live = q < n;
     const bool has_ch = ch < D;
     T go[3] = {0, 0, 0};
     int64_t base[8];
-    if (live && resolve_corners(L, q, D, base)) {
-        const float off[3] = {offsets[3 * q], offsets[3 * q + 1], offsets[3 * q + 2]};
+    float off[3];
+    if (live && src.resolve(q, lane, D, base, off)) {
         AxisWeights<T> aw;
         aw.init(interp, off);
         if (has_ch) {
             const Pack<T, VEC> zv = load_pack<T, VEC>(z + q * D + ch);
             Pack<T, VEC> e[8];
+            if (NEED_GO) {
 #pragma unroll
-            for (int c = 0; c < 8; ++c) e[c] = load_pack<T, VEC>(emb + base[c] + ch);
+                for (int c = 0; c < 8; ++c) e[c] = load_pack<T, VEC>(emb + base[c] + ch);
+            }
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 const T w = aw.weight(c);
@@ -210,32 +287,35 @@ __global__ void __launch_bounds__(256) query_backward_forward_kernel(
 #pragma unroll
                 for (int k = 0; k < VEC; ++k) {
                     g.v[k] = w * zv.v[k];
-                    dot += e[c].v[k] * zv.v[k];
+                    if (NEED_GO) dot += e[c].v[k] * zv.v[k];
                 }
                 atomic_add_pack<T, VEC>(grad_emb + base[c] + ch, g);
-                T wg[3];
-                aw.grad(c, wg);
-                go[0] += dot * wg[0];
-                go[1] += dot * wg[1];
-                go[2] += dot * wg[2];
+                if (NEED_GO) {
+                    T wg[3];
+                    aw.grad(c, wg);
+                    go[0] += dot * wg[0];
+                    go[1] += dot * wg[1];
+                    go[2] += dot * wg[2];
+                }
             }
         }
     }
+    if (!NEED_GO) return;
 #pragma unroll
     for (int d = 0; d < 3; ++d) go[d] = group_sum(go[d], lanes);
     if (live && lane == 0) {
-        grad_off[3 * q] = go[0];
-        grad_off[3 * q + 1] = go[1];
-        grad_off[3 * q + 2] = go[2];
+        grad_off[3 * q] = go[0] * go_scale;
+        grad_off[3 * q + 1] = go[1] * go_scale;
+        grad_off[3 * q + 2] = go[2] * go_scale;
     }
 }
 
 // ---- double backward ----------------------------------------------------------------
-template <typename T, int VEC>
+template <typename T, int VEC, class Src>
 __global__ void __launch_bounds__(256) query_backward_backward_kernel(
-        const T* __restrict__ ggo, const T* __restrict__ z, const T* __restrict__ emb,
-        const float* __restrict__ offsets, QueryLuts L, T* __restrict__ grad_z, T* __restrict__ grad_emb,
-        int64_t n, int D, int lane_shift, int interp) {
+        const T* __restrict__ ggo, const T* __restrict__ z, const T* __restrict__ emb, Src src,
+        T* __restrict__ grad_z, T* __restrict__ grad_emb, T go_scale, int64_t n, int D, int lane_shift,
+        int interp) {
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t q = tid >> lane_shift;
     const int lane = (int)(tid & ((1 << lane_shift) - 1));
@@ -245,9 +325,9 @@ __global__ void __launch_bounds__(256) query_backward_backward_kernel(
 #pragma unroll
     for (int k = 0; k < VEC; ++k) gz.v[k] = 0;
     int64_t base[8];
-    if (resolve_corners(L, q, D, base)) {
-        const float off[3] = {offsets[3 * q], offsets[3 * q + 1], offsets[3 * q + 2]};
-        const T g3[3] = {ggo[3 * q], ggo[3 * q + 1], ggo[3 * q + 2]};
+    float off[3];
+    if (src.resolve(q, lane, D, base, off)) {
+        const T g3[3] = {ggo[3 * q] * go_scale, ggo[3 * q + 1] * go_scale, ggo[3 * q + 2] * go_scale};
         AxisWeights<T> aw;
         aw.init(interp, off);
         const Pack<T, VEC> zv = load_pack<T, VEC>(z + q * D + ch);
@@ -323,52 +403,110 @@ static int check_lut_alignment(const void* c2c, const void* c2g) {
         }                                                   \
     }
 
-template <typename T>
-static int forward_impl(int interp, const void* emb, const float* offsets, const QueryLuts& L, void* out,
-                        int64_t n, int64_t D, cudaStream_t st) {
+template <typename T, class Src>
+static int forward_impl(int interp, const void* emb, const Src& src, void* out, int64_t n, int64_t D,
+                        cudaStream_t st) {
     const void* ptrs[] = {emb, out};
     const Shape sh = pick_shape(D, sizeof(T), ptrs, 2);
     const int64_t threads = n << sh.lane_shift;
     const unsigned grid = (unsigned)((threads + 255) / 256);
     ASHB_VEC_SWITCH(T, sh,
-                    (query_forward_kernel<T, VEC><<<grid, 256, 0, st>>>(static_cast<const T*>(emb), offsets, L,
-                                                                         static_cast<T*>(out), n, (int)D,
-                                                                         sh.lane_shift, interp)));
+                    (query_forward_kernel<T, VEC, Src><<<grid, 256, 0, st>>>(static_cast<const T*>(emb), src,
+                                                                              static_cast<T*>(out), n, (int)D,
+                                                                              sh.lane_shift, interp)));
     ASHB_LAUNCH_CHECK();
     return ASHB_OK;
 }
 
-template <typename T>
-static int backward_forward_impl(int interp, const void* z, const void* emb, const float* offsets,
-                                 const QueryLuts& L, void* grad_emb, void* grad_off, int64_t n, int64_t D,
-                                 cudaStream_t st) {
+template <typename T, class Src>
+static int backward_forward_impl(int interp, const void* z, const void* emb, const Src& src, void* grad_emb,
+                                 void* grad_off, double go_scale, int64_t n, int64_t D, cudaStream_t st) {
     const void* ptrs[] = {emb, z, grad_emb};
     const Shape sh = pick_shape(D, sizeof(T), ptrs, 3);
     const int64_t threads = n << sh.lane_shift;
     const unsigned grid = (unsigned)((threads + 255) / 256);
     ASHB_VEC_SWITCH(T, sh,
-                    (query_backward_forward_kernel<T, VEC><<<grid, 256, 0, st>>>(
-                            static_cast<const T*>(z), static_cast<const T*>(emb), offsets, L,
-                            static_cast<T*>(grad_emb), static_cast<T*>(grad_off), n, (int)D, sh.lane_shift,
-                            interp)));
+                    if (grad_off != nullptr) {
+                        query_backward_forward_kernel<T, VEC, Src, true><<<grid, 256, 0, st>>>(
+                                static_cast<const T*>(z), static_cast<const T*>(emb), src,
+                                static_cast<T*>(grad_emb), static_cast<T*>(grad_off), (T)go_scale, n, (int)D,
+                                sh.lane_shift, interp);
+                    } else {
+                        query_backward_forward_kernel<T, VEC, Src, false><<<grid, 256, 0, st>>>(
+                                static_cast<const T*>(z), static_cast<const T*>(emb), src,
+                                static_cast<T*>(grad_emb), nullptr, (T)go_scale, n, (int)D, sh.lane_shift, interp);
+                    });
     ASHB_LAUNCH_CHECK();
     return ASHB_OK;
 }
 
-template <typename T>
-static int backward_backward_impl(int interp, const void* ggo, const void* z, const void* emb,
-                                  const float* offsets, const QueryLuts& L, void* grad_z, void* grad_emb,
-                                  int64_t n, int64_t D, cudaStream_t st) {
+template <typename T, class Src>
+static int backward_backward_impl(int interp, const void* ggo, const void* z, const void* emb, const Src& src,
+                                  void* grad_z, void* grad_emb, double go_scale, int64_t n, int64_t D,
+                                  cudaStream_t st) {
     const void* ptrs[] = {emb, z, grad_emb, grad_z};
     const Shape sh = pick_shape(D, sizeof(T), ptrs, 4);
     const int64_t threads = n << sh.lane_shift;
     const unsigned grid = (unsigned)((threads + 255) / 256);
     ASHB_VEC_SWITCH(T, sh,
-                    (query_backward_backward_kernel<T, VEC><<<grid, 256, 0, st>>>(
-                            static_cast<const T*>(ggo), static_cast<const T*>(z), static_cast<const T*>(emb),
-                            offsets, L, static_cast<T*>(grad_z), static_cast<T*>(grad_emb), n, (int)D,
+                    (query_backward_backward_kernel<T, VEC, Src><<<grid, 256, 0, st>>>(
+                            static_cast<const T*>(ggo), static_cast<const T*>(z), static_cast<const T*>(emb), src,
+                            static_cast<T*>(grad_z), static_cast<T*>(grad_emb), (T)go_scale, n, (int)D,
                             sh.lane_shift, interp)));
     ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+// ---- block-neighbour table ---------------------------------------------------------------
+// For every live (block coordinate -> index) pair: the indices of the 8 blocks at offsets
+// {0,1}^3 (bit d of the column = offset along axis d), -1 where absent, and optionally the
+// coordinate itself.  One table scan + 8 probes per block replaces items() + find(8n) + two
+// scatters of ash/grid.py:566-617.  Rows of inactive indices must be pre-filled with -1.
+__global__ void __launch_bounds__(256) build_nb_lut_kernel(Table16 t, int32_t* __restrict__ lut,
+                                                           int32_t* __restrict__ coords, int64_t n_emb) {
+    const uint64_t n_slots = (uint64_t)t.mask + 1;
+    for (uint64_t s = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; s < n_slots;
+         s += (uint64_t)gridDim.x * blockDim.x) {
+        const Entry e = t.read_const((uint32_t)s);
+        if (e.val < 0 || e.val >= n_emb) continue;
+        int32_t row[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+            row[c] = c == 0 ? e.val : lookup(t, e.k0 + (c & 1), e.k1 + ((c >> 1) & 1), e.k2 + ((c >> 2) & 1), 0);
+        int4* dst = reinterpret_cast<int4*>(lut + (int64_t)e.val * 8);
+        dst[0] = make_int4(row[0], row[1], row[2], row[3]);
+        dst[1] = make_int4(row[4], row[5], row[6], row[7]);
+        if (coords) {
+            coords[3 * (int64_t)e.val] = e.k0;
+            coords[3 * (int64_t)e.val + 1] = e.k1;
+            coords[3 * (int64_t)e.val + 2] = e.k2;
+        }
+    }
+}
+
+static int make_fused_source(ashb_map* m, const float* x, float cell_size, const float* origin, int G,
+                             const int32_t* nb_lut, const int32_t* gi_in, int32_t* gi_out, uint8_t* mask_out,
+                             int64_t n_emb, FusedSource* out) {
+    ASHB_REQUIRE(m != nullptr && m->slots != nullptr, "null or destroyed map");
+    ASHB_REQUIRE(m->key_dim == 3, "the grid query needs a 3-D map");
+    ASHB_REQUIRE(G >= 1 && G <= 64 && cell_size > 0.f, "bad grid_dim or cell_size");
+    ASHB_REQUIRE(x && nb_lut, "null buffer");
+    ASHB_REQUIRE(((uintptr_t)nb_lut & 15) == 0, "neighbour table must be 16-byte aligned");
+    FusedSource f{};
+    f.table = table16_of(m);
+    f.x = x;
+    for (int d = 0; d < 3; ++d) f.org[d] = origin ? origin[d] : 0.f;
+    f.inv_cell = 1.0f / cell_size;
+    f.G = G;
+    f.G_f = (float)G;
+    f.inv_G = 1.0f / (float)G;
+    f.nb_lut = nb_lut;
+    f.gi_in = gi_in;
+    f.gi_out = gi_out;
+    f.mask_out = mask_out;
+    f.n_emb = n_emb;
+    f.cells_per_grid = (int64_t)G * G * G;
+    *out = f;
     return ASHB_OK;
 }
 
@@ -387,10 +525,10 @@ int ashb_query_forward(int dtype, int interp, const void* embeddings, const floa
     ASHB_REQUIRE(embeddings && offsets && grid_indices && cell_indices && masks && g2g && c2c && c2g && out,
                  "null buffer");
     if (int rc = check_lut_alignment(c2c, c2g)) return rc;
-    const QueryLuts L{grid_indices, cell_indices, masks, g2g, c2c, c2g, n_emb, cells_per_grid};
+    const LutSource src{offsets, QueryLuts{grid_indices, cell_indices, masks, g2g, c2c, c2g, n_emb, cells_per_grid}};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return dtype == ASHB_F32 ? forward_impl<float>(interp, embeddings, offsets, L, out, n, D, st)
-                             : forward_impl<double>(interp, embeddings, offsets, L, out, n, D, st);
+    return dtype == ASHB_F32 ? forward_impl<float>(interp, embeddings, src, out, n, D, st)
+                             : forward_impl<double>(interp, embeddings, src, out, n, D, st);
 }
 
 int ashb_query_backward_forward(int dtype, int interp, const void* z, const void* embeddings,
@@ -410,11 +548,11 @@ int ashb_query_backward_forward(int dtype, int interp, const void* z, const void
                          grad_offsets,
                  "null buffer");
     if (int rc = check_lut_alignment(c2c, c2g)) return rc;
-    const QueryLuts L{grid_indices, cell_indices, masks, g2g, c2c, c2g, n_emb, cells_per_grid};
-    return dtype == ASHB_F32 ? backward_forward_impl<float>(interp, z, embeddings, offsets, L, grad_embeddings,
-                                                            grad_offsets, n, D, st)
-                             : backward_forward_impl<double>(interp, z, embeddings, offsets, L,
-                                                             grad_embeddings, grad_offsets, n, D, st);
+    const LutSource src{offsets, QueryLuts{grid_indices, cell_indices, masks, g2g, c2c, c2g, n_emb, cells_per_grid}};
+    return dtype == ASHB_F32 ? backward_forward_impl<float>(interp, z, embeddings, src, grad_embeddings,
+                                                            grad_offsets, 1.0, n, D, st)
+                             : backward_forward_impl<double>(interp, z, embeddings, src, grad_embeddings,
+                                                             grad_offsets, 1.0, n, D, st);
 }
 
 int ashb_query_backward_backward(int dtype, int interp, const void* grad_grad_offsets, const void* z,
@@ -434,12 +572,91 @@ int ashb_query_backward_backward(int dtype, int interp, const void* grad_grad_of
                          g2g && c2c && c2g && grad_z,
                  "null buffer");
     if (int rc = check_lut_alignment(c2c, c2g)) return rc;
-    const QueryLuts L{grid_indices, cell_indices, masks, g2g, c2c, c2g, n_emb, cells_per_grid};
+    const LutSource src{offsets, QueryLuts{grid_indices, cell_indices, masks, g2g, c2c, c2g, n_emb, cells_per_grid}};
     return dtype == ASHB_F32
-                   ? backward_backward_impl<float>(interp, grad_grad_offsets, z, embeddings, offsets, L, grad_z,
-                                                   grad_embeddings, n, D, st)
-                   : backward_backward_impl<double>(interp, grad_grad_offsets, z, embeddings, offsets, L,
-                                                    grad_z, grad_embeddings, n, D, st);
+                   ? backward_backward_impl<float>(interp, grad_grad_offsets, z, embeddings, src, grad_z,
+                                                   grad_embeddings, 1.0, n, D, st)
+                   : backward_backward_impl<double>(interp, grad_grad_offsets, z, embeddings, src, grad_z,
+                                                    grad_embeddings, 1.0, n, D, st);
+}
+
+int ashb_grid_build_neighbor_lut(ashb_map* m, int32_t* lut, int32_t* grid_coords, int64_t n_emb, void* stream) {
+    ASHB_REQUIRE(m != nullptr && m->slots != nullptr, "null or destroyed map");
+    ASHB_REQUIRE(m->key_dim == 3 && lut != nullptr && n_emb >= 1, "needs a 3-D map and an output table");
+    ASHB_REQUIRE(((uintptr_t)lut & 15) == 0, "neighbour table must be 16-byte aligned");
+    DeviceGuard guard(m->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    ASHB_CUDA_TRY(cudaMemsetAsync(lut, 0xFF, (size_t)n_emb * 8 * sizeof(int32_t), st));
+    if (grid_coords) ASHB_CUDA_TRY(cudaMemsetAsync(grid_coords, 0xFF, (size_t)n_emb * 3 * sizeof(int32_t), st));
+    build_nb_lut_kernel<<<wave_grid((int64_t)m->n_slots, 256, 8), 256, 0, st>>>(table16_of(m), lut, grid_coords,
+                                                                                 n_emb);
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+int ashb_grid_query_forward(ashb_map* m, int dtype, int interp, const void* embeddings, const float* x,
+                            float cell_size, const float* origin, int G, const int32_t* nb_lut, void* out,
+                            uint8_t* masks, int32_t* block_idx_out, int64_t n, int64_t n_emb, int64_t D,
+                            void* stream) {
+    if (int rc = check_query_args(dtype, interp, n, n_emb, (int64_t)G * G * G, D)) return rc;
+    if (n == 0) return ASHB_OK;
+    ASHB_REQUIRE(embeddings && out && masks, "null buffer");
+    FusedSource src;
+    if (int rc = make_fused_source(m, x, cell_size, origin, G, nb_lut, nullptr, block_idx_out, masks, n_emb, &src))
+        return rc;
+    DeviceGuard guard(m->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == ASHB_F32 ? forward_impl<float>(interp, embeddings, src, out, n, D, st)
+                             : forward_impl<double>(interp, embeddings, src, out, n, D, st);
+}
+
+int ashb_grid_query_backward(ashb_map* m, int dtype, int interp, const void* z, const void* embeddings,
+                             const float* x, float cell_size, const float* origin, int G, const int32_t* nb_lut,
+                             const int32_t* block_idx, void* grad_embeddings, void* grad_x, int zero_grad,
+                             int64_t n, int64_t n_emb, int64_t D, void* stream) {
+    if (int rc = check_query_args(dtype, interp, n, n_emb, (int64_t)G * G * G, D)) return rc;
+    ASHB_REQUIRE(grad_embeddings != nullptr, "null grad_embeddings");
+    ASHB_REQUIRE(m != nullptr, "null map");
+    DeviceGuard guard(m->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t elem = dtype == ASHB_F32 ? 4 : 8;
+    if (zero_grad)
+        ASHB_CUDA_TRY(cudaMemsetAsync(grad_embeddings, 0, (size_t)n_emb * G * G * G * D * elem, st));
+    if (n == 0) return ASHB_OK;
+    ASHB_REQUIRE(z && embeddings, "null buffer");
+    FusedSource src;
+    if (int rc = make_fused_source(m, x, cell_size, origin, G, nb_lut, block_idx, nullptr, nullptr, n_emb, &src))
+        return rc;
+    const double scale = (double)(1.0f / cell_size);  // the float reciprocal the forward split multiplies by
+    return dtype == ASHB_F32 ? backward_forward_impl<float>(interp, z, embeddings, src, grad_embeddings, grad_x,
+                                                            scale, n, D, st)
+                             : backward_forward_impl<double>(interp, z, embeddings, src, grad_embeddings, grad_x,
+                                                             scale, n, D, st);
+}
+
+int ashb_grid_query_backward_backward(ashb_map* m, int dtype, int interp, const void* grad_grad_x, const void* z,
+                                      const void* embeddings, const float* x, float cell_size,
+                                      const float* origin, int G, const int32_t* nb_lut,
+                                      const int32_t* block_idx, void* grad_z, void* grad_embeddings,
+                                      int zero_grad, int64_t n, int64_t n_emb, int64_t D, void* stream) {
+    if (int rc = check_query_args(dtype, interp, n, n_emb, (int64_t)G * G * G, D)) return rc;
+    ASHB_REQUIRE(grad_embeddings != nullptr, "null grad_embeddings");
+    ASHB_REQUIRE(m != nullptr, "null map");
+    DeviceGuard guard(m->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t elem = dtype == ASHB_F32 ? 4 : 8;
+    if (zero_grad)
+        ASHB_CUDA_TRY(cudaMemsetAsync(grad_embeddings, 0, (size_t)n_emb * G * G * G * D * elem, st));
+    if (n == 0) return ASHB_OK;
+    ASHB_REQUIRE(grad_grad_x && z && embeddings && grad_z, "null buffer");
+    FusedSource src;
+    if (int rc = make_fused_source(m, x, cell_size, origin, G, nb_lut, block_idx, nullptr, nullptr, n_emb, &src))
+        return rc;
+    const double scale = (double)(1.0f / cell_size);  // the float reciprocal the forward split multiplies by
+    return dtype == ASHB_F32 ? backward_backward_impl<float>(interp, grad_grad_x, z, embeddings, src, grad_z,
+                                                             grad_embeddings, scale, n, D, st)
+                             : backward_backward_impl<double>(interp, grad_grad_x, z, embeddings, src, grad_z,
+                                                              grad_embeddings, scale, n, D, st);
 }
 
 }  // extern "C"
