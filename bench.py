@@ -36,6 +36,11 @@ CPU_SCALE = 16  # the CPU arms run a 1/16-scale sample
 FWD_BYTES = 12 + 32 * EMB_DIM + 4 * EMB_DIM + 1          # x, 8 corner rows, y, mask
 BWD_BYTES = 4 * EMB_DIM + 12 + 32 * EMB_DIM + 32 * EMB_DIM + 12  # z, x, corner rows, gradient rows, grad x
 FIND_BYTES = 12 + 16 + 8 + 1                              # key, one slot, index, mask
+# dram__bytes_read.sum + dram__bytes_write.sum per unit from the ncu captures summarised under profiles/
+# (taken on a reduced case whose tables are still many times L2; traffic per unit carries over)
+BWD_TRAFFIC_PER_QUERY = 1432 + 469
+FWD_TRAFFIC_PER_QUERY = 762 + 64
+FIND_TRAFFIC_PER_QUERY = 124 + 9
 
 
 def measured_peak_gbs():
@@ -190,19 +195,118 @@ def workload_config():
     }
 
 
+# ------------------------------------------------------------------------------ secondary rows
+def measure_tsdf(ash, bw, device, peak, n_frames=100, H=480, W=640):
+    """RGB-D fusion step: voxel 0.015 m, grid_dim 8, sdf + rgb + weight, synthetic 640x480 depth
+    frames ray-cast from 20 spheres + 6 box planes, random poses; frames/s of the two fused launches."""
+    from ash.fusion import TSDFFusion
+
+    cell, G, depth_max, cap = 0.015, 8, 5.0, 400_000
+    grid = ash.UnBoundedSparseDenseGrid(3, cap, 5, G, cell_size=cell, device=device)
+    fusion = TSDFFusion(grid, dilation=1)
+    scene = bw.Scene(device)
+    K = bw.intrinsics(H, W)
+    frames = []
+    for pose in bw.camera_poses(n_frames):
+        depth, color = scene.render(K.to(device), pose.float().to(device), H, W)
+        frames.append(ash.DotDict(depth=depth, depth_scale=1.0, depth_max=depth_max, intrinsic=K,
+                                  extrinsic=torch.linalg.inv(pose), rgb=color))
+    counter = torch.zeros(1, dtype=torch.int64, device=device)
+    torch.cuda.synchronize()
+
+    def run():
+        for d in frames:
+            fusion.fuse_frame(d, counter=counter)
+
+    ms = event_ms(run)
+    blocks = grid.engine.size()
+    status = grid.engine.backend.status()
+    updated_cells = int(counter.item()) * G**3
+    bytes_ = n_frames * H * W * 16 + updated_cells * 40
+    gbs = bytes_ / (ms * 1e-3) / 1e9
+    return {"workload": f"{n_frames} frames {W}x{H}, voxel {cell} m, grid_dim {G}, 5 channels, dilation 1",
+            "frames_per_s": round(n_frames / (ms * 1e-3), 1), "ms_per_frame": round(ms / n_frames, 4),
+            "active_blocks": blocks, "status": status, "cell_updates_per_s": round(updated_cells / (ms * 1e-3) / 1e9, 3),
+            "cell_updates_unit": "G cells/s",
+            "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4)}}
+
+
+def measure_bounded(ash, bw, device, peak):
+    """Bounded grid at resolution 512 (64 blocks x grid_dim 8 per axis), sdf + rgb channels: 7x7x7
+    Gaussian filter through the neighbourhood convolution, ray near/far and ray sampling for 8192
+    rays with up to 128 samples each."""
+    G, S, D = 8, 64, 4
+    grid = ash.BoundedSparseDenseGrid(3, 80_000, D, grid_dim=G, sparse_grid_dim=S, device=device)
+    scene = bw.Scene(device)
+    g = torch.Generator(device=device).manual_seed(bw.SEED + 5)
+    # surface points of the scene's spheres and box planes, scaled from the 10 m box into [-1, 1]^3
+    n_s = 400_000
+    pick = torch.randint(scene.centres.shape[0], (n_s,), generator=g, device=device)
+    dirs = torch.nn.functional.normalize(torch.randn(n_s, 3, generator=g, device=device), dim=-1)
+    pts = scene.centres[pick] + scene.radii[pick, None] * dirs
+    walls = (torch.rand(n_s, 3, generator=g, device=device) - 0.5) * 2 * scene.half
+    axis = torch.randint(3, (n_s,), generator=g, device=device)
+    side = torch.randint(2, (n_s,), generator=g, device=device).float() * 2 - 1
+    walls[torch.arange(n_s, device=device), axis] = side * scene.half * 0.98
+    pts = torch.cat([pts, walls]) / scene.half * 0.97
+    grid.spatial_init_(pts, dilation=0)
+    with torch.no_grad():
+        grid.embeddings.normal_(0, 0.1)
+    n_blocks = grid.engine.size()
+    for _ in range(2):
+        grid.gaussian_filter_(7, 1.0)
+    conv_ms = event_ms(lambda: grid.gaussian_filter_(7, 1.0))
+    cells = n_blocks * G**3
+    conv_no_reuse = cells * 4 * D * (343 + 1) / (conv_ms * 1e-3) / 1e9
+    conv_reuse = cells * 8 * D / (conv_ms * 1e-3) / 1e9
+    n_rays = 8192
+    o = (torch.rand(n_rays, 3, generator=g, device=device) - 0.5) * 1.2
+    tgt = (torch.rand(n_rays, 3, generator=g, device=device) - 0.5) * 1.2
+    d = torch.nn.functional.normalize(tgt - o, dim=-1)
+    grid.ray_find_near_far(o, d, 0.06, 1.0, 0.01)
+    nf_ms = event_ms(lambda: grid.ray_find_near_far(o, d, 0.06, 1.0, 0.01))
+    nears, fars = grid.ray_find_near_far(o, d, 0.06, 1.0, 0.01)
+    hit = nears >= 0
+    o, d, nears, fars = o[hit], d[hit], nears[hit], fars[hit]
+    grid.ray_sample(o, d, nears, fars, 128)
+    rs_ms = event_ms(lambda: grid.ray_sample(o, d, nears, fars, 128))
+    n_samples = int(grid.ray_sample(o, d, nears, fars, 128)[0].numel())
+    ray_gbs = (o.shape[0] * 24 + n_samples * 20) / (rs_ms * 1e-3) / 1e9
+    return {
+        "workload": f"bounded grid 512^3 ({S} blocks x grid_dim {G}), {D} channels, {n_blocks} active blocks",
+        "gaussian_filter_7x7x7": {"ms": round(conv_ms, 3), "cells_per_s": round(cells / (conv_ms * 1e-3) / 1e9, 3),
+                                  "cells_unit": "G cells/s", "achieved_gbs_no_reuse_bound": round(conv_no_reuse, 1),
+                                  "achieved_gbs_perfect_reuse_bound": round(conv_reuse, 1),
+                                  "frac_of_peak_no_reuse": round(conv_no_reuse / peak, 4)},
+        "ray_find_near_far": {"rays": n_rays, "ms": round(nf_ms, 4), "rays_per_s": round(n_rays / (nf_ms * 1e-3) / 1e6, 2),
+                              "unit": "M rays/s"},
+        "ray_sample": {"rays": int(o.shape[0]), "samples": n_samples, "ms": round(rs_ms, 4),
+                       "samples_per_s": round(n_samples / (rs_ms * 1e-3) / 1e6, 2), "unit": "M samples/s",
+                       "achieved_gbs": round(ray_gbs, 2), "frac": round(ray_gbs / peak, 5)},
+    }
+
+
 # ------------------------------------------------------------------------------ GPU arm
 def main():
+    global N_BLOCKS, N_QUERIES, HASH_KEYS, HASH_CAPACITY
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-hash", action="store_true", help="skip the hash-engine side measurement")
+    ap.add_argument("--blocks", type=int, default=N_BLOCKS, help="profiling aid: smaller table (default: the workload's 500k)")
+    ap.add_argument("--queries", type=int, default=N_QUERIES, help="profiling aid: fewer queries per step (default 4M)")
+    ap.add_argument("--hash-keys", type=int, default=HASH_KEYS, help="profiling aid: fewer keys (default 50M)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--no-extras", action="store_true", help="skip the fusion / convolution / ray sampler side measurements")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
     args.warmup = max(args.warmup, 3)
+    reduced = (args.blocks, args.queries, args.hash_keys) != (N_BLOCKS, N_QUERIES, HASH_KEYS)
+    N_BLOCKS, N_QUERIES, HASH_KEYS = args.blocks, args.queries, args.hash_keys
+    HASH_CAPACITY = HASH_KEYS * 64 // 50
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -325,6 +429,8 @@ def main():
     e2e_value = world * N_QUERIES / e2e_sec / 1e6
 
     line = {
+        **({"reduced_sizes_not_the_benchmark": {"blocks": N_BLOCKS, "queries": N_QUERIES, "hash_keys": HASH_KEYS}}
+           if reduced else {}),
         "metric": "M trilinear queries/s (fwd+bwd)", "value": round(value, 2), "unit": "M queries/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(),
@@ -338,7 +444,7 @@ def main():
         line["roofline"] = {
             "kernel": "query_backward_forward_kernel<float,4,FusedSource>", "bound": "hbm", "achieved": round(achieved, 1),
             "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4), "peak_kind": peak_kind,
-            "traffic": None, "ms_per_launch": round(bp_ms, 4),
+            "traffic": N_QUERIES * BWD_TRAFFIC_PER_QUERY, "ms_per_launch": round(bp_ms, 4),
             "note": "dominant kernel of the library; timed alone on a persistent gradient buffer "
                     "(the API-faithful step adds a 16.4 GB cudaMemsetAsync before it)",
         }
@@ -346,7 +452,8 @@ def main():
         table_bytes = N_BLOCKS * GRID_DIM**3 * EMB_DIM * 4
         step_bytes = N_QUERIES * (FWD_BYTES + BWD_BYTES) + table_bytes
         line["kernels"] = {
-            "query_forward": {"ms": round(f_ms, 4), "achieved_gbs": round(fa, 1), "frac": round(fa / peak, 4)},
+            "query_forward": {"ms": round(f_ms, 4), "achieved_gbs": round(fa, 1), "frac": round(fa / peak, 4),
+                              "traffic": N_QUERIES * FWD_TRAFFIC_PER_QUERY},
             "query_backward_dense(memset+kernel)": {"ms": round(b_ms, 4)},
             "step_api_faithful": {"bytes": step_bytes, "achieved_gbs": round(step_bytes / (ms_per_step * 1e-3) / 1e9, 1),
                                   "frac": round(step_bytes / (ms_per_step * 1e-3) / 1e9 / peak, 4)},
@@ -387,11 +494,17 @@ def main():
             "value": round(HASH_KEYS / (t_find * 1e-3) / 1e6, 1), "unit": "M finds/s", "ms": round(t_find, 4),
             "hit_rate": round(hit, 4),
             "roofline": {"bound": "hbm", "achieved": round(fa, 1), "peak": peak, "unit": "GB/s", "frac": round(fa / peak, 4),
-                         "peak_kind": peak_kind, "traffic": None},
+                         "peak_kind": peak_kind, "traffic": HASH_KEYS * FIND_TRAFFIC_PER_QUERY},
             "insert_M_per_s": round(HASH_KEYS / (t_ins * 1e-3) / 1e6, 1),
             "erase_M_per_s": round(HASH_KEYS / 8 / (t_er * 1e-3) / 1e6, 1), "items_ms": round(t_items, 3),
         }
         del hm, heap, q, uniq
+        torch.cuda.empty_cache()
+
+    if rank == 0 and not args.no_extras:
+        line["tsdf_fusion"] = measure_tsdf(ash, bw, device, peak)
+        torch.cuda.empty_cache()
+        line["bounded_grid"] = measure_bounded(ash, bw, device, peak)
         torch.cuda.empty_cache()
 
     if rank == 0 and world == 1 and not args.no_cpu:

@@ -210,6 +210,15 @@ int ashb_conv_forward(int dtype, const void* inputs, const void* weights, const 
                       int64_t num_grids, int64_t n_emb, int64_t cells_per_grid, int64_t D,
                       int64_t num_cell_nbs, int64_t num_grid_nbs, void* stream);
 
+/* The same convolution for the window SparseDenseGrid.convolution builds (ash/grid.py:476-520):
+ * two-sided, radius <= G, float32.  The two per-cell tables are implied by (G, radius) and are
+ * not passed; lut_grid_nb27 int64 [n_emb][27] is the radius-1 two-sided block table
+ * (column = (ox+1) + 3 (oy+1) + 9 (oz+1)); weights [(2R+1)^3][D] with x fastest.  One CTA per
+ * listed block works from a shared-memory halo tile.  Same results as ashb_conv_forward. */
+int ashb_conv_forward_tiled(const float* inputs, const float* weights, const int64_t* grid_indices,
+                            const int64_t* lut_grid_nb27, float* outputs, int zero_output,
+                            int64_t num_grids, int64_t n_emb, int G, int radius, int64_t D, void* stream);
+
 /* ---------------------------------------------------------------- ray sampler
  * All lengths in cell units; rays float32 [n][3]; bbox float32 [3] each; the map
  * must have key_dim 3 (ash/src/sampler.cu:89-99).  Positions are fma(t, d, o) in

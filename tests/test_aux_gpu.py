@@ -29,9 +29,13 @@ def _shell_grid(G, D, cls="plain", n_blocks=300, seed=0, cell_size=0.05):
     return grid, blocks
 
 
-@pytest.mark.parametrize("G,D,size", [(8, 4, 7), (4, 1, 3), (8, 5, 3), (2, 3, 5), (8, 16, 3)])
-def test_convolution_vs_oracle(G, D, size):
+@pytest.mark.parametrize("tiled", [True, False])
+@pytest.mark.parametrize("G,D,size", [(8, 4, 7), (4, 1, 3), (8, 5, 3), (2, 3, 5), (8, 16, 3), (8, 2, 5), (4, 6, 9), (3, 2, 3)])
+def test_convolution_vs_oracle(G, D, size, tiled):
+    """tiled: the shared-memory halo kernel SparseDenseGrid.convolution uses for float32 windows
+    within one block; not tiled: the table-driven kernel behind the reference's native interface."""
     grid, _ = _shell_grid(G, D, n_blocks=120, seed=G + D)
+    grid.tiled_convolution = tiled
     r = size // 2
     gen = torch.Generator(device=DEV).manual_seed(1)
     weights = torch.rand(size, size, size, D, generator=gen, device=DEV)

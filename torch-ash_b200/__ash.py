@@ -63,6 +63,7 @@ _lib.ashb_grid_query_backward.argtypes = [_vp, _int, _int, _vp, _vp, _vp, _f32, 
                                           _i64, _i64, _i64, _vp]
 _lib.ashb_grid_query_backward_backward.argtypes = [_vp, _int, _int, _vp, _vp, _vp, _vp, _f32, _vp, _int, _vp, _vp, _vp,
                                                    _vp, _int, _i64, _i64, _i64, _vp]
+_lib.ashb_conv_forward_tiled.argtypes = [_vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _int, _int, _i64, _vp]
 
 STATUS_CAPACITY, STATUS_PROBE, STATUS_SPIN, STATUS_DUPLICATE = 1, 2, 4, 8
 _DTYPES = {torch.float32: 0, torch.float64: 1}
@@ -591,3 +592,23 @@ def grid_query_backward_backward(hashmap, grad_grad_x, z, embeddings, x, cell_si
         bidx.data_ptr() if bidx is not None else None, grad_z.data_ptr(), grad_emb.data_ptr(), zero, n, emb.shape[0],
         emb.shape[2], _stream(dev)))
     return grad_z, grad_emb
+
+
+def convolution_forward_tiled(inputs, weights, grid_indices, lut_grid_nb27, grid_dim, radius):
+    """Shared-memory tiled form of ``convolution_forward`` for a two-sided window of ``radius`` <=
+    ``grid_dim`` cells (float32).  ``weights`` ((2R+1)^3, D), ``lut_grid_nb27`` int64
+    (num_embeddings, 27); the per-cell tables are implied.  No counterpart in the reference."""
+    inp = _cuda(inputs, "inputs", torch.float32)
+    w = _cuda(weights, "weights", torch.float32)
+    gi = _cuda(grid_indices, "grid_indices", torch.int64).view(-1)
+    g27 = _cuda(lut_grid_nb27, "lut_grid_nb27", torch.int64)
+    n_emb, cells, D = inp.shape
+    S = 2 * int(radius) + 1
+    if cells != int(grid_dim) ** 3 or w.shape != (S**3, D) or g27.shape != (n_emb, 27):
+        raise RuntimeError("convolution_forward_tiled: shapes do not match (grid_dim, radius)")
+    out = torch.empty_like(inp)
+    with torch.cuda.device(inp.device):
+        _check(_lib.ashb_conv_forward_tiled(
+            inp.data_ptr(), w.data_ptr(), gi.data_ptr(), g27.data_ptr(), out.data_ptr(), 1, gi.shape[0], n_emb,
+            int(grid_dim), int(radius), D, _stream(inp.device)))
+    return out

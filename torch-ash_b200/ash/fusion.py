@@ -40,10 +40,11 @@ class TSDFFusion:
             self._bounds = (None, None)
 
     @torch.no_grad()
-    def fuse_frame(self, datum) -> None:
+    def fuse_frame(self, datum, counter=None) -> None:
         """``datum``: depth (H, W) raw, depth_scale, depth_max, intrinsic (3, 3), extrinsic (4, 4)
         world -> camera, rgb (H, W, 3); as demo/rgbd_fusion.py:199-254 (``datum.depth`` is scaled to
-        metres in place there too)."""
+        metres in place there too).  ``counter``: optional int64 device tensor incremented by the
+        number of blocks fused."""
         datum.depth *= datum.depth_scale
         depth = datum.depth
         K = torch.as_tensor(datum.intrinsic).double().cpu()
@@ -56,7 +57,7 @@ class TSDFFusion:
             g.grid_dim, self.dilation, self._coords, self._touched, self._stamp, *self._bounds)
         backend.tsdf_integrate(
             g.embeddings.data, g.grid_dim, self._coords, self._touched, self._stamp, depth, datum.rgb, K.tolist(),
-            E.tolist(), datum.depth_max, g.cell_size, self._origin, self.trunc)
+            E.tolist(), datum.depth_max, g.cell_size, self._origin, self.trunc, counter=counter)
         # the engine's host-side size bound is stale after native insertions
         g.engine._size_bound = g.engine.capacity
 

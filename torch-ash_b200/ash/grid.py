@@ -57,6 +57,7 @@ class SparseDenseGrid(ASHModule):
         # (it is described to the kernel by an origin and a cell size); set to False to force the
         # reference's split + find + pre-split kernel sequence.
         self.fused = True
+        self.tiled_convolution = True
         self._lut32 = None
         self._lut32_source = None
         self._own_transform = self.transform_world_to_cell
@@ -251,10 +252,16 @@ class SparseDenseGrid(ASHModule):
         assert weights.shape[:3] == (2 * radius + 1,) * 3
         assert weights.shape[3] == inputs.shape[-1] and weights.device == inputs.device
 
-        lut_c2g, lut_c2c = self.construct_cell_neighbor_lut(radius, bidirectional=True)
         grid_radius = (radius + self.grid_dim - 1) // self.grid_dim
         _, lut_g2g = self.construct_grid_neighbor_lut(grid_radius, bidirectional=True)
         _, _, grid_indices, cell_indices = self.items()
+        if (self.tiled_convolution and inputs.is_cuda and inputs.dtype == torch.float32 and 1 <= radius <= self.grid_dim
+                and hasattr(backend, "convolution_forward_tiled")):
+            # the per-cell tables of this window are pure arithmetic: one CTA per block works
+            # from a shared-memory halo tile instead of 2 x 343 table reads per cell
+            return backend.convolution_forward_tiled(
+                inputs, weights.view(-1, weights.shape[-1]), grid_indices, lut_g2g, self.grid_dim, radius)
+        lut_c2g, lut_c2c = self.construct_cell_neighbor_lut(radius, bidirectional=True)
         return backend.convolution_forward(
             inputs, weights.view(lut_c2g.shape[1], weights.shape[-1]), torch.ones_like(inputs, dtype=torch.bool),
             grid_indices, cell_indices, lut_g2g, lut_c2c, lut_c2g, self.grid_dim)
