@@ -258,23 +258,28 @@ int ashb_ray_sample_fill(ashb_map* map, const float* ray_origins, const float* r
  * (0 < depth < depth_max) is inserted if absent; for each such block idx,
  * grid_coords[idx] (int32 [n_emb][3]) receives its coordinate and touched[idx]
  * (uint32 [n_emb]) receives `stamp` (non-zero, different per frame).  bound_lo/bound_hi:
- * HOST int32[3] half-open range of admissible block coordinates, or NULL for none. */
+ * HOST int32[3] half-open range of admissible block coordinates, or NULL for none.
+ * touched_list int32 [n_emb] + touched_count int32 [1] (both device, both optional): the
+ * compact list of the blocks stamped by this call, for ashb_tsdf_integrate. */
 int ashb_tsdf_touch(ashb_map* map, const float* depth, int H, int W, const float* intrinsic,
                     const float* cam_to_world, float depth_max, float cell_size, const float* origin,
                     int G, int dilation, const int32_t* bound_lo, const int32_t* bound_hi,
-                    int32_t* grid_coords, uint32_t* touched, uint32_t stamp, void* stream);
+                    int32_t* grid_coords, uint32_t* touched, uint32_t stamp, int32_t* touched_list,
+                    int32_t* touched_count, void* stream);
 
 /* Step 2, fusion (project_points_to_rgbd + the running average,
  * demo/rgbd_fusion.py:76-110, :236-254) over every cell of every block whose
  * touched[idx] == stamp.  embeddings float32 [n_emb][G^3][D], 5 <= D <= 16, with sdf at
  * sdf_channel, colour at rgb_channel..+2 and the weight at weight_channel (the demo uses
- * 0, 1, 4).  n_integrated_dev: optional device counter incremented once per fused block. */
+ * 0, 1, 4).  n_integrated_dev: optional device counter incremented once per fused block.
+ * With the list of step 1 a few persistent CTAs walk exactly the stamped blocks; without it
+ * (NULL, NULL) one CTA per embedding row checks its stamp. */
 int ashb_tsdf_integrate(void* embeddings, int64_t n_emb, int G, int64_t D, const int32_t* grid_coords,
                         const uint32_t* touched, uint32_t stamp, const float* depth, const float* color,
                         int H, int W, const float* intrinsic, const float* world_to_cam, float depth_max,
                         float cell_size, const float* origin, float trunc, int sdf_channel,
                         int rgb_channel, int weight_channel, unsigned long long* n_integrated_dev,
-                        void* stream);
+                        const int32_t* touched_list, const int32_t* touched_count, void* stream);
 
 /* One whole fusion step (allocation + fusion, as the two calls above) that allocates nothing.
  * It has no counterpart in the reference.  It exists for callers that must not allocate device

@@ -130,7 +130,7 @@ def test_tsdf_fusion_vs_oracle(H, W):
         depth, color = scene.render(K.to(DEV), pose.float().to(DEV), H, W)
         datum = ash.DotDict(depth=depth.clone(), depth_scale=1.0, depth_max=depth_max, intrinsic=K, extrinsic=E, rgb=color)
         fusion.fuse_frame(datum)
-        ref.fuse_frame(depth.cpu().numpy(), color.cpu().numpy(), K.numpy(), E.numpy(), torch.linalg.inv(E).numpy(), depth_max)
+        ref.fuse_frame(depth.cpu().numpy(), color.cpu().numpy(), K.numpy(), E.numpy(), np.linalg.inv(E.numpy()), depth_max)
     assert grid.engine.backend.status() == 0
     keys, idx = grid.engine.items()
     rkeys, ridx = ref.map.items()

@@ -42,7 +42,7 @@ def test_static_scratch_fusion_matches_regular_path():
                                       extrinsic=E, rgb=color))
         __ash.tsdf_fuse_frame_static(
             static.engine.backend, static.embeddings.data, G, depth, color, K.double().tolist(), E.tolist(),
-            torch.linalg.inv(E).tolist(), depth_max, cell, [0.0, 0.0, 0.0], dil, fusion.trunc)
+            np.linalg.inv(E.numpy()).tolist(), depth_max, cell, [0.0, 0.0, 0.0], dil, fusion.trunc)
         k_r, e_r = _sorted_state(regular)
         k_s, e_s = _sorted_state(static)
         assert len(k_r) > 50, "the frame must allocate blocks"

@@ -52,9 +52,9 @@ _lib.ashb_ray_find_near_far.argtypes = [_vp] * 7 + [_f32] * 4 + [_i64, _vp]
 _lib.ashb_ray_sample_count.argtypes = [_vp] * 6 + [_i64, _f32, _i64, _vp]
 _lib.ashb_ray_sample_fill.argtypes = [_vp] * 9 + [_i64, _f32, _i64, _vp]
 _lib.ashb_tsdf_touch.argtypes = [_vp, _vp, _int, _int, _vp, _vp, _f32, _f32, _vp, _int, _int, _vp, _vp, _vp, _vp,
-                                 _c.c_uint32, _vp]
+                                 _c.c_uint32, _vp, _vp, _vp]
 _lib.ashb_tsdf_integrate.argtypes = [_vp, _i64, _int, _i64, _vp, _vp, _c.c_uint32, _vp, _vp, _int, _int, _vp, _vp,
-                                     _f32, _f32, _vp, _f32, _int, _int, _int, _vp, _vp]
+                                     _f32, _f32, _vp, _f32, _int, _int, _int, _vp, _vp, _vp, _vp]
 _lib.ashb_tsdf_fuse_frame_static.argtypes = [_vp, _vp, _i64, _int, _i64, _vp, _vp, _int, _int, _vp, _vp, _vp, _f32, _f32,
                                              _vp, _int, _vp, _vp, _f32, _int, _int, _int, _vp]
 _lib.ashb_grid_build_neighbor_lut.argtypes = [_vp, _vp, _vp, _i64, _vp]
@@ -424,12 +424,15 @@ def ray_sample(hashmap, ray_origins, ray_directions, ray_nears, ray_fars, bbox_m
 
 
 def _host_floats(values, n):
-    arr = (_f32 * n)(*[float(v) for v in values])
-    return arr
+    """A C float[n] from a flat or nested sequence / array (row major)."""
+    flat = []
+    for v in values:
+        flat.extend(v) if hasattr(v, "__len__") else flat.append(v)
+    return (_f32 * n)(*[float(v) for v in flat[:n]])
 
 
 def tsdf_touch(hashmap, depth, intrinsic, cam_to_world, depth_max, cell_size, origin, grid_dim, dilation,
-               grid_coords, touched, stamp, bound_lo=None, bound_hi=None):
+               grid_coords, touched, stamp, bound_lo=None, bound_hi=None, touched_list=None, touched_count=None):
     """Allocate and stamp the blocks seen by a depth frame (no counterpart in the reference's
     native module; replaces the allocation half of demo/rgbd_fusion.py:199-224).
     ``intrinsic`` (3,3), ``cam_to_world`` (>=3,4) and ``origin`` (3,) are host values."""
@@ -445,12 +448,14 @@ def tsdf_touch(hashmap, depth, intrinsic, cam_to_world, depth_max, cell_size, or
     hi = (_c.c_int32 * 3)(*bound_hi) if bound_hi is not None else None
     _check(_lib.ashb_tsdf_touch(
         hashmap._h, depth.data_ptr(), H, W, K, Ei, float(depth_max), float(cell_size), org, int(grid_dim),
-        int(dilation), lo, hi, grid_coords.data_ptr(), touched.data_ptr(), int(stamp), _stream(dev)))
+        int(dilation), lo, hi, grid_coords.data_ptr(), touched.data_ptr(), int(stamp),
+        touched_list.data_ptr() if touched_list is not None else None,
+        touched_count.data_ptr() if touched_count is not None else None, _stream(dev)))
 
 
 def tsdf_integrate(embeddings, grid_dim, grid_coords, touched, stamp, depth, color, intrinsic, world_to_cam,
                    depth_max, cell_size, origin, trunc, sdf_channel=0, rgb_channel=1, weight_channel=4,
-                   counter=None):
+                   counter=None, touched_list=None, touched_count=None):
     """Fuse a frame into every stamped block in place (replaces demo/rgbd_fusion.py:226-254)."""
     emb = embeddings
     if not emb.is_cuda or emb.dtype != torch.float32 or not emb.is_contiguous() or emb.dim() != 3:
@@ -468,7 +473,9 @@ def tsdf_integrate(embeddings, grid_dim, grid_coords, touched, stamp, depth, col
             emb.data_ptr(), emb.shape[0], int(grid_dim), emb.shape[2], grid_coords.data_ptr(), touched.data_ptr(),
             int(stamp), depth.data_ptr(), color.data_ptr(), H, W, K, E, float(depth_max), float(cell_size), org,
             float(trunc), int(sdf_channel), int(rgb_channel), int(weight_channel),
-            counter.data_ptr() if counter is not None else None, _stream(emb.device)))
+            counter.data_ptr() if counter is not None else None,
+            touched_list.data_ptr() if touched_list is not None else None,
+            touched_count.data_ptr() if touched_count is not None else None, _stream(emb.device)))
 
 
 def tsdf_fuse_frame_static(hashmap, embeddings, grid_dim, depth, color, intrinsic, world_to_cam, cam_to_world,

@@ -11,12 +11,20 @@ Embedding layout as in the demo (:239-241): channel 0 sdf, 1..3 rgb, 4 weight.
 """
 from typing import Union
 
+import numpy as np
 import torch
 
 from .common import _get_c_extension
 from .grid import BoundedSparseDenseGrid, UnBoundedSparseDenseGrid
 
 backend = _get_c_extension()
+
+
+def _host_matrix(m) -> np.ndarray:
+    """A small camera matrix as float64 numpy on the host, whatever it arrived as."""
+    if torch.is_tensor(m):
+        m = m.detach().cpu().numpy()
+    return np.asarray(m, dtype=np.float64)
 
 
 class TSDFFusion:
@@ -31,6 +39,8 @@ class TSDFFusion:
         # (stamp) that touched it
         self._coords = torch.zeros((grid.num_embeddings, 3), dtype=torch.int32, device=dev)
         self._touched = torch.zeros(grid.num_embeddings, dtype=torch.int32, device=dev)
+        self._list = torch.zeros(grid.num_embeddings, dtype=torch.int32, device=dev)  # blocks touched by the frame
+        self._count = torch.zeros(1, dtype=torch.int32, device=dev)
         self._stamp = 0
         if isinstance(grid, BoundedSparseDenseGrid):
             self._origin = [float(v) for v in grid.bbox_min.tolist()]
@@ -47,17 +57,19 @@ class TSDFFusion:
         number of blocks fused."""
         datum.depth *= datum.depth_scale
         depth = datum.depth
-        K = torch.as_tensor(datum.intrinsic).double().cpu()
-        E = torch.as_tensor(datum.extrinsic).double().cpu()
-        Ei = torch.linalg.inv(E)
+        K = _host_matrix(datum.intrinsic)
+        E = _host_matrix(datum.extrinsic)
+        Ei = np.linalg.inv(E)
         self._stamp = self._stamp % 0x7FFFFFFF + 1
         g = self.grid
         backend.tsdf_touch(
-            g.engine.backend, depth, K.tolist(), Ei.tolist(), datum.depth_max, g.cell_size, self._origin,
-            g.grid_dim, self.dilation, self._coords, self._touched, self._stamp, *self._bounds)
+            g.engine.backend, depth, K, Ei, datum.depth_max, g.cell_size, self._origin, g.grid_dim, self.dilation,
+            self._coords, self._touched, self._stamp, *self._bounds, touched_list=self._list,
+            touched_count=self._count)
         backend.tsdf_integrate(
-            g.embeddings.data, g.grid_dim, self._coords, self._touched, self._stamp, depth, datum.rgb, K.tolist(),
-            E.tolist(), datum.depth_max, g.cell_size, self._origin, self.trunc, counter=counter)
+            g.embeddings.data, g.grid_dim, self._coords, self._touched, self._stamp, depth, datum.rgb, K, E,
+            datum.depth_max, g.cell_size, self._origin, self.trunc, counter=counter, touched_list=self._list,
+            touched_count=self._count)
         # the engine's host-side size bound is stale after native insertions
         g.engine._size_bound = g.engine.capacity
 

@@ -51,7 +51,9 @@ __global__ void __launch_bounds__(256) tsdf_touch_kernel(Table16 t, int32_t* __r
                                                          float3 origin, float inv_G, int dilation,
                                                          int3 lo, int3 hi, int bounded,
                                                          int32_t* __restrict__ grid_coords,
-                                                         uint32_t* __restrict__ touched, uint32_t stamp) {
+                                                         uint32_t* __restrict__ touched, uint32_t stamp,
+                                                         int32_t* __restrict__ touched_list,
+                                                         int32_t* touched_count) {
     const int64_t pix = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     bool valid = pix < (int64_t)H * W;
     int bx = 0, by = 0, bz = 0;
@@ -124,7 +126,12 @@ __global__ void __launch_bounds__(256) tsdf_touch_kernel(Table16 t, int32_t* __r
                 grid_coords[3 * idx] = kx;
                 grid_coords[3 * idx + 1] = ky;
                 grid_coords[3 * idx + 2] = kz;
-                touched[idx] = stamp;
+                if (touched_list) {
+                    // first toucher of the frame appends the block to the compact work list
+                    if (atomicExch(&touched[idx], stamp) != stamp) touched_list[atomicAdd(touched_count, 1)] = idx;
+                } else {
+                    touched[idx] = stamp;
+                }
             }
 }
 
@@ -134,10 +141,15 @@ __global__ void __launch_bounds__(256) tsdf_integrate_kernel(
         float* __restrict__ emb, const int32_t* __restrict__ grid_coords, const uint32_t* __restrict__ touched,
         uint32_t stamp, const float* __restrict__ depth, const float* __restrict__ color, int H, int W, Camera cam,
         float depth_max, float cell_size, float3 origin, int G, int cells, float trunc, int sdf_ch, int rgb_ch,
-        int w_ch, unsigned long long* n_integrated) {
+        int w_ch, unsigned long long* n_integrated, int64_t n_emb, const int32_t* __restrict__ touched_list,
+        const int32_t* __restrict__ touched_count) {
     extern __shared__ float tile[];  // cells * D floats
-    const int64_t idx = blockIdx.x;
-    if (touched[idx] != stamp) return;
+    // Work items: the compact list written by the touch kernel (a few persistent CTAs walk it),
+    // or, without a list, every embedding row whose stamp matches (one CTA per row).
+    const int64_t n_items = touched_list ? (int64_t)*touched_count : n_emb;
+    for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const int64_t idx = touched_list ? (int64_t)touched_list[item] : item;
+    if (!touched_list && touched[idx] != stamp) continue;
     float* block = emb + idx * (int64_t)cells * D;
     const int n_float = cells * D;
     // rows are 16-byte aligned when cells * D * 4 is a multiple of 16
@@ -199,6 +211,8 @@ __global__ void __launch_bounds__(256) tsdf_integrate_kernel(
         for (int i = threadIdx.x; i < n_float; i += blockDim.x) block[i] = tile[i];
     }
     if (threadIdx.x == 0 && n_integrated) atomicAdd(n_integrated, 1ull);
+    __syncthreads();  // the tile is reused by the next item
+    }
 }
 
 }  // namespace ashb
@@ -210,7 +224,8 @@ extern "C" {
 int ashb_tsdf_touch(ashb_map* m, const float* depth, int H, int W, const float* intrinsic,
                     const float* cam_to_world, float depth_max, float cell_size, const float* origin, int G,
                     int dilation, const int32_t* bound_lo, const int32_t* bound_hi, int32_t* grid_coords,
-                    uint32_t* touched, uint32_t stamp, void* stream) {
+                    uint32_t* touched, uint32_t stamp, int32_t* touched_list, int32_t* touched_count,
+                    void* stream) {
     ASHB_REQUIRE(m != nullptr && m->slots != nullptr, "null or destroyed map");
     ASHB_REQUIRE(m->key_dim == 3, "TSDF integration needs a 3-D map");
     ASHB_REQUIRE(depth && intrinsic && cam_to_world && origin && grid_coords && touched, "null buffer");
@@ -225,12 +240,14 @@ int ashb_tsdf_touch(ashb_map* m, const float* depth, int H, int W, const float* 
     const int bounded = bound_lo != nullptr && bound_hi != nullptr;
     const int3 lo = bounded ? make_int3(bound_lo[0], bound_lo[1], bound_lo[2]) : make_int3(0, 0, 0);
     const int3 hi = bounded ? make_int3(bound_hi[0], bound_hi[1], bound_hi[2]) : make_int3(0, 0, 0);
+    ASHB_REQUIRE((touched_list == nullptr) == (touched_count == nullptr), "pass both the list and its counter, or neither");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int64_t n = (int64_t)H * W;
+    if (touched_count) ASHB_CUDA_TRY(cudaMemsetAsync(touched_count, 0, sizeof(int32_t), st));
     tsdf_touch_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
             table16_of(m), m->heap, m->counter, (int32_t)m->capacity, depth, H, W, cam, depth_max,
             1.0f / cell_size, make_float3(origin[0], origin[1], origin[2]), 1.0f / (float)G, dilation, lo, hi,
-            bounded, grid_coords, touched, stamp);
+            bounded, grid_coords, touched, stamp, touched_list, touched_count);
     ASHB_LAUNCH_CHECK();
     return ASHB_OK;
 }
@@ -239,7 +256,9 @@ int ashb_tsdf_integrate(void* embeddings, int64_t n_emb, int G, int64_t D, const
                         const uint32_t* touched, uint32_t stamp, const float* depth, const float* color, int H,
                         int W, const float* intrinsic, const float* world_to_cam, float depth_max,
                         float cell_size, const float* origin, float trunc, int sdf_channel, int rgb_channel,
-                        int weight_channel, unsigned long long* n_integrated_dev, void* stream) {
+                        int weight_channel, unsigned long long* n_integrated_dev, const int32_t* touched_list,
+                        const int32_t* touched_count, void* stream) {
+    ASHB_REQUIRE((touched_list == nullptr) == (touched_count == nullptr), "pass both the list and its counter, or neither");
     ASHB_REQUIRE(embeddings && grid_coords && touched && depth && color && intrinsic && world_to_cam && origin,
                  "null buffer");
     ASHB_REQUIRE(n_emb >= 1 && G >= 1 && G <= 16 && H > 0 && W > 0, "bad sizes");
@@ -255,15 +274,18 @@ int ashb_tsdf_integrate(void* embeddings, int64_t n_emb, int G, int64_t D, const
     const size_t smem = (size_t)cells * D * sizeof(float);
     ASHB_REQUIRE(smem <= 200 * 1024, "block of %zu bytes does not fit in shared memory", smem);
     const float3 org = make_float3(origin[0], origin[1], origin[2]);
+    // with a work list: a whole number of waves of persistent CTAs; without: one CTA per row
+    const unsigned launch_ctas =
+            touched_list ? (unsigned)(n_emb < (int64_t)sm_count() * 8 ? n_emb : (int64_t)sm_count() * 8) : (unsigned)n_emb;
 #define ASHB_TSDF_LAUNCH(DD)                                                                               \
     case DD: {                                                                                             \
         if (smem > 48 * 1024)                                                                              \
             ASHB_CUDA_TRY(cudaFuncSetAttribute(tsdf_integrate_kernel<DD>,                                  \
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));  \
-        tsdf_integrate_kernel<DD><<<(unsigned)n_emb, 256, smem, st>>>(                                     \
+        tsdf_integrate_kernel<DD><<<launch_ctas, 256, smem, st>>>(                                         \
                 static_cast<float*>(embeddings), grid_coords, touched, stamp, depth, color, H, W, cam,     \
                 depth_max, cell_size, org, G, cells, trunc, sdf_channel, rgb_channel, weight_channel,      \
-                n_integrated_dev);                                                                         \
+                n_integrated_dev, n_emb, touched_list, touched_count);                                     \
     } break;
     switch ((int)D) {
         ASHB_TSDF_LAUNCH(5)
@@ -329,11 +351,11 @@ int ashb_tsdf_fuse_frame_static(ashb_map* m, void* embeddings, int64_t n_emb, in
     ASHB_CUDA_TRY(cudaMemsetAsync(touched, 0, (size_t)n_emb * sizeof(uint32_t), st));
     const uint32_t stamp = 1;
     if (int rc = ashb_tsdf_touch(m, depth, H, W, intrinsic, cam_to_world, depth_max, cell_size, origin, G, dilation,
-                                 bound_lo, bound_hi, coords, touched, stamp, stream))
+                                 bound_lo, bound_hi, coords, touched, stamp, nullptr, nullptr, stream))
         return rc;
     return ashb_tsdf_integrate(embeddings, n_emb, G, D, coords, touched, stamp, depth, color, H, W, intrinsic,
                                world_to_cam, depth_max, cell_size, origin, trunc, sdf_channel, rgb_channel,
-                               weight_channel, nullptr, stream);
+                               weight_channel, nullptr, nullptr, nullptr, stream);
 }
 
 }  // extern "C"
