@@ -35,6 +35,7 @@ HASH_KEYS, HASH_CAPACITY = 50_000_000, 64_000_000
 CPU_SCALE = 16  # the CPU arms run a 1/16-scale sample
 FWD_BYTES = 12 + 32 * EMB_DIM + 4 * EMB_DIM + 1          # x, 8 corner rows, y, mask
 BWD_BYTES = 4 * EMB_DIM + 12 + 32 * EMB_DIM + 32 * EMB_DIM + 12  # z, x, corner rows, gradient rows, grad x
+BWDBWD_BYTES = 12 + 4 * EMB_DIM + 12 + 32 * EMB_DIM + 32 * EMB_DIM + 4 * EMB_DIM  # ggx, z, x, rows, gradient rows, grad z
 FIND_BYTES = 12 + 16 + 8 + 1                              # key, one slot, index, mask
 # dram__bytes_read.sum + dram__bytes_write.sum per unit from the ncu captures summarised under profiles/
 # (taken on a reduced case whose tables are still many times L2; traffic per unit carries over)
@@ -165,6 +166,26 @@ def cpu_query_sample(bw, steps, warmup):
     return n_q / sec / 1e6, sec, oracle.num_threads(), (
         f"{n_q} queries over {n_blocks} blocks (1/{CPU_SCALE} of the workload), forward + backward with a fresh "
         f"dense gradient, mean of {len(times)} steps")
+
+
+def cpu_hash_sample(bw):
+    """Hash find of the CPU restatement on a 1/16-scale sample; M finds/s."""
+    import oracle
+
+    cpu = torch.device("cpu")
+    n = HASH_KEYS // CPU_SCALE
+    uniq = bw.hash_keys_clustered(n // 2, cpu)
+    om = oracle.OracleHashMap(3, HASH_CAPACITY // CPU_SCALE)
+    om.insert_keys(torch.cat([uniq, uniq]).numpy())
+    fresh = bw.hash_keys_clustered(n // 2, cpu, seed=bw.SEED + 77)
+    q = torch.cat([uniq, fresh])[torch.randperm(n, generator=torch.Generator().manual_seed(1))].numpy()
+    om.find(q)
+    t0 = time.perf_counter()
+    reps = 3
+    for _ in range(reps):
+        om.find(q)
+    sec = (time.perf_counter() - t0) / reps
+    return n / sec / 1e6, f"{n} finds in a table of {om.size()} keys (1/{CPU_SCALE} of the workload), mean of {reps}"
 
 
 def run_reference_arm(args):
@@ -391,6 +412,17 @@ def main():
                                                        "linear", grad_embeddings_out=gacc))
         if i >= args.warmup:
             bwd_persist_ms.append(t)
+    # double backward (the eikonal-style gradient-of-gradient pass), same persistent buffer
+    ggx = torch.randn(N_QUERIES, 3, device=device, generator=torch.Generator(device=device).manual_seed(5))
+    bwdbwd_ms = []
+    for i in range(args.warmup + args.steps):
+        x = xs[i % n_batches]
+        _, _, bidx = __ash.grid_query_forward(hm, emb, x, cell_size, origin, GRID_DIM, lut32, "linear")
+        t = event_ms(lambda: __ash.grid_query_backward_backward(hm, ggx, z, emb, x, cell_size, origin, GRID_DIM, lut32,
+                                                                bidx, "linear", grad_embeddings_out=gacc))
+        if i >= args.warmup:
+            bwdbwd_ms.append(t)
+    del ggx
     barrier()
 
     # gradient synchronisation cost (not on the timed data path): one dense all-reduce
@@ -455,6 +487,10 @@ def main():
             "query_forward": {"ms": round(f_ms, 4), "achieved_gbs": round(fa, 1), "frac": round(fa / peak, 4),
                               "traffic": N_QUERIES * FWD_TRAFFIC_PER_QUERY},
             "query_backward_dense(memset+kernel)": {"ms": round(b_ms, 4)},
+            "query_backward_backward(persistent gradient)": {
+                "ms": round(statistics.mean(bwdbwd_ms), 4),
+                "achieved_gbs": round(N_QUERIES * BWDBWD_BYTES / (statistics.mean(bwdbwd_ms) * 1e-3) / 1e9, 1),
+                "frac": round(N_QUERIES * BWDBWD_BYTES / (statistics.mean(bwdbwd_ms) * 1e-3) / 1e9 / peak, 4)},
             "step_api_faithful": {"bytes": step_bytes, "achieved_gbs": round(step_bytes / (ms_per_step * 1e-3) / 1e9, 1),
                                   "frac": round(step_bytes / (ms_per_step * 1e-3) / 1e9 / peak, 4)},
             "frac_of_8TBs_nominal": round(achieved / 8000.0, 4),
@@ -501,6 +537,40 @@ def main():
         del hm, heap, q, uniq
         torch.cuda.empty_cache()
 
+    if dist is not None and not args.no_hash:
+        # hash engine partitioned by key hash over the ranks, keys routed with all-to-all(v)
+        from ash.distributed import PartitionedHashMap
+
+        per_rank = HASH_KEYS // world
+        pm = PartitionedHashMap(3, HASH_CAPACITY, device)
+        uniq = bw.hash_keys_clustered(per_rank // 2, device, seed=bw.SEED + 4 + 1000 * rank)
+        g = torch.Generator(device=device).manual_seed(bw.SEED + 9 + rank)
+        keys = torch.cat([uniq, uniq])[torch.randperm(per_rank, generator=g, device=device)]
+        pm.find(keys[:1024])  # sets up the all-to-all connections outside the timed insert
+        barrier()
+        t_ins = event_ms(lambda: pm.insert_keys(keys))
+        fresh = bw.hash_keys_clustered(per_rank // 2, device, seed=bw.SEED + 77 + 1000 * rank)
+        q = torch.cat([uniq, fresh])[torch.randperm(per_rank, generator=g, device=device)]
+        del keys, fresh
+        for _ in range(2):
+            pm.find(q)
+        barrier()
+        reps = 5
+        t_find = event_ms(lambda: [pm.find(q) for _ in range(reps)]) / reps
+        hit = float(pm.find(q)[1].float().mean())
+        total = pm.size()
+        t = torch.tensor([t_ins, t_find], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if rank == 0:
+            line["hash_find_partitioned"] = {
+                "workload": f"{HASH_KEYS} keys over {world} ranks (owner = key hash mod {world}), all-to-all(v) routing of "
+                            "keys and of (index, mask) answers; 50% duplicates, 50% hit rate",
+                "value": round(HASH_KEYS / (float(t[1]) * 1e-3) / 1e6, 1), "unit": "M finds/s", "ms": round(float(t[1]), 3),
+                "insert_M_per_s": round(HASH_KEYS / (float(t[0]) * 1e-3) / 1e6, 1), "hit_rate": round(hit, 4),
+                "live_keys": total}
+        del pm, uniq, q
+        torch.cuda.empty_cache()
+
     if rank == 0 and not args.no_extras:
         line["tsdf_fusion"] = measure_tsdf(ash, bw, device, peak)
         torch.cuda.empty_cache()
@@ -510,6 +580,10 @@ def main():
     if rank == 0 and world == 1 and not args.no_cpu:
         v, sec, cores, sample = cpu_query_sample(bw, 2, 1)
         line["cpu_baseline"] = {"value": round(v, 4), "unit": "M queries/s", "cores": cores, "kind": "port", "sample": sample}
+        if "hash_find" in line:
+            hv, hsample = cpu_hash_sample(bw)
+            line["hash_find"]["cpu_baseline"] = {"value": round(hv, 2), "unit": "M finds/s", "cores": cores, "kind": "port",
+                                                 "sample": hsample}
 
     if dist is not None:
         dist.barrier()

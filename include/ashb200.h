@@ -160,7 +160,8 @@ int ashb_query_backward_backward(int dtype, int interp, const void* grad_grad_of
  * world -> cell transform, block / cell / offset split (ash/grid.py:183-199), hash find of the
  * block, neighbour resolution, gather and interpolation -- in one launch instead of ~15 torch
  * launches + find + query_forward.  x float32 [n][3] world positions; cell = (x - origin) *
- * (1 / cell_size) with origin a HOST float[3] (NULL = zero); nb_lut int32 [n_emb][8]: index of
+ * (float)(1.0 / cell_size) (the reciprocal is formed in double and rounded once, which is what
+ * `tensor / python_float` evaluates to on a CUDA tensor) with origin a HOST float[3] (NULL = zero); nb_lut int32 [n_emb][8]: index of
  * the block at offset (bit0, bit1, bit2) of the column, -1 absent (column 0 is the block
  * itself); the map must have key_dim 3.  Results are identical to the split + pre-split entry
  * points above. */
@@ -175,7 +176,7 @@ int ashb_grid_build_neighbor_lut(ashb_map* map, int32_t* nb_lut, int32_t* grid_c
  * and gets a zero row, as ash/src/grid.cu:109-111); block_idx_out int32 [n] (optional) = block
  * index per query, -1 on a miss, to be handed to the two backward entry points. */
 int ashb_grid_query_forward(ashb_map* map, int dtype, int interp, const void* embeddings, const float* x,
-                            float cell_size, const float* origin, int G, const int32_t* nb_lut, void* out,
+                            double cell_size, const float* origin, int G, const int32_t* nb_lut, void* out,
                             uint8_t* masks, int32_t* block_idx_out, int64_t n, int64_t n_emb, int64_t D,
                             void* stream);
 
@@ -183,16 +184,31 @@ int ashb_grid_query_forward(ashb_map* map, int dtype, int interp, const void* em
  * when the positions need no gradient and the eight embedding rows per query are not read at
  * all.  grad_embeddings accumulated (zero_grad as above).  block_idx NULL = probe the map again. */
 int ashb_grid_query_backward(ashb_map* map, int dtype, int interp, const void* z, const void* embeddings,
-                             const float* x, float cell_size, const float* origin, int G,
+                             const float* x, double cell_size, const float* origin, int G,
                              const int32_t* nb_lut, const int32_t* block_idx, void* grad_embeddings,
                              void* grad_x, int zero_grad, int64_t n, int64_t n_emb, int64_t D, void* stream);
 
 /* grad_grad_x [n][3] (type of embeddings): gradient arriving at grad_x. */
 int ashb_grid_query_backward_backward(ashb_map* map, int dtype, int interp, const void* grad_grad_x,
                                       const void* z, const void* embeddings, const float* x,
-                                      float cell_size, const float* origin, int G, const int32_t* nb_lut,
+                                      double cell_size, const float* origin, int G, const int32_t* nb_lut,
                                       const int32_t* block_idx, void* grad_z, void* grad_embeddings,
                                       int zero_grad, int64_t n, int64_t n_emb, int64_t D, void* stream);
+
+/* Block allocation from points: replaces SparseDenseGrid.spatial_init_ (ash/grid.py:121-159) --
+ * floor(points / cell / G), neighbourhood enumeration, the temporary HashSet used to
+ * deduplicate, insert_keys and find -- with one launch.  points float32 [n][3] world positions.
+ * Every block within `dilation` blocks (two-sided if bidirectional, else offsets 0..dilation)
+ * of a point's block is inserted if absent; points whose own block lies outside
+ * [bound_lo, bound_hi) (HOST int32[3], NULL = unbounded) are ignored, as are neighbours
+ * outside it.  For each such block idx: grid_coords[idx] (int32 [n_emb][3]) gets its
+ * coordinate, touched[idx] (uint32 [n_emb]) gets `stamp` (non-zero, different per call) and,
+ * if given, touched_list int32 [n_emb] / touched_count int32 [1] get the compact list. */
+int ashb_grid_spatial_init(ashb_map* map, const float* points, int64_t n, double cell_size,
+                           const float* origin, int G, int dilation, int bidirectional,
+                           const int32_t* bound_lo, const int32_t* bound_hi, int32_t* grid_coords,
+                           uint32_t* touched, uint32_t stamp, int32_t* touched_list,
+                           int32_t* touched_count, void* stream);
 
 /* ---------------------------------------------------------------- neighbourhood convolution */
 
@@ -262,7 +278,7 @@ int ashb_ray_sample_fill(ashb_map* map, const float* ray_origins, const float* r
  * touched_list int32 [n_emb] + touched_count int32 [1] (both device, both optional): the
  * compact list of the blocks stamped by this call, for ashb_tsdf_integrate. */
 int ashb_tsdf_touch(ashb_map* map, const float* depth, int H, int W, const float* intrinsic,
-                    const float* cam_to_world, float depth_max, float cell_size, const float* origin,
+                    const float* cam_to_world, float depth_max, double cell_size, const float* origin,
                     int G, int dilation, const int32_t* bound_lo, const int32_t* bound_hi,
                     int32_t* grid_coords, uint32_t* touched, uint32_t stamp, int32_t* touched_list,
                     int32_t* touched_count, void* stream);
@@ -277,7 +293,7 @@ int ashb_tsdf_touch(ashb_map* map, const float* depth, int H, int W, const float
 int ashb_tsdf_integrate(void* embeddings, int64_t n_emb, int G, int64_t D, const int32_t* grid_coords,
                         const uint32_t* touched, uint32_t stamp, const float* depth, const float* color,
                         int H, int W, const float* intrinsic, const float* world_to_cam, float depth_max,
-                        float cell_size, const float* origin, float trunc, int sdf_channel,
+                        double cell_size, const float* origin, float trunc, int sdf_channel,
                         int rgb_channel, int weight_channel, unsigned long long* n_integrated_dev,
                         const int32_t* touched_list, const int32_t* touched_count, void* stream);
 
@@ -298,10 +314,19 @@ int ashb_tsdf_static_max_blocks(void);
 int ashb_tsdf_fuse_frame_static(ashb_map* map, void* embeddings, int64_t n_emb, int G, int64_t D,
                                 const float* depth, const float* color, int H, int W,
                                 const float* intrinsic, const float* world_to_cam,
-                                const float* cam_to_world, float depth_max, float cell_size,
+                                const float* cam_to_world, float depth_max, double cell_size,
                                 const float* origin, int dilation, const int32_t* bound_lo,
                                 const int32_t* bound_hi, float trunc, int sdf_channel, int rgb_channel,
                                 int weight_channel, void* stream);
+
+/* ---------------------------------------------------------------- multi-GPU key routing
+ * For a hash map partitioned over `world` ranks by key hash (no counterpart in the reference,
+ * which is single-GPU): groups keys int32 [n][key_dim] by owner rank into keys_out (same shape),
+ * writes perm_out int64 [n] (source row of every output row) and counts_host int64 [world]
+ * (HOST: rows per owner, i.e. the send counts of the all-to-all).  scratch_dev: device buffer
+ * of at least 1024 bytes.  Synchronises `stream`. */
+int ashb_route_by_owner(const int32_t* keys, int64_t n, int key_dim, int world, int32_t* keys_out,
+                        int64_t* perm_out, int64_t* counts_host, void* scratch_dev, void* stream);
 
 /* ---------------------------------------------------------------- runtime knobs */
 

@@ -39,7 +39,8 @@ def unproject(depth, K, cam_to_world, depth_max):
 
 def touched_blocks(points, cell_size, origin, G, dilation, bounds=None):
     """ash/grid.py:132-148 with bidirectional dilation: unique block coordinates."""
-    inv_cell, inv_G = f32(1.0) / f32(cell_size), f32(1.0) / f32(G)
+    # reciprocals formed in double and rounded once, as torch does for `tensor / python_float`
+    inv_cell, inv_G = f32(1.0 / float(cell_size)), f32(1.0 / float(G))
     cells = (points - np.asarray(origin, f32)) * inv_cell
     blocks = np.floor(cells * inv_G).astype(np.int32)
     r = np.arange(-dilation, dilation + 1, dtype=np.int32)
@@ -79,7 +80,7 @@ class OracleTSDF:
     """Unbounded (origin 0) or bounded (origin = bbox_min) grid state on the CPU."""
 
     def __init__(self, num_embeddings, G, cell_size, dilation, D=5, origin=(0, 0, 0), bounds=None):
-        self.G, self.cell_size, self.dilation, self.origin, self.bounds = G, f32(cell_size), dilation, origin, bounds
+        self.G, self.cell_size, self.dilation, self.origin, self.bounds = G, float(cell_size), dilation, origin, bounds
         self.map = OracleHashMap(3, num_embeddings)
         self.emb = np.zeros((num_embeddings, G**3, D), f32)
         self.trunc = f32(dilation * cell_size * G)
@@ -99,7 +100,7 @@ class OracleTSDF:
         assert ok.all()
         # ash/grid.py:275-288 cell_to_world
         cells = (blocks[:, None, :] * self.G + self.cell_coords[None, :, :]).astype(f32)
-        pos = (cells * self.cell_size + np.asarray(self.origin, f32)).reshape(-1, 3)
+        pos = (cells * f32(self.cell_size) + np.asarray(self.origin, f32)).reshape(-1, 3)
         sdf, rgb, w = project(pos, K, world_to_cam[:3], color.astype(f32), depth, depth_max, self.trunc)
         e = self.emb[idx]  # (n, cells, D)
         n = len(blocks)

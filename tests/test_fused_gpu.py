@@ -115,3 +115,55 @@ def test_scatter_only_backward_when_positions_need_no_gradient():
         grads.append(grid.embeddings.grad.clone())
         assert (xr.grad is not None) == needs
     torch.testing.assert_close(grads[0], grads[1], rtol=4e-5, atol=4e-6)
+
+
+@pytest.mark.parametrize("kind", ["plain", "unbounded", "bounded"])
+@pytest.mark.parametrize("dilation,bidirectional", [(0, False), (1, False), (1, True), (2, True)])
+def test_fused_spatial_init_equals_python_sequence(kind, dilation, bidirectional):
+    """One-launch block allocation vs the floor / enumerate / temporary-hash-set / insert / find
+    sequence of ash/grid.py:121-159: same set of touched blocks, consistent indices, same table."""
+    import ash
+
+    def make():
+        if kind == "plain":
+            return ash.SparseDenseGrid(3, 80000, 1, 4, DEV)
+        if kind == "unbounded":
+            return ash.UnBoundedSparseDenseGrid(3, 80000, 1, 4, cell_size=0.03, device=DEV)
+        return ash.BoundedSparseDenseGrid(3, 80000, 1, grid_dim=4, sparse_grid_dim=10, device=DEV)
+
+    g = torch.Generator(device=DEV).manual_seed(dilation * 2 + bidirectional)
+    a, b = make(), make()
+    extent = {"plain": 60.0, "unbounded": 1.5, "bounded": 1.3}[kind]
+    pts = (torch.rand(3000, 3, generator=g, device=DEV) - 0.5) * 2 * extent
+    b.fused = False
+    for part in (pts[:2000], pts[1000:]):  # the second call meets blocks that already exist
+        ca, _, ia, _ = a.spatial_init_(part, dilation=dilation, bidirectional=bidirectional)
+        cb, _, ib, _ = b.spatial_init_(part, dilation=dilation, bidirectional=bidirectional)
+        sa = {tuple(r) for r in ca.view(-1, 3).tolist()}
+        sb = {tuple(r) for r in cb.view(-1, 3).tolist()}
+        assert sa == sb and len(sa) == ca.shape[0] > 0
+        # returned indices are the table's indices of the returned coordinates
+        found, ok = a.engine.find(ca.view(-1, 3))
+        assert ok.all() and torch.equal(found, ia.view(-1))
+    ka = {tuple(r) for r in a.engine.keys().tolist()}
+    kb = {tuple(r) for r in b.engine.keys().tolist()}
+    assert ka == kb and a.engine.size() == b.engine.size()
+    assert a.engine.backend.status() == 0
+
+
+@pytest.mark.parametrize("dim,world", [(3, 2), (3, 8), (1, 3), (4, 5), (2, 64)])
+def test_native_key_routing_matches_owner_function(dim, world):
+    import __ash
+    from ash.distributed import owner_of
+
+    g = torch.Generator(device=DEV).manual_seed(dim * 100 + world)
+    keys = torch.randint(-2**20, 2**20, (100003, dim), generator=g, device=DEV, dtype=torch.int32)
+    grouped, perm, counts = __ash.route_by_owner(keys, world)
+    owners = owner_of(keys, world)
+    assert counts == torch.bincount(owners, minlength=world).tolist()
+    assert torch.equal(torch.sort(perm)[0], torch.arange(keys.shape[0], device=DEV))
+    assert torch.equal(grouped, keys[perm])
+    go = owner_of(grouped, world)
+    assert (go[1:] >= go[:-1]).all()  # grouped by ascending owner
+    e, p, c = __ash.route_by_owner(keys[:0], world)
+    assert e.shape == (0, dim) and p.numel() == 0 and sum(c) == 0

@@ -51,19 +51,22 @@ _lib.ashb_conv_forward.argtypes = [_int] + [_vp] * 9 + [_int] + [_i64] * 6 + [_v
 _lib.ashb_ray_find_near_far.argtypes = [_vp] * 7 + [_f32] * 4 + [_i64, _vp]
 _lib.ashb_ray_sample_count.argtypes = [_vp] * 6 + [_i64, _f32, _i64, _vp]
 _lib.ashb_ray_sample_fill.argtypes = [_vp] * 9 + [_i64, _f32, _i64, _vp]
-_lib.ashb_tsdf_touch.argtypes = [_vp, _vp, _int, _int, _vp, _vp, _f32, _f32, _vp, _int, _int, _vp, _vp, _vp, _vp,
+_lib.ashb_tsdf_touch.argtypes = [_vp, _vp, _int, _int, _vp, _vp, _f32, _c.c_double, _vp, _int, _int, _vp, _vp, _vp, _vp,
                                  _c.c_uint32, _vp, _vp, _vp]
 _lib.ashb_tsdf_integrate.argtypes = [_vp, _i64, _int, _i64, _vp, _vp, _c.c_uint32, _vp, _vp, _int, _int, _vp, _vp,
-                                     _f32, _f32, _vp, _f32, _int, _int, _int, _vp, _vp, _vp, _vp]
-_lib.ashb_tsdf_fuse_frame_static.argtypes = [_vp, _vp, _i64, _int, _i64, _vp, _vp, _int, _int, _vp, _vp, _vp, _f32, _f32,
+                                     _f32, _c.c_double, _vp, _f32, _int, _int, _int, _vp, _vp, _vp, _vp]
+_lib.ashb_tsdf_fuse_frame_static.argtypes = [_vp, _vp, _i64, _int, _i64, _vp, _vp, _int, _int, _vp, _vp, _vp, _f32, _c.c_double,
                                              _vp, _int, _vp, _vp, _f32, _int, _int, _int, _vp]
 _lib.ashb_grid_build_neighbor_lut.argtypes = [_vp, _vp, _vp, _i64, _vp]
-_lib.ashb_grid_query_forward.argtypes = [_vp, _int, _int, _vp, _vp, _f32, _vp, _int, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]
-_lib.ashb_grid_query_backward.argtypes = [_vp, _int, _int, _vp, _vp, _vp, _f32, _vp, _int, _vp, _vp, _vp, _vp, _int,
+_lib.ashb_grid_query_forward.argtypes = [_vp, _int, _int, _vp, _vp, _c.c_double, _vp, _int, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]
+_lib.ashb_grid_query_backward.argtypes = [_vp, _int, _int, _vp, _vp, _vp, _c.c_double, _vp, _int, _vp, _vp, _vp, _vp, _int,
                                           _i64, _i64, _i64, _vp]
-_lib.ashb_grid_query_backward_backward.argtypes = [_vp, _int, _int, _vp, _vp, _vp, _vp, _f32, _vp, _int, _vp, _vp, _vp,
+_lib.ashb_grid_query_backward_backward.argtypes = [_vp, _int, _int, _vp, _vp, _vp, _vp, _c.c_double, _vp, _int, _vp, _vp, _vp,
                                                    _vp, _int, _i64, _i64, _i64, _vp]
 _lib.ashb_conv_forward_tiled.argtypes = [_vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _int, _int, _i64, _vp]
+_lib.ashb_grid_spatial_init.argtypes = [_vp, _vp, _i64, _c.c_double, _vp, _int, _int, _int, _vp, _vp, _vp, _vp, _c.c_uint32,
+                                        _vp, _vp, _vp]
+_lib.ashb_route_by_owner.argtypes = [_vp, _i64, _int, _int, _vp, _vp, _vp, _vp, _vp]
 
 STATUS_CAPACITY, STATUS_PROBE, STATUS_SPIN, STATUS_DUPLICATE = 1, 2, 4, 8
 _DTYPES = {torch.float32: 0, torch.float64: 1}
@@ -619,3 +622,37 @@ def convolution_forward_tiled(inputs, weights, grid_indices, lut_grid_nb27, grid
             inp.data_ptr(), w.data_ptr(), gi.data_ptr(), g27.data_ptr(), out.data_ptr(), 1, gi.shape[0], n_emb,
             int(grid_dim), int(radius), D, _stream(inp.device)))
     return out
+
+
+def grid_spatial_init(hashmap, points, cell_size, origin, grid_dim, dilation, bidirectional, grid_coords, touched,
+                      stamp, touched_list, touched_count, bound_lo=None, bound_hi=None):
+    """Allocate the blocks around ``points`` (N, 3) float32 world positions in one launch and
+    leave their compact list in ``touched_list[:touched_count]``; replaces the temporary hash
+    set + insert + find sequence of ash/grid.py:121-159.  No counterpart in the reference's
+    native module."""
+    dev = hashmap.device()
+    pts = _cuda(points, "points", torch.float32)
+    if pts.dim() != 2 or pts.shape[1] != 3:
+        raise RuntimeError("points must be (N, 3)")
+    lo = (_c.c_int32 * 3)(*bound_lo) if bound_lo is not None else None
+    hi = (_c.c_int32 * 3)(*bound_hi) if bound_hi is not None else None
+    _check(_lib.ashb_grid_spatial_init(
+        hashmap._h, pts.data_ptr(), pts.shape[0], float(cell_size), _host_floats(origin, 3), int(grid_dim),
+        int(dilation), int(bool(bidirectional)), lo, hi, grid_coords.data_ptr(), touched.data_ptr(), int(stamp),
+        touched_list.data_ptr(), touched_count.data_ptr(), _stream(dev)))
+
+
+def route_by_owner(keys, world):
+    """Group ``keys`` int32 (N, dim) by owner rank for the key-hash-partitioned map: returns
+    (keys grouped by owner, perm int64 (N,) = source row of every grouped row, send counts list).
+    No counterpart in the reference (single-GPU)."""
+    keys = _cuda(keys, "keys", torch.int32)
+    n, dim = keys.shape
+    out = torch.empty_like(keys)
+    perm = torch.empty(n, dtype=torch.int64, device=keys.device)
+    scratch = torch.empty(128, dtype=torch.int64, device=keys.device)
+    counts = (_i64 * int(world))()
+    with torch.cuda.device(keys.device):
+        _check(_lib.ashb_route_by_owner(keys.data_ptr(), n, dim, int(world), out.data_ptr(), perm.data_ptr(), counts,
+                                        scratch.data_ptr(), _stream(keys.device)))
+    return out, perm, list(counts)

@@ -19,7 +19,10 @@ from typing import Optional, Tuple
 import torch
 import torch.distributed as dist
 
+from .common import _get_c_extension
 from .core import ASHEngine
+
+backend = _get_c_extension()
 
 
 def owner_of(keys: torch.Tensor, world_size: int) -> torch.Tensor:
@@ -38,21 +41,28 @@ def owner_of(keys: torch.Tensor, world_size: int) -> torch.Tensor:
 class _Route:
     """One all-to-all(v) pattern: which rows go where, and how to bring answers back."""
 
-    def __init__(self, dest: torch.Tensor, group) -> None:
+    def __init__(self, keys: torch.Tensor, group) -> None:
         world = dist.get_world_size(group)
         self.group = group
-        self.order = torch.argsort(dest, stable=True)          # rows grouped by destination
-        send = torch.bincount(dest, minlength=world)
+        if keys.is_cuda and hasattr(backend, "route_by_owner"):
+            # native two-pass grouping: histogram + warp-aggregated scatter
+            self.sorted_keys, self.order, self.send_counts = backend.route_by_owner(keys, world)
+        else:
+            dest = owner_of(keys, world)
+            self.order = torch.argsort(dest, stable=True)      # rows grouped by destination
+            self.sorted_keys = keys[self.order].contiguous()
+            self.send_counts = torch.bincount(dest, minlength=world).tolist()
+        send = torch.tensor(self.send_counts, dtype=torch.int64, device=keys.device)
         recv = torch.empty_like(send)
         dist.all_to_all_single(recv, send, group=group)        # how many rows every peer sends me
-        self.send_counts = send.tolist()
         self.recv_counts = recv.tolist()
         self.n_recv = int(sum(self.recv_counts))
 
-    def forward(self, rows: torch.Tensor) -> torch.Tensor:
-        """Send ``rows`` (N, C) to their destinations; returns what this rank received."""
+    def forward(self) -> torch.Tensor:
+        """Ship the grouped keys to their owners; returns the keys this rank received."""
+        rows = self.sorted_keys
         out = torch.empty((self.n_recv,) + tuple(rows.shape[1:]), dtype=rows.dtype, device=rows.device)
-        dist.all_to_all_single(out, rows[self.order].contiguous(), self.recv_counts, self.send_counts, group=self.group)
+        dist.all_to_all_single(out, rows, self.recv_counts, self.send_counts, group=self.group)
         return out
 
     def backward(self, answers: torch.Tensor) -> torch.Tensor:
@@ -85,8 +95,8 @@ class PartitionedHashMap:
     def _route(self, keys: torch.Tensor) -> Tuple[_Route, torch.Tensor]:
         keys = keys.to(self.device, torch.int32).contiguous()
         assert keys.dim() == 2 and keys.shape[1] == self.key_dim, "keys shape mismatch"
-        route = _Route(owner_of(keys, self.world), self.group)
-        return route, route.forward(keys)
+        route = _Route(keys, self.group)
+        return route, route.forward()
 
     def insert_keys(self, keys: torch.Tensor) -> None:
         _, mine = self._route(keys)
@@ -106,10 +116,10 @@ class PartitionedHashMap:
         else:
             idx = torch.empty(0, dtype=torch.int64, device=self.device)
             masks = torch.empty(0, dtype=torch.bool, device=self.device)
-        global_idx = torch.where(masks, idx * self.world + self.rank, torch.zeros_like(idx))
-        packed = torch.stack([global_idx, masks.to(torch.int64)], dim=1)
-        back = route.backward(packed)
-        return back[:, 0].contiguous(), back[:, 1].to(torch.bool)
+        # one int64 per key on the wire: the global index, or -1 for a miss
+        answers = route.backward(torch.where(masks, idx * self.world + self.rank, torch.full_like(idx, -1)))
+        found = answers >= 0
+        return answers.clamp_(min=0), found
 
     def local_items(self) -> Tuple[torch.Tensor, torch.Tensor]:
         """This rank's (keys, GLOBAL indices)."""

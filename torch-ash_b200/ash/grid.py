@@ -69,6 +69,9 @@ class SparseDenseGrid(ASHModule):
         Returns ``(grid_coords (n,1,3) int32, cell_coords (1,G^3,3) int32, grid_indices (n,1)
         int64, cell_indices (1,G^3) int64)`` of the touched blocks, new or not.
         """
+        if (self.fused and points.is_cuda and hasattr(backend, "grid_spatial_init")
+                and self.transform_world_to_cell is self._own_transform):
+            return self._spatial_init_fused(points, dilation, bidirectional)
         points = self.transform_world_to_cell(points)
         block = self.grids_in_bound(torch.floor(points / self.grid_dim).int())
         offsets, _ = enumerate_neighbor_coord_offsets(self.in_dim, dilation, bidirectional, self.device)
@@ -90,6 +93,40 @@ class SparseDenseGrid(ASHModule):
             assert masks.all(), "grid capacity exhausted during spatial_init_"
         return (
             unique.view(-1, 1, self.in_dim),
+            self.cell_coords.view(1, -1, self.in_dim),
+            grid_indices.view(-1, 1),
+            self.cell_indices.view(1, -1),
+        )
+
+    def _block_bounds(self):
+        """Half-open range of admissible block coordinates, or (None, None)."""
+        return None, None
+
+    def _spatial_init_fused(self, points: torch.Tensor, dilation: int, bidirectional: bool):
+        """One launch: block of every point, neighbourhood, insert-if-absent, compact list of the
+        touched blocks.  The temporary hash set, insert, keys() and find of the reference's
+        sequence disappear; one device read (the list length) remains."""
+        n_emb = self.num_embeddings
+        if getattr(self, "_touch_scratch", None) is None:
+            dev = self.device
+            self._touch_scratch = (
+                torch.zeros((n_emb, 3), dtype=torch.int32, device=dev), torch.zeros(n_emb, dtype=torch.int32, device=dev),
+                torch.zeros(n_emb, dtype=torch.int32, device=dev), torch.zeros(1, dtype=torch.int32, device=dev))
+            self._touch_stamp = 0
+        coords, touched, tlist, tcount = self._touch_scratch
+        self._touch_stamp = self._touch_stamp % 0x7FFFFFFF + 1
+        origin, cell_size = self._cell_frame()
+        lo, hi = self._block_bounds()
+        backend.grid_spatial_init(
+            self.engine.backend, points.to(torch.float32).contiguous().view(-1, self.in_dim), cell_size, origin,
+            self.grid_dim, dilation, bidirectional, coords, touched, self._touch_stamp, tlist, tcount, lo, hi)
+        n = int(tcount.item())
+        st = self.engine.backend.status()
+        assert not (st & backend.STATUS_CAPACITY), "grid capacity exhausted during spatial_init_"
+        self.engine._size_bound = self.engine.capacity  # native insertions bypass the host-side bound
+        grid_indices = tlist[:n].long()
+        return (
+            coords[grid_indices].view(-1, 1, self.in_dim),
             self.cell_coords.view(1, -1, self.in_dim),
             grid_indices.view(-1, 1),
             self.cell_indices.view(1, -1),
@@ -379,6 +416,9 @@ class BoundedSparseDenseGrid(SparseDenseGrid):
     def grids_in_bound(self, grid_coords: torch.Tensor) -> torch.Tensor:
         inside = ((grid_coords >= 0) & (grid_coords < self.sparse_grid_dim)).all(dim=-1)
         return grid_coords[inside]
+
+    def _block_bounds(self):
+        return [0, 0, 0], [self.sparse_grid_dim] * 3
 
     def dense_init_(self):
         """Activate every block of the box."""

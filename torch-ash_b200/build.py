@@ -48,7 +48,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         obj = os.path.join(obj_dir, os.path.basename(src)[:-3] + ".o")
         if not force and os.path.exists(obj) and os.path.getmtime(obj) > max(os.path.getmtime(src), dep_time):
             return obj, False
-        cmd = [_nvcc(), *NVCC_FLAGS, "-c", src, "-o", obj]
+        cmd = [_nvcc(), *NVCC_FLAGS, *os.environ.get("ASHB_NVCC_EXTRA", "").split(), "-c", src, "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         r = subprocess.run(cmd, env=env, capture_output=True, text=True)

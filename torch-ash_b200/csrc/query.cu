@@ -254,8 +254,11 @@ __global__ void __launch_bounds__(256) query_forward_kernel(const T* __restrict_
 // grad_off receives d/d offset times `go_scale` (1 for the pre-split interface, 1 / cell_size
 // when the caller differentiates w.r.t. world positions).  With grad_off == nullptr only the
 // scatter runs: the eight embedding rows are not read at all.
+#ifndef ASHB_BWD_MIN_BLOCKS
+#define ASHB_BWD_MIN_BLOCKS 1
+#endif
 template <typename T, int VEC, class Src, bool NEED_GO>
-__global__ void __launch_bounds__(256) query_backward_forward_kernel(
+__global__ void __launch_bounds__(256, ASHB_BWD_MIN_BLOCKS) query_backward_forward_kernel(
         const T* __restrict__ z, const T* __restrict__ emb, Src src, T* __restrict__ grad_emb,
         T* __restrict__ grad_off, T go_scale, int64_t n, int D, int lane_shift, int interp) {
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -312,7 +315,7 @@ __global__ void __launch_bounds__(256) query_backward_forward_kernel(
 
 // ---- double backward ----------------------------------------------------------------
 template <typename T, int VEC, class Src>
-__global__ void __launch_bounds__(256) query_backward_backward_kernel(
+__global__ void __launch_bounds__(256, ASHB_BWD_MIN_BLOCKS) query_backward_backward_kernel(
         const T* __restrict__ ggo, const T* __restrict__ z, const T* __restrict__ emb, Src src,
         T* __restrict__ grad_z, T* __restrict__ grad_emb, T go_scale, int64_t n, int D, int lane_shift,
         int interp) {
@@ -484,19 +487,20 @@ __global__ void __launch_bounds__(256) build_nb_lut_kernel(Table16 t, int32_t* _
     }
 }
 
-static int make_fused_source(ashb_map* m, const float* x, float cell_size, const float* origin, int G,
+static int make_fused_source(ashb_map* m, const float* x, double cell_size, const float* origin, int G,
                              const int32_t* nb_lut, const int32_t* gi_in, int32_t* gi_out, uint8_t* mask_out,
                              int64_t n_emb, FusedSource* out) {
     ASHB_REQUIRE(m != nullptr && m->slots != nullptr, "null or destroyed map");
     ASHB_REQUIRE(m->key_dim == 3, "the grid query needs a 3-D map");
-    ASHB_REQUIRE(G >= 1 && G <= 64 && cell_size > 0.f, "bad grid_dim or cell_size");
+    ASHB_REQUIRE(G >= 1 && G <= 64 && cell_size > 0.0, "bad grid_dim or cell_size");
     ASHB_REQUIRE(x && nb_lut, "null buffer");
     ASHB_REQUIRE(((uintptr_t)nb_lut & 15) == 0, "neighbour table must be 16-byte aligned");
     FusedSource f{};
     f.table = table16_of(m);
     f.x = x;
     for (int d = 0; d < 3; ++d) f.org[d] = origin ? origin[d] : 0.f;
-    f.inv_cell = 1.0f / cell_size;
+    // the reciprocal is formed in double and rounded once, as torch does for `tensor / python_float`
+    f.inv_cell = (float)(1.0 / cell_size);
     f.G = G;
     f.G_f = (float)G;
     f.inv_G = 1.0f / (float)G;
@@ -595,7 +599,7 @@ int ashb_grid_build_neighbor_lut(ashb_map* m, int32_t* lut, int32_t* grid_coords
 }
 
 int ashb_grid_query_forward(ashb_map* m, int dtype, int interp, const void* embeddings, const float* x,
-                            float cell_size, const float* origin, int G, const int32_t* nb_lut, void* out,
+                            double cell_size, const float* origin, int G, const int32_t* nb_lut, void* out,
                             uint8_t* masks, int32_t* block_idx_out, int64_t n, int64_t n_emb, int64_t D,
                             void* stream) {
     if (int rc = check_query_args(dtype, interp, n, n_emb, (int64_t)G * G * G, D)) return rc;
@@ -611,7 +615,7 @@ int ashb_grid_query_forward(ashb_map* m, int dtype, int interp, const void* embe
 }
 
 int ashb_grid_query_backward(ashb_map* m, int dtype, int interp, const void* z, const void* embeddings,
-                             const float* x, float cell_size, const float* origin, int G, const int32_t* nb_lut,
+                             const float* x, double cell_size, const float* origin, int G, const int32_t* nb_lut,
                              const int32_t* block_idx, void* grad_embeddings, void* grad_x, int zero_grad,
                              int64_t n, int64_t n_emb, int64_t D, void* stream) {
     if (int rc = check_query_args(dtype, interp, n, n_emb, (int64_t)G * G * G, D)) return rc;
@@ -627,7 +631,7 @@ int ashb_grid_query_backward(ashb_map* m, int dtype, int interp, const void* z, 
     FusedSource src;
     if (int rc = make_fused_source(m, x, cell_size, origin, G, nb_lut, block_idx, nullptr, nullptr, n_emb, &src))
         return rc;
-    const double scale = (double)(1.0f / cell_size);  // the float reciprocal the forward split multiplies by
+    const double scale = (double)(float)(1.0 / cell_size);  // the float reciprocal the forward split multiplies by
     return dtype == ASHB_F32 ? backward_forward_impl<float>(interp, z, embeddings, src, grad_embeddings, grad_x,
                                                             scale, n, D, st)
                              : backward_forward_impl<double>(interp, z, embeddings, src, grad_embeddings, grad_x,
@@ -635,7 +639,7 @@ int ashb_grid_query_backward(ashb_map* m, int dtype, int interp, const void* z, 
 }
 
 int ashb_grid_query_backward_backward(ashb_map* m, int dtype, int interp, const void* grad_grad_x, const void* z,
-                                      const void* embeddings, const float* x, float cell_size,
+                                      const void* embeddings, const float* x, double cell_size,
                                       const float* origin, int G, const int32_t* nb_lut,
                                       const int32_t* block_idx, void* grad_z, void* grad_embeddings,
                                       int zero_grad, int64_t n, int64_t n_emb, int64_t D, void* stream) {
@@ -652,7 +656,7 @@ int ashb_grid_query_backward_backward(ashb_map* m, int dtype, int interp, const 
     FusedSource src;
     if (int rc = make_fused_source(m, x, cell_size, origin, G, nb_lut, block_idx, nullptr, nullptr, n_emb, &src))
         return rc;
-    const double scale = (double)(1.0f / cell_size);  // the float reciprocal the forward split multiplies by
+    const double scale = (double)(float)(1.0 / cell_size);  // the float reciprocal the forward split multiplies by
     return dtype == ASHB_F32 ? backward_backward_impl<float>(interp, grad_grad_x, z, embeddings, src, grad_z,
                                                              grad_embeddings, scale, n, D, st)
                              : backward_backward_impl<double>(interp, grad_grad_x, z, embeddings, src, grad_z,

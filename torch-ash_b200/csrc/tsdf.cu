@@ -45,37 +45,28 @@ __device__ __forceinline__ float dot3(const float* r, float x, float y, float z)
 }
 
 // ---- touch -------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) tsdf_touch_kernel(Table16 t, int32_t* __restrict__ heap, int32_t* counter,
-                                                         int32_t capacity, const float* __restrict__ depth, int H,
-                                                         int W, Camera cam, float depth_max, float inv_cell,
-                                                         float3 origin, float inv_G, int dilation,
-                                                         int3 lo, int3 hi, int bounded,
-                                                         int32_t* __restrict__ grid_coords,
-                                                         uint32_t* __restrict__ touched, uint32_t stamp,
-                                                         int32_t* __restrict__ touched_list,
-                                                         int32_t* touched_count) {
-    const int64_t pix = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    bool valid = pix < (int64_t)H * W;
-    int bx = 0, by = 0, bz = 0;
-    if (valid) {
-        const float d = depth[pix];
-        valid = d > 0.f && d < depth_max;
-        if (valid) {
-            const int v = (int)(pix / W), u = (int)(pix - (int64_t)v * W);
-            // camera point of pixel (u, v) at depth d for K = [fx 0 cx; 0 fy cy; 0 0 1]
-            const float xc = __fdiv_rn(__fmul_rn(__fsub_rn((float)u, cam.K[2]), d), cam.K[0]);
-            const float yc = __fdiv_rn(__fmul_rn(__fsub_rn((float)v, cam.K[5]), d), cam.K[4]);
-            const float wx = affine3(cam.Ei, xc, yc, d);
-            const float wy = affine3(cam.Ei + 4, xc, yc, d);
-            const float wz = affine3(cam.Ei + 8, xc, yc, d);
-            // world -> cell -> block as the Python layer does on a CUDA tensor:
-            // multiply by the float reciprocals (ash/grid.py:132-134, :756, :846)
-            bx = (int)floorf(__fmul_rn(__fmul_rn(__fsub_rn(wx, origin.x), inv_cell), inv_G));
-            by = (int)floorf(__fmul_rn(__fmul_rn(__fsub_rn(wy, origin.y), inv_cell), inv_G));
-            bz = (int)floorf(__fmul_rn(__fmul_rn(__fsub_rn(wz, origin.z), inv_cell), inv_G));
-        }
-    }
-    // one lane per distinct block in the warp does the neighbourhood
+struct TouchTarget {
+    int32_t* heap;
+    int32_t* counter;
+    int32_t capacity;
+    int lo_off, hi_off;  // neighbourhood offsets per axis: [-dilation, dilation] or [0, dilation]
+    int3 lo, hi;         // admissible block coordinates (half open) when bounded
+    int bounded;
+    int32_t* grid_coords;
+    uint32_t* touched;
+    uint32_t stamp;
+    int32_t* touched_list;
+    int32_t* touched_count;
+};
+
+// Called by every lane of a warp (`valid` lanes carry a block): one lane per distinct block
+// inserts-if-absent the blocks of its neighbourhood, records their coordinates and stamps them.
+__device__ __forceinline__ void touch_neighbourhood(const Table16& t, const TouchTarget& tt, bool valid, int bx,
+                                                    int by, int bz) {
+    // a point whose own block is out of bounds contributes nothing (ash/grid.py:134-135)
+    if (valid && tt.bounded &&
+        (bx < tt.lo.x || by < tt.lo.y || bz < tt.lo.z || bx >= tt.hi.x || by >= tt.hi.y || bz >= tt.hi.z))
+        valid = false;
     const unsigned active = __ballot_sync(0xffffffffu, valid);
     if (!valid) return;
     const unsigned long long packed = ((unsigned long long)(unsigned)bx * 0x9E3779B97F4A7C15ull) ^
@@ -88,11 +79,12 @@ __global__ void __launch_bounds__(256) tsdf_touch_kernel(Table16 t, int32_t* __r
               lbz = __shfl_sync(peers, bz, leader);
     if ((int)(threadIdx.x & 31) != leader && lbx == bx && lby == by && lbz == bz) return;
 
-    for (int dz = -dilation; dz <= dilation; ++dz)
-        for (int dy = -dilation; dy <= dilation; ++dy)
-            for (int dx = -dilation; dx <= dilation; ++dx) {
+    for (int dz = tt.lo_off; dz <= tt.hi_off; ++dz)
+        for (int dy = tt.lo_off; dy <= tt.hi_off; ++dy)
+            for (int dx = tt.lo_off; dx <= tt.hi_off; ++dx) {
                 const int kx = bx + dx, ky = by + dy, kz = bz + dz;
-                if (bounded && (kx < lo.x || ky < lo.y || kz < lo.z || kx >= hi.x || ky >= hi.y || kz >= hi.z))
+                if (tt.bounded && (kx < tt.lo.x || ky < tt.lo.y || kz < tt.lo.z || kx >= tt.hi.x || ky >= tt.hi.y ||
+                                   kz >= tt.hi.z))
                     continue;
                 // fast path: the block exists already (probe at L2: this launch mutates the table)
                 int idx = -1;
@@ -112,27 +104,71 @@ __global__ void __launch_bounds__(256) tsdf_touch_kernel(Table16 t, int32_t* __r
                     bool present = false;
                     const int64_t slot = emplace(t, kx, ky, kz, 0, kPending, &present);
                     if (slot < 0) continue;  // another thread of this launch owns it and stamps it
-                    const int top = atomicAdd(counter, 1);
-                    if (top >= capacity) {
-                        atomicSub(counter, 1);
+                    const int top = atomicAdd(tt.counter, 1);
+                    if (top >= tt.capacity) {
+                        atomicSub(tt.counter, 1);
                         *reinterpret_cast<volatile int*>(t.val_ptr((uint32_t)slot)) = kTomb;
                         atomicOr(t.status, ASHB_STATUS_CAPACITY);
                         continue;
                     }
-                    idx = heap[top];
+                    idx = tt.heap[top];
                     *reinterpret_cast<volatile int*>(t.val_ptr((uint32_t)slot)) = idx;
                 }
                 // the coordinate is recorded for blocks allocated by other means too
-                grid_coords[3 * idx] = kx;
-                grid_coords[3 * idx + 1] = ky;
-                grid_coords[3 * idx + 2] = kz;
-                if (touched_list) {
-                    // first toucher of the frame appends the block to the compact work list
-                    if (atomicExch(&touched[idx], stamp) != stamp) touched_list[atomicAdd(touched_count, 1)] = idx;
+                tt.grid_coords[3 * idx] = kx;
+                tt.grid_coords[3 * idx + 1] = ky;
+                tt.grid_coords[3 * idx + 2] = kz;
+                if (tt.touched_list) {
+                    // first toucher of the call appends the block to the compact work list
+                    if (atomicExch(&tt.touched[idx], tt.stamp) != tt.stamp)
+                        tt.touched_list[atomicAdd(tt.touched_count, 1)] = idx;
                 } else {
-                    touched[idx] = stamp;
+                    tt.touched[idx] = tt.stamp;
                 }
             }
+}
+
+// world -> cell -> block as the Python layer does on a CUDA tensor: multiply by the float
+// reciprocals (ash/grid.py:132-134, :756, :846)
+__device__ __forceinline__ int block_of(float w, float org, float inv_cell, float inv_G) {
+    return (int)floorf(__fmul_rn(__fmul_rn(__fsub_rn(w, org), inv_cell), inv_G));
+}
+
+__global__ void __launch_bounds__(256) tsdf_touch_kernel(Table16 t, TouchTarget tt, const float* __restrict__ depth,
+                                                         int H, int W, Camera cam, float depth_max, float inv_cell,
+                                                         float3 origin, float inv_G) {
+    const int64_t pix = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    bool valid = pix < (int64_t)H * W;
+    int bx = 0, by = 0, bz = 0;
+    if (valid) {
+        const float d = depth[pix];
+        valid = d > 0.f && d < depth_max;
+        if (valid) {
+            const int v = (int)(pix / W), u = (int)(pix - (int64_t)v * W);
+            // camera point of pixel (u, v) at depth d for K = [fx 0 cx; 0 fy cy; 0 0 1]
+            const float xc = __fdiv_rn(__fmul_rn(__fsub_rn((float)u, cam.K[2]), d), cam.K[0]);
+            const float yc = __fdiv_rn(__fmul_rn(__fsub_rn((float)v, cam.K[5]), d), cam.K[4]);
+            bx = block_of(affine3(cam.Ei, xc, yc, d), origin.x, inv_cell, inv_G);
+            by = block_of(affine3(cam.Ei + 4, xc, yc, d), origin.y, inv_cell, inv_G);
+            bz = block_of(affine3(cam.Ei + 8, xc, yc, d), origin.z, inv_cell, inv_G);
+        }
+    }
+    touch_neighbourhood(t, tt, valid, bx, by, bz);
+}
+
+// SparseDenseGrid.spatial_init_ (ash/grid.py:121-159) without its temporary hash set: one
+// thread per point.
+__global__ void __launch_bounds__(256) points_touch_kernel(Table16 t, TouchTarget tt, const float* __restrict__ pts,
+                                                           int64_t n, float inv_cell, float3 origin, float inv_G) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool valid = i < n;
+    int bx = 0, by = 0, bz = 0;
+    if (valid) {
+        bx = block_of(pts[3 * i], origin.x, inv_cell, inv_G);
+        by = block_of(pts[3 * i + 1], origin.y, inv_cell, inv_G);
+        bz = block_of(pts[3 * i + 2], origin.z, inv_cell, inv_G);
+    }
+    touch_neighbourhood(t, tt, valid, bx, by, bz);
 }
 
 // ---- integrate ---------------------------------------------------------------------
@@ -221,33 +257,80 @@ using namespace ashb;
 
 extern "C" {
 
+static int make_touch_target(ashb_map* m, int dilation, int bidirectional, const int32_t* bound_lo,
+                             const int32_t* bound_hi, int32_t* grid_coords, uint32_t* touched, uint32_t stamp,
+                             int32_t* touched_list, int32_t* touched_count, TouchTarget* out) {
+    ASHB_REQUIRE(m != nullptr && m->slots != nullptr, "null or destroyed map");
+    ASHB_REQUIRE(m->key_dim == 3, "block allocation needs a 3-D map");
+    ASHB_REQUIRE(grid_coords && touched, "null buffer");
+    ASHB_REQUIRE(dilation >= 0 && dilation <= 4, "dilation %d not in 0..4", dilation);
+    ASHB_REQUIRE(stamp != 0, "stamp 0 is reserved for 'never touched'");
+    ASHB_REQUIRE((touched_list == nullptr) == (touched_count == nullptr),
+                 "pass both the list and its counter, or neither");
+    TouchTarget tt{};
+    tt.heap = m->heap;
+    tt.counter = m->counter;
+    tt.capacity = (int32_t)m->capacity;
+    tt.lo_off = bidirectional ? -dilation : 0;
+    tt.hi_off = dilation;
+    tt.bounded = bound_lo != nullptr && bound_hi != nullptr;
+    if (tt.bounded) {
+        tt.lo = make_int3(bound_lo[0], bound_lo[1], bound_lo[2]);
+        tt.hi = make_int3(bound_hi[0], bound_hi[1], bound_hi[2]);
+    }
+    tt.grid_coords = grid_coords;
+    tt.touched = touched;
+    tt.stamp = stamp;
+    tt.touched_list = touched_list;
+    tt.touched_count = touched_count;
+    *out = tt;
+    return ASHB_OK;
+}
+
 int ashb_tsdf_touch(ashb_map* m, const float* depth, int H, int W, const float* intrinsic,
-                    const float* cam_to_world, float depth_max, float cell_size, const float* origin, int G,
+                    const float* cam_to_world, float depth_max, double cell_size, const float* origin, int G,
                     int dilation, const int32_t* bound_lo, const int32_t* bound_hi, int32_t* grid_coords,
                     uint32_t* touched, uint32_t stamp, int32_t* touched_list, int32_t* touched_count,
                     void* stream) {
-    ASHB_REQUIRE(m != nullptr && m->slots != nullptr, "null or destroyed map");
-    ASHB_REQUIRE(m->key_dim == 3, "TSDF integration needs a 3-D map");
-    ASHB_REQUIRE(depth && intrinsic && cam_to_world && origin && grid_coords && touched, "null buffer");
-    ASHB_REQUIRE(H > 0 && W > 0 && G > 0 && cell_size > 0.f && dilation >= 0 && dilation <= 4, "bad frame or grid geometry");
-    ASHB_REQUIRE(stamp != 0, "stamp 0 is reserved for 'never touched'");
+    TouchTarget tt;
+    if (int rc = make_touch_target(m, dilation, 1, bound_lo, bound_hi, grid_coords, touched, stamp, touched_list,
+                                   touched_count, &tt))
+        return rc;
+    ASHB_REQUIRE(depth && intrinsic && cam_to_world && origin, "null buffer");
+    ASHB_REQUIRE(H > 0 && W > 0 && G > 0 && cell_size > 0.0, "bad frame or grid geometry");
     DeviceGuard guard(m->device);
     Camera cam{};
     for (int i = 0; i < 9; ++i) cam.K[i] = intrinsic[i];
     for (int i = 0; i < 12; ++i) cam.Ei[i] = cam_to_world[i];
     ASHB_REQUIRE(cam.K[0] != 0.f && cam.K[4] != 0.f && cam.K[1] == 0.f && cam.K[3] == 0.f,
                  "intrinsic must be a skew-free pinhole matrix");
-    const int bounded = bound_lo != nullptr && bound_hi != nullptr;
-    const int3 lo = bounded ? make_int3(bound_lo[0], bound_lo[1], bound_lo[2]) : make_int3(0, 0, 0);
-    const int3 hi = bounded ? make_int3(bound_hi[0], bound_hi[1], bound_hi[2]) : make_int3(0, 0, 0);
-    ASHB_REQUIRE((touched_list == nullptr) == (touched_count == nullptr), "pass both the list and its counter, or neither");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int64_t n = (int64_t)H * W;
     if (touched_count) ASHB_CUDA_TRY(cudaMemsetAsync(touched_count, 0, sizeof(int32_t), st));
     tsdf_touch_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
-            table16_of(m), m->heap, m->counter, (int32_t)m->capacity, depth, H, W, cam, depth_max,
-            1.0f / cell_size, make_float3(origin[0], origin[1], origin[2]), 1.0f / (float)G, dilation, lo, hi,
-            bounded, grid_coords, touched, stamp, touched_list, touched_count);
+            table16_of(m), tt, depth, H, W, cam, depth_max, (float)(1.0 / cell_size),
+            make_float3(origin[0], origin[1], origin[2]), 1.0f / (float)G);
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+int ashb_grid_spatial_init(ashb_map* m, const float* points, int64_t n, double cell_size, const float* origin, int G,
+                           int dilation, int bidirectional, const int32_t* bound_lo, const int32_t* bound_hi,
+                           int32_t* grid_coords, uint32_t* touched, uint32_t stamp, int32_t* touched_list,
+                           int32_t* touched_count, void* stream) {
+    TouchTarget tt;
+    if (int rc = make_touch_target(m, dilation, bidirectional, bound_lo, bound_hi, grid_coords, touched, stamp,
+                                   touched_list, touched_count, &tt))
+        return rc;
+    ASHB_REQUIRE(n >= 0 && G > 0 && cell_size > 0.0, "bad point count or grid geometry");
+    DeviceGuard guard(m->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (touched_count) ASHB_CUDA_TRY(cudaMemsetAsync(touched_count, 0, sizeof(int32_t), st));
+    if (n == 0) return ASHB_OK;
+    ASHB_REQUIRE(points != nullptr, "null points");
+    const float3 org = origin ? make_float3(origin[0], origin[1], origin[2]) : make_float3(0.f, 0.f, 0.f);
+    points_touch_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(table16_of(m), tt, points, n, (float)(1.0 / cell_size),
+                                                                      org, 1.0f / (float)G);
     ASHB_LAUNCH_CHECK();
     return ASHB_OK;
 }
@@ -255,7 +338,7 @@ int ashb_tsdf_touch(ashb_map* m, const float* depth, int H, int W, const float* 
 int ashb_tsdf_integrate(void* embeddings, int64_t n_emb, int G, int64_t D, const int32_t* grid_coords,
                         const uint32_t* touched, uint32_t stamp, const float* depth, const float* color, int H,
                         int W, const float* intrinsic, const float* world_to_cam, float depth_max,
-                        float cell_size, const float* origin, float trunc, int sdf_channel, int rgb_channel,
+                        double cell_size, const float* origin, float trunc, int sdf_channel, int rgb_channel,
                         int weight_channel, unsigned long long* n_integrated_dev, const int32_t* touched_list,
                         const int32_t* touched_count, void* stream) {
     ASHB_REQUIRE((touched_list == nullptr) == (touched_count == nullptr), "pass both the list and its counter, or neither");
@@ -284,7 +367,7 @@ int ashb_tsdf_integrate(void* embeddings, int64_t n_emb, int G, int64_t D, const
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));  \
         tsdf_integrate_kernel<DD><<<launch_ctas, 256, smem, st>>>(                                         \
                 static_cast<float*>(embeddings), grid_coords, touched, stamp, depth, color, H, W, cam,     \
-                depth_max, cell_size, org, G, cells, trunc, sdf_channel, rgb_channel, weight_channel,      \
+                depth_max, (float)cell_size, org, G, cells, trunc, sdf_channel, rgb_channel, weight_channel,      \
                 n_integrated_dev, n_emb, touched_list, touched_count);                                     \
     } break;
     switch ((int)D) {
@@ -332,7 +415,7 @@ int ashb_tsdf_static_max_blocks(void) { return ASHB_TSDF_STATIC_MAX_BLOCKS; }
 int ashb_tsdf_fuse_frame_static(ashb_map* m, void* embeddings, int64_t n_emb, int G, int64_t D,
                                 const float* depth, const float* color, int H, int W, const float* intrinsic,
                                 const float* world_to_cam, const float* cam_to_world, float depth_max,
-                                float cell_size, const float* origin, int dilation, const int32_t* bound_lo,
+                                double cell_size, const float* origin, int dilation, const int32_t* bound_lo,
                                 const int32_t* bound_hi, float trunc, int sdf_channel, int rgb_channel,
                                 int weight_channel, void* stream) {
     ASHB_REQUIRE(m != nullptr && m->slots != nullptr, "null or destroyed map");
