@@ -284,15 +284,45 @@ def measure_bounded(ash, bw, device, peak):
     o = (torch.rand(n_rays, 3, generator=g, device=device) - 0.5) * 1.2
     tgt = (torch.rand(n_rays, 3, generator=g, device=device) - 0.5) * 1.2
     d = torch.nn.functional.normalize(tgt - o, dim=-1)
-    grid.ray_find_near_far(o, d, 0.06, 1.0, 0.01)
-    nf_ms = event_ms(lambda: grid.ray_find_near_far(o, d, 0.06, 1.0, 0.01))
-    nears, fars = grid.ray_find_near_far(o, d, 0.06, 1.0, 0.01)
+    grid.ray_find_near_far(o, d, 0.06, 2.5, 0.01)
+    nf_ms = event_ms(lambda: grid.ray_find_near_far(o, d, 0.06, 2.5, 0.01))
+    nears, fars = grid.ray_find_near_far(o, d, 0.06, 2.5, 0.01)
     hit = nears >= 0
     o, d, nears, fars = o[hit], d[hit], nears[hit], fars[hit]
     grid.ray_sample(o, d, nears, fars, 128)
     rs_ms = event_ms(lambda: grid.ray_sample(o, d, nears, fars, 128))
     n_samples = int(grid.ray_sample(o, d, nears, fars, 128)[0].numel())
     ray_gbs = (o.shape[0] * 24 + n_samples * 20) / (rs_ms * 1e-3) / 1e9
+
+    # one volume-rendering training step over those rays, composed as the reference's
+    # PlainVoxels.forward + loss.backward() (demo/train_scene_recon.py:64-161, :316-343)
+    from ash.render import SDFToDensity, accumulate_along_rays, render_weight_from_density
+
+    to_sigma = SDFToDensity(min_beta=grid.cell_size, init_beta=2 * grid.cell_size).to(device)
+    n_r = o.shape[0]
+
+    def train_step():
+        grid.embeddings.grad = None
+        ri, t0, t1, _ = grid.ray_sample(o, d, nears, fars, 128)
+        t_mid = 0.5 * (t0 + t1).view(-1, 1)
+        x = (o[ri] + t_mid * d[ri]).requires_grad_(True)
+        emb, masks = grid(x, interpolation="linear")
+        sdf, rgb = emb[:, 0:1].contiguous(), emb[:, 1:4].contiguous()
+        (sdf_grad,) = torch.autograd.grad(sdf, x, torch.ones_like(sdf), create_graph=True)
+        sigma = to_sigma(sdf) * masks.view(-1, 1).float()
+        w = render_weight_from_density(t0.view(-1, 1), t1.view(-1, 1), sigma, ri, n_r)
+        rendered = accumulate_along_rays(w, ri, rgb, n_r)
+        depth = accumulate_along_rays(w, ri, t_mid, n_r)
+        loss = (rendered - 0.5).abs().mean() + 0.1 * (depth - 0.3).abs().mean() \
+            + 0.1 * ((sdf_grad.norm(dim=-1) - 1) ** 2).mean()
+        loss.backward()
+        return loss
+
+    for _ in range(3):
+        train_step()
+    reps = 10
+    step_ms = event_ms(lambda: [train_step() for _ in range(reps)]) / reps
+    grid.embeddings.grad = None
     return {
         "workload": f"bounded grid 512^3 ({S} blocks x grid_dim {G}), {D} channels, {n_blocks} active blocks",
         "gaussian_filter_7x7x7": {"ms": round(conv_ms, 3), "cells_per_s": round(cells / (conv_ms * 1e-3) / 1e9, 3),
@@ -304,6 +334,11 @@ def measure_bounded(ash, bw, device, peak):
         "ray_sample": {"rays": int(o.shape[0]), "samples": n_samples, "ms": round(rs_ms, 4),
                        "samples_per_s": round(n_samples / (rs_ms * 1e-3) / 1e6, 2), "unit": "M samples/s",
                        "achieved_gbs": round(ray_gbs, 2), "frac": round(ray_gbs / peak, 5)},
+        "volume_rendering_train_step": {
+            "what": "ray_sample + fused query + eikonal double backward + density + rendering + loss.backward(), "
+                    "fresh dense gradient", "rays": int(n_r), "samples": n_samples, "ms": round(step_ms, 3),
+            "rays_per_s": round(n_r / (step_ms * 1e-3) / 1e6, 3), "unit": "M rays/s",
+            "samples_per_s": round(n_samples / (step_ms * 1e-3) / 1e6, 2)},
     }
 
 

@@ -319,6 +319,35 @@ int ashb_tsdf_fuse_frame_static(ashb_map* map, void* embeddings, int64_t n_emb, 
                                 const int32_t* bound_hi, float trunc, int sdf_channel, int rgb_channel,
                                 int weight_channel, void* stream);
 
+/* ---------------------------------------------------------------- volume-rendering accumulation
+ * The step right after the grid query in the reference's training loop, which the reference
+ * delegates to a third-party package outside its tree (demo/train_scene_recon.py:111-150:
+ * nerfacc.render_weight_from_density, nerfacc.accumulate_along_rays).  Samples are packed as the
+ * ray sampler emits them: ray_indices int64 [m] non-decreasing, per-sample t_starts / t_ends /
+ * sigmas float32 [m].  alpha = 1 - exp(-sigma (t_end - t_start)), T = running product of
+ * (1 - alpha) over the earlier samples of the ray, weight = T alpha. */
+
+/* seg_start / seg_end int64 [n_rays]: first and one-past-last sample of every ray (0, 0 for rays
+ * without samples). */
+int ashb_render_segments(const int64_t* ray_indices, int64_t m, int64_t n_rays, int64_t* seg_start,
+                         int64_t* seg_end, void* stream);
+int ashb_render_weights_forward(const float* t_starts, const float* t_ends, const float* sigmas,
+                                const int64_t* seg_start, const int64_t* seg_end, int64_t n_rays,
+                                float* weights, void* stream);
+/* grad_sigmas [m] from grad_weights [m] (and the forward's weights). */
+int ashb_render_weights_backward(const float* t_starts, const float* t_ends, const float* sigmas,
+                                 const float* weights, const float* grad_weights,
+                                 const int64_t* seg_start, const int64_t* seg_end, int64_t n_rays,
+                                 float* grad_sigmas, void* stream);
+/* out [n_rays][C] = sum over the ray's samples of weight * values [m][C] (values NULL: C = 1, value 1). */
+int ashb_render_accumulate_forward(const float* weights, const float* values, int C,
+                                   const int64_t* seg_start, const int64_t* seg_end, int64_t n_rays,
+                                   float* out, void* stream);
+/* grad_weights [m] and/or grad_values [m][C] (either may be NULL) from grad_out [n_rays][C]. */
+int ashb_render_accumulate_backward(const float* weights, const float* values, const float* grad_out,
+                                    const int64_t* ray_indices, int64_t m, int64_t n_rays, int C,
+                                    float* grad_weights, float* grad_values, void* stream);
+
 /* ---------------------------------------------------------------- multi-GPU key routing
  * For a hash map partitioned over `world` ranks by key hash (no counterpart in the reference,
  * which is single-GPU): groups keys int32 [n][key_dim] by owner rank into keys_out (same shape),

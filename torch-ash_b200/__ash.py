@@ -67,6 +67,11 @@ _lib.ashb_conv_forward_tiled.argtypes = [_vp, _vp, _vp, _vp, _vp, _int, _i64, _i
 _lib.ashb_grid_spatial_init.argtypes = [_vp, _vp, _i64, _c.c_double, _vp, _int, _int, _int, _vp, _vp, _vp, _vp, _c.c_uint32,
                                         _vp, _vp, _vp]
 _lib.ashb_route_by_owner.argtypes = [_vp, _i64, _int, _int, _vp, _vp, _vp, _vp, _vp]
+_lib.ashb_render_segments.argtypes = [_vp, _i64, _i64, _vp, _vp, _vp]
+_lib.ashb_render_weights_forward.argtypes = [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp]
+_lib.ashb_render_weights_backward.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp]
+_lib.ashb_render_accumulate_forward.argtypes = [_vp, _vp, _int, _vp, _vp, _i64, _vp, _vp]
+_lib.ashb_render_accumulate_backward.argtypes = [_vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _vp, _vp]
 
 STATUS_CAPACITY, STATUS_PROBE, STATUS_SPIN, STATUS_DUPLICATE = 1, 2, 4, 8
 _DTYPES = {torch.float32: 0, torch.float64: 1}
@@ -656,3 +661,81 @@ def route_by_owner(keys, world):
         _check(_lib.ashb_route_by_owner(keys.data_ptr(), n, dim, int(world), out.data_ptr(), perm.data_ptr(), counts,
                                         scratch.data_ptr(), _stream(keys.device)))
     return out, perm, list(counts)
+
+
+# ---------------------------------------------------------------------------------------------
+# Volume-rendering accumulation over packed ray samples (no counterpart in the reference's native
+# module: its demo calls a third-party package for this step).
+
+def render_segments(ray_indices, n_rays):
+    """(seg_start, seg_end) int64 (n_rays,): sample range of every ray; ray_indices non-decreasing."""
+    ri = _cuda(ray_indices, "ray_indices", torch.int64).view(-1)
+    start = torch.empty(n_rays, dtype=torch.int64, device=ri.device)
+    end = torch.empty(n_rays, dtype=torch.int64, device=ri.device)
+    with torch.cuda.device(ri.device):
+        _check(_lib.ashb_render_segments(ri.data_ptr(), ri.shape[0], n_rays, start.data_ptr(), end.data_ptr(),
+                                         _stream(ri.device)))
+    return start, end
+
+
+def _f32_flat(t, name):
+    return _cuda(t, name, torch.float32).reshape(-1)
+
+
+def _samples_by_channels(values, m):
+    """values as (m, C) float32, or None."""
+    if values is None:
+        return None
+    v = _cuda(values, "values", torch.float32)
+    channels = v.shape[-1] if v.dim() > 1 else 1
+    return v.reshape(m, channels)
+
+
+def render_weights_forward(t_starts, t_ends, sigmas, seg_start, seg_end):
+    ts, te, sg = _f32_flat(t_starts, "t_starts"), _f32_flat(t_ends, "t_ends"), _f32_flat(sigmas, "sigmas")
+    if not (ts.shape == te.shape == sg.shape):
+        raise RuntimeError("t_starts, t_ends and sigmas must have one value per sample")
+    w = torch.empty_like(sg)
+    with torch.cuda.device(sg.device):
+        _check(_lib.ashb_render_weights_forward(ts.data_ptr(), te.data_ptr(), sg.data_ptr(), seg_start.data_ptr(),
+                                                seg_end.data_ptr(), seg_start.shape[0], w.data_ptr(), _stream(sg.device)))
+    return w
+
+
+def render_weights_backward(t_starts, t_ends, sigmas, weights, grad_weights, seg_start, seg_end):
+    ts, te, sg = _f32_flat(t_starts, "t_starts"), _f32_flat(t_ends, "t_ends"), _f32_flat(sigmas, "sigmas")
+    w, gw = _f32_flat(weights, "weights"), _f32_flat(grad_weights, "grad_weights")
+    gs = torch.empty_like(sg)
+    with torch.cuda.device(sg.device):
+        _check(_lib.ashb_render_weights_backward(
+            ts.data_ptr(), te.data_ptr(), sg.data_ptr(), w.data_ptr(), gw.data_ptr(), seg_start.data_ptr(),
+            seg_end.data_ptr(), seg_start.shape[0], gs.data_ptr(), _stream(sg.device)))
+    return gs
+
+
+def render_accumulate_forward(weights, values, seg_start, seg_end):
+    w = _f32_flat(weights, "weights")
+    v = _samples_by_channels(values, w.shape[0])
+    C = v.shape[1] if v is not None else 1
+    out = torch.empty((seg_start.shape[0], C), dtype=torch.float32, device=w.device)
+    with torch.cuda.device(w.device):
+        _check(_lib.ashb_render_accumulate_forward(
+            w.data_ptr(), v.data_ptr() if v is not None else None, C, seg_start.data_ptr(), seg_end.data_ptr(),
+            seg_start.shape[0], out.data_ptr(), _stream(w.device)))
+    return out
+
+
+def render_accumulate_backward(weights, values, grad_out, ray_indices, n_rays, need_weights=True, need_values=True):
+    w = _f32_flat(weights, "weights")
+    m = w.shape[0]
+    v = _samples_by_channels(values, m)
+    C = v.shape[1] if v is not None else 1
+    go = _cuda(grad_out, "grad_out", torch.float32).reshape(n_rays, C)
+    ri = _cuda(ray_indices, "ray_indices", torch.int64).view(-1)
+    gw = torch.empty(m, dtype=torch.float32, device=w.device) if need_weights else None
+    gv = torch.empty((m, C), dtype=torch.float32, device=w.device) if (need_values and v is not None) else None
+    with torch.cuda.device(w.device):
+        _check(_lib.ashb_render_accumulate_backward(
+            w.data_ptr(), v.data_ptr() if v is not None else None, go.data_ptr(), ri.data_ptr(), m, n_rays, C,
+            gw.data_ptr() if gw is not None else None, gv.data_ptr() if gv is not None else None, _stream(w.device)))
+    return gw, gv
