@@ -235,6 +235,23 @@ int ashb_conv_forward_tiled(const float* inputs, const float* weights, const int
                             const int64_t* lut_grid_nb27, float* outputs, int zero_output,
                             int64_t num_grids, int64_t n_emb, int G, int radius, int64_t D, void* stream);
 
+/* ---------------------------------------------------------------- iso-surface vertices */
+
+/* Replaces isosurface_extraction_kernel + isosurface_extraction (ash/src/grid.cu:453-604),
+ * float32.  sdfs / weights [n_emb][cells_per_grid]; grid_indices int64 [num_grids];
+ * grid_coords_table int32 [n_emb][3]; cell_coords_table int32 [cells_per_grid][3]; the three
+ * radius-1 one-sided tables as for the query.  One call with positions == NULL counts (the
+ * reference's first launch); a second call with positions float32 [max_out][3] fills (its second
+ * launch).  *n_out (HOST) = number of crossings found; cursor_dev: 8 bytes of device scratch.
+ * Positions are in cell units, order unspecified.  Synchronises `stream`. */
+int ashb_isosurface_extraction(const float* sdfs, const float* weights, const int64_t* grid_indices,
+                               const int32_t* grid_coords_table, const int64_t* lut_grid_nb2grid_idx,
+                               const int32_t* cell_coords_table, const int64_t* lut_cell_nb2cell_idx,
+                               const int64_t* lut_cell_nb2grid_nb, float* positions, int64_t max_out,
+                               int64_t* n_out, void* cursor_dev, float iso_value, float weight_thr,
+                               int grid_dim, int64_t cells_per_grid, int64_t n_emb, int64_t num_grids,
+                               void* stream);
+
 /* ---------------------------------------------------------------- ray sampler
  * All lengths in cell units; rays float32 [n][3]; bbox float32 [3] each; the map
  * must have key_dim 3 (ash/src/sampler.cu:89-99).  Positions are fma(t, d, o) in

@@ -491,6 +491,54 @@ void oracle_ray_sample_pass(const oracle_map* m, const float* ray_o,
     }
 }
 
+/* ------------------------------------------------------------------------- */
+/* Iso-surface vertices                                                      */
+/* ------------------------------------------------------------------------- */
+
+/* ash/src/grid.cu:453-532 isosurface_extraction_kernel: for every cell of the listed
+ * blocks with weight >= weight_thr, look at its +x, +y, +z neighbour in turn; a sign
+ * change of (sdf - iso_value) towards a neighbour with enough weight emits the linearly
+ * interpolated crossing, in cell units.  A missing neighbour BLOCK ends the cell's loop
+ * (`return`, :508-510), later axes included.  positions == NULL counts only (:556-572).
+ * Sequential, so the output order is the scan order (the reference's is the order of its
+ * atomic counter, i.e. unspecified).  Returns the number of vertices. */
+int64_t oracle_isosurface_extraction_f32(
+        const float* sdfs, const float* weights, const int64_t* grid_indices,
+        const int32_t* grid_coords_table, const int64_t* g2g, const int32_t* cell_coords_table,
+        const int64_t* c2c, const int64_t* c2g, float* positions, float iso_value,
+        float weight_thr, int grid_dim, int64_t cells_per_grid, int64_t num_grids) {
+    int64_t count = 0;
+    for (int64_t i = 0; i < num_grids * cells_per_grid; ++i) {
+        const int64_t grid_idx = grid_indices[i / cells_per_grid];
+        const int64_t cell_idx = i % cells_per_grid;
+        const float self_sdf = sdfs[grid_idx * cells_per_grid + cell_idx];
+        const float self_weight = weights[grid_idx * cells_per_grid + cell_idx];
+        const float self_isodiff = self_sdf - iso_value;
+        if (self_weight < weight_thr) continue;
+        for (int d = 0; d < 3; ++d) {
+            const int cell_nb = 1 << d;
+            const int64_t grid_nb_idx = g2g[grid_idx * 8 + c2g[cell_idx * 8 + cell_nb]];
+            if (grid_nb_idx == -1) break;
+            const int64_t cell_nb_idx = c2c[cell_idx * 8 + cell_nb];
+            const float nb_sdf = sdfs[grid_nb_idx * cells_per_grid + cell_nb_idx];
+            const float nb_weight = weights[grid_nb_idx * cells_per_grid + cell_nb_idx];
+            const float nb_isodiff = nb_sdf - iso_value;
+            if (self_isodiff * nb_isodiff < 0 && nb_weight >= weight_thr) {
+                if (positions) {
+                    const float ratio = self_isodiff / (self_isodiff - nb_isodiff);
+                    for (int k = 0; k < 3; ++k) {
+                        const int self_pos = grid_coords_table[grid_idx * 3 + k] * grid_dim +
+                                             cell_coords_table[cell_idx * 3 + k];
+                        positions[count * 3 + k] = (float)self_pos + ratio * (k == d ? 1.0f : 0.0f);
+                    }
+                }
+                ++count;
+            }
+        }
+    }
+    return count;
+}
+
 int oracle_num_threads(void) {
     int n = 1;
 #ifdef _OPENMP

@@ -119,3 +119,10 @@ def ray_sample(hashmap, o, d, nears, fars, bbox_min, bbox_max, max_samples_per_r
         hashmap._m, _np(o), _np(d), _np(nears), _np(fars), _np(bbox_min), _np(bbox_max), max_samples_per_ray, grid2cell
     )
     return tuple(torch.from_numpy(x) for x in r)
+
+
+def isosurface_extraction(sdfs, weights, grid_indices, grid_coords_table, g2g, cell_coords_table, c2c, c2g, grid_dim,
+                          iso_value, weight_thr):
+    return torch.from_numpy(
+        _o.isosurface_extraction(_np(sdfs), _np(weights), _np(grid_indices), _np(grid_coords_table), _np(g2g),
+                                 _np(cell_coords_table), _np(c2c), _np(c2g), grid_dim, iso_value, weight_thr))

@@ -142,3 +142,40 @@ def test_tsdf_fusion_vs_oracle(H, W):
     want = ref.emb[ridx[rorder]]
     assert (want[..., 4] > 0).mean() > 0.02
     np.testing.assert_allclose(got, want, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("G", [8, 4, 2])
+def test_isosurface_vertices_vs_oracle_and_sphere(G):
+    """Vertex-only iso-surface (ash/src/grid.cu:453-604) against the CPU restatement as a SET of
+    positions (the order is the order of an atomic counter), and a known answer: crossings of a
+    sphere's signed distance lie on the sphere."""
+    import ash
+
+    cell = 0.05
+    grid = ash.UnBoundedSparseDenseGrid(3, 6000, 2, G, cell_size=cell, device=DEV)
+    gen = torch.Generator(device=DEV).manual_seed(G)
+    dirs = torch.nn.functional.normalize(torch.randn(20000, 3, generator=gen, device=DEV), dim=-1)
+    grid.spatial_init_(dirs * 0.8, dilation=1, bidirectional=True)
+    gc, cc, gi, ci = grid.items()
+    pos = grid.cell_to_world(gc, cc).view(gi.shape[0], -1, 3)
+    sdf = torch.zeros(6000, G**3, device=DEV)
+    w = torch.zeros(6000, G**3, device=DEV)
+    sdf[gi.view(-1)] = pos.norm(dim=-1) - 0.8
+    w[gi.view(-1)] = (torch.rand(pos.shape[:2], generator=gen, device=DEV) > 0.1).float() * 2  # some cells unobserved
+    out = grid.marching_cubes(sdf, w, vertices_only=True, weight_thr=1.0)
+    verts = out["positions"]
+    assert verts.shape[0] > 500 and verts.shape[1] == 3
+    # a linear interpolation of the distance along an edge of length `cell` is within cell^2 / r of the sphere
+    assert ((verts.norm(dim=-1) - 0.8).abs() < cell * cell).all()
+    t = lambda a: a.detach().cpu().numpy()
+    _, idx = grid.engine.items()
+    ref = oracle.isosurface_extraction(
+        t(sdf), t(w), t(idx), t(grid.grid_coords), t(grid.lut_grid_nb2grid_idx), t(grid.cell_coords),
+        t(grid.lut_cell_nb2cell_idx), t(grid.lut_cell_nb2grid_nb), G, 0.0, 1.0)
+    got = t(verts / cell) if False else t(grid.transform_world_to_cell(verts))
+    assert len(ref) == len(got)
+    order_r, order_g = np.lexsort(np.round(ref, 3).T[::-1]), np.lexsort(np.round(got, 3).T[::-1])
+    np.testing.assert_allclose(got[order_g], ref[order_r], rtol=0, atol=2e-3)
+    assert grid.marching_cubes(sdf + 10.0, w, vertices_only=True) is None
+    with pytest.raises(NotImplementedError):
+        grid.marching_cubes(sdf, w)

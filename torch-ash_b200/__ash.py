@@ -72,6 +72,7 @@ _lib.ashb_render_weights_forward.argtypes = [_vp, _vp, _vp, _vp, _vp, _i64, _vp,
 _lib.ashb_render_weights_backward.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp]
 _lib.ashb_render_accumulate_forward.argtypes = [_vp, _vp, _int, _vp, _vp, _i64, _vp, _vp]
 _lib.ashb_render_accumulate_backward.argtypes = [_vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _vp, _vp]
+_lib.ashb_isosurface_extraction.argtypes = [_vp] * 9 + [_i64, _c.POINTER(_i64), _vp, _f32, _f32, _int, _i64, _i64, _i64, _vp]
 
 STATUS_CAPACITY, STATUS_PROBE, STATUS_SPIN, STATUS_DUPLICATE = 1, 2, 4, 8
 _DTYPES = {torch.float32: 0, torch.float64: 1}
@@ -739,3 +740,38 @@ def render_accumulate_backward(weights, values, grad_out, ray_indices, n_rays, n
             w.data_ptr(), v.data_ptr() if v is not None else None, go.data_ptr(), ri.data_ptr(), m, n_rays, C,
             gw.data_ptr() if gw is not None else None, gv.data_ptr() if gv is not None else None, _stream(w.device)))
     return gw, gv
+
+
+def isosurface_extraction(sdfs, weights, grid_indices, grid_coords_table, lut_grid_nb2grid_idx, cell_coords_table,
+                          lut_cell_nb2cell_idx, lut_cell_nb2grid_nb, grid_dim, iso_value, weight_thr):
+    """ash/src/grid.cu:534-604: (n, 3) float32 zero crossings along +x/+y/+z cell edges, in cell units."""
+    sd = _cuda(sdfs, "sdfs", torch.float32)
+    n_emb = lut_grid_nb2grid_idx.shape[0]
+    sd = sd.reshape(n_emb, -1)
+    wt = _cuda(weights, "weights", torch.float32).reshape(sd.shape)
+    dev = sd.device
+    gi = _cuda(grid_indices, "grid_indices", torch.int64).view(-1)
+    gct = _cuda(grid_coords_table, "grid_coords_table", torch.int32)
+    cct = _cuda(cell_coords_table, "cell_coords_table", torch.int32)
+    g2g = _cuda(lut_grid_nb2grid_idx, "lut_grid_nb2grid_idx", torch.int64)
+    c2c = _cuda(lut_cell_nb2cell_idx, "lut_cell_nb2cell_idx", torch.int64)
+    c2g = _cuda(lut_cell_nb2grid_nb, "lut_cell_nb2grid_nb", torch.int64)
+    cells = sd.shape[1]
+    if gct.shape != (n_emb, 3) or cct.shape != (cells, 3) or c2c.shape != (cells, 8) or c2g.shape != (cells, 8):
+        raise RuntimeError("isosurface_extraction: table shapes do not match sdfs")
+    cursor = torch.empty(1, dtype=torch.int64, device=dev)
+    n = _i64()
+
+    def run(out, max_out):
+        with torch.cuda.device(dev):
+            _check(_lib.ashb_isosurface_extraction(
+                sd.data_ptr(), wt.data_ptr(), gi.data_ptr(), gct.data_ptr(), g2g.data_ptr(), cct.data_ptr(),
+                c2c.data_ptr(), c2g.data_ptr(), out.data_ptr() if out is not None else None, max_out, _c.byref(n),
+                cursor.data_ptr(), float(iso_value), float(weight_thr), int(grid_dim), cells, n_emb, gi.shape[0],
+                _stream(dev)))
+
+    run(None, 0)
+    positions = torch.empty((n.value, 3), dtype=torch.float32, device=dev)
+    if n.value:
+        run(positions, n.value)
+    return positions

@@ -353,9 +353,34 @@ class SparseDenseGrid(ASHModule):
     # ------------------------------------------------------------------ surface extraction
     def marching_cubes(self, tsdfs, weights, color_fn=None, normal_fn=None, iso_value: float = 0.0,
                        weight_thr: float = 1.0, vertices_only=False):
-        raise NotImplementedError(
-            "mesh extraction (ash/grid.py:628-711, ash/src/grid.cu:453-946) is outside the hot path "
-            "this library implements")
+        """Iso-surface of ``tsdfs`` (num_embeddings, G^3[, 1]) where ``weights`` >= ``weight_thr``.
+
+        ``vertices_only=True``: the zero crossings along the +x/+y/+z cell edges
+        (ash/src/grid.cu:453-604), returned as a dict of world ``positions`` (n, 3) and, if the
+        callbacks are given, ``colors`` / ``normals`` -- the reference wraps the same arrays in an
+        Open3D point cloud (ash/grid.py:657-682), a package this library does not depend on.
+        Returns None when the surface is empty.  Triangle extraction (ash/src/grid.cu:607-946) is
+        outside the hot path this library implements.
+        """
+        if not vertices_only:
+            raise NotImplementedError(
+                "triangle extraction (ash/src/grid.cu:607-946) is outside the hot path this library "
+                "implements; use vertices_only=True for the iso-surface points")
+        if self.grid_coords is None or self.lut_grid_nb2grid_idx is None:
+            self.construct_grid_neighbor_lut_(radius=1, bidirectional=False)
+        _, grid_indices = self.engine.items()
+        vertices = backend.isosurface_extraction(
+            tsdfs, weights, grid_indices, self.grid_coords, self.lut_grid_nb2grid_idx, self.cell_coords,
+            self.lut_cell_nb2cell_idx, self.lut_cell_nb2grid_nb, self.grid_dim, iso_value, weight_thr)
+        if len(vertices) == 0:
+            return None
+        positions = self.transform_cell_to_world(vertices)
+        cloud = {"positions": positions}
+        if color_fn is not None:
+            cloud["colors"] = color_fn(positions)
+        if normal_fn is not None:
+            cloud["normals"] = normal_fn(positions)
+        return cloud
 
 
 class UnBoundedSparseDenseGrid(SparseDenseGrid):
