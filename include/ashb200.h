@@ -108,6 +108,13 @@ int ashb_map_items(ashb_map* map, int32_t* keys_out_dev, int64_t* indices_out_de
 int ashb_map_load_states(ashb_map* map, const int32_t* keys_dev, const int64_t* indices_dev,
                          int64_t n, const int32_t* heap_src_dev, void* stream);
 
+/* Rebuilds the table from its live entries, dropping the tombstones that erase leaves behind
+ * (open addressing keeps erased slots occupied so that probe chains stay intact; after heavy
+ * insert / erase traffic they lengthen every probe).  Indices, heap and size are unchanged.  The
+ * reference has no counterpart: its chained third-party map frees nodes on erase.  Allocates a
+ * second table for the duration of the call and synchronises `stream`. */
+int ashb_map_rehash(ashb_map* map, void* stream);
+
 /* ---------------------------------------------------------------- grid query
  * Layouts (ash/grid_query.py:40-55): embeddings [n_emb][cells_per_grid][D]
  * (D <= 16), offsets float32 [n][3] (always float32, ash/src/grid.cu:71),

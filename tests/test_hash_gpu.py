@@ -273,3 +273,35 @@ def test_empty_batches_and_errors():
         __ash.HashMap(5, 10, torch.arange(10, dtype=torch.int32, device=DEV), DEV)
     with pytest.raises(RuntimeError):
         __ash.HashMap(3, 10, torch.arange(10, dtype=torch.int32), torch.device("cpu"))
+
+
+@pytest.mark.parametrize("dim", [3, 4])
+def test_rehash_keeps_associations_and_drops_tombstones(dim):
+    """Long insert / erase histories: the engine rebuilds its table from the live entries once the
+    erased slots pass half the capacity; key -> index associations, size and the heap survive."""
+    import __ash
+    from ash import ASHEngine
+
+    cap = 20000
+    eng = ASHEngine(dim, cap, DEV)
+    rehashes = []
+    real = eng.backend.rehash
+    eng.backend.rehash = lambda: (rehashes.append(1), real())[1]
+    keep = _diag_keys(dim, 5000)
+    eng.insert_keys(keep)
+    idx0, _ = eng.find(keep)
+    for rnd in range(12):
+        churn = _rand_keys(9000, dim, 10_000 * (rnd + 1), 10_000 * (rnd + 2), seed=rnd).to(DEV)
+        eng.insert_keys(churn)
+        eng.erase(churn)
+        assert eng.size() == 5000
+    assert len(rehashes) >= 4
+    idx1, ok = eng.find(keep)
+    assert ok.all() and torch.equal(idx1, idx0)
+    # explicit call on the native map: nothing observable changes
+    eng.backend.rehash()
+    k, i = eng.items()
+    assert k.shape[0] == 5000 and eng.backend.status() == 0
+    assert torch.equal(torch.sort(i)[0], torch.sort(idx0)[0])
+    eng.insert_keys(_diag_keys(dim, cap))  # fill to capacity: every index is handed out exactly once
+    assert eng.size() == cap and torch.unique(eng.find(_diag_keys(dim, cap))[0]).numel() == cap

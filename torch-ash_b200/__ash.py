@@ -43,6 +43,7 @@ _lib.ashb_map_insert_values.argtypes = [_vp, _vp, _i64, _int, _vp, _vp, _vp, _vp
 _lib.ashb_map_erase.argtypes = [_vp, _vp, _i64, _vp]
 _lib.ashb_map_items.argtypes = [_vp, _vp, _vp, _i64, _c.POINTER(_i64), _vp]
 _lib.ashb_map_load_states.argtypes = [_vp, _vp, _vp, _i64, _vp, _vp]
+_lib.ashb_map_rehash.argtypes = [_vp, _vp]
 _lib.ashb_query_forward.argtypes = [_int, _int] + [_vp] * 9 + [_i64] * 4 + [_vp]
 _lib.ashb_query_backward_forward.argtypes = [_int, _int] + [_vp] * 11 + [_int] + [_i64] * 4 + [_vp]
 _lib.ashb_query_backward_backward.argtypes = [_int, _int] + [_vp] * 12 + [_int] + [_i64] * 4 + [_vp]
@@ -245,6 +246,10 @@ class HashMap:
         st = _c.c_uint32()
         _check(_lib.ashb_map_status(self._h, _stream(self._device), _c.byref(st)))
         return int(st.value)
+
+    def rehash(self) -> None:
+        """Rebuild the table from its live entries, dropping erased slots (indices unchanged)."""
+        _check(_lib.ashb_map_rehash(self._h, _stream(self._device)))
 
     @property
     def handle(self) -> int:

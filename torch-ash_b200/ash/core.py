@@ -40,6 +40,10 @@ class ASHEngine(nn.Module):
         # cannot overflow skip the device round trip the reference pays twice
         # per call (ash/core.py:203-205).
         self._size_bound = 0
+        # Upper bound on the erased slots (tombstones) the open-addressing table carries.  When it
+        # passes half the capacity the table is rebuilt from its live entries, so that long
+        # insert / erase histories (fusion with pruning) do not lengthen every probe.
+        self._erased_bound = 0
         self.register_load_state_dict_post_hook(ASHEngine._post_load_state_dict_hook)
 
     # ------------------------------------------------------------------ state
@@ -147,10 +151,15 @@ class ASHEngine(nn.Module):
             warnings.warn("empty keys")
             return
         self.backend.erase(keys)
+        self._erased_bound += keys.shape[0]
+        if self._erased_bound > self.capacity // 2 and hasattr(self.backend, "rehash"):
+            self.backend.rehash()
+            self._erased_bound = 0
 
     def clear(self) -> None:
         self.backend.clear()
         self._size_bound = 0
+        self._erased_bound = 0
 
     def size(self) -> int:
         self._size_bound = self.backend.size()

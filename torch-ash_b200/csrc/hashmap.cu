@@ -166,6 +166,22 @@ __global__ void __launch_bounds__(256) load_states_kernel(Table t, const int32_t
     if (present) atomicOr(t.status, ASHB_STATUS_DUPLICATE);
 }
 
+// ---- rehash ------------------------------------------------------------------------
+// Copies every live (key, index) pair of `src` into the empty table `dst`; erased slots
+// (tombstones) are left behind, so probe sequences are short again.
+template <class Table, int DIM>
+__global__ void __launch_bounds__(256) rehash_kernel(Table dst, Table src) {
+    const uint64_t n_slots = (uint64_t)src.mask + 1;
+    for (uint64_t s = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; s < n_slots;
+         s += (uint64_t)gridDim.x * blockDim.x) {
+        const Entry e = src.read_const((uint32_t)s);
+        if (e.val < 0) continue;
+        bool present = false;
+        emplace(dst, e.k0, e.k1, e.k2, e.k3, e.val, &present);
+        if (present) atomicOr(dst.status, ASHB_STATUS_DUPLICATE);
+    }
+}
+
 __global__ void set_counter_kernel(int32_t* counter, int32_t v) { *counter = v; }
 
 __global__ void reset_heap_kernel(int32_t* __restrict__ heap, int64_t capacity) {
@@ -473,6 +489,36 @@ int ashb_map_load_states(ashb_map* m, const int32_t* keys, const int64_t* indice
     ASHB_REQUIRE(keys && indices, "null buffer");
     ASHB_DIM_LAUNCH(load_states_kernel, m, blocks_for(n, 256), 256, st, keys, indices, n);
     ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+int ashb_map_rehash(ashb_map* m, void* stream) {
+    ASHB_MAP_PROLOGUE(m);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    void* fresh = nullptr;
+    ASHB_CUDA_TRY(cudaMalloc(&fresh, m->n_slots * m->slot_bytes));
+    cudaError_t e = cudaMemsetAsync(fresh, 0xFF, m->n_slots * m->slot_bytes, st);
+    if (e == cudaSuccess) {
+        const unsigned grid = wave_grid((int64_t)m->n_slots, 256, 8);
+        const uint32_t mask = (uint32_t)(m->n_slots - 1);
+        if (m->key_dim == 4) {
+            rehash_kernel<Table32, 4><<<grid, 256, 0, st>>>(Table32{static_cast<Slot32*>(fresh), mask, m->status},
+                                                            Table32{static_cast<Slot32*>(m->slots), mask, m->status});
+        } else {
+            rehash_kernel<Table16, 3><<<grid, 256, 0, st>>>(Table16{static_cast<uint4*>(fresh), mask, m->status},
+                                                            Table16{static_cast<uint4*>(m->slots), mask, m->status});
+        }
+        e = cudaGetLastError();
+    }
+    // the old table must outlive the copy; rehashing is rare, so simply wait for it
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) {
+        set_error("rehash failed: %s", cudaGetErrorString(e));
+        cudaFree(fresh);
+        return ASHB_ERR_CUDA;
+    }
+    cudaFree(m->slots);
+    m->slots = fresh;
     return ASHB_OK;
 }
 
