@@ -189,7 +189,9 @@ int ashb_grid_query_forward(ashb_map* map, int dtype, int interp, const void* em
 
 /* grad_x [n][3] (type of embeddings) = d/d offsets * (1 / cell_size), fully written; pass NULL
  * when the positions need no gradient and the eight embedding rows per query are not read at
- * all.  grad_embeddings accumulated (zero_grad as above).  block_idx NULL = probe the map again. */
+ * all.  grad_embeddings accumulated (zero_grad as above); pass NULL when only grad_x is wanted (the
+ * first-order pass of a gradient-of-gradient loss) and nothing is scattered.  block_idx NULL =
+ * probe the map again. */
 int ashb_grid_query_backward(ashb_map* map, int dtype, int interp, const void* z, const void* embeddings,
                              const float* x, double cell_size, const float* origin, int G,
                              const int32_t* nb_lut, const int32_t* block_idx, void* grad_embeddings,

@@ -167,3 +167,37 @@ def test_native_key_routing_matches_owner_function(dim, world):
     assert (go[1:] >= go[:-1]).all()  # grouped by ascending owner
     e, p, c = __ash.route_by_owner(keys[:0], world)
     assert e.shape == (0, dim) and p.numel() == 0 and sum(c) == 0
+
+
+@pytest.mark.parametrize("kind,G,D", [("unbounded", 8, 16), ("plain", 4, 3)])
+def test_in_place_gradient_mode_equals_dense_mode(kind, G, D):
+    """grad_mode="in_place": both backward passes add straight into embeddings.grad.  A training step
+    with a rendering-style term AND an eikonal (gradient-of-gradient) term must leave the same
+    gradient as the reference's dense contract, also when accumulated over two steps; and a pass that
+    only asks for d/dx must not touch the embedding gradient."""
+    grid, x = _make(kind, G, D, seed=11)
+
+    def step(xx):
+        xr = xx.clone().requires_grad_(True)
+        y, _ = grid(xr, "linear")
+        (gx,) = torch.autograd.grad(y[:, :1], xr, torch.ones_like(y[:, :1]), create_graph=True)
+        loss = (y * y).sum() + ((gx.norm(dim=-1) - 1) ** 2).sum()
+        loss.backward()
+        return xr.grad
+
+    results = {}
+    for mode in ("dense", "in_place"):
+        grid.grad_mode = mode
+        grid.embeddings.grad = None
+        gx1 = step(x[:3000])
+        gx2 = step(x[2000:])
+        results[mode] = (grid.embeddings.grad.clone(), gx1, gx2)
+    for a, b in zip(results["dense"], results["in_place"]):
+        torch.testing.assert_close(a, b, rtol=2e-4, atol=1e-5 * max(1.0, float(a.abs().max())))
+    # first-order pass alone: nothing lands in the embedding gradient
+    grid.embeddings.grad.zero_()
+    xr = x.clone().requires_grad_(True)
+    y, _ = grid(xr, "linear")
+    (gx,) = torch.autograd.grad(y.sum(), xr)
+    assert torch.count_nonzero(grid.embeddings.grad) == 0 and torch.count_nonzero(gx) > 0
+    grid.grad_mode = "dense"

@@ -569,25 +569,29 @@ def grid_query_forward(hashmap, embeddings, x, cell_size, origin, grid_dim, nb_l
 
 
 def grid_query_backward(hashmap, z, embeddings, x, cell_size, origin, grid_dim, nb_lut, block_idx, interpolation,
-                        grad_embeddings_out=None, need_grad_x=True):
-    """Returns (grad_embeddings, grad_x (N, 3) in the embeddings' dtype, or None if not needed)."""
+                        grad_embeddings_out=None, need_grad_x=True, need_grad_embeddings=True):
+    """Returns (grad_embeddings, grad_x (N, 3) in the embeddings' dtype); either is None when not needed."""
     emb, x, nb_lut = _fused_args(hashmap, embeddings, x, nb_lut)
     n, dev = x.shape[0], emb.device
     z = _cuda(z, "z", emb.dtype)
     if z.shape != (n, emb.shape[2]):
         raise RuntimeError("z must be (num_queries, embedding_dim)")
-    if grad_embeddings_out is None:
+    if not need_grad_embeddings:
+        grad_emb, zero = None, 0
+    elif grad_embeddings_out is None:
         grad_emb, zero = torch.empty_like(emb), 1
     else:
         grad_emb, zero = grad_embeddings_out, 0
         if grad_emb.shape != emb.shape or grad_emb.dtype != emb.dtype or not grad_emb.is_contiguous():
             raise RuntimeError("grad_embeddings_out must match embeddings")
+    if grad_emb is None and not need_grad_x:
+        return None, None
     grad_x = torch.empty((n, 3), dtype=emb.dtype, device=dev) if need_grad_x else None
     bidx = _cuda(block_idx, "block_idx", torch.int32) if block_idx is not None else None
     _check(_lib.ashb_grid_query_backward(
         hashmap._h, _dtype_code(emb), _interp_code(interpolation), z.data_ptr(), emb.data_ptr(), x.data_ptr(),
         float(cell_size), _host_floats(origin, 3), int(grid_dim), nb_lut.data_ptr(),
-        bidx.data_ptr() if bidx is not None else None, grad_emb.data_ptr(),
+        bidx.data_ptr() if bidx is not None else None, grad_emb.data_ptr() if grad_emb is not None else None,
         grad_x.data_ptr() if need_grad_x else None, zero, n, emb.shape[0], emb.shape[2], _stream(dev)))
     return grad_emb, grad_x
 

@@ -58,6 +58,12 @@ class SparseDenseGrid(ASHModule):
         # reference's split + find + pre-split kernel sequence.
         self.fused = True
         self.tiled_convolution = True
+        # "dense" (the reference's contract): every backward call returns a fresh, zero-filled,
+        # table-sized gradient that autograd accumulates into embeddings.grad.  "in_place": the
+        # fused backward passes add straight into embeddings.grad (created as zeros when missing),
+        # which saves a table-sized allocation + zero-fill (+ add) per call; clear the gradient with
+        # embeddings.grad.zero_() or zero_grad(set_to_none=False) between steps as usual.
+        self.grad_mode = "dense"
         self._lut32 = None
         self._lut32_source = None
         self._own_transform = self.transform_world_to_cell
@@ -161,7 +167,15 @@ class SparseDenseGrid(ASHModule):
                 and hasattr(backend, "grid_query_forward")
                 and self.transform_world_to_cell is self._own_transform):
             origin, cell_size = self._cell_frame()
-            geom = (self.engine.backend, self._neighbor_lut32(), cell_size, origin, self.grid_dim, interpolation)
+            grad_buffer = None
+            if self.grad_mode == "in_place" and self.embeddings.requires_grad and torch.is_grad_enabled():
+                if self.embeddings.grad is None:
+                    self.embeddings.grad = torch.zeros_like(self.embeddings)
+                grad_buffer = self.embeddings.grad
+            elif self.grad_mode not in ("dense", "in_place"):
+                raise ValueError(f"Unknown grad_mode: {self.grad_mode}")
+            geom = (self.engine.backend, self._neighbor_lut32(), cell_size, origin, self.grid_dim, interpolation,
+                    grad_buffer)
             return FusedGridQuery.apply(self.embeddings, x, geom)
 
         x = self.transform_world_to_cell(x)

@@ -17,6 +17,22 @@ from .common import _get_c_extension
 
 backend = _get_c_extension()
 
+def _engine_wants_gradient_of(leaf: torch.Tensor) -> bool:
+    """Inside a backward pass: will the running autograd task deliver a gradient to ``leaf``?
+    ``torch.autograd.grad(y, x)`` asks only for x, and then the table-sized embedding gradient need
+    not be produced at all.  Answers True whenever it cannot tell."""
+    try:
+        if not leaf.requires_grad:
+            return False
+        if leaf.grad_fn is not None:
+            return True
+        with torch.enable_grad():  # backward runs with grad mode off, which would hide the node
+            accumulate_node = leaf.view_as(leaf).grad_fn.next_functions[0][0]
+        return bool(torch._C._will_engine_execute_node(accumulate_node))
+    except Exception:  # not in a backward pass, or the query is not available in this torch
+        return True
+
+
 _N_FWD_INPUTS = 10   # embeddings, offsets, 3 index tensors, 3 lookup tables, grid_dim, interpolation
 _N_BWD_INPUTS = 11   # z + the above
 
@@ -80,12 +96,15 @@ class FusedGridQuery(torch.autograd.Function):
     Same values and the same gradient structure as ``SparseDenseGrid.query`` followed by
     ``SparseDenseGridQuery``: differentiable w.r.t. ``embeddings`` and ``x`` (through the
     offsets, d offset / d x = 1 / cell_size), twice differentiable w.r.t. ``embeddings`` and the
-    incoming gradient.  ``geom`` = (hashmap, nb_lut int32, cell_size, origin, grid_dim, interpolation).
+    incoming gradient.  ``geom`` = (hashmap, nb_lut int32, cell_size, origin, grid_dim, interpolation,
+    grad_buffer).  With a ``grad_buffer`` (a tensor shaped like ``embeddings``) both backward passes ADD
+    their embedding gradient into it and report no gradient for ``embeddings`` to autograd: the
+    table-sized allocation and zero-fill per backward call disappear.
     """
 
     @staticmethod
     def forward(ctx, embeddings, x, geom):
-        hashmap, nb_lut, cell_size, origin, grid_dim, interpolation = geom
+        hashmap, nb_lut, cell_size, origin, grid_dim, interpolation, _ = geom
         y, masks, block_idx = backend.grid_query_forward(
             hashmap, embeddings, x, cell_size, origin, grid_dim, nb_lut, interpolation)
         ctx.save_for_backward(embeddings, x, block_idx)
@@ -98,22 +117,31 @@ class FusedGridQuery(torch.autograd.Function):
         embeddings, x, block_idx = ctx.saved_tensors
         # positions that need no gradient spare the backward its eight embedding-row reads
         need_grad_x = bool(ctx.needs_input_grad[1])
+        # ... and a pass that only asks for d/dx (the first-order pass of an eikonal term) spares the
+        # scatter into the table-sized embedding gradient
+        need_grad_emb = bool(ctx.needs_input_grad[0]) and _engine_wants_gradient_of(embeddings)
+        if not need_grad_x and not need_grad_emb:
+            return None, None, None
         grad_embeddings, grad_x = FusedGridQueryBackward.apply(
-            z.contiguous(), embeddings, x, block_idx, ctx.geom, need_grad_x)
+            z.contiguous(), embeddings, x, block_idx, ctx.geom, need_grad_x, need_grad_emb)
         return grad_embeddings, grad_x, None
 
 
 class FusedGridQueryBackward(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, z, embeddings, x, block_idx, geom, need_grad_x=True):
-        hashmap, nb_lut, cell_size, origin, grid_dim, interpolation = geom
+    def forward(ctx, z, embeddings, x, block_idx, geom, need_grad_x=True, need_grad_emb=True):
+        hashmap, nb_lut, cell_size, origin, grid_dim, interpolation, grad_buffer = geom
         ctx.save_for_backward(z, embeddings, x, block_idx)
         ctx.geom = geom
         ctx.set_materialize_grads(False)
         grad_embeddings, grad_x = backend.grid_query_backward(
             hashmap, z, embeddings, x, cell_size, origin, grid_dim, nb_lut, block_idx, interpolation,
-            need_grad_x=need_grad_x)
+            grad_embeddings_out=grad_buffer, need_grad_x=need_grad_x, need_grad_embeddings=need_grad_emb)
+        if grad_buffer is not None:
+            grad_embeddings = None  # already added into the buffer
         if grad_x is None:
+            if grad_embeddings is None:
+                return None, None
             ctx.mark_non_differentiable(grad_embeddings)
             return grad_embeddings, None
         return grad_embeddings, grad_x.to(x.dtype)
@@ -121,10 +149,12 @@ class FusedGridQueryBackward(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_grad_embeddings, grad_grad_x):
         if grad_grad_x is None:
-            return (None,) * 6
+            return (None,) * 7
         z, embeddings, x, block_idx = ctx.saved_tensors
-        hashmap, nb_lut, cell_size, origin, grid_dim, interpolation = ctx.geom
+        hashmap, nb_lut, cell_size, origin, grid_dim, interpolation, grad_buffer = ctx.geom
         grad_z, grad_embeddings = backend.grid_query_backward_backward(
             hashmap, grad_grad_x.to(embeddings.dtype).contiguous(), z, embeddings, x, cell_size, origin, grid_dim,
-            nb_lut, block_idx, interpolation)
-        return grad_z, grad_embeddings, None, None, None, None
+            nb_lut, block_idx, interpolation, grad_embeddings_out=grad_buffer)
+        if grad_buffer is not None:
+            grad_embeddings = None
+        return grad_z, grad_embeddings, None, None, None, None, None

@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(256) query_forward_kernel(const T* __restrict_
 #ifndef ASHB_BWD_MIN_BLOCKS
 #define ASHB_BWD_MIN_BLOCKS 1
 #endif
-template <typename T, int VEC, class Src, bool NEED_GO>
+template <typename T, int VEC, class Src, bool NEED_GO, bool NEED_GE = true>
 __global__ void __launch_bounds__(256, ASHB_BWD_MIN_BLOCKS) query_backward_forward_kernel(
         const T* __restrict__ z, const T* __restrict__ emb, Src src, T* __restrict__ grad_emb,
         T* __restrict__ grad_off, T go_scale, int64_t n, int D, int lane_shift, int interp) {
@@ -292,7 +292,7 @@ __global__ void __launch_bounds__(256, ASHB_BWD_MIN_BLOCKS) query_backward_forwa
                     g.v[k] = w * zv.v[k];
                     if (NEED_GO) dot += e[c].v[k] * zv.v[k];
                 }
-                atomic_add_pack<T, VEC>(grad_emb + base[c] + ch, g);
+                if (NEED_GE) atomic_add_pack<T, VEC>(grad_emb + base[c] + ch, g);
                 if (NEED_GO) {
                     T wg[3];
                     aw.grad(c, wg);
@@ -429,7 +429,11 @@ static int backward_forward_impl(int interp, const void* z, const void* emb, con
     const int64_t threads = n << sh.lane_shift;
     const unsigned grid = (unsigned)((threads + 255) / 256);
     ASHB_VEC_SWITCH(T, sh,
-                    if (grad_off != nullptr) {
+                    if (grad_emb == nullptr) {
+                        query_backward_forward_kernel<T, VEC, Src, true, false><<<grid, 256, 0, st>>>(
+                                static_cast<const T*>(z), static_cast<const T*>(emb), src, nullptr,
+                                static_cast<T*>(grad_off), (T)go_scale, n, (int)D, sh.lane_shift, interp);
+                    } else if (grad_off != nullptr) {
                         query_backward_forward_kernel<T, VEC, Src, true><<<grid, 256, 0, st>>>(
                                 static_cast<const T*>(z), static_cast<const T*>(emb), src,
                                 static_cast<T*>(grad_emb), static_cast<T*>(grad_off), (T)go_scale, n, (int)D,
@@ -619,12 +623,12 @@ int ashb_grid_query_backward(ashb_map* m, int dtype, int interp, const void* z, 
                              const int32_t* block_idx, void* grad_embeddings, void* grad_x, int zero_grad,
                              int64_t n, int64_t n_emb, int64_t D, void* stream) {
     if (int rc = check_query_args(dtype, interp, n, n_emb, (int64_t)G * G * G, D)) return rc;
-    ASHB_REQUIRE(grad_embeddings != nullptr, "null grad_embeddings");
+    ASHB_REQUIRE(grad_embeddings != nullptr || grad_x != nullptr, "nothing to compute: both outputs are null");
     ASHB_REQUIRE(m != nullptr, "null map");
     DeviceGuard guard(m->device);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t elem = dtype == ASHB_F32 ? 4 : 8;
-    if (zero_grad)
+    if (zero_grad && grad_embeddings)
         ASHB_CUDA_TRY(cudaMemsetAsync(grad_embeddings, 0, (size_t)n_emb * G * G * G * D * elem, st));
     if (n == 0) return ASHB_OK;
     ASHB_REQUIRE(z && embeddings, "null buffer");
