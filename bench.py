@@ -488,6 +488,53 @@ def main():
         if i >= args.warmup:
             e2e_times.append(time.perf_counter() - t0)
     grid.embeddings.grad = None
+
+    # the same end-to-end step with gradients accumulated in place and cleared row-wise afterwards
+    grid.grad_mode = "in_place"
+    e2e_ip_times = []
+    for i in range(args.warmup + args.steps):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        x = x_host[i % n_batches].to(device, non_blocking=True).requires_grad_(True)
+        y, masks = grid(x, interpolation="linear")
+        loss = y.sum()
+        loss.backward()
+        loss_value = loss.item()
+        grid.zero_grad_rows_(x)  # this step's zero_grad
+        torch.cuda.synchronize()
+        if i >= args.warmup:
+            e2e_ip_times.append(time.perf_counter() - t0)
+    e2e_ip_sec = sum(e2e_ip_times) / len(e2e_ip_times)
+    assert int(torch.count_nonzero(grid.embeddings.grad[:1000])) == 0
+    grid.grad_mode = "dense"
+    grid.embeddings.grad = None
+
+    # the whole "forward + backward + double backward" step through the public API (eikonal-style
+    # gradient-of-gradient term on the first channel), in both gradient modes, inputs resident
+    full_step_ms = {}
+    for mode in ("dense", "in_place"):
+        grid.grad_mode = mode
+        grid.embeddings.grad = None
+        times = []
+        for i in range(3 + min(args.steps, 5)):
+            if mode == "in_place" and grid.embeddings.grad is not None:
+                grid.embeddings.grad.zero_()
+            else:
+                grid.embeddings.grad = None
+
+            def full_step():
+                x = xs[i % n_batches].detach().requires_grad_(True)
+                y, _ = grid(x, interpolation="linear")
+                (gx,) = torch.autograd.grad(y[:, :1], x, torch.ones_like(y[:, :1]), create_graph=True)
+                (y.sum() + ((gx.norm(dim=-1) - 1) ** 2).mean()).backward()
+
+            t = event_ms(full_step)
+            if i >= 3:
+                times.append(t)
+        full_step_ms[mode] = statistics.mean(times)
+    grid.grad_mode = "dense"
+    grid.embeddings.grad = None
+    torch.cuda.empty_cache()
     e2e_sec = sum(e2e_times) / len(e2e_times)
     if dist is not None:
         t = torch.tensor([e2e_sec], device=device, dtype=torch.float64)
@@ -534,6 +581,17 @@ def main():
             "value": round(world * N_QUERIES / ((f_ms + bp_ms) * 1e-3) / 1e6, 2), "unit": "M queries/s",
             "ms_per_step": round(f_ms + bp_ms, 4),
             "note": "same kernels, gradient accumulated into a long-lived buffer instead of a fresh zero-filled one"}
+        line["full_step_fwd_bwd_double_bwd"] = {
+            "what": "grid(x) + autograd.grad(sdf, x, create_graph=True) + (sum + eikonal).backward() through the public "
+                    "API, positions resident in HBM; in_place adds into embeddings.grad (zeroed outside the timed call)",
+            "dense_ms": round(full_step_ms["dense"], 3), "in_place_ms": round(full_step_ms["in_place"], 3),
+            "dense_M_queries_per_s": round(world * N_QUERIES / (full_step_ms["dense"] * 1e-3) / 1e6, 1),
+            "in_place_M_queries_per_s": round(world * N_QUERIES / (full_step_ms["in_place"] * 1e-3) / 1e6, 1)}
+        line["e2e_in_place_grad"] = {
+            "value": round(world * N_QUERIES / e2e_ip_sec / 1e6, 2), "unit": "M queries/s",
+            "ms_per_step": round(e2e_ip_sec * 1e3, 4),
+            "note": "as e2e, with grid.grad_mode = 'in_place' and grid.zero_grad_rows_(x) as the step's zero_grad "
+                    "(rank-local time)"}
         line["zero_row_fraction"] = round(zero_rows, 4)
         if allreduce_ms is not None:
             line["grad_allreduce_ms"] = round(allreduce_ms, 3)

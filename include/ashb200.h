@@ -219,6 +219,13 @@ int ashb_grid_spatial_init(ashb_map* map, const float* points, int64_t n, double
                            uint32_t* touched, uint32_t stamp, int32_t* touched_list,
                            int32_t* touched_count, void* stream);
 
+/* Writes zeros to the 8 corner rows of every query of the batch in grad_embeddings: clears
+ * exactly what ashb_grid_query_backward / _backward_backward added for that batch, at the cost of
+ * one pass over the batch instead of a table-sized memset.  No counterpart in the reference. */
+int ashb_grid_zero_rows(ashb_map* map, int dtype, void* grad_embeddings, const float* x, double cell_size,
+                        const float* origin, int G, const int32_t* nb_lut, const int32_t* block_idx,
+                        int64_t n, int64_t n_emb, int64_t D, void* stream);
+
 /* ---------------------------------------------------------------- neighbourhood convolution */
 
 /* Replaces convolution_forward_kernel + convolution_forward (ash/src/grid.cu:951-1043).

@@ -201,3 +201,26 @@ def test_in_place_gradient_mode_equals_dense_mode(kind, G, D):
     (gx,) = torch.autograd.grad(y.sum(), xr)
     assert torch.count_nonzero(grid.embeddings.grad) == 0 and torch.count_nonzero(gx) > 0
     grid.grad_mode = "dense"
+
+
+def test_zero_grad_rows_clears_exactly_what_a_batch_added():
+    grid, x = _make("unbounded", 8, 16, seed=21)
+    grid.grad_mode = "in_place"
+    grid.embeddings.grad = None
+    for part in (x[:2500], x[2500:]):
+        y, _ = grid(part.clone().requires_grad_(True), "smooth_step")
+        y.sum().backward()
+    assert torch.count_nonzero(grid.embeddings.grad) > 0
+    both = grid.embeddings.grad.clone()
+    grid.zero_grad_rows_(x[2500:])
+    # what is left is what the first part alone adds, on rows the second part does not share
+    grid2_grad = grid.embeddings.grad.clone()
+    grid.embeddings.grad.zero_()
+    y, _ = grid(x[2500:].clone().requires_grad_(True), "smooth_step")
+    y.sum().backward()
+    second_rows = grid.embeddings.grad.abs().sum(dim=-1) > 0
+    assert torch.count_nonzero(grid2_grad[second_rows]) == 0
+    assert torch.equal(grid2_grad[~second_rows], both[~second_rows])
+    grid.zero_grad_rows_(x[2500:])
+    assert torch.count_nonzero(grid.embeddings.grad) == 0
+    grid.grad_mode = "dense"

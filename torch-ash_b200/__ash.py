@@ -74,6 +74,7 @@ _lib.ashb_render_weights_backward.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp,
 _lib.ashb_render_accumulate_forward.argtypes = [_vp, _vp, _int, _vp, _vp, _i64, _vp, _vp]
 _lib.ashb_render_accumulate_backward.argtypes = [_vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _vp, _vp]
 _lib.ashb_isosurface_extraction.argtypes = [_vp] * 9 + [_i64, _c.POINTER(_i64), _vp, _f32, _f32, _int, _i64, _i64, _i64, _vp]
+_lib.ashb_grid_zero_rows.argtypes = [_vp, _int, _vp, _vp, _c.c_double, _vp, _int, _vp, _vp, _i64, _i64, _i64, _vp]
 
 STATUS_CAPACITY, STATUS_PROBE, STATUS_SPIN, STATUS_DUPLICATE = 1, 2, 4, 8
 _DTYPES = {torch.float32: 0, torch.float64: 1}
@@ -784,3 +785,15 @@ def isosurface_extraction(sdfs, weights, grid_indices, grid_coords_table, lut_gr
     if n.value:
         run(positions, n.value)
     return positions
+
+
+def grid_zero_rows(hashmap, grad_embeddings, x, cell_size, origin, grid_dim, nb_lut, block_idx=None):
+    """Zero, in ``grad_embeddings``, the corner rows the batch ``x`` touches (in place)."""
+    g, x, nb_lut = _fused_args(hashmap, grad_embeddings, x, nb_lut)
+    if g.data_ptr() != grad_embeddings.data_ptr():
+        raise RuntimeError("grad_embeddings must be contiguous (it is modified in place)")
+    bidx = _cuda(block_idx, "block_idx", torch.int32) if block_idx is not None else None
+    _check(_lib.ashb_grid_zero_rows(
+        hashmap._h, _dtype_code(g), g.data_ptr(), x.data_ptr(), float(cell_size), _host_floats(origin, 3),
+        int(grid_dim), nb_lut.data_ptr(), bidx.data_ptr() if bidx is not None else None, x.shape[0], g.shape[0],
+        g.shape[2], _stream(g.device)))

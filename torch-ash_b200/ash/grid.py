@@ -188,6 +188,19 @@ class SparseDenseGrid(ASHModule):
             self.lut_cell_nb2cell_idx, self.lut_cell_nb2grid_nb, self.grid_dim, interpolation)
         return features, masks
 
+    @torch.no_grad()
+    def zero_grad_rows_(self, x: torch.Tensor) -> None:
+        """Clear, in ``embeddings.grad``, exactly the rows that queries at world positions ``x``
+        touch: with ``grad_mode = "in_place"`` this replaces the table-sized zero-fill between steps
+        by one pass over the batch (call it with the positions of the step just taken)."""
+        if self.embeddings.grad is None:
+            return
+        if self.lut_grid_nb2grid_idx is None:
+            self.construct_grid_neighbor_lut_(radius=1, bidirectional=False)
+        origin, cell_size = self._cell_frame()
+        backend.grid_zero_rows(self.engine.backend, self.embeddings.grad, x.detach().to(torch.float32), cell_size,
+                               origin, self.grid_dim, self._neighbor_lut32())
+
     def _cell_frame(self):
         """(origin, cell_size) such that cell position = (world - origin) / cell_size."""
         return [0.0, 0.0, 0.0], 1.0

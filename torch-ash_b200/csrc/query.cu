@@ -313,6 +313,27 @@ __global__ void __launch_bounds__(256, ASHB_BWD_MIN_BLOCKS) query_backward_forwa
     }
 }
 
+// ---- clear the rows a batch touches ---------------------------------------------------
+// Writes zeros to the 8 corner rows of every query: the sparse counterpart of zero-filling a
+// table-sized gradient buffer between steps when gradients are accumulated in place.
+template <typename T, int VEC, class Src>
+__global__ void __launch_bounds__(256) query_zero_rows_kernel(Src src, T* __restrict__ grad_emb, int64_t n, int D,
+                                                              int lane_shift) {
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t q = tid >> lane_shift;
+    const int lane = (int)(tid & ((1 << lane_shift) - 1));
+    const int ch = lane * VEC;
+    if (q >= n || ch >= D) return;
+    int64_t base[8];
+    float off[3];
+    if (!src.resolve(q, lane, D, base, off)) return;
+    Pack<T, VEC> zero;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) zero.v[k] = 0;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) store_pack<T, VEC>(grad_emb + base[c] + ch, zero);
+}
+
 // ---- double backward ----------------------------------------------------------------
 template <typename T, int VEC, class Src>
 __global__ void __launch_bounds__(256, ASHB_BWD_MIN_BLOCKS) query_backward_backward_kernel(
@@ -665,6 +686,38 @@ int ashb_grid_query_backward_backward(ashb_map* m, int dtype, int interp, const 
                                                              grad_embeddings, scale, n, D, st)
                              : backward_backward_impl<double>(interp, grad_grad_x, z, embeddings, src, grad_z,
                                                               grad_embeddings, scale, n, D, st);
+}
+
+}  // extern "C"
+
+template <typename T>
+static int zero_rows_impl(const FusedSource& src, void* grad_emb, int64_t n, int64_t D, cudaStream_t st) {
+    const void* ptrs[] = {grad_emb};
+    const Shape sh = pick_shape(D, sizeof(T), ptrs, 1);
+    const int64_t threads = n << sh.lane_shift;
+    const unsigned grid = (unsigned)((threads + 255) / 256);
+    ASHB_VEC_SWITCH(T, sh,
+                    (query_zero_rows_kernel<T, VEC, FusedSource><<<grid, 256, 0, st>>>(src, static_cast<T*>(grad_emb), n,
+                                                                                        (int)D, sh.lane_shift)));
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+extern "C" {
+
+int ashb_grid_zero_rows(ashb_map* m, int dtype, void* grad_embeddings, const float* x, double cell_size,
+                        const float* origin, int G, const int32_t* nb_lut, const int32_t* block_idx, int64_t n,
+                        int64_t n_emb, int64_t D, void* stream) {
+    if (int rc = check_query_args(dtype, ASHB_LINEAR, n, n_emb, (int64_t)G * G * G, D)) return rc;
+    if (n == 0) return ASHB_OK;
+    ASHB_REQUIRE(grad_embeddings != nullptr && m != nullptr, "null buffer");
+    FusedSource src;
+    if (int rc = make_fused_source(m, x, cell_size, origin, G, nb_lut, block_idx, nullptr, nullptr, n_emb, &src))
+        return rc;
+    DeviceGuard guard(m->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == ASHB_F32 ? zero_rows_impl<float>(src, grad_embeddings, n, D, st)
+                             : zero_rows_impl<double>(src, grad_embeddings, n, D, st);
 }
 
 }  // extern "C"
