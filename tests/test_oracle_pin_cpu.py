@@ -9,7 +9,8 @@ import sys
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF = os.environ.get("ASH_REFERENCE_ROOT", "/root/reference")
+# default: a checkout named "reference" beside this repository
+REF = os.environ.get("ASH_REFERENCE_ROOT", os.path.join(os.path.dirname(ROOT), "reference"))
 
 
 @pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "unittests")), reason="reference tree not available")
