@@ -188,6 +188,60 @@ def cpu_hash_sample(bw):
     return n / sec / 1e6, f"{n} finds in a table of {om.size()} keys (1/{CPU_SCALE} of the workload), mean of {reps}"
 
 
+def cpu_tsdf_sample(bw, H=480, W=640):
+    """One fusion frame of the numpy restatement (same scene, pose and frame size); frames/s."""
+    import numpy as np
+
+    from oracle import tsdf as otsdf
+
+    cpu = torch.device("cpu")
+    scene = bw.Scene(cpu)
+    K = bw.intrinsics(H, W)
+    ref = otsdf.OracleTSDF(40_000, 8, 0.015, 1)
+    times = []
+    for pose in bw.camera_poses(2):
+        depth, color = scene.render(K, pose.float(), H, W)
+        E = torch.linalg.inv(pose).numpy()
+        t0 = time.perf_counter()
+        ref.fuse_frame(depth.numpy(), color.numpy(), K.numpy(), E, np.linalg.inv(E), 5.0)
+        times.append(time.perf_counter() - t0)
+    sec = min(times)
+    return 1.0 / sec, f"1 frame {W}x{H} (best of 2), numpy restatement of the demo's torch-op fusion step"
+
+
+def cpu_conv_sample(bw):
+    """7x7x7 window convolution of the CPU restatement over a 1/16-scale bounded grid; G cells/s."""
+    import numpy as np
+
+    import oracle
+
+    G, D, R = 8, 4, 3
+    blocks = bw.block_coords_blob(27_000 // CPU_SCALE, torch.device("cpu"), n_blobs=4).numpy()
+    n = len(blocks)
+    om = oracle.OracleHashMap(3, n)
+    om.insert_keys(blocks)
+    idx, _ = om.find(blocks)
+    r = np.arange(-1, 2)
+    boffs = np.stack(np.meshgrid(r, r, r, indexing="ij"), -1).reshape(-1, 3)[:, ::-1]       # x fastest
+    nb_idx, nb_ok = om.find((blocks[:, None, :] + boffs[None]).reshape(-1, 3).astype(np.int32))
+    g2g = np.full((n, 27), -1, np.int64)
+    g2g[idx] = np.where(nb_ok, nb_idx, -1).reshape(-1, 27)
+    c = np.arange(G**3)
+    cc = np.stack([c % G, (c // G) % G, c // (G * G)], 1)
+    w = np.arange(-R, R + 1)
+    coffs = np.stack(np.meshgrid(w, w, w, indexing="ij"), -1).reshape(-1, 3)[:, ::-1]
+    nb = cc[:, None, :] + coffs[None]
+    c2c = ((nb % G) * np.array([1, G, G * G])).sum(-1).astype(np.int64)
+    c2g = (((nb // G) + 1) * np.array([1, 3, 9])).sum(-1).astype(np.int64)
+    rng = np.random.default_rng(0)
+    inputs = rng.standard_normal((n, G**3, D), dtype=np.float32)
+    weights = rng.random((343, D), dtype=np.float32)
+    t0 = time.perf_counter()
+    oracle.convolution_forward(inputs, weights, np.ones(n * G**3, np.uint8), idx, np.arange(G**3), g2g, c2c, c2g)
+    sec = time.perf_counter() - t0
+    return n * G**3 / sec / 1e9, f"{n} blocks x 512 cells x {D} channels (1/{CPU_SCALE} of the workload), one pass"
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -673,6 +727,13 @@ def main():
     if rank == 0 and world == 1 and not args.no_cpu:
         v, sec, cores, sample = cpu_query_sample(bw, 2, 1)
         line["cpu_baseline"] = {"value": round(v, 4), "unit": "M queries/s", "cores": cores, "kind": "port", "sample": sample}
+        if "tsdf_fusion" in line:
+            fv, fsample = cpu_tsdf_sample(bw)
+            line["tsdf_fusion"]["cpu_baseline"] = {"value": round(fv, 3), "unit": "frames/s", "cores": 1, "kind": "port",
+                                                   "sample": fsample}
+            cv, csample = cpu_conv_sample(bw)
+            line["bounded_grid"]["gaussian_filter_7x7x7"]["cpu_baseline"] = {
+                "value": round(cv, 4), "unit": "G cells/s", "cores": cores, "kind": "port", "sample": csample}
         if "hash_find" in line:
             hv, hsample = cpu_hash_sample(bw)
             line["hash_find"]["cpu_baseline"] = {"value": round(hv, 2), "unit": "M finds/s", "cores": cores, "kind": "port",
