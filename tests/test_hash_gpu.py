@@ -305,3 +305,61 @@ def test_rehash_keeps_associations_and_drops_tombstones(dim):
     assert torch.equal(torch.sort(i)[0], torch.sort(idx0)[0])
     eng.insert_keys(_diag_keys(dim, cap))  # fill to capacity: every index is handed out exactly once
     assert eng.size() == cap and torch.unique(eng.find(_diag_keys(dim, cap))[0]).numel() == cap
+
+
+@pytest.mark.parametrize("dim", [1, 2, 3, 4])
+def test_random_op_sequences_against_dict_model(dim):
+    """Seeded random sequences of insert / erase / find / items / clear over a small key range (many
+    collisions, re-insertions of erased keys, in-batch duplicates, occasional rebuilds) against a
+    plain Python dict: hit masks, sizes, index stability while a key lives, index uniqueness among
+    live keys, indices within [0, capacity)."""
+    import __ash
+
+    cap = 600
+    rng = np.random.default_rng(dim)
+    heap = torch.arange(cap, dtype=torch.int32, device=DEV)
+    m = __ash.HashMap(dim, cap, heap, DEV)
+    model = {}  # key tuple -> index
+
+    # the key universe stays below the capacity: which keys an overfull map drops is order dependent
+    span = {1: 250, 2: 11, 3: 4, 4: 2}[dim]
+
+    def draw(n):
+        return rng.integers(-span, span, size=(n, dim)).astype(np.int32)
+
+    for step in range(300):
+        op = rng.choice(["insert", "erase", "find", "items", "rehash", "clear"], p=[0.35, 0.25, 0.25, 0.1, 0.04, 0.01])
+        if op == "insert":
+            k = draw(int(rng.integers(1, 120)))
+            m.insert_keys(torch.from_numpy(k).to(DEV))
+            idx, ok = m.find(torch.from_numpy(k).to(DEV))
+            assert ok.all()
+            for key, i in zip(map(tuple, k), idx.tolist()):
+                if key in model:
+                    assert model[key] == i, "index of a live key changed"
+                else:
+                    model[key] = i
+        elif op == "erase":
+            k = draw(int(rng.integers(1, 80)))
+            m.erase(torch.from_numpy(k).to(DEV))
+            for key in map(tuple, k):
+                model.pop(key, None)
+        elif op == "find":
+            k = draw(200)
+            idx, ok = m.find(torch.from_numpy(k).to(DEV))
+            for key, i, hit in zip(map(tuple, k), idx.tolist(), ok.tolist()):
+                assert hit == (key in model)
+                assert i == (model[key] if hit else 0)
+        elif op == "items":
+            ks, idx = m.items()
+            got = {tuple(a): b for a, b in zip(ks.tolist(), idx.tolist())}
+            assert got == model
+        elif op == "rehash":
+            m.rehash()
+        else:
+            m.clear()
+            model.clear()
+        assert m.size() == len(model)
+        live = list(model.values())
+        assert len(set(live)) == len(live) and all(0 <= i < cap for i in live)
+    assert m.status() == 0
