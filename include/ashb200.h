@@ -392,6 +392,10 @@ int ashb_route_by_owner(const int32_t* keys, int64_t n, int key_dim, int world, 
 
 /* ---------------------------------------------------------------- runtime knobs */
 
+/* Selects the kernel behind ashb_map_find for key_dim <= 3: 0 = one thread per key (default),
+ * 1 = eight lanes per key reading a whole 128-byte line of slots per step.  Same results. */
+int ashb_set_find_cooperative(int enable);
+
 /* cudaLimitMaxL2FetchGranularity of the current context (32, 64 or 128 bytes); a
  * performance hint that lasts as long as the process.  No counterpart in the reference. */
 int ashb_set_l2_fetch_granularity(int bytes);

@@ -363,3 +363,32 @@ def test_random_op_sequences_against_dict_model(dim):
         live = list(model.values())
         assert len(set(live)) == len(live) and all(0 <= i < cap for i in live)
     assert m.status() == 0
+
+
+@pytest.mark.parametrize("dim", [1, 2, 3])
+def test_cooperative_find_equals_one_thread_find(dim):
+    """The eight-lanes-per-key find kernel answers exactly as the one-thread kernel, also across
+    tombstones, long probe chains (load 0.5) and batch sizes that are not a multiple of the group."""
+    import __ash
+
+    g = torch.Generator(device=DEV).manual_seed(40 + dim)
+    cap = 5000
+    span = {1: 20000, 2: 140, 3: 12}[dim]
+    keys = torch.randint(-span, span, (cap * 3, dim), dtype=torch.int32, device=DEV, generator=g)
+    heap = torch.arange(cap, dtype=torch.int32, device=DEV)
+    m = __ash.HashMap(dim, cap, heap, DEV)
+    m.insert_keys(keys)                       # fills the table to its capacity: load 0.5
+    m.erase(keys[::7].contiguous())           # tombstones inside the chains
+    m.insert_keys(keys[1::5].contiguous())
+    q = torch.randint(-span, span, (10007, dim), dtype=torch.int32, device=DEV, generator=g)
+    try:
+        for n in (10007, 1, 9, 0):
+            __ash.set_find_cooperative(False)
+            a = m.find(q[:n])
+            __ash.set_find_cooperative(True)
+            b = m.find(q[:n])
+            assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+            if n > 100:
+                assert 0.05 < float(a[1].float().mean()) < 1.0
+    finally:
+        __ash.set_find_cooperative(False)

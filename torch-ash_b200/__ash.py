@@ -74,6 +74,7 @@ _lib.ashb_render_weights_backward.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp,
 _lib.ashb_render_accumulate_forward.argtypes = [_vp, _vp, _int, _vp, _vp, _i64, _vp, _vp]
 _lib.ashb_render_accumulate_backward.argtypes = [_vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _vp, _vp]
 _lib.ashb_isosurface_extraction.argtypes = [_vp] * 9 + [_i64, _c.POINTER(_i64), _vp, _f32, _f32, _int, _i64, _i64, _i64, _vp]
+_lib.ashb_set_find_cooperative.argtypes = [_int]
 _lib.ashb_grid_zero_rows.argtypes = [_vp, _int, _vp, _vp, _c.c_double, _vp, _int, _vp, _vp, _i64, _i64, _i64, _vp]
 
 STATUS_CAPACITY, STATUS_PROBE, STATUS_SPIN, STATUS_DUPLICATE = 1, 2, 4, 8
@@ -84,6 +85,12 @@ _INTERP = {"linear": 0, "smooth_step": 1}
 def _check(rc: int):
     if rc != 0:
         raise RuntimeError(f"libashb200: {_lib.ashb_last_error_string().decode()} (status {rc})")
+
+
+def set_find_cooperative(enable: bool) -> None:
+    """Process-wide choice of the find kernel for key_dim <= 3: one thread per key (default, the
+    faster one for tables beyond L2) or eight lanes per key reading whole 128-byte lines of slots."""
+    _check(_lib.ashb_set_find_cooperative(int(bool(enable))))
 
 
 def _stream(device: torch.device) -> int:

@@ -51,6 +51,55 @@ __global__ void __launch_bounds__(256) find_kernel(Table t, const int32_t* __res
     masks[i] = (uint8_t)(found >= 0);
 }
 
+// Sub-warp cooperative variant for 16-byte slots: 8 lanes serve one query and read the whole
+// 128-byte line (8 slots) that holds the key's home slot with one coalesced request, then the
+// next line, and so on; a ballot finds the first slot in probe order that is empty or holds the
+// key, so the answer is identical to the one-thread probe.  It moves the same DRAM lines as the
+// one-thread kernel but needs one round trip per LINE of the probe chain instead of one per slot.
+template <int DIM>
+__global__ void __launch_bounds__(256) find_coop_kernel(Table16 t, const int32_t* __restrict__ keys, int64_t n,
+                                                        int64_t* __restrict__ indices, uint8_t* __restrict__ masks) {
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t q = tid >> 3;
+    const int sub = (int)(tid & 7);
+    const int group_shift = (int)(threadIdx.x & 31) & ~7;  // first lane of this 8-lane group in the warp
+    const bool live = q < n;
+    int k0 = 0, k1 = 0, k2 = 0, k3 = 0;
+    if (live) load_key<DIM>(keys, q, k0, k1, k2, k3);
+    const uint32_t home = hash_key(k0, k1, k2, k3) & t.mask;
+    uint32_t line = home & ~7u;
+    bool done = !live, first = true;
+    int found = -1;
+    const uint32_t n_lines = (t.mask >> 3) + 1;
+    for (uint32_t it = 0; it <= n_lines && __any_sync(0xffffffffu, !done); ++it) {
+        Entry e{0, 0, 0, 0, kTomb};
+        const uint32_t slot = line + sub;
+        if (!done) e = t.read_const(slot);
+        const bool in_chain = !first || slot >= home;  // the chain starts at the home slot
+        const unsigned hit = __ballot_sync(0xffffffffu, !done && in_chain && e.val >= 0 && key_match(e, k0, k1, k2, k3));
+        const unsigned empty = __ballot_sync(0xffffffffu, !done && in_chain && e.val == kEmpty);
+        const unsigned g_hit = (hit >> group_shift) & 0xFFu, g_empty = (empty >> group_shift) & 0xFFu;
+        const int first_hit = g_hit ? __ffs(g_hit) - 1 : 99, first_empty = g_empty ? __ffs(g_empty) - 1 : 99;
+        const int src = group_shift + (first_hit < 99 ? first_hit : 0);
+        const int val = __shfl_sync(0xffffffffu, e.val, src);
+        if (!done) {
+            if (first_hit < first_empty) {
+                found = val;
+                done = true;
+            } else if (first_empty < 99) {
+                done = true;
+            } else {
+                line = (line + 8) & t.mask;
+                first = false;
+            }
+        }
+    }
+    if (live && sub == 0) {
+        indices[q] = found >= 0 ? (int64_t)found : 0;
+        masks[q] = (uint8_t)(found >= 0);
+    }
+}
+
 // ---- insert ----------------------------------------------------------------------
 struct ValueCtx {
     int n;
@@ -299,6 +348,9 @@ int check_map(ashb_map* m) {
 
 }  // namespace
 
+// Which find kernel ashb_map_find launches for 16-byte slots (process-wide switch).
+static bool g_find_cooperative = false;
+
 extern "C" {
 
 int ashb_map_create(int key_dim, int64_t capacity, int32_t* heap_dev, int device, ashb_map** out) {
@@ -401,8 +453,23 @@ int ashb_map_find(ashb_map* m, const int32_t* keys, int64_t n, int64_t* indices,
     if (n == 0) return ASHB_OK;
     ASHB_REQUIRE(keys && indices && masks, "null buffer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    ASHB_DIM_LAUNCH(find_kernel, m, blocks_for(n, 256), 256, st, keys, n, indices, masks);
+    if (g_find_cooperative && m->key_dim <= 3) {
+        const Table16 t = table16_of(m);
+        const unsigned grid = blocks_for(n * 8, 256);
+        switch (m->key_dim) {
+            case 1: find_coop_kernel<1><<<grid, 256, 0, st>>>(t, keys, n, indices, masks); break;
+            case 2: find_coop_kernel<2><<<grid, 256, 0, st>>>(t, keys, n, indices, masks); break;
+            default: find_coop_kernel<3><<<grid, 256, 0, st>>>(t, keys, n, indices, masks); break;
+        }
+    } else {
+        ASHB_DIM_LAUNCH(find_kernel, m, blocks_for(n, 256), 256, st, keys, n, indices, masks);
+    }
     ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+int ashb_set_find_cooperative(int enable) {
+    g_find_cooperative = enable != 0;
     return ASHB_OK;
 }
 
