@@ -377,6 +377,29 @@ def measure_bounded(ash, bw, device, peak):
     reps = 10
     step_ms = event_ms(lambda: [train_step() for _ in range(reps)]) / reps
     grid.embeddings.grad = None
+
+    # the same step through the one-launch renderer (near/far + sampling + query + gradient of the
+    # signed distance + density + accumulation fused; one more launch for the whole backward)
+    from ash.render import render_rays
+
+    def fused_step(rays_o, rays_d):
+        grid.embeddings.grad = None
+        beta = to_sigma.min_beta + to_sigma.beta.abs()
+        res = render_rays(grid, rays_o, rays_d, 0.06, 2.5, 128, beta, "linear", skip_rays_without_hit=True)
+        loss = (res["rgb"] - 0.5).abs().mean() + 0.1 * (res["depth"] - 0.3).abs().mean() \
+            + 0.1 * res["eikonal_l2"].sum() / res["n_samples"].sum().clamp_min(1)
+        loss.backward()
+        return loss
+
+    for _ in range(3):
+        fused_step(o, d)
+    fused_ms = event_ms(lambda: [fused_step(o, d) for _ in range(reps)]) / reps
+    with torch.no_grad():
+        beta0 = (to_sigma.min_beta + to_sigma.beta.abs()).detach()
+        fwd_only_ms = event_ms(lambda: [render_rays(grid, o, d, 0.06, 2.5, 128, beta0, "linear", True)
+                                        for _ in range(reps)]) / reps
+        fused_samples = int(render_rays(grid, o, d, 0.06, 2.5, 128, beta0, "linear", True)["n_samples"].sum())
+    grid.embeddings.grad = None
     return {
         "workload": f"bounded grid 512^3 ({S} blocks x grid_dim {G}), {D} channels, {n_blocks} active blocks",
         "gaussian_filter_7x7x7": {"ms": round(conv_ms, 3), "cells_per_s": round(cells / (conv_ms * 1e-3) / 1e9, 3),
@@ -393,6 +416,15 @@ def measure_bounded(ash, bw, device, peak):
                     "fresh dense gradient", "rays": int(n_r), "samples": n_samples, "ms": round(step_ms, 3),
             "rays_per_s": round(n_r / (step_ms * 1e-3) / 1e6, 3), "unit": "M rays/s",
             "samples_per_s": round(n_samples / (step_ms * 1e-3) / 1e6, 2)},
+        "volume_rendering_train_step_fused": {
+            "what": "render_rays (near/far + sampling + query + sdf gradient + density + accumulation in one launch) "
+                    "+ loss + backward (one launch), fresh dense gradient; near/far included, which the row above "
+                    "leaves outside its timed step",
+            "rays": int(n_r), "samples": fused_samples, "ms": round(fused_ms, 3),
+            "rays_per_s": round(n_r / (fused_ms * 1e-3) / 1e6, 3), "unit": "M rays/s",
+            "samples_per_s": round(fused_samples / (fused_ms * 1e-3) / 1e6, 2),
+            "forward_only_ms": round(fwd_only_ms, 4),
+            "speedup_over_composed_step": round(step_ms / fused_ms, 2)},
     }
 
 

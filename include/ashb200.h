@@ -381,6 +381,38 @@ int ashb_render_accumulate_backward(const float* weights, const float* values, c
                                     const int64_t* ray_indices, int64_t m, int64_t n_rays, int C,
                                     float* grad_weights, float* grad_values, void* stream);
 
+/* ---------------------------------------------------------------- fused ray renderer
+ * One launch per direction for what the reference's training step composes from
+ * ray_find_near_far -> ray_sample -> grid query -> autograd.grad(sdf, x) -> normalize ->
+ * SDFToDensity -> render_weight_from_density / accumulate_along_rays
+ * (demo/train_scene_recon.py:64-161, ash/src/sampler.cu:7-215, ash/src/grid.cu:69-255): no
+ * per-sample tensor is written.  Channel 0 of an embedding row is the signed distance, channels
+ * 1..3 the colour (D >= 4).  The map must be the grid's 3-D block map; nb_lut int32 [n_emb][8]
+ * from ashb_grid_build_neighbor_lut; cell_size / origin (host float[3] or NULL) as in
+ * ashb_grid_query_forward; ray_o_world and ray_o_cell float [n_rays][3] are the ray origins in
+ * world and in cell units, ray_d the (unscaled) directions; bbox and t range in cell units as for
+ * ashb_ray_find_near_far; beta: DEVICE float[1], the density scale (min_beta + |parameter|).
+ * skip_missed != 0: rays that meet no occupied block are not sampled (all outputs 0).
+ * out float [n_rays][16]: rgb[0..2], depth[3] (sum w * t_mid, world units), normal[4..6],
+ * accumulated weight[7], sum | |grad sdf| - 1 | [8], sum (|grad sdf| - 1)^2 [9], sample count[10],
+ * near[11], far[12] (world units, as ray_find_near_far returns them), [13..15] = 0. */
+int ashb_render_rays_forward(ashb_map* map, int interp, const float* embeddings, int64_t n_emb, int grid_dim, int D,
+                             const int32_t* nb_lut, double cell_size, const float* origin,
+                             const float* ray_o_world, const float* ray_o_cell, const float* ray_d,
+                             const float* bbox_min_cell, const float* bbox_max_cell, float t_min_cell,
+                             float t_max_cell, int64_t max_samples_per_ray, int skip_missed, const float* beta,
+                             float* out, int64_t n_rays, void* stream);
+/* Gradients of a scalar loss given grad_out float [n_rays][16] (columns 0..9 are read) and the
+ * forward's `out`: ADDS into grad_embeddings (same shape as embeddings) and grad_beta (DEVICE
+ * float[1]); the caller zero-fills both (or keeps accumulating).  Re-marches every ray. */
+int ashb_render_rays_backward(ashb_map* map, int interp, const float* embeddings, int64_t n_emb, int grid_dim, int D,
+                              const int32_t* nb_lut, double cell_size, const float* origin,
+                              const float* ray_o_world, const float* ray_o_cell, const float* ray_d,
+                              const float* bbox_min_cell, const float* bbox_max_cell, float t_min_cell,
+                              float t_max_cell, int64_t max_samples_per_ray, int skip_missed, const float* beta,
+                              const float* out, const float* grad_out, float* grad_embeddings, float* grad_beta,
+                              int64_t n_rays, void* stream);
+
 /* ---------------------------------------------------------------- multi-GPU key routing
  * For a hash map partitioned over `world` ranks by key hash (no counterpart in the reference,
  * which is single-GPU): groups keys int32 [n][key_dim] by owner rank into keys_out (same shape),

@@ -75,6 +75,9 @@ _lib.ashb_render_accumulate_forward.argtypes = [_vp, _vp, _int, _vp, _vp, _i64, 
 _lib.ashb_render_accumulate_backward.argtypes = [_vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _vp, _vp]
 _lib.ashb_isosurface_extraction.argtypes = [_vp] * 9 + [_i64, _c.POINTER(_i64), _vp, _f32, _f32, _int, _i64, _i64, _i64, _vp]
 _lib.ashb_set_find_cooperative.argtypes = [_int]
+_RAY_ARGS = [_vp, _int, _vp, _i64, _int, _int, _vp, _c.c_double, _vp, _vp, _vp, _vp, _vp, _vp, _f32, _f32, _i64, _int, _vp]
+_lib.ashb_render_rays_forward.argtypes = _RAY_ARGS + [_vp, _i64, _vp]
+_lib.ashb_render_rays_backward.argtypes = _RAY_ARGS + [_vp, _vp, _vp, _vp, _i64, _vp]
 _lib.ashb_grid_zero_rows.argtypes = [_vp, _int, _vp, _vp, _c.c_double, _vp, _int, _vp, _vp, _i64, _i64, _i64, _vp]
 
 STATUS_CAPACITY, STATUS_PROBE, STATUS_SPIN, STATUS_DUPLICATE = 1, 2, 4, 8
@@ -804,3 +807,71 @@ def grid_zero_rows(hashmap, grad_embeddings, x, cell_size, origin, grid_dim, nb_
         hashmap._h, _dtype_code(g), g.data_ptr(), x.data_ptr(), float(cell_size), _host_floats(origin, 3),
         int(grid_dim), nb_lut.data_ptr(), bidx.data_ptr() if bidx is not None else None, x.shape[0], g.shape[0],
         g.shape[2], _stream(g.device)))
+
+
+# ---------------------------------------------------------------------------------------------
+# Fused ray renderer (no counterpart in the reference's native module: its demo composes this
+# from ray_find_near_far, ray_sample, the grid query, autograd.grad and a third-party package).
+
+def _ray_args(hashmap, embeddings, nb_lut, cell_size, origin, ray_o_world, ray_o_cell, ray_d, bbox_min_cell,
+              bbox_max_cell, t_min_cell, t_max_cell, max_samples_per_ray, skip_missed, beta, interpolation):
+    emb = _cuda(embeddings, "embeddings", torch.float32)
+    if emb.dim() != 3 or emb.shape[2] < 4:
+        raise RuntimeError("ray rendering needs embeddings (num_embeddings, G^3, D >= 4): signed distance + colour")
+    G = round(emb.shape[1] ** (1.0 / 3.0))
+    if G ** 3 != emb.shape[1]:
+        raise RuntimeError("embeddings.shape[1] is not a cube")
+    lut = _cuda(nb_lut, "nb_lut", torch.int32)
+    ow = _cuda(ray_o_world, "ray_o_world", torch.float32)
+    oc = _cuda(ray_o_cell, "ray_o_cell", torch.float32)
+    d = _cuda(ray_d, "ray_d", torch.float32)
+    if not (ow.shape == oc.shape == d.shape and ow.dim() == 2 and ow.shape[1] == 3):
+        raise RuntimeError("ray origins and directions must be (n_rays, 3)")
+    lo = _cuda(bbox_min_cell, "bbox_min", torch.float32).view(-1)
+    hi = _cuda(bbox_max_cell, "bbox_max", torch.float32).view(-1)
+    b = _cuda(beta, "beta", torch.float32).view(-1)
+    org = (_f32 * 3)(*[float(v) for v in origin]) if origin is not None else None
+    keep = (emb, lut, ow, oc, d, lo, hi, b, org)
+    args = [hashmap._h, _INTERP[interpolation], emb.data_ptr(), emb.shape[0], G, emb.shape[2], lut.data_ptr(),
+            float(cell_size), org, ow.data_ptr(), oc.data_ptr(), d.data_ptr(), lo.data_ptr(), hi.data_ptr(),
+            float(t_min_cell), float(t_max_cell), int(max_samples_per_ray), int(bool(skip_missed)), b.data_ptr()]
+    return args, keep, emb, ow.shape[0]
+
+
+def render_rays_forward(hashmap, embeddings, nb_lut, cell_size, origin, ray_o_world, ray_o_cell, ray_d, bbox_min_cell,
+                        bbox_max_cell, t_min_cell, t_max_cell, max_samples_per_ray, skip_missed, beta,
+                        interpolation="linear"):
+    """(n_rays, 16) float32 rows: rgb, depth, normal, accumulated weight, the two eikonal sums,
+    sample count, near, far (columns as documented for ashb_render_rays_forward)."""
+    args, keep, emb, n = _ray_args(hashmap, embeddings, nb_lut, cell_size, origin, ray_o_world, ray_o_cell, ray_d,
+                                   bbox_min_cell, bbox_max_cell, t_min_cell, t_max_cell, max_samples_per_ray,
+                                   skip_missed, beta, interpolation)
+    out = torch.empty((n, 16), dtype=torch.float32, device=emb.device)
+    with torch.cuda.device(emb.device):
+        _check(_lib.ashb_render_rays_forward(*args, out.data_ptr(), n, _stream(emb.device)))
+    return out
+
+
+def render_rays_backward(hashmap, embeddings, nb_lut, cell_size, origin, ray_o_world, ray_o_cell, ray_d, bbox_min_cell,
+                         bbox_max_cell, t_min_cell, t_max_cell, max_samples_per_ray, skip_missed, beta, out, grad_out,
+                         interpolation="linear", grad_embeddings_out=None):
+    """(grad_embeddings, grad_beta (1,)); adds into ``grad_embeddings_out`` when given, else into
+    a fresh zero-filled tensor shaped like ``embeddings``."""
+    args, keep, emb, n = _ray_args(hashmap, embeddings, nb_lut, cell_size, origin, ray_o_world, ray_o_cell, ray_d,
+                                   bbox_min_cell, bbox_max_cell, t_min_cell, t_max_cell, max_samples_per_ray,
+                                   skip_missed, beta, interpolation)
+    out = _cuda(out, "out", torch.float32)
+    go = _cuda(grad_out, "grad_out", torch.float32)
+    if out.shape != (n, 16) or go.shape != (n, 16):
+        raise RuntimeError("out and grad_out must be (n_rays, 16)")
+    if grad_embeddings_out is None:
+        ge = torch.zeros_like(emb)
+    else:
+        ge = grad_embeddings_out
+        if not (ge.is_cuda and ge.is_contiguous() and ge.shape == emb.shape and ge.dtype == emb.dtype):
+            raise RuntimeError("grad_embeddings_out must be a contiguous CUDA tensor shaped like embeddings")
+    gb = torch.zeros(1, dtype=torch.float32, device=emb.device)
+    with torch.cuda.device(emb.device):
+        _check(_lib.ashb_render_rays_backward(*args, out.data_ptr(), go.data_ptr(), ge.data_ptr(), gb.data_ptr(), n,
+                                              _stream(emb.device)))
+    return ge, gb

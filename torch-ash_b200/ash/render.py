@@ -84,3 +84,68 @@ class SDFToDensity(nn.Module):
     def forward(self, sdf: torch.Tensor) -> torch.Tensor:
         beta = self.min_beta + torch.abs(self.beta)
         return (1 / beta) * (0.5 + 0.5 * sdf.sign() * torch.expm1(-sdf.abs() / beta))
+
+
+class _RenderRays(torch.autograd.Function):
+    """One launch forward, one launch backward for the whole ray -> pixel composition."""
+
+    @staticmethod
+    def forward(ctx, embeddings, beta, geom, rays):
+        rows = backend.render_rays_forward(geom[0], embeddings, *geom[1:4], *rays, beta, geom[4])
+        ctx.save_for_backward(embeddings, beta, rows)
+        ctx.geom, ctx.rays = geom, rays
+        return rows
+
+    @staticmethod
+    def backward(ctx, grad_rows):
+        embeddings, beta, rows = ctx.saved_tensors
+        geom, rays = ctx.geom, ctx.rays
+        grad_buffer = geom[5]
+        grad_embeddings, grad_beta = backend.render_rays_backward(
+            geom[0], embeddings, *geom[1:4], *rays, beta, rows, grad_rows.contiguous(), geom[4],
+            grad_embeddings_out=grad_buffer)
+        if grad_buffer is not None or not ctx.needs_input_grad[0]:
+            grad_embeddings = None
+        return grad_embeddings, grad_beta.view(beta.shape) if ctx.needs_input_grad[1] else None, None, None
+
+
+def render_rays(grid, rays_o: torch.Tensor, rays_d: torch.Tensor, t_min: float, t_max: float,
+                max_samples_per_ray: int, beta: torch.Tensor, interpolation: str = "linear",
+                skip_rays_without_hit: bool = False) -> dict:
+    """Render rays through ``grid`` in one fused launch: what the reference's training step
+    composes from ``grid.ray_find_near_far`` -> ``grid.ray_sample`` -> ``grid(x)`` ->
+    ``autograd.grad(sdf, x)`` -> normalize -> ``SDFToDensity`` -> weights -> accumulation
+    (demo/train_scene_recon.py:64-161), with no per-sample tensor.
+
+    ``grid.embeddings[..., 0]`` is the signed distance, ``[..., 1:4]`` the colour.  ``beta`` is the
+    density scale as a tensor of one element (``min_beta + |parameter|``).  Differentiable w.r.t.
+    ``grid.embeddings`` (dense gradient, or added into ``embeddings.grad`` with
+    ``grid.grad_mode = "in_place"``) and ``beta``; ray origins and directions get no gradient.
+
+    Returns a dict of per-ray tensors: ``rgb`` (n, 3), ``depth`` (n, 1) = sum of weight * t_mid,
+    ``normal`` (n, 3), ``weights`` (n, 1), ``eikonal_l1`` / ``eikonal_l2`` (n, 1) = sums over the
+    ray's samples of ``| |grad sdf| - 1 |`` and its square, ``n_samples`` (n, 1), ``near``,
+    ``far`` (n, 1) as ``ray_find_near_far`` returns them.
+    """
+    if interpolation not in ("linear", "smooth_step"):
+        raise ValueError(f"Unknown interpolation: {interpolation}")
+    if grid.transform_world_to_cell is not grid._own_transform:
+        raise RuntimeError("render_rays needs the grid's own world <-> cell transform")
+    if grid.grid_coords is None or grid.lut_grid_nb2grid_idx is None:
+        grid.construct_grid_neighbor_lut_(radius=1, bidirectional=False)
+    origin, cell_size = grid._cell_frame()
+    grad_buffer = None
+    if grid.grad_mode == "in_place" and grid.embeddings.requires_grad and torch.is_grad_enabled():
+        if grid.embeddings.grad is None:
+            grid.embeddings.grad = torch.zeros_like(grid.embeddings)
+        grad_buffer = grid.embeddings.grad
+    with torch.no_grad():
+        bbox_min, bbox_max = grid.get_bbox()
+        rays = (rays_o.contiguous(), grid.transform_world_to_cell(rays_o).contiguous(), rays_d.contiguous(),
+                grid.transform_world_to_cell(bbox_min).contiguous(), grid.transform_world_to_cell(bbox_max).contiguous(),
+                t_min / grid.cell_size, t_max / grid.cell_size, int(max_samples_per_ray), bool(skip_rays_without_hit))
+    geom = (grid.engine.backend, grid._neighbor_lut32(), cell_size, origin, interpolation, grad_buffer)
+    rows = _RenderRays.apply(grid.embeddings, beta.to(torch.float32), geom, rays)
+    return {"rgb": rows[:, 0:3], "depth": rows[:, 3:4], "normal": rows[:, 4:7], "weights": rows[:, 7:8],
+            "eikonal_l1": rows[:, 8:9], "eikonal_l2": rows[:, 9:10], "n_samples": rows[:, 10:11].detach(),
+            "near": rows[:, 11:12].detach(), "far": rows[:, 12:13].detach()}

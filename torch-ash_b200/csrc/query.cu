@@ -18,7 +18,7 @@
 //                block / cell / offset split (ash/grid.py:183-199), hash probe of the
 //                block, corner cells by add-with-carry, and an int32 block-neighbour
 //                row read only by queries whose cell touches a +x/+y/+z block face.
-#include "hashmap.cuh"
+#include "query.cuh"
 
 namespace ashb {
 
@@ -69,45 +69,6 @@ template <>
 __device__ __forceinline__ void atomic_add_pack<float, 2>(float* p, const Pack<float, 2>& r) {
     atomicAdd(reinterpret_cast<float2*>(p), make_float2(r.v[0], r.v[1]));
 }
-
-// ash/src/grid.cu:7-41
-template <typename T>
-__device__ __forceinline__ T interp_fn(int interp, T x) {
-    return interp == ASHB_SMOOTH_STEP ? x * x * (3 - 2 * x) : x;
-}
-template <typename T>
-__device__ __forceinline__ T dinterp_fn(int interp, T x) {
-    return interp == ASHB_SMOOTH_STEP ? 6 * x * (1 - x) : T(1);
-}
-
-// Per-axis weights of the two corners along each axis and their derivatives.
-// w[d][b]: b = 0 -> corner at the cell origin (argument 1 - offset, evaluated
-// in float as the reference does, grid.cu:117), b = 1 -> far corner.
-template <typename T>
-struct AxisWeights {
-    T w[3][2];
-    T dw[3][2];
-    __device__ __forceinline__ void init(int interp, const float* off) {
-#pragma unroll
-        for (int d = 0; d < 3; ++d) {
-            const T x1 = (T)off[d];
-            const T x0 = (T)(1.0f - off[d]);
-            w[d][0] = interp_fn<T>(interp, x0);
-            w[d][1] = interp_fn<T>(interp, x1);
-            dw[d][0] = -dinterp_fn<T>(interp, x0);
-            dw[d][1] = dinterp_fn<T>(interp, x1);
-        }
-    }
-    __device__ __forceinline__ T weight(int c) const {
-        return w[0][c & 1] * w[1][(c >> 1) & 1] * w[2][(c >> 2) & 1];
-    }
-    __device__ __forceinline__ void grad(int c, T* g) const {
-        const int bx = c & 1, by = (c >> 1) & 1, bz = (c >> 2) & 1;
-        g[0] = dw[0][bx] * w[1][by] * w[2][bz];
-        g[1] = w[0][bx] * dw[1][by] * w[2][bz];
-        g[2] = w[0][bx] * w[1][by] * dw[2][bz];
-    }
-};
 
 struct QueryLuts {
     const int64_t* __restrict__ grid_indices;
@@ -175,41 +136,15 @@ struct FusedSource {
 
     __device__ __forceinline__ bool resolve(int64_t q, int lane, int64_t D, int64_t* base, float* off) const {
         int blk[3], cell[3];
-#pragma unroll
-        for (int d = 0; d < 3; ++d) {
-            const float xc = __fmul_rn(__fsub_rn(x[3 * q + d], org[d]), inv_cell);
-            const float bf = floorf(__fmul_rn(xc, inv_G));
-            const float local = __fsub_rn(xc, __fmul_rn(bf, G_f));
-            const float cf = floorf(local);
-            off[d] = __fsub_rn(local, cf);
-            blk[d] = (int)bf;
-            // `local` can round up to exactly G for tiny negative positions
-            cell[d] = min(max((int)cf, 0), G - 1);
-        }
+        const float xw[3] = {x[3 * q], x[3 * q + 1], x[3 * q + 2]};
+        split_world_position(xw, org, inv_cell, inv_G, G_f, G, blk, cell, off);
         const int gi = gi_in ? gi_in[q] : lookup(table, blk[0], blk[1], blk[2], 0);
         if (lane == 0) {
             if (gi_out) gi_out[q] = gi;
             if (mask_out) mask_out[q] = (uint8_t)(gi >= 0);
         }
         if (gi < 0 || gi >= n_emb) return false;
-        const int32_t* row = nb_lut + (int64_t)gi * 8;
-        bool ok = true;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            int cc[3], nb = 0;
-#pragma unroll
-            for (int d = 0; d < 3; ++d) {
-                cc[d] = cell[d] + ((c >> d) & 1);
-                if (cc[d] == G) {
-                    cc[d] = 0;
-                    nb |= 1 << d;
-                }
-            }
-            const int g = nb ? __ldg(row + nb) : gi;
-            ok = ok && g >= 0 && g < n_emb;
-            base[c] = ((int64_t)g * cells_per_grid + (cc[0] + (cc[1] + cc[2] * G) * G)) * D;
-        }
-        return ok;
+        return corner_rows(nb_lut, gi, cell, G, n_emb, cells_per_grid, D, base);
     }
 };
 

@@ -9,22 +9,9 @@
 // One thread marches one ray; the loops are data dependent and bounded by
 // (t_max - t_min) / step.  The table of a scene (<= a few hundred thousand
 // blocks x 16 bytes) stays L2 resident.
-#include "hashmap.cuh"
+#include "sampler.cuh"
 
 namespace ashb {
-
-__device__ __forceinline__ bool block_active(const Table16& t, const float* p, float cell2grid) {
-    const int bx = (int)floorf(p[0] * cell2grid);
-    const int by = (int)floorf(p[1] * cell2grid);
-    const int bz = (int)floorf(p[2] * cell2grid);
-    return lookup(t, bx, by, bz, 0) >= 0;
-}
-
-__device__ __forceinline__ void ray_at(const float* o, const float* d, float t, float* p) {
-    p[0] = __fmaf_rn(t, d[0], o[0]);
-    p[1] = __fmaf_rn(t, d[1], o[1]);
-    p[2] = __fmaf_rn(t, d[2], o[2]);
-}
 
 // ash/src/sampler.cu:7-71
 __global__ void __launch_bounds__(128) ray_near_far_kernel(Table16 t, const float* __restrict__ ray_o,
@@ -39,22 +26,8 @@ __global__ void __launch_bounds__(128) ray_near_far_kernel(Table16 t, const floa
     const float hi[3] = {bbox_max[0], bbox_max[1], bbox_max[2]};
     const float o[3] = {ray_o[3 * i], ray_o[3 * i + 1], ray_o[3 * i + 2]};
     const float d[3] = {ray_d[3 * i], ray_d[3 * i + 1], ray_d[3 * i + 2]};
-    const float cell2grid = (float)(1.0 / (double)grid2cell);
-    const float step = (float)((double)grid2cell * 0.5);
-    float near = -1.f, far = t_max, tt = t_min;
-    // step > 0 is checked by the host, so the march ends after (t_max - t_min) / step rounds
-    while (tt < t_max) {
-        float p[3];
-        ray_at(o, d, tt, p);
-        const bool inside = p[0] >= lo[0] && p[0] <= hi[0] && p[1] >= lo[1] && p[1] <= hi[1] &&
-                            p[2] >= lo[2] && p[2] <= hi[2];
-        if (!inside) break;
-        if (block_active(t, p, cell2grid)) {
-            near = near < 0.f ? tt : fmaxf(near - step, t_min);
-            far = fminf(tt + step, t_max);
-        }
-        tt += step;
-    }
+    float near, far;
+    march_near_far(t, o, d, lo, hi, t_min, t_max, grid2cell, near, far);
     nears[i] = near;
     fars[i] = far;
 }
@@ -78,8 +51,7 @@ __global__ void __launch_bounds__(128) ray_sample_kernel(Table16 t, const float*
     const float d[3] = {ray_d[3 * i], ray_d[3 * i + 1], ray_d[3 * i + 2]};
     const float ray_near = ray_nears[i], ray_far = ray_fars[i];
     const float cell2grid = (float)(1.0 / (double)grid2cell);
-    // sampler.cu:151: max(0.7, float) is a double max whose result is stored as float
-    const float cell_step = (float)fmax(0.7, (double)((ray_far - ray_near) / (float)max_samples));
+    const float cell_step = sample_cell_step(ray_near, ray_far, max_samples);
     const float grid_step = cell_step * grid2cell;
     float tt = ray_near, seg_near = ray_near;
     int64_t local = 0;
