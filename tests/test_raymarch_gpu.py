@@ -161,3 +161,67 @@ def test_embedding_dim_below_four_is_refused():
     d = torch.nn.functional.normalize(torch.ones(4, 3, device=DEV), dim=-1)
     with pytest.raises(RuntimeError):
         render_rays(grid, o, d, 0.05, 1.0, 8, torch.tensor([0.1], device=DEV))
+
+
+def test_fused_forward_against_the_cpu_oracle():
+    """Per-ray outputs of the one-launch renderer against the CPU oracle run stage by stage:
+    oracle near/far -> oracle sampler -> oracle query forward + d/d offset -> numpy density ->
+    oracle rendering quadrature."""
+    import numpy as np
+
+    import oracle
+    from oracle import render as orender
+
+    f32 = np.float32
+    grid = make_grid("bounded", 4, seed=31)
+    n = 800
+    o, d = make_rays(grid, n, 19, torch.zeros(3, device=DEV))
+    t_min, t_max, max_samples, beta = 0.05, 2.0, 40, 0.03
+    with torch.no_grad():
+        out = render_rays(grid, o, d, t_min, t_max, max_samples, torch.tensor([beta], device=DEV), "linear")
+
+    G, cs = grid.grid_dim, grid.cell_size
+    keys, idx = grid.engine.items()
+    hm = oracle.OracleHashMap(3, grid.engine.capacity)
+    hm.load_states(keys.cpu().numpy(), idx.cpu().numpy(), grid.engine._heap.cpu().numpy())
+    o_c = grid.transform_world_to_cell(o).cpu().numpy()
+    o_w, d_np = o.cpu().numpy(), d.cpu().numpy()
+    lo, hi = (grid.transform_world_to_cell(b).cpu().numpy() for b in grid.get_bbox())
+    nears_c, fars_c = oracle.ray_find_near_far(hm, o_c, d_np, lo, hi, t_min / cs, t_max / cs, 0.01 / cs, float(G))
+    nears_w, fars_w = nears_c * f32(cs), fars_c * f32(cs)
+    inv_cs = f32(1.0 / cs)
+    ri, t0c, t1c, _ = oracle.ray_sample(hm, o_c, d_np, nears_w * inv_cs, fars_w * inv_cs, lo, hi, max_samples, float(G))
+    t0w, t1w = t0c * f32(cs), t1c * f32(cs)
+    t_mid = f32(0.5) * (t0w + t1w)
+    x = o_w[ri] + t_mid[:, None] * d_np[ri]
+    xc = (x - np.asarray(grid._origin, f32)) * inv_cs
+    block = np.floor(xc * f32(1.0 / G))
+    local = xc - block * f32(G)
+    cell = np.floor(local)
+    off = (local - cell).astype(f32)
+    gi, mk = hm.find(block.astype(np.int32))
+    ci = (np.clip(cell.astype(np.int64), 0, G - 1) * np.array([1, G, G * G])).sum(-1)
+    luts = [t.cpu().numpy() for t in (grid.lut_grid_nb2grid_idx, grid.lut_cell_nb2cell_idx, grid.lut_cell_nb2grid_nb)]
+    emb = grid.embeddings.detach().cpu().numpy()
+    y = oracle.query_forward(emb, off, gi, ci, mk, *luts, "linear")
+    z = np.zeros_like(y)
+    z[:, 0] = 1
+    _, grad_off = oracle.query_backward_forward(z, emb, off, gi, ci, mk, *luts, "linear")
+    g = grad_off.astype(np.float64) * float(inv_cs)
+    gnorm = np.linalg.norm(g, axis=1, keepdims=True)
+    normals = g / np.maximum(gnorm, 1e-12)
+    sdf = y[:, 0].astype(np.float64)
+    sigma = (1 / beta) * (0.5 + 0.5 * np.sign(sdf) * np.expm1(-np.abs(sdf) / beta)) * mk
+    w = orender.render_weights(t0w, t1w, sigma, ri, n)
+    want = np.concatenate([orender.accumulate(w, ri, y[:, 1:4], n), orender.accumulate(w, ri, t_mid, n),
+                           orender.accumulate(w, ri, normals, n), orender.accumulate(w, ri, None, n),
+                           orender.accumulate(np.ones_like(w), ri, np.abs(gnorm - 1), n),
+                           orender.accumulate(np.ones_like(w), ri, (gnorm - 1) ** 2, n),
+                           orender.accumulate(np.ones_like(w), ri, None, n)], axis=1)
+    got = torch.cat([out[k] for k in ("rgb", "depth", "normal", "weights", "eikonal_l1", "eikonal_l2", "n_samples")],
+                    dim=1).cpu().numpy()
+    assert len(ri) > 5 * n
+    np.testing.assert_array_equal(got[:, 10], want[:, 10])                     # same samples on every ray
+    np.testing.assert_array_equal(out["near"].cpu().numpy().ravel(), nears_w)  # bit-exact first stage
+    np.testing.assert_array_equal(out["far"].cpu().numpy().ravel(), fars_w)
+    np.testing.assert_allclose(got, want, rtol=2e-4, atol=2e-5)
