@@ -301,7 +301,7 @@ static int make_ray_grid(RayGrid& g, ashb_map* m, int interp, const float* emb, 
     ASHB_REQUIRE(interp == ASHB_LINEAR || interp == ASHB_SMOOTH_STEP, "unknown interpolation");
     ASHB_REQUIRE(emb && nb_lut && bbox_min && bbox_max, "null buffer");
     ASHB_REQUIRE(n_emb > 0 && grid_dim >= 1 && D >= 4, "needs embedding_dim >= 4 (signed distance + colour)");
-    ASHB_REQUIRE(cell_size > 0.0 && max_samples > 0, "bad cell size or sample budget");
+    ASHB_REQUIRE(cell_size > 0.0 && max_samples > 0, "bad cell size or sample limit");
     ASHB_REQUIRE(t_min == t_min && t_max == t_max && t_max - t_min < 3.0e38f, "ray range must be finite");
     g.table = table16_of(m);
     g.emb = emb;

@@ -115,7 +115,7 @@ int ashb_ray_sample_count(ashb_map* m, const float* ray_o, const float* ray_d, c
                           const float* ray_fars, int64_t* counts, int64_t max_samples_per_ray,
                           float grid2cell, int64_t n, void* stream) {
     if (int rc = check_sampler_map(m)) return rc;
-    ASHB_REQUIRE(n >= 0 && grid2cell > 0.f && max_samples_per_ray > 0, "bad ray count, grid_dim or sample budget");
+    ASHB_REQUIRE(n >= 0 && grid2cell > 0.f && max_samples_per_ray > 0, "bad ray count, grid_dim or sample limit");
     if (n == 0) return ASHB_OK;
     ASHB_REQUIRE(ray_o && ray_d && ray_nears && ray_fars && counts, "null buffer");
     DeviceGuard guard(m->device);
@@ -132,7 +132,7 @@ int ashb_ray_sample_fill(ashb_map* m, const float* ray_o, const float* ray_d, co
                          float* t_nears, float* t_fars, int64_t max_samples_per_ray, float grid2cell,
                          int64_t n, void* stream) {
     if (int rc = check_sampler_map(m)) return rc;
-    ASHB_REQUIRE(n >= 0 && grid2cell > 0.f && max_samples_per_ray > 0, "bad ray count, grid_dim or sample budget");
+    ASHB_REQUIRE(n >= 0 && grid2cell > 0.f && max_samples_per_ray > 0, "bad ray count, grid_dim or sample limit");
     if (n == 0) return ASHB_OK;
     ASHB_REQUIRE(ray_o && ray_d && ray_nears && ray_fars && prefix_sum, "null buffer");
     DeviceGuard guard(m->device);
