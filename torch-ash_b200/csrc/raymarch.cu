@@ -127,45 +127,67 @@ __device__ __forceinline__ void eval_sample(const RayGrid& G, const float* o_w, 
     s.sigma = density(s.sdf, beta, alpha) * s.hit;
 }
 
-// Near/far + the sampler's march; calls f(t0c, t1c, block, block index) for every emitted
-// interval, in order (block = the active block the march found at the interval's start).
-// Returns false when the ray is skipped (no occupied block met and skip_missed set).
-// KNOWN_RANGE: near_w / far_w come in (the backward pass reads them from the forward's output row)
-// and the first stage is not repeated.
-template <bool KNOWN_RANGE, class F>
-__device__ __forceinline__ bool march_ray(const RayGrid& G, const float* o_c, const float* d, float& near_w,
-                                          float& far_w, F&& f) {
-    if (!KNOWN_RANGE) {
-        const float lo[3] = {G.bbox_min[0], G.bbox_min[1], G.bbox_min[2]};
-        const float hi[3] = {G.bbox_max[0], G.bbox_max[1], G.bbox_max[2]};
-        float near_c, far_c;
-        march_near_far(G.table, o_c, d, lo, hi, G.t_min, G.t_max, G.grid2cell, near_c, far_c);
-        // lengths leave the first stage in world units and re-enter the second in cell units
-        near_w = __fmul_rn(near_c, G.cell);
-        far_w = __fmul_rn(far_c, G.cell);
-    }
-    if (near_w < 0.f && G.skip_missed) return false;
-    const float ray_near = __fmul_rn(near_w, G.inv_cell), ray_far = __fmul_rn(far_w, G.inv_cell);
-    const float cell2grid = (float)(1.0 / (double)G.grid2cell);
-    const float cell_step = sample_cell_step(ray_near, ray_far, G.max_samples);
-    const float grid_step = cell_step * G.grid2cell;
-    float tt = ray_near, seg_near = ray_near;
-    while (tt < ray_far) {
-        float p[3];
-        ray_at(o_c, d, tt, p);
-        const int blk[3] = {(int)floorf(p[0] * cell2grid), (int)floorf(p[1] * cell2grid),
-                            (int)floorf(p[2] * cell2grid)};  // as block_active places it
-        const int gi = lookup(G.table, blk[0], blk[1], blk[2], 0);
-        if (gi < 0) {
-            tt += grid_step;
-        } else {
-            tt += cell_step;
-            f(seg_near, tt, blk, gi);
-            seg_near = tt;
+// Near/far + the sampler's march as a resumable state: next() advances the ray to its next
+// interval inside an occupied block.  The kernels call it in warp-converged rounds (every lane
+// marches to its next interval, then all lanes evaluate their intervals together), so a warp pays
+// for one evaluation per round instead of one per march step in which any lane has a sample.
+struct RayMarcher {
+    float tt, seg_near, ray_far, cell_step, grid_step, cell2grid;
+    bool active;
+
+    // KNOWN_RANGE: near_w / far_w come in (the backward pass reads them from the forward's output
+    // row) and the first stage is not repeated.
+    template <bool KNOWN_RANGE>
+    __device__ __forceinline__ void start(const RayGrid& G, const float* o_c, const float* d, bool live, float& near_w,
+                                          float& far_w) {
+        active = live;
+        tt = seg_near = ray_far = cell_step = grid_step = cell2grid = 0.f;
+        if (!live) return;
+        if (!KNOWN_RANGE) {
+            const float lo[3] = {G.bbox_min[0], G.bbox_min[1], G.bbox_min[2]};
+            const float hi[3] = {G.bbox_max[0], G.bbox_max[1], G.bbox_max[2]};
+            float near_c, far_c;
+            march_near_far(G.table, o_c, d, lo, hi, G.t_min, G.t_max, G.grid2cell, near_c, far_c);
+            // lengths leave the first stage in world units and re-enter the second in cell units
+            near_w = __fmul_rn(near_c, G.cell);
+            far_w = __fmul_rn(far_c, G.cell);
         }
+        if (near_w < 0.f && G.skip_missed) {  // no occupied block met: the ray is not sampled
+            active = false;
+            return;
+        }
+        const float ray_near = __fmul_rn(near_w, G.inv_cell);
+        ray_far = __fmul_rn(far_w, G.inv_cell);
+        cell2grid = (float)(1.0 / (double)G.grid2cell);
+        cell_step = sample_cell_step(ray_near, ray_far, G.max_samples);
+        grid_step = cell_step * G.grid2cell;
+        tt = seg_near = ray_near;
     }
-    return true;
-}
+
+    // The interval [t0c, t1c] (cell units), the active block found at its start and that block's
+    // index; false when the ray is finished.
+    __device__ __forceinline__ bool next(const RayGrid& G, const float* o_c, const float* d, float& t0c, float& t1c,
+                                         int* blk, int& gi) {
+        while (active && tt < ray_far) {
+            float p[3];
+            ray_at(o_c, d, tt, p);
+            blk[0] = (int)floorf(p[0] * cell2grid);  // as block_active places it
+            blk[1] = (int)floorf(p[1] * cell2grid);
+            blk[2] = (int)floorf(p[2] * cell2grid);
+            gi = lookup(G.table, blk[0], blk[1], blk[2], 0);
+            if (gi < 0) {
+                tt += grid_step;
+            } else {
+                t0c = seg_near;
+                tt += cell_step;
+                t1c = seg_near = tt;
+                return true;
+            }
+        }
+        active = false;
+        return false;
+    }
+};
 
 template <bool ALIGNED>
 __global__ void __launch_bounds__(128) render_rays_forward_kernel(RayGrid G, const float* __restrict__ ray_o_world,
@@ -174,33 +196,43 @@ __global__ void __launch_bounds__(128) render_rays_forward_kernel(RayGrid G, con
                                                                   const float* __restrict__ beta_ptr,
                                                                   float* __restrict__ out, int64_t n) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const float o_w[3] = {ray_o_world[3 * i], ray_o_world[3 * i + 1], ray_o_world[3 * i + 2]};
-    const float o_c[3] = {ray_o_cell[3 * i], ray_o_cell[3 * i + 1], ray_o_cell[3 * i + 2]};
-    const float d[3] = {ray_d[3 * i], ray_d[3 * i + 1], ray_d[3 * i + 2]};
+    const bool live = i < n;  // whole warps stay together for the round votes below
+    const int64_t r3 = live ? 3 * i : 0;
+    const float o_w[3] = {ray_o_world[r3], ray_o_world[r3 + 1], ray_o_world[r3 + 2]};
+    const float o_c[3] = {ray_o_cell[r3], ray_o_cell[r3 + 1], ray_o_cell[r3 + 2]};
+    const float d[3] = {ray_d[r3], ray_d[r3 + 1], ray_d[r3 + 2]};
     const float beta = beta_ptr[0];
     const float alpha = __frcp_rn(beta);
     float acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};  // rgb, depth, normal, weight, eikonal L1, L2
-    float depth_tau = 0.f, count = 0.f, near_w, far_w;
-    march_ray<false>(G, o_c, d, near_w, far_w, [&](float t0c, float t1c, const int* blk, int gi) {
-        Sample s;
-        eval_sample<ALIGNED>(G, o_w, d, t0c, t1c, blk, gi, beta, alpha, s);
-        const float tau = s.sigma * s.dt;
-        const float w = expf(-depth_tau) * -expm1f(-tau);
-        depth_tau += tau;
-        acc[0] += w * s.rgb[0];
-        acc[1] += w * s.rgb[1];
-        acc[2] += w * s.rgb[2];
-        acc[3] += w * s.t_mid;
-        acc[4] += w * s.nrm[0];
-        acc[5] += w * s.nrm[1];
-        acc[6] += w * s.nrm[2];
-        acc[7] += w;
-        const float r = s.gnorm - 1.f;
-        acc[8] += fabsf(r);
-        acc[9] += r * r;
-        count += 1.f;
-    });
+    float depth_tau = 0.f, count = 0.f, near_w = 0.f, far_w = 0.f;
+    RayMarcher m;
+    m.start<false>(G, o_c, d, live, near_w, far_w);
+    for (;;) {
+        float t0c, t1c;
+        int blk[3], gi;
+        const bool have = m.next(G, o_c, d, t0c, t1c, blk, gi);
+        if (!__any_sync(0xffffffffu, have)) break;
+        if (have) {
+            Sample s;
+            eval_sample<ALIGNED>(G, o_w, d, t0c, t1c, blk, gi, beta, alpha, s);
+            const float tau = s.sigma * s.dt;
+            const float w = expf(-depth_tau) * -expm1f(-tau);
+            depth_tau += tau;
+            acc[0] += w * s.rgb[0];
+            acc[1] += w * s.rgb[1];
+            acc[2] += w * s.rgb[2];
+            acc[3] += w * s.t_mid;
+            acc[4] += w * s.nrm[0];
+            acc[5] += w * s.nrm[1];
+            acc[6] += w * s.nrm[2];
+            acc[7] += w;
+            const float r = s.gnorm - 1.f;
+            acc[8] += fabsf(r);
+            acc[9] += r * r;
+            count += 1.f;
+        }
+    }
+    if (!live) return;
     float* row = out + i * kRayOut;
 #pragma unroll
     for (int k = 0; k < 10; ++k) row[k] = acc[k];
@@ -220,68 +252,74 @@ __global__ void __launch_bounds__(128) render_rays_backward_kernel(RayGrid G, co
                                                                    float* __restrict__ grad_emb,
                                                                    float* __restrict__ grad_beta, int64_t n) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    float gbeta = 0.f;
-    if (i < n) {
-        const float o_w[3] = {ray_o_world[3 * i], ray_o_world[3 * i + 1], ray_o_world[3 * i + 2]};
-        const float o_c[3] = {ray_o_cell[3 * i], ray_o_cell[3 * i + 1], ray_o_cell[3 * i + 2]};
-        const float d[3] = {ray_d[3 * i], ray_d[3 * i + 1], ray_d[3 * i + 2]};
-        const float beta = beta_ptr[0];
-        const float alpha = __frcp_rn(beta);
-        float go[10];
+    const bool live = i < n;
+    const int64_t r3 = live ? 3 * i : 0, r16 = live ? i * kRayOut : 0;
+    const float o_w[3] = {ray_o_world[r3], ray_o_world[r3 + 1], ray_o_world[r3 + 2]};
+    const float o_c[3] = {ray_o_cell[r3], ray_o_cell[r3 + 1], ray_o_cell[r3 + 2]};
+    const float d[3] = {ray_d[r3], ray_d[r3 + 1], ray_d[r3 + 2]};
+    const float beta = beta_ptr[0];
+    const float alpha = __frcp_rn(beta);
+    float go[10];
 #pragma unroll
-        for (int k = 0; k < 10; ++k) go[k] = grad_out[i * kRayOut + k];
-        // sum over the ray of (d loss / d w_k) * w_k, from the forward outputs
-        float total = 0.f;
+    for (int k = 0; k < 10; ++k) go[k] = grad_out[r16 + k];
+    // sum over the ray of (d loss / d w_k) * w_k, from the forward outputs
+    float total = 0.f;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) total += go[k] * out[i * kRayOut + k];
-        float depth_tau = 0.f, prefix = 0.f;
-        float near_w = out[i * kRayOut + 11], far_w = out[i * kRayOut + 12];
-        march_ray<true>(G, o_c, d, near_w, far_w, [&](float t0c, float t1c, const int* blk, int gi) {
-            Sample s;
-            eval_sample<ALIGNED>(G, o_w, d, t0c, t1c, blk, gi, beta, alpha, s);
-            const float tau = s.sigma * s.dt;
-            const float T = expf(-depth_tau);
-            const float w = T * -expm1f(-tau);
-            depth_tau += tau;
-            const float gw = go[0] * s.rgb[0] + go[1] * s.rgb[1] + go[2] * s.rgb[2] + go[3] * s.t_mid +
-                             go[4] * s.nrm[0] + go[5] * s.nrm[1] + go[6] * s.nrm[2] + go[7];
-            prefix += gw * w;
-            // d loss / d sigma_j = dt_j * (g_j * (T_j - w_j) - sum_{k>j} g_k w_k)
-            const float dsigma = s.dt * (gw * (T - w) - (total - prefix)) * s.hit;
-            // density(sdf, beta) = alpha * h, h = 0.5 + 0.5 * sign * expm1(-|sdf| / beta)
-            const float a = fabsf(s.sdf);
-            const float sgn = s.sdf > 0.f ? 1.f : (s.sdf < 0.f ? -1.f : 0.f);
-            const float ex = expf(-a / beta);
-            const float h = 0.5f + 0.5f * sgn * expm1f(-a / beta);
-            gbeta += dsigma * (-h * alpha * alpha + alpha * 0.5f * sgn * ex * a * alpha * alpha);
-            if (!s.ok) return;
-            const float dsdf = dsigma * (-0.5f * alpha * alpha * ex * sgn * sgn);
-            // d loss / d (world gradient of the signed distance): through the rendered normal and
-            // through the two eikonal sums
-            float dn[3] = {w * go[4], w * go[5], w * go[6]}, dg[3];
-            if (s.gnorm > 1e-12f) {
-                const float nd = s.nrm[0] * dn[0] + s.nrm[1] * dn[1] + s.nrm[2] * dn[2];
-                const float r = s.gnorm - 1.f;
-                const float eik = go[8] * (r > 0.f ? 1.f : (r < 0.f ? -1.f : 0.f)) + go[9] * 2.f * r;
+    for (int k = 0; k < 8; ++k) total += go[k] * out[r16 + k];
+    float depth_tau = 0.f, prefix = 0.f, gbeta = 0.f;
+    float near_w = out[r16 + 11], far_w = out[r16 + 12];
+    RayMarcher m;
+    m.start<true>(G, o_c, d, live, near_w, far_w);
+    for (;;) {
+        float t0c, t1c;
+        int blk[3], gi;
+        const bool have = m.next(G, o_c, d, t0c, t1c, blk, gi);
+        if (!__any_sync(0xffffffffu, have)) break;
+        if (!have) continue;
+        Sample s;
+        eval_sample<ALIGNED>(G, o_w, d, t0c, t1c, blk, gi, beta, alpha, s);
+        const float tau = s.sigma * s.dt;
+        const float T = expf(-depth_tau);
+        const float w = T * -expm1f(-tau);
+        depth_tau += tau;
+        const float gw = go[0] * s.rgb[0] + go[1] * s.rgb[1] + go[2] * s.rgb[2] + go[3] * s.t_mid +
+                         go[4] * s.nrm[0] + go[5] * s.nrm[1] + go[6] * s.nrm[2] + go[7];
+        prefix += gw * w;
+        // d loss / d sigma_j = dt_j * (g_j * (T_j - w_j) - sum_{k>j} g_k w_k)
+        const float dsigma = s.dt * (gw * (T - w) - (total - prefix)) * s.hit;
+        // density(sdf, beta) = alpha * h, h = 0.5 + 0.5 * sign * expm1(-|sdf| / beta)
+        const float a = fabsf(s.sdf);
+        const float sgn = s.sdf > 0.f ? 1.f : (s.sdf < 0.f ? -1.f : 0.f);
+        const float ex = expf(-a / beta);
+        const float h = 0.5f + 0.5f * sgn * expm1f(-a / beta);
+        gbeta += dsigma * (-h * alpha * alpha + alpha * 0.5f * sgn * ex * a * alpha * alpha);
+        if (!s.ok) continue;
+        const float dsdf = dsigma * (-0.5f * alpha * alpha * ex * sgn * sgn);
+        // d loss / d (world gradient of the signed distance): through the rendered normal and
+        // through the two eikonal sums
+        float dn[3] = {w * go[4], w * go[5], w * go[6]}, dg[3];
+        if (s.gnorm > 1e-12f) {
+            const float nd = s.nrm[0] * dn[0] + s.nrm[1] * dn[1] + s.nrm[2] * dn[2];
+            const float r = s.gnorm - 1.f;
+            const float eik = go[8] * (r > 0.f ? 1.f : (r < 0.f ? -1.f : 0.f)) + go[9] * 2.f * r;
 #pragma unroll
-                for (int k = 0; k < 3; ++k) dg[k] = (dn[k] - s.nrm[k] * nd) / s.gnorm + eik * s.nrm[k];
-            } else {
+            for (int k = 0; k < 3; ++k) dg[k] = (dn[k] - s.nrm[k] * nd) / s.gnorm + eik * s.nrm[k];
+        } else {
 #pragma unroll
-                for (int k = 0; k < 3; ++k) dg[k] = dn[k] / 1e-12f;
-            }
+            for (int k = 0; k < 3; ++k) dg[k] = dn[k] / 1e-12f;
+        }
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const float wc = s.aw.weight(c);
-                float wg[3];
-                s.aw.grad(c, wg);
-                float v[4];
-                v[0] = wc * dsdf + (wg[0] * dg[0] + wg[1] * dg[1] + wg[2] * dg[2]) * G.inv_cell;
-                v[1] = wc * w * go[0];
-                v[2] = wc * w * go[1];
-                v[3] = wc * w * go[2];
-                add_row4<ALIGNED>(grad_emb + s.base[c], v);
-            }
-        });
+        for (int c = 0; c < 8; ++c) {
+            const float wc = s.aw.weight(c);
+            float wg[3];
+            s.aw.grad(c, wg);
+            float v[4];
+            v[0] = wc * dsdf + (wg[0] * dg[0] + wg[1] * dg[1] + wg[2] * dg[2]) * G.inv_cell;
+            v[1] = wc * w * go[0];
+            v[2] = wc * w * go[1];
+            v[3] = wc * w * go[2];
+            add_row4<ALIGNED>(grad_emb + s.base[c], v);
+        }
     }
     // one atomic per warp for the density parameter
 #pragma unroll
