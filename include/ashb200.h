@@ -424,6 +424,12 @@ int ashb_route_by_owner(const int32_t* keys, int64_t n, int key_dim, int world, 
 
 /* ---------------------------------------------------------------- runtime knobs */
 
+/* Selects how ashb_query_backward_forward and ashb_grid_query_backward scatter the embedding
+ * gradient: 0 = one vector reduction per lane and corner (default), 1 = lanes of a warp that add to
+ * the same row slice are combined first and one of them issues the reduction.  Same sums up to
+ * floating-point order. */
+int ashb_set_scatter_aggregation(int enable);
+
 /* Selects the kernel behind ashb_map_find for key_dim <= 3: 0 = one thread per key (default),
  * 1 = eight lanes per key reading a whole 128-byte line of slots per step.  Same results. */
 int ashb_set_find_cooperative(int enable);

@@ -224,3 +224,31 @@ def test_zero_grad_rows_clears_exactly_what_a_batch_added():
     grid.zero_grad_rows_(x[2500:])
     assert torch.count_nonzero(grid.embeddings.grad) == 0
     grid.grad_mode = "dense"
+
+
+@pytest.mark.parametrize("D", [1, 4, 12, 16])
+def test_warp_aggregated_scatter_gives_the_same_gradient(D):
+    """The opt-in backward that combines, inside a warp, the contributions of queries sharing a
+    corner row (one reduction per distinct row slice) sums to the same gradient as the default."""
+    import __ash
+
+    grid, x = _make("unbounded", 4, D, seed=77)
+    # many queries in few cells: every warp holds duplicates
+    x = torch.cat([x[:64].repeat(40, 1) + 1e-3 * torch.rand(2560, 3, device=x.device), x]).contiguous()
+    z = torch.randn(x.shape[0], D, device=x.device)
+    origin, cell_size = grid._cell_frame()
+    args = (grid.engine.backend, z, grid.embeddings.detach(), x, cell_size, origin, grid.grid_dim, grid._neighbor_lut32())
+    _, _, bidx = __ash.grid_query_forward(args[0], args[2], x, cell_size, origin, grid.grid_dim, args[7], "linear")
+    out = {}
+    try:
+        for agg in (False, True):
+            __ash.set_scatter_aggregation(agg)
+            out[agg] = __ash.grid_query_backward(*args, bidx, "linear")
+            only = __ash.grid_query_backward(*args, bidx, "linear", need_grad_x=False)
+            torch.testing.assert_close(only[0], out[agg][0], rtol=1e-4, atol=1e-5 * float(out[agg][0].abs().max()))
+    finally:
+        __ash.set_scatter_aggregation(False)
+    scale = float(out[False][0].abs().max())
+    assert scale > 0
+    torch.testing.assert_close(out[True][0], out[False][0], rtol=1e-4, atol=1e-5 * scale)
+    assert torch.equal(out[True][1], out[False][1])

@@ -75,6 +75,7 @@ _lib.ashb_render_accumulate_forward.argtypes = [_vp, _vp, _int, _vp, _vp, _i64, 
 _lib.ashb_render_accumulate_backward.argtypes = [_vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _vp, _vp]
 _lib.ashb_isosurface_extraction.argtypes = [_vp] * 9 + [_i64, _c.POINTER(_i64), _vp, _f32, _f32, _int, _i64, _i64, _i64, _vp]
 _lib.ashb_set_find_cooperative.argtypes = [_int]
+_lib.ashb_set_scatter_aggregation.argtypes = [_int]
 _RAY_ARGS = [_vp, _int, _vp, _i64, _int, _int, _vp, _c.c_double, _vp, _vp, _vp, _vp, _vp, _vp, _f32, _f32, _i64, _int, _vp]
 _lib.ashb_render_rays_forward.argtypes = _RAY_ARGS + [_vp, _i64, _vp]
 _lib.ashb_render_rays_backward.argtypes = _RAY_ARGS + [_vp, _vp, _vp, _vp, _i64, _vp]
@@ -88,6 +89,13 @@ _INTERP = {"linear": 0, "smooth_step": 1}
 def _check(rc: int):
     if rc != 0:
         raise RuntimeError(f"libashb200: {_lib.ashb_last_error_string().decode()} (status {rc})")
+
+
+def set_scatter_aggregation(enable: bool) -> None:
+    """Process-wide: combine, inside a warp, the gradient contributions of queries that share a
+    corner row before the atomic reduction (helps batches whose neighbours in memory are
+    neighbours in space, such as samples in marching order; costs a little on scattered batches)."""
+    _check(_lib.ashb_set_scatter_aggregation(int(bool(enable))))
 
 
 def set_find_cooperative(enable: bool) -> None:

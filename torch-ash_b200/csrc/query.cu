@@ -248,6 +248,91 @@ __global__ void __launch_bounds__(256, ASHB_BWD_MIN_BLOCKS) query_backward_forwa
     }
 }
 
+// ---- backward with warp-aggregated scatter ----------------------------------------------
+// Lanes of a warp that are about to add to the SAME gradient row slice (queries that share a corner,
+// as consecutive samples along a ray do) are found with a match on the element offset; their
+// contributions are summed with shuffles and the lowest lane issues one vector reduction for all.
+// Every lane of the warp takes part in the match (lanes without a contribution use a key of their
+// own), and the shuffle rounds are bounded by the largest peer group in the warp: none when no
+// two lanes collide.
+template <typename T, int VEC>
+__device__ __forceinline__ void scatter_aggregated(T* grad, int64_t elem_off, const Pack<T, VEC>& g, bool valid) {
+    const int wl = threadIdx.x & 31;
+    const unsigned long long key = valid ? (unsigned long long)elem_off : (0xFFFFFFFF00000000ull | (unsigned)wl);
+    const unsigned peers = __match_any_sync(0xffffffffu, key);
+    const int rounds = __reduce_max_sync(0xffffffffu, __popc(peers));
+    Pack<T, VEC> sum = g;
+    unsigned rest = peers & ~(1u << wl);
+    for (int it = 1; it < rounds; ++it) {
+        const bool take = rest != 0;
+        const int from = take ? __ffs(rest) - 1 : wl;
+        rest &= rest - 1;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            const T v = __shfl_sync(0xffffffffu, g.v[k], from);
+            if (take) sum.v[k] += v;
+        }
+    }
+    if (valid && wl == __ffs(peers) - 1) atomic_add_pack<T, VEC>(grad + elem_off, sum);
+}
+
+template <typename T, int VEC, class Src, bool NEED_GO>
+__global__ void __launch_bounds__(256) query_backward_forward_agg_kernel(
+        const T* __restrict__ z, const T* __restrict__ emb, Src src, T* __restrict__ grad_emb,
+        T* __restrict__ grad_off, T go_scale, int64_t n, int D, int lane_shift, int interp) {
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t q = tid >> lane_shift;
+    const int lanes = 1 << lane_shift;
+    const int lane = (int)(tid & (lanes - 1));
+    const int ch = lane * VEC;
+    const bool live = q < n;
+    int64_t base[8];
+    float off[3] = {0.f, 0.f, 0.f};
+#pragma unroll
+    for (int c = 0; c < 8; ++c) base[c] = 0;
+    const bool ok = live && src.resolve(q, lane, D, base, off);
+    const bool valid = ok && ch < D;
+    AxisWeights<T> aw;
+    aw.init(interp, off);
+    Pack<T, VEC> zv;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) zv.v[k] = 0;
+    if (valid) zv = load_pack<T, VEC>(z + q * D + ch);
+    Pack<T, VEC> e[8];
+    if (NEED_GO && valid) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) e[c] = load_pack<T, VEC>(emb + base[c] + ch);
+    }
+    T go[3] = {0, 0, 0};
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        const T w = aw.weight(c);
+        Pack<T, VEC> g;
+        T dot = 0;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            g.v[k] = w * zv.v[k];
+            if (NEED_GO && valid) dot += e[c].v[k] * zv.v[k];
+        }
+        scatter_aggregated<T, VEC>(grad_emb, base[c] + ch, g, valid);
+        if (NEED_GO) {
+            T wg[3];
+            aw.grad(c, wg);
+            go[0] += dot * wg[0];
+            go[1] += dot * wg[1];
+            go[2] += dot * wg[2];
+        }
+    }
+    if (!NEED_GO) return;
+#pragma unroll
+    for (int d = 0; d < 3; ++d) go[d] = group_sum(go[d], lanes);
+    if (live && lane == 0) {
+        grad_off[3 * q] = go[0] * go_scale;
+        grad_off[3 * q + 1] = go[1] * go_scale;
+        grad_off[3 * q + 2] = go[2] * go_scale;
+    }
+}
+
 // ---- clear the rows a batch touches ---------------------------------------------------
 // Writes zeros to the 8 corner rows of every query: the sparse counterpart of zero-filling a
 // table-sized gradient buffer between steps when gradients are accumulated in place.
@@ -311,6 +396,9 @@ __global__ void __launch_bounds__(256, ASHB_BWD_MIN_BLOCKS) query_backward_backw
 }
 
 // ---- host-side dispatch ---------------------------------------------------------------
+// Process-wide: scatter the first-order embedding gradient with warp aggregation of duplicate rows.
+static bool g_scatter_aggregation = false;
+
 struct Shape {
     int vec;         // channels per lane
     int lane_shift;  // log2(lanes per query)
@@ -384,6 +472,22 @@ static int backward_forward_impl(int interp, const void* z, const void* emb, con
     const Shape sh = pick_shape(D, sizeof(T), ptrs, 3);
     const int64_t threads = n << sh.lane_shift;
     const unsigned grid = (unsigned)((threads + 255) / 256);
+    if (g_scatter_aggregation && grad_emb != nullptr) {
+        ASHB_VEC_SWITCH(T, sh,
+                        if (grad_off != nullptr) {
+                            query_backward_forward_agg_kernel<T, VEC, Src, true><<<grid, 256, 0, st>>>(
+                                    static_cast<const T*>(z), static_cast<const T*>(emb), src,
+                                    static_cast<T*>(grad_emb), static_cast<T*>(grad_off), (T)go_scale, n, (int)D,
+                                    sh.lane_shift, interp);
+                        } else {
+                            query_backward_forward_agg_kernel<T, VEC, Src, false><<<grid, 256, 0, st>>>(
+                                    static_cast<const T*>(z), static_cast<const T*>(emb), src,
+                                    static_cast<T*>(grad_emb), nullptr, (T)go_scale, n, (int)D, sh.lane_shift,
+                                    interp);
+                        });
+        ASHB_LAUNCH_CHECK();
+        return ASHB_OK;
+    }
     ASHB_VEC_SWITCH(T, sh,
                     if (grad_emb == nullptr) {
                         query_backward_forward_kernel<T, VEC, Src, true, false><<<grid, 256, 0, st>>>(
@@ -653,6 +757,11 @@ int ashb_grid_zero_rows(ashb_map* m, int dtype, void* grad_embeddings, const flo
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return dtype == ASHB_F32 ? zero_rows_impl<float>(src, grad_embeddings, n, D, st)
                              : zero_rows_impl<double>(src, grad_embeddings, n, D, st);
+}
+
+int ashb_set_scatter_aggregation(int enable) {
+    g_scatter_aggregation = enable != 0;
+    return ASHB_OK;
 }
 
 }  // extern "C"
