@@ -306,15 +306,13 @@ def measure_tsdf(ash, bw, device, peak, n_frames=100, H=480, W=640):
             "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4)}}
 
 
-def measure_bounded(ash, bw, device, peak):
-    """Bounded grid at resolution 512 (64 blocks x grid_dim 8 per axis), sdf + rgb channels: 7x7x7
-    Gaussian filter through the neighbourhood convolution, ray near/far and ray sampling for 8192
-    rays with up to 128 samples each."""
+def build_bounded_grid(ash, bw, device):
+    """Bounded grid at resolution 512 over the synthetic scene's surfaces (spheres + box planes),
+    scaled from the 10 m box into [-1, 1]^3; 4 channels (signed distance + colour)."""
     G, S, D = 8, 64, 4
     grid = ash.BoundedSparseDenseGrid(3, 80_000, D, grid_dim=G, sparse_grid_dim=S, device=device)
     scene = bw.Scene(device)
     g = torch.Generator(device=device).manual_seed(bw.SEED + 5)
-    # surface points of the scene's spheres and box planes, scaled from the 10 m box into [-1, 1]^3
     n_s = 400_000
     pick = torch.randint(scene.centres.shape[0], (n_s,), generator=g, device=device)
     dirs = torch.nn.functional.normalize(torch.randn(n_s, 3, generator=g, device=device), dim=-1)
@@ -327,6 +325,61 @@ def measure_bounded(ash, bw, device, peak):
     grid.spatial_init_(pts, dilation=0)
     with torch.no_grad():
         grid.embeddings.normal_(0, 0.1)
+    return grid, g
+
+
+def measure_rays_sharded(ash, bw, device, dist, rank, world):
+    """Config-5 training step on every rank: replicated bounded grid (rank 0's structure and values
+    broadcast to all), 8192 rays per rank, fused render + loss + backward, then the dense all-reduce
+    of the embedding gradient; time = max over ranks."""
+    from ash.distributed import allreduce_gradients, broadcast_state
+    from ash.render import SDFToDensity, render_rays
+
+    grid, _ = build_bounded_grid(ash, bw, device)
+    grid.gaussian_filter_(7, 1.0)
+    broadcast_state(grid, src=0)
+    to_sigma = SDFToDensity(min_beta=grid.cell_size, init_beta=2 * grid.cell_size).to(device)
+    g = torch.Generator(device=device).manual_seed(bw.SEED + 50 + rank)
+    n_rays = 8192
+    o = (torch.rand(n_rays, 3, generator=g, device=device) - 0.5) * 1.2
+    d = torch.nn.functional.normalize((torch.rand(n_rays, 3, generator=g, device=device) - 0.5) * 1.2 - o, dim=-1)
+
+    def step(sync):
+        grid.embeddings.grad = None
+        beta = to_sigma.min_beta + to_sigma.beta.abs()
+        res = render_rays(grid, o, d, 0.06, 2.5, 128, beta, "linear", skip_rays_without_hit=True)
+        loss = (res["rgb"] - 0.5).abs().mean() + 0.1 * (res["depth"] - 0.3).abs().mean() \
+            + 0.1 * res["eikonal_l2"].sum() / res["n_samples"].sum().clamp_min(1)
+        loss.backward()
+        if sync:
+            allreduce_gradients(grid)
+
+    out = {}
+    for sync in (False, True):
+        for _ in range(3):
+            step(sync)
+        dist.barrier()
+        torch.cuda.synchronize()
+        reps = 10
+        ms = event_ms(lambda: [step(sync) for _ in range(reps)]) / reps
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out[sync] = float(t.item())
+    grid.embeddings.grad = None
+    return {"what": "fused render + loss + backward on 8192 rays per rank over a replicated bounded grid "
+                    "(structure and values broadcast from rank 0), with and without the dense gradient all-reduce",
+            "rays": n_rays * world, "active_blocks": grid.engine.size(),
+            "gradient_bytes": grid.embeddings.numel() * 4,
+            "ms_without_allreduce": round(out[False], 3), "ms_with_allreduce": round(out[True], 3),
+            "rays_per_s": round(n_rays * world / (out[True] * 1e-3) / 1e6, 3), "unit": "M rays/s"}
+
+
+def measure_bounded(ash, bw, device, peak):
+    """Bounded grid at resolution 512 (64 blocks x grid_dim 8 per axis), sdf + rgb channels: 7x7x7
+    Gaussian filter through the neighbourhood convolution, ray near/far and ray sampling for 8192
+    rays with up to 128 samples each."""
+    G, S, D = 8, 64, 4
+    grid, g = build_bounded_grid(ash, bw, device)
     n_blocks = grid.engine.size()
     for _ in range(2):
         grid.gaussian_filter_(7, 1.0)
@@ -470,6 +523,12 @@ def main():
 
     peak, peak_kind = measured_peak_gbs()
     grid, blocks = build_grid(ash, bw, device, N_BLOCKS)
+    if dist is not None:
+        # replicas must agree on which row is which block before their gradients can be summed
+        from ash.distributed import broadcast_state
+
+        broadcast_state(grid, src=0)
+        grid.construct_grid_neighbor_lut_(radius=1, bidirectional=False)
     emb = grid.embeddings.detach()
     hm, lut32 = grid.engine.backend, grid._neighbor_lut32()
     origin, cell_size = grid._cell_frame()
@@ -768,6 +827,12 @@ def main():
                 "insert_M_per_s": round(HASH_KEYS / (float(t[0]) * 1e-3) / 1e6, 1), "hit_rate": round(hit, 4),
                 "live_keys": total}
         del pm, uniq, q
+        torch.cuda.empty_cache()
+
+    if dist is not None and not args.no_extras:
+        sharded = measure_rays_sharded(ash, bw, device, dist, rank, world)
+        if rank == 0:
+            line["volume_rendering_train_step_sharded"] = sharded
         torch.cuda.empty_cache()
 
     if rank == 0 and not args.no_extras:

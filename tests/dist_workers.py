@@ -79,16 +79,38 @@ def replicated_grid_worker(rank, world, port, backend, use_cuda):
         import ash
         from ash.distributed import allreduce_gradients, shard_rows
 
-        torch.manual_seed(0)  # identical replicas
+        from ash.distributed import broadcast_state
+
+        torch.manual_seed(0)  # the same random draws on every rank
         G, D = 4, 3
         grid = ash.SparseDenseGrid(3, 64, D, G, device)
         r = torch.arange(-1, 2, dtype=torch.int32)
         blocks = torch.stack(torch.meshgrid(r, r, r, indexing="ij"), -1).view(-1, 3)
-        grid.engine.insert_keys(blocks.to(device))
-        idx, ok = grid.engine.find(blocks.to(device))
+        # every rank inserts the blocks in an order of its own, so the key -> index maps differ ...
+        order = torch.roll(torch.arange(27), 5 * rank) if rank % 2 == 0 else torch.arange(26, -1, -1)
+        for chunk in order.split(7):
+            grid.engine.insert_keys(blocks[chunk].to(device))
         vals = torch.randn(27, G**3, D)
+        idx, ok = grid.engine.find(blocks.to(device))
         with torch.no_grad():
-            grid.embeddings[idx] = vals.to(device)
+            grid.embeddings[idx] = vals.to(device) + rank  # ... and so do the values
+        gathered = [torch.empty_like(idx) for _ in range(world)]
+        dist.all_gather(gathered, idx)
+        assert not all(torch.equal(g, gathered[0]) for g in gathered), "replicas already aligned: test is vacuous"
+        # ... until rank 0's structure and values are broadcast
+        broadcast_state(grid, src=0)
+        idx, ok = grid.engine.find(blocks.to(device))
+        assert bool(ok.all()) and grid.engine.size() == 27
+        dist.all_gather(gathered, idx)
+        assert all(torch.equal(g, gathered[0]) for g in gathered)
+        emb = [torch.empty_like(grid.embeddings) for _ in range(world)]
+        dist.all_gather(emb, grid.embeddings.detach())
+        assert all(torch.equal(e, emb[0]) for e in emb)
+        torch.testing.assert_close(grid.embeddings.detach()[idx].cpu(), vals)
+        # the replica keeps working as a map: a new key takes a free index on every rank
+        grid.engine.insert_keys(torch.tensor([[7, 7, 7]], dtype=torch.int32, device=device))
+        assert grid.engine.size() == 28
+        grid.engine.erase(torch.tensor([[7, 7, 7]], dtype=torch.int32, device=device))
         x = (torch.rand(600, 3) * 3 - 1.2) * G
         y, _ = grid(shard_rows(x, rank, world).to(device), "linear")
         (y * y).sum().backward()

@@ -73,10 +73,14 @@ class ASHEngine(nn.Module):
         assert self._heap.numel() == self.capacity
         active_keys = self._keys[:n]
         self._key_check(active_keys)
-        self.backend.load_states(
-            {"active_keys": active_keys, "active_indices": self._indices[:n], "heap": self._heap}
-        )
+        # Loading replaces the contents: an engine that already holds keys (a replica being
+        # re-aligned with another rank) must not keep its old key -> index pairs.  clear() resets the
+        # aliased free-index stack, so the loaded one is set aside first.
+        heap = self._heap.clone()
+        self.backend.clear()
+        self.backend.load_states({"active_keys": active_keys, "active_indices": self._indices[:n], "heap": heap})
         self._size_bound = n
+        self._erased_bound = 0
 
     # ------------------------------------------------------------------ checks
     def _key_check(self, keys: torch.Tensor) -> None:

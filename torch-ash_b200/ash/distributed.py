@@ -12,7 +12,11 @@ backend works, which is how the host logic is tested with gloo on CPU):
   it.  A global index is ``local_index * P + owner``.
 * Replicated grid, sharded queries -- every rank holds the whole grid and queries its own shard
   of the batch with no communication; ``allreduce_gradients`` sums the embedding gradients
-  afterwards (dense all-reduce: right for tables up to a few GB).
+  afterwards (dense all-reduce: right for tables up to a few GB).  Row ``i`` of the embeddings
+  must mean the same block on every rank for that sum to be meaningful, and the index a key
+  receives depends on the order in which concurrent inserts win, which differs from process to
+  process: ``broadcast_state`` copies one rank's key -> index map, free-index stack and
+  parameters to all others (call it after every change of the block structure).
 """
 from typing import Optional, Tuple
 
@@ -144,6 +148,26 @@ def shard_rows(x: torch.Tensor, rank: Optional[int] = None, world: Optional[int]
     n = x.shape[0]
     lo, hi = n * rank // world, n * (rank + 1) // world
     return x[lo:hi]
+
+
+@torch.no_grad()
+def broadcast_state(module: torch.nn.Module, src: int = 0, group=None) -> None:
+    """Make this rank's ``module`` (a grid, ``HashMap``, ``HashEmbedding`` ... built with the same
+    sizes on every rank) identical to rank ``src``'s: the engines' active keys with THEIR indices,
+    the free-index stacks, and every parameter and buffer.  Goes through the reference's own
+    checkpoint format (``state_dict`` / ``load_state_dict``, ash/core.py:92-135), one broadcast
+    per tensor; lookup tables derived from the block structure are dropped and rebuilt on demand."""
+    state = module.state_dict()  # views of this module's own tensors
+    for name in sorted(state.keys()):
+        dist.broadcast(state[name], src=src, group=group)
+    module.load_state_dict(state)  # rebuilds every engine's table from the received pairs
+    for m in module.modules():
+        if hasattr(m, "lut_grid_nb2grid_idx"):
+            m.grid_coords = None
+            m.lut_grid_nb2grid_idx = None
+        if hasattr(m, "_lut32"):
+            m._lut32 = None
+            m._lut32_source = None
 
 
 def allreduce_gradients(module: torch.nn.Module, group=None) -> None:
