@@ -116,7 +116,7 @@ def test_ray_marched_training_step():
         assert torch.isfinite(grid.embeddings.grad).all() and grid.embeddings.grad[..., 0].abs().sum() > 0
         assert grid.embeddings.grad[..., 1:4].abs().sum() > 0 and to_sigma.beta.grad is not None
         opt.step()
-        losses.append(float(loss))
+        losses.append(float(loss.detach()))
         if step == 0:
             # rays aimed at the sphere see it at about the right depth (|o| - radius = 0.3)
             seen = opacity.view(-1) > 0.9
