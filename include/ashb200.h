@@ -268,6 +268,34 @@ int ashb_isosurface_extraction(const float* sdfs, const float* weights, const in
                                int grid_dim, int64_t cells_per_grid, int64_t n_emb, int64_t num_grids,
                                void* stream);
 
+/* ---------------------------------------------------------------- iso-surface triangles
+ * Replaces marching_cubes_table_idx_kernel / _vertex_kernel / _triangle_kernel + marching_cubes
+ * (ash/src/grid.cu:607-946), float32, tables as for ashb_isosurface_extraction.  A cube sits at
+ * every cell of a listed block whose 8 corners (cell and +x/+y/+z neighbours) exist and reach
+ * weight_thr; corner c is inside when sdf - iso_value < 0.
+ *   _count classifies every cube into codes uint8 [num_grids * cells_per_grid], requests the
+ *          vertices of cut edges in edge_vertex int32 [n_emb * cells_per_grid * 3] (both are
+ *          caller-allocated scratch, passed on to _fill) and returns the number of distinct
+ *          vertices and of triangles (HOST).  Synchronises `stream`.
+ *   _fill  writes vertices float32 [n_vertices][3] (cell units, the reference's interpolation)
+ *          and triangles int32 [n_triangles][3] (vertex ids).  No host synchronisation.
+ * counters_dev: 16 bytes of device scratch.  The triangulation table is this library's own, not
+ * the reference's (ash/src/mc_macros.h): how ambiguous patterns are split, the order of a
+ * triangle's corners (normals point towards increasing sdf) and the output order differ. */
+int ashb_marching_cubes_count(const float* sdfs, const float* weights, const int64_t* grid_indices,
+                              const int64_t* lut_grid_nb2grid_idx, const int64_t* lut_cell_nb2cell_idx,
+                              const int64_t* lut_cell_nb2grid_nb, uint8_t* codes, int32_t* edge_vertex,
+                              void* counters_dev, float iso_value, float weight_thr, int64_t cells_per_grid,
+                              int64_t n_emb, int64_t num_grids, int64_t* n_vertices, int64_t* n_triangles,
+                              void* stream);
+int ashb_marching_cubes_fill(const float* sdfs, const int64_t* grid_indices, const int32_t* grid_coords_table,
+                             const int64_t* lut_grid_nb2grid_idx, const int32_t* cell_coords_table,
+                             const int64_t* lut_cell_nb2cell_idx, const int64_t* lut_cell_nb2grid_nb,
+                             const uint8_t* codes, int32_t* edge_vertex, void* counters_dev, float* vertices,
+                             int64_t n_vertices, int32_t* triangles, int64_t n_triangles, float iso_value,
+                             int grid_dim, int64_t cells_per_grid, int64_t n_emb, int64_t num_grids,
+                             void* stream);
+
 /* ---------------------------------------------------------------- ray sampler
  * All lengths in cell units; rays float32 [n][3]; bbox float32 [3] each; the map
  * must have key_dim 3 (ash/src/sampler.cu:89-99).  Positions are fma(t, d, o) in

@@ -539,6 +539,104 @@ int64_t oracle_isosurface_extraction_f32(
     return count;
 }
 
+/* ash/src/grid.cu:607-946 (marching_cubes: table-index, vertex and triangle kernels), in the
+ * same three stages.  A cube sits at every cell of an active block whose own weight and the
+ * weights of its 8 corners (the cell and its +x/+y/+z neighbours through the lookup tables)
+ * reach weight_thr and whose neighbour blocks all exist (:640-668); corner c is inside when
+ * sdf - iso_value < 0.  Every cut edge of a valid cube gets ONE vertex, owned by the cell at
+ * the edge's lower corner and placed by linear interpolation (:744-770); triangles index
+ * those vertices (:800-836).
+ *
+ * The reference's triangulation table (ash/src/mc_macros.h) is not reproduced: corner / edge
+ * numbering and the table come from the generated mc_tables.h, so WHICH vertices a cube
+ * connects in ambiguous patterns, the order of a triangle's corners, and the output order are
+ * parity-unpinned against the reference; vertex positions follow the reference's formula.
+ *
+ * scratch: int32[num_embeddings * cells_per_grid * 3], vertex index per (cell, direction).
+ * vertices / triangles == NULL counts only.  Returns 0, fills *n_vertices, *n_triangles. */
+#include "mc_tables.h"
+
+int64_t oracle_marching_cubes_f32(
+        const float* sdfs, const float* weights, const int64_t* grid_indices,
+        const int32_t* grid_coords_table, const int64_t* g2g, const int32_t* cell_coords_table,
+        const int64_t* c2c, const int64_t* c2g, int32_t* scratch, int64_t num_embeddings,
+        float* vertices, int32_t* triangles, float iso_value, float weight_thr, int grid_dim,
+        int64_t cells_per_grid, int64_t num_grids, int64_t* n_vertices, int64_t* n_triangles) {
+    const int64_t n_cells = num_grids * cells_per_grid;
+    uint8_t* codes = (uint8_t*)calloc((size_t)(n_cells > 0 ? n_cells : 1), 1);
+    for (int64_t i = 0; i < num_embeddings * cells_per_grid * 3; ++i) scratch[i] = -2;  /* no vertex wanted */
+    /* stage 1: corner pattern of every valid cube; request the vertices of its cut edges */
+    for (int64_t i = 0; i < n_cells; ++i) {
+        const int64_t grid_idx = grid_indices[i / cells_per_grid];
+        const int64_t cell_idx = i % cells_per_grid;
+        int code = 0, valid = 1;
+        int64_t corner_cell[8];
+        for (int c = 0; c < 8 && valid; ++c) {
+            const int64_t g = g2g[grid_idx * 8 + c2g[cell_idx * 8 + c]];
+            if (g == -1) { valid = 0; break; }
+            corner_cell[c] = g * cells_per_grid + c2c[cell_idx * 8 + c];
+            if (weights[corner_cell[c]] < weight_thr) { valid = 0; break; }
+            code |= ((sdfs[corner_cell[c]] - iso_value) < 0) << c;
+        }
+        if (!valid || code == 0 || code == 255) continue;
+        codes[i] = (uint8_t)code;
+        for (int e = 0; e < 12; ++e) {
+            if (!(kMcEdgeMask[code] & (1 << e))) continue;
+            const int d = e / 4, j = e % 4;
+            const int lower = ((j & 1) << ((d + 1) % 3)) | ((j >> 1) << ((d + 2) % 3));
+            scratch[corner_cell[lower] * 3 + d] = -1;  /* wanted */
+        }
+    }
+    /* stage 2: one vertex per wanted edge, in the scan order of the owning cells */
+    int64_t nv = 0;
+    for (int64_t i = 0; i < n_cells; ++i) {
+        const int64_t grid_idx = grid_indices[i / cells_per_grid];
+        const int64_t cell_idx = i % cells_per_grid;
+        const int64_t self = grid_idx * cells_per_grid + cell_idx;
+        for (int d = 0; d < 3; ++d) {
+            if (scratch[self * 3 + d] != -1) continue;
+            const int64_t g = g2g[grid_idx * 8 + c2g[cell_idx * 8 + (1 << d)]];
+            const int64_t nb = g * cells_per_grid + c2c[cell_idx * 8 + (1 << d)];
+            const float self_isodiff = sdfs[self] - iso_value;
+            const float nb_isodiff = sdfs[nb] - iso_value;
+            if (vertices) {
+                const float ratio = self_isodiff / (self_isodiff - nb_isodiff);
+                for (int k = 0; k < 3; ++k) {
+                    const int self_pos = grid_coords_table[grid_idx * 3 + k] * grid_dim +
+                                         cell_coords_table[cell_idx * 3 + k];
+                    vertices[nv * 3 + k] = (float)self_pos + ratio * (k == d ? 1.0f : 0.0f);
+                }
+            }
+            scratch[self * 3 + d] = (int32_t)nv++;
+        }
+    }
+    /* stage 3: triangles of every valid cube */
+    int64_t nt = 0;
+    for (int64_t i = 0; i < n_cells; ++i) {
+        const int code = codes[i];
+        if (!code) continue;
+        const int64_t grid_idx = grid_indices[i / cells_per_grid];
+        const int64_t cell_idx = i % cells_per_grid;
+        for (int t = 0; t < kMcTriCount[code]; ++t) {
+            if (triangles) {
+                for (int v = 0; v < 3; ++v) {
+                    const int e = kMcTris[code][3 * t + v];
+                    const int d = e / 4, j = e % 4;
+                    const int lower = ((j & 1) << ((d + 1) % 3)) | ((j >> 1) << ((d + 2) % 3));
+                    const int64_t g = g2g[grid_idx * 8 + c2g[cell_idx * 8 + lower]];
+                    const int64_t owner = g * cells_per_grid + c2c[cell_idx * 8 + lower];
+                    triangles[nt * 3 + v] = scratch[owner * 3 + d];
+                }
+            }
+            ++nt;
+        }
+    }
+    free(codes);
+    *n_vertices = nv;
+    *n_triangles = nt;
+    return 0;
+}
+
 int oracle_num_threads(void) {
     int n = 1;
 #ifdef _OPENMP

@@ -126,3 +126,10 @@ def isosurface_extraction(sdfs, weights, grid_indices, grid_coords_table, g2g, c
     return torch.from_numpy(
         _o.isosurface_extraction(_np(sdfs), _np(weights), _np(grid_indices), _np(grid_coords_table), _np(g2g),
                                  _np(cell_coords_table), _np(c2c), _np(c2g), grid_dim, iso_value, weight_thr))
+
+
+def marching_cubes(sdfs, weights, grid_indices, grid_coords_table, g2g, cell_coords_table, c2c, c2g, grid_dim,
+                   iso_value, weight_thr):
+    tris, verts = _o.marching_cubes(_np(sdfs), _np(weights), _np(grid_indices), _np(grid_coords_table), _np(g2g),
+                                    _np(cell_coords_table), _np(c2c), _np(c2g), grid_dim, iso_value, weight_thr)
+    return torch.from_numpy(tris), torch.from_numpy(verts)

@@ -177,5 +177,3 @@ def test_isosurface_vertices_vs_oracle_and_sphere(G):
     order_r, order_g = np.lexsort(np.round(ref, 3).T[::-1]), np.lexsort(np.round(got, 3).T[::-1])
     np.testing.assert_allclose(got[order_g], ref[order_r], rtol=0, atol=2e-3)
     assert grid.marching_cubes(sdf + 10.0, w, vertices_only=True) is None
-    with pytest.raises(NotImplementedError):
-        grid.marching_cubes(sdf, w)

@@ -76,6 +76,8 @@ _lib.ashb_render_accumulate_backward.argtypes = [_vp, _vp, _vp, _vp, _i64, _i64,
 _lib.ashb_isosurface_extraction.argtypes = [_vp] * 9 + [_i64, _c.POINTER(_i64), _vp, _f32, _f32, _int, _i64, _i64, _i64, _vp]
 _lib.ashb_set_find_cooperative.argtypes = [_int]
 _lib.ashb_set_scatter_aggregation.argtypes = [_int]
+_lib.ashb_marching_cubes_count.argtypes = [_vp] * 9 + [_f32, _f32, _i64, _i64, _i64, _c.POINTER(_i64), _c.POINTER(_i64), _vp]
+_lib.ashb_marching_cubes_fill.argtypes = [_vp] * 11 + [_i64, _vp, _i64, _f32, _int, _i64, _i64, _i64, _vp]
 _RAY_ARGS = [_vp, _int, _vp, _i64, _int, _int, _vp, _c.c_double, _vp, _vp, _vp, _vp, _vp, _vp, _f32, _f32, _i64, _int, _vp]
 _lib.ashb_render_rays_forward.argtypes = _RAY_ARGS + [_vp, _i64, _vp]
 _lib.ashb_render_rays_backward.argtypes = _RAY_ARGS + [_vp, _vp, _vp, _vp, _i64, _vp]
@@ -803,6 +805,44 @@ def isosurface_extraction(sdfs, weights, grid_indices, grid_coords_table, lut_gr
     if n.value:
         run(positions, n.value)
     return positions
+
+
+def marching_cubes(sdfs, weights, grid_indices, grid_coords_table, lut_grid_nb2grid_idx, cell_coords_table,
+                   lut_cell_nb2cell_idx, lut_cell_nb2grid_nb, grid_dim, iso_value, weight_thr):
+    """ash/src/grid.cu:840-946: (triangles (T, 3) int32 vertex ids, vertices (V, 3) float32 in cell
+    units).  Triangle normals point towards increasing sdf; the triangulation table is this
+    library's own."""
+    sd = _cuda(sdfs, "sdfs", torch.float32)
+    n_emb = lut_grid_nb2grid_idx.shape[0]
+    sd = sd.reshape(n_emb, -1)
+    wt = _cuda(weights, "weights", torch.float32).reshape(sd.shape)
+    dev = sd.device
+    gi = _cuda(grid_indices, "grid_indices", torch.int64).view(-1)
+    gct = _cuda(grid_coords_table, "grid_coords_table", torch.int32)
+    cct = _cuda(cell_coords_table, "cell_coords_table", torch.int32)
+    g2g = _cuda(lut_grid_nb2grid_idx, "lut_grid_nb2grid_idx", torch.int64)
+    c2c = _cuda(lut_cell_nb2cell_idx, "lut_cell_nb2cell_idx", torch.int64)
+    c2g = _cuda(lut_cell_nb2grid_nb, "lut_cell_nb2grid_nb", torch.int64)
+    cells = sd.shape[1]
+    if gct.shape != (n_emb, 3) or cct.shape != (cells, 3) or c2c.shape != (cells, 8) or c2g.shape != (cells, 8):
+        raise RuntimeError("marching_cubes: table shapes do not match sdfs")
+    codes = torch.empty(max(gi.shape[0] * cells, 1), dtype=torch.uint8, device=dev)
+    edge_vertex = torch.empty(n_emb * cells * 3, dtype=torch.int32, device=dev)
+    counters = torch.empty(2, dtype=torch.int64, device=dev)
+    nv, nt = _i64(), _i64()
+    with torch.cuda.device(dev):
+        _check(_lib.ashb_marching_cubes_count(
+            sd.data_ptr(), wt.data_ptr(), gi.data_ptr(), g2g.data_ptr(), c2c.data_ptr(), c2g.data_ptr(), codes.data_ptr(),
+            edge_vertex.data_ptr(), counters.data_ptr(), float(iso_value), float(weight_thr), cells, n_emb, gi.shape[0],
+            _c.byref(nv), _c.byref(nt), _stream(dev)))
+        vertices = torch.empty((nv.value, 3), dtype=torch.float32, device=dev)
+        triangles = torch.empty((nt.value, 3), dtype=torch.int32, device=dev)
+        _check(_lib.ashb_marching_cubes_fill(
+            sd.data_ptr(), gi.data_ptr(), gct.data_ptr(), g2g.data_ptr(), cct.data_ptr(), c2c.data_ptr(), c2g.data_ptr(),
+            codes.data_ptr(), edge_vertex.data_ptr(), counters.data_ptr(), vertices.data_ptr() if nv.value else None,
+            nv.value, triangles.data_ptr() if nt.value else None, nt.value, float(iso_value), int(grid_dim), cells, n_emb,
+            gi.shape[0], _stream(dev)))
+    return triangles, vertices
 
 
 def grid_zero_rows(hashmap, grad_embeddings, x, cell_size, origin, grid_dim, nb_lut, block_idx=None):

@@ -383,31 +383,35 @@ class SparseDenseGrid(ASHModule):
         """Iso-surface of ``tsdfs`` (num_embeddings, G^3[, 1]) where ``weights`` >= ``weight_thr``.
 
         ``vertices_only=True``: the zero crossings along the +x/+y/+z cell edges
-        (ash/src/grid.cu:453-604), returned as a dict of world ``positions`` (n, 3) and, if the
-        callbacks are given, ``colors`` / ``normals`` -- the reference wraps the same arrays in an
-        Open3D point cloud (ash/grid.py:657-682), a package this library does not depend on.
-        Returns None when the surface is empty.  Triangle extraction (ash/src/grid.cu:607-946) is
-        outside the hot path this library implements.
+        (ash/src/grid.cu:453-604), returned as a dict of world ``positions`` (n, 3).
+        ``vertices_only=False``: the triangle mesh (ash/src/grid.cu:607-946): a dict of world
+        ``positions`` (V, 3) and ``triangles`` (T, 3) int32 vertex ids, normals (right-hand rule)
+        towards increasing tsdf.  If the callbacks are given, ``colors`` / ``normals`` are evaluated
+        at the positions.  The reference wraps the same arrays in Open3D geometry
+        (ash/grid.py:657-712), a package this library does not depend on; ``ash.mesh.write_ply``
+        stores the dict in a file.  Returns None when the surface is empty.
         """
-        if not vertices_only:
-            raise NotImplementedError(
-                "triangle extraction (ash/src/grid.cu:607-946) is outside the hot path this library "
-                "implements; use vertices_only=True for the iso-surface points")
         if self.grid_coords is None or self.lut_grid_nb2grid_idx is None:
             self.construct_grid_neighbor_lut_(radius=1, bidirectional=False)
         _, grid_indices = self.engine.items()
-        vertices = backend.isosurface_extraction(
-            tsdfs, weights, grid_indices, self.grid_coords, self.lut_grid_nb2grid_idx, self.cell_coords,
-            self.lut_cell_nb2cell_idx, self.lut_cell_nb2grid_nb, self.grid_dim, iso_value, weight_thr)
+        tables = (grid_indices, self.grid_coords, self.lut_grid_nb2grid_idx, self.cell_coords,
+                  self.lut_cell_nb2cell_idx, self.lut_cell_nb2grid_nb, self.grid_dim, iso_value, weight_thr)
+        triangles = None
+        if vertices_only:
+            vertices = backend.isosurface_extraction(tsdfs, weights, *tables)
+        else:
+            triangles, vertices = backend.marching_cubes(tsdfs, weights, *tables)
         if len(vertices) == 0:
             return None
         positions = self.transform_cell_to_world(vertices)
-        cloud = {"positions": positions}
+        surface = {"positions": positions}
+        if triangles is not None:
+            surface["triangles"] = triangles
         if color_fn is not None:
-            cloud["colors"] = color_fn(positions)
+            surface["colors"] = color_fn(positions)
         if normal_fn is not None:
-            cloud["normals"] = normal_fn(positions)
-        return cloud
+            surface["normals"] = normal_fn(positions)
+        return surface
 
 
 class UnBoundedSparseDenseGrid(SparseDenseGrid):
