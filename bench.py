@@ -296,6 +296,16 @@ def measure_tsdf(ash, bw, device, peak, n_frames=100, H=480, W=640):
     ms = event_ms(run)
     blocks = grid.engine.size()
     status = grid.engine.backend.status()
+    # triangle mesh of the fused volume (sdf = channel 0, weight = channel 4)
+    with torch.no_grad():
+        sdf = grid.embeddings[..., 0].contiguous()
+        wgt = grid.embeddings[..., 4].contiguous()
+    grid.marching_cubes(sdf, wgt, vertices_only=False, weight_thr=1.0)
+    mesh = {}
+    mesh_ms = event_ms(lambda: mesh.update(grid.marching_cubes(sdf, wgt, vertices_only=False, weight_thr=1.0) or {}))
+    n_tri = int(mesh["triangles"].shape[0]) if "triangles" in mesh else 0
+    n_vert = int(mesh["positions"].shape[0]) if "positions" in mesh else 0
+    mesh_bytes = blocks * G**3 * (8 * 8 + 1 + 12 + 12 + 1) + n_vert * 12 + n_tri * 12
     updated_cells = int(counter.item()) * G**3
     bytes_ = n_frames * H * W * 16 + updated_cells * 40
     gbs = bytes_ / (ms * 1e-3) / 1e9
@@ -303,6 +313,12 @@ def measure_tsdf(ash, bw, device, peak, n_frames=100, H=480, W=640):
             "frames_per_s": round(n_frames / (ms * 1e-3), 1), "ms_per_frame": round(ms / n_frames, 4),
             "active_blocks": blocks, "status": status, "cell_updates_per_s": round(updated_cells / (ms * 1e-3) / 1e9, 3),
             "cell_updates_unit": "G cells/s",
+            "marching_cubes": {"ms": round(mesh_ms, 3), "vertices": n_vert, "triangles": n_tri,
+                               "cubes_per_s": round(blocks * G**3 / (mesh_ms * 1e-3) / 1e9, 3), "cubes_unit": "G cubes/s",
+                               "achieved_gbs": round(mesh_bytes / (mesh_ms * 1e-3) / 1e9, 1),
+                               "note": "classify + vertices + triangles (3 launches, one host read) over every cell of "
+                                       "the active blocks; bytes = 8 corner (sdf, weight) pairs + code + edge slots per "
+                                       "cube + outputs"},
             "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4)}}
 
 
