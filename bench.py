@@ -367,11 +367,13 @@ def measure_rays_sharded(ash, bw, device, dist, rank, world):
         loss = (res["rgb"] - 0.5).abs().mean() + 0.1 * (res["depth"] - 0.3).abs().mean() \
             + 0.1 * res["eikonal_l2"].sum() / res["n_samples"].sum().clamp_min(1)
         loss.backward()
-        if sync:
+        if sync == "dense":
+            allreduce_gradients(grid, sparse_below=0.0)
+        elif sync == "block_sparse":
             allreduce_gradients(grid)
 
     out = {}
-    for sync in (False, True):
+    for sync in (None, "dense", "block_sparse"):
         for _ in range(3):
             step(sync)
         dist.barrier()
@@ -383,11 +385,13 @@ def measure_rays_sharded(ash, bw, device, dist, rank, world):
         out[sync] = float(t.item())
     grid.embeddings.grad = None
     return {"what": "fused render + loss + backward on 8192 rays per rank over a replicated bounded grid "
-                    "(structure and values broadcast from rank 0), with and without the dense gradient all-reduce",
+                    "(structure and values broadcast from rank 0): without gradient exchange, with the dense all-reduce of "
+                    "the whole table, and with the block-sparse exchange of the touched blocks",
             "rays": n_rays * world, "active_blocks": grid.engine.size(),
             "gradient_bytes": grid.embeddings.numel() * 4,
-            "ms_without_allreduce": round(out[False], 3), "ms_with_allreduce": round(out[True], 3),
-            "rays_per_s": round(n_rays * world / (out[True] * 1e-3) / 1e6, 3), "unit": "M rays/s"}
+            "ms_without_allreduce": round(out[None], 3), "ms_with_dense_allreduce": round(out["dense"], 3),
+            "ms_with_block_sparse_allreduce": round(out["block_sparse"], 3),
+            "rays_per_s": round(n_rays * world / (out["block_sparse"] * 1e-3) / 1e6, 3), "unit": "M rays/s"}
 
 
 def measure_bounded(ash, bw, device, peak):

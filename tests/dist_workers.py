@@ -114,8 +114,15 @@ def replicated_grid_worker(rank, world, port, backend, use_cuda):
         x = (torch.rand(600, 3) * 3 - 1.2) * G
         y, _ = grid(shard_rows(x, rank, world).to(device), "linear")
         (y * y).sum().backward()
-        allreduce_gradients(grid)
+        local = grid.embeddings.grad.clone()
+        allreduce_gradients(grid)                       # block-sparse exchange (few blocks touched)
         summed = grid.embeddings.grad[idx].cpu()
+        dense = local.clone()
+        dist.all_reduce(dense)                          # the plain dense sum of the same gradients
+        torch.testing.assert_close(grid.embeddings.grad, dense, rtol=0, atol=0)
+        grid.embeddings.grad.copy_(local)
+        allreduce_gradients(grid, sparse_below=0.0)     # forced dense path
+        torch.testing.assert_close(grid.embeddings.grad, dense, rtol=0, atol=0)
         # one process, whole batch
         grid.embeddings.grad = None
         y_all, _ = grid(x.to(device), "linear")

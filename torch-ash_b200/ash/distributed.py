@@ -170,8 +170,30 @@ def broadcast_state(module: torch.nn.Module, src: int = 0, group=None) -> None:
             m._lut32_source = None
 
 
-def allreduce_gradients(module: torch.nn.Module, group=None) -> None:
-    """Sum the gradients of a replicated grid's parameters over the ranks (dense all-reduce)."""
+def allreduce_gradients(module: torch.nn.Module, group=None, sparse_below: float = 0.5) -> None:
+    """Sum the gradients of a replicated module's parameters over the ranks.
+
+    A gradient with the shape of a grid's embeddings, ``(num_embeddings, cells, dim)``, is usually
+    zero outside the blocks the step's samples fell in.  Its rows are then exchanged block-sparsely:
+    the per-block "any entry nonzero" flags are combined over the ranks (a few KB), every rank
+    packs the flagged blocks -- the same ones, in the same order, on all ranks -- into one buffer,
+    that buffer is all-reduced and unpacked.  When more than ``sparse_below`` of the blocks are
+    flagged (or the tensor is not 3-D) the whole gradient is all-reduced instead.
+    """
     for p in module.parameters():
-        if p.grad is not None:
-            dist.all_reduce(p.grad, group=group)
+        g = p.grad
+        if g is None:
+            continue
+        if g.dim() != 3 or sparse_below <= 0 or not g.is_contiguous():
+            dist.all_reduce(g, group=group)
+            continue
+        blocks = g.view(g.shape[0], -1)
+        touched = (blocks != 0).any(dim=1).to(torch.int32)
+        dist.all_reduce(touched, op=dist.ReduceOp.MAX, group=group)
+        rows = touched.nonzero().view(-1)
+        if rows.numel() > sparse_below * g.shape[0]:
+            dist.all_reduce(g, group=group)
+        elif rows.numel() > 0:
+            packed = blocks[rows]
+            dist.all_reduce(packed, group=group)
+            blocks[rows] = packed
