@@ -53,50 +53,63 @@ def measured_peak_gbs():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons of the job's GPUs with nvidia-smi.  The process is
+    started ahead of time (it needs a few hundred ms to come up); only samples stamped between
+    ``begin()`` and ``stop()`` -- the loaded region -- are kept."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index):
-        self.index, self.proc = index, None
-
-    def __enter__(self):
+    def __init__(self, indices):
+        self.proc, self.t0 = None, None
+        self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if not indices:
+            return
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                ["nvidia-smi", "-i", ",".join(str(i) for i in indices), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
-        return self
 
-    def __exit__(self, *exc):
-        self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+    def begin(self):
+        self.t0 = time.time()
+
+    def stop(self):
         if self.proc is None:
             return
-        time.sleep(0.15)
+        t1 = time.time()
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
         except Exception:
             self.proc.kill()
             return
+        import datetime
+
         sm, mx, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for line in out.strip().splitlines():
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 6:
+            if len(parts) < 7:
                 continue
             try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
+                stamp = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                clock, clock_max = float(parts[1]), float(parts[2])
             except ValueError:
                 continue
-            for name, flag in zip(names, parts[2:6]):
+            if self.t0 is not None and not (self.t0 - 0.02 <= stamp <= t1 + 0.02):
+                continue
+            sm.append(clock)
+            mx.append(clock_max)
+            for name, flag in zip(names, parts[3:7]):
                 if flag.lower().startswith("active"):
                     reasons.add(name)
         if sm:
-            self.result = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons)}
+            self.result = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                           "samples": len(sm)}
 
 
 def event_ms(fn, stream=None):
@@ -583,16 +596,20 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # rank 0 samples the clocks of every GPU of the job from before the warm-up until the kernel-level
+    # loops below are done (all of it under load); the timed region lies inside
+    clocks = ClockSampler(list(range(world)) if rank == 0 else [])
+    time.sleep(0.5 if rank == 0 else 0.0)
     for i in range(args.warmup):
         step(i, False)
     barrier()
-    with ClockSampler(local_rank) as clocks:
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for i in range(args.steps):
-            step(i, True)
-        end.record()
-        barrier()
+    clocks.begin()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(args.steps):
+        step(i, True)
+    end.record()
+    barrier()
     total_ms = start.elapsed_time(end)
     for ev in marks:
         fwd_ms.append(ev[0].elapsed_time(ev[1]))
@@ -625,6 +642,7 @@ def main():
             bwdbwd_ms.append(t)
     del ggx
     barrier()
+    clocks.stop()
 
     # gradient synchronisation cost (not on the timed data path): one dense all-reduce
     allreduce_ms = None
