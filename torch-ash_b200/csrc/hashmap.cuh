@@ -50,9 +50,25 @@ struct Table16 {
         return Entry{(int)r.x, (int)r.y, (int)r.z, 0, (int)r.w};
     }
     // Read-only probe (find / items): table is constant for the launch.
-    __device__ __forceinline__ Entry read_const(uint32_t s) const { return unpack(__ldg(slots + s)); }
+    // The loads name a 64-byte L2 fetch size: a probe needs one 16-byte slot of a random line, and
+    // the default fill of the whole 128-byte line from DRAM is wasted traffic (measured: find
+    // 1.216 -> 1.185 ms at 50M keys).
+    __device__ __forceinline__ Entry read_const(uint32_t s) const {
+        uint4 u;
+        asm volatile("ld.global.nc.L2::64B.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w)
+                     : "l"(slots + s));
+        return unpack(u);
+    }
     // Probe inside a mutating launch: read at L2, where the atomics resolve.
-    __device__ __forceinline__ Entry read_fresh(uint32_t s) const { return unpack(__ldcg(slots + s)); }
+    __device__ __forceinline__ Entry read_fresh(uint32_t s) const {
+        uint4 u;
+        asm volatile("ld.global.cg.L2::64B.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w)
+                     : "l"(slots + s)
+                     : "memory");
+        return unpack(u);
+    }
     // Try to turn the free slot `s` (last seen as `expected`) into {key, PENDING}.
     // On failure `observed` holds what is there now.
     __device__ __forceinline__ bool claim(uint32_t s, const Entry& expected, int k0, int k1, int k2,

@@ -48,6 +48,18 @@ __device__ __forceinline__ Pack<T, VEC> load_pack(const T* p) {
     return r;
 }
 
+// Rows of 4 floats per lane are gathered from random lines: naming a 64-byte L2 fetch size keeps
+// the DRAM fill to the half line that holds the 64-byte row (measured: backward 1.54 -> 1.44 ms,
+// forward 0.606 -> 0.591 ms at 4M queries).
+template <>
+__device__ __forceinline__ Pack<float, 4> load_pack<float, 4>(const float* p) {
+    Pack<float, 4> r;
+    asm volatile("ld.global.nc.L2::64B.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3])
+                 : "l"(p));
+    return r;
+}
+
 template <typename T, int VEC>
 __device__ __forceinline__ void store_pack(T* p, const Pack<T, VEC>& r) {
     using V = typename Vec<T, VEC>::type;

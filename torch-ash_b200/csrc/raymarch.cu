@@ -55,8 +55,10 @@ struct Sample {
 template <bool ALIGNED>
 __device__ __forceinline__ void load_row4(const float* p, float* v) {
     if (ALIGNED) {
-        const float4 r = __ldg(reinterpret_cast<const float4*>(p));
-        v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+        // 64-byte L2 fetch size: one 16-byte row slice of a random line is wanted
+        asm volatile("ld.global.nc.L2::64B.v4.f32 {%0,%1,%2,%3}, [%4];"
+                     : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3])
+                     : "l"(p));
     } else {
         v[0] = __ldg(p); v[1] = __ldg(p + 1); v[2] = __ldg(p + 2); v[3] = __ldg(p + 3);
     }
