@@ -52,6 +52,30 @@ __device__ __forceinline__ Pack<T, VEC> load_pack(const T* p) {
 // the DRAM fill to the half line that holds the 64-byte row (measured: backward 1.54 -> 1.44 ms,
 // forward 0.606 -> 0.591 ms at 4M queries).
 template <>
+__device__ __forceinline__ Pack<float, 1> load_pack<float, 1>(const float* p) {
+    Pack<float, 1> r;
+    asm volatile("ld.global.nc.L2::64B.f32 %0, [%1];" : "=f"(r.v[0]) : "l"(p));
+    return r;
+}
+template <>
+__device__ __forceinline__ Pack<float, 2> load_pack<float, 2>(const float* p) {
+    Pack<float, 2> r;
+    asm volatile("ld.global.nc.L2::64B.v2.f32 {%0,%1}, [%2];" : "=f"(r.v[0]), "=f"(r.v[1]) : "l"(p));
+    return r;
+}
+template <>
+__device__ __forceinline__ Pack<double, 1> load_pack<double, 1>(const double* p) {
+    Pack<double, 1> r;
+    asm volatile("ld.global.nc.L2::64B.f64 %0, [%1];" : "=d"(r.v[0]) : "l"(p));
+    return r;
+}
+template <>
+__device__ __forceinline__ Pack<double, 2> load_pack<double, 2>(const double* p) {
+    Pack<double, 2> r;
+    asm volatile("ld.global.nc.L2::64B.v2.f64 {%0,%1}, [%2];" : "=d"(r.v[0]), "=d"(r.v[1]) : "l"(p));
+    return r;
+}
+template <>
 __device__ __forceinline__ Pack<float, 4> load_pack<float, 4>(const float* p) {
     Pack<float, 4> r;
     asm volatile("ld.global.nc.L2::64B.v4.f32 {%0,%1,%2,%3}, [%4];"
@@ -98,6 +122,7 @@ struct QueryLuts {
 // out, its indices are out of range, or any neighbour block is absent: the
 // reference leaves such rows zero (grid.cu:81-83, :109-111, :209-216).
 struct LutSource {
+    static constexpr int kForwardMinBlocks = 1;
     const float* __restrict__ offsets;
     QueryLuts L;
 
@@ -132,7 +157,13 @@ struct LutSource {
 // Positions in.  The split follows the Python layer operation by operation as it
 // evaluates on a CUDA tensor (ash/grid.py:192-197, :756, :846): divisions by the
 // cell size and by G are multiplications by float reciprocals, each rounded.
+// Forward kernel with this source: 6 resident CTAs (<= 40 registers) measured 0.556 ms against
+// 0.591 ms unconstrained (48 registers) and 0.601 ms at 8 CTAs (spills) for 4M queries.
+#ifndef ASHB_FWD_MIN_BLOCKS
+#define ASHB_FWD_MIN_BLOCKS 6
+#endif
 struct FusedSource {
+    static constexpr int kForwardMinBlocks = ASHB_FWD_MIN_BLOCKS;
     Table16 table;
     const float* __restrict__ x;          // (n, 3) world positions
     float org[3];                         // world position of cell (0,0,0)
@@ -168,7 +199,7 @@ __device__ __forceinline__ T group_sum(T v, int lanes) {
 
 // ---- forward -------------------------------------------------------------------
 template <typename T, int VEC, class Src>
-__global__ void __launch_bounds__(256) query_forward_kernel(const T* __restrict__ emb, Src src,
+__global__ void __launch_bounds__(256, Src::kForwardMinBlocks) query_forward_kernel(const T* __restrict__ emb, Src src,
                                                             T* __restrict__ out, int64_t n, int D,
                                                             int lane_shift, int interp) {
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
