@@ -39,9 +39,9 @@ BWDBWD_BYTES = 12 + 4 * EMB_DIM + 12 + 32 * EMB_DIM + 32 * EMB_DIM + 4 * EMB_DIM
 FIND_BYTES = 12 + 16 + 8 + 1                              # key, one slot, index, mask
 # dram__bytes_read.sum + dram__bytes_write.sum per unit from the ncu captures summarised under profiles/
 # (taken on a reduced case whose tables are still many times L2; traffic per unit carries over)
-BWD_TRAFFIC_PER_QUERY = 1432 + 469
-FWD_TRAFFIC_PER_QUERY = 762 + 64
-FIND_TRAFFIC_PER_QUERY = 124 + 9
+BWD_TRAFFIC_PER_QUERY = 1192 + 469
+FWD_TRAFFIC_PER_QUERY = 523 + 65
+FIND_TRAFFIC_PER_QUERY = 73 + 9
 
 
 def measured_peak_gbs():
@@ -574,6 +574,16 @@ def main():
     zero_rows = float(((y0 == 0).all(dim=1) & m0).float().mean())
     del y0, m0
 
+    # ceiling for scattered accesses: 16-byte reads at random 64-byte-aligned places of the table
+    random_reads = {}
+    n_reads = 50_000_000 if not reduced else 5_000_000
+    for fetch in (64, 128):
+        for _ in range(2):
+            __ash.measure_random_reads(emb, n_reads, fetch, seed=7)
+        ms = statistics.mean(event_ms(lambda: __ash.measure_random_reads(emb, n_reads, fetch, seed=11 + k))
+                             for k in range(5))
+        random_reads[fetch] = n_reads / (ms * 1e-3) / 1e9
+
     fwd_ms, bwd_ms, bwd_persist_ms = [], [], []
     marks = []  # (before fwd, between, after bwd) events of every timed step; read after the region
 
@@ -796,6 +806,15 @@ def main():
             "note": "as e2e, with grid.grad_mode = 'in_place' and grid.zero_grad_rows_(x) as the step's zero_grad "
                     "(rank-local time)"}
         line["zero_row_fraction"] = round(zero_rows, 4)
+        line["random_access"] = {
+            "what": "16-byte reads at random 64-byte-aligned places of the 16.4 GB table, one per thread, L2 fetch size "
+                    "64 or 128 bytes: the rate at which this GPU's memory serves scattered accesses",
+            "G_reads_per_s_fetch64": round(random_reads[64], 2), "G_reads_per_s_fetch128": round(random_reads[128], 2),
+            "forward_frac": round(N_QUERIES * 5 / (f_ms * 1e-3) / 1e9 / random_reads[128], 4),
+            "backward_frac": round(N_QUERIES * 13 / (bp_ms * 1e-3) / 1e9 / random_reads[128], 4),
+            "note": "scattered accesses per query: forward 1 slot + 4 x-adjacent row pairs (128 B each) = 5; backward "
+                    "1 slot + 4 row pairs + 4 gradient row pairs read and written back = 13; frac = accesses/s over "
+                    "the measured random-read rate"}
         if allreduce_ms is not None:
             line["grad_allreduce_ms"] = round(allreduce_ms, 3)
 
@@ -827,6 +846,7 @@ def main():
             "hit_rate": round(hit, 4),
             "roofline": {"bound": "hbm", "achieved": round(fa, 1), "peak": peak, "unit": "GB/s", "frac": round(fa / peak, 4),
                          "peak_kind": peak_kind, "traffic": HASH_KEYS * FIND_TRAFFIC_PER_QUERY},
+            "frac_of_random_read_rate": round(HASH_KEYS / (t_find * 1e-3) / 1e9 / random_reads[64], 4),
             "insert_M_per_s": round(HASH_KEYS / (t_ins * 1e-3) / 1e6, 1),
             "erase_M_per_s": round(HASH_KEYS / 8 / (t_er * 1e-3) / 1e6, 1), "items_ms": round(t_items, 3),
         }

@@ -462,6 +462,14 @@ int ashb_set_scatter_aggregation(int enable);
  * 1 = eight lanes per key reading a whole 128-byte line of slots per step.  Same results. */
 int ashb_set_find_cooperative(int enable);
 
+/* Measurement aid (no counterpart in the reference): launches n_reads threads that each read one
+ * 16-byte word at a pseudo-random 64-byte-aligned place of `buffer` (device, 64-byte aligned,
+ * `bytes` long, any content), naming an L2 fetch size of fetch_bytes (64 or 128).  Timed by the
+ * caller, the reads per second it reaches are the ceiling for the probe and gather kernels, whose
+ * accesses are as scattered.  sink_dev: 8 bytes of device scratch. */
+int ashb_measure_random_reads(const void* buffer, int64_t bytes, int64_t n_reads, int fetch_bytes, uint32_t seed,
+                              void* sink_dev, void* stream);
+
 /* cudaLimitMaxL2FetchGranularity of the current context (32, 64 or 128 bytes); a
  * performance hint that lasts as long as the process.  No counterpart in the reference. */
 int ashb_set_l2_fetch_granularity(int bytes);

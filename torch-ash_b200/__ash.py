@@ -76,6 +76,7 @@ _lib.ashb_render_accumulate_backward.argtypes = [_vp, _vp, _vp, _vp, _i64, _i64,
 _lib.ashb_isosurface_extraction.argtypes = [_vp] * 9 + [_i64, _c.POINTER(_i64), _vp, _f32, _f32, _int, _i64, _i64, _i64, _vp]
 _lib.ashb_set_find_cooperative.argtypes = [_int]
 _lib.ashb_set_scatter_aggregation.argtypes = [_int]
+_lib.ashb_measure_random_reads.argtypes = [_vp, _i64, _i64, _int, _c.c_uint32, _vp, _vp]
 _lib.ashb_marching_cubes_count.argtypes = [_vp] * 9 + [_f32, _f32, _i64, _i64, _i64, _c.POINTER(_i64), _c.POINTER(_i64), _vp]
 _lib.ashb_marching_cubes_fill.argtypes = [_vp] * 11 + [_i64, _vp, _i64, _f32, _int, _i64, _i64, _i64, _vp]
 _RAY_ARGS = [_vp, _int, _vp, _i64, _int, _int, _vp, _c.c_double, _vp, _vp, _vp, _vp, _vp, _vp, _f32, _f32, _i64, _int, _vp]
@@ -91,6 +92,16 @@ _INTERP = {"linear": 0, "smooth_step": 1}
 def _check(rc: int):
     if rc != 0:
         raise RuntimeError(f"libashb200: {_lib.ashb_last_error_string().decode()} (status {rc})")
+
+
+def measure_random_reads(buffer: torch.Tensor, n_reads: int, fetch_bytes: int = 64, seed: int = 1) -> None:
+    """Launch ``n_reads`` scattered 16-byte reads over ``buffer`` (a large CUDA tensor); time it from
+    outside.  The reads per second reached are the ceiling for the probe / gather kernels."""
+    buf = _cuda(buffer, "buffer")
+    sink = torch.zeros(1, dtype=torch.int64, device=buf.device)
+    with torch.cuda.device(buf.device):
+        _check(_lib.ashb_measure_random_reads(buf.data_ptr(), buf.numel() * buf.element_size(), int(n_reads),
+                                              int(fetch_bytes), int(seed) & 0xFFFFFFFF, sink.data_ptr(), _stream(buf.device)))
 
 
 def set_scatter_aggregation(enable: bool) -> None:

@@ -31,9 +31,48 @@ int sm_count() {
     return cached;
 }
 
+// Measurement aid: every thread reads one 16-byte word at a pseudo-random 64-byte-aligned place
+// of a large buffer.  The rate it reaches (reads per second) is the ceiling for the library's
+// probe and gather kernels, whose DRAM accesses are just as scattered: at that rate the memory
+// is busy opening rows, whatever the number of bytes each access returns.
+template <bool FETCH64>
+__global__ void __launch_bounds__(256) random_read_kernel(const uint4* __restrict__ buf, uint64_t granules, int64_t n,
+                                                          uint32_t seed, unsigned long long* __restrict__ sink) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint64_t h = ((uint64_t)fmix32((uint32_t)i ^ seed) << 32) | fmix32((uint32_t)(i >> 32) + 0x9E3779B9u * (uint32_t)i + seed);
+    const uint4* p = buf + (h % granules) * 4;
+    uint4 v;
+    if (FETCH64)
+        asm volatile("ld.global.nc.L2::64B.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    else
+        asm volatile("ld.global.nc.L2::128B.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    if ((v.x ^ v.y ^ v.z ^ v.w) == 0x5A17C0DEu) atomicAdd(sink, 1ull);  // keeps the load alive
+}
+
 }  // namespace ashb
 
 extern "C" {
+
+int ashb_measure_random_reads(const void* buffer, int64_t bytes, int64_t n_reads, int fetch_bytes, uint32_t seed,
+                              void* sink_dev, void* stream) {
+    ASHB_REQUIRE(buffer != nullptr && sink_dev != nullptr, "null buffer");
+    ASHB_REQUIRE(bytes >= 64 && n_reads >= 0, "bad sizes");
+    ASHB_REQUIRE(fetch_bytes == 64 || fetch_bytes == 128, "fetch size must be 64 or 128");
+    ASHB_REQUIRE(((uintptr_t)buffer & 63) == 0, "buffer must be 64-byte aligned");
+    if (n_reads == 0) return ASHB_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const unsigned grid = (unsigned)((n_reads + 255) / 256);
+    const uint64_t granules = (uint64_t)bytes / 64;
+    if (fetch_bytes == 64)
+        ashb::random_read_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint4*>(buffer), granules, n_reads, seed,
+                                                             static_cast<unsigned long long*>(sink_dev));
+    else
+        ashb::random_read_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint4*>(buffer), granules, n_reads, seed,
+                                                              static_cast<unsigned long long*>(sink_dev));
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
 
 const char* ashb_last_error_string(void) { return ashb::g_error; }
 
