@@ -137,3 +137,11 @@ def test_ply_round_trip(tmp_path):
     area = 0.5 * np.linalg.norm(np.cross(tri[:, 1] - tri[:, 0], tri[:, 2] - tri[:, 0]), axis=1).sum()
     assert len(tri) == 2 * 15 * 15 and abs(area - (15 * cell) ** 2) < 1e-4
     assert (np.cross(tri[:, 1] - tri[:, 0], tri[:, 2] - tri[:, 0])[:, 2] > 0).all()   # normals along +z
+
+
+def test_fuser_pruning_on_the_gpu():
+    import ash
+    import prune_scenario
+
+    prune_scenario.check_mesh_pruning(ash, DEV)
+    prune_scenario.check_weight_pruning(ash, DEV)

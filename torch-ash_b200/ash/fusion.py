@@ -77,3 +77,54 @@ class TSDFFusion:
     def fuse_dataset(self, frames) -> None:
         for datum in frames:
             self.fuse_frame(datum)
+
+    @torch.no_grad()
+    def prune_by_weight_(self, grid_mean_weight_thr: float = 1) -> int:
+        """Erase the blocks whose mean fusion weight stays below the threshold and clear their rows
+        (demo/rgbd_fusion.py:112-128); returns how many were erased."""
+        grid_coords, _, grid_indices, _ = self.grid.items()
+        if grid_indices.numel() == 0:
+            return 0
+        rows = grid_indices.view(-1)
+        weak = self.grid.embeddings[rows, :, 4].mean(dim=1) < grid_mean_weight_thr
+        n = int(weak.sum())
+        if n:
+            self.grid.engine.erase(grid_coords.view(-1, 3)[weak].contiguous())
+            self.grid.embeddings[rows[weak]] = 0
+        self.grid.construct_grid_neighbor_lut_(radius=1, bidirectional=False)
+        return n
+
+    @torch.no_grad()
+    def prune_by_mesh_connected_components_(self, ratio_to_largest_component: float = 0.5) -> int:
+        """Keep only the blocks around the large connected pieces of the fused surface
+        (demo/rgbd_fusion.py:130-197): mesh the volume, drop the components with fewer triangles
+        than ``ratio_to_largest_component`` of the largest, re-derive the blocks within one block of
+        the remaining vertices, erase every other block.  Returns how many blocks were erased."""
+        from .hashmap import HashSet
+        from .mesh import connected_triangle_components
+
+        g = self.grid
+        sdf = g.embeddings[..., 0].contiguous()
+        weight = g.embeddings[..., 4].contiguous()
+        mesh = g.marching_cubes(sdf, weight, vertices_only=False, iso_value=0.0, weight_thr=1)
+        if mesh is None:
+            return 0
+        triangles, positions = mesh["triangles"], mesh["positions"]
+        component, sizes = connected_triangle_components(triangles, positions.shape[0])
+        keep_component = sizes > ratio_to_largest_component * sizes.max()
+        kept_vertices = torch.unique(triangles[keep_component[component]].long().reshape(-1))
+        xyz = positions[kept_vertices]
+
+        around = UnBoundedSparseDenseGrid(3, g.num_embeddings, 1, g.grid_dim, cell_size=g.cell_size, device=g.device) \
+            if not isinstance(g, BoundedSparseDenseGrid) else \
+            BoundedSparseDenseGrid(3, g.num_embeddings, 1, g.grid_dim, g.sparse_grid_dim, g.bbox_min, g.bbox_max, g.device)
+        around.spatial_init_(xyz, dilation=1, bidirectional=True)
+        all_coords = g.items()[0].view(-1, 3)
+        kept_coords = around.items()[0].view(-1, 3)
+        kept = HashSet(key_dim=3, capacity=int(len(all_coords) * 1.2) + 1, device=g.device)
+        kept.insert(kept_coords)
+        to_prune = all_coords[~kept.find(all_coords)].contiguous()
+        if len(to_prune):
+            g.engine.erase(to_prune)
+        g.construct_grid_neighbor_lut_(radius=1, bidirectional=False)
+        return int(len(to_prune))

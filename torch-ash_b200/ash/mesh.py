@@ -90,3 +90,24 @@ def read_ply(path: str) -> Dict[str, np.ndarray]:
             face = np.frombuffer(f.read(n_face * 13), dtype=[("n", "u1"), ("v", "<i4", (3,))])
             out["triangles"] = face["v"].copy()
     return out
+
+
+def connected_triangle_components(triangles: torch.Tensor, n_vertices: int):
+    """Connected components of a triangle mesh (triangles joined through shared vertices):
+    ``(component of every triangle (T,) int64 in [0, n), triangles per component (n,) int64)``.
+    Label propagation with pointer jumping in torch ops, on whatever device ``triangles`` is on."""
+    t = triangles.long()
+    if t.numel() == 0:
+        return t.new_zeros(0), t.new_zeros(0)
+    label = torch.arange(n_vertices, device=t.device)
+    flat = t.reshape(-1)
+    while True:
+        lowest = label[t].min(dim=1).values
+        new = label.scatter_reduce(0, flat, lowest.repeat_interleave(3), reduce="amin")
+        for _ in range(4):
+            new = new[new]
+        if torch.equal(new, label):
+            break
+        label = new
+    _, component, sizes = torch.unique(label[t[:, 0]], return_inverse=True, return_counts=True)
+    return component, sizes
