@@ -188,7 +188,8 @@ def allreduce_gradients(module: torch.nn.Module, group=None, sparse_below: float
             dist.all_reduce(g, group=group)
             continue
         blocks = g.view(g.shape[0], -1)
-        touched = (blocks != 0).any(dim=1).to(torch.int32)
+        # one reduction pass, no table-sized temporary; NaN / inf entries count as touched
+        touched = (torch.linalg.vector_norm(blocks, ord=float("inf"), dim=1) != 0).to(torch.int32)
         dist.all_reduce(touched, op=dist.ReduceOp.MAX, group=group)
         rows = touched.nonzero().view(-1)
         if rows.numel() > sparse_below * g.shape[0]:
