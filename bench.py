@@ -255,6 +255,99 @@ def cpu_conv_sample(bw):
     return n * G**3 / sec / 1e9, f"{n} blocks x 512 cells x {D} channels (1/{CPU_SCALE} of the workload), one pass"
 
 
+def cpu_config1(bw):
+    """The CPU-runnable configuration at FULL size on the CPU restatement: 100k keys with sdf(1) +
+    rgb(3) values into capacity 200k, 100k finds (50 % hits), then 2,048 blocks x grid_dim 8 x 1
+    channel and 100k trilinear queries forward + backward.  Seconds with all threads and with one."""
+    import numpy as np
+
+    import oracle
+
+    cpu = torch.device("cpu")
+    keys = bw.hash_keys_uniform(100_000, -512, 512, cpu).numpy()
+    q = bw.hash_queries_half_hit(torch.from_numpy(keys), -512, 512).numpy()
+    vals = {"sdf": keys[:, :1].astype(np.float32) * np.float32(0.001), "rgb": keys.astype(np.float32) / np.float32(512)}
+    G, n_blocks, n_q = 8, 2048, 100_000
+    blocks = bw.block_coords_cube(n_blocks, cpu).numpy()
+    x = bw.points_in_blocks(torch.from_numpy(blocks), n_q, G, 1.0, cpu).numpy()
+    emb = np.random.default_rng(bw.SEED).standard_normal((n_blocks, G**3, 1), dtype=np.float32) * np.float32(0.1)
+    offs = np.array([[(c >> d) & 1 for d in range(3)] for c in range(8)], np.int32)
+    cells = np.arange(G**3)
+    cc = np.stack([cells % G, (cells // G) % G, cells // (G * G)], 1)
+    nb = cc[:, None, :] + offs[None]
+    c2c = ((nb % G) * np.array([1, G, G * G])).sum(-1).astype(np.int64)
+    c2g = ((nb // G) * np.array([1, 2, 4])).sum(-1).astype(np.int64)
+    z = np.ones((n_q, 1), np.float32)
+
+    def run():
+        t0 = time.perf_counter()
+        hm = oracle.OracleHashMap(3, 200_000)
+        ext = {"sdf": np.zeros((200_000, 1), np.float32), "rgb": np.zeros((200_000, 3), np.float32)}
+        hm.insert(keys, vals, ext)
+        idx, mask = hm.find(q)
+        got = ext["rgb"][idx]
+        t1 = time.perf_counter()
+        gm = oracle.OracleHashMap(3, n_blocks)
+        gm.insert_keys(blocks)
+        idx_of, _ = gm.find(blocks)
+        nb_idx, nb_ok = gm.find((blocks[:, None, :] + offs[None]).reshape(-1, 3))
+        g2g = np.full((n_blocks, 8), -1, np.int64)
+        g2g[idx_of] = np.where(nb_ok, nb_idx, -1).reshape(-1, 8)
+        bl = np.floor(x / G)
+        local = x - bl * G
+        cell = np.floor(local)
+        gi, mk = gm.find(bl.astype(np.int32))
+        ci = (cell.astype(np.int64) * np.array([1, G, G * G])).sum(-1)
+        off = (local - cell).astype(np.float32)
+        oracle.query_forward(emb, off, gi, ci, mk, g2g, c2c, c2g, "linear")
+        oracle.query_backward_forward(z, emb, off, gi, ci, mk, g2g, c2c, c2g, "linear")
+        t2 = time.perf_counter()
+        return t1 - t0, t2 - t1, float(mask.mean()), got.shape
+
+    threads = oracle.num_threads()
+    run()
+    all_threads = min((run()[:2] for _ in range(3)), key=sum)
+    oracle.set_num_threads(1)
+    one_thread = min((run()[:2] for _ in range(2)), key=sum)
+    oracle.set_num_threads(threads)
+    return {"cores": threads, "hash_ms": round(all_threads[0] * 1e3, 3), "grid_ms": round(all_threads[1] * 1e3, 3),
+            "hash_ms_1_thread": round(one_thread[0] * 1e3, 3), "grid_ms_1_thread": round(one_thread[1] * 1e3, 3),
+            "kind": "port", "sample": "the whole configuration, best of 3 (1 thread: best of 2); numpy glue included"}
+
+
+def measure_config1(ash, bw, device):
+    """The same configuration through the public API on the GPU (CUDA events, warm)."""
+    keys = bw.hash_keys_uniform(100_000, -512, 512, device)
+    q = bw.hash_queries_half_hit(keys, -512, 512)
+    vals = {"sdf": keys[:, :1].float() * 0.001, "rgb": keys.float() / 512}
+    blocks = bw.block_coords_cube(2048, device)
+    x0 = bw.points_in_blocks(blocks, 100_000, 8, 1.0, device)
+
+    def hash_part():
+        hm = ash.HashMap(3, {"sdf": 1, "rgb": 3}, 200_000, device)
+        hm.insert(keys, vals)
+        return hm.find(q, return_values=True)
+
+    def grid_part():
+        grid = ash.SparseDenseGrid(3, 2048, 1, 8, device)
+        grid.engine.insert_keys(blocks)
+        with torch.no_grad():
+            grid.embeddings.normal_(0, 0.1)
+        x = x0.clone().requires_grad_(True)
+        y, _ = grid(x, "linear")
+        y.sum().backward()
+
+    for _ in range(3):
+        hash_part(), grid_part()
+    reps = 10
+    h = min(event_ms(lambda: [hash_part() for _ in range(reps)]) for _ in range(3)) / reps
+    g = min(event_ms(lambda: [grid_part() for _ in range(reps)]) for _ in range(3)) / reps
+    return {"workload": "100k int32x3 keys + sdf(1)/rgb(3) values into capacity 200k, 100k finds at 50% hits with "
+                        "values; then 2,048 blocks, grid_dim 8, 1 channel ~N(0,0.1), 100k trilinear queries forward "
+                        "+ backward; map / grid construction and neighbour table included",
+            "hash_ms": round(h, 4), "grid_ms": round(g, 4)}
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -899,7 +992,12 @@ def main():
         line["bounded_grid"] = measure_bounded(ash, bw, device, peak)
         torch.cuda.empty_cache()
 
+    if rank == 0 and not args.no_extras:
+        line["config1_cpu_runnable"] = measure_config1(ash, bw, device)
+
     if rank == 0 and world == 1 and not args.no_cpu:
+        if "config1_cpu_runnable" in line:
+            line["config1_cpu_runnable"]["cpu_baseline"] = cpu_config1(bw)
         v, sec, cores, sample = cpu_query_sample(bw, 2, 1)
         line["cpu_baseline"] = {"value": round(v, 4), "unit": "M queries/s", "cores": cores, "kind": "port", "sample": sample}
         if "tsdf_fusion" in line:

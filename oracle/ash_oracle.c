@@ -637,6 +637,14 @@ int64_t oracle_marching_cubes_f32(
     return 0;
 }
 
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    omp_set_num_threads(n > 0 ? n : 1);
+#else
+    (void)n;
+#endif
+}
+
 int oracle_num_threads(void) {
     int n = 1;
 #ifdef _OPENMP
