@@ -252,3 +252,44 @@ def test_warp_aggregated_scatter_gives_the_same_gradient(D):
     assert scale > 0
     torch.testing.assert_close(out[True][0], out[False][0], rtol=1e-4, atol=1e-5 * scale)
     assert torch.equal(out[True][1], out[False][1])
+
+
+def test_fused_forward_backward_replays_from_a_cuda_graph():
+    """A training step on the fused path has no host synchronisation, so it can be captured once
+    and replayed: the replay on new positions equals the eager step on the same positions."""
+    grid, x = _make("unbounded", 8, 16, seed=5)
+    static_x = x.clone().requires_grad_(True)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):              # warm-up outside the capture, as torch asks
+        for _ in range(3):
+            grid.embeddings.grad = None
+            y, _ = grid(static_x, "linear")
+            y.sum().backward()
+    torch.cuda.current_stream().wait_stream(side)
+    grid.embeddings.grad = None
+    static_x.grad = None
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y, masks = grid(static_x, "linear")
+        loss = (y * y).sum()
+        loss.backward()
+    g = torch.Generator(device=DEV).manual_seed(9)
+    for trial in range(2):
+        new_x = (x + 0.01 * torch.randn(x.shape, generator=g, device=DEV)).contiguous()
+        with torch.no_grad():
+            static_x.copy_(new_x)
+        graph.replay()
+        got = (y.clone(), masks.clone(), grid.embeddings.grad.clone(), static_x.grad.clone())
+        # eager step on the same positions, on a second grid object sharing nothing with the graph
+        ref_x = new_x.clone().requires_grad_(True)
+        saved = grid.embeddings.grad
+        grid.embeddings.grad = None
+        ry, rm = grid(ref_x, "linear")
+        (ry * ry).sum().backward()
+        want = (ry, rm, grid.embeddings.grad, ref_x.grad)
+        grid.embeddings.grad = saved
+        assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
+        scale = float(want[2].abs().max())
+        torch.testing.assert_close(got[2], want[2], rtol=1e-4, atol=1e-5 * scale)
+        torch.testing.assert_close(got[3], want[3], rtol=1e-4, atol=1e-5 * float(want[3].abs().max()))
