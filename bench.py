@@ -607,6 +607,28 @@ def measure_bounded(ash, bw, device, peak):
     for _ in range(3):
         fused_step(o, d)
     fused_ms = min(event_ms(lambda: [fused_step(o, d) for _ in range(reps)]) for _ in range(3)) / reps
+    # ... and the same fused step as one CUDA-graph replay (nothing in it synchronises with the host)
+    side = torch.cuda.Stream(device)
+    side.wait_stream(torch.cuda.current_stream(device))
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            fused_step(o, d)
+    torch.cuda.current_stream(device).wait_stream(side)
+    grid.embeddings.grad = None
+    to_sigma.beta.grad = None
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        beta = to_sigma.min_beta + to_sigma.beta.abs()
+        res = render_rays(grid, o, d, 0.06, 2.5, 128, beta, "linear", skip_rays_without_hit=True)
+        graph_loss = (res["rgb"] - 0.5).abs().mean() + 0.1 * (res["depth"] - 0.3).abs().mean() \
+            + 0.1 * res["eikonal_l2"].sum() / res["n_samples"].sum().clamp_min(1)
+        graph_loss.backward()
+    graph.replay()
+    fused_graph_ms = min(event_ms(lambda: [graph.replay() for _ in range(reps)]) for _ in range(3)) / reps
+    eager_loss = float(fused_step(o, d).detach())
+    graph.replay()
+    assert abs(float(graph_loss.detach()) - eager_loss) <= 1e-4 * abs(eager_loss) + 1e-6
+    del graph
     with torch.no_grad():
         beta0 = (to_sigma.min_beta + to_sigma.beta.abs()).detach()
         fwd_only_ms = event_ms(lambda: [render_rays(grid, o, d, 0.06, 2.5, 128, beta0, "linear", True)
@@ -636,7 +658,7 @@ def measure_bounded(ash, bw, device, peak):
             "rays": int(n_r), "samples": fused_samples, "ms": round(fused_ms, 3),
             "rays_per_s": round(n_r / (fused_ms * 1e-3) / 1e6, 3), "unit": "M rays/s",
             "samples_per_s": round(fused_samples / (fused_ms * 1e-3) / 1e6, 2),
-            "forward_only_ms": round(fwd_only_ms, 4),
+            "forward_only_ms": round(fwd_only_ms, 4), "cuda_graph_replay_ms": round(fused_graph_ms, 3),
             "speedup_over_composed_step": round(step_ms / fused_ms, 2)},
     }
 
