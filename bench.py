@@ -1016,11 +1016,13 @@ def main():
         fresh = bw.hash_keys_clustered(per_rank // 2, device, seed=bw.SEED + 77 + 1000 * rank)
         q = torch.cat([uniq, fresh])[torch.randperm(per_rank, generator=g, device=device)]
         del keys, fresh
-        for _ in range(2):
+        for _ in range(5):  # the first calls pay for the caching allocator's new blocks
             pm.find(q)
-        barrier()
-        reps = 5
-        t_find = event_ms(lambda: [pm.find(q) for _ in range(reps)]) / reps
+        find_times = []
+        for _ in range(10):
+            barrier()
+            find_times.append(event_ms(lambda: pm.find(q)))
+        t_find = statistics.median(find_times)
         hit = float(pm.find(q)[1].float().mean())
         total = pm.size()
         t = torch.tensor([t_ins, t_find], device=device, dtype=torch.float64)
