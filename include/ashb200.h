@@ -450,6 +450,31 @@ int ashb_render_rays_backward(ashb_map* map, int interp, const float* embeddings
 int ashb_route_by_owner(const int32_t* keys, int64_t n, int key_dim, int world, int32_t* keys_out,
                         int64_t* perm_out, int64_t* counts_host, void* scratch_dev, void* stream);
 
+/* ---------------------------------------------------------------- peer-memory transport
+ * find over the key-hash-partitioned map without a data collective (no counterpart in the
+ * reference).  Every rank has a mailbox of mailbox_bytes, mapped into every other rank;
+ * peer_bases_dev is a DEVICE array [world] with the address of every rank's mailbox as seen from
+ * this rank.  Sections of a mailbox: inbox (int4 records {k0, k1, k2, position}; world regions of
+ * region_capacity records, region r written by rank r), counts int32 [world], answers int64
+ * [answer_capacity].  Keys of 1 to 3 columns.
+ *   ashb_peer_route_keys   writes every key of the batch into its owner's inbox and publishes the
+ *                          per-region counts; cursor_dev int32 [world] scratch; records beyond
+ *                          region_capacity are dropped and ASHB_STATUS_CAPACITY is or-ed into
+ *                          status_dev.
+ *   ashb_peer_find_answer  probes the records of this rank's inbox and stores each answer (global
+ *                          index local * world + rank, or -1) into the asker's answers section at
+ *                          the recorded position.
+ * The caller orders the two across the ranks (all route calls complete before any answer call
+ * starts, all answer calls complete before the answers are read or the next route call starts),
+ * e.g. with a small collective on the same stream between them.  No host synchronisation. */
+int ashb_peer_route_keys(const int32_t* keys, int64_t n, int key_dim, int world, int rank,
+                         void* const* peer_bases_dev, int64_t mailbox_bytes, int64_t inbox_offset,
+                         int64_t counts_offset, int64_t answers_offset, int64_t region_capacity,
+                         int64_t answer_capacity, int32_t* cursor_dev, uint32_t* status_dev, void* stream);
+int ashb_peer_find_answer(ashb_map* map, int world, int rank, void* const* peer_bases_dev, int64_t mailbox_bytes,
+                          int64_t inbox_offset, int64_t counts_offset, int64_t answers_offset,
+                          int64_t region_capacity, int64_t answer_capacity, void* stream);
+
 /* ---------------------------------------------------------------- runtime knobs */
 
 /* Selects how ashb_query_backward_forward and ashb_grid_query_backward scatter the embedding

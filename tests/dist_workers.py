@@ -130,3 +130,36 @@ def replicated_grid_worker(rank, world, port, backend, use_cuda):
         torch.testing.assert_close(summed, grid.embeddings.grad[idx].cpu(), rtol=1e-4, atol=1e-5)
     finally:
         dist.destroy_process_group()
+
+
+def peer_find_worker(rank, world, port):
+    """find over peer memory == find over all-to-all(v), for full, ragged and empty batches."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        from ash.distributed import PartitionedHashMap
+
+        g = torch.Generator(device=device).manual_seed(100 + rank)
+        pm = PartitionedHashMap(3, 400_000, device, peer_max_batch=120_000)
+        keys = torch.randint(-300, 300, (100_000, 3), dtype=torch.int32, device=device, generator=g)
+        pm.insert_keys(keys)
+        for n in (100_000, 37_001 + 11 * rank, 0 if rank == 0 else 5):
+            q = torch.cat([keys[: n // 2], torch.randint(-300, 300, (n - n // 2, 3), dtype=torch.int32, device=device,
+                                                         generator=g)])
+            for _ in range(2):   # the mailbox is reused from call to call
+                idx_p, ok_p = pm.find(q)
+            box, pm.mailbox = pm.mailbox, None
+            idx_c, ok_c = pm.find(q)
+            pm.mailbox = box
+            assert torch.equal(ok_p, ok_c) and torch.equal(idx_p, idx_c)
+            if n > 1000:
+                assert 0.5 <= float(ok_p.float().mean()) <= 1.0
+        assert int(box.status.item()) == 0
+        big = torch.randint(-300, 300, (130_000, 3), dtype=torch.int32, device=device, generator=g)
+        idx_b, ok_b = pm.find(big)        # beyond peer_max_batch: falls back to the collective path
+        assert idx_b.shape == (130_000,)
+    finally:
+        dist.destroy_process_group()

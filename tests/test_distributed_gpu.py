@@ -22,3 +22,7 @@ def test_partitioned_hash_map_nccl():
 
 def test_replicated_grid_gradient_sum_nccl():
     mp.spawn(dist_workers.replicated_grid_worker, args=(2, _free_port(), "nccl", True), nprocs=2, join=True)
+
+
+def test_partitioned_find_over_peer_memory():
+    mp.spawn(dist_workers.peer_find_worker, args=(2, _free_port()), nprocs=2, join=True)

@@ -76,6 +76,8 @@ _lib.ashb_render_accumulate_backward.argtypes = [_vp, _vp, _vp, _vp, _i64, _i64,
 _lib.ashb_isosurface_extraction.argtypes = [_vp] * 9 + [_i64, _c.POINTER(_i64), _vp, _f32, _f32, _int, _i64, _i64, _i64, _vp]
 _lib.ashb_set_find_cooperative.argtypes = [_int]
 _lib.ashb_set_scatter_aggregation.argtypes = [_int]
+_lib.ashb_peer_route_keys.argtypes = [_vp, _i64, _int, _int, _int, _vp] + [_i64] * 6 + [_vp, _vp, _vp]
+_lib.ashb_peer_find_answer.argtypes = [_vp, _int, _int, _vp] + [_i64] * 6 + [_vp]
 _lib.ashb_measure_random_reads.argtypes = [_vp, _i64, _i64, _int, _c.c_uint32, _vp, _vp]
 _lib.ashb_marching_cubes_count.argtypes = [_vp] * 9 + [_f32, _f32, _i64, _i64, _i64, _c.POINTER(_i64), _c.POINTER(_i64), _vp]
 _lib.ashb_marching_cubes_fill.argtypes = [_vp] * 11 + [_i64, _vp, _i64, _f32, _int, _i64, _i64, _i64, _vp]
@@ -934,3 +936,22 @@ def render_rays_backward(hashmap, embeddings, nb_lut, cell_size, origin, ray_o_w
         _check(_lib.ashb_render_rays_backward(*args, out.data_ptr(), go.data_ptr(), ge.data_ptr(), gb.data_ptr(), n,
                                               _stream(emb.device)))
     return ge, gb
+
+
+# ---------------------------------------------------------------------------------------------
+# Peer-memory transport of the partitioned map (no counterpart in the reference).  ``layout`` =
+# (peer_bases_dev: address of the device array of mailbox addresses, mailbox_bytes, inbox_offset,
+# counts_offset, answers_offset, region_capacity, answer_capacity).
+
+def peer_route_keys(keys, world, rank, layout, cursor, status):
+    keys = _cuda(keys, "keys", torch.int32)
+    n, dim = keys.shape
+    with torch.cuda.device(keys.device):
+        _check(_lib.ashb_peer_route_keys(keys.data_ptr(), n, dim, int(world), int(rank), *[int(v) for v in layout],
+                                         cursor.data_ptr(), status.data_ptr(), _stream(keys.device)))
+
+
+def peer_find_answer(hashmap, world, rank, layout):
+    dev = hashmap._device
+    with torch.cuda.device(dev):
+        _check(_lib.ashb_peer_find_answer(hashmap._h, int(world), int(rank), *[int(v) for v in layout], _stream(dev)))

@@ -79,6 +79,33 @@ class _Route:
         return out
 
 
+class _PeerMailbox:
+    """Symmetric device memory of the peer transport: one mailbox per rank, mapped into every
+    rank (``torch.distributed._symmetric_memory``), laid out as inbox | counts | answers."""
+
+    def __init__(self, world: int, rank: int, max_batch: int, device, group) -> None:
+        import torch.distributed._symmetric_memory as symm
+
+        self.world, self.rank, self.max_batch = world, rank, int(max_batch)
+        inbox_bytes = world * self.max_batch * 16
+        counts_offset = (inbox_bytes + 255) // 256 * 256
+        answers_offset = counts_offset + 256
+        total = answers_offset + self.max_batch * 8
+        self.buffer = symm.empty(total, dtype=torch.uint8, device=device)
+        self.handle = symm.rendezvous(self.buffer, group if group is not None else dist.group.WORLD)
+        self.layout = (self.handle.buffer_ptrs_dev, total, 0, counts_offset, answers_offset, self.max_batch,
+                       self.max_batch)
+        self.answers = self.buffer[answers_offset:answers_offset + self.max_batch * 8].view(torch.int64)
+        self.cursor = torch.zeros(world, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.token = torch.zeros(1, dtype=torch.int32, device=device)
+        self.group = group
+
+    def barrier(self) -> None:
+        """Stream-ordered: enqueued behind this rank's kernels, completes when every rank got here."""
+        dist.all_reduce(self.token, group=self.group)
+
+
 class PartitionedHashMap:
     """Key-hash-partitioned hash map over the ranks of ``group``.
 
@@ -86,7 +113,12 @@ class PartitionedHashMap:
     size, including empty).  ``find`` answers in the caller's order.
     """
 
-    def __init__(self, key_dim: int, capacity: int, device, group=None, slack: float = 1.25):
+    def __init__(self, key_dim: int, capacity: int, device, group=None, slack: float = 1.25,
+                 peer_max_batch: int = 0):
+        """``peer_max_batch`` > 0 (CUDA, key_dim <= 3): ``find`` on batches of up to that many keys
+        per rank goes over peer memory -- keys written straight into the owners' inboxes, answers
+        straight back into the askers' buffers, two launches and two one-element collectives per
+        rank -- instead of grouping + all-to-all(v) each way."""
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -95,6 +127,10 @@ class PartitionedHashMap:
         self.local_capacity = int(-(-capacity // self.world) * slack) + 64
         self.engine = ASHEngine(key_dim, self.local_capacity, device)
         self.device = self.engine.device
+        self.mailbox = None
+        if peer_max_batch > 0:
+            assert self.device.type == "cuda" and key_dim <= 3, "the peer transport needs CUDA and key_dim <= 3"
+            self.mailbox = _PeerMailbox(self.world, self.rank, peer_max_batch, self.device, group)
 
     def _route(self, keys: torch.Tensor) -> Tuple[_Route, torch.Tensor]:
         keys = keys.to(self.device, torch.int32).contiguous()
@@ -114,6 +150,8 @@ class PartitionedHashMap:
 
     def find(self, keys: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         """(global indices int64 (N,), masks bool (N,)); a miss has index 0 and mask False."""
+        if self.mailbox is not None and keys.shape[0] <= self.mailbox.max_batch:
+            return self._find_over_peer_memory(keys)
         route, mine = self._route(keys)
         if mine.shape[0]:
             idx, masks = self.engine.find(mine)
@@ -122,6 +160,18 @@ class PartitionedHashMap:
             masks = torch.empty(0, dtype=torch.bool, device=self.device)
         # one int64 per key on the wire: the global index, or -1 for a miss
         answers = route.backward(torch.where(masks, idx * self.world + self.rank, torch.full_like(idx, -1)))
+        found = answers >= 0
+        return answers.clamp_(min=0), found
+
+    def _find_over_peer_memory(self, keys: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        box = self.mailbox
+        keys = keys.to(self.device, torch.int32).contiguous()
+        assert keys.dim() == 2 and keys.shape[1] == self.key_dim, "keys shape mismatch"
+        backend.peer_route_keys(keys, self.world, self.rank, box.layout, box.cursor, box.status)
+        box.barrier()                      # every inbox is complete
+        backend.peer_find_answer(self.engine.backend, self.world, self.rank, box.layout)
+        box.barrier()                      # every answer has landed; the inboxes may be reused
+        answers = box.answers[:keys.shape[0]].clone()
         found = answers >= 0
         return answers.clamp_(min=0), found
 

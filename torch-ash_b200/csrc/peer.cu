@@ -1,0 +1,156 @@
+// Peer-memory transport for the key-hash-partitioned hash map (one process per GPU, every rank's
+// mailbox mapped into every other rank over NVLink).  The reference is single-GPU and has no
+// counterpart.  A find over the partitioned map is two launches per rank and no data collective:
+//
+//   route   every key is written straight into its OWNER's inbox as a 16-byte record
+//           {k0, k1, k2, position in the asker's batch}.  Rank r owns region r of every inbox, so
+//           the write position comes from a LOCAL cursor (one atomic per warp and owner) and no
+//           remote atomic is needed; the per-region counts are published to the owners at the end.
+//   (stream-ordered barrier across the ranks: a collective on a one-element tensor)
+//   answer  every owner probes the records of its inbox and stores each answer (global index or
+//           -1) straight into the ASKER's answer buffer at the recorded position.
+//   (barrier)
+//
+// Neither kernel waits on another GPU: ordering comes from the barriers the host enqueues between
+// them.  Every remote address is base[peer] + offset with the offset checked against the layout
+// the caller describes; records that would not fit are dropped and reported in a status word.
+#include "hashmap.cuh"
+
+namespace ashb {
+
+constexpr int kPeerMaxWorld = 64;
+
+// Same owner function as route.cu / ash.distributed.owner_of (int64 wrap-around arithmetic).
+__device__ __forceinline__ int peer_owner_of(int k0, int k1, int k2, int dim, int world) {
+    const unsigned long long primes[3] = {73856093ull, 19349663ull, 83492791ull};
+    const int k[3] = {k0, k1, k2};
+    long long h = 0;
+    for (int d = 0; d < dim; ++d) h ^= (long long)((unsigned long long)(long long)k[d] * primes[d]);
+    h = (long long)((unsigned long long)(h ^ (h >> 15)) * 0x2C1B3C6Dull);
+    h ^= h >> 12;
+    long long r = h % world;
+    return (int)(r < 0 ? r + world : r);
+}
+
+struct PeerLayout {
+    void* const* bases;      // device array [world]: base address of every rank's mailbox as mapped here
+    int64_t inbox_offset;    // int4 records, world regions of region_capacity each
+    int64_t counts_offset;   // int32 [world]: records in each region
+    int64_t answers_offset;  // int64 [answer_capacity]
+    int64_t region_capacity;
+    int64_t answer_capacity;
+    int world, rank;
+};
+
+template <int DIM>
+__global__ void __launch_bounds__(256) peer_route_kernel(const int32_t* __restrict__ keys, int64_t n, PeerLayout L,
+                                                         int* __restrict__ cursor, uint32_t* __restrict__ status) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    const bool live = i < n;
+    int k0 = 0, k1 = 0, k2 = 0, k3 = 0;
+    if (live) load_key<DIM>(keys, i, k0, k1, k2, k3);
+    // lanes without a key take a negative owner of their own, so that they match nobody
+    const int owner = live ? peer_owner_of(k0, k1, k2, DIM, L.world) : -1 - lane;
+    const unsigned peers = __match_any_sync(0xffffffffu, owner);
+    const int leader = __ffs(peers) - 1;
+    int base = 0;
+    if (live && lane == leader) base = atomicAdd(&cursor[owner], __popc(peers));
+    base = __shfl_sync(0xffffffffu, base, leader);
+    if (!live) return;
+    const int64_t slot = (int64_t)base + __popc(peers & lanemask_lt());
+    if (slot >= L.region_capacity) {
+        atomicOr(status, ASHB_STATUS_CAPACITY);
+        return;
+    }
+    int4* inbox = reinterpret_cast<int4*>(static_cast<char*>(L.bases[owner]) + L.inbox_offset);
+    inbox[(int64_t)L.rank * L.region_capacity + slot] = make_int4(k0, k1, k2, (int)i);
+}
+
+__global__ void peer_publish_counts_kernel(PeerLayout L, const int* __restrict__ cursor) {
+    const int o = threadIdx.x;
+    if (o >= L.world) return;
+    int* counts = reinterpret_cast<int*>(static_cast<char*>(L.bases[o]) + L.counts_offset);
+    const int64_t c = cursor[o];
+    counts[L.rank] = (int)(c < L.region_capacity ? c : L.region_capacity);
+}
+
+__global__ void __launch_bounds__(256) peer_answer_kernel(Table16 t, PeerLayout L) {
+    const int region = blockIdx.y;  // the rank that asked
+    const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const char* mine = static_cast<const char*>(L.bases[L.rank]);
+    const int count = __ldcg(reinterpret_cast<const int*>(mine + L.counts_offset) + region);
+    if (j >= count || j >= L.region_capacity) return;
+    const int4 rec = __ldcg(reinterpret_cast<const int4*>(mine + L.inbox_offset) + (int64_t)region * L.region_capacity + j);
+    const int idx = lookup(t, rec.x, rec.y, rec.z, 0);
+    const long long answer = idx >= 0 ? (long long)idx * L.world + L.rank : -1ll;
+    if (rec.w < 0 || rec.w >= L.answer_capacity) return;  // a position no batch can have
+    long long* answers = reinterpret_cast<long long*>(static_cast<char*>(L.bases[region]) + L.answers_offset);
+    answers[rec.w] = answer;
+}
+
+}  // namespace ashb
+
+using namespace ashb;
+
+static int check_layout(const PeerLayout& L, int64_t mailbox_bytes) {
+    ASHB_REQUIRE(L.bases != nullptr, "null peer table");
+    ASHB_REQUIRE(L.world >= 1 && L.world <= kPeerMaxWorld && L.rank >= 0 && L.rank < L.world, "bad world / rank");
+    ASHB_REQUIRE(L.region_capacity >= 1 && L.answer_capacity >= 1 && L.answer_capacity <= 0x7fffffffll,
+                 "bad capacities");
+    ASHB_REQUIRE(L.inbox_offset >= 0 && L.inbox_offset % 16 == 0 && L.counts_offset % 4 == 0 && L.answers_offset % 8 == 0,
+                 "misaligned mailbox sections");
+    const int64_t inbox_end = L.inbox_offset + (int64_t)L.world * L.region_capacity * 16;
+    const int64_t counts_end = L.counts_offset + (int64_t)L.world * 4;
+    const int64_t answers_end = L.answers_offset + L.answer_capacity * 8;
+    ASHB_REQUIRE(inbox_end <= L.counts_offset && counts_end <= L.answers_offset && answers_end <= mailbox_bytes,
+                 "mailbox sections overlap or exceed the mailbox");
+    return ASHB_OK;
+}
+
+extern "C" {
+
+int ashb_peer_route_keys(const int32_t* keys, int64_t n, int key_dim, int world, int rank,
+                         void* const* peer_bases_dev, int64_t mailbox_bytes, int64_t inbox_offset,
+                         int64_t counts_offset, int64_t answers_offset, int64_t region_capacity,
+                         int64_t answer_capacity, int32_t* cursor_dev, uint32_t* status_dev, void* stream) {
+    const PeerLayout L{peer_bases_dev, inbox_offset, counts_offset, answers_offset, region_capacity, answer_capacity,
+                       world, rank};
+    if (int rc = check_layout(L, mailbox_bytes)) return rc;
+    ASHB_REQUIRE(key_dim >= 1 && key_dim <= 3, "the peer transport carries keys of 1 to 3 columns");
+    ASHB_REQUIRE(n >= 0 && n <= answer_capacity, "batch of %lld keys exceeds the mailbox's %lld", (long long)n,
+                 (long long)answer_capacity);
+    ASHB_REQUIRE(cursor_dev && status_dev && (n == 0 || keys), "null buffer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    ASHB_CUDA_TRY(cudaMemsetAsync(cursor_dev, 0, (size_t)world * sizeof(int32_t), st));
+    if (n > 0) {
+        const unsigned grid = (unsigned)((n + 255) / 256);
+        switch (key_dim) {
+            case 1: peer_route_kernel<1><<<grid, 256, 0, st>>>(keys, n, L, cursor_dev, status_dev); break;
+            case 2: peer_route_kernel<2><<<grid, 256, 0, st>>>(keys, n, L, cursor_dev, status_dev); break;
+            default: peer_route_kernel<3><<<grid, 256, 0, st>>>(keys, n, L, cursor_dev, status_dev); break;
+        }
+        ASHB_LAUNCH_CHECK();
+    }
+    peer_publish_counts_kernel<<<1, kPeerMaxWorld, 0, st>>>(L, cursor_dev);
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+int ashb_peer_find_answer(ashb_map* m, int world, int rank, void* const* peer_bases_dev, int64_t mailbox_bytes,
+                          int64_t inbox_offset, int64_t counts_offset, int64_t answers_offset,
+                          int64_t region_capacity, int64_t answer_capacity, void* stream) {
+    const PeerLayout L{peer_bases_dev, inbox_offset, counts_offset, answers_offset, region_capacity, answer_capacity,
+                       world, rank};
+    if (int rc = check_layout(L, mailbox_bytes)) return rc;
+    ASHB_REQUIRE(m != nullptr && m->slots != nullptr, "null or destroyed map");
+    ASHB_REQUIRE(m->key_dim <= 3, "the peer transport carries keys of 1 to 3 columns");
+    DeviceGuard guard(m->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const dim3 grid((unsigned)((region_capacity + 255) / 256), (unsigned)world);
+    peer_answer_kernel<<<grid, 256, 0, st>>>(table16_of(m), L);
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+}  // extern "C"
