@@ -474,6 +474,11 @@ int ashb_peer_route_keys(const int32_t* keys, int64_t n, int key_dim, int world,
 int ashb_peer_find_answer(ashb_map* map, int world, int rank, void* const* peer_bases_dev, int64_t mailbox_bytes,
                           int64_t inbox_offset, int64_t counts_offset, int64_t answers_offset,
                           int64_t region_capacity, int64_t answer_capacity, void* stream);
+/* Insert-if-absent (erase == 0) or erase (erase != 0) of the records in this rank's inbox, after an
+ * ashb_peer_route_keys on every rank and the barrier; nothing goes back to the askers. */
+int ashb_peer_update(ashb_map* map, int erase, int world, int rank, void* const* peer_bases_dev,
+                     int64_t mailbox_bytes, int64_t inbox_offset, int64_t counts_offset, int64_t answers_offset,
+                     int64_t region_capacity, int64_t answer_capacity, void* stream);
 
 /* ---------------------------------------------------------------- runtime knobs */
 

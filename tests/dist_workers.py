@@ -158,6 +158,22 @@ def peer_find_worker(rank, world, port):
             if n > 1000:
                 assert 0.5 <= float(ok_p.float().mean()) <= 1.0
         assert int(box.status.item()) == 0
+        # insert and erase over peer memory against a second map that only uses the collectives
+        ref = PartitionedHashMap(3, 400_000, device)
+        ref.insert_keys(keys)
+        more = torch.randint(-300, 300, (60_000 + 7 * rank, 3), dtype=torch.int32, device=device, generator=g)
+        gone = torch.cat([keys[::3], more[::5]])
+        for m in (pm, ref):
+            m.insert_keys(more)
+            m.insert_keys(more[:1000])     # duplicates of present keys change nothing
+            m.erase(gone)
+        assert pm.size() == ref.size()
+        probe = torch.cat([keys, more, torch.randint(-300, 300, (5000, 3), dtype=torch.int32, device=device, generator=g)])
+        assert torch.equal(pm.find(probe)[1], ref.find(probe)[1])
+        mine, _ = pm.local_items()
+        theirs, _ = ref.local_items()
+        order = lambda k: k[torch.argsort(k[:, 0].long() * 1_000_003 + k[:, 1].long() * 1009 + k[:, 2].long(), stable=True)]
+        assert torch.equal(order(mine), order(theirs))   # every owner holds exactly the same keys
         big = torch.randint(-300, 300, (130_000, 3), dtype=torch.int32, device=device, generator=g)
         idx_b, ok_b = pm.find(big)        # beyond peer_max_batch: falls back to the collective path
         assert idx_b.shape == (130_000,)

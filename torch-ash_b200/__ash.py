@@ -78,6 +78,7 @@ _lib.ashb_set_find_cooperative.argtypes = [_int]
 _lib.ashb_set_scatter_aggregation.argtypes = [_int]
 _lib.ashb_peer_route_keys.argtypes = [_vp, _i64, _int, _int, _int, _vp] + [_i64] * 6 + [_vp, _vp, _vp]
 _lib.ashb_peer_find_answer.argtypes = [_vp, _int, _int, _vp] + [_i64] * 6 + [_vp]
+_lib.ashb_peer_update.argtypes = [_vp, _int, _int, _int, _vp] + [_i64] * 6 + [_vp]
 _lib.ashb_measure_random_reads.argtypes = [_vp, _i64, _i64, _int, _c.c_uint32, _vp, _vp]
 _lib.ashb_marching_cubes_count.argtypes = [_vp] * 9 + [_f32, _f32, _i64, _i64, _i64, _c.POINTER(_i64), _c.POINTER(_i64), _vp]
 _lib.ashb_marching_cubes_fill.argtypes = [_vp] * 11 + [_i64, _vp, _i64, _f32, _int, _i64, _i64, _i64, _vp]
@@ -955,3 +956,11 @@ def peer_find_answer(hashmap, world, rank, layout):
     dev = hashmap._device
     with torch.cuda.device(dev):
         _check(_lib.ashb_peer_find_answer(hashmap._h, int(world), int(rank), *[int(v) for v in layout], _stream(dev)))
+
+
+def peer_update(hashmap, erase, world, rank, layout):
+    """Insert-if-absent (or erase) the keys other ranks routed into this rank's inbox."""
+    dev = hashmap._device
+    with torch.cuda.device(dev):
+        _check(_lib.ashb_peer_update(hashmap._h, int(bool(erase)), int(world), int(rank), *[int(v) for v in layout],
+                                     _stream(dev)))

@@ -139,14 +139,35 @@ class PartitionedHashMap:
         return route, route.forward()
 
     def insert_keys(self, keys: torch.Tensor) -> None:
+        if self.mailbox is not None and keys.shape[0] <= self.mailbox.max_batch:
+            return self._update_over_peer_memory(keys, erase=False)
         _, mine = self._route(keys)
         if mine.shape[0]:
             self.engine.insert_keys(mine)
 
     def erase(self, keys: torch.Tensor) -> None:
+        if self.mailbox is not None and keys.shape[0] <= self.mailbox.max_batch:
+            return self._update_over_peer_memory(keys, erase=True)
         _, mine = self._route(keys)
         if mine.shape[0]:
             self.engine.erase(mine)
+
+    def _update_over_peer_memory(self, keys: torch.Tensor, erase: bool) -> None:
+        box = self.mailbox
+        keys = keys.to(self.device, torch.int32).contiguous()
+        assert keys.dim() == 2 and keys.shape[1] == self.key_dim, "keys shape mismatch"
+        backend.peer_route_keys(keys, self.world, self.rank, box.layout, box.cursor, box.status)
+        box.barrier()                      # every inbox is complete
+        backend.peer_update(self.engine.backend, erase, self.world, self.rank, box.layout)
+        box.barrier()                      # every inbox has been consumed and may be reused
+        # the engine's host-side bounds are stale after native updates
+        self.engine._size_bound = self.engine.capacity
+        if erase:
+            # as ASHEngine.erase: rebuild the table once the erased keys may fill half of it
+            self.engine._erased_bound += keys.shape[0]
+            if self.engine._erased_bound > self.engine.capacity // 2:
+                self.engine.backend.rehash()
+                self.engine._erased_bound = 0
 
     def find(self, keys: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         """(global indices int64 (N,), masks bool (N,)); a miss has index 0 and mask False."""

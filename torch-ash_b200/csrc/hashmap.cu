@@ -145,28 +145,12 @@ __global__ void __launch_bounds__(256) insert_kernel(Table t, const int32_t* __r
         bool present = false;
         slot = emplace(t, k0, k1, k2, k3, kPending, &present);
     }
-    // Warp-aggregated pop of the free-index stack: one atomic per warp.
-    const bool won = slot >= 0;
-    const unsigned ballot = __ballot_sync(0xffffffffu, won);
-    if (ballot == 0) return;
-    const int leader = __ffs(ballot) - 1;
-    int base = 0;
-    if ((int)(threadIdx.x & 31) == leader) base = atomicAdd(counter, __popc(ballot));
-    base = __shfl_sync(0xffffffffu, base, leader);
-    if (!won) return;
-    const int top = base + __popc(ballot & lanemask_lt());
-    if (top >= capacity) {
-        // No free index left: undo the pop, give the slot back, record it.
-        atomicSub(counter, 1);
-        *reinterpret_cast<volatile int*>(t.val_ptr((uint32_t)slot)) = kTomb;
-        atomicOr(t.status, ASHB_STATUS_CAPACITY);
-        return;
-    }
-    const int idx = heap[top];
+    const int idx = pop_index_for_slot(t, slot, heap, counter, capacity);
+    if (idx < 0) return;
     for (int j = 0; j < vctx.n; ++j)
         copy_row(vctx.src[j] + i * vctx.row_bytes[j], vctx.dst[j] + (long long)idx * vctx.row_bytes[j],
                  vctx.row_bytes[j], vctx.word[j]);
-    *reinterpret_cast<volatile int*>(t.val_ptr((uint32_t)slot)) = idx;
+    publish_index(t, slot, idx);
 }
 
 // ---- erase -----------------------------------------------------------------------
@@ -178,28 +162,9 @@ __global__ void __launch_bounds__(256) erase_kernel(Table t, const int32_t* __re
     if (i < n) {
         int k0, k1, k2, k3;
         load_key<DIM>(keys, i, k0, k1, k2, k3);
-        uint32_t s = hash_key(k0, k1, k2, k3) & t.mask;
-        for (uint32_t probe = 0; probe <= t.mask; ++probe) {
-            const Entry e = t.read_fresh(s);
-            if (e.val == kEmpty) break;
-            if (e.val >= 0 && key_match(e, k0, k1, k2, k3)) {
-                // In-batch duplicates race here; exactly one CAS succeeds.
-                if (atomicCAS(t.val_ptr(s), e.val, kTomb) == e.val) idx = e.val;
-                break;
-            }
-            s = (s + 1) & t.mask;
-        }
+        idx = tombstone_key(t, k0, k1, k2, k3);
     }
-    const bool won = idx >= 0;
-    const unsigned ballot = __ballot_sync(0xffffffffu, won);
-    if (ballot == 0) return;
-    const int leader = __ffs(ballot) - 1;
-    int base = 0;
-    if ((int)(threadIdx.x & 31) == leader) base = atomicSub(counter, __popc(ballot));
-    base = __shfl_sync(0xffffffffu, base, leader);
-    if (!won) return;
-    const int top = base - __popc(ballot & lanemask_lt());
-    if (top >= 1) heap[top - 1] = idx;
+    push_freed_index(idx, heap, counter);
 }
 
 // ---- load_states -----------------------------------------------------------------

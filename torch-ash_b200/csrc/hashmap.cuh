@@ -190,6 +190,70 @@ __device__ __forceinline__ int64_t emplace(const Table& t, int k0, int k1, int k
     return -1;
 }
 
+// Second half of an insert, called by ALL lanes of a warp: the lanes that claimed a slot (slot >= 0)
+// pop their row indices from the free-index stack with one atomic for the warp.  Returns the
+// index, or -1 for lanes without a slot or when the stack is empty (the slot is then given back and
+// ASHB_STATUS_CAPACITY recorded).  The caller copies its value rows and then publishes the index
+// with publish_index.
+template <class Table>
+__device__ __forceinline__ int pop_index_for_slot(const Table& t, int64_t slot, int32_t* __restrict__ heap,
+                                                  int32_t* counter, int32_t capacity) {
+    const bool won = slot >= 0;
+    const unsigned ballot = __ballot_sync(0xffffffffu, won);
+    if (ballot == 0) return -1;
+    const int leader = __ffs(ballot) - 1;
+    int base = 0;
+    if ((int)(threadIdx.x & 31) == leader) base = atomicAdd(counter, __popc(ballot));
+    base = __shfl_sync(0xffffffffu, base, leader);
+    if (!won) return -1;
+    const int top = base + __popc(ballot & lanemask_lt());
+    if (top >= capacity) {
+        // No free index left: undo the pop, give the slot back, record it.
+        atomicSub(counter, 1);
+        *reinterpret_cast<volatile int*>(t.val_ptr((uint32_t)slot)) = kTomb;
+        atomicOr(t.status, ASHB_STATUS_CAPACITY);
+        return -1;
+    }
+    return heap[top];
+}
+
+template <class Table>
+__device__ __forceinline__ void publish_index(const Table& t, int64_t slot, int idx) {
+    *reinterpret_cast<volatile int*>(t.val_ptr((uint32_t)slot)) = idx;
+}
+
+// First half of an erase: turns the key's slot into a tombstone; returns the freed row index or -1.
+template <class Table>
+__device__ __forceinline__ int tombstone_key(const Table& t, int k0, int k1, int k2, int k3) {
+    uint32_t s = hash_key(k0, k1, k2, k3) & t.mask;
+    for (uint32_t probe = 0; probe <= t.mask; ++probe) {
+        const Entry e = t.read_fresh(s);
+        if (e.val == kEmpty) break;
+        if (e.val >= 0 && key_match(e, k0, k1, k2, k3)) {
+            // In-batch duplicates race here; exactly one CAS succeeds.
+            if (atomicCAS(t.val_ptr(s), e.val, kTomb) == e.val) return e.val;
+            break;
+        }
+        s = (s + 1) & t.mask;
+    }
+    return -1;
+}
+
+// Second half of an erase, called by ALL lanes of a warp: freed indices (idx >= 0) go back on the
+// stack with one atomic for the warp.
+__device__ __forceinline__ void push_freed_index(int idx, int32_t* __restrict__ heap, int32_t* counter) {
+    const bool won = idx >= 0;
+    const unsigned ballot = __ballot_sync(0xffffffffu, won);
+    if (ballot == 0) return;
+    const int leader = __ffs(ballot) - 1;
+    int base = 0;
+    if ((int)(threadIdx.x & 31) == leader) base = atomicSub(counter, __popc(ballot));
+    base = __shfl_sync(0xffffffffu, base, leader);
+    if (!won) return;
+    const int top = base - __popc(ballot & lanemask_lt());
+    if (top >= 1) heap[top - 1] = idx;
+}
+
 // Read-only lookup: index of the key or -1.
 template <class Table>
 __device__ __forceinline__ int lookup(const Table& t, int k0, int k1, int k2, int k3) {

@@ -89,6 +89,28 @@ __global__ void __launch_bounds__(256) peer_answer_kernel(Table16 t, PeerLayout 
     answers[rec.w] = answer;
 }
 
+// insert-if-absent / erase of the records in this rank's inbox (no answers go back)
+template <bool ERASE>
+__global__ void __launch_bounds__(256) peer_update_kernel(Table16 t, PeerLayout L, int32_t* __restrict__ heap,
+                                                          int32_t* counter, int32_t capacity) {
+    const int region = blockIdx.y;
+    const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const char* mine = static_cast<const char*>(L.bases[L.rank]);
+    const int count = __ldcg(reinterpret_cast<const int*>(mine + L.counts_offset) + region);
+    const bool live = j < count && j < L.region_capacity;
+    int4 rec = make_int4(0, 0, 0, 0);
+    if (live) rec = __ldcg(reinterpret_cast<const int4*>(mine + L.inbox_offset) + (int64_t)region * L.region_capacity + j);
+    // whole warps go through the stack operations below
+    if (ERASE) {
+        push_freed_index(live ? tombstone_key(t, rec.x, rec.y, rec.z, 0) : -1, heap, counter);
+    } else {
+        bool present = false;
+        const int64_t slot = live ? emplace(t, rec.x, rec.y, rec.z, 0, kPending, &present) : -1;
+        const int idx = pop_index_for_slot(t, slot, heap, counter, capacity);
+        if (idx >= 0) publish_index(t, slot, idx);
+    }
+}
+
 }  // namespace ashb
 
 using namespace ashb;
@@ -149,6 +171,25 @@ int ashb_peer_find_answer(ashb_map* m, int world, int rank, void* const* peer_ba
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const dim3 grid((unsigned)((region_capacity + 255) / 256), (unsigned)world);
     peer_answer_kernel<<<grid, 256, 0, st>>>(table16_of(m), L);
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+int ashb_peer_update(ashb_map* m, int erase, int world, int rank, void* const* peer_bases_dev,
+                     int64_t mailbox_bytes, int64_t inbox_offset, int64_t counts_offset, int64_t answers_offset,
+                     int64_t region_capacity, int64_t answer_capacity, void* stream) {
+    const PeerLayout L{peer_bases_dev, inbox_offset, counts_offset, answers_offset, region_capacity, answer_capacity,
+                       world, rank};
+    if (int rc = check_layout(L, mailbox_bytes)) return rc;
+    ASHB_REQUIRE(m != nullptr && m->slots != nullptr, "null or destroyed map");
+    ASHB_REQUIRE(m->key_dim <= 3, "the peer transport carries keys of 1 to 3 columns");
+    DeviceGuard guard(m->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const dim3 grid((unsigned)((region_capacity + 255) / 256), (unsigned)world);
+    if (erase)
+        peer_update_kernel<true><<<grid, 256, 0, st>>>(table16_of(m), L, m->heap, m->counter, (int32_t)m->capacity);
+    else
+        peer_update_kernel<false><<<grid, 256, 0, st>>>(table16_of(m), L, m->heap, m->counter, (int32_t)m->capacity);
     ASHB_LAUNCH_CHECK();
     return ASHB_OK;
 }
