@@ -450,6 +450,25 @@ int ashb_render_rays_backward(ashb_map* map, int interp, const float* embeddings
 int ashb_route_by_owner(const int32_t* keys, int64_t n, int key_dim, int world, int32_t* keys_out,
                         int64_t* perm_out, int64_t* counts_host, void* scratch_dev, void* stream);
 
+/* ---------------------------------------------------------------- table sharded over the GPUs of a box
+ * ashb_grid_query_forward / _backward for an embedding table split by block over `world` GPUs
+ * (no counterpart in the reference): block g lives on GPU g % world as row g / world of that
+ * GPU's shard float32 [ceil(n_emb / world)][G^3][D]; emb_bases_dev / grad_bases_dev are DEVICE
+ * arrays [world] of the shards' addresses as mapped into this GPU (peer memory).  The map and
+ * nb_lut are this rank's replicas of the block structure (n_emb = global number of rows).  The
+ * forward reads corner rows from their owners with plain loads; the backward ADDS gradient rows
+ * straight into the owners' gradient shards with vector reductions (and writes grad_x, or skips it
+ * when NULL).  The caller orders the launches across the ranks: parameters must be final on every
+ * rank before any forward, and every backward must be complete before a gradient shard is read. */
+int ashb_grid_query_forward_sharded(ashb_map* map, int interp, const void* const* emb_bases_dev, int world,
+                                    const float* x, double cell_size, const float* origin, int G,
+                                    const int32_t* nb_lut, float* out, uint8_t* masks, int32_t* block_idx_out,
+                                    int64_t n, int64_t n_emb, int64_t D, void* stream);
+int ashb_grid_query_backward_sharded(ashb_map* map, int interp, const float* z, const void* const* emb_bases_dev,
+                                     void* const* grad_bases_dev, int world, const float* x, double cell_size,
+                                     const float* origin, int G, const int32_t* nb_lut, const int32_t* block_idx,
+                                     float* grad_x, int64_t n, int64_t n_emb, int64_t D, void* stream);
+
 /* ---------------------------------------------------------------- peer-memory transport
  * find over the key-hash-partitioned map without a data collective (no counterpart in the
  * reference).  Every rank has a mailbox of mailbox_bytes, mapped into every other rank;

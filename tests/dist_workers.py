@@ -179,3 +179,65 @@ def peer_find_worker(rank, world, port):
         assert idx_b.shape == (130_000,)
     finally:
         dist.destroy_process_group()
+
+
+def sharded_grid_worker(rank, world, port):
+    """A table sharded over the ranks answers like a replicated one, and the gradient shards hold
+    the rows of the summed dense gradient."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        import ash
+        import bench_workloads as bw
+        from ash.distributed import ShardedSparseDenseGrid
+
+        G, D, n_blocks, cell = 4, 8, 301, 0.05
+        blocks = bw.block_coords_blob(n_blocks, device, n_blobs=3, seed=7)
+        full = torch.randn(n_blocks + 40, G**3, D, generator=torch.Generator().manual_seed(1)).to(device)
+        for interpolation in ("linear", "smooth_step"):
+            # the replicated reference: the whole table on every rank
+            ref = ash.UnBoundedSparseDenseGrid(3, n_blocks + 40, D, G, cell_size=cell, device=device)
+            ref.engine.insert_keys(blocks[torch.randperm(n_blocks, device=device)])   # an order of its own per rank
+            sharded = ShardedSparseDenseGrid(3, n_blocks + 40, D, G, cell_size=cell, device=device)
+            sharded.engine.insert_keys(blocks)
+            sharded.sync_structure_(src=0)
+            # give both the same values per BLOCK (their indices differ)
+            idx_ref, _ = ref.engine.find(blocks)
+            idx_sh, _ = sharded.engine.find(blocks)
+            gathered = [torch.empty_like(idx_sh) for _ in range(world)]
+            dist.all_gather(gathered, idx_sh)
+            assert all(torch.equal(g, gathered[0]) for g in gathered)
+            with torch.no_grad():
+                ref.embeddings[idx_ref] = full[:n_blocks]
+                mine = idx_sh % world == rank
+                sharded.embeddings[idx_sh[mine] // world] = full[:n_blocks][mine]
+            g = torch.Generator(device=device).manual_seed(50 + rank)
+            pick = torch.randint(n_blocks, (4000 + 13 * rank,), device=device, generator=g)
+            x = ((blocks[pick].float() + torch.rand(len(pick), 3, device=device, generator=g) * 1.4 - 0.2) * G * cell)
+            w = torch.randn(len(pick), D, device=device, generator=g)
+            xr = x.clone().requires_grad_(True)
+            yr, mr = ref(xr, interpolation)
+            (yr * w).sum().backward()
+            dense = ref.embeddings.grad.clone()
+            # the dense gradients of all ranks, per block, summed: what an all-reduce would give
+            per_block = dense[idx_ref]
+            dist.all_reduce(per_block)
+            for trial in range(2):   # the second pass reuses the zeroed gradient shard
+                sharded.zero_grad_shard_()
+                xs = x.clone().requires_grad_(True)
+                ys, ms = sharded(xs, interpolation)
+                (ys * w).sum().backward()
+                sharded.finish_backward()
+                assert torch.equal(ms, mr) and torch.equal(ys, yr)
+                torch.testing.assert_close(xs.grad, xr.grad, rtol=1e-5, atol=1e-5 * float(xr.grad.abs().max()))
+                got = sharded.embeddings.grad[idx_sh[mine] // world]
+                want = per_block[mine]
+                torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-5 * float(want.abs().max()))
+            assert 0.3 < float(mr.float().mean()) < 1.0
+            dist.barrier()
+            del sharded, ref
+    finally:
+        dist.destroy_process_group()

@@ -26,3 +26,7 @@ def test_replicated_grid_gradient_sum_nccl():
 
 def test_partitioned_find_over_peer_memory():
     mp.spawn(dist_workers.peer_find_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
+def test_sharded_grid_matches_replicated_grid():
+    mp.spawn(dist_workers.sharded_grid_worker, args=(2, _free_port()), nprocs=2, join=True)

@@ -79,6 +79,10 @@ _lib.ashb_set_scatter_aggregation.argtypes = [_int]
 _lib.ashb_peer_route_keys.argtypes = [_vp, _i64, _int, _int, _int, _vp] + [_i64] * 6 + [_vp, _vp, _vp]
 _lib.ashb_peer_find_answer.argtypes = [_vp, _int, _int, _vp] + [_i64] * 6 + [_vp]
 _lib.ashb_peer_update.argtypes = [_vp, _int, _int, _int, _vp] + [_i64] * 6 + [_vp]
+_lib.ashb_grid_query_forward_sharded.argtypes = [_vp, _int, _vp, _int, _vp, _c.c_double, _vp, _int, _vp, _vp, _vp, _vp,
+                                                 _i64, _i64, _i64, _vp]
+_lib.ashb_grid_query_backward_sharded.argtypes = [_vp, _int, _vp, _vp, _vp, _int, _vp, _c.c_double, _vp, _int, _vp, _vp,
+                                                  _vp, _i64, _i64, _i64, _vp]
 _lib.ashb_measure_random_reads.argtypes = [_vp, _i64, _i64, _int, _c.c_uint32, _vp, _vp]
 _lib.ashb_marching_cubes_count.argtypes = [_vp] * 9 + [_f32, _f32, _i64, _i64, _i64, _c.POINTER(_i64), _c.POINTER(_i64), _vp]
 _lib.ashb_marching_cubes_fill.argtypes = [_vp] * 11 + [_i64, _vp, _i64, _f32, _int, _i64, _i64, _i64, _vp]
@@ -964,3 +968,46 @@ def peer_update(hashmap, erase, world, rank, layout):
     with torch.cuda.device(dev):
         _check(_lib.ashb_peer_update(hashmap._h, int(bool(erase)), int(world), int(rank), *[int(v) for v in layout],
                                      _stream(dev)))
+
+
+# ---------------------------------------------------------------------------------------------
+# Grid query over an embedding table sharded by block over the GPUs of one box (peer memory).
+# ``emb_bases`` / ``grad_bases``: addresses of device arrays [world] holding every shard's address
+# as mapped into this GPU.  No counterpart in the reference.
+
+def grid_query_forward_sharded(hashmap, emb_bases, world, n_emb, embedding_dim, x, cell_size, origin, grid_dim, nb_lut,
+                               interpolation):
+    """Returns (features (N, D) float32, masks bool (N,), block_idx int32 (N,))."""
+    x = _cuda(x, "x", torch.float32)
+    nb_lut = _cuda(nb_lut, "nb_lut", torch.int32)
+    if x.dim() != 2 or x.shape[1] != 3 or nb_lut.shape != (n_emb, 8):
+        raise RuntimeError("x must be (N, 3) and nb_lut int32 (num_embeddings, 8)")
+    n, dev = x.shape[0], x.device
+    out = torch.empty((n, embedding_dim), dtype=torch.float32, device=dev)
+    masks = torch.empty(n, dtype=torch.bool, device=dev)
+    bidx = torch.empty(n, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _check(_lib.ashb_grid_query_forward_sharded(
+            hashmap._h, _interp_code(interpolation), int(emb_bases), int(world), x.data_ptr(), float(cell_size),
+            _host_floats(origin, 3), int(grid_dim), nb_lut.data_ptr(), out.data_ptr(), masks.data_ptr(), bidx.data_ptr(),
+            n, int(n_emb), int(embedding_dim), _stream(dev)))
+    return out, masks, bidx
+
+
+def grid_query_backward_sharded(hashmap, z, emb_bases, grad_bases, world, n_emb, x, cell_size, origin, grid_dim, nb_lut,
+                                block_idx, interpolation, need_grad_x=True):
+    """Adds the embedding gradient into the owners' gradient shards; returns grad_x (N, 3) or None."""
+    x = _cuda(x, "x", torch.float32)
+    z = _cuda(z, "z", torch.float32)
+    nb_lut = _cuda(nb_lut, "nb_lut", torch.int32)
+    bidx = _cuda(block_idx, "block_idx", torch.int32)
+    n, dev = x.shape[0], x.device
+    if z.dim() != 2 or z.shape[0] != n or bidx.shape != (n,) or nb_lut.shape != (n_emb, 8):
+        raise RuntimeError("z must be (N, D), block_idx (N,), nb_lut int32 (num_embeddings, 8)")
+    grad_x = torch.empty((n, 3), dtype=torch.float32, device=dev) if need_grad_x else None
+    with torch.cuda.device(dev):
+        _check(_lib.ashb_grid_query_backward_sharded(
+            hashmap._h, _interp_code(interpolation), z.data_ptr(), int(emb_bases), int(grad_bases), int(world),
+            x.data_ptr(), float(cell_size), _host_floats(origin, 3), int(grid_dim), nb_lut.data_ptr(), bidx.data_ptr(),
+            grad_x.data_ptr() if need_grad_x else None, n, int(n_emb), z.shape[1], _stream(dev)))
+    return grad_x

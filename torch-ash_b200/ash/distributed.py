@@ -25,6 +25,7 @@ import torch.distributed as dist
 
 from .common import _get_c_extension
 from .core import ASHEngine
+from .grid import UnBoundedSparseDenseGrid
 
 backend = _get_c_extension()
 
@@ -269,3 +270,110 @@ def allreduce_gradients(module: torch.nn.Module, group=None, sparse_below: float
             packed = blocks[rows]
             dist.all_reduce(packed, group=group)
             blocks[rows] = packed
+
+
+class _ShardedGridQuery(torch.autograd.Function):
+    """Query of a table sharded over the ranks: rows read from, and gradient rows added into,
+    their owners' memory."""
+
+    @staticmethod
+    def forward(ctx, embeddings, x, grid, interpolation):
+        geom = grid._sharded_geometry()
+        y, masks, block_idx = backend.grid_query_forward_sharded(
+            grid.engine.backend, grid._emb_bases, grid.world, grid.num_embeddings, grid.embedding_dim, x, *geom,
+            interpolation)
+        ctx.save_for_backward(x, block_idx)
+        ctx.grid, ctx.geom, ctx.interpolation = grid, geom, interpolation
+        ctx.mark_non_differentiable(masks)
+        return y, masks
+
+    @staticmethod
+    def backward(ctx, z, _grad_masks):
+        x, block_idx = ctx.saved_tensors
+        grid = ctx.grid
+        grad_x = backend.grid_query_backward_sharded(
+            grid.engine.backend, z.contiguous(), grid._emb_bases, grid._grad_bases, grid.world, grid.num_embeddings, x,
+            *ctx.geom, block_idx, ctx.interpolation, need_grad_x=bool(ctx.needs_input_grad[1]))
+        return None, grad_x, None, None   # the embedding gradient went straight into the owners' shards
+
+
+class ShardedSparseDenseGrid(UnBoundedSparseDenseGrid):
+    """A sparse-dense grid whose embedding table is SPLIT over the ranks of one box instead of
+    replicated: block ``g`` lives on rank ``g % world`` as row ``g // world`` of that rank's shard,
+    and every shard (and its gradient) is mapped into every rank over NVLink.  A query reads its
+    corner rows from their owners and its backward adds gradient rows straight into the owners'
+    gradient shards, so there is no gradient all-reduce and each rank holds 1 / world of the table.
+
+    The block structure (hash map, neighbour table) is replicated: build it the same way on every
+    rank, then call ``sync_structure_()``.  ``embeddings`` is this rank's shard
+    ``(ceil(num_embeddings / world), G^3, D)``; ``embeddings.grad`` is its gradient shard.  A step::
+
+        grid.zero_grad_shard_()
+        y, masks = grid(x)            # every rank, its own positions
+        loss(y).backward()
+        grid.finish_backward()        # all gradient rows have landed: embeddings.grad is complete
+        optimizer.step()              # on this rank's shard
+
+    Only the query is provided on a sharded grid (no convolution, fusion or iso-surface)."""
+
+    def __init__(self, in_dim: int, num_embeddings: int, embedding_dim: int, grid_dim: int, cell_size: float = 1.0,
+                 device=None, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self._rows_per_rank = -(-num_embeddings // self.world)
+        super().__init__(in_dim, num_embeddings, embedding_dim, grid_dim, cell_size=cell_size, device=device)
+        import torch.distributed._symmetric_memory as symm
+
+        pg = group if group is not None else dist.group.WORLD
+        self._emb_handle = symm.rendezvous(self._emb_shard, pg)
+        self._emb_bases = self._emb_handle.buffer_ptrs_dev
+        self._grad_shard = symm.empty(tuple(self.embeddings.shape), dtype=torch.float32, device=self.device)
+        self._grad_shard.zero_()
+        self._grad_handle = symm.rendezvous(self._grad_shard, pg)
+        self._grad_bases = self._grad_handle.buffer_ptrs_dev
+        self.embeddings.grad = self._grad_shard
+        self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.fused = True
+
+    def _allocate_embeddings(self) -> torch.Tensor:
+        import torch.distributed._symmetric_memory as symm
+
+        shard = symm.empty((self._rows_per_rank, self.num_cells_per_grid, self.embedding_dim), dtype=torch.float32,
+                           device=self.device)
+        self._emb_shard = shard.zero_()
+        return self._emb_shard
+
+    def _barrier(self) -> None:
+        """Stream-ordered: behind this rank's kernels, complete when every rank got here."""
+        dist.all_reduce(self._token, group=self.group)
+
+    def _sharded_geometry(self):
+        origin, cell_size = self._cell_frame()
+        return cell_size, origin, self.grid_dim, self._neighbor_lut32()
+
+    @torch.no_grad()
+    def sync_structure_(self, src: int = 0) -> None:
+        """Give every rank rank ``src``'s key -> index map (shards are addressed by index)."""
+        broadcast_state(self.engine, src=src, group=self.group)
+        self.construct_grid_neighbor_lut_(radius=1, bidirectional=False)
+
+    def owned_rows(self) -> torch.Tensor:
+        """Global row indices of this rank's shard rows, in shard order."""
+        return torch.arange(self._rows_per_rank, device=self.device) * self.world + self.rank
+
+    def forward(self, x: torch.Tensor, interpolation: str = "smooth_step"):
+        if interpolation not in ("linear", "smooth_step"):
+            raise ValueError(f"Unknown interpolation: {interpolation}")
+        if self.grid_coords is None or self.lut_grid_nb2grid_idx is None:
+            self.construct_grid_neighbor_lut_(radius=1, bidirectional=False)
+        self._barrier()   # every rank's parameters and zeroed gradient shards are final
+        return _ShardedGridQuery.apply(self.embeddings, x.to(torch.float32).contiguous(), self, interpolation)
+
+    def finish_backward(self) -> None:
+        self._barrier()   # every rank's gradient rows have landed
+        self.embeddings.grad = self._grad_shard
+
+    @torch.no_grad()
+    def zero_grad_shard_(self) -> None:
+        self._grad_shard.zero_()

@@ -39,8 +39,7 @@ class SparseDenseGrid(ASHModule):
         self.transform_cell_to_world = lambda x: x
 
         self.engine = ASHEngine(in_dim, num_embeddings, self.device)
-        self.embeddings = nn.Parameter(
-            torch.zeros(num_embeddings, self.num_cells_per_grid, embedding_dim, device=self.device))
+        self.embeddings = nn.Parameter(self._allocate_embeddings())
 
         # Dense (per-cell) structure is fixed by grid_dim and built once.
         self.cell_indices = torch.arange(self.num_cells_per_grid, dtype=torch.long, device=self.device)
@@ -67,6 +66,10 @@ class SparseDenseGrid(ASHModule):
         self._lut32 = None
         self._lut32_source = None
         self._own_transform = self.transform_world_to_cell
+
+    def _allocate_embeddings(self) -> torch.Tensor:
+        """Storage of the embedding table (overridden where the table lives elsewhere)."""
+        return torch.zeros(self.num_embeddings, self.num_cells_per_grid, self.embedding_dim, device=self.device)
 
     # ------------------------------------------------------------------ allocation
     def spatial_init_(self, points: torch.Tensor, dilation: int = 1, bidirectional: bool = False):

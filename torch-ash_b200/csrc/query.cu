@@ -126,6 +126,15 @@ struct LutSource {
     const float* __restrict__ offsets;
     QueryLuts L;
 
+    // Row addressing: one table in this GPU's memory.
+    template <typename T>
+    __device__ __forceinline__ const T* in_row(const T* emb, int64_t b) const { return emb + b; }
+    template <typename T>
+    __device__ __forceinline__ T* out_row(T* grad, int64_t b) const { return grad + b; }
+    template <typename T, int VEC>
+    __device__ __forceinline__ Pack<T, VEC> load_row(const T* p) const { return load_pack<T, VEC>(p); }
+
+
     __device__ __forceinline__ bool resolve(int64_t q, int lane, int64_t D, int64_t* base, float* off) const {
         (void)lane;
         if (!L.masks[q]) return false;
@@ -164,6 +173,14 @@ struct LutSource {
 #endif
 struct FusedSource {
     static constexpr int kForwardMinBlocks = ASHB_FWD_MIN_BLOCKS;
+    // Row addressing: one table in this GPU's memory.
+    template <typename T>
+    __device__ __forceinline__ const T* in_row(const T* emb, int64_t b) const { return emb + b; }
+    template <typename T>
+    __device__ __forceinline__ T* out_row(T* grad, int64_t b) const { return grad + b; }
+    template <typename T, int VEC>
+    __device__ __forceinline__ Pack<T, VEC> load_row(const T* p) const { return load_pack<T, VEC>(p); }
+
     Table16 table;
     const float* __restrict__ x;          // (n, 3) world positions
     float org[3];                         // world position of cell (0,0,0)
@@ -177,8 +194,9 @@ struct FusedSource {
     int64_t n_emb;
     int64_t cells_per_grid;
 
-    __device__ __forceinline__ bool resolve(int64_t q, int lane, int64_t D, int64_t* base, float* off) const {
-        int blk[3], cell[3];
+    // Block index of query q (probe or saved), its cell and offsets; side outputs written by lane 0.
+    __device__ __forceinline__ int locate(int64_t q, int lane, int* cell, float* off) const {
+        int blk[3];
         const float xw[3] = {x[3 * q], x[3 * q + 1], x[3 * q + 2]};
         split_world_position(xw, org, inv_cell, inv_G, G_f, G, blk, cell, off);
         const int gi = gi_in ? gi_in[q] : lookup(table, blk[0], blk[1], blk[2], 0);
@@ -186,8 +204,69 @@ struct FusedSource {
             if (gi_out) gi_out[q] = gi;
             if (mask_out) mask_out[q] = (uint8_t)(gi >= 0);
         }
+        return gi;
+    }
+
+    __device__ __forceinline__ bool resolve(int64_t q, int lane, int64_t D, int64_t* base, float* off) const {
+        int cell[3];
+        const int gi = locate(q, lane, cell, off);
         if (gi < 0 || gi >= n_emb) return false;
         return corner_rows(nb_lut, gi, cell, G, n_emb, cells_per_grid, D, base);
+    }
+};
+
+// The table split over `world` GPUs by block: block g lives on GPU g % world as row g / world of
+// that GPU's shard, and every shard is mapped into this GPU (peer memory over NVLink).  A corner
+// row is then a peer address: rows are read with plain loads from, and gradients reduced straight
+// into, the owner's memory -- the exchange a replicated table would need afterwards (a table-sized
+// all-reduce) does not exist.  `base` carries the owner in its top byte.
+struct ShardedSource : FusedSource {
+    static constexpr int kForwardMinBlocks = 1;
+    const void* const* __restrict__ emb_bases;   // device array [world]
+    void* const* __restrict__ grad_bases;        // device array [world] (backward only)
+    int world;
+
+    static constexpr int kOwnerShift = 56;
+    template <typename T>
+    __device__ __forceinline__ const T* in_row(const T*, int64_t b) const {
+        return static_cast<const T*>(emb_bases[b >> kOwnerShift]) + (b & ((1ll << kOwnerShift) - 1));
+    }
+    template <typename T>
+    __device__ __forceinline__ T* out_row(T*, int64_t b) const {
+        return static_cast<T*>(grad_bases[b >> kOwnerShift]) + (b & ((1ll << kOwnerShift) - 1));
+    }
+    template <typename T, int VEC>
+    __device__ __forceinline__ Pack<T, VEC> load_row(const T* p) const {
+        using V = typename Vec<T, VEC>::type;
+        Pack<T, VEC> r;
+        *reinterpret_cast<V*>(r.v) = *reinterpret_cast<const V*>(p);  // plain load: the row may be a peer's
+        return r;
+    }
+
+    __device__ __forceinline__ bool resolve(int64_t q, int lane, int64_t D, int64_t* base, float* off) const {
+        int cell[3];
+        const int gi = locate(q, lane, cell, off);
+        if (gi < 0 || gi >= n_emb) return false;
+        const int32_t* row = nb_lut + (int64_t)gi * 8;
+        bool ok = true;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            int cc[3], nb = 0;
+#pragma unroll
+            for (int d = 0; d < 3; ++d) {
+                cc[d] = cell[d] + ((c >> d) & 1);
+                if (cc[d] == G) {
+                    cc[d] = 0;
+                    nb |= 1 << d;
+                }
+            }
+            const int g = nb ? __ldg(row + nb) : gi;
+            const bool here = g >= 0 && g < n_emb;
+            ok = ok && here;
+            const int64_t local = here ? g / world : 0, owner = here ? g % world : 0;
+            base[c] = ((local * cells_per_grid + (cc[0] + (cc[1] + cc[2] * G) * G)) * D) | (owner << kOwnerShift);
+        }
+        return ok;
     }
 };
 
@@ -217,7 +296,7 @@ __global__ void __launch_bounds__(256, Src::kForwardMinBlocks) query_forward_ker
         aw.init(interp, off);
         Pack<T, VEC> e[8];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) e[c] = load_pack<T, VEC>(emb + base[c] + ch);
+        for (int c = 0; c < 8; ++c) e[c] = src.template load_row<T, VEC>(src.in_row(emb, base[c]) + ch);
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
             const T w = aw.weight(c);
@@ -258,7 +337,7 @@ __global__ void __launch_bounds__(256, ASHB_BWD_MIN_BLOCKS) query_backward_forwa
             Pack<T, VEC> e[8];
             if (NEED_GO) {
 #pragma unroll
-                for (int c = 0; c < 8; ++c) e[c] = load_pack<T, VEC>(emb + base[c] + ch);
+                for (int c = 0; c < 8; ++c) e[c] = src.template load_row<T, VEC>(src.in_row(emb, base[c]) + ch);
             }
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
@@ -270,7 +349,7 @@ __global__ void __launch_bounds__(256, ASHB_BWD_MIN_BLOCKS) query_backward_forwa
                     g.v[k] = w * zv.v[k];
                     if (NEED_GO) dot += e[c].v[k] * zv.v[k];
                 }
-                if (NEED_GE) atomic_add_pack<T, VEC>(grad_emb + base[c] + ch, g);
+                if (NEED_GE) atomic_add_pack<T, VEC>(src.out_row(grad_emb, base[c]) + ch, g);
                 if (NEED_GO) {
                     T wg[3];
                     aw.grad(c, wg);
@@ -344,7 +423,7 @@ __global__ void __launch_bounds__(256) query_backward_forward_agg_kernel(
     Pack<T, VEC> e[8];
     if (NEED_GO && valid) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c) e[c] = load_pack<T, VEC>(emb + base[c] + ch);
+        for (int c = 0; c < 8; ++c) e[c] = src.template load_row<T, VEC>(src.in_row(emb, base[c]) + ch);
     }
     T go[3] = {0, 0, 0};
 #pragma unroll
@@ -357,7 +436,7 @@ __global__ void __launch_bounds__(256) query_backward_forward_agg_kernel(
             g.v[k] = w * zv.v[k];
             if (NEED_GO && valid) dot += e[c].v[k] * zv.v[k];
         }
-        scatter_aggregated<T, VEC>(grad_emb, base[c] + ch, g, valid);
+        scatter_aggregated<T, VEC>(src.out_row(grad_emb, 0), base[c] + ch, g, valid);
         if (NEED_GO) {
             T wg[3];
             aw.grad(c, wg);
@@ -394,7 +473,7 @@ __global__ void __launch_bounds__(256) query_zero_rows_kernel(Src src, T* __rest
 #pragma unroll
     for (int k = 0; k < VEC; ++k) zero.v[k] = 0;
 #pragma unroll
-    for (int c = 0; c < 8; ++c) store_pack<T, VEC>(grad_emb + base[c] + ch, zero);
+    for (int c = 0; c < 8; ++c) store_pack<T, VEC>(src.out_row(grad_emb, base[c]) + ch, zero);
 }
 
 // ---- double backward ----------------------------------------------------------------
@@ -420,7 +499,7 @@ __global__ void __launch_bounds__(256, ASHB_BWD_MIN_BLOCKS) query_backward_backw
         const Pack<T, VEC> zv = load_pack<T, VEC>(z + q * D + ch);
         Pack<T, VEC> e[8];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) e[c] = load_pack<T, VEC>(emb + base[c] + ch);
+        for (int c = 0; c < 8; ++c) e[c] = src.template load_row<T, VEC>(src.in_row(emb, base[c]) + ch);
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
             T wg[3];
@@ -432,7 +511,7 @@ __global__ void __launch_bounds__(256, ASHB_BWD_MIN_BLOCKS) query_backward_backw
                 g.v[k] = dot * zv.v[k];
                 gz.v[k] += dot * e[c].v[k];
             }
-            atomic_add_pack<T, VEC>(grad_emb + base[c] + ch, g);
+            atomic_add_pack<T, VEC>(src.out_row(grad_emb, base[c]) + ch, g);
         }
     }
     store_pack<T, VEC>(grad_z + q * D + ch, gz);
@@ -743,6 +822,69 @@ int ashb_grid_query_backward(ashb_map* m, int dtype, int interp, const void* z, 
                                                             scale, n, D, st)
                              : backward_forward_impl<double>(interp, z, embeddings, src, grad_embeddings, grad_x,
                                                              scale, n, D, st);
+}
+
+// ---- the table split over the GPUs of one box (peer memory) ---------------------------------
+static int make_sharded_source(ashb_map* m, const void* const* emb_bases, void* const* grad_bases, int world,
+                               const float* x, double cell_size, const float* origin, int G, const int32_t* nb_lut,
+                               const int32_t* gi_in, int32_t* gi_out, uint8_t* mask_out, int64_t n_emb,
+                               ShardedSource* out) {
+    ASHB_REQUIRE(world >= 1 && world <= 64 && emb_bases != nullptr, "bad world size or null shard table");
+    FusedSource f;
+    if (int rc = make_fused_source(m, x, cell_size, origin, G, nb_lut, gi_in, gi_out, mask_out, n_emb, &f)) return rc;
+    ShardedSource s{};
+    static_cast<FusedSource&>(s) = f;
+    s.emb_bases = emb_bases;
+    s.grad_bases = grad_bases;
+    s.world = world;
+    *out = s;
+    return ASHB_OK;
+}
+
+int ashb_grid_query_forward_sharded(ashb_map* m, int interp, const void* const* emb_bases_dev, int world,
+                                    const float* x, double cell_size, const float* origin, int G,
+                                    const int32_t* nb_lut, float* out, uint8_t* masks, int32_t* block_idx_out,
+                                    int64_t n, int64_t n_emb, int64_t D, void* stream) {
+    if (int rc = check_query_args(ASHB_F32, interp, n, n_emb, (int64_t)G * G * G, D)) return rc;
+    if (n == 0) return ASHB_OK;
+    ASHB_REQUIRE(out && masks, "null buffer");
+    ShardedSource src;
+    if (int rc = make_sharded_source(m, emb_bases_dev, nullptr, world, x, cell_size, origin, G, nb_lut, nullptr,
+                                     block_idx_out, masks, n_emb, &src))
+        return rc;
+    DeviceGuard guard(m->device);
+    return forward_impl<float>(interp, nullptr, src, out, n, D, static_cast<cudaStream_t>(stream));
+}
+
+int ashb_grid_query_backward_sharded(ashb_map* m, int interp, const float* z, const void* const* emb_bases_dev,
+                                     void* const* grad_bases_dev, int world, const float* x, double cell_size,
+                                     const float* origin, int G, const int32_t* nb_lut, const int32_t* block_idx,
+                                     float* grad_x, int64_t n, int64_t n_emb, int64_t D, void* stream) {
+    if (int rc = check_query_args(ASHB_F32, interp, n, n_emb, (int64_t)G * G * G, D)) return rc;
+    if (n == 0) return ASHB_OK;
+    ASHB_REQUIRE(z && grad_bases_dev, "null buffer");
+    ShardedSource src;
+    if (int rc = make_sharded_source(m, emb_bases_dev, grad_bases_dev, world, x, cell_size, origin, G, nb_lut,
+                                     block_idx, nullptr, nullptr, n_emb, &src))
+        return rc;
+    DeviceGuard guard(m->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const void* ptrs[] = {z};
+    const Shape sh = pick_shape(D, sizeof(float), ptrs, 1);
+    const int64_t threads = n << sh.lane_shift;
+    const unsigned grid = (unsigned)((threads + 255) / 256);
+    const float scale = (float)(1.0 / cell_size);
+    float* none = nullptr;
+    ASHB_VEC_SWITCH(float, sh,
+                    if (grad_x != nullptr) {
+                        query_backward_forward_kernel<float, VEC, ShardedSource, true><<<grid, 256, 0, st>>>(
+                                z, none, src, none, grad_x, scale, n, (int)D, sh.lane_shift, interp);
+                    } else {
+                        query_backward_forward_kernel<float, VEC, ShardedSource, false><<<grid, 256, 0, st>>>(
+                                z, none, src, none, none, scale, n, (int)D, sh.lane_shift, interp);
+                    });
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
 }
 
 int ashb_grid_query_backward_backward(ashb_map* m, int dtype, int interp, const void* grad_grad_x, const void* z,
