@@ -533,6 +533,49 @@ def measure_rays_sharded(ash, bw, device, dist, rank, world):
             "rays_per_s": round(n_rays * world / (out["block_sparse"] * 1e-3) / 1e6, 3), "unit": "M rays/s"}
 
 
+def measure_sharded_table(ash, bw, device, dist, rank, world, n_blocks, n_queries, steps):
+    """The microbench table SPLIT over the ranks (block g on rank g % world, shards mapped into
+    every rank over NVLink) instead of replicated: forward reads corner rows from their owners, the
+    backward reduces gradient rows straight into the owners' gradient shards, so a training step
+    needs no gradient all-reduce.  One step = zero the gradient shard + forward + backward of this
+    rank's positions + the barrier after which every shard's gradient is complete."""
+    from ash.distributed import ShardedSparseDenseGrid
+
+    grid = ShardedSparseDenseGrid(3, n_blocks, EMB_DIM, GRID_DIM, cell_size=1.0, device=device)
+    blocks = bw.block_coords_blob(n_blocks, device)
+    grid.engine.insert_keys(blocks)
+    grid.sync_structure_(src=0)
+    with torch.no_grad():
+        grid.embeddings.normal_(0.0, 0.01, generator=torch.Generator(device=device).manual_seed(bw.SEED + 3 + rank))
+    xs = [bw.points_in_blocks(blocks, n_queries, GRID_DIM, 1.0, device, seed=bw.SEED + 100 * rank + s) for s in range(4)]
+
+    def step(i, need_grad_x):
+        grid.zero_grad_shard_()
+        x = xs[i % 4].detach().requires_grad_(need_grad_x)
+        y, _ = grid(x, interpolation="linear")
+        y.sum().backward()
+        grid.finish_backward()
+
+    out = {}
+    for need_grad_x in (True, False):
+        for i in range(3):
+            step(i, need_grad_x)
+        dist.barrier()
+        torch.cuda.synchronize()
+        ms = event_ms(lambda: [step(i, need_grad_x) for i in range(steps)]) / steps
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out[need_grad_x] = float(t.item())
+    shard_bytes = grid.embeddings.numel() * 4
+    del grid
+    return {"what": "table split over the ranks by block, shards mapped into every rank (peer memory); step = zero the "
+                    "gradient shard + forward + backward + completion barrier, through autograd; no gradient all-reduce",
+            "table_bytes_per_gpu": shard_bytes, "queries_per_step": n_queries * world,
+            "ms_per_step": round(out[True], 4), "value": round(world * n_queries / (out[True] * 1e-3) / 1e6, 2),
+            "unit": "M queries/s (fwd+bwd, gradients complete on their owners)",
+            "ms_per_step_embedding_gradient_only": round(out[False], 4)}
+
+
 def measure_bounded(ash, bw, device, peak):
     """Bounded grid at resolution 512 (64 blocks x grid_dim 8 per axis), sdf + rgb channels: 7x7x7
     Gaussian filter through the neighbourhood convolution, ray near/far and ray sampling for 8192
@@ -1069,6 +1112,13 @@ def main():
         torch.cuda.empty_cache()
 
     if dist is not None and not args.no_extras:
+        try:
+            split = measure_sharded_table(ash, bw, device, dist, rank, world, N_BLOCKS, N_QUERIES, min(args.steps, 10))
+        except Exception as exc:  # symmetric memory unavailable on this box
+            split = {"unavailable": f"{type(exc).__name__}: {exc}"}
+        if rank == 0:
+            line["sharded_table"] = split
+        torch.cuda.empty_cache()
         sharded = measure_rays_sharded(ash, bw, device, dist, rank, world)
         if rank == 0:
             line["volume_rendering_train_step_sharded"] = sharded
