@@ -469,6 +469,14 @@ int ashb_grid_query_backward_sharded(ashb_map* map, int interp, const float* z, 
                                      const float* origin, int G, const int32_t* nb_lut, const int32_t* block_idx,
                                      float* grad_x, int64_t n, int64_t n_emb, int64_t D, void* stream);
 
+/* Double backward over the sharded table (as ashb_grid_query_backward_backward): grad_z [n][D] is
+ * written, the embedding gradient is ADDED into the owners' gradient shards. */
+int ashb_grid_query_backward_backward_sharded(ashb_map* map, int interp, const float* grad_grad_x, const float* z,
+                                              const void* const* emb_bases_dev, void* const* grad_bases_dev,
+                                              int world, const float* x, double cell_size, const float* origin,
+                                              int G, const int32_t* nb_lut, const int32_t* block_idx, float* grad_z,
+                                              int64_t n, int64_t n_emb, int64_t D, void* stream);
+
 /* ---------------------------------------------------------------- peer-memory transport
  * find over the key-hash-partitioned map without a data collective (no counterpart in the
  * reference).  Every rank has a mailbox of mailbox_bytes, mapped into every other rank;

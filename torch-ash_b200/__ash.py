@@ -81,6 +81,8 @@ _lib.ashb_peer_find_answer.argtypes = [_vp, _int, _int, _vp] + [_i64] * 6 + [_vp
 _lib.ashb_peer_update.argtypes = [_vp, _int, _int, _int, _vp] + [_i64] * 6 + [_vp]
 _lib.ashb_grid_query_forward_sharded.argtypes = [_vp, _int, _vp, _int, _vp, _c.c_double, _vp, _int, _vp, _vp, _vp, _vp,
                                                  _i64, _i64, _i64, _vp]
+_lib.ashb_grid_query_backward_backward_sharded.argtypes = [_vp, _int, _vp, _vp, _vp, _vp, _int, _vp, _c.c_double, _vp, _int,
+                                                           _vp, _vp, _vp, _i64, _i64, _i64, _vp]
 _lib.ashb_grid_query_backward_sharded.argtypes = [_vp, _int, _vp, _vp, _vp, _int, _vp, _c.c_double, _vp, _int, _vp, _vp,
                                                   _vp, _i64, _i64, _i64, _vp]
 _lib.ashb_measure_random_reads.argtypes = [_vp, _i64, _i64, _int, _c.c_uint32, _vp, _vp]
@@ -1011,3 +1013,23 @@ def grid_query_backward_sharded(hashmap, z, emb_bases, grad_bases, world, n_emb,
             x.data_ptr(), float(cell_size), _host_floats(origin, 3), int(grid_dim), nb_lut.data_ptr(), bidx.data_ptr(),
             grad_x.data_ptr() if need_grad_x else None, n, int(n_emb), z.shape[1], _stream(dev)))
     return grad_x
+
+
+def grid_query_backward_backward_sharded(hashmap, grad_grad_x, z, emb_bases, grad_bases, world, n_emb, x, cell_size,
+                                         origin, grid_dim, nb_lut, block_idx, interpolation):
+    """Adds the second-order embedding gradient into the owners' gradient shards; returns grad_z (N, D)."""
+    x = _cuda(x, "x", torch.float32)
+    z = _cuda(z, "z", torch.float32)
+    ggx = _cuda(grad_grad_x, "grad_grad_x", torch.float32)
+    nb_lut = _cuda(nb_lut, "nb_lut", torch.int32)
+    bidx = _cuda(block_idx, "block_idx", torch.int32)
+    n, dev = x.shape[0], x.device
+    if z.dim() != 2 or z.shape[0] != n or ggx.shape != (n, 3) or bidx.shape != (n,) or nb_lut.shape != (n_emb, 8):
+        raise RuntimeError("z must be (N, D), grad_grad_x (N, 3), block_idx (N,), nb_lut int32 (num_embeddings, 8)")
+    grad_z = torch.empty_like(z)
+    with torch.cuda.device(dev):
+        _check(_lib.ashb_grid_query_backward_backward_sharded(
+            hashmap._h, _interp_code(interpolation), ggx.data_ptr(), z.data_ptr(), int(emb_bases), int(grad_bases),
+            int(world), x.data_ptr(), float(cell_size), _host_floats(origin, 3), int(grid_dim), nb_lut.data_ptr(),
+            bidx.data_ptr(), grad_z.data_ptr(), n, int(n_emb), z.shape[1], _stream(dev)))
+    return grad_z

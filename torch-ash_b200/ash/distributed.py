@@ -283,18 +283,42 @@ class _ShardedGridQuery(torch.autograd.Function):
             grid.engine.backend, grid._emb_bases, grid.world, grid.num_embeddings, grid.embedding_dim, x, *geom,
             interpolation)
         ctx.save_for_backward(x, block_idx)
-        ctx.grid, ctx.geom, ctx.interpolation = grid, geom, interpolation
+        ctx.grid, ctx.geom, ctx.interpolation, ctx.embeddings = grid, geom, interpolation, embeddings
         ctx.mark_non_differentiable(masks)
         return y, masks
 
     @staticmethod
     def backward(ctx, z, _grad_masks):
         x, block_idx = ctx.saved_tensors
-        grid = ctx.grid
-        grad_x = backend.grid_query_backward_sharded(
-            grid.engine.backend, z.contiguous(), grid._emb_bases, grid._grad_bases, grid.world, grid.num_embeddings, x,
-            *ctx.geom, block_idx, ctx.interpolation, need_grad_x=bool(ctx.needs_input_grad[1]))
+        grad_x = _ShardedGridQueryBackward.apply(z.contiguous(), ctx.embeddings, x, block_idx, ctx.grid, ctx.geom,
+                                                 ctx.interpolation, bool(ctx.needs_input_grad[1]))
         return None, grad_x, None, None   # the embedding gradient went straight into the owners' shards
+
+
+class _ShardedGridQueryBackward(torch.autograd.Function):
+    """First-order backward of the sharded query, itself differentiable w.r.t. the incoming gradient
+    (and, through the owners' gradient shards, the embeddings) so that gradient-of-gradient losses
+    train; the double-backward gradient w.r.t. positions is dropped as in ash/grid_query.py."""
+
+    @staticmethod
+    def forward(ctx, z, embeddings, x, block_idx, grid, geom, interpolation, need_grad_x):
+        ctx.save_for_backward(z, x, block_idx)
+        ctx.grid, ctx.geom, ctx.interpolation = grid, geom, interpolation
+        ctx.set_materialize_grads(False)
+        return backend.grid_query_backward_sharded(
+            grid.engine.backend, z, grid._emb_bases, grid._grad_bases, grid.world, grid.num_embeddings, x, *geom,
+            block_idx, interpolation, need_grad_x=need_grad_x)
+
+    @staticmethod
+    def backward(ctx, grad_grad_x):
+        if grad_grad_x is None:
+            return (None,) * 8
+        z, x, block_idx = ctx.saved_tensors
+        grid = ctx.grid
+        grad_z = backend.grid_query_backward_backward_sharded(
+            grid.engine.backend, grad_grad_x.contiguous(), z, grid._emb_bases, grid._grad_bases, grid.world,
+            grid.num_embeddings, x, *ctx.geom, block_idx, ctx.interpolation)
+        return (grad_z,) + (None,) * 7
 
 
 class ShardedSparseDenseGrid(UnBoundedSparseDenseGrid):

@@ -887,6 +887,33 @@ int ashb_grid_query_backward_sharded(ashb_map* m, int interp, const float* z, co
     return ASHB_OK;
 }
 
+int ashb_grid_query_backward_backward_sharded(ashb_map* m, int interp, const float* grad_grad_x, const float* z,
+                                              const void* const* emb_bases_dev, void* const* grad_bases_dev,
+                                              int world, const float* x, double cell_size, const float* origin,
+                                              int G, const int32_t* nb_lut, const int32_t* block_idx, float* grad_z,
+                                              int64_t n, int64_t n_emb, int64_t D, void* stream) {
+    if (int rc = check_query_args(ASHB_F32, interp, n, n_emb, (int64_t)G * G * G, D)) return rc;
+    if (n == 0) return ASHB_OK;
+    ASHB_REQUIRE(grad_grad_x && z && grad_z && grad_bases_dev, "null buffer");
+    ShardedSource src;
+    if (int rc = make_sharded_source(m, emb_bases_dev, grad_bases_dev, world, x, cell_size, origin, G, nb_lut,
+                                     block_idx, nullptr, nullptr, n_emb, &src))
+        return rc;
+    DeviceGuard guard(m->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const void* ptrs[] = {z, grad_z};
+    const Shape sh = pick_shape(D, sizeof(float), ptrs, 2);
+    const int64_t threads = n << sh.lane_shift;
+    const unsigned grid = (unsigned)((threads + 255) / 256);
+    const float scale = (float)(1.0 / cell_size);
+    float* none = nullptr;
+    ASHB_VEC_SWITCH(float, sh,
+                    (query_backward_backward_kernel<float, VEC, ShardedSource><<<grid, 256, 0, st>>>(
+                            grad_grad_x, z, none, src, grad_z, none, scale, n, (int)D, sh.lane_shift, interp)));
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
 int ashb_grid_query_backward_backward(ashb_map* m, int dtype, int interp, const void* grad_grad_x, const void* z,
                                       const void* embeddings, const float* x, double cell_size,
                                       const float* origin, int G, const int32_t* nb_lut,
