@@ -457,8 +457,8 @@ int ashb_route_by_owner(const int32_t* keys, int64_t n, int key_dim, int world, 
  * arrays [world] of the shards' addresses as mapped into this GPU (peer memory).  The map and
  * nb_lut are this rank's replicas of the block structure (n_emb = global number of rows).  The
  * forward reads corner rows from their owners with plain loads; the backward ADDS gradient rows
- * straight into the owners' gradient shards with vector reductions (and writes grad_x, or skips it
- * when NULL).  The caller orders the launches across the ranks: parameters must be final on every
+ * straight into the owners' gradient shards with vector reductions unless need_grad_embeddings is 0
+ * (a pass that only wants d/dx), and writes grad_x, or skips it when NULL.  The caller orders the launches across the ranks: parameters must be final on every
  * rank before any forward, and every backward must be complete before a gradient shard is read. */
 int ashb_grid_query_forward_sharded(ashb_map* map, int interp, const void* const* emb_bases_dev, int world,
                                     const float* x, double cell_size, const float* origin, int G,
@@ -467,7 +467,8 @@ int ashb_grid_query_forward_sharded(ashb_map* map, int interp, const void* const
 int ashb_grid_query_backward_sharded(ashb_map* map, int interp, const float* z, const void* const* emb_bases_dev,
                                      void* const* grad_bases_dev, int world, const float* x, double cell_size,
                                      const float* origin, int G, const int32_t* nb_lut, const int32_t* block_idx,
-                                     float* grad_x, int64_t n, int64_t n_emb, int64_t D, void* stream);
+                                     float* grad_x, int need_grad_embeddings, int64_t n, int64_t n_emb, int64_t D,
+                                     void* stream);
 
 /* Double backward over the sharded table (as ashb_grid_query_backward_backward): grad_z [n][D] is
  * written, the embedding gradient is ADDED into the owners' gradient shards. */

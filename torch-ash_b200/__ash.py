@@ -84,7 +84,7 @@ _lib.ashb_grid_query_forward_sharded.argtypes = [_vp, _int, _vp, _int, _vp, _c.c
 _lib.ashb_grid_query_backward_backward_sharded.argtypes = [_vp, _int, _vp, _vp, _vp, _vp, _int, _vp, _c.c_double, _vp, _int,
                                                            _vp, _vp, _vp, _i64, _i64, _i64, _vp]
 _lib.ashb_grid_query_backward_sharded.argtypes = [_vp, _int, _vp, _vp, _vp, _int, _vp, _c.c_double, _vp, _int, _vp, _vp,
-                                                  _vp, _i64, _i64, _i64, _vp]
+                                                  _vp, _int, _i64, _i64, _i64, _vp]
 _lib.ashb_measure_random_reads.argtypes = [_vp, _i64, _i64, _int, _c.c_uint32, _vp, _vp]
 _lib.ashb_marching_cubes_count.argtypes = [_vp] * 9 + [_f32, _f32, _i64, _i64, _i64, _c.POINTER(_i64), _c.POINTER(_i64), _vp]
 _lib.ashb_marching_cubes_fill.argtypes = [_vp] * 11 + [_i64, _vp, _i64, _f32, _int, _i64, _i64, _i64, _vp]
@@ -997,8 +997,9 @@ def grid_query_forward_sharded(hashmap, emb_bases, world, n_emb, embedding_dim, 
 
 
 def grid_query_backward_sharded(hashmap, z, emb_bases, grad_bases, world, n_emb, x, cell_size, origin, grid_dim, nb_lut,
-                                block_idx, interpolation, need_grad_x=True):
-    """Adds the embedding gradient into the owners' gradient shards; returns grad_x (N, 3) or None."""
+                                block_idx, interpolation, need_grad_x=True, need_grad_embeddings=True):
+    """Adds the embedding gradient into the owners' gradient shards (unless not needed); returns
+    grad_x (N, 3) or None."""
     x = _cuda(x, "x", torch.float32)
     z = _cuda(z, "z", torch.float32)
     nb_lut = _cuda(nb_lut, "nb_lut", torch.int32)
@@ -1006,12 +1007,15 @@ def grid_query_backward_sharded(hashmap, z, emb_bases, grad_bases, world, n_emb,
     n, dev = x.shape[0], x.device
     if z.dim() != 2 or z.shape[0] != n or bidx.shape != (n,) or nb_lut.shape != (n_emb, 8):
         raise RuntimeError("z must be (N, D), block_idx (N,), nb_lut int32 (num_embeddings, 8)")
+    if not need_grad_x and not need_grad_embeddings:
+        return None
     grad_x = torch.empty((n, 3), dtype=torch.float32, device=dev) if need_grad_x else None
     with torch.cuda.device(dev):
         _check(_lib.ashb_grid_query_backward_sharded(
             hashmap._h, _interp_code(interpolation), z.data_ptr(), int(emb_bases), int(grad_bases), int(world),
             x.data_ptr(), float(cell_size), _host_floats(origin, 3), int(grid_dim), nb_lut.data_ptr(), bidx.data_ptr(),
-            grad_x.data_ptr() if need_grad_x else None, n, int(n_emb), z.shape[1], _stream(dev)))
+            grad_x.data_ptr() if need_grad_x else None, int(bool(need_grad_embeddings)), n, int(n_emb), z.shape[1],
+            _stream(dev)))
     return grad_x
 
 

@@ -290,8 +290,12 @@ class _ShardedGridQuery(torch.autograd.Function):
     @staticmethod
     def backward(ctx, z, _grad_masks):
         x, block_idx = ctx.saved_tensors
+        from .grid_query import _engine_wants_gradient_of
+
+        # a pass that only asks for d/dx (the first-order pass of an eikonal term) must not add to the shards
+        need_grad_emb = bool(ctx.needs_input_grad[0]) and _engine_wants_gradient_of(ctx.embeddings)
         grad_x = _ShardedGridQueryBackward.apply(z.contiguous(), ctx.embeddings, x, block_idx, ctx.grid, ctx.geom,
-                                                 ctx.interpolation, bool(ctx.needs_input_grad[1]))
+                                                 ctx.interpolation, bool(ctx.needs_input_grad[1]), need_grad_emb)
         return None, grad_x, None, None   # the embedding gradient went straight into the owners' shards
 
 
@@ -301,24 +305,24 @@ class _ShardedGridQueryBackward(torch.autograd.Function):
     train; the double-backward gradient w.r.t. positions is dropped as in ash/grid_query.py."""
 
     @staticmethod
-    def forward(ctx, z, embeddings, x, block_idx, grid, geom, interpolation, need_grad_x):
+    def forward(ctx, z, embeddings, x, block_idx, grid, geom, interpolation, need_grad_x, need_grad_emb):
         ctx.save_for_backward(z, x, block_idx)
         ctx.grid, ctx.geom, ctx.interpolation = grid, geom, interpolation
         ctx.set_materialize_grads(False)
         return backend.grid_query_backward_sharded(
             grid.engine.backend, z, grid._emb_bases, grid._grad_bases, grid.world, grid.num_embeddings, x, *geom,
-            block_idx, interpolation, need_grad_x=need_grad_x)
+            block_idx, interpolation, need_grad_x=need_grad_x, need_grad_embeddings=need_grad_emb)
 
     @staticmethod
     def backward(ctx, grad_grad_x):
         if grad_grad_x is None:
-            return (None,) * 8
+            return (None,) * 9
         z, x, block_idx = ctx.saved_tensors
         grid = ctx.grid
         grad_z = backend.grid_query_backward_backward_sharded(
             grid.engine.backend, grad_grad_x.contiguous(), z, grid._emb_bases, grid._grad_bases, grid.world,
             grid.num_embeddings, x, *ctx.geom, block_idx, ctx.interpolation)
-        return (grad_z,) + (None,) * 7
+        return (grad_z,) + (None,) * 8
 
 
 class ShardedSparseDenseGrid(UnBoundedSparseDenseGrid):

@@ -859,10 +859,12 @@ int ashb_grid_query_forward_sharded(ashb_map* m, int interp, const void* const* 
 int ashb_grid_query_backward_sharded(ashb_map* m, int interp, const float* z, const void* const* emb_bases_dev,
                                      void* const* grad_bases_dev, int world, const float* x, double cell_size,
                                      const float* origin, int G, const int32_t* nb_lut, const int32_t* block_idx,
-                                     float* grad_x, int64_t n, int64_t n_emb, int64_t D, void* stream) {
+                                     float* grad_x, int need_grad_embeddings, int64_t n, int64_t n_emb, int64_t D,
+                                     void* stream) {
     if (int rc = check_query_args(ASHB_F32, interp, n, n_emb, (int64_t)G * G * G, D)) return rc;
     if (n == 0) return ASHB_OK;
-    ASHB_REQUIRE(z && grad_bases_dev, "null buffer");
+    ASHB_REQUIRE(z && (grad_bases_dev || !need_grad_embeddings), "null buffer");
+    ASHB_REQUIRE(need_grad_embeddings || grad_x, "nothing to compute");
     ShardedSource src;
     if (int rc = make_sharded_source(m, emb_bases_dev, grad_bases_dev, world, x, cell_size, origin, G, nb_lut,
                                      block_idx, nullptr, nullptr, n_emb, &src))
@@ -876,7 +878,10 @@ int ashb_grid_query_backward_sharded(ashb_map* m, int interp, const float* z, co
     const float scale = (float)(1.0 / cell_size);
     float* none = nullptr;
     ASHB_VEC_SWITCH(float, sh,
-                    if (grad_x != nullptr) {
+                    if (!need_grad_embeddings) {
+                        query_backward_forward_kernel<float, VEC, ShardedSource, true, false><<<grid, 256, 0, st>>>(
+                                z, none, src, none, grad_x, scale, n, (int)D, sh.lane_shift, interp);
+                    } else if (grad_x != nullptr) {
                         query_backward_forward_kernel<float, VEC, ShardedSource, true><<<grid, 256, 0, st>>>(
                                 z, none, src, none, grad_x, scale, n, (int)D, sh.lane_shift, interp);
                     } else {
