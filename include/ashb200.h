@@ -483,25 +483,34 @@ int ashb_grid_query_backward_backward_sharded(ashb_map* map, int interp, const f
  * reference).  Every rank has a mailbox of mailbox_bytes, mapped into every other rank;
  * peer_bases_dev is a DEVICE array [world] with the address of every rank's mailbox as seen from
  * this rank.  Sections of a mailbox: inbox (int4 records {k0, k1, k2, position}; world regions of
- * region_capacity records, region r written by rank r), counts int32 [world], answers int64
- * [answer_capacity].  Keys of 1 to 3 columns.
+ * region_capacity <= 2^26 records, region r written by rank r), counts int32 [world], answers int64
+ * [world][region_capacity] (region o written by owner o, in the order of its inbox region).  A
+ * batch has at most answer_capacity keys.  Keys of 1 to 3 columns.
  *   ashb_peer_route_keys   writes every key of the batch into its owner's inbox and publishes the
- *                          per-region counts; cursor_dev int32 [world] scratch; records beyond
- *                          region_capacity are dropped and ASHB_STATUS_CAPACITY is or-ed into
- *                          status_dev.
- *   ashb_peer_find_answer  probes the records of this rank's inbox and stores each answer (global
- *                          index local * world + rank, or -1) into the asker's answers section at
- *                          the recorded position.
+ *                          per-region counts; cursor_dev int32 [world] scratch; where_dev int32 [n]
+ *                          (or NULL) receives owner << 26 | slot of every key (-1: dropped);
+ *                          records beyond region_capacity are dropped and ASHB_STATUS_CAPACITY is
+ *                          or-ed into status_dev.
+ *   ashb_peer_find_answer  probes the records of this rank's inbox and stores the answers (global
+ *                          index local * world + rank, or -1) into its region of the asker's
+ *                          answers section, contiguously in inbox order.
+ *   ashb_peer_unpack_answers  the asker's side, after the second barrier: indices int64 [n] (0 for
+ *                          a miss) and masks uint8 [n] gathered from its own answers section.
  * The caller orders the two across the ranks (all route calls complete before any answer call
  * starts, all answer calls complete before the answers are read or the next route call starts),
  * e.g. with a small collective on the same stream between them.  No host synchronisation. */
 int ashb_peer_route_keys(const int32_t* keys, int64_t n, int key_dim, int world, int rank,
                          void* const* peer_bases_dev, int64_t mailbox_bytes, int64_t inbox_offset,
                          int64_t counts_offset, int64_t answers_offset, int64_t region_capacity,
-                         int64_t answer_capacity, int32_t* cursor_dev, uint32_t* status_dev, void* stream);
+                         int64_t answer_capacity, int32_t* cursor_dev, int32_t* where_dev, uint32_t* status_dev,
+                         void* stream);
 int ashb_peer_find_answer(ashb_map* map, int world, int rank, void* const* peer_bases_dev, int64_t mailbox_bytes,
                           int64_t inbox_offset, int64_t counts_offset, int64_t answers_offset,
                           int64_t region_capacity, int64_t answer_capacity, void* stream);
+int ashb_peer_unpack_answers(const int32_t* where_dev, int64_t n, int world, int rank, void* const* peer_bases_dev,
+                             int64_t mailbox_bytes, int64_t inbox_offset, int64_t counts_offset,
+                             int64_t answers_offset, int64_t region_capacity, int64_t answer_capacity,
+                             int64_t* indices, uint8_t* masks, void* stream);
 /* Insert-if-absent (erase == 0) or erase (erase != 0) of the records in this rank's inbox, after an
  * ashb_peer_route_keys on every rank and the barrier; nothing goes back to the askers. */
 int ashb_peer_update(ashb_map* map, int erase, int world, int rank, void* const* peer_bases_dev,

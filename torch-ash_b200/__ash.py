@@ -76,7 +76,8 @@ _lib.ashb_render_accumulate_backward.argtypes = [_vp, _vp, _vp, _vp, _i64, _i64,
 _lib.ashb_isosurface_extraction.argtypes = [_vp] * 9 + [_i64, _c.POINTER(_i64), _vp, _f32, _f32, _int, _i64, _i64, _i64, _vp]
 _lib.ashb_set_find_cooperative.argtypes = [_int]
 _lib.ashb_set_scatter_aggregation.argtypes = [_int]
-_lib.ashb_peer_route_keys.argtypes = [_vp, _i64, _int, _int, _int, _vp] + [_i64] * 6 + [_vp, _vp, _vp]
+_lib.ashb_peer_route_keys.argtypes = [_vp, _i64, _int, _int, _int, _vp] + [_i64] * 6 + [_vp, _vp, _vp, _vp]
+_lib.ashb_peer_unpack_answers.argtypes = [_vp, _i64, _int, _int, _vp] + [_i64] * 6 + [_vp, _vp, _vp]
 _lib.ashb_peer_find_answer.argtypes = [_vp, _int, _int, _vp] + [_i64] * 6 + [_vp]
 _lib.ashb_peer_update.argtypes = [_vp, _int, _int, _int, _vp] + [_i64] * 6 + [_vp]
 _lib.ashb_grid_query_forward_sharded.argtypes = [_vp, _int, _vp, _int, _vp, _c.c_double, _vp, _int, _vp, _vp, _vp, _vp,
@@ -950,12 +951,24 @@ def render_rays_backward(hashmap, embeddings, nb_lut, cell_size, origin, ray_o_w
 # (peer_bases_dev: address of the device array of mailbox addresses, mailbox_bytes, inbox_offset,
 # counts_offset, answers_offset, region_capacity, answer_capacity).
 
-def peer_route_keys(keys, world, rank, layout, cursor, status):
+def peer_route_keys(keys, world, rank, layout, cursor, status, where=None):
     keys = _cuda(keys, "keys", torch.int32)
     n, dim = keys.shape
     with torch.cuda.device(keys.device):
         _check(_lib.ashb_peer_route_keys(keys.data_ptr(), n, dim, int(world), int(rank), *[int(v) for v in layout],
-                                         cursor.data_ptr(), status.data_ptr(), _stream(keys.device)))
+                                         cursor.data_ptr(), where.data_ptr() if where is not None else None,
+                                         status.data_ptr(), _stream(keys.device)))
+
+
+def peer_unpack_answers(where, n, world, rank, layout):
+    """(indices int64 (n,), masks bool (n,)) gathered from this rank's own answers section."""
+    dev = where.device
+    indices = torch.empty(n, dtype=torch.int64, device=dev)
+    masks = torch.empty(n, dtype=torch.bool, device=dev)
+    with torch.cuda.device(dev):
+        _check(_lib.ashb_peer_unpack_answers(where.data_ptr(), int(n), int(world), int(rank), *[int(v) for v in layout],
+                                             indices.data_ptr(), masks.data_ptr(), _stream(dev)))
+    return indices, masks
 
 
 def peer_find_answer(hashmap, world, rank, layout):

@@ -82,7 +82,8 @@ class _Route:
 
 class _PeerMailbox:
     """Symmetric device memory of the peer transport: one mailbox per rank, mapped into every
-    rank (``torch.distributed._symmetric_memory``), laid out as inbox | counts | answers."""
+    rank (``torch.distributed._symmetric_memory``), laid out as inbox | counts | answers (``world``
+    regions each), plus the local note of where every key of the current batch went."""
 
     def __init__(self, world: int, rank: int, max_batch: int, device, group) -> None:
         import torch.distributed._symmetric_memory as symm
@@ -91,12 +92,12 @@ class _PeerMailbox:
         inbox_bytes = world * self.max_batch * 16
         counts_offset = (inbox_bytes + 255) // 256 * 256
         answers_offset = counts_offset + 256
-        total = answers_offset + self.max_batch * 8
+        total = answers_offset + world * self.max_batch * 8
         self.buffer = symm.empty(total, dtype=torch.uint8, device=device)
         self.handle = symm.rendezvous(self.buffer, group if group is not None else dist.group.WORLD)
         self.layout = (self.handle.buffer_ptrs_dev, total, 0, counts_offset, answers_offset, self.max_batch,
                        self.max_batch)
-        self.answers = self.buffer[answers_offset:answers_offset + self.max_batch * 8].view(torch.int64)
+        self.where = torch.empty(self.max_batch, dtype=torch.int32, device=device)
         self.cursor = torch.zeros(world, dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.token = torch.zeros(1, dtype=torch.int32, device=device)
@@ -189,13 +190,11 @@ class PartitionedHashMap:
         box = self.mailbox
         keys = keys.to(self.device, torch.int32).contiguous()
         assert keys.dim() == 2 and keys.shape[1] == self.key_dim, "keys shape mismatch"
-        backend.peer_route_keys(keys, self.world, self.rank, box.layout, box.cursor, box.status)
+        backend.peer_route_keys(keys, self.world, self.rank, box.layout, box.cursor, box.status, where=box.where)
         box.barrier()                      # every inbox is complete
         backend.peer_find_answer(self.engine.backend, self.world, self.rank, box.layout)
         box.barrier()                      # every answer has landed; the inboxes may be reused
-        answers = box.answers[:keys.shape[0]].clone()
-        found = answers >= 0
-        return answers.clamp_(min=0), found
+        return backend.peer_unpack_answers(box.where, keys.shape[0], self.world, self.rank, box.layout)
 
     def local_items(self) -> Tuple[torch.Tensor, torch.Tensor]:
         """This rank's (keys, GLOBAL indices)."""

@@ -7,8 +7,11 @@
 //           the write position comes from a LOCAL cursor (one atomic per warp and owner) and no
 //           remote atomic is needed; the per-region counts are published to the owners at the end.
 //   (stream-ordered barrier across the ranks: a collective on a one-element tensor)
-//   answer  every owner probes the records of its inbox and stores each answer (global index or
-//           -1) straight into the ASKER's answer buffer at the recorded position.
+//   answer  every owner probes the records of its inbox and stores the answers (global index or
+//           -1) straight into the ASKER's answer buffer, region by region in inbox order, so that
+//           the peer stores of a warp are contiguous (scattered 8-byte peer stores ran at a
+//           fraction of the link rate); the asker remembers, per key, which owner and slot it
+//           used and gathers its answers locally afterwards.
 //   (barrier)
 //
 // Neither kernel waits on another GPU: ordering comes from the barriers the host enqueues between
@@ -36,15 +39,18 @@ struct PeerLayout {
     void* const* bases;      // device array [world]: base address of every rank's mailbox as mapped here
     int64_t inbox_offset;    // int4 records, world regions of region_capacity each
     int64_t counts_offset;   // int32 [world]: records in each region
-    int64_t answers_offset;  // int64 [answer_capacity]
+    int64_t answers_offset;  // int64 [world][region_capacity]: region o = answers of owner o, in inbox order
     int64_t region_capacity;
     int64_t answer_capacity;
     int world, rank;
 };
 
+constexpr int kWhereOwnerShift = 26;  // where[i] = owner << 26 | slot
+
 template <int DIM>
 __global__ void __launch_bounds__(256) peer_route_kernel(const int32_t* __restrict__ keys, int64_t n, PeerLayout L,
-                                                         int* __restrict__ cursor, uint32_t* __restrict__ status) {
+                                                         int* __restrict__ cursor, int32_t* __restrict__ where,
+                                                         uint32_t* __restrict__ status) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int lane = threadIdx.x & 31;
     const bool live = i < n;
@@ -61,10 +67,12 @@ __global__ void __launch_bounds__(256) peer_route_kernel(const int32_t* __restri
     const int64_t slot = (int64_t)base + __popc(peers & lanemask_lt());
     if (slot >= L.region_capacity) {
         atomicOr(status, ASHB_STATUS_CAPACITY);
+        if (where) where[i] = -1;
         return;
     }
     int4* inbox = reinterpret_cast<int4*>(static_cast<char*>(L.bases[owner]) + L.inbox_offset);
     inbox[(int64_t)L.rank * L.region_capacity + slot] = make_int4(k0, k1, k2, (int)i);
+    if (where) where[i] = (int)((unsigned)owner << kWhereOwnerShift | (unsigned)slot);
 }
 
 __global__ void peer_publish_counts_kernel(PeerLayout L, const int* __restrict__ cursor) {
@@ -84,9 +92,26 @@ __global__ void __launch_bounds__(256) peer_answer_kernel(Table16 t, PeerLayout 
     const int4 rec = __ldcg(reinterpret_cast<const int4*>(mine + L.inbox_offset) + (int64_t)region * L.region_capacity + j);
     const int idx = lookup(t, rec.x, rec.y, rec.z, 0);
     const long long answer = idx >= 0 ? (long long)idx * L.world + L.rank : -1ll;
-    if (rec.w < 0 || rec.w >= L.answer_capacity) return;  // a position no batch can have
     long long* answers = reinterpret_cast<long long*>(static_cast<char*>(L.bases[region]) + L.answers_offset);
-    answers[rec.w] = answer;
+    answers[(int64_t)L.rank * L.region_capacity + j] = answer;   // my region of the asker's answers
+}
+
+// The asker's side: answer of key i = answers[owner(i)][slot(i)] of its own mailbox.
+__global__ void __launch_bounds__(256) peer_unpack_kernel(PeerLayout L, const int32_t* __restrict__ where, int64_t n,
+                                                          int64_t* __restrict__ indices, uint8_t* __restrict__ masks) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int w = where[i];
+    long long answer = -1;
+    if (w >= 0) {
+        const int owner = (int)((unsigned)w >> kWhereOwnerShift);
+        const int64_t slot = (unsigned)w & ((1u << kWhereOwnerShift) - 1);
+        const char* mine = static_cast<const char*>(L.bases[L.rank]);
+        if (owner < L.world && slot < L.region_capacity)
+            answer = __ldcg(reinterpret_cast<const long long*>(mine + L.answers_offset) + (int64_t)owner * L.region_capacity + slot);
+    }
+    indices[i] = answer >= 0 ? answer : 0;
+    masks[i] = (uint8_t)(answer >= 0);
 }
 
 // insert-if-absent / erase of the records in this rank's inbox (no answers go back)
@@ -118,13 +143,14 @@ using namespace ashb;
 static int check_layout(const PeerLayout& L, int64_t mailbox_bytes) {
     ASHB_REQUIRE(L.bases != nullptr, "null peer table");
     ASHB_REQUIRE(L.world >= 1 && L.world <= kPeerMaxWorld && L.rank >= 0 && L.rank < L.world, "bad world / rank");
-    ASHB_REQUIRE(L.region_capacity >= 1 && L.answer_capacity >= 1 && L.answer_capacity <= 0x7fffffffll,
-                 "bad capacities");
+    ASHB_REQUIRE(L.region_capacity >= 1 && L.region_capacity <= (1ll << kWhereOwnerShift) && L.answer_capacity >= 1 &&
+                         L.answer_capacity <= 0x7fffffffll,
+                 "bad capacities (a region holds at most 2^26 records)");
     ASHB_REQUIRE(L.inbox_offset >= 0 && L.inbox_offset % 16 == 0 && L.counts_offset % 4 == 0 && L.answers_offset % 8 == 0,
                  "misaligned mailbox sections");
     const int64_t inbox_end = L.inbox_offset + (int64_t)L.world * L.region_capacity * 16;
     const int64_t counts_end = L.counts_offset + (int64_t)L.world * 4;
-    const int64_t answers_end = L.answers_offset + L.answer_capacity * 8;
+    const int64_t answers_end = L.answers_offset + (int64_t)L.world * L.region_capacity * 8;
     ASHB_REQUIRE(inbox_end <= L.counts_offset && counts_end <= L.answers_offset && answers_end <= mailbox_bytes,
                  "mailbox sections overlap or exceed the mailbox");
     return ASHB_OK;
@@ -135,7 +161,8 @@ extern "C" {
 int ashb_peer_route_keys(const int32_t* keys, int64_t n, int key_dim, int world, int rank,
                          void* const* peer_bases_dev, int64_t mailbox_bytes, int64_t inbox_offset,
                          int64_t counts_offset, int64_t answers_offset, int64_t region_capacity,
-                         int64_t answer_capacity, int32_t* cursor_dev, uint32_t* status_dev, void* stream) {
+                         int64_t answer_capacity, int32_t* cursor_dev, int32_t* where_dev, uint32_t* status_dev,
+                         void* stream) {
     const PeerLayout L{peer_bases_dev, inbox_offset, counts_offset, answers_offset, region_capacity, answer_capacity,
                        world, rank};
     if (int rc = check_layout(L, mailbox_bytes)) return rc;
@@ -148,9 +175,9 @@ int ashb_peer_route_keys(const int32_t* keys, int64_t n, int key_dim, int world,
     if (n > 0) {
         const unsigned grid = (unsigned)((n + 255) / 256);
         switch (key_dim) {
-            case 1: peer_route_kernel<1><<<grid, 256, 0, st>>>(keys, n, L, cursor_dev, status_dev); break;
-            case 2: peer_route_kernel<2><<<grid, 256, 0, st>>>(keys, n, L, cursor_dev, status_dev); break;
-            default: peer_route_kernel<3><<<grid, 256, 0, st>>>(keys, n, L, cursor_dev, status_dev); break;
+            case 1: peer_route_kernel<1><<<grid, 256, 0, st>>>(keys, n, L, cursor_dev, where_dev, status_dev); break;
+            case 2: peer_route_kernel<2><<<grid, 256, 0, st>>>(keys, n, L, cursor_dev, where_dev, status_dev); break;
+            default: peer_route_kernel<3><<<grid, 256, 0, st>>>(keys, n, L, cursor_dev, where_dev, status_dev); break;
         }
         ASHB_LAUNCH_CHECK();
     }
@@ -171,6 +198,22 @@ int ashb_peer_find_answer(ashb_map* m, int world, int rank, void* const* peer_ba
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const dim3 grid((unsigned)((region_capacity + 255) / 256), (unsigned)world);
     peer_answer_kernel<<<grid, 256, 0, st>>>(table16_of(m), L);
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+int ashb_peer_unpack_answers(const int32_t* where_dev, int64_t n, int world, int rank, void* const* peer_bases_dev,
+                             int64_t mailbox_bytes, int64_t inbox_offset, int64_t counts_offset,
+                             int64_t answers_offset, int64_t region_capacity, int64_t answer_capacity,
+                             int64_t* indices, uint8_t* masks, void* stream) {
+    const PeerLayout L{peer_bases_dev, inbox_offset, counts_offset, answers_offset, region_capacity, answer_capacity,
+                       world, rank};
+    if (int rc = check_layout(L, mailbox_bytes)) return rc;
+    ASHB_REQUIRE(n >= 0 && n <= answer_capacity, "bad count");
+    if (n == 0) return ASHB_OK;
+    ASHB_REQUIRE(where_dev && indices && masks, "null buffer");
+    peer_unpack_kernel<<<(unsigned)((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(L, where_dev, n,
+                                                                                                   indices, masks);
     ASHB_LAUNCH_CHECK();
     return ASHB_OK;
 }
