@@ -463,12 +463,12 @@ int ashb_route_by_owner(const int32_t* keys, int64_t n, int key_dim, int world, 
 int ashb_grid_query_forward_sharded(ashb_map* map, int interp, const void* const* emb_bases_dev, int world,
                                     const float* x, double cell_size, const float* origin, int G,
                                     const int32_t* nb_lut, float* out, uint8_t* masks, int32_t* block_idx_out,
-                                    int64_t n, int64_t n_emb, int64_t D, void* stream);
+                                    float* rows_out, int64_t n, int64_t n_emb, int64_t D, void* stream);
 int ashb_grid_query_backward_sharded(ashb_map* map, int interp, const float* z, const void* const* emb_bases_dev,
                                      void* const* grad_bases_dev, int world, const float* x, double cell_size,
                                      const float* origin, int G, const int32_t* nb_lut, const int32_t* block_idx,
-                                     float* grad_x, int need_grad_embeddings, int64_t n, int64_t n_emb, int64_t D,
-                                     void* stream);
+                                     float* grad_x, int need_grad_embeddings, const float* rows_in, int64_t n,
+                                     int64_t n_emb, int64_t D, void* stream);
 
 /* Double backward over the sharded table (as ashb_grid_query_backward_backward): grad_z [n][D] is
  * written, the embedding gradient is ADDED into the owners' gradient shards. */
@@ -476,7 +476,8 @@ int ashb_grid_query_backward_backward_sharded(ashb_map* map, int interp, const f
                                               const void* const* emb_bases_dev, void* const* grad_bases_dev,
                                               int world, const float* x, double cell_size, const float* origin,
                                               int G, const int32_t* nb_lut, const int32_t* block_idx, float* grad_z,
-                                              int64_t n, int64_t n_emb, int64_t D, void* stream);
+                                              const float* rows_in, int64_t n, int64_t n_emb, int64_t D,
+                                              void* stream);
 
 /* ---------------------------------------------------------------- peer-memory transport
  * find over the key-hash-partitioned map without a data collective (no counterpart in the

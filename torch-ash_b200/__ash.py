@@ -81,11 +81,11 @@ _lib.ashb_peer_unpack_answers.argtypes = [_vp, _i64, _int, _int, _vp] + [_i64] *
 _lib.ashb_peer_find_answer.argtypes = [_vp, _int, _int, _vp] + [_i64] * 6 + [_vp]
 _lib.ashb_peer_update.argtypes = [_vp, _int, _int, _int, _vp] + [_i64] * 6 + [_vp]
 _lib.ashb_grid_query_forward_sharded.argtypes = [_vp, _int, _vp, _int, _vp, _c.c_double, _vp, _int, _vp, _vp, _vp, _vp,
-                                                 _i64, _i64, _i64, _vp]
+                                                 _vp, _i64, _i64, _i64, _vp]
 _lib.ashb_grid_query_backward_backward_sharded.argtypes = [_vp, _int, _vp, _vp, _vp, _vp, _int, _vp, _c.c_double, _vp, _int,
-                                                           _vp, _vp, _vp, _i64, _i64, _i64, _vp]
+                                                           _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]
 _lib.ashb_grid_query_backward_sharded.argtypes = [_vp, _int, _vp, _vp, _vp, _int, _vp, _c.c_double, _vp, _int, _vp, _vp,
-                                                  _vp, _int, _i64, _i64, _i64, _vp]
+                                                  _vp, _int, _vp, _i64, _i64, _i64, _vp]
 _lib.ashb_measure_random_reads.argtypes = [_vp, _i64, _i64, _int, _c.c_uint32, _vp, _vp]
 _lib.ashb_marching_cubes_count.argtypes = [_vp] * 9 + [_f32, _f32, _i64, _i64, _i64, _c.POINTER(_i64), _c.POINTER(_i64), _vp]
 _lib.ashb_marching_cubes_fill.argtypes = [_vp] * 11 + [_i64, _vp, _i64, _f32, _int, _i64, _i64, _i64, _vp]
@@ -991,8 +991,9 @@ def peer_update(hashmap, erase, world, rank, layout):
 # as mapped into this GPU.  No counterpart in the reference.
 
 def grid_query_forward_sharded(hashmap, emb_bases, world, n_emb, embedding_dim, x, cell_size, origin, grid_dim, nb_lut,
-                               interpolation):
-    """Returns (features (N, D) float32, masks bool (N,), block_idx int32 (N,))."""
+                               interpolation, keep_rows=False):
+    """Returns (features (N, D) float32, masks bool (N,), block_idx int32 (N,), rows): ``rows`` is
+    the local copy (N, 8, D) of the fetched corner rows when ``keep_rows``, else None."""
     x = _cuda(x, "x", torch.float32)
     nb_lut = _cuda(nb_lut, "nb_lut", torch.int32)
     if x.dim() != 2 or x.shape[1] != 3 or nb_lut.shape != (n_emb, 8):
@@ -1001,16 +1002,18 @@ def grid_query_forward_sharded(hashmap, emb_bases, world, n_emb, embedding_dim, 
     out = torch.empty((n, embedding_dim), dtype=torch.float32, device=dev)
     masks = torch.empty(n, dtype=torch.bool, device=dev)
     bidx = torch.empty(n, dtype=torch.int32, device=dev)
+    # rows of queries that resolve to nothing are never written -- and never read back either
+    rows = torch.empty((n, 8, embedding_dim), dtype=torch.float32, device=dev) if keep_rows else None
     with torch.cuda.device(dev):
         _check(_lib.ashb_grid_query_forward_sharded(
             hashmap._h, _interp_code(interpolation), int(emb_bases), int(world), x.data_ptr(), float(cell_size),
             _host_floats(origin, 3), int(grid_dim), nb_lut.data_ptr(), out.data_ptr(), masks.data_ptr(), bidx.data_ptr(),
-            n, int(n_emb), int(embedding_dim), _stream(dev)))
-    return out, masks, bidx
+            rows.data_ptr() if keep_rows else None, n, int(n_emb), int(embedding_dim), _stream(dev)))
+    return out, masks, bidx, rows
 
 
 def grid_query_backward_sharded(hashmap, z, emb_bases, grad_bases, world, n_emb, x, cell_size, origin, grid_dim, nb_lut,
-                                block_idx, interpolation, need_grad_x=True, need_grad_embeddings=True):
+                                block_idx, interpolation, need_grad_x=True, need_grad_embeddings=True, rows=None):
     """Adds the embedding gradient into the owners' gradient shards (unless not needed); returns
     grad_x (N, 3) or None."""
     x = _cuda(x, "x", torch.float32)
@@ -1027,13 +1030,13 @@ def grid_query_backward_sharded(hashmap, z, emb_bases, grad_bases, world, n_emb,
         _check(_lib.ashb_grid_query_backward_sharded(
             hashmap._h, _interp_code(interpolation), z.data_ptr(), int(emb_bases), int(grad_bases), int(world),
             x.data_ptr(), float(cell_size), _host_floats(origin, 3), int(grid_dim), nb_lut.data_ptr(), bidx.data_ptr(),
-            grad_x.data_ptr() if need_grad_x else None, int(bool(need_grad_embeddings)), n, int(n_emb), z.shape[1],
-            _stream(dev)))
+            grad_x.data_ptr() if need_grad_x else None, int(bool(need_grad_embeddings)),
+            rows.data_ptr() if rows is not None else None, n, int(n_emb), z.shape[1], _stream(dev)))
     return grad_x
 
 
 def grid_query_backward_backward_sharded(hashmap, grad_grad_x, z, emb_bases, grad_bases, world, n_emb, x, cell_size,
-                                         origin, grid_dim, nb_lut, block_idx, interpolation):
+                                         origin, grid_dim, nb_lut, block_idx, interpolation, rows=None):
     """Adds the second-order embedding gradient into the owners' gradient shards; returns grad_z (N, D)."""
     x = _cuda(x, "x", torch.float32)
     z = _cuda(z, "z", torch.float32)
@@ -1048,5 +1051,6 @@ def grid_query_backward_backward_sharded(hashmap, grad_grad_x, z, emb_bases, gra
         _check(_lib.ashb_grid_query_backward_backward_sharded(
             hashmap._h, _interp_code(interpolation), ggx.data_ptr(), z.data_ptr(), int(emb_bases), int(grad_bases),
             int(world), x.data_ptr(), float(cell_size), _host_floats(origin, 3), int(grid_dim), nb_lut.data_ptr(),
-            bidx.data_ptr(), grad_z.data_ptr(), n, int(n_emb), z.shape[1], _stream(dev)))
+            bidx.data_ptr(), grad_z.data_ptr(), rows.data_ptr() if rows is not None else None, n, int(n_emb), z.shape[1],
+            _stream(dev)))
     return grad_z

@@ -278,9 +278,11 @@ class _ShardedGridQuery(torch.autograd.Function):
     @staticmethod
     def forward(ctx, embeddings, x, grid, interpolation):
         geom = grid._sharded_geometry()
-        y, masks, block_idx = backend.grid_query_forward_sharded(
+        keep = grid.keep_fetched_rows and x.requires_grad and torch.is_grad_enabled()
+        y, masks, block_idx, rows = backend.grid_query_forward_sharded(
             grid.engine.backend, grid._emb_bases, grid.world, grid.num_embeddings, grid.embedding_dim, x, *geom,
-            interpolation)
+            interpolation, keep_rows=keep)
+        ctx.rows = rows   # local copy of the fetched corner rows: the backward passes need not cross the link again
         ctx.save_for_backward(x, block_idx)
         ctx.grid, ctx.geom, ctx.interpolation, ctx.embeddings = grid, geom, interpolation, embeddings
         ctx.mark_non_differentiable(masks)
@@ -294,7 +296,8 @@ class _ShardedGridQuery(torch.autograd.Function):
         # a pass that only asks for d/dx (the first-order pass of an eikonal term) must not add to the shards
         need_grad_emb = bool(ctx.needs_input_grad[0]) and _engine_wants_gradient_of(ctx.embeddings)
         grad_x = _ShardedGridQueryBackward.apply(z.contiguous(), ctx.embeddings, x, block_idx, ctx.grid, ctx.geom,
-                                                 ctx.interpolation, bool(ctx.needs_input_grad[1]), need_grad_emb)
+                                                 ctx.interpolation, bool(ctx.needs_input_grad[1]), need_grad_emb,
+                                                 ctx.rows)
         return None, grad_x, None, None   # the embedding gradient went straight into the owners' shards
 
 
@@ -304,24 +307,24 @@ class _ShardedGridQueryBackward(torch.autograd.Function):
     train; the double-backward gradient w.r.t. positions is dropped as in ash/grid_query.py."""
 
     @staticmethod
-    def forward(ctx, z, embeddings, x, block_idx, grid, geom, interpolation, need_grad_x, need_grad_emb):
+    def forward(ctx, z, embeddings, x, block_idx, grid, geom, interpolation, need_grad_x, need_grad_emb, rows):
         ctx.save_for_backward(z, x, block_idx)
-        ctx.grid, ctx.geom, ctx.interpolation = grid, geom, interpolation
+        ctx.grid, ctx.geom, ctx.interpolation, ctx.rows = grid, geom, interpolation, rows
         ctx.set_materialize_grads(False)
         return backend.grid_query_backward_sharded(
             grid.engine.backend, z, grid._emb_bases, grid._grad_bases, grid.world, grid.num_embeddings, x, *geom,
-            block_idx, interpolation, need_grad_x=need_grad_x, need_grad_embeddings=need_grad_emb)
+            block_idx, interpolation, need_grad_x=need_grad_x, need_grad_embeddings=need_grad_emb, rows=rows)
 
     @staticmethod
     def backward(ctx, grad_grad_x):
         if grad_grad_x is None:
-            return (None,) * 9
+            return (None,) * 10
         z, x, block_idx = ctx.saved_tensors
         grid = ctx.grid
         grad_z = backend.grid_query_backward_backward_sharded(
             grid.engine.backend, grad_grad_x.contiguous(), z, grid._emb_bases, grid._grad_bases, grid.world,
-            grid.num_embeddings, x, *ctx.geom, block_idx, ctx.interpolation)
-        return (grad_z,) + (None,) * 8
+            grid.num_embeddings, x, *ctx.geom, block_idx, ctx.interpolation, rows=ctx.rows)
+        return (grad_z,) + (None,) * 9
 
 
 class ShardedSparseDenseGrid(UnBoundedSparseDenseGrid):
@@ -362,6 +365,9 @@ class ShardedSparseDenseGrid(UnBoundedSparseDenseGrid):
         self.embeddings.grad = self._grad_shard
         self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.fused = True
+        # Keep a local copy (N, 8, D) of the corner rows a forward fetched when the positions need a
+        # gradient: d/dx in the backward passes then reads the copy instead of the owners' memory.
+        self.keep_fetched_rows = True
 
     def _allocate_embeddings(self) -> torch.Tensor:
         import torch.distributed._symmetric_memory as symm

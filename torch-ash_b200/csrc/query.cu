@@ -132,7 +132,9 @@ struct LutSource {
     template <typename T>
     __device__ __forceinline__ T* out_row(T* grad, int64_t b) const { return grad + b; }
     template <typename T, int VEC>
-    __device__ __forceinline__ Pack<T, VEC> load_row(const T* p) const { return load_pack<T, VEC>(p); }
+    __device__ __forceinline__ Pack<T, VEC> corner(const T* emb, int64_t b, int64_t, int, int ch, int) const {
+        return load_pack<T, VEC>(emb + b + ch);
+    }
 
 
     __device__ __forceinline__ bool resolve(int64_t q, int lane, int64_t D, int64_t* base, float* off) const {
@@ -179,7 +181,9 @@ struct FusedSource {
     template <typename T>
     __device__ __forceinline__ T* out_row(T* grad, int64_t b) const { return grad + b; }
     template <typename T, int VEC>
-    __device__ __forceinline__ Pack<T, VEC> load_row(const T* p) const { return load_pack<T, VEC>(p); }
+    __device__ __forceinline__ Pack<T, VEC> corner(const T* emb, int64_t b, int64_t, int, int ch, int) const {
+        return load_pack<T, VEC>(emb + b + ch);
+    }
 
     Table16 table;
     const float* __restrict__ x;          // (n, 3) world positions
@@ -235,11 +239,21 @@ struct ShardedSource : FusedSource {
     __device__ __forceinline__ T* out_row(T*, int64_t b) const {
         return static_cast<T*>(grad_bases[b >> kOwnerShift]) + (b & ((1ll << kOwnerShift) - 1));
     }
+    // Corner c of query q.  The forward can keep a LOCAL copy of the rows it fetched (rows_out,
+    // [n][8][D]) and the backward passes read that copy (rows_in) instead of crossing NVLink again.
+    float* __restrict__ rows_out;
+    const float* __restrict__ rows_in;
     template <typename T, int VEC>
-    __device__ __forceinline__ Pack<T, VEC> load_row(const T* p) const {
+    __device__ __forceinline__ Pack<T, VEC> corner(const T* emb, int64_t b, int64_t q, int c, int ch, int D) const {
         using V = typename Vec<T, VEC>::type;
         Pack<T, VEC> r;
-        *reinterpret_cast<V*>(r.v) = *reinterpret_cast<const V*>(p);  // plain load: the row may be a peer's
+        const int64_t kept = (q * 8 + c) * D + ch;
+        if (rows_in) {
+            *reinterpret_cast<V*>(r.v) = *reinterpret_cast<const V*>(reinterpret_cast<const T*>(rows_in) + kept);
+            return r;
+        }
+        *reinterpret_cast<V*>(r.v) = *reinterpret_cast<const V*>(in_row(emb, b) + ch);  // plain load: may be a peer's
+        if (rows_out) *reinterpret_cast<V*>(reinterpret_cast<T*>(rows_out) + kept) = *reinterpret_cast<const V*>(r.v);
         return r;
     }
 
@@ -296,7 +310,7 @@ __global__ void __launch_bounds__(256, Src::kForwardMinBlocks) query_forward_ker
         aw.init(interp, off);
         Pack<T, VEC> e[8];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) e[c] = src.template load_row<T, VEC>(src.in_row(emb, base[c]) + ch);
+        for (int c = 0; c < 8; ++c) e[c] = src.template corner<T, VEC>(emb, base[c], q, c, ch, D);
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
             const T w = aw.weight(c);
@@ -337,7 +351,7 @@ __global__ void __launch_bounds__(256, ASHB_BWD_MIN_BLOCKS) query_backward_forwa
             Pack<T, VEC> e[8];
             if (NEED_GO) {
 #pragma unroll
-                for (int c = 0; c < 8; ++c) e[c] = src.template load_row<T, VEC>(src.in_row(emb, base[c]) + ch);
+                for (int c = 0; c < 8; ++c) e[c] = src.template corner<T, VEC>(emb, base[c], q, c, ch, D);
             }
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
@@ -423,7 +437,7 @@ __global__ void __launch_bounds__(256) query_backward_forward_agg_kernel(
     Pack<T, VEC> e[8];
     if (NEED_GO && valid) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c) e[c] = src.template load_row<T, VEC>(src.in_row(emb, base[c]) + ch);
+        for (int c = 0; c < 8; ++c) e[c] = src.template corner<T, VEC>(emb, base[c], q, c, ch, D);
     }
     T go[3] = {0, 0, 0};
 #pragma unroll
@@ -499,7 +513,7 @@ __global__ void __launch_bounds__(256, ASHB_BWD_MIN_BLOCKS) query_backward_backw
         const Pack<T, VEC> zv = load_pack<T, VEC>(z + q * D + ch);
         Pack<T, VEC> e[8];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) e[c] = src.template load_row<T, VEC>(src.in_row(emb, base[c]) + ch);
+        for (int c = 0; c < 8; ++c) e[c] = src.template corner<T, VEC>(emb, base[c], q, c, ch, D);
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
             T wg[3];
@@ -828,7 +842,7 @@ int ashb_grid_query_backward(ashb_map* m, int dtype, int interp, const void* z, 
 static int make_sharded_source(ashb_map* m, const void* const* emb_bases, void* const* grad_bases, int world,
                                const float* x, double cell_size, const float* origin, int G, const int32_t* nb_lut,
                                const int32_t* gi_in, int32_t* gi_out, uint8_t* mask_out, int64_t n_emb,
-                               ShardedSource* out) {
+                               float* rows_out, const float* rows_in, ShardedSource* out) {
     ASHB_REQUIRE(world >= 1 && world <= 64 && emb_bases != nullptr, "bad world size or null shard table");
     FusedSource f;
     if (int rc = make_fused_source(m, x, cell_size, origin, G, nb_lut, gi_in, gi_out, mask_out, n_emb, &f)) return rc;
@@ -837,6 +851,8 @@ static int make_sharded_source(ashb_map* m, const void* const* emb_bases, void* 
     s.emb_bases = emb_bases;
     s.grad_bases = grad_bases;
     s.world = world;
+    s.rows_out = rows_out;
+    s.rows_in = rows_in;
     *out = s;
     return ASHB_OK;
 }
@@ -844,13 +860,13 @@ static int make_sharded_source(ashb_map* m, const void* const* emb_bases, void* 
 int ashb_grid_query_forward_sharded(ashb_map* m, int interp, const void* const* emb_bases_dev, int world,
                                     const float* x, double cell_size, const float* origin, int G,
                                     const int32_t* nb_lut, float* out, uint8_t* masks, int32_t* block_idx_out,
-                                    int64_t n, int64_t n_emb, int64_t D, void* stream) {
+                                    float* rows_out, int64_t n, int64_t n_emb, int64_t D, void* stream) {
     if (int rc = check_query_args(ASHB_F32, interp, n, n_emb, (int64_t)G * G * G, D)) return rc;
     if (n == 0) return ASHB_OK;
     ASHB_REQUIRE(out && masks, "null buffer");
     ShardedSource src;
     if (int rc = make_sharded_source(m, emb_bases_dev, nullptr, world, x, cell_size, origin, G, nb_lut, nullptr,
-                                     block_idx_out, masks, n_emb, &src))
+                                     block_idx_out, masks, n_emb, rows_out, nullptr, &src))
         return rc;
     DeviceGuard guard(m->device);
     return forward_impl<float>(interp, nullptr, src, out, n, D, static_cast<cudaStream_t>(stream));
@@ -859,19 +875,19 @@ int ashb_grid_query_forward_sharded(ashb_map* m, int interp, const void* const* 
 int ashb_grid_query_backward_sharded(ashb_map* m, int interp, const float* z, const void* const* emb_bases_dev,
                                      void* const* grad_bases_dev, int world, const float* x, double cell_size,
                                      const float* origin, int G, const int32_t* nb_lut, const int32_t* block_idx,
-                                     float* grad_x, int need_grad_embeddings, int64_t n, int64_t n_emb, int64_t D,
-                                     void* stream) {
+                                     float* grad_x, int need_grad_embeddings, const float* rows_in, int64_t n,
+                                     int64_t n_emb, int64_t D, void* stream) {
     if (int rc = check_query_args(ASHB_F32, interp, n, n_emb, (int64_t)G * G * G, D)) return rc;
     if (n == 0) return ASHB_OK;
     ASHB_REQUIRE(z && (grad_bases_dev || !need_grad_embeddings), "null buffer");
     ASHB_REQUIRE(need_grad_embeddings || grad_x, "nothing to compute");
     ShardedSource src;
     if (int rc = make_sharded_source(m, emb_bases_dev, grad_bases_dev, world, x, cell_size, origin, G, nb_lut,
-                                     block_idx, nullptr, nullptr, n_emb, &src))
+                                     block_idx, nullptr, nullptr, n_emb, nullptr, rows_in, &src))
         return rc;
     DeviceGuard guard(m->device);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const void* ptrs[] = {z};
+    const void* ptrs[] = {z, rows_in};
     const Shape sh = pick_shape(D, sizeof(float), ptrs, 1);
     const int64_t threads = n << sh.lane_shift;
     const unsigned grid = (unsigned)((threads + 255) / 256);
@@ -896,17 +912,18 @@ int ashb_grid_query_backward_backward_sharded(ashb_map* m, int interp, const flo
                                               const void* const* emb_bases_dev, void* const* grad_bases_dev,
                                               int world, const float* x, double cell_size, const float* origin,
                                               int G, const int32_t* nb_lut, const int32_t* block_idx, float* grad_z,
-                                              int64_t n, int64_t n_emb, int64_t D, void* stream) {
+                                              const float* rows_in, int64_t n, int64_t n_emb, int64_t D,
+                                              void* stream) {
     if (int rc = check_query_args(ASHB_F32, interp, n, n_emb, (int64_t)G * G * G, D)) return rc;
     if (n == 0) return ASHB_OK;
     ASHB_REQUIRE(grad_grad_x && z && grad_z && grad_bases_dev, "null buffer");
     ShardedSource src;
     if (int rc = make_sharded_source(m, emb_bases_dev, grad_bases_dev, world, x, cell_size, origin, G, nb_lut,
-                                     block_idx, nullptr, nullptr, n_emb, &src))
+                                     block_idx, nullptr, nullptr, n_emb, nullptr, rows_in, &src))
         return rc;
     DeviceGuard guard(m->device);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const void* ptrs[] = {z, grad_z};
+    const void* ptrs[] = {z, grad_z, rows_in};
     const Shape sh = pick_shape(D, sizeof(float), ptrs, 2);
     const int64_t threads = n << sh.lane_shift;
     const unsigned grid = (unsigned)((threads + 255) / 256);
