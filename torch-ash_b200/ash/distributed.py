@@ -365,11 +365,12 @@ class ShardedSparseDenseGrid(UnBoundedSparseDenseGrid):
         self.embeddings.grad = self._grad_shard
         self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.fused = True
-        # Keep a local copy (N, 8, D) of the corner rows a forward fetched when the positions need a
-        # gradient: d/dx in the backward passes then reads the copy instead of the owners' memory.
-        # It costs a local write and read of every row to save the remote (world - 1) / world of
-        # them: measured a loss on 2 GPUs (9.25 against 7.99 ms per step), so on by default beyond.
-        self.keep_fetched_rows = self.world > 2
+        # Option: keep a local copy (N, 8, D) of the corner rows a forward fetched when the positions
+        # need a gradient, so that d/dx in the backward passes reads the copy instead of the owners'
+        # memory.  Measured no gain (2 GPUs: 9.25 against 7.99 ms per step; 8 GPUs: 13.3 against
+        # 12.2 ms): the step is bound by the 16-byte gradient reductions crossing the links, not by
+        # the second read of the rows.  Off by default.
+        self.keep_fetched_rows = False
 
     def _allocate_embeddings(self) -> torch.Tensor:
         import torch.distributed._symmetric_memory as symm
