@@ -143,7 +143,7 @@ def peer_find_worker(rank, world, port):
         from ash.distributed import PartitionedHashMap
 
         g = torch.Generator(device=device).manual_seed(100 + rank)
-        pm = PartitionedHashMap(3, 400_000, device, peer_max_batch=120_000)
+        pm = PartitionedHashMap(3, 400_000, device, peer_max_batch=180_000)
         keys = torch.randint(-300, 300, (100_000, 3), dtype=torch.int32, device=device, generator=g)
         pm.insert_keys(keys)
         for n in (100_000, 37_001 + 11 * rank, 0 if rank == 0 else 5):
@@ -174,9 +174,12 @@ def peer_find_worker(rank, world, port):
         theirs, _ = ref.local_items()
         order = lambda k: k[torch.argsort(k[:, 0].long() * 1_000_003 + k[:, 1].long() * 1009 + k[:, 2].long(), stable=True)]
         assert torch.equal(order(mine), order(theirs))   # every owner holds exactly the same keys
-        big = torch.randint(-300, 300, (130_000, 3), dtype=torch.int32, device=device, generator=g)
-        idx_b, ok_b = pm.find(big)        # beyond peer_max_batch: falls back to the collective path
-        assert idx_b.shape == (130_000,)
+        big = torch.randint(-300, 300, (190_000, 3), dtype=torch.int32, device=device, generator=g)
+        try:                              # beyond peer_max_batch: refused on every rank alike
+            pm.find(big)
+            raise AssertionError("an oversized batch was accepted")
+        except ValueError:
+            pass
     finally:
         dist.destroy_process_group()
 

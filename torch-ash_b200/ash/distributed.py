@@ -117,8 +117,8 @@ class PartitionedHashMap:
 
     def __init__(self, key_dim: int, capacity: int, device, group=None, slack: float = 1.25,
                  peer_max_batch: int = 0):
-        """``peer_max_batch`` > 0 (CUDA, key_dim <= 3): ``find`` on batches of up to that many keys
-        per rank goes over peer memory -- keys written straight into the owners' inboxes, answers
+        """``peer_max_batch`` > 0 (CUDA, key_dim <= 3): find / insert / erase on batches of up to that
+        many keys per rank (larger ones are refused) go over peer memory -- keys written straight into the owners' inboxes, answers
         straight back into the askers' buffers, two launches and two one-element collectives per
         rank -- instead of grouping + all-to-all(v) each way."""
         self.group = group
@@ -140,15 +140,24 @@ class PartitionedHashMap:
         route = _Route(keys, self.group)
         return route, route.forward()
 
+    def _over_peer_memory(self, keys: torch.Tensor) -> bool:
+        """Every rank must take the same path: with a mailbox, a batch beyond its size is an error
+        rather than a silent switch to the collectives that the other ranks would not follow."""
+        if self.mailbox is None:
+            return False
+        if keys.shape[0] > self.mailbox.max_batch:
+            raise ValueError(f"batch of {keys.shape[0]} keys exceeds peer_max_batch = {self.mailbox.max_batch}")
+        return True
+
     def insert_keys(self, keys: torch.Tensor) -> None:
-        if self.mailbox is not None and keys.shape[0] <= self.mailbox.max_batch:
+        if self._over_peer_memory(keys):
             return self._update_over_peer_memory(keys, erase=False)
         _, mine = self._route(keys)
         if mine.shape[0]:
             self.engine.insert_keys(mine)
 
     def erase(self, keys: torch.Tensor) -> None:
-        if self.mailbox is not None and keys.shape[0] <= self.mailbox.max_batch:
+        if self._over_peer_memory(keys):
             return self._update_over_peer_memory(keys, erase=True)
         _, mine = self._route(keys)
         if mine.shape[0]:
@@ -173,7 +182,7 @@ class PartitionedHashMap:
 
     def find(self, keys: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         """(global indices int64 (N,), masks bool (N,)); a miss has index 0 and mask False."""
-        if self.mailbox is not None and keys.shape[0] <= self.mailbox.max_batch:
+        if self._over_peer_memory(keys):
             return self._find_over_peer_memory(keys)
         route, mine = self._route(keys)
         if mine.shape[0]:
