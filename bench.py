@@ -695,9 +695,10 @@ def measure_bounded(ash, bw, device, peak):
             "rays_per_s": round(n_r / (step_ms * 1e-3) / 1e6, 3), "unit": "M rays/s",
             "samples_per_s": round(n_samples / (step_ms * 1e-3) / 1e6, 2)},
         "volume_rendering_train_step_fused": {
-            "what": "render_rays (near/far + sampling + query + sdf gradient + density + accumulation in one launch) "
-                    "+ loss + backward (one launch), fresh dense gradient; near/far included, which the row above "
-                    "leaves outside its timed step",
+            "what": "render_rays (near/far + sampling listed per ray in one launch, then query + sdf gradient + density "
+                    "+ accumulation by one warp per ray in a second) + loss + backward (one launch over the listed "
+                    "intervals), fresh dense gradient; near/far included, which the row above leaves outside its "
+                    "timed step",
             "rays": int(n_r), "samples": fused_samples, "ms": round(fused_ms, 3),
             "rays_per_s": round(n_r / (fused_ms * 1e-3) / 1e6, 3), "unit": "M rays/s",
             "samples_per_s": round(fused_samples / (fused_ms * 1e-3) / 1e6, 2),

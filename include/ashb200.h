@@ -450,6 +450,31 @@ int ashb_render_rays_backward(ashb_map* map, int interp, const float* embeddings
 int ashb_route_by_owner(const int32_t* keys, int64_t n, int key_dim, int world, int32_t* keys_out,
                         int64_t* perm_out, int64_t* counts_host, void* scratch_dev, void* stream);
 
+/* The same renderer with the samples of a ray evaluated in parallel: _intervals marches every ray
+ * once (one thread per ray) and lists its intervals, float32 [n_rays][stride][2] (t0, t1 in cell
+ * units), with counts int32 [n_rays] and near_far float32 [n_rays][2] (world units); intervals
+ * beyond `stride` are dropped and ASHB_STATUS_CAPACITY is set in the map's status word (stride =
+ * max_samples_per_ray + 2 always suffices).  _forward / _backward then spend one WARP per ray on
+ * the listed intervals (32 at a time, transmittance by a warp scan); `out` and the gradients are
+ * as for ashb_render_rays_forward / _backward, up to floating-point summation order. */
+int ashb_render_rays_intervals(ashb_map* map, int interp, const float* embeddings, int64_t n_emb, int grid_dim, int D,
+                               const int32_t* nb_lut, double cell_size, const float* origin,
+                               const float* ray_o_cell, const float* ray_d, const float* bbox_min_cell,
+                               const float* bbox_max_cell, float t_min_cell, float t_max_cell,
+                               int64_t max_samples_per_ray, int skip_missed, float* intervals, int32_t* counts,
+                               float* near_far, int64_t stride, int64_t n_rays, void* stream);
+int ashb_render_intervals_forward(ashb_map* map, int interp, const float* embeddings, int64_t n_emb, int grid_dim,
+                                  int D, const int32_t* nb_lut, double cell_size, const float* origin,
+                                  const float* ray_o_world, const float* ray_d, const float* beta,
+                                  const float* intervals, const int32_t* counts, const float* near_far, int64_t stride,
+                                  float* out, int64_t n_rays, void* stream);
+int ashb_render_intervals_backward(ashb_map* map, int interp, const float* embeddings, int64_t n_emb, int grid_dim,
+                                   int D, const int32_t* nb_lut, double cell_size, const float* origin,
+                                   const float* ray_o_world, const float* ray_d, const float* beta,
+                                   const float* intervals, const int32_t* counts, int64_t stride, const float* out,
+                                   const float* grad_out, float* grad_embeddings, float* grad_beta, int64_t n_rays,
+                                   void* stream);
+
 /* ---------------------------------------------------------------- table sharded over the GPUs of a box
  * ashb_grid_query_forward / _backward for an embedding table split by block over `world` GPUs
  * (no counterpart in the reference): block g lives on GPU g % world as row g / world of that

@@ -79,8 +79,9 @@ def loss_of(res, coef):
 CASES = [("bounded", 4, "linear"), ("bounded", 5, "linear"), ("unbounded", 4, "smooth_step"), ("unbounded", 8, "linear")]
 
 
+@pytest.mark.parametrize("parallel", [False, True])
 @pytest.mark.parametrize("kind,D,interpolation", CASES)
-def test_fused_renderer_matches_the_composed_chain(kind, D, interpolation):
+def test_fused_renderer_matches_the_composed_chain(kind, D, interpolation, parallel):
     grid = make_grid(kind, D, seed=3 + D)
     centre = torch.zeros(3, device=DEV) if kind == "bounded" else torch.tensor([0.3, -0.2, 0.1], device=DEV)
     n = 3000
@@ -102,7 +103,7 @@ def test_fused_renderer_matches_the_composed_chain(kind, D, interpolation):
     grid.embeddings.grad = None
     to_sigma.beta.grad = None
     beta = to_sigma.min_beta + to_sigma.beta.abs()
-    out = render_rays(grid, o, d, t_min, t_max, 48, beta, interpolation)
+    out = render_rays(grid, o, d, t_min, t_max, 48, beta, interpolation, parallel_samples=parallel)
     loss_of(out, coef).backward()
     ge, gb = grid.embeddings.grad, to_sigma.beta.grad
 
@@ -126,6 +127,13 @@ def test_rays_without_a_hit_can_be_skipped():
     with torch.no_grad():
         full = render_rays(grid, o, d, 0.05, 2.0, 32, beta)
         skip = render_rays(grid, o, d, 0.05, 2.0, 32, beta, skip_rays_without_hit=True)
+        listed = render_rays(grid, o, d, 0.05, 2.0, 32, beta, skip_rays_without_hit=True, parallel_samples=True)
+    for k in ("n_samples", "near", "far"):
+        assert torch.equal(listed[k], skip[k])
+    for k in ("rgb", "depth", "normal", "weights"):
+        torch.testing.assert_close(listed[k], skip[k], rtol=2e-4, atol=2e-5)
+    with torch.no_grad():
+        pass
     missed = full["near"].view(-1) < 0
     assert int(missed.sum()) >= 500 and int((~missed).sum()) > 500
     for k in ("rgb", "depth", "normal", "weights", "n_samples"):
@@ -143,8 +151,8 @@ def test_in_place_gradient_mode_and_empty_batch():
     dense, gb = grid.embeddings.grad.clone(), beta.grad.clone()
     grid.embeddings.grad, beta.grad = None, None
     grid.grad_mode = "in_place"
-    for _ in range(2):                       # accumulates: two passes give twice the gradient
-        out = render_rays(grid, o, d, 0.05, 2.0, 32, beta)
+    for parallel in (False, True):           # accumulates: two passes give twice the gradient
+        out = render_rays(grid, o, d, 0.05, 2.0, 32, beta, parallel_samples=parallel)
         (out["rgb"].sum() + out["depth"].sum()).backward()
     grid.grad_mode = "dense"
     scale = float(dense.abs().max())
@@ -163,7 +171,8 @@ def test_embedding_dim_below_four_is_refused():
         render_rays(grid, o, d, 0.05, 1.0, 8, torch.tensor([0.1], device=DEV))
 
 
-def test_fused_forward_against_the_cpu_oracle():
+@pytest.mark.parametrize("parallel", [False, True])
+def test_fused_forward_against_the_cpu_oracle(parallel):
     """Per-ray outputs of the one-launch renderer against the CPU oracle run stage by stage:
     oracle near/far -> oracle sampler -> oracle query forward + d/d offset -> numpy density ->
     oracle rendering quadrature."""
@@ -178,7 +187,8 @@ def test_fused_forward_against_the_cpu_oracle():
     o, d = make_rays(grid, n, 19, torch.zeros(3, device=DEV))
     t_min, t_max, max_samples, beta = 0.05, 2.0, 40, 0.03
     with torch.no_grad():
-        out = render_rays(grid, o, d, t_min, t_max, max_samples, torch.tensor([beta], device=DEV), "linear")
+        out = render_rays(grid, o, d, t_min, t_max, max_samples, torch.tensor([beta], device=DEV), "linear",
+                          parallel_samples=parallel)
 
     G, cs = grid.grid_dim, grid.cell_size
     keys, idx = grid.engine.items()

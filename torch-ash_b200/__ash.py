@@ -92,6 +92,11 @@ _lib.ashb_marching_cubes_fill.argtypes = [_vp] * 11 + [_i64, _vp, _i64, _f32, _i
 _RAY_ARGS = [_vp, _int, _vp, _i64, _int, _int, _vp, _c.c_double, _vp, _vp, _vp, _vp, _vp, _vp, _f32, _f32, _i64, _int, _vp]
 _lib.ashb_render_rays_forward.argtypes = _RAY_ARGS + [_vp, _i64, _vp]
 _lib.ashb_render_rays_backward.argtypes = _RAY_ARGS + [_vp, _vp, _vp, _vp, _i64, _vp]
+_RAY_GRID = [_vp, _int, _vp, _i64, _int, _int, _vp, _c.c_double, _vp]
+_lib.ashb_render_rays_intervals.argtypes = _RAY_GRID + [_vp, _vp, _vp, _vp, _f32, _f32, _i64, _int, _vp, _vp, _vp, _i64, _i64,
+                                                        _vp]
+_lib.ashb_render_intervals_forward.argtypes = _RAY_GRID + [_vp] * 6 + [_i64, _vp, _i64, _vp]
+_lib.ashb_render_intervals_backward.argtypes = _RAY_GRID + [_vp] * 5 + [_i64, _vp, _vp, _vp, _vp, _i64, _vp]
 _lib.ashb_grid_zero_rows.argtypes = [_vp, _int, _vp, _vp, _c.c_double, _vp, _int, _vp, _vp, _i64, _i64, _i64, _vp]
 
 STATUS_CAPACITY, STATUS_PROBE, STATUS_SPIN, STATUS_DUPLICATE = 1, 2, 4, 8
@@ -1054,3 +1059,83 @@ def grid_query_backward_backward_sharded(hashmap, grad_grad_x, z, emb_bases, gra
             bidx.data_ptr(), grad_z.data_ptr(), rows.data_ptr() if rows is not None else None, n, int(n_emb), z.shape[1],
             _stream(dev)))
     return grad_z
+
+
+def _ray_grid_args(hashmap, embeddings, nb_lut, cell_size, origin, interpolation):
+    emb = _cuda(embeddings, "embeddings", torch.float32)
+    if emb.dim() != 3 or emb.shape[2] < 4:
+        raise RuntimeError("ray rendering needs embeddings (num_embeddings, G^3, D >= 4): signed distance + colour")
+    G = round(emb.shape[1] ** (1.0 / 3.0))
+    if G ** 3 != emb.shape[1]:
+        raise RuntimeError("embeddings.shape[1] is not a cube")
+    lut = _cuda(nb_lut, "nb_lut", torch.int32)
+    org = (_f32 * 3)(*[float(v) for v in origin]) if origin is not None else None
+    args = [hashmap._h, _INTERP[interpolation], emb.data_ptr(), emb.shape[0], G, emb.shape[2], lut.data_ptr(),
+            float(cell_size), org]
+    return args, (emb, lut, org)
+
+
+def render_rays_intervals(hashmap, embeddings, nb_lut, cell_size, origin, ray_o_cell, ray_d, bbox_min_cell,
+                          bbox_max_cell, t_min_cell, t_max_cell, max_samples_per_ray, skip_missed,
+                          interpolation="linear"):
+    """March every ray once: (intervals (n, stride, 2) float32 in cell units, counts int32 (n,),
+    near_far float32 (n, 2) in world units)."""
+    args, keep = _ray_grid_args(hashmap, embeddings, nb_lut, cell_size, origin, interpolation)
+    oc = _cuda(ray_o_cell, "ray_o_cell", torch.float32)
+    d = _cuda(ray_d, "ray_d", torch.float32)
+    lo = _cuda(bbox_min_cell, "bbox_min", torch.float32).view(-1)
+    hi = _cuda(bbox_max_cell, "bbox_max", torch.float32).view(-1)
+    n, dev = oc.shape[0], oc.device
+    stride = int(max_samples_per_ray) + 2
+    intervals = torch.empty((n, stride, 2), dtype=torch.float32, device=dev)
+    counts = torch.empty(n, dtype=torch.int32, device=dev)
+    near_far = torch.empty((n, 2), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _check(_lib.ashb_render_rays_intervals(*args, oc.data_ptr(), d.data_ptr(), lo.data_ptr(), hi.data_ptr(),
+                                               float(t_min_cell), float(t_max_cell), int(max_samples_per_ray),
+                                               int(bool(skip_missed)), intervals.data_ptr(), counts.data_ptr(),
+                                               near_far.data_ptr(), stride, n, _stream(dev)))
+    return intervals, counts, near_far
+
+
+def render_intervals_forward(hashmap, embeddings, nb_lut, cell_size, origin, ray_o_world, ray_d, beta, intervals, counts,
+                             near_far, interpolation="linear"):
+    """(n_rays, 16) rows as ``render_rays_forward``, one warp per ray over the listed intervals."""
+    args, keep = _ray_grid_args(hashmap, embeddings, nb_lut, cell_size, origin, interpolation)
+    ow = _cuda(ray_o_world, "ray_o_world", torch.float32)
+    d = _cuda(ray_d, "ray_d", torch.float32)
+    b = _cuda(beta, "beta", torch.float32).view(-1)
+    n, dev = ow.shape[0], ow.device
+    out = torch.empty((n, 16), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _check(_lib.ashb_render_intervals_forward(*args, ow.data_ptr(), d.data_ptr(), b.data_ptr(), intervals.data_ptr(),
+                                                  counts.data_ptr(), near_far.data_ptr(), intervals.shape[1],
+                                                  out.data_ptr(), n, _stream(dev)))
+    return out
+
+
+def render_intervals_backward(hashmap, embeddings, nb_lut, cell_size, origin, ray_o_world, ray_d, beta, intervals, counts,
+                              out, grad_out, interpolation="linear", grad_embeddings_out=None):
+    """(grad_embeddings, grad_beta (1,)) as ``render_rays_backward``, without marching again."""
+    args, keep = _ray_grid_args(hashmap, embeddings, nb_lut, cell_size, origin, interpolation)
+    emb = keep[0]
+    ow = _cuda(ray_o_world, "ray_o_world", torch.float32)
+    d = _cuda(ray_d, "ray_d", torch.float32)
+    b = _cuda(beta, "beta", torch.float32).view(-1)
+    out = _cuda(out, "out", torch.float32)
+    go = _cuda(grad_out, "grad_out", torch.float32)
+    n, dev = ow.shape[0], ow.device
+    if out.shape != (n, 16) or go.shape != (n, 16):
+        raise RuntimeError("out and grad_out must be (n_rays, 16)")
+    if grad_embeddings_out is None:
+        ge = torch.zeros_like(emb)
+    else:
+        ge = grad_embeddings_out
+        if not (ge.is_cuda and ge.is_contiguous() and ge.shape == emb.shape and ge.dtype == emb.dtype):
+            raise RuntimeError("grad_embeddings_out must be a contiguous CUDA tensor shaped like embeddings")
+    gb = torch.zeros(1, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _check(_lib.ashb_render_intervals_backward(*args, ow.data_ptr(), d.data_ptr(), b.data_ptr(), intervals.data_ptr(),
+                                                   counts.data_ptr(), intervals.shape[1], out.data_ptr(), go.data_ptr(),
+                                                   ge.data_ptr(), gb.data_ptr(), n, _stream(dev)))
+    return ge, gb

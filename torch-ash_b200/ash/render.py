@@ -87,11 +87,22 @@ class SDFToDensity(nn.Module):
 
 
 class _RenderRays(torch.autograd.Function):
-    """One launch forward, one launch backward for the whole ray -> pixel composition."""
+    """One launch forward, one launch backward for the whole ray -> pixel composition -- or, with
+    ``parallel_samples``, a marching launch that lists every ray's intervals followed by a
+    warp-per-ray evaluation (and a backward that reuses the list)."""
 
     @staticmethod
-    def forward(ctx, embeddings, beta, geom, rays):
-        rows = backend.render_rays_forward(geom[0], embeddings, *geom[1:4], *rays, beta, geom[4])
+    def forward(ctx, embeddings, beta, geom, rays, parallel_samples):
+        ctx.listed = None
+        if parallel_samples:
+            o_world, o_cell, d = rays[0], rays[1], rays[2]
+            intervals, counts, near_far = backend.render_rays_intervals(
+                geom[0], embeddings, *geom[1:4], o_cell, d, *rays[3:], geom[4])
+            rows = backend.render_intervals_forward(geom[0], embeddings, *geom[1:4], o_world, d, beta, intervals,
+                                                    counts, near_far, geom[4])
+            ctx.listed = (intervals, counts)
+        else:
+            rows = backend.render_rays_forward(geom[0], embeddings, *geom[1:4], *rays, beta, geom[4])
         ctx.save_for_backward(embeddings, beta, rows)
         ctx.geom, ctx.rays = geom, rays
         return rows
@@ -101,17 +112,22 @@ class _RenderRays(torch.autograd.Function):
         embeddings, beta, rows = ctx.saved_tensors
         geom, rays = ctx.geom, ctx.rays
         grad_buffer = geom[5]
-        grad_embeddings, grad_beta = backend.render_rays_backward(
-            geom[0], embeddings, *geom[1:4], *rays, beta, rows, grad_rows.contiguous(), geom[4],
-            grad_embeddings_out=grad_buffer)
+        if ctx.listed is not None:
+            grad_embeddings, grad_beta = backend.render_intervals_backward(
+                geom[0], embeddings, *geom[1:4], rays[0], rays[2], beta, *ctx.listed, rows, grad_rows.contiguous(),
+                geom[4], grad_embeddings_out=grad_buffer)
+        else:
+            grad_embeddings, grad_beta = backend.render_rays_backward(
+                geom[0], embeddings, *geom[1:4], *rays, beta, rows, grad_rows.contiguous(), geom[4],
+                grad_embeddings_out=grad_buffer)
         if grad_buffer is not None or not ctx.needs_input_grad[0]:
             grad_embeddings = None
-        return grad_embeddings, grad_beta.view(beta.shape) if ctx.needs_input_grad[1] else None, None, None
+        return grad_embeddings, grad_beta.view(beta.shape) if ctx.needs_input_grad[1] else None, None, None, None
 
 
 def render_rays(grid, rays_o: torch.Tensor, rays_d: torch.Tensor, t_min: float, t_max: float,
                 max_samples_per_ray: int, beta: torch.Tensor, interpolation: str = "linear",
-                skip_rays_without_hit: bool = False) -> dict:
+                skip_rays_without_hit: bool = False, parallel_samples: Optional[bool] = None) -> dict:
     """Render rays through ``grid`` in one fused launch: what the reference's training step
     composes from ``grid.ray_find_near_far`` -> ``grid.ray_sample`` -> ``grid(x)`` ->
     ``autograd.grad(sdf, x)`` -> normalize -> ``SDFToDensity`` -> weights -> accumulation
@@ -121,6 +137,13 @@ def render_rays(grid, rays_o: torch.Tensor, rays_d: torch.Tensor, t_min: float, 
     density scale as a tensor of one element (``min_beta + |parameter|``).  Differentiable w.r.t.
     ``grid.embeddings`` (dense gradient, or added into ``embeddings.grad`` with
     ``grid.grad_mode = "in_place"``) and ``beta``; ray origins and directions get no gradient.
+
+    ``parallel_samples``: a marching launch lists every ray's intervals ((max_samples_per_ray + 2) x
+    8 bytes per ray) and a warp per ray evaluates them 32 at a time; the backward reuses the list.
+    Same results up to floating-point summation order.  It shortens the dependent chain of a ray, which
+    is what bounds small batches (8192 rays: forward 0.14 against 0.19 ms, backward 0.04 against
+    0.17 ms), and wastes lanes on large ones (262144 rays: 0.98 + 1.14 against 0.82 + 0.74 ms);
+    ``None`` picks it for batches of up to 32768 rays.
 
     Returns a dict of per-ray tensors: ``rgb`` (n, 3), ``depth`` (n, 1) = sum of weight * t_mid,
     ``normal`` (n, 3), ``weights`` (n, 1), ``eikonal_l1`` / ``eikonal_l2`` (n, 1) = sums over the
@@ -145,7 +168,9 @@ def render_rays(grid, rays_o: torch.Tensor, rays_d: torch.Tensor, t_min: float, 
                 grid.transform_world_to_cell(bbox_min).contiguous(), grid.transform_world_to_cell(bbox_max).contiguous(),
                 t_min / grid.cell_size, t_max / grid.cell_size, int(max_samples_per_ray), bool(skip_rays_without_hit))
     geom = (grid.engine.backend, grid._neighbor_lut32(), cell_size, origin, interpolation, grad_buffer)
-    rows = _RenderRays.apply(grid.embeddings, beta.to(torch.float32), geom, rays)
+    if parallel_samples is None:
+        parallel_samples = rays_o.shape[0] <= 32768
+    rows = _RenderRays.apply(grid.embeddings, beta.to(torch.float32), geom, rays, bool(parallel_samples))
     return {"rgb": rows[:, 0:3], "depth": rows[:, 3:4], "normal": rows[:, 4:7], "weights": rows[:, 7:8],
             "eikonal_l1": rows[:, 8:9], "eikonal_l2": rows[:, 9:10], "n_samples": rows[:, 10:11].detach(),
             "near": rows[:, 11:12].detach(), "far": rows[:, 12:13].detach()}

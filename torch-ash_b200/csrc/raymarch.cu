@@ -16,6 +16,8 @@
 // loads (one float4 each when the row stride allows).  The backward pass re-marches the ray and
 // needs no saved per-sample state: the suffix sum of the transmittance gradient is closed with the
 // forward outputs (sum_k g_k w_k = <grad_out, out> over the accumulated channels).
+#include <climits>
+
 #include "query.cuh"
 #include "sampler.cuh"
 
@@ -127,6 +129,51 @@ __device__ __forceinline__ void eval_sample(const RayGrid& G, const float* o_w, 
 #pragma unroll
     for (int k = 0; k < 3; ++k) s.nrm[k] = s.g[k] / den;
     s.sigma = density(s.sdf, beta, alpha) * s.hit;
+}
+
+// Gradient of one sample given d loss / d (its weight) = gw, its weight w, the transmittance T in
+// front of it and the sum of gw * w over the samples behind it: adds the embedding gradient of its
+// 8 corner rows and returns its contribution to d loss / d beta.
+template <bool ALIGNED>
+__device__ __forceinline__ float sample_gradient(const RayGrid& G, const Sample& s, const float* go, float w, float T,
+                                                 float gw, float behind, float beta, float alpha,
+                                                 float* __restrict__ grad_emb) {
+    // d loss / d sigma_j = dt_j * (g_j * (T_j - w_j) - sum_{k>j} g_k w_k)
+    const float dsigma = s.dt * (gw * (T - w) - behind) * s.hit;
+    // density(sdf, beta) = alpha * h, h = 0.5 + 0.5 * sign * expm1(-|sdf| / beta)
+    const float a = fabsf(s.sdf);
+    const float sgn = s.sdf > 0.f ? 1.f : (s.sdf < 0.f ? -1.f : 0.f);
+    const float ex = expf(-a / beta);
+    const float h = 0.5f + 0.5f * sgn * expm1f(-a / beta);
+    const float gbeta = dsigma * (-h * alpha * alpha + alpha * 0.5f * sgn * ex * a * alpha * alpha);
+    if (!s.ok) return gbeta;
+    const float dsdf = dsigma * (-0.5f * alpha * alpha * ex * sgn * sgn);
+    // d loss / d (world gradient of the signed distance): through the rendered normal and
+    // through the two eikonal sums
+    float dn[3] = {w * go[4], w * go[5], w * go[6]}, dg[3];
+    if (s.gnorm > 1e-12f) {
+        const float nd = s.nrm[0] * dn[0] + s.nrm[1] * dn[1] + s.nrm[2] * dn[2];
+        const float r = s.gnorm - 1.f;
+        const float eik = go[8] * (r > 0.f ? 1.f : (r < 0.f ? -1.f : 0.f)) + go[9] * 2.f * r;
+#pragma unroll
+        for (int k = 0; k < 3; ++k) dg[k] = (dn[k] - s.nrm[k] * nd) / s.gnorm + eik * s.nrm[k];
+    } else {
+#pragma unroll
+        for (int k = 0; k < 3; ++k) dg[k] = dn[k] / 1e-12f;
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        const float wc = s.aw.weight(c);
+        float wg[3];
+        s.aw.grad(c, wg);
+        float v[4];
+        v[0] = wc * dsdf + (wg[0] * dg[0] + wg[1] * dg[1] + wg[2] * dg[2]) * G.inv_cell;
+        v[1] = wc * w * go[0];
+        v[2] = wc * w * go[1];
+        v[3] = wc * w * go[2];
+        add_row4<ALIGNED>(grad_emb + s.base[c], v);
+    }
+    return gbeta;
 }
 
 // Near/far + the sampler's march as a resumable state: next() advances the ray to its next
@@ -287,46 +334,161 @@ __global__ void __launch_bounds__(128) render_rays_backward_kernel(RayGrid G, co
         const float gw = go[0] * s.rgb[0] + go[1] * s.rgb[1] + go[2] * s.rgb[2] + go[3] * s.t_mid +
                          go[4] * s.nrm[0] + go[5] * s.nrm[1] + go[6] * s.nrm[2] + go[7];
         prefix += gw * w;
-        // d loss / d sigma_j = dt_j * (g_j * (T_j - w_j) - sum_{k>j} g_k w_k)
-        const float dsigma = s.dt * (gw * (T - w) - (total - prefix)) * s.hit;
-        // density(sdf, beta) = alpha * h, h = 0.5 + 0.5 * sign * expm1(-|sdf| / beta)
-        const float a = fabsf(s.sdf);
-        const float sgn = s.sdf > 0.f ? 1.f : (s.sdf < 0.f ? -1.f : 0.f);
-        const float ex = expf(-a / beta);
-        const float h = 0.5f + 0.5f * sgn * expm1f(-a / beta);
-        gbeta += dsigma * (-h * alpha * alpha + alpha * 0.5f * sgn * ex * a * alpha * alpha);
-        if (!s.ok) continue;
-        const float dsdf = dsigma * (-0.5f * alpha * alpha * ex * sgn * sgn);
-        // d loss / d (world gradient of the signed distance): through the rendered normal and
-        // through the two eikonal sums
-        float dn[3] = {w * go[4], w * go[5], w * go[6]}, dg[3];
-        if (s.gnorm > 1e-12f) {
-            const float nd = s.nrm[0] * dn[0] + s.nrm[1] * dn[1] + s.nrm[2] * dn[2];
-            const float r = s.gnorm - 1.f;
-            const float eik = go[8] * (r > 0.f ? 1.f : (r < 0.f ? -1.f : 0.f)) + go[9] * 2.f * r;
-#pragma unroll
-            for (int k = 0; k < 3; ++k) dg[k] = (dn[k] - s.nrm[k] * nd) / s.gnorm + eik * s.nrm[k];
-        } else {
-#pragma unroll
-            for (int k = 0; k < 3; ++k) dg[k] = dn[k] / 1e-12f;
-        }
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            const float wc = s.aw.weight(c);
-            float wg[3];
-            s.aw.grad(c, wg);
-            float v[4];
-            v[0] = wc * dsdf + (wg[0] * dg[0] + wg[1] * dg[1] + wg[2] * dg[2]) * G.inv_cell;
-            v[1] = wc * w * go[0];
-            v[2] = wc * w * go[1];
-            v[3] = wc * w * go[2];
-            add_row4<ALIGNED>(grad_emb + s.base[c], v);
-        }
+        gbeta += sample_gradient<ALIGNED>(G, s, go, w, T, gw, total - prefix, beta, alpha, grad_emb);
     }
     // one atomic per warp for the density parameter
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) gbeta += __shfl_xor_sync(0xffffffffu, gbeta, o);
     if ((threadIdx.x & 31) == 0 && gbeta != 0.f) atomicAdd(grad_beta, gbeta);
+}
+
+// ---- the same renderer with the samples of a ray evaluated in parallel -------------------------
+// One thread per ray only marches (near/far + interval sampler) and writes the ray's intervals into
+// a fixed-stride list; then one WARP per ray evaluates 32 intervals at a time (queries, gradient of
+// the signed distance, density) and closes the transmittance with a warp scan.  The dependent chain
+// of a ray is then its probes plus ceil(samples / 32) evaluation rounds instead of one evaluation
+// per sample; the backward reuses the list and does not march at all.
+__global__ void __launch_bounds__(128) ray_intervals_kernel(RayGrid G, const float* __restrict__ ray_o_cell,
+                                                            const float* __restrict__ ray_d,
+                                                            float2* __restrict__ intervals, int* __restrict__ counts,
+                                                            float* __restrict__ near_far, int stride, int64_t n,
+                                                            uint32_t* __restrict__ status) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float o_c[3] = {ray_o_cell[3 * i], ray_o_cell[3 * i + 1], ray_o_cell[3 * i + 2]};
+    const float d[3] = {ray_d[3 * i], ray_d[3 * i + 1], ray_d[3 * i + 2]};
+    float near_w = 0.f, far_w = 0.f;
+    RayMarcher m;
+    m.start<false>(G, o_c, d, true, near_w, far_w);
+    int k = 0;
+    float t0c, t1c;
+    int blk[3], gi;
+    while (m.next(G, o_c, d, t0c, t1c, blk, gi)) {
+        if (k < stride)
+            intervals[i * stride + k] = make_float2(t0c, t1c);
+        else
+            atomicOr(status, ASHB_STATUS_CAPACITY);  // more intervals than the list holds: dropped
+        ++k;
+    }
+    counts[i] = k < stride ? k : stride;
+    near_far[2 * i] = near_w;
+    near_far[2 * i + 1] = far_w;
+}
+
+__device__ __forceinline__ float warp_scan_inclusive(float v, int lane) {
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float u = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += u;
+    }
+    return v;
+}
+
+template <bool ALIGNED>
+__global__ void __launch_bounds__(256) render_intervals_forward_kernel(
+        RayGrid G, const float* __restrict__ ray_o_world, const float* __restrict__ ray_d,
+        const float* __restrict__ beta_ptr, const float2* __restrict__ intervals, const int* __restrict__ counts,
+        const float* __restrict__ near_far, int stride, float* __restrict__ out, int64_t n) {
+    const int64_t ray = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (ray >= n) return;  // whole warps
+    const float o_w[3] = {ray_o_world[3 * ray], ray_o_world[3 * ray + 1], ray_o_world[3 * ray + 2]};
+    const float d[3] = {ray_d[3 * ray], ray_d[3 * ray + 1], ray_d[3 * ray + 2]};
+    const float beta = beta_ptr[0];
+    const float alpha = __frcp_rn(beta);
+    const int count = counts[ray];
+    const int no_hint[3] = {INT_MIN, INT_MIN, INT_MIN};
+    float acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+    float carry = 0.f;
+    for (int base = 0; base < count; base += 32) {
+        const int j = base + lane;
+        const bool live = j < count;
+        Sample s;
+        float tau = 0.f;
+        if (live) {
+            const float2 iv = intervals[ray * stride + j];
+            eval_sample<ALIGNED>(G, o_w, d, iv.x, iv.y, no_hint, -1, beta, alpha, s);
+            tau = s.sigma * s.dt;
+        }
+        const float incl = warp_scan_inclusive(tau, lane);
+        if (live) {
+            const float w = expf(-(carry + incl - tau)) * -expm1f(-tau);
+            acc[0] += w * s.rgb[0];
+            acc[1] += w * s.rgb[1];
+            acc[2] += w * s.rgb[2];
+            acc[3] += w * s.t_mid;
+            acc[4] += w * s.nrm[0];
+            acc[5] += w * s.nrm[1];
+            acc[6] += w * s.nrm[2];
+            acc[7] += w;
+            const float r = s.gnorm - 1.f;
+            acc[8] += fabsf(r);
+            acc[9] += r * r;
+        }
+        carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+#pragma unroll
+    for (int k = 0; k < 10; ++k) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], o);
+    }
+    if (lane == 0) {
+        float* row = out + ray * kRayOut;
+#pragma unroll
+        for (int k = 0; k < 10; ++k) row[k] = acc[k];
+        row[10] = (float)count;
+        row[11] = near_far[2 * ray];
+        row[12] = near_far[2 * ray + 1];
+        row[13] = row[14] = row[15] = 0.f;
+    }
+}
+
+template <bool ALIGNED>
+__global__ void __launch_bounds__(256) render_intervals_backward_kernel(
+        RayGrid G, const float* __restrict__ ray_o_world, const float* __restrict__ ray_d,
+        const float* __restrict__ beta_ptr, const float2* __restrict__ intervals, const int* __restrict__ counts,
+        int stride, const float* __restrict__ out, const float* __restrict__ grad_out, float* __restrict__ grad_emb,
+        float* __restrict__ grad_beta, int64_t n) {
+    const int64_t ray = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (ray >= n) return;  // whole warps
+    const float o_w[3] = {ray_o_world[3 * ray], ray_o_world[3 * ray + 1], ray_o_world[3 * ray + 2]};
+    const float d[3] = {ray_d[3 * ray], ray_d[3 * ray + 1], ray_d[3 * ray + 2]};
+    const float beta = beta_ptr[0];
+    const float alpha = __frcp_rn(beta);
+    const int count = counts[ray];
+    const int no_hint[3] = {INT_MIN, INT_MIN, INT_MIN};
+    float go[10];
+#pragma unroll
+    for (int k = 0; k < 10; ++k) go[k] = grad_out[ray * kRayOut + k];
+    float total = 0.f;  // sum over the ray of (d loss / d w_k) * w_k, from the forward outputs
+#pragma unroll
+    for (int k = 0; k < 8; ++k) total += go[k] * out[ray * kRayOut + k];
+    float carry_tau = 0.f, carry_gw = 0.f, gbeta = 0.f;
+    for (int base = 0; base < count; base += 32) {
+        const int j = base + lane;
+        const bool live = j < count;
+        Sample s;
+        float tau = 0.f, gw = 0.f;
+        if (live) {
+            const float2 iv = intervals[ray * stride + j];
+            eval_sample<ALIGNED>(G, o_w, d, iv.x, iv.y, no_hint, -1, beta, alpha, s);
+            tau = s.sigma * s.dt;
+            gw = go[0] * s.rgb[0] + go[1] * s.rgb[1] + go[2] * s.rgb[2] + go[3] * s.t_mid + go[4] * s.nrm[0] +
+                 go[5] * s.nrm[1] + go[6] * s.nrm[2] + go[7];
+        }
+        const float incl_tau = warp_scan_inclusive(tau, lane);
+        const float T = expf(-(carry_tau + incl_tau - tau));
+        const float w = live ? T * -expm1f(-tau) : 0.f;
+        const float incl_gw = warp_scan_inclusive(gw * w, lane);
+        if (live)
+            gbeta += sample_gradient<ALIGNED>(G, s, go, w, T, gw, total - (carry_gw + incl_gw), beta, alpha, grad_emb);
+        carry_tau += __shfl_sync(0xffffffffu, incl_tau, 31);
+        carry_gw += __shfl_sync(0xffffffffu, incl_gw, 31);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) gbeta += __shfl_xor_sync(0xffffffffu, gbeta, o);
+    if (lane == 0 && gbeta != 0.f) atomicAdd(grad_beta, gbeta);
 }
 
 }  // namespace ashb
@@ -335,11 +497,12 @@ using namespace ashb;
 
 static int make_ray_grid(RayGrid& g, ashb_map* m, int interp, const float* emb, int64_t n_emb, int grid_dim, int D,
                          const int32_t* nb_lut, double cell_size, const float* origin, const float* bbox_min,
-                         const float* bbox_max, float t_min, float t_max, int64_t max_samples, int skip_missed) {
+                         const float* bbox_max, float t_min, float t_max, int64_t max_samples, int skip_missed,
+                         bool marches = true) {
     ASHB_REQUIRE(m != nullptr && m->slots != nullptr, "null or destroyed map");
     ASHB_REQUIRE(m->key_dim == 3, "ray rendering needs a 3-D map");
     ASHB_REQUIRE(interp == ASHB_LINEAR || interp == ASHB_SMOOTH_STEP, "unknown interpolation");
-    ASHB_REQUIRE(emb && nb_lut && bbox_min && bbox_max, "null buffer");
+    ASHB_REQUIRE(emb && nb_lut && (!marches || (bbox_min && bbox_max)), "null buffer");
     ASHB_REQUIRE(n_emb > 0 && grid_dim >= 1 && D >= 4, "needs embedding_dim >= 4 (signed distance + colour)");
     ASHB_REQUIRE(cell_size > 0.0 && max_samples > 0, "bad cell size or sample limit");
     ASHB_REQUIRE(t_min == t_min && t_max == t_max && t_max - t_min < 3.0e38f, "ray range must be finite");
@@ -416,6 +579,85 @@ int ashb_render_rays_backward(ashb_map* map, int interp, const float* embeddings
     else
         render_rays_backward_kernel<false><<<grid, 128, 0, st>>>(g, ray_o_world, ray_o_cell, ray_d, beta, out, grad_out,
                                                                  grad_embeddings, grad_beta, n_rays);
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+int ashb_render_rays_intervals(ashb_map* map, int interp, const float* embeddings, int64_t n_emb, int grid_dim, int D,
+                               const int32_t* nb_lut, double cell_size, const float* origin,
+                               const float* ray_o_cell, const float* ray_d, const float* bbox_min_cell,
+                               const float* bbox_max_cell, float t_min_cell, float t_max_cell,
+                               int64_t max_samples_per_ray, int skip_missed, float* intervals, int32_t* counts,
+                               float* near_far, int64_t stride, int64_t n_rays, void* stream) {
+    RayGrid g;
+    if (int rc = make_ray_grid(g, map, interp, embeddings, n_emb, grid_dim, D, nb_lut, cell_size, origin, bbox_min_cell,
+                               bbox_max_cell, t_min_cell, t_max_cell, max_samples_per_ray, skip_missed))
+        return rc;
+    ASHB_REQUIRE(n_rays >= 0 && stride >= 1 && stride <= 0x7fffffffll, "bad ray count or stride");
+    if (n_rays == 0) return ASHB_OK;
+    ASHB_REQUIRE(ray_o_cell && ray_d && intervals && counts && near_far, "null buffer");
+    ASHB_REQUIRE(((uintptr_t)intervals & 7) == 0, "interval list must be 8-byte aligned");
+    DeviceGuard guard(map->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    ray_intervals_kernel<<<(unsigned)((n_rays + 127) / 128), 128, 0, st>>>(
+            g, ray_o_cell, ray_d, reinterpret_cast<float2*>(intervals), counts, near_far, (int)stride, n_rays,
+            map->status);
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+int ashb_render_intervals_forward(ashb_map* map, int interp, const float* embeddings, int64_t n_emb, int grid_dim,
+                                  int D, const int32_t* nb_lut, double cell_size, const float* origin,
+                                  const float* ray_o_world, const float* ray_d, const float* beta,
+                                  const float* intervals, const int32_t* counts, const float* near_far, int64_t stride,
+                                  float* out, int64_t n_rays, void* stream) {
+    RayGrid g;  // no marching here: the box and the ray range are not used
+    if (int rc = make_ray_grid(g, map, interp, embeddings, n_emb, grid_dim, D, nb_lut, cell_size, origin, nullptr,
+                               nullptr, 0.f, 1.f, 1, 0, false))
+        return rc;
+    ASHB_REQUIRE(n_rays >= 0 && stride >= 1, "bad ray count or stride");
+    if (n_rays == 0) return ASHB_OK;
+    ASHB_REQUIRE(ray_o_world && ray_d && beta && intervals && counts && near_far && out, "null buffer");
+    DeviceGuard guard(map->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const unsigned grid = (unsigned)((n_rays * 32 + 255) / 256);
+    const float2* iv = reinterpret_cast<const float2*>(intervals);
+    if (D % 4 == 0)
+        render_intervals_forward_kernel<true><<<grid, 256, 0, st>>>(g, ray_o_world, ray_d, beta, iv, counts, near_far,
+                                                                    (int)stride, out, n_rays);
+    else
+        render_intervals_forward_kernel<false><<<grid, 256, 0, st>>>(g, ray_o_world, ray_d, beta, iv, counts, near_far,
+                                                                     (int)stride, out, n_rays);
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+int ashb_render_intervals_backward(ashb_map* map, int interp, const float* embeddings, int64_t n_emb, int grid_dim,
+                                   int D, const int32_t* nb_lut, double cell_size, const float* origin,
+                                   const float* ray_o_world, const float* ray_d, const float* beta,
+                                   const float* intervals, const int32_t* counts, int64_t stride, const float* out,
+                                   const float* grad_out, float* grad_embeddings, float* grad_beta, int64_t n_rays,
+                                   void* stream) {
+    RayGrid g;  // no marching here: the box and the ray range are not used
+    if (int rc = make_ray_grid(g, map, interp, embeddings, n_emb, grid_dim, D, nb_lut, cell_size, origin, nullptr,
+                               nullptr, 0.f, 1.f, 1, 0, false))
+        return rc;
+    ASHB_REQUIRE(n_rays >= 0 && stride >= 1, "bad ray count or stride");
+    if (n_rays == 0) return ASHB_OK;
+    ASHB_REQUIRE(ray_o_world && ray_d && beta && intervals && counts && out && grad_out && grad_embeddings && grad_beta,
+                 "null buffer");
+    DeviceGuard guard(map->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const unsigned grid = (unsigned)((n_rays * 32 + 255) / 256);
+    const float2* iv = reinterpret_cast<const float2*>(intervals);
+    if (D % 4 == 0)
+        render_intervals_backward_kernel<true><<<grid, 256, 0, st>>>(g, ray_o_world, ray_d, beta, iv, counts,
+                                                                     (int)stride, out, grad_out, grad_embeddings,
+                                                                     grad_beta, n_rays);
+    else
+        render_intervals_backward_kernel<false><<<grid, 256, 0, st>>>(g, ray_o_world, ray_d, beta, iv, counts,
+                                                                      (int)stride, out, grad_out, grad_embeddings,
+                                                                      grad_beta, n_rays);
     ASHB_LAUNCH_CHECK();
     return ASHB_OK;
 }
