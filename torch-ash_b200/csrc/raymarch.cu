@@ -361,15 +361,15 @@ __global__ void __launch_bounds__(128) ray_intervals_kernel(RayGrid G, const flo
     RayMarcher m;
     m.start<false>(G, o_c, d, true, near_w, far_w);
     int k = 0;
-    float t0c, t1c;
-    int blk[3], gi;
-    while (m.next(G, o_c, d, t0c, t1c, blk, gi)) {
-        if (k < stride)
-            intervals[i * stride + k] = make_float2(t0c, t1c);
-        else
-            atomicOr(status, ASHB_STATUS_CAPACITY);  // more intervals than the list holds: dropped
-        ++k;
-    }
+    if (m.active)
+        march_intervals(G.table, o_c, d, m.tt, m.ray_far, m.cell_step, m.grid_step, m.cell2grid,
+                        [&](float seg_near, float seg_far) {
+                            if (k < stride)
+                                intervals[i * stride + k] = make_float2(seg_near, seg_far);
+                            else
+                                atomicOr(status, ASHB_STATUS_CAPACITY);  // more intervals than the list holds
+                            ++k;
+                        });
     counts[i] = k < stride ? k : stride;
     near_far[2 * i] = near_w;
     near_far[2 * i + 1] = far_w;

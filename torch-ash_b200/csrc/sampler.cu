@@ -53,29 +53,20 @@ __global__ void __launch_bounds__(128) ray_sample_kernel(Table16 t, const float*
     const float cell2grid = (float)(1.0 / (double)grid2cell);
     const float cell_step = sample_cell_step(ray_near, ray_far, max_samples);
     const float grid_step = cell_step * grid2cell;
-    float tt = ray_near, seg_near = ray_near;
     int64_t local = 0;
     int64_t start = 0, end = 0;
     if (FILL) {
         start = i == 0 ? 0 : prefix[i - 1];
         end = prefix[i];
     }
-    while (tt < ray_far) {
-        float p[3];
-        ray_at(o, d, tt, p);
-        if (!block_active(t, p, cell2grid)) {
-            tt += grid_step;
-        } else {
-            tt += cell_step;
-            if (FILL && start + local < end) {
-                ray_indices[start + local] = i;
-                t_nears[start + local] = seg_near;
-                t_fars[start + local] = tt;
-            }
-            seg_near = tt;
-            ++local;
+    march_intervals(t, o, d, ray_near, ray_far, cell_step, grid_step, cell2grid, [&](float seg_near, float seg_far) {
+        if (FILL && start + local < end) {
+            ray_indices[start + local] = i;
+            t_nears[start + local] = seg_near;
+            t_fars[start + local] = seg_far;
         }
-    }
+        ++local;
+    });
     if (!FILL) counts[i] = local;
     // The two passes must agree; a mismatch means the table changed in between.
     if (FILL && start + local != end) atomicOr(status, ASHB_STATUS_PROBE);

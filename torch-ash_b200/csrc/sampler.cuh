@@ -106,4 +106,53 @@ __device__ __forceinline__ float sample_cell_step(float ray_near, float ray_far,
     return (float)fmax(0.7, (double)((ray_far - ray_near) / (float)max_samples));
 }
 
+// The interval sampler's march (ash/src/sampler.cu:123-215) with four probes in flight: from
+// `near` to `far`, a cell step inside occupied blocks -- each such step is an interval, reported to
+// emit(t_start, t_end) -- and a block step outside.  The next positions are guessed from the kind of
+// step taken last, their probes are issued together, and the steps are replayed in order; the
+// first step whose outcome differs from the guess ends the round, because the positions after it
+// were guessed with the wrong stride.  `tt` goes through exactly the values of the
+// one-probe-at-a-time march.
+template <class Emit>
+__device__ __forceinline__ void march_intervals(const Table16& t, const float* o, const float* d, float ray_near,
+                                                float ray_far, float cell_step, float grid_step, float cell2grid,
+                                                Emit&& emit) {
+    constexpr int kAhead = 4;
+    float tt = ray_near, seg_near = ray_near;
+    bool guess_active = true;
+    while (tt < ray_far) {
+        const float stride_guess = guess_active ? cell_step : grid_step;
+        float ts[kAhead];
+        ProbeStart ps[kAhead];
+        float t_k = tt;
+#pragma unroll
+        for (int a = 0; a < kAhead; ++a) {
+            ts[a] = t_k;
+            float p[3];
+            ray_at(o, d, t_k, p);
+            ps[a] = probe_begin(t, p, cell2grid, t_k < ray_far);
+            t_k += stride_guess;
+        }
+#pragma unroll
+        for (int a = 0; a < kAhead; ++a) {
+            if (!(ts[a] < ray_far)) {
+                tt = ts[a];
+                break;
+            }
+            const bool active = probe_finish(t, ps[a]);
+            if (active) {
+                tt = ts[a] + cell_step;
+                emit(seg_near, tt);
+                seg_near = tt;
+            } else {
+                tt = ts[a] + grid_step;
+            }
+            if (active != guess_active) {
+                guess_active = active;
+                break;
+            }
+        }
+    }
+}
+
 }  // namespace ashb
