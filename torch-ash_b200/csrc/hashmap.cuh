@@ -217,6 +217,39 @@ __device__ __forceinline__ int pop_index_for_slot(const Table& t, int64_t slot, 
     return heap[top];
 }
 
+// The same for a whole CTA of 256 threads (all of them call it): the warps' counts meet in shared
+// memory and ONE atomic per CTA reserves the indices, an eighth of the same-address atomics of the
+// warp-level form.
+template <class Table>
+__device__ __forceinline__ int pop_index_for_slot_cta(const Table& t, int64_t slot, int32_t* __restrict__ heap,
+                                                      int32_t* counter, int32_t capacity) {
+    __shared__ int warp_count[8];
+    __shared__ int cta_base;
+    const bool won = slot >= 0;
+    const unsigned ballot = __ballot_sync(0xffffffffu, won);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) warp_count[warp] = __popc(ballot);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int total = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) total += warp_count[w];
+        cta_base = total ? atomicAdd(counter, total) : 0;
+    }
+    __syncthreads();
+    if (!won) return -1;
+    int before = 0;
+    for (int w = 0; w < warp; ++w) before += warp_count[w];
+    const int top = cta_base + before + __popc(ballot & lanemask_lt());
+    if (top >= capacity) {
+        atomicSub(counter, 1);
+        *reinterpret_cast<volatile int*>(t.val_ptr((uint32_t)slot)) = kTomb;
+        atomicOr(t.status, ASHB_STATUS_CAPACITY);
+        return -1;
+    }
+    return heap[top];
+}
+
 template <class Table>
 __device__ __forceinline__ void publish_index(const Table& t, int64_t slot, int idx) {
     *reinterpret_cast<volatile int*>(t.val_ptr((uint32_t)slot)) = idx;
@@ -251,6 +284,29 @@ __device__ __forceinline__ void push_freed_index(int idx, int32_t* __restrict__ 
     base = __shfl_sync(0xffffffffu, base, leader);
     if (!won) return;
     const int top = base - __popc(ballot & lanemask_lt());
+    if (top >= 1) heap[top - 1] = idx;
+}
+
+// The same for a whole CTA of 256 threads: one atomic per CTA.
+__device__ __forceinline__ void push_freed_index_cta(int idx, int32_t* __restrict__ heap, int32_t* counter) {
+    __shared__ int warp_count[8];
+    __shared__ int cta_base;
+    const bool won = idx >= 0;
+    const unsigned ballot = __ballot_sync(0xffffffffu, won);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) warp_count[warp] = __popc(ballot);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int total = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) total += warp_count[w];
+        cta_base = total ? atomicSub(counter, total) : 0;
+    }
+    __syncthreads();
+    if (!won) return;
+    int before = 0;
+    for (int w = 0; w < warp; ++w) before += warp_count[w];
+    const int top = cta_base - before - __popc(ballot & lanemask_lt());
     if (top >= 1) heap[top - 1] = idx;
 }
 

@@ -125,13 +125,13 @@ __global__ void __launch_bounds__(256) peer_update_kernel(Table16 t, PeerLayout 
     const bool live = j < count && j < L.region_capacity;
     int4 rec = make_int4(0, 0, 0, 0);
     if (live) rec = __ldcg(reinterpret_cast<const int4*>(mine + L.inbox_offset) + (int64_t)region * L.region_capacity + j);
-    // whole warps go through the stack operations below
+    // the whole CTA (256 threads) goes through the stack operations below: one atomic per CTA
     if (ERASE) {
-        push_freed_index(live ? tombstone_key(t, rec.x, rec.y, rec.z, 0) : -1, heap, counter);
+        push_freed_index_cta(live ? tombstone_key(t, rec.x, rec.y, rec.z, 0) : -1, heap, counter);
     } else {
         bool present = false;
         const int64_t slot = live ? emplace(t, rec.x, rec.y, rec.z, 0, kPending, &present) : -1;
-        const int idx = pop_index_for_slot(t, slot, heap, counter, capacity);
+        const int idx = pop_index_for_slot_cta(t, slot, heap, counter, capacity);
         if (idx >= 0) publish_index(t, slot, idx);
     }
 }
