@@ -58,13 +58,23 @@ __global__ void __launch_bounds__(256) peer_route_kernel(const int32_t* __restri
     if (live) load_key<DIM>(keys, i, k0, k1, k2, k3);
     // lanes without a key take a negative owner of their own, so that they match nobody
     const int owner = live ? peer_owner_of(k0, k1, k2, DIM, L.world) : -1 - lane;
+    // slots are reserved per CTA: the warps' per-owner groups meet in shared memory and one global
+    // atomic per (CTA, owner) follows, instead of one per (warp, owner)
+    __shared__ int cta_count[kPeerMaxWorld];
+    __shared__ int cta_base[kPeerMaxWorld];
+    for (int o = threadIdx.x; o < L.world; o += blockDim.x) cta_count[o] = 0;
+    __syncthreads();
     const unsigned peers = __match_any_sync(0xffffffffu, owner);
     const int leader = __ffs(peers) - 1;
-    int base = 0;
-    if (live && lane == leader) base = atomicAdd(&cursor[owner], __popc(peers));
-    base = __shfl_sync(0xffffffffu, base, leader);
+    int within = 0;
+    if (live && lane == leader) within = atomicAdd(&cta_count[owner], __popc(peers));
+    within = __shfl_sync(0xffffffffu, within, leader);
+    __syncthreads();
+    for (int o = threadIdx.x; o < L.world; o += blockDim.x)
+        cta_base[o] = cta_count[o] ? atomicAdd(&cursor[o], cta_count[o]) : 0;
+    __syncthreads();
     if (!live) return;
-    const int64_t slot = (int64_t)base + __popc(peers & lanemask_lt());
+    const int64_t slot = (int64_t)cta_base[owner] + within + __popc(peers & lanemask_lt());
     if (slot >= L.region_capacity) {
         atomicOr(status, ASHB_STATUS_CAPACITY);
         if (where) where[i] = -1;
