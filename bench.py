@@ -1066,14 +1066,22 @@ def main():
         keys = torch.cat([uniq, uniq])[torch.randperm(per_rank, generator=g, device=device)]
         # throw-away maps take the first inserts (connection set-up, the allocator's new blocks); the
         # second one is timed as the all-to-all(v) variant of the insert
-        for _ in range(2):
-            warm = PartitionedHashMap(3, HASH_CAPACITY, device)
-            barrier()
-            t_ins_nccl = event_ms(lambda: warm.insert_keys(keys))
-            del warm
-        pm.find(keys[:1024])
-        barrier()
-        t_ins = event_ms(lambda: pm.insert_keys(keys))     # over peer memory
+        def timed_insert(target):
+            """Median of three inserts of the whole batch into the emptied map (the first, untimed, pays
+            for connection set-up and the allocator's new blocks)."""
+            times = []
+            for rep in range(4):
+                target.engine.clear()
+                barrier()
+                t = event_ms(lambda: target.insert_keys(keys))
+                if rep:
+                    times.append(t)
+            return statistics.median(times)
+
+        warm = PartitionedHashMap(3, HASH_CAPACITY, device)
+        t_ins_nccl = timed_insert(warm)                     # all-to-all(v)
+        del warm
+        t_ins = timed_insert(pm)                            # over peer memory (when available)
         fresh = bw.hash_keys_clustered(per_rank // 2, device, seed=bw.SEED + 77 + 1000 * rank)
         q = torch.cat([uniq, fresh])[torch.randperm(per_rank, generator=g, device=device)]
         del keys, fresh
