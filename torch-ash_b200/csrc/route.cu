@@ -3,9 +3,10 @@
 // The reference is single-GPU and has no counterpart.
 //
 //   count    per-CTA histogram of owners in shared memory, one atomic per (CTA, rank)
-//   scatter  each warp groups its lanes by owner (__match_any_sync) and reserves their output
-//            range with one atomic per (warp, rank); rows land grouped by owner, and `perm`
-//            remembers where each came from so that answers can be put back in caller order.
+//   scatter  each warp groups its lanes by owner (__match_any_sync), the groups of a CTA meet in
+//            shared memory and one atomic per (CTA, rank) reserves their output range; rows land
+//            grouped by owner, and `perm` remembers where each came from so that answers can be
+//            put back in caller order.
 #include "common.cuh"
 
 namespace ashb {
@@ -47,16 +48,27 @@ __global__ void __launch_bounds__(256) route_scatter_kernel(const int32_t* __res
                                                             int32_t* __restrict__ keys_out,
                                                             int64_t* __restrict__ perm_out) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int lane = threadIdx.x & 31;
     const bool live = i < n;
-    const int owner = live ? owner_of_key(keys + i * dim, dim, world) : -1;
-    const unsigned active = __ballot_sync(0xffffffffu, live);
-    if (!live) return;
-    const unsigned peers = __match_any_sync(active, owner);
+    // lanes without a key take a negative owner of their own, so that they match nobody
+    const int owner = live ? owner_of_key(keys + i * dim, dim, world) : -1 - lane;
+    // output ranges are reserved per CTA: the warps' per-owner groups meet in shared memory and one
+    // global atomic per (CTA, owner) follows
+    __shared__ unsigned int cta_count[kMaxWorld];
+    __shared__ unsigned long long cta_base[kMaxWorld];
+    for (int o = threadIdx.x; o < world; o += blockDim.x) cta_count[o] = 0;
+    __syncthreads();
+    const unsigned peers = __match_any_sync(0xffffffffu, owner);
     const int leader = __ffs(peers) - 1;
-    unsigned long long base = 0;
-    if ((int)(threadIdx.x & 31) == leader) base = atomicAdd(&cursors[owner], (unsigned long long)__popc(peers));
-    base = __shfl_sync(peers, base, leader);
-    const int64_t pos = offsets.start[owner] + (int64_t)base + __popc(peers & lanemask_lt());
+    unsigned int within = 0;
+    if (live && lane == leader) within = atomicAdd(&cta_count[owner], (unsigned)__popc(peers));
+    within = __shfl_sync(0xffffffffu, within, leader);
+    __syncthreads();
+    for (int o = threadIdx.x; o < world; o += blockDim.x)
+        cta_base[o] = cta_count[o] ? atomicAdd(&cursors[o], (unsigned long long)cta_count[o]) : 0ull;
+    __syncthreads();
+    if (!live) return;
+    const int64_t pos = offsets.start[owner] + (int64_t)cta_base[owner] + within + __popc(peers & lanemask_lt());
     for (int d = 0; d < dim; ++d) keys_out[pos * dim + d] = keys[i * dim + d];
     perm_out[pos] = i;
 }
