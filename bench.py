@@ -178,7 +178,7 @@ def cpu_query_sample(bw, steps, warmup):
     sec = sum(times) / len(times)
     return n_q / sec / 1e6, sec, oracle.num_threads(), (
         f"{n_q} queries over {n_blocks} blocks (1/{CPU_SCALE} of the workload), forward + backward with a fresh "
-        f"dense gradient, mean of {len(times)} steps")
+        f"dense gradient, mean of {len(times)} timed steps after {warmup} warm-up steps, {oracle.num_threads()} threads")
 
 
 def cpu_hash_sample(bw):
@@ -381,13 +381,27 @@ def measure_config1(ash, bw, device):
             "hash_ms": round(h, 4), "grid_ms": round(g, 4)}
 
 
+def use_all_host_cores():
+    """The CPU arms use every core of the box whatever the launcher exported: torch.distributed.run
+    sets OMP_NUM_THREADS=1 for its children, which would time a one-thread CPU port."""
+    import oracle
+
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    oracle.set_num_threads(cores)
+    return oracle.num_threads()
+
+
 def run_reference_arm(args):
+    """The CPU restatement of the reference's kernels on the box's host cores: exactly ``--steps``
+    timed steps after ``--warmup`` untimed ones, each step forward + backward (fresh dense gradient)
+    of a 1/16-scale sample of the workload.  Rank 0 alone runs it."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     import bench_workloads as bw
 
-    value, sec, cores, sample = cpu_query_sample(bw, max(1, min(args.steps, 5)), max(1, min(args.warmup, 2)))
+    use_all_host_cores()
+    value, sec, cores, sample = cpu_query_sample(bw, max(1, args.steps), max(0, args.warmup))
     line = {
         "impl": "reference", "metric": "M trilinear queries/s (fwd+bwd)", "value": round(value, 4), "unit": "M queries/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 3),
@@ -576,6 +590,198 @@ def measure_sharded_table(ash, bw, device, dist, rank, world, n_blocks, n_querie
             "ms_per_step_embedding_gradient_only": round(out[False], 4)}
 
 
+def build_routed_grid(bw, device, n_blocks, max_batch, seed_rank):
+    """The microbench table split over the ranks by block (owner = hash of the coarse block
+    coordinate), each rank's shard filled with its own values."""
+    from ash.distributed import RoutedSparseDenseGrid
+
+    grid = RoutedSparseDenseGrid(3, n_blocks, EMB_DIM, GRID_DIM, cell_size=1.0, device=device, max_batch=max_batch)
+    blocks = bw.block_coords_blob(n_blocks, device)
+    grid.engine.insert_keys(blocks)
+    grid.sync_structure_(src=0)
+    with torch.no_grad():
+        grid.embeddings.normal_(0.0, 0.01, generator=torch.Generator(device=device).manual_seed(bw.SEED + 3 + seed_rank))
+    return grid, blocks
+
+
+def measure_routed(ash, bw, device, dist, rank, world, grid, blocks, n_queries, steps, warmup, with_e2e):
+    """One complete training step per rank on the table SPLIT over the ranks, queries routed to the
+    owners: zero the gradient shard, forward, backward (gradient w.r.t. embeddings AND positions);
+    when the step ends every rank's gradient shard is complete -- there is nothing left to exchange.
+    Returns per-step time (max over ranks), per-phase times of rank 0 and, optionally, the
+    end-to-end time through the public API with positions from pinned host memory."""
+    import __ash
+
+    D = EMB_DIM
+    xs = [bw.points_in_blocks(blocks, n_queries, GRID_DIM, 1.0, device, seed=bw.SEED + 100 * rank + s) for s in range(4)]
+    z = torch.ones(n_queries, D, device=device)
+    box, hm, geom = grid._mailbox, grid.engine.backend, grid._routed_geometry()
+    where = box.where[:n_queries]
+    names = ("zero_grad", "route", "barrier1", "forward", "barrier2", "unpack_y", "send_z", "barrier3", "backward",
+             "barrier4", "unpack_grad_x")
+
+    def step(i, marks=None):
+        def mark():
+            if marks is not None:
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                marks.append(e)
+
+        x = xs[i % 4]
+        mark()
+        grid.zero_grad_shard_()
+        mark()
+        __ash.routed_route(hm, x, geom, box.layout, box.cursor, where, box.status)
+        mark()
+        grid._barrier()
+        mark()
+        __ash.routed_forward(hm, grid._emb_bases, geom, box.layout, "linear")
+        mark()
+        grid._barrier()
+        mark()
+        y, masks = __ash.routed_unpack_y(where, n_queries, D, box.layout)
+        mark()
+        __ash.routed_send_z(where, z, box.layout)
+        mark()
+        grid._barrier()
+        mark()
+        __ash.routed_backward(hm, grid._emb_bases, grid._grad_bases, geom, box.layout, "linear", True)
+        mark()
+        grid._barrier()
+        mark()
+        gx = __ash.routed_unpack_grad_x(where, n_queries, D, box.layout)
+        mark()
+        return y, masks, gx
+
+    for i in range(warmup):
+        step(i)
+    dist.barrier()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(steps):
+        step(i)
+    end.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([start.elapsed_time(end) / steps], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    grid.check_status()
+    # per-phase times (a second, instrumented pass; rank 0's view)
+    phases = {k: [] for k in names}
+    for i in range(min(steps, 5)):
+        marks = []
+        step(i, marks)
+        torch.cuda.synchronize()
+        for k, a, b in zip(names, marks[:-1], marks[1:]):
+            phases[k].append(a.elapsed_time(b))
+    phase_ms = {k: round(statistics.mean(v), 4) for k, v in phases.items()}
+    out = {"ms_per_step": ms, "phase_ms_rank0": phase_ms, "queries_per_rank": n_queries,
+           "nvlink_bytes_per_rank_per_step": int(n_queries * (world - 1) / world * (16 + 4 * D + 4 * D + 16))}
+    if with_e2e:
+        x_host = [x.cpu().pin_memory() for x in xs]
+        copy_stream = torch.cuda.Stream(device)
+        main = torch.cuda.current_stream(device)
+
+        def fetch(i):
+            with torch.cuda.stream(copy_stream):
+                xb = x_host[i % 4].to(device, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(copy_stream)
+            return xb, ev
+
+        nxt = fetch(0)
+        dist.barrier()
+        torch.cuda.synchronize()
+        t_begin = None
+        for i in range(warmup + steps):
+            if i == warmup:
+                dist.barrier()
+                torch.cuda.synchronize()
+                t_begin = time.perf_counter()
+            xb, ev = nxt
+            nxt = fetch(i + 1)
+            main.wait_event(ev)
+            xb.record_stream(main)
+            grid.zero_grad_shard_()
+            y, _ = grid(xb.requires_grad_(True), interpolation="linear")
+            loss = y.sum()
+            loss.backward()
+            loss_value = loss.item()  # device -> host read of the step's result
+        torch.cuda.synchronize()
+        t = torch.tensor([(time.perf_counter() - t_begin) / steps], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out["e2e_sec"] = float(t.item())
+    return out
+
+
+def multi_gpu_parity(ash, bw, device, dist, rank, world):
+    """Small-case parity of the multi-GPU paths, computed before anything is timed: the routed
+    sharded grid against a replicated grid (result rows bit for bit, position gradients and the
+    gradient shards against the all-reduced dense gradient), and the partitioned hash map over
+    peer memory against the same map over all-to-all(v) and against a single map of the union."""
+    from ash.distributed import PartitionedHashMap, RoutedSparseDenseGrid
+
+    G, D, n_blocks, n = 8, EMB_DIM, 4000, 20000
+    blocks = bw.block_coords_blob(n_blocks, device, n_blobs=4, seed=bw.SEED + 21)
+    full = torch.randn(n_blocks, G**3, D, generator=torch.Generator().manual_seed(3)).to(device)
+    ref = ash.SparseDenseGrid(3, n_blocks, D, G, device)
+    ref.engine.insert_keys(blocks[torch.randperm(n_blocks, device=device)])
+    routed = RoutedSparseDenseGrid(3, n_blocks, D, G, cell_size=1.0, device=device, max_batch=n)
+    routed.engine.insert_keys(blocks)
+    routed.sync_structure_(src=0)
+    idx_ref, _ = ref.engine.find(blocks)
+    idx_rt, _ = routed.engine.find(blocks)
+    pos_of = torch.full((n_blocks,), -1, dtype=torch.int64, device=device)
+    pos_of[idx_rt] = torch.arange(n_blocks, device=device)
+    mine = pos_of[routed.owned_blocks()]
+    with torch.no_grad():
+        ref.embeddings[idx_ref] = full
+        routed.embeddings[: mine.numel()] = full[mine]
+    x = bw.points_in_blocks(blocks, n, G, 1.0, device, seed=bw.SEED + 31 + rank)
+    w = torch.randn(n, D, device=device, generator=torch.Generator(device=device).manual_seed(5 + rank))
+    xr = x.clone().requires_grad_(True)
+    yr, mr = ref(xr, "linear")
+    (yr * w).sum().backward()
+    per_block = ref.embeddings.grad[idx_ref].clone()
+    dist.all_reduce(per_block)
+    xs = x.clone().requires_grad_(True)
+    routed.zero_grad_shard_()
+    ys, ms = routed(xs, "linear")
+    (ys * w).sum().backward()
+    routed.check_status()
+    got, want = routed.embeddings.grad[: mine.numel()], per_block[mine]
+    res = torch.tensor([float(torch.equal(ys, yr) and torch.equal(ms, mr)), -float((xs.grad - xr.grad).abs().max()),
+                        -float((got - want).abs().max()), -float(want.abs().max())], device=device, dtype=torch.float64)
+    dist.all_reduce(res, op=dist.ReduceOp.MIN)
+    del routed, ref
+
+    keys = bw.hash_keys_clustered(40_000, device, n_clusters=16, seed=bw.SEED + 200 + rank)
+    pm = PartitionedHashMap(3, 200_000 * world, device, peer_max_batch=60_000)
+    pm.insert_keys(keys)
+    q = torch.cat([keys[:20_000], bw.hash_keys_clustered(20_000, device, n_clusters=16, seed=bw.SEED + 300 + rank)])
+    a = pm.find(q)
+    box, pm.mailbox = pm.mailbox, None
+    b = pm.find(q)
+    pm.mailbox = box
+    gathered = [torch.empty_like(keys) for _ in range(world)]
+    dist.all_gather(gathered, keys)
+    single = ash.HashSet(3, 200_000 * world, device)
+    single.insert(torch.cat(gathered))
+    single_mask = single.find(q)
+    h = torch.tensor([float(torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])), float(torch.equal(a[1], single_mask))],
+                     device=device, dtype=torch.float64)
+    dist.all_reduce(h, op=dist.ReduceOp.MIN)
+    return {"routed_grid_y_equals_replicated": bool(res[0] == 1.0),
+            "routed_grid_grad_x_max_abs_err": float(-res[1]),
+            "routed_grid_grad_shard_vs_allreduced_dense_max_abs_err": float(-res[2]),
+            "grad_magnitude": float(-res[3]),
+            "partitioned_find_peer_equals_all_to_all": bool(h[0] == 1.0),
+            "partitioned_find_masks_equal_single_map": bool(h[1] == 1.0),
+            "case": f"{n_blocks} blocks, {n} queries per rank; 40k keys per rank, 40k finds per rank; min / max over {world} ranks"}
+
+
 def measure_bounded(ash, bw, device, peak):
     """Bounded grid at resolution 512 (64 blocks x grid_dim 8 per axis), sdf + rgb channels: 7x7x7
     Gaussian filter through the neighbourhood convolution, ray near/far and ray sampling for 8192
@@ -747,6 +953,24 @@ def main():
     import bench_workloads as bw
 
     peak, peak_kind = measured_peak_gbs()
+    multi = None
+    if dist is not None:
+        # The multi-GPU step: table split over the ranks, queries routed to the owners; every rank's
+        # gradient shard is complete when the step ends.  Parity of the multi-GPU paths first.
+        multi = {"parity": multi_gpu_parity(ash, bw, device, dist, rank, world)}
+        rgrid, rblocks = build_routed_grid(bw, device, N_BLOCKS, N_QUERIES, rank)
+        sampler = ClockSampler(list(range(world)) if rank == 0 else [])
+        time.sleep(0.5 if rank == 0 else 0.0)
+        sampler.begin()
+        multi["weak"] = measure_routed(ash, bw, device, dist, rank, world, rgrid, rblocks, N_QUERIES, args.steps,
+                                       args.warmup, with_e2e=True)
+        sampler.stop()
+        multi["clocks"] = sampler.result
+        multi["strong"] = measure_routed(ash, bw, device, dist, rank, world, rgrid, rblocks, N_QUERIES // world,
+                                         min(args.steps, 10), 3, with_e2e=False)
+        multi["table_bytes_per_gpu"] = rgrid.embeddings.numel() * 4
+        del rgrid, rblocks
+        torch.cuda.empty_cache()
     grid, blocks = build_grid(ash, bw, device, N_BLOCKS)
     if dist is not None:
         # replicas must agree on which row is which block before their gradients can be summed
@@ -957,6 +1181,45 @@ def main():
                         "host memory through a double-buffered loader (copy of step i+1 overlaps step i), loss read back",
                 "unpipelined_value": round(world * N_QUERIES / e2e_serial_sec / 1e6, 2)},
     }
+    if multi is not None:
+        # N > 1: the job is ONE table of N_BLOCKS blocks split over the ranks and 4M queries per rank
+        # per step; `value` counts a step as done when every rank's gradient shard is complete.
+        weak, strong = multi["weak"], multi["strong"]
+        line["replicated_no_exchange"] = {
+            "value": line["value"], "unit": "M queries/s", "ms_per_step": line["ms_per_step"], "e2e": line["e2e"],
+            "note": "every rank holds the WHOLE table and queries its own 4M-position shard; no communication, and the "
+                    "per-rank dense gradients are NOT summed (the all-reduce that would do it is grad_allreduce_ms): "
+                    "an upper bound, not a training step"}
+        line.update({
+            "value": round(world * N_QUERIES / (weak["ms_per_step"] * 1e-3) / 1e6, 2),
+            "ms_per_step": round(weak["ms_per_step"], 4), "clocks": multi["clocks"], "gpu_launches": 7 * args.steps,
+            "e2e": {"value": round(world * N_QUERIES / weak["e2e_sec"] / 1e6, 2), "unit": "M queries/s",
+                    "h2d_bytes_per_step": N_QUERIES * 12, "d2h_bytes_per_step": 4,
+                    "ms_per_step": round(weak["e2e_sec"] * 1e3, 4),
+                    "note": "RoutedSparseDenseGrid.__call__ + backward per rank (zero the gradient shard, forward, "
+                            "backward; gradient shards complete), positions from pinned host memory through a "
+                            "double-buffered loader, loss read back; max over ranks"}})
+        line["config"]["parallelism"] = (
+            f"table of {N_BLOCKS} blocks split over the {world} ranks by block (owner = hash of the coarse block "
+            "coordinate), 4M queries per rank routed to the owners of their blocks over NVLink peer memory (16-byte "
+            "record out, result row back; dL/dy out, dL/dx back), owners gather / scatter in their own HBM; every "
+            "gradient shard is complete when the step ends, no all-reduce")
+        line["config"]["workload"] = line["config"]["workload"].replace(
+            "fresh dense gradient per step", "gradient shard zero-filled per step, gradients complete on the owners")
+        line["config"]["cache"] = f"inputs larger than L2: {multi['table_bytes_per_gpu'] / 1e9:.1f} GB shard per GPU, 4 rotating query batches"
+        line["config"]["parity"] = multi["parity"]
+        nv = weak["nvlink_bytes_per_rank_per_step"]
+        line["multi_gpu_step"] = {
+            "phase_ms_rank0": weak["phase_ms_rank0"], "table_bytes_per_gpu": multi["table_bytes_per_gpu"],
+            "nvlink_bytes_per_rank_per_step": nv,
+            "nvlink_GBs_per_gpu_per_direction_over_the_step": round(nv / (weak["ms_per_step"] * 1e-3) / 1e9, 1),
+            "note": "phases of one step as rank 0 sees them (CUDA events); barrier = one-element NCCL all-reduce, its "
+                    "time includes waiting for the slowest rank"}
+        line["strong_scaling"] = {
+            "what": f"the same step with {N_QUERIES} queries IN TOTAL ({N_QUERIES // world} per rank), as the benchmark "
+                    "configuration states it", "value": round(world * (N_QUERIES // world) / (strong["ms_per_step"] * 1e-3) / 1e6, 2),
+            "unit": "M queries/s", "ms_per_step": round(strong["ms_per_step"], 4),
+            "phase_ms_rank0": strong["phase_ms_rank0"]}
     if rank == 0:
         f_ms, b_ms, bp_ms = statistics.mean(fwd_ms), statistics.mean(bwd_ms), statistics.mean(bwd_persist_ms)
         achieved = N_QUERIES * BWD_BYTES / (bp_ms * 1e-3) / 1e9

@@ -73,6 +73,12 @@ int ashb_map_size(ashb_map* map, void* stream, int64_t* size_out);
  * has undefined behaviour (ash/src/hashmap_gpu.cuh:226-227, :420). */
 int ashb_map_status(ashb_map* map, void* stream, uint32_t* status_out);
 
+/* The same without waiting: the status word is copied to status_out_host (host memory, pinned for
+ * the copy to be asynchronous) and cleared, both enqueued on `stream`; the caller reads the host
+ * word once work it enqueued later on that stream (an event) has completed.  No counterpart in the
+ * reference. */
+int ashb_map_status_async(ashb_map* map, uint32_t* status_out_host, void* stream);
+
 /* Replaces find_kernel + HashMapGPUImpl::find (ash/src/hashmap_gpu.cuh:164-208).
  * keys_dev int32[n][key_dim]; indices_dev int64[n] (0 on a miss); masks_dev
  * uint8[n] (1 hit / 0 miss).  Every output element is written. */
@@ -203,6 +209,28 @@ int ashb_grid_query_backward_backward(ashb_map* map, int dtype, int interp, cons
                                       double cell_size, const float* origin, int G, const int32_t* nb_lut,
                                       const int32_t* block_idx, void* grad_z, void* grad_embeddings,
                                       int zero_grad, int64_t n, int64_t n_emb, int64_t D, void* stream);
+
+/* The two backward passes above with the embedding gradient WRITTEN as a row list instead of added
+ * into a table-sized buffer (the dense `at::zeros_like(embeddings)` of ash/src/grid.cu:276 and :415):
+ * idx_out int64 [2][8 n] and rows_out [8 n][D] (type of embeddings), record c * n + q = corner c of
+ * query q: idx_out[0] = block index, idx_out[1] = cell index, rows_out = that corner's gradient row.
+ * Together they are an uncoalesced sparse tensor of the table's shape (repeated cells add up).
+ * Queries without a gradient write zero rows pointing at valid cells.  second_order == 0: the
+ * first-order pass, side_out = grad_x [n][3] or NULL (then the embedding rows are not read);
+ * second_order != 0: the double backward, grad_grad_x required, side_out = grad_z [n][D].
+ * Nothing is read-modify-written and every store is coalesced. */
+int ashb_grid_query_backward_rows(ashb_map* map, int dtype, int interp, int second_order, const void* grad_grad_x,
+                                  const void* z, const void* embeddings, const float* x, double cell_size,
+                                  const float* origin, int G, const int32_t* nb_lut, const int32_t* block_idx,
+                                  int64_t* idx_out, void* rows_out, void* side_out, int64_t n, int64_t n_emb,
+                                  int64_t D, void* stream);
+
+/* Applies a row list to a dense buffer shaped like the table: dst[idx[0][r]][idx[1][r]][:] +=
+ * alpha * rows[r][:] for r < m (idx int64 [2][m]); records with an index out of range and all-zero
+ * rows are skipped.  dst may be a gradient buffer (alpha = 1) or the parameters themselves
+ * (alpha = -learning rate).  No counterpart in the reference. */
+int ashb_rows_scatter_add(int dtype, void* dst, const int64_t* idx, const void* rows, int64_t m, int64_t n_emb,
+                          int64_t cells_per_grid, int64_t D, double alpha, void* stream);
 
 /* Block allocation from points: replaces SparseDenseGrid.spatial_init_ (ash/grid.py:121-159) --
  * floor(points / cell / G), neighbourhood enumeration, the temporary HashSet used to
@@ -543,6 +571,63 @@ int ashb_peer_update(ashb_map* map, int erase, int world, int rank, void* const*
                      int64_t mailbox_bytes, int64_t inbox_offset, int64_t counts_offset, int64_t answers_offset,
                      int64_t region_capacity, int64_t answer_capacity, void* stream);
 
+/* ---------------------------------------------------------------- table sharded over the GPUs, queries routed to the owners
+ * (no counterpart in the reference, which is single-GPU).  The table is split by BLOCK over `world`
+ * ranks: row_of uint32 [n_emb] (replicated) = owner << 26 | row of the block in the owner's shard;
+ * emb_bases_dev / grad_bases_dev: device arrays [world] of the shards' (and gradient shards') base
+ * addresses as mapped into this rank; the hash map and nb_lut are replicated.  Instead of reading
+ * rows from their owners, every query is SENT to the owner of its block, which interpolates in its
+ * own memory and returns the result row; the backward sends dL/dy the same way and the owner adds
+ * the gradient rows into its own gradient shard and returns dL/dx.  Corner rows in a neighbour
+ * block of another owner are read / reduced over peer memory directly.
+ *
+ * Mailbox (symmetric memory, one per rank, peer_bases_dev [world]): inbox_x float4 [world][cap]
+ * {x, y, z, block index}, counts int32 [world], inbox_z float [world][cap][D], out_y float
+ * [world][cap][D], out_gx float4 [world][cap]; all offsets in bytes, multiples of 16 (counts: 4).
+ * Rank r writes only region r of another rank's sections.  world <= 32, region_capacity < 2^26.
+ * A step on every rank: route | barrier | forward | barrier | unpack_y | ... | send_z | barrier |
+ * backward | barrier | unpack_grad_x, the barriers being collectives the caller enqueues on the
+ * same stream; no kernel waits on another GPU.  where_dev int32 [n]: owner << 26 | slot per query
+ * (-1: no block there, or dropped because its region was full -> ASHB_STATUS_CAPACITY in
+ * status_dev). */
+int ashb_routed_route(ashb_map* map, const float* x, int64_t n, double cell_size, const float* origin, int G,
+                      const int32_t* nb_lut, const uint32_t* row_of, int64_t n_emb, int64_t D,
+                      void* const* peer_bases_dev, int64_t mailbox_bytes, int64_t inbox_x_offset,
+                      int64_t counts_offset, int64_t inbox_z_offset, int64_t out_y_offset, int64_t out_gx_offset,
+                      int64_t region_capacity, int world, int rank, int32_t* cursor_dev, int32_t* where_dev,
+                      uint32_t* status_dev, void* stream);
+/* Owner side: interpolate every record of this rank's inbox (semantics of ashb_grid_query_forward)
+ * and store row j of region r into rank r's out_y[rank][j]. */
+int ashb_routed_forward(ashb_map* map, int interp, const void* const* emb_bases_dev, double cell_size,
+                        const float* origin, int G, const int32_t* nb_lut, const uint32_t* row_of, int64_t n_emb,
+                        int64_t D, void* const* peer_bases_dev, int64_t mailbox_bytes, int64_t inbox_x_offset,
+                        int64_t counts_offset, int64_t inbox_z_offset, int64_t out_y_offset, int64_t out_gx_offset,
+                        int64_t region_capacity, int world, int rank, void* stream);
+/* Asker side: y [n][D] and masks uint8 [n] (optional) from this rank's out_y, in query order. */
+int ashb_routed_unpack_y(const int32_t* where_dev, int64_t n, float* y, uint8_t* masks, int64_t D,
+                         void* const* peer_bases_dev, int64_t mailbox_bytes, int64_t inbox_x_offset,
+                         int64_t counts_offset, int64_t inbox_z_offset, int64_t out_y_offset, int64_t out_gx_offset,
+                         int64_t region_capacity, int world, int rank, void* stream);
+/* Asker side: z [n][D] = dL/dy of every query into its owner's inbox_z, at the slot routing gave it. */
+int ashb_routed_send_z(const int32_t* where_dev, int64_t n, const float* z, int64_t D,
+                       void* const* peer_bases_dev, int64_t mailbox_bytes, int64_t inbox_x_offset,
+                       int64_t counts_offset, int64_t inbox_z_offset, int64_t out_y_offset, int64_t out_gx_offset,
+                       int64_t region_capacity, int world, int rank, void* stream);
+/* Owner side: semantics of ashb_grid_query_backward for every record: gradient rows ADDED into the
+ * owners' gradient shards, dL/dx (times 1 / cell_size) stored into the asker's out_gx unless
+ * need_grad_x == 0 (then the embedding rows are not read). */
+int ashb_routed_backward(ashb_map* map, int interp, const void* const* emb_bases_dev, void* const* grad_bases_dev,
+                         int need_grad_x, double cell_size, const float* origin, int G, const int32_t* nb_lut,
+                         const uint32_t* row_of, int64_t n_emb, int64_t D, void* const* peer_bases_dev,
+                         int64_t mailbox_bytes, int64_t inbox_x_offset, int64_t counts_offset,
+                         int64_t inbox_z_offset, int64_t out_y_offset, int64_t out_gx_offset,
+                         int64_t region_capacity, int world, int rank, void* stream);
+/* Asker side: grad_x [n][3] from this rank's out_gx, zero rows for queries without a block. */
+int ashb_routed_unpack_grad_x(const int32_t* where_dev, int64_t n, float* grad_x, int64_t D,
+                              void* const* peer_bases_dev, int64_t mailbox_bytes, int64_t inbox_x_offset,
+                              int64_t counts_offset, int64_t inbox_z_offset, int64_t out_y_offset,
+                              int64_t out_gx_offset, int64_t region_capacity, int world, int rank, void* stream);
+
 /* ---------------------------------------------------------------- runtime knobs */
 
 /* Selects how ashb_query_backward_forward and ashb_grid_query_backward scatter the embedding
@@ -555,6 +640,13 @@ int ashb_set_scatter_aggregation(int enable);
  * 1 = eight lanes per key reading a whole 128-byte line of slots per step.  Same results. */
 int ashb_set_find_cooperative(int enable);
 
+/* Occupancy filter of ashb_map_find for key_dim <= 3 (no counterpart in the reference).  Every map
+ * keeps one bit per slot, set when a key is first stored there; a find whose home slot never held a
+ * key is a miss and is answered from that bit map, which stays in L2 for tables far larger than L2,
+ * without touching the table.  mode -1 (default): used for tables of 64 MB and more; 0: never;
+ * 1: always.  Same results in every mode. */
+int ashb_set_find_filter(int mode);
+
 /* Measurement aid (no counterpart in the reference): launches n_reads threads that each read one
  * 16-byte word at a pseudo-random 64-byte-aligned place of `buffer` (device, 64-byte aligned,
  * `bytes` long, any content), naming an L2 fetch size of fetch_bytes (64 or 128).  Timed by the
@@ -562,6 +654,11 @@ int ashb_set_find_cooperative(int enable);
  * accesses are as scattered.  sink_dev: 8 bytes of device scratch. */
 int ashb_measure_random_reads(const void* buffer, int64_t bytes, int64_t n_reads, int fetch_bytes, uint32_t seed,
                               void* sink_dev, void* stream);
+/* The same with reads_per_thread (1, 2, 4 or 8) independent reads issued by every thread before any
+ * is consumed (n_reads in total): tells a latency limit (the rate rises with it) from a limit of the
+ * memory system (it does not). */
+int ashb_measure_random_reads_ilp(const void* buffer, int64_t bytes, int64_t n_reads, int fetch_bytes,
+                                  int reads_per_thread, uint32_t seed, void* sink_dev, void* stream);
 
 /* cudaLimitMaxL2FetchGranularity of the current context (32, 64 or 128 bytes); a
  * performance hint that lasts as long as the process.  No counterpart in the reference. */

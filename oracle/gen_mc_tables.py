@@ -1,6 +1,6 @@
 """Generates ``mc_tables.h``: the per-cube triangulation table of the iso-surface mesher.
 
-    python gen_mc_tables.py            # rewrites mc_tables.h next to this file and in oracle/
+    python oracle/gen_mc_tables.py     # rewrites mc_tables.h next to this file and beside the CUDA kernels
 
 The table is DERIVED here, not transcribed from anywhere: for each of the 256 inside/outside
 patterns of a cube's corners the iso-surface is traced on the cube's faces and the resulting closed
@@ -15,7 +15,10 @@ Conventions (shared by the CUDA kernels and the CPU oracle through the generated
   face rule            on a face whose corners alternate inside / outside the surface cuts off
                        each INSIDE corner on its own.  The rule reads only the face's own four
                        signs, so the two cubes sharing a face agree and the mesh has no cracks.
-  orientation          triangle normals (right-hand rule) point to the OUTSIDE (increasing value).
+  orientation          triangle normals (right-hand rule) point to the OUTSIDE (increasing value):
+                       the winding of the reference's OUTPUT -- its table (ash/src/mc_macros.h) holds
+                       the mirrored winding and its kernel writes every triangle in reverse vertex
+                       order (ash/src/grid.cu:836).
 """
 import os
 
@@ -204,8 +207,8 @@ def render(tris, masks):
 
 if __name__ == "__main__":
     t, m = build()
-    # one copy beside the kernels, one beside the CPU oracle (which builds on its own)
-    for folder in (HERE, os.path.join(HERE, "..", "..", "oracle")):
+    # one copy beside the CPU oracle (which builds on its own), one beside the CUDA kernels
+    for folder in (HERE, os.path.join(HERE, "..", "torch-ash_b200", "csrc")):
         with open(os.path.join(folder, "mc_tables.h"), "w") as f:
             f.write(render(t, m))
     print("max triangles per cube:", max(len(r) for r in t) // 3, "total:", sum(len(r) for r in t) // 3)

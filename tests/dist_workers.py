@@ -180,6 +180,19 @@ def peer_find_worker(rank, world, port):
             raise AssertionError("an oversized batch was accepted")
         except ValueError:
             pass
+        # an owner whose share of the capacity overflows drops the excess keys and says so, whichever
+        # transport delivered them (the reference warns and goes on, ash/core.py:206-211)
+        import warnings
+
+        crowd = torch.randint(-300, 300, (3000, 3), dtype=torch.int32, device=device, generator=g)
+        for peer_max_batch in (0, 4096):
+            small = PartitionedHashMap(3, 64, device, peer_max_batch=peer_max_batch)
+            with warnings.catch_warnings(record=True) as caught:
+                warnings.simplefilter("always")
+                small.insert_keys(crowd)
+                n = small.size()        # the deferred report of the peer transport is due here at the latest
+            assert any("capacity" in str(w.message) for w in caught), f"no overflow warning (peer_max_batch={peer_max_batch})"
+            assert 0 < n <= world * small.local_capacity
     finally:
         dist.destroy_process_group()
 
@@ -249,5 +262,73 @@ def sharded_grid_worker(rank, world, port):
             assert 0.3 < float(mr.float().mean()) < 1.0
             dist.barrier()
             del sharded, ref
+    finally:
+        dist.destroy_process_group()
+
+
+def routed_grid_worker(rank, world, port):
+    """A table sharded over the ranks with the queries routed to the owners answers like a replicated
+    table, returns the same gradients for the positions, and leaves in every gradient shard the
+    rows of the summed dense gradient; also when a batch is empty or ragged, and over two steps."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        import ash
+        import bench_workloads as bw
+        from ash.distributed import RoutedSparseDenseGrid
+
+        G, n_blocks, cell = 4, 301, 0.05
+        blocks = bw.block_coords_blob(n_blocks, device, n_blobs=3, seed=7)
+        for D, interpolation in ((8, "linear"), (16, "smooth_step"), (3, "linear")):
+            full = torch.randn(n_blocks, G**3, D, generator=torch.Generator().manual_seed(1)).to(device)
+            ref = ash.UnBoundedSparseDenseGrid(3, n_blocks + 40, D, G, cell_size=cell, device=device)
+            ref.engine.insert_keys(blocks[torch.randperm(n_blocks, device=device)])   # an order of its own per rank
+            routed = RoutedSparseDenseGrid(3, n_blocks + 40, D, G, cell_size=cell, device=device, max_batch=8192)
+            routed.engine.insert_keys(blocks)
+            routed.sync_structure_(src=0)
+            idx_ref, _ = ref.engine.find(blocks)
+            idx_rt, _ = routed.engine.find(blocks)
+            pos_of = torch.full((n_blocks + 40,), -1, dtype=torch.int64, device=device)
+            pos_of[idx_rt] = torch.arange(n_blocks, device=device)
+            mine = pos_of[routed.owned_blocks()]                  # positions in `blocks` of this shard's rows
+            assert (mine >= 0).all()
+            counts = torch.tensor([mine.numel()], device=device)
+            dist.all_reduce(counts)
+            assert int(counts.item()) == n_blocks                 # every block has exactly one owner
+            with torch.no_grad():
+                ref.embeddings[idx_ref] = full
+                routed.embeddings[: mine.numel()] = full[mine]
+            g = torch.Generator(device=device).manual_seed(50 + rank)
+            for n in (4000 + 13 * rank, 0 if rank == 0 else 257, 1500):
+                pick = torch.randint(n_blocks, (n,), device=device, generator=g)
+                x = ((blocks[pick].float() + torch.rand(n, 3, device=device, generator=g) * 1.4 - 0.2) * G * cell)
+                w = torch.randn(n, D, device=device, generator=g)
+                xr = x.clone().requires_grad_(True)
+                ref.embeddings.grad = None
+                yr, mr = ref(xr, interpolation)
+                (yr * w).sum().backward()
+                dense = ref.embeddings.grad if ref.embeddings.grad is not None else torch.zeros_like(ref.embeddings)
+                per_block = dense[idx_ref].clone()
+                dist.all_reduce(per_block)                        # what a dense gradient all-reduce would give
+                for need_grad_x in (True, False):
+                    routed.zero_grad_shard_()
+                    xs = x.clone().requires_grad_(need_grad_x)
+                    ys, ms = routed(xs, interpolation)
+                    (ys * w).sum().backward()
+                    routed.check_status()
+                    assert torch.equal(ms, mr) and torch.equal(ys, yr)
+                    if need_grad_x and n:
+                        torch.testing.assert_close(xs.grad, xr.grad, rtol=1e-4, atol=1e-5 * float(xr.grad.abs().max()))
+                    got = routed.embeddings.grad[: mine.numel()]
+                    want = per_block[mine]
+                    torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-5 * max(1.0, float(want.abs().max())))
+                    assert torch.count_nonzero(routed.embeddings.grad[mine.numel():]) == 0
+                if n > 1000:
+                    assert 0.3 < float(mr.float().mean()) < 1.0
+            dist.barrier()
+            del routed, ref
     finally:
         dist.destroy_process_group()

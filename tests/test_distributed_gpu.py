@@ -30,3 +30,7 @@ def test_partitioned_find_over_peer_memory():
 
 def test_sharded_grid_matches_replicated_grid():
     mp.spawn(dist_workers.sharded_grid_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
+def test_routed_grid_matches_replicated_grid():
+    mp.spawn(dist_workers.routed_grid_worker, args=(2, _free_port()), nprocs=2, join=True)

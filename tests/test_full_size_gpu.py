@@ -2,13 +2,15 @@
 properties (the CPU oracle cannot run these sizes in seconds): adjoint identities between forward,
 backward and double backward, exact linearity, weight normalisation; set semantics, idempotence
 and index stability of the hash engine.  Config 1 (the CPU-runnable one) is compared with the
-oracle directly."""
+oracle directly, and so is a random sample of the queries of config 3 at full table size (the
+blocks the sample touches are copied to the host; the 16.4 GB stay on the GPU)."""
 import numpy as np
 import pytest
 import torch
 
 import bench_workloads as bw
 import oracle
+import sum_bounds as sb
 
 pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda:0")
@@ -59,8 +61,93 @@ def test_config1_hash_and_grid_against_oracle():
     y_ref = oracle.query_forward(interpolation="linear", **o)
     ge_ref, go_ref = oracle.query_backward_forward(np.ones((100_000, 1), np.float32), interpolation="linear", **o)
     np.testing.assert_allclose(t(y), y_ref, rtol=1e-5, atol=1e-6)
-    np.testing.assert_allclose(t(grid.embeddings.grad), ge_ref, rtol=4e-5, atol=4e-6)
-    np.testing.assert_allclose(t(x.grad) * 0.01, go_ref, rtol=4e-5, atol=4e-5)  # d offset / d x = 1 / cell_size
+    # gradients: 1e-5 * sum|terms| + 1e-6 against the float64 oracle (the scatter order is not fixed)
+    ones = np.ones((100_000, 1))
+    ge64, go64 = oracle.query_backward_forward(ones, interpolation="linear", **sb.as_float64(o))
+    mag = sb.magnitudes(o, "linear", z=ones)
+    sb.assert_within(t(grid.embeddings.grad), ge64, mag["grad_emb"], "config 1 grad_emb")
+    # d offset / d x = 1 / cell_size = 100: compare in offset units
+    sb.assert_within(t(x.grad).astype(np.float64) * 0.01, go64, mag["grad_off"], "config 1 grad_x")
+    np.testing.assert_allclose(ge_ref, ge64, rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(go_ref, go64, rtol=1e-5, atol=1e-6)
+
+
+def test_config3_full_size_sample_against_oracle():
+    """Config 3 at its full table size (500k blocks x 512 cells x 16 channels = 16.4 GB, row offsets
+    beyond 2^31 elements, where a 32-bit index as in ash/src/grid.cu:121 overflows) against the oracle on a random sample of 20,000 of its 4M queries: the
+    neighbourhoods of the blocks the sample falls in are copied to the host as a sub-table with
+    re-numbered blocks, the oracle runs forward / backward / double backward on it in float64, and
+    the CUDA kernels -- run on the FULL table -- must agree at 1e-5 * sum|terms| + 1e-6."""
+    _need_gb(60)
+    import __ash
+    import ash
+
+    nb, D, G, nq, ns = 500_000, 16, 8, 4_000_000, 20_000
+    grid = ash.SparseDenseGrid(3, nb, D, G, DEV)
+    blocks = bw.block_coords_blob(nb, DEV)
+    grid.engine.insert_keys(blocks)
+    g = torch.Generator(device=DEV).manual_seed(5)
+    with torch.no_grad():
+        grid.embeddings.normal_(0, 0.01, generator=g)
+    grid.construct_grid_neighbor_lut_(1, False)
+    emb, hm, lut = grid.embeddings.detach(), grid.engine.backend, grid._neighbor_lut32()
+    x = bw.points_in_blocks(blocks, nq, G, 1.0, DEV)
+    args = (1.0, [0.0, 0.0, 0.0], G, lut)
+    pick = torch.randperm(nq, generator=g, device=DEV)[:ns]
+    xs = x[pick].contiguous()
+
+    # the sample's view of the table: its blocks and their neighbourhoods, re-numbered 0..m-1
+    gi, ci, off, mk = grid.query(xs)
+    nbr = grid.lut_grid_nb2grid_idx[gi.clamp_min(0)]                      # (ns, 8) block indices, -1 absent
+    nbr = torch.where(mk[:, None], nbr, torch.full_like(nbr, -1))
+    touched = torch.unique(nbr[nbr >= 0])
+    assert int(touched.max()) * G**3 * D > 2**31, "the sample must reach rows beyond 31-bit element offsets"
+    remap = torch.full((nb,), -1, dtype=torch.int64, device=DEV)
+    remap[touched] = torch.arange(touched.numel(), device=DEV)
+    g2g_sub = torch.full((touched.numel(), 8), -1, dtype=torch.int64, device=DEV)
+    own = remap[gi[mk]]
+    g2g_sub[own] = torch.where(nbr[mk] >= 0, remap[nbr[mk].clamp_min(0)], torch.full_like(nbr[mk], -1))
+    t = lambda a: a.detach().cpu().numpy()
+    o = dict(emb=t(emb[touched]), offsets=t(off), grid_indices=t(torch.where(mk, remap[gi.clamp_min(0)], gi)),
+             cell_indices=t(ci), masks=t(mk), g2g=t(g2g_sub), c2c=t(grid.lut_cell_nb2cell_idx),
+             c2g=t(grid.lut_cell_nb2grid_nb))
+    o64 = sb.as_float64(o)
+    z = torch.randn(ns, D, generator=g, device=DEV)
+    v = torch.randn(ns, 3, generator=g, device=DEV)
+    z64, v64 = t(z).astype(np.float64), t(v).astype(np.float64)
+    mag = sb.magnitudes(o, "smooth_step", z=z64, ggo=v64)
+
+    # forward: the sample alone, and as part of the whole 4M batch (same rows, bit for bit)
+    y, masks, bidx = __ash.grid_query_forward(hm, emb, xs, *args, "smooth_step")
+    y_all, _, _ = __ash.grid_query_forward(hm, emb, x, *args, "smooth_step")
+    assert torch.equal(y_all[pick], y) and torch.equal(masks, mk)
+    del y_all
+    sb.assert_within(t(y), oracle.query_forward(interpolation="smooth_step", **o64), mag["y"], "config 3 y")
+    assert 0.0 < float(((y == 0).all(dim=1) & masks).float().mean()) < 0.1   # absent-neighbour rows are in the sample
+
+    # backward of the sample into a zeroed table-sized gradient
+    ge = torch.zeros_like(emb)
+    _, gx = __ash.grid_query_backward(hm, z, emb, xs, *args, bidx, "smooth_step", grad_embeddings_out=ge)
+    ge64, go64 = oracle.query_backward_forward(z64, interpolation="smooth_step", **o64)
+    sb.assert_within(t(ge[touched]), ge64, mag["grad_emb"], "config 3 grad_emb")
+    sb.assert_within(t(gx), go64, mag["grad_off"], "config 3 grad_x")
+    # nothing landed outside the sample's blocks
+    inside = ge[touched].sum(dtype=torch.float64)
+    total = sum(ge[i : i + 50_000].sum(dtype=torch.float64) for i in range(0, nb, 50_000))
+    assert abs(float(total - inside)) <= 1e-9 * max(1.0, abs(float(total)))
+    # the same gradient as a row list
+    idx, rows, gx_r = __ash.grid_query_backward_rows(hm, z, emb, xs, *args, bidx, "smooth_step")
+    assert torch.equal(gx_r, gx)
+    ge.zero_()
+    __ash.rows_scatter_add(ge, idx, rows)
+    sb.assert_within(t(ge[touched]), ge64, mag["grad_emb"], "config 3 grad_emb (row list)")
+
+    # double backward
+    ge.zero_()
+    gz, _ = __ash.grid_query_backward_backward(hm, v, z, emb, xs, *args, bidx, "smooth_step", grad_embeddings_out=ge)
+    gz64, ge264, _ = oracle.query_backward_backward(v64, z64, interpolation="smooth_step", **o64)
+    sb.assert_within(t(gz), gz64, mag["grad_z"], "config 3 grad_z")
+    sb.assert_within(t(ge[touched]), ge264, mag["grad2_emb"], "config 3 grad2_emb")
 
 
 def test_config3_trilinear_full_size_identities():

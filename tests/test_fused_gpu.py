@@ -203,6 +203,102 @@ def test_in_place_gradient_mode_equals_dense_mode(kind, G, D):
     grid.grad_mode = "dense"
 
 
+@pytest.mark.parametrize("kind,G,D", [("unbounded", 8, 16), ("plain", 4, 3), ("bounded", 2, 5), ("plain", 8, 1)])
+def test_row_list_gradient_mode_equals_dense_mode(kind, G, D):
+    """grad_mode="row_list": both backward passes hand autograd an uncoalesced sparse gradient (8
+    records per query).  Densified it must equal the reference's dense contract for a step with a
+    rendering-style term AND an eikonal (gradient-of-gradient) term, also accumulated over two
+    steps, with identical gradients for the positions; records of queries without a gradient are
+    zero rows at valid cells; and applying the list to the parameters is a gradient-descent step."""
+    import __ash
+
+    grid, x = _make(kind, G, D, seed=13)
+
+    def step(xx):
+        xr = xx.clone().requires_grad_(True)
+        y, _ = grid(xr, "smooth_step")
+        (gx,) = torch.autograd.grad(y[:, :1], xr, torch.ones_like(y[:, :1]), create_graph=True)
+        loss = (y * y).sum() + ((gx.norm(dim=-1) - 1) ** 2).sum()
+        loss.backward()
+        return xr.grad
+
+    results = {}
+    for mode in ("dense", "row_list"):
+        grid.grad_mode = mode
+        grid.embeddings.grad = None
+        gx1 = step(x[:3000])
+        gx2 = step(x[2000:])
+        g = grid.embeddings.grad
+        assert g.is_sparse == (mode == "row_list")
+        results[mode] = (g.to_dense() if g.is_sparse else g.clone(), gx1, gx2)
+    for a, b in zip(results["dense"], results["row_list"]):
+        torch.testing.assert_close(a, b, rtol=2e-4, atol=1e-5 * max(1.0, float(a.abs().max())))
+
+    # one first-order backward: the list itself
+    grid.embeddings.grad = None
+    y, masks = grid(x.clone(), "linear")
+    y.sum().backward()
+    g = grid.embeddings.grad
+    idx, rows = g._indices(), g._values()
+    n = x.shape[0]
+    assert idx.shape == (2, 8 * n) and rows.shape == (8 * n, D)
+    assert int(idx[0].min()) >= 0 and int(idx[0].max()) < grid.num_embeddings
+    assert int(idx[1].min()) >= 0 and int(idx[1].max()) < G**3
+    answered = masks & (y != 0).any(dim=1)
+    assert torch.count_nonzero(rows.view(8, n, D)[:, ~answered]) == 0
+    # corner weights of a query sum to 1: with z = 1 every channel of its 8 rows sums to 1
+    torch.testing.assert_close(rows.view(8, n, D)[:, answered].sum(dim=0),
+                               torch.ones(int(answered.sum()), D, device=DEV), rtol=1e-5, atol=1e-6)
+    # the list applied to the parameters = a plain gradient-descent step
+    dense = g.to_dense()
+    before = grid.embeddings.detach().clone()
+    grid.apply_row_list_(alpha=-0.25)
+    torch.testing.assert_close(grid.embeddings.detach(), before - 0.25 * dense, rtol=1e-5, atol=1e-6)
+    # ... and to a dense buffer = the dense gradient
+    buf = torch.zeros_like(before)
+    __ash.rows_scatter_add(buf, idx, rows)
+    torch.testing.assert_close(buf, dense, rtol=1e-5, atol=1e-6)
+    # positions that need no gradient: same list, no grad_x
+    grid.embeddings.grad = None
+    (grid(x.clone(), "linear")[0]).sum().backward()
+    torch.testing.assert_close(grid.embeddings.grad.to_dense(), dense, rtol=1e-5, atol=1e-6)
+    # float64 tables
+    grid.embeddings.grad = None
+    grid.grad_mode = "dense"
+
+
+def test_row_list_entry_point_float64_and_second_order():
+    """ashb_grid_query_backward_rows through the shim in float64, first and second order, against the
+    dense entry points (exact up to the order of the sums)."""
+    import __ash
+
+    grid, x = _make("unbounded", 4, 6, seed=17)
+    emb = grid.embeddings.detach().double()
+    origin, cell_size = grid._cell_frame()
+    hm, lut = grid.engine.backend, grid._neighbor_lut32()
+    n = x.shape[0]
+    gen = torch.Generator(device=DEV).manual_seed(3)
+    z = torch.randn(n, 6, generator=gen, device=DEV, dtype=torch.float64)
+    ggx = torch.randn(n, 3, generator=gen, device=DEV, dtype=torch.float64)
+    _, _, bidx = __ash.grid_query_forward(hm, emb, x, cell_size, origin, 4, lut, "smooth_step")
+    ge, gx = __ash.grid_query_backward(hm, z, emb, x, cell_size, origin, 4, lut, bidx, "smooth_step")
+    idx, rows, gx_r = __ash.grid_query_backward_rows(hm, z, emb, x, cell_size, origin, 4, lut, bidx, "smooth_step")
+    buf = torch.zeros_like(emb)
+    __ash.rows_scatter_add(buf, idx, rows)
+    torch.testing.assert_close(buf, ge, rtol=1e-12, atol=1e-12)
+    assert torch.equal(gx, gx_r)
+    gz, ge2 = __ash.grid_query_backward_backward(hm, ggx, z, emb, x, cell_size, origin, 4, lut, bidx, "smooth_step")
+    idx, rows, gz_r = __ash.grid_query_backward_rows(hm, z, emb, x, cell_size, origin, 4, lut, bidx, "smooth_step",
+                                                     grad_grad_x=ggx)
+    buf.zero_()
+    __ash.rows_scatter_add(buf, idx, rows)
+    torch.testing.assert_close(buf, ge2, rtol=1e-12, atol=1e-12)
+    assert torch.equal(gz, gz_r)
+    # empty batch
+    idx, rows, side = __ash.grid_query_backward_rows(hm, z[:0], emb, x[:0], cell_size, origin, 4, lut, bidx[:0], "linear")
+    assert idx.shape == (2, 0) and rows.shape == (0, 6) and side.shape == (0, 3)
+
+
 def test_zero_grad_rows_clears_exactly_what_a_batch_added():
     grid, x = _make("unbounded", 8, 16, seed=21)
     grid.grad_mode = "in_place"

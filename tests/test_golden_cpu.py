@@ -32,6 +32,10 @@ def test_bounded_golden(ash_cpu):
     gc.check_bounded(ash_cpu, CPU)
 
 
+def test_reference_written_checkpoints_load(ash_cpu):
+    gc.check_checkpoints(ash_cpu, CPU)
+
+
 def test_engine_contract(ash_cpu, tmp_path):
     """unittests/test_engine.py semantics on the host side: index set, duplicates, state_dict
     round trip incl. the empty map, resize, warnings on empty input and on overflow."""

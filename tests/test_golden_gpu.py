@@ -28,6 +28,12 @@ def test_bounded_golden():
     gc.check_bounded(ash, DEV)
 
 
+def test_reference_written_checkpoints_load():
+    import ash
+
+    gc.check_checkpoints(ash, DEV)
+
+
 def test_smoke_entry():
     import __graft_entry__
 

@@ -1,11 +1,15 @@
 """Sparse-dense grid parity on the GPU: the reference's unittests/test_sparsedense_grid.py
 replayed on the CUDA library, and forward / backward / double-backward outputs compared with
-the CPU oracle (fp32: 1e-5 relative / 1e-6 absolute, the tolerance the task states; fp64 tighter)."""
+the CPU oracle.  fp32 results are held to the task's 1e-5 relative / 1e-6 absolute against the
+oracle evaluated in float64 on the same inputs, relative to the sum of the magnitudes of the terms
+each output adds up (tests/sum_bounds.py) -- the order of the scattered sums changes from run to
+run, their bound does not; float64 results are compared directly at 1e-12."""
 import numpy as np
 import pytest
 import torch
 
 import oracle
+import sum_bounds as sb
 
 pytestmark = pytest.mark.gpu
 
@@ -119,33 +123,43 @@ def test_forward_backward_double_backward_vs_oracle(D, G, interp, dtype):
     assert 0 < masks.sum() < n
     emb = grid.embeddings.detach()
     luts = (grid.lut_grid_nb2grid_idx, grid.lut_cell_nb2cell_idx, grid.lut_cell_nb2grid_nb)
-    rt, at = (RTOL, ATOL) if dtype == torch.float32 else (1e-12, 1e-13)
-    # scattered sums meet in nondeterministic order; allow a few ulps more there
-    rt_s, at_s = (4 * RTOL, 4 * ATOL) if dtype == torch.float32 else (1e-11, 1e-12)
+    f32 = dtype == torch.float32
+    z = torch.rand(n, D, generator=gen, device=DEV, dtype=dtype) - 0.5
+    ggo = torch.rand(n, 3, generator=gen, device=DEV, dtype=dtype) - 0.5
+    o64 = sb.as_float64(o)
+    z64, ggo64 = z.double().cpu().numpy(), ggo.double().cpu().numpy()
+    mag = sb.magnitudes(o, interp, z=z64, ggo=ggo64) if f32 else None
+
+    def check(got, exact, what, extra=0.0):
+        got = got.detach().cpu().numpy()
+        if f32:   # 1e-5 * sum|terms| + 1e-6 against the float64 oracle
+            sb.assert_within(got, exact, mag[what] + extra, what, RTOL, ATOL)
+        else:     # the scattered sums meet in nondeterministic order: a few ulps
+            np.testing.assert_allclose(got, exact, rtol=1e-11, atol=1e-12)
 
     y = __ash.query_forward(emb, off, gi, ci, masks, *luts, G, interp)
-    y_ref = oracle.query_forward(interpolation=interp, **o)
-    _close(y, y_ref, rt, at)
+    y_ref = oracle.query_forward(interpolation=interp, **o64)
+    check(y, y_ref, "y")
+    if f32:  # the plain statement of the tolerance holds too where nothing is scattered
+        _close(y, oracle.query_forward(interpolation=interp, **o), RTOL, ATOL)
     zero_rows = (y_ref == 0).all(axis=1) & o["masks"]
     assert zero_rows.any(), "test must include queries with an absent neighbour block"
 
-    z = torch.rand(n, D, generator=gen, device=DEV, dtype=dtype) - 0.5
     ge, go = __ash.query_backward_forward(z, emb, off, gi, ci, masks, *luts, G, interp)
-    ge_ref, go_ref = oracle.query_backward_forward(z.cpu().numpy(), interpolation=interp, **o)
-    _close(go, go_ref, rt_s, at_s)
-    _close(ge, ge_ref, rt_s, at_s)
+    ge_ref, go_ref = oracle.query_backward_forward(z64, interpolation=interp, **o64)
+    check(go, go_ref, "grad_off")
+    check(ge, ge_ref, "grad_emb")
 
-    ggo = torch.rand(n, 3, generator=gen, device=DEV, dtype=dtype) - 0.5
     gz, ge2, go2 = __ash.query_backward_backward(None, ggo, z, emb, off, gi, ci, masks, *luts, G, interp)
-    gz_ref, ge2_ref, go2_ref = oracle.query_backward_backward(ggo.cpu().numpy(), z.cpu().numpy(), interpolation=interp, **o)
-    _close(gz, gz_ref, rt_s, at_s)
-    _close(ge2, ge2_ref, rt_s, at_s)
+    gz_ref, ge2_ref, go2_ref = oracle.query_backward_backward(ggo64, z64, interpolation=interp, **o64)
+    check(gz, gz_ref, "grad_z")
+    check(ge2, ge2_ref, "grad2_emb")
     assert torch.count_nonzero(go2) == 0
 
-    # accumulate-in-place mode adds on top of what is there
+    # accumulate-in-place mode adds on top of what is there (the 1 already there is one more term)
     acc = torch.ones_like(emb)
     __ash.query_backward_forward(z, emb, off, gi, ci, masks, *luts, G, interp, grad_embeddings_out=acc)
-    _close(acc - 1, ge_ref, 10 * rt_s, 10 * at_s)
+    check(acc - 1, ge_ref, "grad_emb", extra=1.0)
 
 
 @pytest.mark.parametrize("D,G", [(2, 1), (1, 2), (4, 4), (8, 8)])
@@ -165,9 +179,11 @@ def test_autograd_first_order_matches_oracle(D, G):
         (gx,) = torch.autograd.grad((y * w).sum(), x, retain_graph=True)
         (y * w).sum().backward()
         _, o = _oracle_inputs(grid, x.detach())
-        ge_ref, go_ref = oracle.query_backward_forward(w.cpu().numpy(), interpolation=interp, **o)
-        _close(gx, go_ref, 4 * RTOL, 4 * ATOL)  # d offset / d x == 1 for the unit transform
-        _close(grid.embeddings.grad, ge_ref, 4 * RTOL, 4 * ATOL)
+        w64 = w.double().cpu().numpy()
+        ge_ref, go_ref = oracle.query_backward_forward(w64, interpolation=interp, **sb.as_float64(o))
+        mag = sb.magnitudes(o, interp, z=w64)
+        sb.assert_within(gx.cpu().numpy(), go_ref, mag["grad_off"], "grad_x")  # d offset / d x == 1 for the unit transform
+        sb.assert_within(grid.embeddings.grad.cpu().numpy(), ge_ref, mag["grad_emb"], "grad_emb")
 
 
 @pytest.mark.parametrize("D,G", [(1, 2), (4, 4), (16, 8)])
@@ -190,9 +206,10 @@ def test_autograd_double_backward_eikonal(D, G):
     nrm = gx_d.norm(dim=-1, keepdim=True)
     dl_dgx = (2 * (nrm - 1) / n) * gx_d / nrm.clamp_min(1e-30)
     _, o = _oracle_inputs(grid, x.detach())
-    _, ge_ref, _ = oracle.query_backward_backward(
-        dl_dgx.cpu().numpy(), ones.cpu().numpy(), interpolation="linear", **o)
-    _close(grid.embeddings.grad, ge_ref, 1e-4, 1e-6)
+    ggo64, ones64 = dl_dgx.double().cpu().numpy(), ones.double().cpu().numpy()
+    _, ge_ref, _ = oracle.query_backward_backward(ggo64, ones64, interpolation="linear", **sb.as_float64(o))
+    mag = sb.magnitudes(o, "linear", z=ones64, ggo=ggo64)
+    sb.assert_within(grid.embeddings.grad.cpu().numpy(), ge_ref, mag["grad2_emb"], "eikonal grad_emb")
 
 
 def test_gradcheck_float64():

@@ -307,8 +307,19 @@ def test_rehash_keeps_associations_and_drops_tombstones(dim):
     assert eng.size() == cap and torch.unique(eng.find(_diag_keys(dim, cap))[0]).numel() == cap
 
 
+@pytest.fixture(params=[0, 1], ids=["find_unfiltered", "find_filtered"])
+def find_filter(request):
+    """Runs a test with the occupancy filter of find forced off and forced on (the automatic choice
+    would never pick it for tables this small)."""
+    import __ash
+
+    __ash.set_find_filter(request.param)
+    yield request.param
+    __ash.set_find_filter(-1)
+
+
 @pytest.mark.parametrize("dim", [1, 2, 3, 4])
-def test_random_op_sequences_against_dict_model(dim):
+def test_random_op_sequences_against_dict_model(dim, find_filter):
     """Seeded random sequences of insert / erase / find / items / clear over a small key range (many
     collisions, re-insertions of erased keys, in-batch duplicates, occasional rebuilds) against a
     plain Python dict: hit masks, sizes, index stability while a key lives, index uniqueness among
@@ -392,3 +403,58 @@ def test_cooperative_find_equals_one_thread_find(dim):
                 assert 0.05 < float(a[1].float().mean()) < 1.0
     finally:
         __ash.set_find_cooperative(False)
+
+
+@pytest.mark.parametrize("dim", [1, 2, 3])
+def test_find_with_occupancy_filter_equals_plain_find(dim):
+    """The find that consults the one-bit-per-slot occupancy map first answers exactly as the plain
+    probe: in a sparsely filled table (most misses end at the bit map), across tombstones, after
+    clear(), after a state_dict round trip (load_states rebuilds the map) and after rehash()."""
+    import __ash
+    from ash import ASHEngine
+
+    g = torch.Generator(device=DEV).manual_seed(70 + dim)
+    cap = 20000
+    span = {1: 200000, 2: 450, 3: 60}[dim]
+    keys = torch.randint(-span, span, (cap // 4, dim), dtype=torch.int32, device=DEV, generator=g)
+    q = torch.randint(-span, span, (30011, dim), dtype=torch.int32, device=DEV, generator=g)
+    q[::3] = keys[torch.randint(keys.shape[0], (q[::3].shape[0],), device=DEV, generator=g)]
+    eng = ASHEngine(dim=dim, capacity=cap, device=DEV)
+
+    def both(n=None):
+        qq = q if n is None else q[:n]
+        __ash.set_find_filter(0)
+        a = eng.backend.find(qq)
+        __ash.set_find_filter(1)
+        b = eng.backend.find(qq)
+        assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+        return a
+
+    try:
+        both()                                           # empty table: every query is a miss
+        eng.insert_keys(keys)
+        idx, ok = both()
+        assert 0.3 < float(ok.float().mean()) < 0.6
+        for n in (1, 33, 0):
+            both(n)
+        eng.erase(keys[::5].contiguous())                # tombstones keep their bit: chains run through them
+        both()
+        eng.insert_keys(keys[::10].contiguous())         # re-use of erased slots
+        both()
+        state = {k: v.clone() for k, v in eng.state_dict().items()}
+        eng2 = ASHEngine(dim=dim, capacity=cap, device=DEV)
+        eng2.load_state_dict(state)
+        __ash.set_find_filter(1)
+        c = eng2.backend.find(q)
+        a = both()
+        assert torch.equal(a[1], c[1]) and torch.equal(a[0][a[1]], c[0][c[1]])
+        eng.backend.rehash()
+        d = both()
+        assert torch.equal(a[1], d[1]) and torch.equal(a[0], d[0])
+        eng.clear()
+        assert not both()[1].any()
+        eng.insert_keys(keys[:100].contiguous())
+        assert int(both()[1].sum()) >= 100 // 3
+        assert eng.backend.status() == 0
+    finally:
+        __ash.set_find_filter(-1)

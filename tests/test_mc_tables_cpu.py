@@ -1,4 +1,4 @@
-"""The generated marching-cubes table (torch-ash_b200/csrc/gen_mc_tables.py) is derived, not
+"""The generated marching-cubes table (oracle/gen_mc_tables.py) is derived, not
 transcribed, so it is validated by what a triangulation table must guarantee: on closed surfaces
 every mesh edge is shared by exactly two triangles that traverse it in opposite directions (no
 cracks, consistent orientation), the Euler characteristic is that of the surface, normals point
@@ -9,7 +9,7 @@ import os
 import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-_spec = importlib.util.spec_from_file_location("gen_mc_tables", os.path.join(ROOT, "torch-ash_b200", "csrc", "gen_mc_tables.py"))
+_spec = importlib.util.spec_from_file_location("gen_mc_tables", os.path.join(ROOT, "oracle", "gen_mc_tables.py"))
 gen = importlib.util.module_from_spec(_spec)
 _spec.loader.exec_module(gen)
 TRIS, MASKS = gen.build()

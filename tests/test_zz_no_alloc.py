@@ -5,7 +5,8 @@ Some users of the library run where device memory cannot be allocated once work 
 ``ashb_tsdf_fuse_frame_static`` keeps its per-block scratch in a fixed array inside the library.
 This test drives it through the C ABI on two frames in a row and expects exactly what
 ``ashb_tsdf_touch`` + ``ashb_tsdf_integrate`` produce with caller-provided scratch, within the
-tolerance the fusion parity test uses.  It is collected last on purpose."""
+tolerance the fusion parity test uses, and that the amount of free device memory the driver reports
+is the same before and after the second call.  It is collected last on purpose."""
 import numpy as np
 import pytest
 import torch
@@ -40,9 +41,16 @@ def test_static_scratch_fusion_matches_regular_path():
         depth, color = scene.render(K.to(DEV), pose.float().to(DEV), H, W)
         fusion.fuse_frame(ash.DotDict(depth=depth.clone(), depth_scale=1.0, depth_max=depth_max, intrinsic=K,
                                       extrinsic=E, rgb=color))
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         __ash.tsdf_fuse_frame_static(
             static.engine.backend, static.embeddings.data, G, depth, color, K.double().tolist(), E.tolist(),
             np.linalg.inv(E.numpy()).tolist(), depth_max, cell, [0.0, 0.0, 0.0], dil, fusion.trunc)
+        torch.cuda.synchronize()
+        if call > 0:
+            # the driver's count of free device memory has not moved: the call obtained none (the
+            # first call may still have paid for the context's lazily loaded kernels)
+            assert torch.cuda.mem_get_info()[0] == free_before
         k_r, e_r = _sorted_state(regular)
         k_s, e_s = _sorted_state(static)
         assert len(k_r) > 50, "the frame must allocate blocks"

@@ -37,6 +37,7 @@ _lib.ashb_map_destroy.argtypes = [_vp]
 _lib.ashb_map_clear.argtypes = [_vp, _vp]
 _lib.ashb_map_size.argtypes = [_vp, _vp, _c.POINTER(_i64)]
 _lib.ashb_map_status.argtypes = [_vp, _vp, _c.POINTER(_c.c_uint32)]
+_lib.ashb_map_status_async.argtypes = [_vp, _vp, _vp]
 _lib.ashb_map_find.argtypes = [_vp, _vp, _i64, _vp, _vp, _vp]
 _lib.ashb_map_insert_keys.argtypes = [_vp, _vp, _i64, _vp]
 _lib.ashb_map_insert_values.argtypes = [_vp, _vp, _i64, _int, _vp, _vp, _vp, _vp]
@@ -97,6 +98,18 @@ _lib.ashb_render_rays_intervals.argtypes = _RAY_GRID + [_vp, _vp, _vp, _vp, _f32
                                                         _vp]
 _lib.ashb_render_intervals_forward.argtypes = _RAY_GRID + [_vp] * 6 + [_i64, _vp, _i64, _vp]
 _lib.ashb_render_intervals_backward.argtypes = _RAY_GRID + [_vp] * 5 + [_i64, _vp, _vp, _vp, _vp, _i64, _vp]
+_lib.ashb_grid_query_backward_rows.argtypes = [_vp, _int, _int, _int, _vp, _vp, _vp, _vp, _c.c_double, _vp, _int, _vp, _vp,
+                                               _vp, _vp, _vp, _i64, _i64, _i64, _vp]
+_lib.ashb_rows_scatter_add.argtypes = [_int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _c.c_double, _vp]
+_lib.ashb_set_find_filter.argtypes = [_int]
+_lib.ashb_measure_random_reads_ilp.argtypes = [_vp, _i64, _i64, _int, _int, _c.c_uint32, _vp, _vp]
+_ROUTED_LAYOUT = [_vp] + [_i64] * 7 + [_int, _int]
+_lib.ashb_routed_route.argtypes = [_vp, _vp, _i64, _c.c_double, _vp, _int, _vp, _vp, _i64, _i64] + _ROUTED_LAYOUT + [_vp] * 4
+_lib.ashb_routed_forward.argtypes = [_vp, _int, _vp, _c.c_double, _vp, _int, _vp, _vp, _i64, _i64] + _ROUTED_LAYOUT + [_vp]
+_lib.ashb_routed_unpack_y.argtypes = [_vp, _i64, _vp, _vp, _i64] + _ROUTED_LAYOUT + [_vp]
+_lib.ashb_routed_send_z.argtypes = [_vp, _i64, _vp, _i64] + _ROUTED_LAYOUT + [_vp]
+_lib.ashb_routed_backward.argtypes = [_vp, _int, _vp, _vp, _int, _c.c_double, _vp, _int, _vp, _vp, _i64, _i64] + _ROUTED_LAYOUT + [_vp]
+_lib.ashb_routed_unpack_grad_x.argtypes = [_vp, _i64, _vp, _i64] + _ROUTED_LAYOUT + [_vp]
 _lib.ashb_grid_zero_rows.argtypes = [_vp, _int, _vp, _vp, _c.c_double, _vp, _int, _vp, _vp, _i64, _i64, _i64, _vp]
 
 STATUS_CAPACITY, STATUS_PROBE, STATUS_SPIN, STATUS_DUPLICATE = 1, 2, 4, 8
@@ -109,14 +122,23 @@ def _check(rc: int):
         raise RuntimeError(f"libashb200: {_lib.ashb_last_error_string().decode()} (status {rc})")
 
 
-def measure_random_reads(buffer: torch.Tensor, n_reads: int, fetch_bytes: int = 64, seed: int = 1) -> None:
-    """Launch ``n_reads`` scattered 16-byte reads over ``buffer`` (a large CUDA tensor); time it from
-    outside.  The reads per second reached are the ceiling for the probe / gather kernels."""
+def measure_random_reads(buffer: torch.Tensor, n_reads: int, fetch_bytes: int = 64, seed: int = 1,
+                         reads_per_thread: int = 1) -> None:
+    """Launch ``n_reads`` scattered 16-byte reads over ``buffer`` (a large CUDA tensor), ``reads_per_thread``
+    (1, 2, 4, 8) of them in flight per thread; time it from outside.  The reads per second reached are
+    the ceiling for the probe / gather kernels."""
     buf = _cuda(buffer, "buffer")
     sink = torch.zeros(1, dtype=torch.int64, device=buf.device)
     with torch.cuda.device(buf.device):
-        _check(_lib.ashb_measure_random_reads(buf.data_ptr(), buf.numel() * buf.element_size(), int(n_reads),
-                                              int(fetch_bytes), int(seed) & 0xFFFFFFFF, sink.data_ptr(), _stream(buf.device)))
+        _check(_lib.ashb_measure_random_reads_ilp(buf.data_ptr(), buf.numel() * buf.element_size(), int(n_reads),
+                                                  int(fetch_bytes), int(reads_per_thread), int(seed) & 0xFFFFFFFF,
+                                                  sink.data_ptr(), _stream(buf.device)))
+
+
+def set_find_filter(mode: int) -> None:
+    """Process-wide use of the one-bit-per-slot occupancy map in ``HashMap.find`` (key_dim <= 3):
+    -1 automatic (tables of 64 MB and more), 0 never, 1 always.  Same answers in every mode."""
+    _check(_lib.ashb_set_find_filter(int(mode)))
 
 
 def set_scatter_aggregation(enable: bool) -> None:
@@ -293,6 +315,16 @@ class HashMap:
         st = _c.c_uint32()
         _check(_lib.ashb_map_status(self._h, _stream(self._device), _c.byref(st)))
         return int(st.value)
+
+    def status_async(self, host_word: torch.Tensor) -> torch.cuda.Event:
+        """Enqueue a copy of the status word into ``host_word`` (a pinned int32 CPU tensor of one
+        element) and its clearing; returns the event after which ``host_word`` holds it."""
+        if host_word.is_cuda or host_word.dtype != torch.int32 or host_word.numel() != 1 or not host_word.is_pinned():
+            raise RuntimeError("host_word must be a pinned int32 CPU tensor of one element")
+        _check(_lib.ashb_map_status_async(self._h, host_word.data_ptr(), _stream(self._device)))
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self._device))
+        return ev
 
     def rehash(self) -> None:
         """Rebuild the table from its live entries, dropping erased slots (indices unchanged)."""
@@ -664,6 +696,54 @@ def grid_query_backward_backward(hashmap, grad_grad_x, z, embeddings, x, cell_si
         bidx.data_ptr() if bidx is not None else None, grad_z.data_ptr(), grad_emb.data_ptr(), zero, n, emb.shape[0],
         emb.shape[2], _stream(dev)))
     return grad_z, grad_emb
+
+
+def grid_query_backward_rows(hashmap, z, embeddings, x, cell_size, origin, grid_dim, nb_lut, block_idx, interpolation,
+                             need_grad_x=True, grad_grad_x=None):
+    """The backward passes with the embedding gradient as a ROW LIST: returns ``(idx int64 (2, 8N),
+    rows (8N, D), side)``; record ``c * N + q`` is corner ``c`` of query ``q``, ``idx[0]`` its block
+    index, ``idx[1]`` its cell index.  ``side`` is grad_x (N, 3) (None unless ``need_grad_x``) for the
+    first-order pass, or grad_z (N, D) when ``grad_grad_x`` is given (the double backward)."""
+    emb, x, nb_lut = _fused_args(hashmap, embeddings, x, nb_lut)
+    n, dev, D = x.shape[0], emb.device, emb.shape[2]
+    z = _cuda(z, "z", emb.dtype)
+    if z.shape != (n, D):
+        raise RuntimeError("z must be (num_queries, embedding_dim)")
+    second = grad_grad_x is not None
+    ggx = None
+    if second:
+        ggx = _cuda(grad_grad_x, "grad_grad_x", emb.dtype)
+        if ggx.shape != (n, 3):
+            raise RuntimeError("grad_grad_x must be (num_queries, 3)")
+        side = torch.empty_like(z)
+    else:
+        side = torch.empty((n, 3), dtype=emb.dtype, device=dev) if need_grad_x else None
+    idx = torch.empty((2, 8 * n), dtype=torch.int64, device=dev)
+    rows = torch.empty((8 * n, D), dtype=emb.dtype, device=dev)
+    bidx = _cuda(block_idx, "block_idx", torch.int32) if block_idx is not None else None
+    _check(_lib.ashb_grid_query_backward_rows(
+        hashmap._h, _dtype_code(emb), _interp_code(interpolation), int(second), ggx.data_ptr() if second else None,
+        z.data_ptr(), emb.data_ptr(), x.data_ptr(), float(cell_size), _host_floats(origin, 3), int(grid_dim),
+        nb_lut.data_ptr(), bidx.data_ptr() if bidx is not None else None, idx.data_ptr(), rows.data_ptr(),
+        side.data_ptr() if side is not None else None, n, emb.shape[0], D, _stream(dev)))
+    return idx, rows, side
+
+
+def rows_scatter_add(dst, idx, rows, alpha=1.0):
+    """``dst[idx[0][r], idx[1][r], :] += alpha * rows[r]`` for a row list; ``dst`` is a contiguous
+    (num_embeddings, cells_per_grid, D) tensor: a gradient buffer, or the parameters with ``alpha =
+    -learning_rate``."""
+    dst = _cuda(dst, "dst")
+    if dst.dim() != 3 or not dst.is_contiguous():
+        raise RuntimeError("dst must be a contiguous (num_embeddings, cells_per_grid, embedding_dim) tensor")
+    idx = _cuda(idx, "idx", torch.int64)
+    rows = _cuda(rows, "rows", dst.dtype)
+    m = rows.shape[0]
+    if idx.shape != (2, m) or rows.shape != (m, dst.shape[2]):
+        raise RuntimeError("idx must be (2, m) and rows (m, embedding_dim)")
+    with torch.cuda.device(dst.device):
+        _check(_lib.ashb_rows_scatter_add(_dtype_code(dst), dst.data_ptr(), idx.data_ptr(), rows.data_ptr(), m,
+                                          dst.shape[0], dst.shape[1], dst.shape[2], float(alpha), _stream(dst.device)))
 
 
 def convolution_forward_tiled(inputs, weights, grid_indices, lut_grid_nb27, grid_dim, radius):
@@ -1139,3 +1219,52 @@ def render_intervals_backward(hashmap, embeddings, nb_lut, cell_size, origin, ra
                                                    counts.data_ptr(), intervals.shape[1], out.data_ptr(), go.data_ptr(),
                                                    ge.data_ptr(), gb.data_ptr(), n, _stream(dev)))
     return ge, gb
+
+
+# ---- table sharded over the ranks, queries routed to the owners -----------------------------------
+# ``layout`` = (peer_bases_dev, mailbox_bytes, inbox_x, counts, inbox_z, out_y, out_gx, region_capacity, world, rank);
+# ``geom`` = (cell_size, origin, grid_dim, nb_lut int32, row_of int32 viewed as uint32, n_emb, D).
+def _routed_geom(geom):
+    cell_size, origin, grid_dim, nb_lut, row_of, n_emb, D = geom
+    return (float(cell_size), _host_floats(origin, 3), int(grid_dim), nb_lut.data_ptr(), row_of.data_ptr(), int(n_emb), int(D))
+
+
+def routed_route(hashmap, x, geom, layout, cursor, where, status):
+    """Send every position of ``x`` (N, 3) float32 to the owner of its block; ``where`` int32 (N,)
+    receives owner << 26 | slot (-1: no block there)."""
+    x = _cuda(x, "x", torch.float32)
+    _check(_lib.ashb_routed_route(hashmap._h, x.data_ptr(), x.shape[0], *_routed_geom(geom), *layout, cursor.data_ptr(),
+                                  where.data_ptr(), status.data_ptr(), _stream(x.device)))
+
+
+def routed_forward(hashmap, emb_bases, geom, layout, interpolation):
+    _check(_lib.ashb_routed_forward(hashmap._h, _interp_code(interpolation), emb_bases, *_routed_geom(geom), *layout,
+                                    _stream(hashmap.device())))
+
+
+def routed_unpack_y(where, n, D, layout):
+    dev = where.device
+    y = torch.empty((n, D), dtype=torch.float32, device=dev)
+    masks = torch.empty(n, dtype=torch.bool, device=dev)
+    with torch.cuda.device(dev):
+        _check(_lib.ashb_routed_unpack_y(where.data_ptr(), n, y.data_ptr(), masks.data_ptr(), D, *layout, _stream(dev)))
+    return y, masks
+
+
+def routed_send_z(where, z, layout):
+    z = _cuda(z, "z", torch.float32)
+    with torch.cuda.device(z.device):
+        _check(_lib.ashb_routed_send_z(where.data_ptr(), z.shape[0], z.data_ptr(), z.shape[1], *layout, _stream(z.device)))
+
+
+def routed_backward(hashmap, emb_bases, grad_bases, geom, layout, interpolation, need_grad_x):
+    _check(_lib.ashb_routed_backward(hashmap._h, _interp_code(interpolation), emb_bases, grad_bases, int(bool(need_grad_x)),
+                                     *_routed_geom(geom), *layout, _stream(hashmap.device())))
+
+
+def routed_unpack_grad_x(where, n, D, layout):
+    dev = where.device
+    gx = torch.empty((n, 3), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _check(_lib.ashb_routed_unpack_grad_x(where.data_ptr(), n, gx.data_ptr(), D, *layout, _stream(dev)))
+    return gx

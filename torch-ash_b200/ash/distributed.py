@@ -1,23 +1,29 @@
 """Multi-GPU scaling of the hash engine and the grid query (one process per GPU).
 
 The reference is single-process, single-GPU (no collective anywhere in its tree); this module
-is new.  Two schemes, both on ``torch.distributed`` (NCCL over NVLink/NVSwitch on GPUs; any
-backend works, which is how the host logic is tested with gloo on CPU):
+is new.  Everything sits on ``torch.distributed`` (NCCL over NVLink/NVSwitch on GPUs; the
+collective-only paths work on any backend, which is how the host logic is tested with gloo on CPU):
 
 * ``PartitionedHashMap`` -- a hash map too large for one GPU, partitioned by a hash of the key.
   Rank ``owner(key)`` holds the key in a local ``ASHEngine`` of ``ceil(capacity / P * slack)``
-  entries.  insert / find / erase route keys to their owners with one all-to-all of counts
-  and one all-to-all(v) of the packed int32 keys; find routes ``(index, mask)`` back the same
-  way.  Remote data always lands in local memory through the collective before a kernel reads
-  it.  A global index is ``local_index * P + owner``.
+  entries; a global index is ``local_index * P + owner``.  Two transports: all-to-all(v) of the
+  grouped keys and of the answers (any backend), or -- with ``peer_max_batch`` -- kernels that write
+  keys straight into the owners' mailboxes and answers straight into the askers' over peer memory.
 * Replicated grid, sharded queries -- every rank holds the whole grid and queries its own shard
   of the batch with no communication; ``allreduce_gradients`` sums the embedding gradients
-  afterwards (dense all-reduce: right for tables up to a few GB).  Row ``i`` of the embeddings
-  must mean the same block on every rank for that sum to be meaningful, and the index a key
-  receives depends on the order in which concurrent inserts win, which differs from process to
-  process: ``broadcast_state`` copies one rank's key -> index map, free-index stack and
-  parameters to all others (call it after every change of the block structure).
+  afterwards (right for tables up to a few GB).  Row ``i`` of the embeddings must mean the same
+  block on every rank for that sum to be meaningful, and the index a key receives depends on the
+  order in which concurrent inserts win, which differs from process to process:
+  ``broadcast_state`` copies one rank's key -> index map, free-index stack and parameters to all
+  others (call it after every change of the block structure).
+* ``ShardedSparseDenseGrid`` -- the table split over the ranks by block; queries read their corner
+  rows from, and add their gradient rows into, the owners' memory over NVLink (peer loads and
+  reductions inside the query kernels); all three autograd levels.
+* ``RoutedSparseDenseGrid`` -- the table split over the ranks by block; every query is SENT to the
+  owner of its block, which gathers, interpolates and scatters in its own memory and returns the
+  result row (and dL/dx): a query crosses NVLink as tens of bytes instead of its kilobyte of rows.
 """
+import warnings
 from typing import Optional, Tuple
 
 import torch
@@ -130,9 +136,37 @@ class PartitionedHashMap:
         self.engine = ASHEngine(key_dim, self.local_capacity, device)
         self.device = self.engine.device
         self.mailbox = None
+        self._pending = None   # (pinned status words, event) of the last update over peer memory
         if peer_max_batch > 0:
             assert self.device.type == "cuda" and key_dim <= 3, "the peer transport needs CUDA and key_dim <= 3"
             self.mailbox = _PeerMailbox(self.world, self.rank, peer_max_batch, self.device, group)
+            self._status_host = torch.zeros(2, dtype=torch.int32).pin_memory()
+
+    def _report_update_status(self, wait: bool) -> None:
+        """Surface what the last update over peer memory recorded on THIS owner: the local table's
+        status word (capacity exhausted -> the same warning the collective path gives through
+        ``ASHEngine._after_insert``, ash/core.py:206-211; a probe or wait that gave up -> error) and
+        the mailbox's (a region overflowed -> error).  The words were copied to pinned memory behind
+        the update; they are looked at when the next call finds the copy complete, or at once when
+        ``wait`` (size(), local_items())."""
+        if self._pending is None:
+            return
+        words, event = self._pending
+        if not wait and not event.query():
+            return
+        event.synchronize()
+        self._pending = None
+        table, box = int(words[0]), int(words[1])
+        words.zero_()
+        if table & backend.STATUS_CAPACITY:
+            warnings.warn(
+                f"Insertion exceeds this rank's share ({self.local_capacity}) of the hash map capacity; the keys "
+                "beyond it were dropped. Please resize the hash map or the behavior could be unexpected.")
+        if table & ~backend.STATUS_CAPACITY:
+            raise RuntimeError(f"partitioned hash map: local table status 0x{table:x}")
+        if box:
+            raise RuntimeError("partitioned hash map: a mailbox region overflowed (a rank sent one owner more keys "
+                               "than peer_max_batch)")
 
     def _route(self, keys: torch.Tensor) -> Tuple[_Route, torch.Tensor]:
         keys = keys.to(self.device, torch.int32).contiguous()
@@ -165,12 +199,19 @@ class PartitionedHashMap:
 
     def _update_over_peer_memory(self, keys: torch.Tensor, erase: bool) -> None:
         box = self.mailbox
+        self._report_update_status(wait=False)
         keys = keys.to(self.device, torch.int32).contiguous()
         assert keys.dim() == 2 and keys.shape[1] == self.key_dim, "keys shape mismatch"
         backend.peer_route_keys(keys, self.world, self.rank, box.layout, box.cursor, box.status)
         box.barrier()                      # every inbox is complete
         backend.peer_update(self.engine.backend, erase, self.world, self.rank, box.layout)
         box.barrier()                      # every inbox has been consumed and may be reused
+        # what the owner's table and the mailbox recorded travels to pinned memory behind the update
+        # and is reported by the next call that finds it there (no host synchronisation here)
+        self._report_update_status(wait=True)   # the pinned words are about to be reused
+        self._status_host[1:].copy_(box.status, non_blocking=True)
+        box.status.zero_()
+        self._pending = (self._status_host, self.engine.backend.status_async(self._status_host[:1]))
         # the engine's host-side bounds are stale after native updates
         self.engine._size_bound = self.engine.capacity
         if erase:
@@ -183,6 +224,7 @@ class PartitionedHashMap:
     def find(self, keys: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         """(global indices int64 (N,), masks bool (N,)); a miss has index 0 and mask False."""
         if self._over_peer_memory(keys):
+            self._report_update_status(wait=False)
             return self._find_over_peer_memory(keys)
         route, mine = self._route(keys)
         if mine.shape[0]:
@@ -207,11 +249,13 @@ class PartitionedHashMap:
 
     def local_items(self) -> Tuple[torch.Tensor, torch.Tensor]:
         """This rank's (keys, GLOBAL indices)."""
+        self._report_update_status(wait=True)
         keys, idx = self.engine.items()
         return keys, idx * self.world + self.rank
 
     def size(self) -> int:
         """Total number of live keys over all ranks."""
+        self._report_update_status(wait=True)
         n = torch.tensor([self.engine.size()], dtype=torch.int64, device=self.device)
         dist.all_reduce(n, group=self.group)
         return int(n.item())
@@ -376,9 +420,8 @@ class ShardedSparseDenseGrid(UnBoundedSparseDenseGrid):
         self.fused = True
         # Option: keep a local copy (N, 8, D) of the corner rows a forward fetched when the positions
         # need a gradient, so that d/dx in the backward passes reads the copy instead of the owners'
-        # memory.  Measured no gain (2 GPUs: 9.25 against 7.99 ms per step; 8 GPUs: 13.3 against
-        # 12.2 ms): the step is bound by the 16-byte gradient reductions crossing the links, not by
-        # the second read of the rows.  Off by default.
+        # memory.  Off by default: the step is bound by the gradient reductions crossing the links,
+        # not by the second read of the rows.
         self.keep_fetched_rows = False
 
     def _allocate_embeddings(self) -> torch.Tensor:
@@ -418,6 +461,175 @@ class ShardedSparseDenseGrid(UnBoundedSparseDenseGrid):
     def finish_backward(self) -> None:
         self._barrier()   # every rank's gradient rows have landed
         self.embeddings.grad = self._grad_shard
+
+    @torch.no_grad()
+    def zero_grad_shard_(self) -> None:
+        self._grad_shard.zero_()
+
+
+def coarse_owner_of(block_coords: torch.Tensor, world_size: int, coarse_shift: int = 2) -> torch.Tensor:
+    """Owner rank per BLOCK for ``RoutedSparseDenseGrid``: ``owner_of`` applied to the block
+    coordinate shifted right by ``coarse_shift`` bits per axis, so the 4 x 4 x 4 blocks of one coarse
+    cell -- and with them most +x/+y/+z neighbours of a block -- live on one rank."""
+    return owner_of(torch.bitwise_right_shift(block_coords.to(torch.int64), coarse_shift).to(torch.int32), world_size)
+
+
+class _RoutedMailbox:
+    """Symmetric device memory of the routed query: per rank an inbox of positions, an inbox of
+    incoming gradients, the result rows and the position gradients coming back (``world`` regions of
+    ``region_capacity`` records each; rank r writes region r of its peers' sections)."""
+
+    def __init__(self, world: int, rank: int, region_capacity: int, max_batch: int, D: int, device, group) -> None:
+        import torch.distributed._symmetric_memory as symm
+
+        cap = int(region_capacity)
+        recs = world * cap
+        align = lambda v: (v + 255) // 256 * 256
+        inbox_x = 0
+        counts = align(inbox_x + recs * 16)
+        inbox_z = align(counts + world * 4)
+        out_y = align(inbox_z + recs * D * 4)
+        out_gx = align(out_y + recs * D * 4)
+        total = align(out_gx + recs * 16)
+        self.buffer = symm.empty(total, dtype=torch.uint8, device=device)
+        self.handle = symm.rendezvous(self.buffer, group if group is not None else dist.group.WORLD)
+        self.layout = (self.handle.buffer_ptrs_dev, total, inbox_x, counts, inbox_z, out_y, out_gx, cap, world, rank)
+        self.max_batch = int(max_batch)
+        self.where = torch.empty(self.max_batch, dtype=torch.int32, device=device)
+        self.cursor = torch.zeros(world, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+
+
+class _RoutedGridQuery(torch.autograd.Function):
+    """Forward: route, owners interpolate, gather.  Backward: send dL/dy, owners scatter into their
+    gradient shards and return dL/dx, gather.  Every rank calls both collectively."""
+
+    @staticmethod
+    def forward(ctx, embeddings, x, grid, interpolation):
+        box, geom = grid._mailbox, grid._routed_geometry()
+        n = x.shape[0]
+        if n > box.max_batch:
+            raise ValueError(f"batch of {n} positions exceeds max_batch = {box.max_batch}")
+        where = box.where[:n]
+        backend.routed_route(grid.engine.backend, x, geom, box.layout, box.cursor, where, box.status)
+        grid._barrier()                       # every inbox is complete
+        backend.routed_forward(grid.engine.backend, grid._emb_bases, geom, box.layout, interpolation)
+        grid._barrier()                       # every result row has landed
+        y, masks = backend.routed_unpack_y(where, n, grid.embedding_dim, box.layout)
+        ctx.grid, ctx.geom, ctx.interpolation, ctx.n = grid, geom, interpolation, n
+        ctx.embeddings = embeddings
+        ctx.mark_non_differentiable(masks)
+        return y, masks
+
+    @staticmethod
+    def backward(ctx, z, _grad_masks):
+        grid, box = ctx.grid, ctx.grid._mailbox
+        where = box.where[:ctx.n]             # still this batch's: one batch is in flight at a time
+        need_grad_x = bool(ctx.needs_input_grad[1])
+        backend.routed_send_z(where, z.contiguous(), box.layout)
+        grid._barrier()                       # every owner has the incoming gradients of its records
+        backend.routed_backward(grid.engine.backend, grid._emb_bases, grid._grad_bases, ctx.geom, box.layout,
+                                ctx.interpolation, need_grad_x)
+        grid._barrier()                       # gradient rows and dL/dx have landed; the mailbox is free again
+        grad_x = backend.routed_unpack_grad_x(where, ctx.n, grid.embedding_dim, box.layout) if need_grad_x else None
+        return None, grad_x, None, None       # the embedding gradient went straight into the owners' shards
+
+
+class RoutedSparseDenseGrid(UnBoundedSparseDenseGrid):
+    """A sparse-dense grid whose table is SPLIT over the ranks of one box, queried by sending every
+    position to the rank that owns its block (``coarse_owner_of``): that rank interpolates in its own
+    memory and sends the result row back; in the backward pass it receives dL/dy, adds the gradient
+    rows into ITS gradient shard and returns dL/dx.  A query crosses NVLink as 16 + 4 D bytes each
+    way instead of the ~64 D bytes of its rows; there is no gradient all-reduce, and each rank holds
+    about 1 / world of the table.  A step::
+
+        grid.zero_grad_shard_()
+        y, masks = grid(x)            # every rank, its own positions (collective)
+        loss(y).backward()            # collective; afterwards embeddings.grad is complete
+        optimizer.step()              # on this rank's shard
+
+    The block structure (hash map, neighbour table, block -> (owner, row) table) is replicated: build
+    it the same way on every rank, then call ``sync_structure_()``.  One batch is in flight at a time
+    (forward, then its backward); first-order gradients only."""
+
+    def __init__(self, in_dim: int, num_embeddings: int, embedding_dim: int, grid_dim: int, cell_size: float = 1.0,
+                 device=None, group=None, max_batch: int = 1 << 20, region_slack: float = 1.5, shard_slack: float = 1.25):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        assert self.world <= 32, "at most 32 ranks"
+        self._rows_per_rank = min(num_embeddings, int(-(-num_embeddings // self.world) * shard_slack) + 64)
+        super().__init__(in_dim, num_embeddings, embedding_dim, grid_dim, cell_size=cell_size, device=device)
+        import torch.distributed._symmetric_memory as symm
+
+        pg = group if group is not None else dist.group.WORLD
+        self._emb_handle = symm.rendezvous(self._emb_shard, pg)
+        self._emb_bases = self._emb_handle.buffer_ptrs_dev
+        self._grad_shard = symm.empty(tuple(self.embeddings.shape), dtype=torch.float32, device=self.device)
+        self._grad_shard.zero_()
+        self._grad_handle = symm.rendezvous(self._grad_shard, pg)
+        self._grad_bases = self._grad_handle.buffer_ptrs_dev
+        self.embeddings.grad = self._grad_shard
+        cap = min(max_batch, int(-(-max_batch // self.world) * region_slack) + 1024)
+        self._mailbox = _RoutedMailbox(self.world, self.rank, cap, max_batch, embedding_dim, self.device, group)
+        self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._row_of = None
+        self.fused = True
+
+    def _allocate_embeddings(self) -> torch.Tensor:
+        import torch.distributed._symmetric_memory as symm
+
+        shard = symm.empty((self._rows_per_rank, self.num_cells_per_grid, self.embedding_dim), dtype=torch.float32,
+                           device=self.device)
+        self._emb_shard = shard.zero_()
+        return self._emb_shard
+
+    def _barrier(self) -> None:
+        """Stream-ordered: behind this rank's kernels, complete when every rank got here."""
+        dist.all_reduce(self._token, group=self.group)
+
+    def _routed_geometry(self):
+        origin, cell_size = self._cell_frame()
+        return cell_size, origin, self.grid_dim, self._neighbor_lut32(), self._row_of, self.num_embeddings, self.embedding_dim
+
+    @torch.no_grad()
+    def sync_structure_(self, src: int = 0) -> None:
+        """Give every rank rank ``src``'s key -> index map and derive, identically everywhere, which
+        rank owns which block and at which row of its shard the block lives."""
+        broadcast_state(self.engine, src=src, group=self.group)
+        self.construct_grid_neighbor_lut_(radius=1, bidirectional=False)
+        coords, idx = self.engine.items()
+        owner = coarse_owner_of(coords, self.world)
+        order = torch.argsort(idx)                                  # by block index: the same order on every rank
+        coords, idx, owner = coords[order], idx[order], owner[order]
+        one_hot = torch.nn.functional.one_hot(owner, self.world)
+        local = (torch.cumsum(one_hot, dim=0) - one_hot).gather(1, owner.view(-1, 1)).view(-1)   # rank among its owner's blocks
+        per_owner = one_hot.sum(dim=0)
+        if int(per_owner.max()) > self._rows_per_rank:
+            raise RuntimeError(f"an owner holds {int(per_owner.max())} blocks but a shard has {self._rows_per_rank} rows; "
+                               "raise shard_slack")
+        row_of = torch.zeros(self.num_embeddings, dtype=torch.int64, device=self.device)
+        row_of[idx] = (owner << 26) | local
+        self._row_of = row_of.to(torch.int32)          # bit pattern of the uint32 the kernels read (owner < 32)
+        self._owned_blocks = idx[owner == self.rank]   # global block indices of this shard's rows, in row order
+
+    def owned_blocks(self) -> torch.Tensor:
+        """Global block indices of this rank's shard rows 0 .. n_owned - 1."""
+        return self._owned_blocks
+
+    def forward(self, x: torch.Tensor, interpolation: str = "smooth_step"):
+        if interpolation not in ("linear", "smooth_step"):
+            raise ValueError(f"Unknown interpolation: {interpolation}")
+        if self._row_of is None:
+            raise RuntimeError("call sync_structure_() after building the block structure")
+        self._barrier()   # every rank's parameters and zeroed gradient shards are final, the mailboxes free
+        return _RoutedGridQuery.apply(self.embeddings, x.to(torch.float32).contiguous(), self, interpolation)
+
+    def check_status(self) -> None:
+        """Raise if a routed batch overflowed a mailbox region (host synchronisation)."""
+        if int(self._mailbox.status.item()):
+            self._mailbox.status.zero_()
+            raise RuntimeError("a rank sent one owner more positions than a mailbox region holds; raise region_slack")
 
     @torch.no_grad()
     def zero_grad_shard_(self) -> None:

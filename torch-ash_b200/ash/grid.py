@@ -62,6 +62,11 @@ class SparseDenseGrid(ASHModule):
         # fused backward passes add straight into embeddings.grad (created as zeros when missing),
         # which saves a table-sized allocation + zero-fill (+ add) per call; clear the gradient with
         # embeddings.grad.zero_() or zero_grad(set_to_none=False) between steps as usual.
+        # "row_list": the fused backward passes return an uncoalesced SPARSE gradient (8 records per
+        # query: block index, cell index, row) written with coalesced stores -- no table-sized buffer,
+        # zero-fill or read-modify-write; embeddings.grad is then a sparse tensor, to be consumed by an
+        # optimiser that accepts sparse gradients (torch.optim.SGD / SparseAdam) or by
+        # apply_row_list_(), as with nn.Embedding(sparse=True).
         self.grad_mode = "dense"
         self._lut32 = None
         self._lut32_source = None
@@ -175,6 +180,10 @@ class SparseDenseGrid(ASHModule):
                 if self.embeddings.grad is None:
                     self.embeddings.grad = torch.zeros_like(self.embeddings)
                 grad_buffer = self.embeddings.grad
+            elif self.grad_mode == "row_list":
+                if not hasattr(backend, "grid_query_backward_rows"):
+                    raise ValueError("grad_mode 'row_list' needs the native row-list backward")
+                grad_buffer = "row_list"
             elif self.grad_mode not in ("dense", "in_place"):
                 raise ValueError(f"Unknown grad_mode: {self.grad_mode}")
             geom = (self.engine.backend, self._neighbor_lut32(), cell_size, origin, self.grid_dim, interpolation,
@@ -203,6 +212,19 @@ class SparseDenseGrid(ASHModule):
         origin, cell_size = self._cell_frame()
         backend.grid_zero_rows(self.engine.backend, self.embeddings.grad, x.detach().to(torch.float32), cell_size,
                                origin, self.grid_dim, self._neighbor_lut32())
+
+    @torch.no_grad()
+    def apply_row_list_(self, target: torch.Tensor = None, alpha: float = 1.0) -> None:
+        """Add ``alpha`` times the sparse gradient that ``grad_mode = "row_list"`` left in
+        ``embeddings.grad`` to ``target`` (default: the embeddings themselves, i.e. a plain
+        gradient-descent step with ``alpha = -learning_rate``), one pass over the list."""
+        g = self.embeddings.grad
+        if g is None:
+            return
+        if not g.is_sparse:
+            raise ValueError("embeddings.grad is dense: apply_row_list_ is for grad_mode = 'row_list'")
+        target = self.embeddings.data if target is None else target
+        backend.rows_scatter_add(target, g._indices(), g._values(), alpha)
 
     def _cell_frame(self):
         """(origin, cell_size) such that cell position = (world - origin) / cell_size."""

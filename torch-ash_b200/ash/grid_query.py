@@ -99,7 +99,10 @@ class FusedGridQuery(torch.autograd.Function):
     incoming gradient.  ``geom`` = (hashmap, nb_lut int32, cell_size, origin, grid_dim, interpolation,
     grad_buffer).  With a ``grad_buffer`` (a tensor shaped like ``embeddings``) both backward passes ADD
     their embedding gradient into it and report no gradient for ``embeddings`` to autograd: the
-    table-sized allocation and zero-fill per backward call disappear.
+    table-sized allocation and zero-fill per backward call disappear.  With ``grad_buffer ==
+    "row_list"`` both passes hand autograd an UNCOALESCED SPARSE gradient instead (8 records per
+    query: block index, cell index, row), written with coalesced stores and no read-modify-write;
+    ``embeddings.grad`` is then a sparse tensor, as for ``nn.Embedding(sparse=True)``.
     """
 
     @staticmethod
@@ -134,11 +137,18 @@ class FusedGridQueryBackward(torch.autograd.Function):
         ctx.save_for_backward(z, embeddings, x, block_idx)
         ctx.geom = geom
         ctx.set_materialize_grads(False)
-        grad_embeddings, grad_x = backend.grid_query_backward(
-            hashmap, z, embeddings, x, cell_size, origin, grid_dim, nb_lut, block_idx, interpolation,
-            grad_embeddings_out=grad_buffer, need_grad_x=need_grad_x, need_grad_embeddings=need_grad_emb)
-        if grad_buffer is not None:
-            grad_embeddings = None  # already added into the buffer
+        if isinstance(grad_buffer, str) and need_grad_emb:  # "row_list"
+            idx, rows, grad_x = backend.grid_query_backward_rows(
+                hashmap, z, embeddings, x, cell_size, origin, grid_dim, nb_lut, block_idx, interpolation,
+                need_grad_x=need_grad_x)
+            grad_embeddings = torch.sparse_coo_tensor(idx, rows, embeddings.shape, is_coalesced=False, check_invariants=False)
+        else:
+            dense_out = None if isinstance(grad_buffer, str) else grad_buffer
+            grad_embeddings, grad_x = backend.grid_query_backward(
+                hashmap, z, embeddings, x, cell_size, origin, grid_dim, nb_lut, block_idx, interpolation,
+                grad_embeddings_out=dense_out, need_grad_x=need_grad_x, need_grad_embeddings=need_grad_emb)
+            if dense_out is not None:
+                grad_embeddings = None  # already added into the buffer
         if grad_x is None:
             if grad_embeddings is None:
                 return None, None
@@ -152,6 +162,12 @@ class FusedGridQueryBackward(torch.autograd.Function):
             return (None,) * 7
         z, embeddings, x, block_idx = ctx.saved_tensors
         hashmap, nb_lut, cell_size, origin, grid_dim, interpolation, grad_buffer = ctx.geom
+        if isinstance(grad_buffer, str):  # "row_list"
+            idx, rows, grad_z = backend.grid_query_backward_rows(
+                hashmap, z, embeddings, x, cell_size, origin, grid_dim, nb_lut, block_idx, interpolation,
+                grad_grad_x=grad_grad_x.to(embeddings.dtype).contiguous())
+            grad_embeddings = torch.sparse_coo_tensor(idx, rows, embeddings.shape, is_coalesced=False, check_invariants=False)
+            return grad_z, grad_embeddings, None, None, None, None, None
         grad_z, grad_embeddings = backend.grid_query_backward_backward(
             hashmap, grad_grad_x.to(embeddings.dtype).contiguous(), z, embeddings, x, cell_size, origin, grid_dim,
             nb_lut, block_idx, interpolation, grad_embeddings_out=grad_buffer)

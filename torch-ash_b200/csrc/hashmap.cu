@@ -28,7 +28,10 @@
 namespace ashb {
 
 // ---- find ----------------------------------------------------------------------
-template <class Table, int DIM>
+// FILTER (16-byte slots only): the one-bit-per-slot occupancy map is consulted first.  A key whose
+// home slot never held anything is absent, and the map (1/128 of the table) sits in L2 when the
+// table itself is far beyond it, so such a miss costs no DRAM access at all.
+template <class Table, int DIM, bool FILTER = false>
 __global__ void __launch_bounds__(256) find_kernel(Table t, const int32_t* __restrict__ keys, int64_t n,
                                                    int64_t* __restrict__ indices,
                                                    uint8_t* __restrict__ masks) {
@@ -38,14 +41,18 @@ __global__ void __launch_bounds__(256) find_kernel(Table t, const int32_t* __res
     load_key<DIM>(keys, i, k0, k1, k2, k3);
     uint32_t s = hash_key(k0, k1, k2, k3) & t.mask;
     int found = -1;
-    for (uint32_t probe = 0; probe <= t.mask; ++probe) {
-        const Entry e = t.read_const(s);
-        if (e.val == kEmpty) break;
-        if (e.val >= 0 && key_match(e, k0, k1, k2, k3)) {
-            found = e.val;
-            break;
+    bool absent = false;
+    if constexpr (FILTER) absent = t.never_used(s);
+    if (!absent) {
+        for (uint32_t probe = 0; probe <= t.mask; ++probe) {
+            const Entry e = t.read_const(s);
+            if (e.val == kEmpty) break;
+            if (e.val >= 0 && key_match(e, k0, k1, k2, k3)) {
+                found = e.val;
+                break;
+            }
+            s = (s + 1) & t.mask;
         }
-        s = (s + 1) & t.mask;
     }
     indices[i] = found >= 0 ? (int64_t)found : 0;
     masks[i] = (uint8_t)(found >= 0);
@@ -278,8 +285,7 @@ int dispatch(ashb_map* m, F16&& f16, F32&& f32) {
         Table32 t{static_cast<Slot32*>(m->slots), (uint32_t)(m->n_slots - 1), m->status};
         return f32(t);
     }
-    Table16 t{static_cast<uint4*>(m->slots), (uint32_t)(m->n_slots - 1), m->status};
-    return f16(t);
+    return f16(table16_of(m));
 }
 
 inline unsigned blocks_for(int64_t n, int threads) { return (unsigned)((n + threads - 1) / threads); }
@@ -315,8 +321,14 @@ int check_map(ashb_map* m) {
 
 }  // namespace
 
-// Which find kernel ashb_map_find launches for 16-byte slots (process-wide switch).
+// Which find kernel ashb_map_find launches for 16-byte slots (process-wide switches).
 static bool g_find_cooperative = false;
+// Occupancy filter in find: -1 = automatic (tables of kFilterMinBytes and more, i.e. those that do
+// not stay in L2 anyway), 0 = never, 1 = always.
+static int g_find_filter = -1;
+constexpr size_t kFilterMinBytes = (size_t)64 << 20;
+
+static size_t occupied_bytes(uint64_t n_slots) { return (size_t)(n_slots / 8 < 4 ? 4 : n_slots / 8); }
 
 extern "C" {
 
@@ -344,9 +356,11 @@ int ashb_map_create(int key_dim, int64_t capacity, int32_t* heap_dev, int device
     m->slot_bytes = key_dim == 4 ? sizeof(Slot32) : sizeof(uint4);
     cudaError_t e = cudaMalloc(&m->slots, n * m->slot_bytes);
     if (e == cudaSuccess) e = cudaMalloc(&m->small, 256);
+    if (e == cudaSuccess && key_dim <= 3) e = cudaMalloc(reinterpret_cast<void**>(&m->occupied), occupied_bytes(n));
     if (e != cudaSuccess) {
         set_error("cudaMalloc of %llu-slot table failed: %s", (unsigned long long)n, cudaGetErrorString(e));
         if (m->slots) cudaFree(m->slots);
+        if (m->small) cudaFree(m->small);
         delete m;
         return ASHB_ERR_CUDA;
     }
@@ -358,11 +372,13 @@ int ashb_map_create(int key_dim, int64_t capacity, int32_t* heap_dev, int device
     // the synchronising memset on the legacy stream.
     e = cudaMemset(m->slots, 0xFF, n * m->slot_bytes);
     if (e == cudaSuccess) e = cudaMemset(m->small, 0, 256);
+    if (e == cudaSuccess && m->occupied) e = cudaMemset(m->occupied, 0, occupied_bytes(n));
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     if (e != cudaSuccess) {
         set_error("table initialisation failed: %s", cudaGetErrorString(e));
         cudaFree(m->slots);
         cudaFree(m->small);
+        if (m->occupied) cudaFree(m->occupied);
         delete m;
         return ASHB_ERR_CUDA;
     }
@@ -375,6 +391,7 @@ int ashb_map_destroy(ashb_map* m) {
     DeviceGuard guard(m->device);
     if (m->slots) cudaFree(m->slots);
     if (m->small) cudaFree(m->small);
+    if (m->occupied) cudaFree(m->occupied);
     m->slots = nullptr;
     delete m;
     return ASHB_OK;
@@ -384,6 +401,7 @@ int ashb_map_clear(ashb_map* m, void* stream) {
     ASHB_MAP_PROLOGUE(m);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     ASHB_CUDA_TRY(cudaMemsetAsync(m->slots, 0xFF, m->n_slots * m->slot_bytes, st));
+    if (m->occupied) ASHB_CUDA_TRY(cudaMemsetAsync(m->occupied, 0, occupied_bytes(m->n_slots), st));
     ASHB_CUDA_TRY(cudaMemsetAsync(m->counter, 0, sizeof(int32_t), st));
     reset_heap_kernel<<<wave_grid(m->capacity, 256, 8), 256, 0, st>>>(m->heap, m->capacity);
     ASHB_LAUNCH_CHECK();
@@ -413,6 +431,15 @@ int ashb_map_status(ashb_map* m, void* stream, uint32_t* status_out) {
     return ASHB_OK;
 }
 
+int ashb_map_status_async(ashb_map* m, uint32_t* status_out_host, void* stream) {
+    ASHB_MAP_PROLOGUE(m);
+    ASHB_REQUIRE(status_out_host != nullptr, "status_out_host is null");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    ASHB_CUDA_TRY(cudaMemcpyAsync(status_out_host, m->status, sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
+    ASHB_CUDA_TRY(cudaMemsetAsync(m->status, 0, sizeof(uint32_t), st));
+    return ASHB_OK;
+}
+
 int ashb_map_find(ashb_map* m, const int32_t* keys, int64_t n, int64_t* indices, uint8_t* masks,
                   void* stream) {
     ASHB_MAP_PROLOGUE(m);
@@ -428,6 +455,15 @@ int ashb_map_find(ashb_map* m, const int32_t* keys, int64_t n, int64_t* indices,
             case 2: find_coop_kernel<2><<<grid, 256, 0, st>>>(t, keys, n, indices, masks); break;
             default: find_coop_kernel<3><<<grid, 256, 0, st>>>(t, keys, n, indices, masks); break;
         }
+    } else if (m->occupied != nullptr &&
+               (g_find_filter > 0 || (g_find_filter < 0 && m->n_slots * m->slot_bytes >= kFilterMinBytes))) {
+        const Table16 t = table16_of(m);
+        const unsigned grid = blocks_for(n, 256);
+        switch (m->key_dim) {
+            case 1: find_kernel<Table16, 1, true><<<grid, 256, 0, st>>>(t, keys, n, indices, masks); break;
+            case 2: find_kernel<Table16, 2, true><<<grid, 256, 0, st>>>(t, keys, n, indices, masks); break;
+            default: find_kernel<Table16, 3, true><<<grid, 256, 0, st>>>(t, keys, n, indices, masks); break;
+        }
     } else {
         ASHB_DIM_LAUNCH(find_kernel, m, blocks_for(n, 256), 256, st, keys, n, indices, masks);
     }
@@ -437,6 +473,12 @@ int ashb_map_find(ashb_map* m, const int32_t* keys, int64_t n, int64_t* indices,
 
 int ashb_set_find_cooperative(int enable) {
     g_find_cooperative = enable != 0;
+    return ASHB_OK;
+}
+
+int ashb_set_find_filter(int mode) {
+    ASHB_REQUIRE(mode >= -1 && mode <= 1, "mode must be -1 (automatic), 0 (off) or 1 (on)");
+    g_find_filter = mode;
     return ASHB_OK;
 }
 
@@ -514,6 +556,7 @@ int ashb_map_load_states(ashb_map* m, const int32_t* keys, const int64_t* indice
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // Start from an empty table: loading on top of live entries would mix two states.
     ASHB_CUDA_TRY(cudaMemsetAsync(m->slots, 0xFF, m->n_slots * m->slot_bytes, st));
+    if (m->occupied) ASHB_CUDA_TRY(cudaMemsetAsync(m->occupied, 0, occupied_bytes(m->n_slots), st));
     set_counter_kernel<<<1, 1, 0, st>>>(m->counter, (int32_t)n);
     ASHB_LAUNCH_CHECK();
     if (heap_src != nullptr && heap_src != m->heap)
@@ -530,8 +573,12 @@ int ashb_map_rehash(ashb_map* m, void* stream) {
     ASHB_MAP_PROLOGUE(m);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     void* fresh = nullptr;
+    uint32_t* fresh_occ = nullptr;
     ASHB_CUDA_TRY(cudaMalloc(&fresh, m->n_slots * m->slot_bytes));
-    cudaError_t e = cudaMemsetAsync(fresh, 0xFF, m->n_slots * m->slot_bytes, st);
+    cudaError_t e = cudaSuccess;
+    if (m->occupied) e = cudaMalloc(reinterpret_cast<void**>(&fresh_occ), occupied_bytes(m->n_slots));
+    if (e == cudaSuccess) e = cudaMemsetAsync(fresh, 0xFF, m->n_slots * m->slot_bytes, st);
+    if (e == cudaSuccess && fresh_occ) e = cudaMemsetAsync(fresh_occ, 0, occupied_bytes(m->n_slots), st);
     if (e == cudaSuccess) {
         const unsigned grid = wave_grid((int64_t)m->n_slots, 256, 8);
         const uint32_t mask = (uint32_t)(m->n_slots - 1);
@@ -539,8 +586,8 @@ int ashb_map_rehash(ashb_map* m, void* stream) {
             rehash_kernel<Table32, 4><<<grid, 256, 0, st>>>(Table32{static_cast<Slot32*>(fresh), mask, m->status},
                                                             Table32{static_cast<Slot32*>(m->slots), mask, m->status});
         } else {
-            rehash_kernel<Table16, 3><<<grid, 256, 0, st>>>(Table16{static_cast<uint4*>(fresh), mask, m->status},
-                                                            Table16{static_cast<uint4*>(m->slots), mask, m->status});
+            rehash_kernel<Table16, 3><<<grid, 256, 0, st>>>(
+                    Table16{static_cast<uint4*>(fresh), mask, m->status, fresh_occ}, table16_of(m));
         }
         e = cudaGetLastError();
     }
@@ -549,10 +596,13 @@ int ashb_map_rehash(ashb_map* m, void* stream) {
     if (e != cudaSuccess) {
         set_error("rehash failed: %s", cudaGetErrorString(e));
         cudaFree(fresh);
+        if (fresh_occ) cudaFree(fresh_occ);
         return ASHB_ERR_CUDA;
     }
     cudaFree(m->slots);
+    if (m->occupied) cudaFree(m->occupied);
     m->slots = fresh;
+    m->occupied = fresh_occ;
     return ASHB_OK;
 }
 

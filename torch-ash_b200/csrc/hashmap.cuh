@@ -45,6 +45,11 @@ struct Table16 {
     uint4* slots;
     uint32_t mask;
     uint32_t* status;
+    // One bit per slot, set when a key is first stored there and cleared only with the whole table
+    // (erased slots keep it: probe chains run through them).  At 1/128 of the table's size it stays
+    // in L2 where the table does not, so a find whose home slot never held a key is answered without
+    // a DRAM access.  Null for tables built without one.
+    uint32_t* occupied;
 
     __device__ __forceinline__ Entry unpack(uint4 r) const {
         return Entry{(int)r.x, (int)r.y, (int)r.z, 0, (int)r.w};
@@ -80,7 +85,13 @@ struct Table16 {
         val.v = make_uint4((unsigned)k0, (unsigned)k1, (unsigned)k2, (unsigned)new_val);
         old.q = atomicCAS(reinterpret_cast<unsigned __int128*>(slots + s), cmp.q, val.q);
         observed = unpack(old.v);
-        return old.q == cmp.q;
+        if (old.q != cmp.q) return false;
+        // an erased slot was marked when its first key arrived
+        if (occupied != nullptr && expected.val == kEmpty) atomicOr(occupied + (s >> 5), 1u << (s & 31));
+        return true;
+    }
+    __device__ __forceinline__ bool never_used(uint32_t s) const {
+        return ((__ldg(occupied + (s >> 5)) >> (s & 31)) & 1u) == 0;
     }
     __device__ __forceinline__ int* val_ptr(uint32_t s) const {
         return reinterpret_cast<int*>(slots + s) + 3;
@@ -333,6 +344,7 @@ struct ashb_map {
     uint64_t n_slots;
     void* slots;
     size_t slot_bytes;
+    uint32_t* occupied;          // device: one bit per 16-byte slot (null for key_dim 4)
     int32_t* heap;               // borrowed: the caller's free-index stack
     int32_t* counter;            // device: live keys == popped indices
     uint32_t* status;            // device: ASHB_STATUS_* bits
@@ -343,7 +355,7 @@ struct ashb_map {
 namespace ashb {
 
 inline Table16 table16_of(const ashb_map* m) {
-    return Table16{static_cast<uint4*>(m->slots), (uint32_t)(m->n_slots - 1), m->status};
+    return Table16{static_cast<uint4*>(m->slots), (uint32_t)(m->n_slots - 1), m->status, m->occupied};
 }
 
 // Selects the map's device for the scope of a call.

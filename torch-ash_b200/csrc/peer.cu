@@ -21,7 +21,7 @@
 
 namespace ashb {
 
-constexpr int kPeerMaxWorld = 64;
+constexpr int kPeerMaxWorld = 32;   // where[i] = owner << 26 | slot must stay a non-negative int32
 
 // Same owner function as route.cu / ash.distributed.owner_of (int64 wrap-around arithmetic).
 __device__ __forceinline__ int peer_owner_of(int k0, int k1, int k2, int dim, int world) {

@@ -22,90 +22,6 @@
 
 namespace ashb {
 
-template <typename T, int VEC>
-struct Vec;
-template <>
-struct Vec<float, 1> { using type = float; };
-template <>
-struct Vec<float, 2> { using type = float2; };
-template <>
-struct Vec<float, 4> { using type = float4; };
-template <>
-struct Vec<double, 1> { using type = double; };
-template <>
-struct Vec<double, 2> { using type = double2; };
-
-template <typename T, int VEC>
-struct Pack {
-    T v[VEC];
-};
-
-template <typename T, int VEC>
-__device__ __forceinline__ Pack<T, VEC> load_pack(const T* p) {
-    using V = typename Vec<T, VEC>::type;
-    Pack<T, VEC> r;
-    *reinterpret_cast<V*>(r.v) = __ldg(reinterpret_cast<const V*>(p));
-    return r;
-}
-
-// Rows of 4 floats per lane are gathered from random lines: naming a 64-byte L2 fetch size keeps
-// the DRAM fill to the half line that holds the 64-byte row (measured: backward 1.54 -> 1.44 ms,
-// forward 0.606 -> 0.591 ms at 4M queries).
-template <>
-__device__ __forceinline__ Pack<float, 1> load_pack<float, 1>(const float* p) {
-    Pack<float, 1> r;
-    asm volatile("ld.global.nc.L2::64B.f32 %0, [%1];" : "=f"(r.v[0]) : "l"(p));
-    return r;
-}
-template <>
-__device__ __forceinline__ Pack<float, 2> load_pack<float, 2>(const float* p) {
-    Pack<float, 2> r;
-    asm volatile("ld.global.nc.L2::64B.v2.f32 {%0,%1}, [%2];" : "=f"(r.v[0]), "=f"(r.v[1]) : "l"(p));
-    return r;
-}
-template <>
-__device__ __forceinline__ Pack<double, 1> load_pack<double, 1>(const double* p) {
-    Pack<double, 1> r;
-    asm volatile("ld.global.nc.L2::64B.f64 %0, [%1];" : "=d"(r.v[0]) : "l"(p));
-    return r;
-}
-template <>
-__device__ __forceinline__ Pack<double, 2> load_pack<double, 2>(const double* p) {
-    Pack<double, 2> r;
-    asm volatile("ld.global.nc.L2::64B.v2.f64 {%0,%1}, [%2];" : "=d"(r.v[0]), "=d"(r.v[1]) : "l"(p));
-    return r;
-}
-template <>
-__device__ __forceinline__ Pack<float, 4> load_pack<float, 4>(const float* p) {
-    Pack<float, 4> r;
-    asm volatile("ld.global.nc.L2::64B.v4.f32 {%0,%1,%2,%3}, [%4];"
-                 : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3])
-                 : "l"(p));
-    return r;
-}
-
-template <typename T, int VEC>
-__device__ __forceinline__ void store_pack(T* p, const Pack<T, VEC>& r) {
-    using V = typename Vec<T, VEC>::type;
-    *reinterpret_cast<V*>(p) = *reinterpret_cast<const V*>(r.v);
-}
-
-// Gradient scatter: one vector reduction per lane where the hardware has one
-// (fp32 x2 / x4 on sm_90+), scalar atomics otherwise.
-template <typename T, int VEC>
-__device__ __forceinline__ void atomic_add_pack(T* p, const Pack<T, VEC>& r) {
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) atomicAdd(p + k, r.v[k]);
-}
-template <>
-__device__ __forceinline__ void atomic_add_pack<float, 4>(float* p, const Pack<float, 4>& r) {
-    atomicAdd(reinterpret_cast<float4*>(p), make_float4(r.v[0], r.v[1], r.v[2], r.v[3]));
-}
-template <>
-__device__ __forceinline__ void atomic_add_pack<float, 2>(float* p, const Pack<float, 2>& r) {
-    atomicAdd(reinterpret_cast<float2*>(p), make_float2(r.v[0], r.v[1]));
-}
-
 struct QueryLuts {
     const int64_t* __restrict__ grid_indices;
     const int64_t* __restrict__ cell_indices;
@@ -283,12 +199,6 @@ struct ShardedSource : FusedSource {
         return ok;
     }
 };
-
-template <typename T>
-__device__ __forceinline__ T group_sum(T v, int lanes) {
-    for (int o = lanes >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
 
 // ---- forward -------------------------------------------------------------------
 template <typename T, int VEC, class Src>
@@ -529,6 +439,128 @@ __global__ void __launch_bounds__(256, ASHB_BWD_MIN_BLOCKS) query_backward_backw
         }
     }
     store_pack<T, VEC>(grad_z + q * D + ch, gz);
+}
+
+// ---- backward passes that WRITE the embedding gradient as a row list ---------------------------
+// Instead of adding eight rows per query into a table-sized buffer (a read-modify-write of eight
+// random lines, on top of a table-sized zero-fill when the buffer is fresh), the gradient leaves as
+// 8 n records in corner-major order: record c * n + q = (block index, cell index, row of D values).
+// Every store is coalesced and nothing is read back, so the pass moves its algorithmic bytes and
+// no more.  The list is an uncoalesced sparse tensor of the table's shape (duplicates mean
+// "add"); ashb_rows_scatter_add applies it to any dense buffer (a gradient, or the parameters
+// themselves with a step size).  Queries that produce no gradient (miss, absent neighbour block)
+// write zero rows that point at valid cells spread over the table, so the list is well-formed as it is.
+// SECOND = false: first-order pass (rows = w_c * z, d/d offset as in query_backward_forward_kernel);
+// SECOND = true: double backward (rows = (grad w_c . ggo) * z, grad_z as in
+// query_backward_backward_kernel; `side` is grad_z [n][D], `ggo` the incoming gradient).
+#ifndef ASHB_ROWS_MIN_BLOCKS
+#define ASHB_ROWS_MIN_BLOCKS 3
+#endif
+template <typename T, int VEC, bool SECOND, bool NEED_GO>
+__global__ void __launch_bounds__(256, ASHB_ROWS_MIN_BLOCKS) query_backward_rows_kernel(
+        const T* __restrict__ z, const T* __restrict__ emb, FusedSource src, const T* __restrict__ ggo,
+        int64_t* __restrict__ idx_out, T* __restrict__ rows_out, T* __restrict__ side, T go_scale, int64_t n, int D,
+        int lane_shift, int interp) {
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t q = tid >> lane_shift;
+    const int lanes = 1 << lane_shift;
+    const int lane = (int)(tid & (lanes - 1));
+    const int ch = lane * VEC;
+    const bool live = q < n;
+    const bool has_ch = ch < D;
+    T go[3] = {0, 0, 0};
+    Pack<T, VEC> gz;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) gz.v[k] = 0;
+    if (live) {
+        int cell[3], blocks[8], cells[8];
+        float off[3];
+        const int gi = src.locate(q, lane, cell, off);
+        const bool ok = gi >= 0 && gi < src.n_emb && corner_blocks_cells(src.nb_lut, gi, cell, src.G, src.n_emb, blocks, cells);
+        if (has_ch && !ok) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) store_pack<T, VEC>(rows_out + ((int64_t)c * n + q) * D + ch, gz);
+            if (SECOND) store_pack<T, VEC>(side + q * D + ch, gz);
+        } else if (has_ch) {
+            AxisWeights<T> aw;
+            aw.init(interp, off);
+            const Pack<T, VEC> zv = load_pack<T, VEC>(z + q * D + ch);
+            Pack<T, VEC> e[8];
+            if (SECOND || NEED_GO) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    e[c] = load_pack<T, VEC>(emb + ((int64_t)blocks[c] * src.cells_per_grid + cells[c]) * D + ch);
+            }
+            T g3[3] = {0, 0, 0};
+            if (SECOND) {
+                g3[0] = ggo[3 * q] * go_scale;
+                g3[1] = ggo[3 * q + 1] * go_scale;
+                g3[2] = ggo[3 * q + 2] * go_scale;
+            }
+            T* out = rows_out + q * D + ch;
+            const int64_t corner_stride = n * D;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                T wg[3] = {0, 0, 0};
+                if (SECOND || NEED_GO) aw.grad(c, wg);
+                const T w = SECOND ? wg[0] * g3[0] + wg[1] * g3[1] + wg[2] * g3[2] : aw.weight(c);
+                Pack<T, VEC> g;
+                T dot = 0;
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) {
+                    g.v[k] = w * zv.v[k];
+                    if (SECOND) gz.v[k] += w * e[c].v[k];
+                    if (!SECOND && NEED_GO) dot += e[c].v[k] * zv.v[k];
+                }
+                store_pack<T, VEC>(out, g);
+                out += corner_stride;
+                if (!SECOND && NEED_GO) {
+                    go[0] += dot * wg[0];
+                    go[1] += dot * wg[1];
+                    go[2] += dot * wg[2];
+                }
+            }
+            if (SECOND) store_pack<T, VEC>(side + q * D + ch, gz);
+        }
+        // the 8 index pairs of the query are shared out over its lanes
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            if ((c & (lanes - 1)) != lane) continue;
+            idx_out[(int64_t)c * n + q] = ok ? blocks[c] : (int64_t)(q % src.n_emb);
+            idx_out[(int64_t)(8 + c) * n + q] = ok ? cells[c] : (int64_t)(c % src.cells_per_grid);
+        }
+    }
+    if (SECOND || !NEED_GO) return;
+#pragma unroll
+    for (int d = 0; d < 3; ++d) go[d] = group_sum(go[d], lanes);
+    if (live && lane == 0) {
+        side[3 * q] = go[0] * go_scale;
+        side[3 * q + 1] = go[1] * go_scale;
+        side[3 * q + 2] = go[2] * go_scale;
+    }
+}
+
+// dst[idx[0][r]][idx[1][r]][:] += alpha * rows[r][:] for the m records of a row list.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) rows_scatter_add_kernel(T* __restrict__ dst, const int64_t* __restrict__ idx,
+                                                               const T* __restrict__ rows, int64_t m, int64_t n_emb,
+                                                               int64_t cells, int D, int lane_shift, T alpha) {
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t r = tid >> lane_shift;
+    const int ch = (int)(tid & ((1 << lane_shift) - 1)) * VEC;
+    if (r >= m || ch >= D) return;
+    const int64_t g = idx[r], c = idx[m + r];
+    if (g < 0 || g >= n_emb || c < 0 || c >= cells) return;
+    using V = typename Vec<T, VEC>::type;
+    Pack<T, VEC> v;
+    *reinterpret_cast<V*>(v.v) = *reinterpret_cast<const V*>(rows + r * D + ch);
+    bool any = false;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+        any = any || v.v[k] != 0;
+        v.v[k] *= alpha;
+    }
+    if (any) atomic_add_pack<T, VEC>(dst + (g * cells + c) * D + ch, v);
 }
 
 // ---- host-side dispatch ---------------------------------------------------------------
@@ -964,6 +996,49 @@ int ashb_grid_query_backward_backward(ashb_map* m, int dtype, int interp, const 
 }  // extern "C"
 
 template <typename T>
+static int backward_rows_impl(int interp, bool second, const void* ggo, const void* z, const void* emb,
+                              const FusedSource& src, int64_t* idx_out, void* rows_out, void* side, double go_scale,
+                              int64_t n, int64_t D, cudaStream_t st) {
+    const void* ptrs[] = {emb, z, rows_out, second ? side : nullptr};
+    const Shape sh = pick_shape(D, sizeof(T), ptrs, 4);
+    const int64_t threads = n << sh.lane_shift;
+    const unsigned grid = (unsigned)((threads + 255) / 256);
+    ASHB_VEC_SWITCH(T, sh,
+                    if (second) {
+                        query_backward_rows_kernel<T, VEC, true, false><<<grid, 256, 0, st>>>(
+                                static_cast<const T*>(z), static_cast<const T*>(emb), src, static_cast<const T*>(ggo),
+                                idx_out, static_cast<T*>(rows_out), static_cast<T*>(side), (T)go_scale, n, (int)D,
+                                sh.lane_shift, interp);
+                    } else if (side != nullptr) {
+                        query_backward_rows_kernel<T, VEC, false, true><<<grid, 256, 0, st>>>(
+                                static_cast<const T*>(z), static_cast<const T*>(emb), src, nullptr, idx_out,
+                                static_cast<T*>(rows_out), static_cast<T*>(side), (T)go_scale, n, (int)D, sh.lane_shift,
+                                interp);
+                    } else {
+                        query_backward_rows_kernel<T, VEC, false, false><<<grid, 256, 0, st>>>(
+                                static_cast<const T*>(z), static_cast<const T*>(emb), src, nullptr, idx_out,
+                                static_cast<T*>(rows_out), nullptr, (T)go_scale, n, (int)D, sh.lane_shift, interp);
+                    });
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+template <typename T>
+static int rows_scatter_add_impl(void* dst, const int64_t* idx, const void* rows, int64_t m, int64_t n_emb,
+                                 int64_t cells, int64_t D, double alpha, cudaStream_t st) {
+    const void* ptrs[] = {dst, rows};
+    const Shape sh = pick_shape(D, sizeof(T), ptrs, 2);
+    const int64_t threads = m << sh.lane_shift;
+    const unsigned grid = (unsigned)((threads + 255) / 256);
+    ASHB_VEC_SWITCH(T, sh,
+                    (rows_scatter_add_kernel<T, VEC><<<grid, 256, 0, st>>>(static_cast<T*>(dst), idx,
+                                                                            static_cast<const T*>(rows), m, n_emb, cells,
+                                                                            (int)D, sh.lane_shift, (T)alpha)));
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+template <typename T>
 static int zero_rows_impl(const FusedSource& src, void* grad_emb, int64_t n, int64_t D, cudaStream_t st) {
     const void* ptrs[] = {grad_emb};
     const Shape sh = pick_shape(D, sizeof(T), ptrs, 1);
@@ -991,6 +1066,39 @@ int ashb_grid_zero_rows(ashb_map* m, int dtype, void* grad_embeddings, const flo
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return dtype == ASHB_F32 ? zero_rows_impl<float>(src, grad_embeddings, n, D, st)
                              : zero_rows_impl<double>(src, grad_embeddings, n, D, st);
+}
+
+int ashb_grid_query_backward_rows(ashb_map* m, int dtype, int interp, int second_order, const void* grad_grad_x,
+                                  const void* z, const void* embeddings, const float* x, double cell_size,
+                                  const float* origin, int G, const int32_t* nb_lut, const int32_t* block_idx,
+                                  int64_t* idx_out, void* rows_out, void* side_out, int64_t n, int64_t n_emb, int64_t D,
+                                  void* stream) {
+    if (int rc = check_query_args(dtype, interp, n, n_emb, (int64_t)G * G * G, D)) return rc;
+    ASHB_REQUIRE(m != nullptr, "null map");
+    if (n == 0) return ASHB_OK;
+    ASHB_REQUIRE(z && embeddings && idx_out && rows_out, "null buffer");
+    ASHB_REQUIRE(!second_order || (grad_grad_x && side_out), "the double backward needs grad_grad_x and grad_z");
+    FusedSource src;
+    if (int rc = make_fused_source(m, x, cell_size, origin, G, nb_lut, block_idx, nullptr, nullptr, n_emb, &src))
+        return rc;
+    DeviceGuard guard(m->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const double scale = (double)(float)(1.0 / cell_size);
+    return dtype == ASHB_F32 ? backward_rows_impl<float>(interp, second_order != 0, grad_grad_x, z, embeddings, src,
+                                                         idx_out, rows_out, side_out, scale, n, D, st)
+                             : backward_rows_impl<double>(interp, second_order != 0, grad_grad_x, z, embeddings, src,
+                                                          idx_out, rows_out, side_out, scale, n, D, st);
+}
+
+int ashb_rows_scatter_add(int dtype, void* dst, const int64_t* idx, const void* rows, int64_t m, int64_t n_emb,
+                          int64_t cells_per_grid, int64_t D, double alpha, void* stream) {
+    ASHB_REQUIRE(dtype == ASHB_F32 || dtype == ASHB_F64, "unknown dtype code %d", dtype);
+    ASHB_REQUIRE(m >= 0 && n_emb >= 1 && cells_per_grid >= 1 && D >= 1 && D <= 16, "bad sizes");
+    if (m == 0) return ASHB_OK;
+    ASHB_REQUIRE(dst && idx && rows, "null buffer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == ASHB_F32 ? rows_scatter_add_impl<float>(dst, idx, rows, m, n_emb, cells_per_grid, D, alpha, st)
+                             : rows_scatter_add_impl<double>(dst, idx, rows, m, n_emb, cells_per_grid, D, alpha, st);
 }
 
 int ashb_set_scatter_aggregation(int enable) {
