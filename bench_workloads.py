@@ -153,6 +153,26 @@ def camera_poses(n, seed=SEED + 2, inner=6.0):
     return [look_at(eyes[i], targets[i]) for i in range(n)]
 
 
+def camera_poses_covering(n, seed=SEED + 2, box=10.0, standoff=3.2, jitter=0.4):
+    """Random poses that together see (nearly) the whole room: frame i looks at the wall point in
+    the i-th direction of a spherical Fibonacci lattice from about ``standoff`` metres away (eye and
+    target jittered), so that n = 100 frames of 640 x 480 at depth_max 5 m cover the 600 m^2 of walls
+    and the spheres in front of them once or twice instead of re-observing a few places."""
+    g = torch.Generator().manual_seed(seed)
+    half = box / 2
+    k = torch.arange(n, dtype=torch.float64) + 0.5
+    phi = math.pi * (3.0 - math.sqrt(5.0)) * k
+    zc = 1.0 - 2.0 * k / n
+    rc = (1.0 - zc * zc).clamp_min(0).sqrt()
+    dirs = torch.stack([rc * torch.cos(phi), rc * torch.sin(phi), zc], dim=1)
+    wall = dirs * (half / dirs.abs().max(dim=1, keepdim=True)[0])          # where the direction leaves the box
+    eyes = wall - standoff * dirs + (torch.rand(n, 3, generator=g, dtype=torch.float64) - 0.5) * 2 * jitter
+    eyes = eyes.clamp(-half + 0.8, half - 0.8)
+    targets = wall + (torch.rand(n, 3, generator=g, dtype=torch.float64) - 0.5) * 2 * jitter
+    order = torch.randperm(n, generator=g)                                   # consecutive frames are unrelated views
+    return [look_at(eyes[i], targets[i]) for i in order.tolist()]
+
+
 def intrinsics(H=480, W=640):
     """525-pixel focal length at 640 x 480, principal point at the image centre, scaled with W."""
     s = W / 640.0

@@ -279,6 +279,14 @@ int ashb_conv_forward_tiled(const float* inputs, const float* weights, const int
                             const int64_t* lut_grid_nb27, float* outputs, int zero_output,
                             int64_t num_grids, int64_t n_emb, int G, int radius, int64_t D, void* stream);
 
+/* The tiled form for a SEPARABLE window, weights[z][y][x][c] = wz[z][c] * wy[y][c] * wx[x][c] (the
+ * Gaussian of SparseDenseGrid.gaussian_filter_, ash/grid.py:449-462, is one): weights_1d float32
+ * [3][2 radius + 1][D], axis 0 = x.  Three 1-D passes inside the shared-memory halo tile: 3 (2R+1)
+ * multiply-adds per cell and channel instead of (2R+1)^3; same result up to the order of the sums. */
+int ashb_conv_forward_separable(const float* inputs, const float* weights_1d, const int64_t* grid_indices,
+                                const int64_t* lut_grid_nb27, float* outputs, int zero_output, int64_t num_grids,
+                                int64_t n_emb, int G, int radius, int64_t D, void* stream);
+
 /* ---------------------------------------------------------------- iso-surface vertices */
 
 /* Replaces isosurface_extraction_kernel + isosurface_extraction (ash/src/grid.cu:453-604),
@@ -639,6 +647,10 @@ int ashb_set_scatter_aggregation(int enable);
 /* Selects the kernel behind ashb_map_find for key_dim <= 3: 0 = one thread per key (default),
  * 1 = eight lanes per key reading a whole 128-byte line of slots per step.  Same results. */
 int ashb_set_find_cooperative(int enable);
+
+/* The same choice for ashb_map_erase (replaces the probe of ash/src/hashmap_gpu.cuh:317-336):
+ * 0 = one thread per key (default), 1 = eight lanes per key.  Same results. */
+int ashb_set_erase_cooperative(int enable);
 
 /* Occupancy filter of ashb_map_find for key_dim <= 3 (no counterpart in the reference).  Every map
  * keeps one bit per slot, set when a key is first stored there; a find whose home slot never held a

@@ -179,3 +179,42 @@ def check_checkpoints(ash, device):
     mine = grid.state_dict()
     for name, ref in ck["state_dict"].items():
         assert mine[name].shape == ref.shape and mine[name].dtype == ref.dtype, name
+
+
+def check_resize(ash, device):
+    """Growing keeps every live key at its index, keeps the values, keeps handing out only unused
+    indices afterwards; shrinking (the reference's re-insertion, ash/core.py:266-302) keeps the
+    key -> value association."""
+    g = torch.Generator().manual_seed(9)
+    keys = torch.randint(-30, 30, (900, 3), generator=g, dtype=torch.int32).to(device)
+    val = lambda k: {"sdf": k[:, :1].float() * 0.5 + k[:, 1:2].float() * 11, "rgb": k.float()}
+    hm = ash.HashMap(3, {"sdf": 1, "rgb": 3}, 1000, device)
+    hm.insert(keys, val(keys))
+    hm.erase(keys[:200])                               # the free-index stack is no longer the identity
+    live_keys, live_idx = hm.engine.items()
+    n = hm.size()
+    hm.resize(2500)
+    assert hm.engine.capacity == 2500 and hm.size() == n
+    idx_after, ok = hm.engine.find(live_keys)
+    assert ok.all() and torch.equal(idx_after, live_idx), "growing must not move live keys"
+    masks, _, got = hm.find(live_keys, return_values=True)
+    assert masks.all() and torch.equal(got["rgb"], live_keys.float())
+    fresh = (torch.arange(1500, dtype=torch.int32).view(-1, 1) + 100).tile((1, 3)).to(device)
+    hm.insert(fresh, val(fresh))                       # fills the map beyond its old capacity
+    assert hm.size() == n + 1500
+    all_keys, all_idx = hm.engine.items()
+    assert torch.unique(all_idx).numel() == n + 1500 and int(all_idx.max()) < 2500 and int(all_idx.min()) >= 0
+    masks, _, got = hm.find(all_keys, return_values=True)
+    assert masks.all() and torch.equal(got["rgb"], all_keys.float())
+    assert torch.equal(hm.engine.find(live_keys)[0], live_idx)
+    hm.erase(fresh[:1400])
+    hm.resize(n + 150)                                 # shrink: re-insertion, indices may change
+    assert hm.size() == n + 100
+    masks, _, got = hm.find(all_keys, return_values=True)
+    assert int(masks.sum()) == n + 100 and torch.equal(got["rgb"][masks], all_keys[masks].float())
+    # an empty map and a set grow too
+    empty = ash.HashSet(2, 10, device)
+    empty.resize(50)
+    assert empty.size() == 0 and empty.engine.capacity == 50
+    empty.insert(torch.arange(80, dtype=torch.int32).view(-1, 2).to(device))
+    assert empty.size() == 40

@@ -52,16 +52,30 @@ def test_convolution_vs_oracle(G, D, size, tiled):
     assert np.count_nonzero(ref) > 0
 
 
-def test_gaussian_filter_matches_reference_weights():
-    """gaussian_filter_(7, 1): kernel of ash/grid.py:449-472, normalised, applied in place."""
-    grid, _ = _shell_grid(8, 4, n_blocks=60, seed=3)
+@pytest.mark.parametrize("separable", [False, True])
+@pytest.mark.parametrize("G,D,size,sigma", [(8, 4, 7, 1.0), (8, 16, 3, 0.5), (4, 3, 5, 2.0), (8, 1, 9, 1.5), (2, 2, 3, 1.0)])
+def test_gaussian_filter_matches_reference_weights(G, D, size, sigma, separable):
+    """gaussian_filter_: kernel of ash/grid.py:449-472, normalised, applied in place -- as the full
+    size^3 window and as three 1-D passes (the window is an outer product) -- against the oracle's
+    size^3-tap convolution with the reference's weights, on a blobby block set whose skin blocks
+    miss neighbours (absent blocks count as zero in both)."""
+    grid, _ = _shell_grid(G, D, n_blocks=60, seed=3 + size)
+    grid.separable_gaussian = separable
     before = grid.embeddings.detach().clone()
-    w = grid._gaussian_weights(7, 1.0)
-    assert w.shape == (7, 7, 7) and abs(float(w.sum()) - 1) < 1e-6
+    w = grid._gaussian_weights(size, sigma)
+    assert w.shape == (size,) * 3 and abs(float(w.sum()) - 1) < 1e-6
     assert torch.allclose(w, w.flip(0)) and torch.allclose(w, w.permute(2, 1, 0))
-    grid.gaussian_filter_(7, 1.0)
-    expect = grid.convolution(before, w.view(7, 7, 7, 1).repeat(1, 1, 1, 4).to(DEV))
-    assert torch.allclose(grid.embeddings.detach(), expect)
+    grid.gaussian_filter_(size, sigma)
+    r = size // 2
+    c2g, c2c = grid.construct_cell_neighbor_lut(r, bidirectional=True)
+    _, g2g = grid.construct_grid_neighbor_lut((r + G - 1) // G, bidirectional=True)
+    _, _, gi, ci = grid.items()
+    t = lambda a: a.detach().cpu().numpy()
+    ref = oracle.convolution_forward(
+        t(before), t(w.view(-1, 1).repeat(1, D)), np.ones(gi.numel() * G**3, np.uint8), t(gi), t(ci), t(g2g), t(c2c),
+        t(c2g))
+    np.testing.assert_allclose(t(grid.embeddings), ref, rtol=1e-5, atol=1e-5)
+    assert np.count_nonzero(ref) > 0
 
 
 def _oracle_map_like(grid):

@@ -36,6 +36,10 @@ def test_reference_written_checkpoints_load(ash_cpu):
     gc.check_checkpoints(ash_cpu, CPU)
 
 
+def test_resize_grows_in_place_and_shrinks_by_reinsertion(ash_cpu):
+    gc.check_resize(ash_cpu, CPU)
+
+
 def test_engine_contract(ash_cpu, tmp_path):
     """unittests/test_engine.py semantics on the host side: index set, duplicates, state_dict
     round trip incl. the empty map, resize, warnings on empty input and on overflow."""

@@ -34,6 +34,12 @@ def test_reference_written_checkpoints_load():
     gc.check_checkpoints(ash, DEV)
 
 
+def test_resize_grows_in_place_and_shrinks_by_reinsertion():
+    import ash
+
+    gc.check_resize(ash, DEV)
+
+
 def test_smoke_entry():
     import __graft_entry__
 

@@ -66,6 +66,7 @@ _lib.ashb_grid_query_backward.argtypes = [_vp, _int, _int, _vp, _vp, _vp, _c.c_d
 _lib.ashb_grid_query_backward_backward.argtypes = [_vp, _int, _int, _vp, _vp, _vp, _vp, _c.c_double, _vp, _int, _vp, _vp, _vp,
                                                    _vp, _int, _i64, _i64, _i64, _vp]
 _lib.ashb_conv_forward_tiled.argtypes = [_vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _int, _int, _i64, _vp]
+_lib.ashb_conv_forward_separable.argtypes = [_vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _int, _int, _i64, _vp]
 _lib.ashb_grid_spatial_init.argtypes = [_vp, _vp, _i64, _c.c_double, _vp, _int, _int, _int, _vp, _vp, _vp, _vp, _c.c_uint32,
                                         _vp, _vp, _vp]
 _lib.ashb_route_by_owner.argtypes = [_vp, _i64, _int, _int, _vp, _vp, _vp, _vp, _vp]
@@ -102,6 +103,7 @@ _lib.ashb_grid_query_backward_rows.argtypes = [_vp, _int, _int, _int, _vp, _vp, 
                                                _vp, _vp, _vp, _i64, _i64, _i64, _vp]
 _lib.ashb_rows_scatter_add.argtypes = [_int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _c.c_double, _vp]
 _lib.ashb_set_find_filter.argtypes = [_int]
+_lib.ashb_set_erase_cooperative.argtypes = [_int]
 _lib.ashb_measure_random_reads_ilp.argtypes = [_vp, _i64, _i64, _int, _int, _c.c_uint32, _vp, _vp]
 _ROUTED_LAYOUT = [_vp] + [_i64] * 7 + [_int, _int]
 _lib.ashb_routed_route.argtypes = [_vp, _vp, _i64, _c.c_double, _vp, _int, _vp, _vp, _i64, _i64] + _ROUTED_LAYOUT + [_vp] * 4
@@ -133,6 +135,12 @@ def measure_random_reads(buffer: torch.Tensor, n_reads: int, fetch_bytes: int = 
         _check(_lib.ashb_measure_random_reads_ilp(buf.data_ptr(), buf.numel() * buf.element_size(), int(n_reads),
                                                   int(fetch_bytes), int(reads_per_thread), int(seed) & 0xFFFFFFFF,
                                                   sink.data_ptr(), _stream(buf.device)))
+
+
+def set_erase_cooperative(enable: bool) -> None:
+    """Process-wide choice of the erase kernel for key_dim <= 3: one thread per key (default) or
+    eight lanes per key reading whole 128-byte lines of slots."""
+    _check(_lib.ashb_set_erase_cooperative(int(bool(enable))))
 
 
 def set_find_filter(mode: int) -> None:
@@ -761,6 +769,25 @@ def convolution_forward_tiled(inputs, weights, grid_indices, lut_grid_nb27, grid
     out = torch.empty_like(inp)
     with torch.cuda.device(inp.device):
         _check(_lib.ashb_conv_forward_tiled(
+            inp.data_ptr(), w.data_ptr(), gi.data_ptr(), g27.data_ptr(), out.data_ptr(), 1, gi.shape[0], n_emb,
+            int(grid_dim), int(radius), D, _stream(inp.device)))
+    return out
+
+
+def convolution_forward_separable(inputs, weights_1d, grid_indices, lut_grid_nb27, grid_dim, radius):
+    """``convolution_forward_tiled`` for a separable window: ``weights_1d`` (3, 2R+1, D) float32 holds
+    the x, y and z factors per channel.  No counterpart in the reference."""
+    inp = _cuda(inputs, "inputs", torch.float32)
+    w = _cuda(weights_1d, "weights_1d", torch.float32)
+    gi = _cuda(grid_indices, "grid_indices", torch.int64).view(-1)
+    g27 = _cuda(lut_grid_nb27, "lut_grid_nb27", torch.int64)
+    n_emb, cells, D = inp.shape
+    S = 2 * int(radius) + 1
+    if cells != int(grid_dim) ** 3 or w.shape != (3, S, D) or g27.shape != (n_emb, 27):
+        raise RuntimeError("convolution_forward_separable: shapes do not match (grid_dim, radius)")
+    out = torch.empty_like(inp)
+    with torch.cuda.device(inp.device):
+        _check(_lib.ashb_conv_forward_separable(
             inp.data_ptr(), w.data_ptr(), gi.data_ptr(), g27.data_ptr(), out.data_ptr(), 1, gi.shape[0], n_emb,
             int(grid_dim), int(radius), D, _stream(inp.device)))
     return out

@@ -171,17 +171,34 @@ class ASHEngine(nn.Module):
 
     def resize(self, capacity: int, old_external_values: Dict[str, torch.Tensor] = None,
                new_external_values: Dict[str, torch.Tensor] = None) -> None:
-        """Rebuild with a new capacity, re-inserting the active keys (and moving their value
-        rows from ``old_external_values`` to ``new_external_values``); ash/core.py:266-302."""
+        """Change the capacity, keeping every key -> value association (ash/core.py:266-302).
+
+        Growing keeps every live key at ITS index: a table of the new size is loaded with the
+        (key, index) pairs as a checkpoint would be, the free-index stack is carried over with the
+        new indices appended, and value rows move as one straight copy of the old buffers into the
+        head of the new ones -- no re-insertion, no gather by index.  Shrinking re-inserts the
+        active keys and moves their rows by index, as the reference always does."""
         active_keys, old_indices = self.items()
         n = active_keys.shape[0]
         assert capacity >= n, "new capacity is smaller than the current size"
         assert capacity > 0, "new capacity is 0"
+        old_heap, old_capacity = self._heap, self.capacity
+        in_place = capacity >= old_capacity
         del self.backend
         self.capacity = capacity
         self._register_buffers()
+        if in_place:
+            self._heap[:old_capacity] = old_heap   # entries n .. old_capacity-1 are the old free indices; the new ones follow
         self.backend = backend.HashMap(self.dim, self.capacity, self._heap, self.device)
         self._size_bound = n
+        self._erased_bound = 0
+        if in_place:
+            if n:
+                self.backend.load_states({"active_keys": active_keys, "active_indices": old_indices, "heap": self._heap})
+            if old_external_values is not None and new_external_values is not None:
+                for name, v in old_external_values.items():
+                    new_external_values[name][:old_capacity] = v
+            return
         if n == 0:
             return
         if old_external_values is not None and new_external_values is not None:

@@ -57,6 +57,7 @@ class SparseDenseGrid(ASHModule):
         # reference's split + find + pre-split kernel sequence.
         self.fused = True
         self.tiled_convolution = True
+        self.separable_gaussian = True
         # "dense" (the reference's contract): every backward call returns a fresh, zero-filled,
         # table-sized gradient that autograd accumulates into embeddings.grad.  "in_place": the
         # fused backward passes add straight into embeddings.grad (created as zeros when missing),
@@ -313,22 +314,43 @@ class SparseDenseGrid(ASHModule):
 
     # ------------------------------------------------------------------ filtering
     @staticmethod
-    def _gaussian_weights(size: int, sigma: float) -> torch.Tensor:
-        """Separable kernel of ash/grid.py:449-462: bin masses of a standard normal over
-        ``size`` equal bins of [-sigma, sigma], outer-multiplied and normalised."""
+    def _gaussian_weights_1d(size: int, sigma: float):
+        """The 1-D factor of ash/grid.py:449-462: bin masses of a standard normal over ``size`` equal
+        bins of [-sigma, sigma] (float64 numpy)."""
         import numpy as np
         import scipy.stats as st
 
         edges = np.linspace(-sigma, sigma, size + 1)
-        k1 = np.diff(st.norm.cdf(edges))
+        return np.diff(st.norm.cdf(edges))
+
+    @staticmethod
+    def _gaussian_weights(size: int, sigma: float) -> torch.Tensor:
+        """Separable kernel of ash/grid.py:449-462: the 1-D factor outer-multiplied and normalised."""
+        import numpy as np
+
+        k1 = SparseDenseGrid._gaussian_weights_1d(size, sigma)
         k3 = np.outer(k1, np.outer(k1, k1)).reshape(size, size, size)
         return torch.from_numpy(k3 / k3.sum()).float()
 
     @torch.no_grad()
     def gaussian_filter_(self, size: int, sigma: float) -> None:
-        """In-place ``size``^3 Gaussian smoothing of every embedding channel."""
+        """In-place ``size``^3 Gaussian smoothing of every embedding channel.  The window is an outer
+        product, so on the GPU it runs as three 1-D passes inside the shared-memory tile of the
+        convolution (``separable_gaussian``; same values up to the order of the sums) instead of
+        ``size``^3 taps per cell."""
         assert size % 2 == 1, "size must be odd"
         channels = self.embeddings.shape[-1]
+        radius = size // 2
+        emb = self.embeddings
+        if (self.separable_gaussian and self.tiled_convolution and emb.is_cuda and emb.dtype == torch.float32
+                and 1 <= radius <= self.grid_dim and hasattr(backend, "convolution_forward_separable")):
+            k1 = self._gaussian_weights_1d(size, sigma)
+            k1 = k1 / k1.sum()                       # (k1 (x) k1 (x) k1) / sum = product of the normalised factors
+            w1 = torch.from_numpy(k1).float().view(1, size, 1).repeat(3, 1, channels).contiguous().to(emb.device)
+            _, lut_g2g = self.construct_grid_neighbor_lut(1, bidirectional=True)
+            _, _, grid_indices, _ = self.items()
+            emb.copy_(backend.convolution_forward_separable(emb.data, w1, grid_indices, lut_g2g, self.grid_dim, radius))
+            return
         weights = self._gaussian_weights(size, sigma).view(size, size, size, 1).repeat(1, 1, 1, channels)
         self.embeddings.copy_(self.convolution(self.embeddings, weights.to(self.embeddings.device)))
 

@@ -165,6 +165,105 @@ __global__ void __launch_bounds__(256) conv_tiled_kernel(const float* __restrict
     }
 }
 
+// Separable window: weights[z][y][x][c] = wz[z][c] * wy[y][c] * wx[x][c] (a Gaussian is one).  The
+// same halo tile is staged, then three 1-D passes run inside shared memory -- along x over the
+// whole (G+2R)^2 cross-section, along y over the (G+2R) slabs that remain, along z -- so a
+// (2R+1)^3 window costs 3 (2R+1) multiply-adds per cell and channel instead of (2R+1)^3, and the
+// intermediate sums never exist for cells outside the tile (absent neighbour blocks count as zero
+// exactly as in the full window).  w1: [3][S][D], axis 0 = x.
+template <int CH>
+__global__ void __launch_bounds__(256) conv_separable_kernel(const float* __restrict__ in, const float* __restrict__ w1,
+                                                             const int64_t* __restrict__ grid_indices,
+                                                             const int64_t* __restrict__ g2g27, float* __restrict__ out,
+                                                             int G, int R, int D, int64_t n_emb) {
+    extern __shared__ float smem[];
+    const int S = 2 * R + 1, T = G + 2 * R;
+    const int cells = G * G * G, tile_cells = T * T * T;
+    float* tile = smem;                                   // [T][T][T][CH]; reused for the y-pass sums [T][G][G][CH]
+    float* t1 = smem + (size_t)tile_cells * CH;           // x-pass sums [T][T][G][CH]
+    float* wsm = t1 + (size_t)T * T * G * CH;             // [3][S][CH]
+    __shared__ int64_t nb[27];
+    const int64_t gidx = grid_indices[blockIdx.x];
+    const bool ok = gidx >= 0 && gidx < n_emb;
+    if (threadIdx.x < 27) nb[threadIdx.x] = ok ? g2g27[gidx * 27 + threadIdx.x] : -1;
+    __syncthreads();
+    if (!ok) return;
+    for (int ch0 = 0; ch0 < D; ch0 += CH) {
+        for (int k = threadIdx.x; k < 3 * S * CH; k += blockDim.x) wsm[k] = w1[(int64_t)(k / CH) * D + ch0 + (k % CH)];
+        for (int h = threadIdx.x; h < tile_cells; h += blockDim.x) {
+            const int hx = h % T, hy = (h / T) % T, hz = h / (T * T);
+            const int cx = hx - R, cy = hy - R, cz = hz - R;
+            const int bx = cx < 0 ? -1 : (cx >= G ? 1 : 0), by = cy < 0 ? -1 : (cy >= G ? 1 : 0),
+                      bz = cz < 0 ? -1 : (cz >= G ? 1 : 0);
+            const int64_t g = nb[(bx + 1) + (by + 1) * 3 + (bz + 1) * 9];
+            float v[CH];
+#pragma unroll
+            for (int c = 0; c < CH; ++c) v[c] = 0.f;
+            if (g >= 0 && g < n_emb) {
+                const int lin = (cx - bx * G) + ((cy - by * G) + (cz - bz * G) * G) * G;
+                const float* src = in + (g * cells + lin) * D + ch0;
+                if (CH == 4) {
+                    const float4 t4 = __ldg(reinterpret_cast<const float4*>(src));
+                    v[0] = t4.x, v[1] = t4.y, v[2] = t4.z, v[3] = t4.w;
+                } else {
+#pragma unroll
+                    for (int c = 0; c < CH; ++c) v[c] = __ldg(src + c);
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < CH; ++c) tile[(size_t)h * CH + c] = v[c];
+        }
+        __syncthreads();
+        // along x: t1[z'][y'][x] = sum_k wx[k] * tile[z'][y'][x + k]
+        for (int i = threadIdx.x; i < T * T * G; i += blockDim.x) {
+            const int x = i % G, zy = i / G;
+            const float* row = tile + ((size_t)zy * T + x) * CH;
+            float acc[CH];
+#pragma unroll
+            for (int c = 0; c < CH; ++c) acc[c] = 0.f;
+            for (int k = 0; k < S; ++k)
+#pragma unroll
+                for (int c = 0; c < CH; ++c) acc[c] += row[k * CH + c] * wsm[k * CH + c];
+#pragma unroll
+            for (int c = 0; c < CH; ++c) t1[(size_t)i * CH + c] = acc[c];
+        }
+        __syncthreads();
+        // along y: t2[z'][y][x] = sum_k wy[k] * t1[z'][y + k][x]   (t2 takes the tile's place)
+        float* t2 = tile;
+        for (int i = threadIdx.x; i < T * G * G; i += blockDim.x) {
+            const int x = i % G, y = (i / G) % G, zp = i / (G * G);
+            const float* col = t1 + ((size_t)(zp * T + y) * G + x) * CH;
+            float acc[CH];
+#pragma unroll
+            for (int c = 0; c < CH; ++c) acc[c] = 0.f;
+            for (int k = 0; k < S; ++k)
+#pragma unroll
+                for (int c = 0; c < CH; ++c) acc[c] += col[(size_t)k * G * CH + c] * wsm[(S + k) * CH + c];
+#pragma unroll
+            for (int c = 0; c < CH; ++c) t2[(size_t)i * CH + c] = acc[c];
+        }
+        __syncthreads();
+        // along z: out[z][y][x] = sum_k wz[k] * t2[z + k][y][x]
+        for (int i = threadIdx.x; i < cells; i += blockDim.x) {
+            const float* col = t2 + (size_t)i * CH;
+            float acc[CH];
+#pragma unroll
+            for (int c = 0; c < CH; ++c) acc[c] = 0.f;
+            for (int k = 0; k < S; ++k)
+#pragma unroll
+                for (int c = 0; c < CH; ++c) acc[c] += col[(size_t)k * G * G * CH + c] * wsm[(2 * S + k) * CH + c];
+            float* dst = out + (gidx * cells + i) * D + ch0;
+            if (CH == 4) {
+                *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            } else {
+#pragma unroll
+                for (int c = 0; c < CH; ++c) dst[c] = acc[c];
+            }
+        }
+        __syncthreads();
+    }
+}
+
 }  // namespace ashb
 
 using namespace ashb;
@@ -250,6 +349,39 @@ int ashb_conv_forward_tiled(const float* inputs, const float* weights, const int
     else ASHB_CONV_RADIUS(1, 1)
 #undef ASHB_CONV_RADIUS
 #undef ASHB_CONV_LAUNCH
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+int ashb_conv_forward_separable(const float* inputs, const float* weights_1d, const int64_t* grid_indices,
+                                const int64_t* lut_grid_nb27, float* outputs, int zero_output, int64_t num_grids,
+                                int64_t n_emb, int G, int radius, int64_t D, void* stream) {
+    ASHB_REQUIRE(D >= 1 && D <= 16, "embedding_dim %lld not in 1..16", (long long)D);
+    ASHB_REQUIRE(G >= 1 && G <= 16 && radius >= 1 && radius <= G, "window radius %d must be within one block (G=%d)",
+                 radius, G);
+    ASHB_REQUIRE(num_grids >= 0 && n_emb >= 1 && outputs != nullptr, "bad sizes");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t cells = (int64_t)G * G * G;
+    if (zero_output) ASHB_CUDA_TRY(cudaMemsetAsync(outputs, 0, (size_t)n_emb * cells * D * sizeof(float), st));
+    if (num_grids == 0) return ASHB_OK;
+    ASHB_REQUIRE(inputs && weights_1d && grid_indices && lut_grid_nb27, "null buffer");
+    const int ch = (D % 4 == 0 && ((((uintptr_t)inputs) | ((uintptr_t)outputs)) & 15) == 0) ? 4 : (D % 2 == 0 ? 2 : 1);
+    const int T = G + 2 * radius, S = 2 * radius + 1;
+    const size_t smem = ((size_t)T * T * T + (size_t)T * T * G + (size_t)3 * S) * ch * sizeof(float);
+    ASHB_REQUIRE(smem <= 200 * 1024, "halo tile of %zu bytes does not fit in shared memory", smem);
+#define ASHB_SEP_LAUNCH(CH)                                                                                   \
+    {                                                                                                         \
+        if (smem > 48 * 1024)                                                                                 \
+            ASHB_CUDA_TRY(cudaFuncSetAttribute(conv_separable_kernel<CH>,                                     \
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));     \
+        conv_separable_kernel<CH><<<(unsigned)num_grids, 256, smem, st>>>(inputs, weights_1d, grid_indices,   \
+                                                                           lut_grid_nb27, outputs, G, radius, \
+                                                                           (int)D, n_emb);                    \
+    }
+    if (ch == 4) ASHB_SEP_LAUNCH(4)
+    else if (ch == 2) ASHB_SEP_LAUNCH(2)
+    else ASHB_SEP_LAUNCH(1)
+#undef ASHB_SEP_LAUNCH
     ASHB_LAUNCH_CHECK();
     return ASHB_OK;
 }

@@ -176,6 +176,51 @@ __global__ void __launch_bounds__(256) erase_kernel(Table t, const int32_t* __re
     push_freed_index_cta(idx, heap, counter);  // launched with 256 threads
 }
 
+// Sub-warp cooperative erase for 16-byte slots, the counterpart of find_coop_kernel: 8 lanes serve
+// one key and read the whole 128-byte line (8 slots) that holds its home slot per step; a ballot
+// finds the first slot in probe order that is empty or holds the key, one lane turns it into a
+// tombstone and the freed indices go back on the stack with one atomic per CTA.  Same result as
+// erase_kernel.
+template <int DIM>
+__global__ void __launch_bounds__(256) erase_coop_kernel(Table16 t, const int32_t* __restrict__ keys, int64_t n,
+                                                         int32_t* __restrict__ heap, int32_t* counter) {
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t q = tid >> 3;
+    const int sub = (int)(tid & 7);
+    const int group_shift = (int)(threadIdx.x & 31) & ~7;
+    const bool live = q < n;
+    int k0 = 0, k1 = 0, k2 = 0, k3 = 0;
+    if (live) load_key<DIM>(keys, q, k0, k1, k2, k3);
+    const uint32_t home = hash_key(k0, k1, k2, k3) & t.mask;
+    uint32_t line = home & ~7u;
+    bool done = !live, first = true;
+    int idx = -1;
+    const uint32_t n_lines = (t.mask >> 3) + 1;
+    for (uint32_t it = 0; it <= n_lines && __any_sync(0xffffffffu, !done); ++it) {
+        Entry e{0, 0, 0, 0, kTomb};
+        const uint32_t slot = line + sub;
+        if (!done) e = t.read_fresh(slot);
+        const bool in_chain = !first || slot >= home;
+        const unsigned hit = __ballot_sync(0xffffffffu, !done && in_chain && e.val >= 0 && key_match(e, k0, k1, k2, k3));
+        const unsigned empty = __ballot_sync(0xffffffffu, !done && in_chain && e.val == kEmpty);
+        const unsigned g_hit = (hit >> group_shift) & 0xFFu, g_empty = (empty >> group_shift) & 0xFFu;
+        const int first_hit = g_hit ? __ffs(g_hit) - 1 : 99, first_empty = g_empty ? __ffs(g_empty) - 1 : 99;
+        if (!done) {
+            if (first_hit < first_empty) {
+                // the lane that read the key's slot erases it; in-batch duplicates race, one CAS wins
+                if (sub == first_hit && atomicCAS(t.val_ptr(slot), e.val, kTomb) == e.val) idx = e.val;
+                done = true;
+            } else if (first_empty < 99) {
+                done = true;
+            } else {
+                line = (line + 8) & t.mask;
+                first = false;
+            }
+        }
+    }
+    push_freed_index_cta(idx, heap, counter);  // launched with 256 threads
+}
+
 // ---- load_states -----------------------------------------------------------------
 template <class Table, int DIM>
 __global__ void __launch_bounds__(256) load_states_kernel(Table t, const int32_t* __restrict__ keys,
@@ -326,6 +371,7 @@ static bool g_find_cooperative = false;
 // Occupancy filter in find: -1 = automatic (tables of kFilterMinBytes and more, i.e. those that do
 // not stay in L2 anyway), 0 = never, 1 = always.
 static int g_find_filter = -1;
+static bool g_erase_cooperative = false;
 constexpr size_t kFilterMinBytes = (size_t)64 << 20;
 
 static size_t occupied_bytes(uint64_t n_slots) { return (size_t)(n_slots / 8 < 4 ? 4 : n_slots / 8); }
@@ -527,8 +573,23 @@ int ashb_map_erase(ashb_map* m, const int32_t* keys, int64_t n, void* stream) {
     if (n == 0) return ASHB_OK;
     ASHB_REQUIRE(keys != nullptr, "null keys");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    ASHB_DIM_LAUNCH(erase_kernel, m, blocks_for(n, 256), 256, st, keys, n, m->heap, m->counter);
+    if (g_erase_cooperative && m->key_dim <= 3) {
+        const Table16 t = table16_of(m);
+        const unsigned grid = blocks_for(n * 8, 256);
+        switch (m->key_dim) {
+            case 1: erase_coop_kernel<1><<<grid, 256, 0, st>>>(t, keys, n, m->heap, m->counter); break;
+            case 2: erase_coop_kernel<2><<<grid, 256, 0, st>>>(t, keys, n, m->heap, m->counter); break;
+            default: erase_coop_kernel<3><<<grid, 256, 0, st>>>(t, keys, n, m->heap, m->counter); break;
+        }
+    } else {
+        ASHB_DIM_LAUNCH(erase_kernel, m, blocks_for(n, 256), 256, st, keys, n, m->heap, m->counter);
+    }
     ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+int ashb_set_erase_cooperative(int enable) {
+    g_erase_cooperative = enable != 0;
     return ASHB_OK;
 }
 
