@@ -1258,7 +1258,7 @@ def main():
         line["roofline"]["row_list"] = {
             "kernel": "query_backward_rows_kernel<float,4,false,true>", "bound": "hbm", "achieved": round(rows_gbs, 1),
             "peak": peak, "unit": "GB/s", "frac": round(rows_gbs / peak, 4), "ms_per_launch": round(r_ms, 4),
-            "traffic": N_QUERIES * ROWS_TRAFFIC_PER_QUERY,
+            "traffic": N_QUERIES * ROWS_TRAFFIC_PER_QUERY if ROWS_TRAFFIC_PER_QUERY else None,
             "double_backward": {"kernel": "query_backward_rows_kernel<float,4,true,false>", "ms_per_launch": round(r2_ms, 4),
                                 "frac": round(N_QUERIES * BWDBWD_BYTES / (r2_ms * 1e-3) / 1e9 / peak, 4)},
             "apply_list_ms": round(ra_ms, 4),
@@ -1409,6 +1409,30 @@ def main():
 
         t_find = timed_find()                      # keys and answers over peer memory
         peer_answer = pm.find(q)                   # (the same path twice when the mailbox is unavailable)
+        find_phases = None
+        if pm.mailbox is not None:
+            # the same find, phase by phase (CUDA events between the launches; this rank's view)
+            box_, be = pm.mailbox, __ash
+            names = ("route", "barrier1", "answer", "barrier2", "unpack")
+            acc = {k: [] for k in names}
+            for _ in range(5):
+                barrier()
+                ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+                ev[0].record()
+                be.peer_route_keys(q, world, rank, box_.layout, box_.cursor, box_.status, where=box_.where)
+                ev[1].record()
+                box_.barrier()
+                ev[2].record()
+                be.peer_find_answer(pm.engine.backend, world, rank, box_.layout)
+                ev[3].record()
+                box_.barrier()
+                ev[4].record()
+                be.peer_unpack_answers(box_.where, q.shape[0], world, rank, box_.layout)
+                ev[5].record()
+                torch.cuda.synchronize()
+                for k, a, b in zip(names, ev[:-1], ev[1:]):
+                    acc[k].append(a.elapsed_time(b))
+            find_phases = {k: round(statistics.median(v), 4) for k, v in acc.items()}
         box, pm.mailbox = pm.mailbox, None
         t_find_nccl = timed_find()                 # grouping + all-to-all(v) each way
         nccl_answer = pm.find(q)
@@ -1429,7 +1453,7 @@ def main():
                 "insert_M_per_s": round(HASH_KEYS / (float(t[0]) * 1e-3) / 1e6, 1),
                 "insert_over_nccl_all_to_all_M_per_s": round(HASH_KEYS / (float(t[3]) * 1e-3) / 1e6, 1),
                 "hit_rate": round(hit, 4), **({"note": peer_note} if peer_note else {}),
-                "live_keys": total}
+                "find_phase_ms_rank0": find_phases, "live_keys": total}
         del pm, uniq, q
         torch.cuda.empty_cache()
 

@@ -212,7 +212,7 @@ int ashb_grid_query_backward_backward(ashb_map* map, int dtype, int interp, cons
 
 /* The two backward passes above with the embedding gradient WRITTEN as a row list instead of added
  * into a table-sized buffer (the dense `at::zeros_like(embeddings)` of ash/src/grid.cu:276 and :415):
- * idx_out int64 [2][8 n] and rows_out [8 n][D] (type of embeddings), record c * n + q = corner c of
+ * idx_out int64 [2][8 n] and rows_out [8 n][D] (type of embeddings), record 8 q + c = corner c of
  * query q: idx_out[0] = block index, idx_out[1] = cell index, rows_out = that corner's gradient row.
  * Together they are an uncoalesced sparse tensor of the table's shape (repeated cells add up).
  * Queries without a gradient write zero rows pointing at valid cells.  second_order == 0: the

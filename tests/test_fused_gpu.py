@@ -245,9 +245,9 @@ def test_row_list_gradient_mode_equals_dense_mode(kind, G, D):
     assert int(idx[0].min()) >= 0 and int(idx[0].max()) < grid.num_embeddings
     assert int(idx[1].min()) >= 0 and int(idx[1].max()) < G**3
     answered = masks & (y != 0).any(dim=1)
-    assert torch.count_nonzero(rows.view(8, n, D)[:, ~answered]) == 0
+    assert torch.count_nonzero(rows.view(n, 8, D)[~answered]) == 0
     # corner weights of a query sum to 1: with z = 1 every channel of its 8 rows sums to 1
-    torch.testing.assert_close(rows.view(8, n, D)[:, answered].sum(dim=0),
+    torch.testing.assert_close(rows.view(n, 8, D)[answered].sum(dim=1),
                                torch.ones(int(answered.sum()), D, device=DEV), rtol=1e-5, atol=1e-6)
     # the list applied to the parameters = a plain gradient-descent step
     dense = g.to_dense()

@@ -709,7 +709,7 @@ def grid_query_backward_backward(hashmap, grad_grad_x, z, embeddings, x, cell_si
 def grid_query_backward_rows(hashmap, z, embeddings, x, cell_size, origin, grid_dim, nb_lut, block_idx, interpolation,
                              need_grad_x=True, grad_grad_x=None):
     """The backward passes with the embedding gradient as a ROW LIST: returns ``(idx int64 (2, 8N),
-    rows (8N, D), side)``; record ``c * N + q`` is corner ``c`` of query ``q``, ``idx[0]`` its block
+    rows (8N, D), side)``; record ``8 q + c`` is corner ``c`` of query ``q``, ``idx[0]`` its block
     index, ``idx[1]`` its cell index.  ``side`` is grad_x (N, 3) (None unless ``need_grad_x``) for the
     first-order pass, or grad_z (N, D) when ``grad_grad_x`` is given (the double backward)."""
     emb, x, nb_lut = _fused_args(hashmap, embeddings, x, nb_lut)

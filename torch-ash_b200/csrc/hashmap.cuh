@@ -56,8 +56,7 @@ struct Table16 {
     }
     // Read-only probe (find / items): table is constant for the launch.
     // The loads name a 64-byte L2 fetch size: a probe needs one 16-byte slot of a random line, and
-    // the default fill of the whole 128-byte line from DRAM is wasted traffic (measured: find
-    // 1.216 -> 1.185 ms at 50M keys).
+    // the default fill of the whole 128-byte line from DRAM is wasted traffic.
     __device__ __forceinline__ Entry read_const(uint32_t s) const {
         uint4 u;
         asm volatile("ld.global.nc.L2::64B.v4.u32 {%0,%1,%2,%3}, [%4];"

@@ -84,8 +84,8 @@ struct LutSource {
 // Positions in.  The split follows the Python layer operation by operation as it
 // evaluates on a CUDA tensor (ash/grid.py:192-197, :756, :846): divisions by the
 // cell size and by G are multiplications by float reciprocals, each rounded.
-// Forward kernel with this source: 6 resident CTAs (<= 40 registers) measured 0.556 ms against
-// 0.591 ms unconstrained (48 registers) and 0.601 ms at 8 CTAs (spills) for 4M queries.
+// The forward kernel with this source is built for 6 resident CTAs (<= 40 registers): faster than
+// unconstrained (48 registers) and than 8 CTAs (spills).
 #ifndef ASHB_FWD_MIN_BLOCKS
 #define ASHB_FWD_MIN_BLOCKS 6
 #endif
@@ -444,7 +444,8 @@ __global__ void __launch_bounds__(256, ASHB_BWD_MIN_BLOCKS) query_backward_backw
 // ---- backward passes that WRITE the embedding gradient as a row list ---------------------------
 // Instead of adding eight rows per query into a table-sized buffer (a read-modify-write of eight
 // random lines, on top of a table-sized zero-fill when the buffer is fresh), the gradient leaves as
-// 8 n records in corner-major order: record c * n + q = (block index, cell index, row of D values).
+// 8 n records in query-major order: record 8 q + c = (block index, cell index, row of D values) of
+// corner c of query q, so a CTA writes three contiguous streams.
 // Every store is coalesced and nothing is read back, so the pass moves its algorithmic bytes and
 // no more.  The list is an uncoalesced sparse tensor of the table's shape (duplicates mean
 // "add"); ashb_rows_scatter_add applies it to any dense buffer (a gradient, or the parameters
@@ -479,7 +480,7 @@ __global__ void __launch_bounds__(256, ASHB_ROWS_MIN_BLOCKS) query_backward_rows
         const bool ok = gi >= 0 && gi < src.n_emb && corner_blocks_cells(src.nb_lut, gi, cell, src.G, src.n_emb, blocks, cells);
         if (has_ch && !ok) {
 #pragma unroll
-            for (int c = 0; c < 8; ++c) store_pack<T, VEC>(rows_out + ((int64_t)c * n + q) * D + ch, gz);
+            for (int c = 0; c < 8; ++c) store_pack<T, VEC>(rows_out + (q * 8 + c) * D + ch, gz);
             if (SECOND) store_pack<T, VEC>(side + q * D + ch, gz);
         } else if (has_ch) {
             AxisWeights<T> aw;
@@ -497,8 +498,8 @@ __global__ void __launch_bounds__(256, ASHB_ROWS_MIN_BLOCKS) query_backward_rows
                 g3[1] = ggo[3 * q + 1] * go_scale;
                 g3[2] = ggo[3 * q + 2] * go_scale;
             }
-            T* out = rows_out + q * D + ch;
-            const int64_t corner_stride = n * D;
+            T* out = rows_out + q * 8 * D + ch;
+            const int64_t corner_stride = D;
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 T wg[3] = {0, 0, 0};
@@ -526,8 +527,8 @@ __global__ void __launch_bounds__(256, ASHB_ROWS_MIN_BLOCKS) query_backward_rows
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
             if ((c & (lanes - 1)) != lane) continue;
-            idx_out[(int64_t)c * n + q] = ok ? blocks[c] : (int64_t)(q % src.n_emb);
-            idx_out[(int64_t)(8 + c) * n + q] = ok ? cells[c] : (int64_t)(c % src.cells_per_grid);
+            idx_out[q * 8 + c] = ok ? blocks[c] : (int64_t)(q % src.n_emb);
+            idx_out[(n + q) * 8 + c] = ok ? cells[c] : (int64_t)(c % src.cells_per_grid);
         }
     }
     if (SECOND || !NEED_GO) return;

@@ -73,8 +73,7 @@ __device__ __forceinline__ Pack<T, VEC> load_pack(const T* p) {
 }
 
 // Rows of 4 floats per lane are gathered from random lines: naming a 64-byte L2 fetch size keeps
-// the DRAM fill to the half line that holds the 64-byte row (measured: backward 1.54 -> 1.44 ms,
-// forward 0.606 -> 0.591 ms at 4M queries).
+// the DRAM fill to the half line that holds the 64-byte row.
 template <>
 __device__ __forceinline__ Pack<float, 1> load_pack<float, 1>(const float* p) {
     Pack<float, 1> r;

@@ -59,73 +59,86 @@ struct TouchTarget {
     int32_t* touched_count;
 };
 
-// Called by every lane of a warp (`valid` lanes carry a block): one lane per distinct block
-// inserts-if-absent the blocks of its neighbourhood, records their coordinates and stamps them.
+// Insert-if-absent of block (kx, ky, kz), its coordinate recorded and its stamp set; appended to the
+// compact list by the first toucher of the call.
+__device__ __forceinline__ void touch_block(const Table16& t, const TouchTarget& tt, int kx, int ky, int kz) {
+    if (tt.bounded && (kx < tt.lo.x || ky < tt.lo.y || kz < tt.lo.z || kx >= tt.hi.x || ky >= tt.hi.y || kz >= tt.hi.z))
+        return;
+    // fast path: the block exists already (probe at L2: this launch mutates the table)
+    int idx = -1;
+    {
+        uint32_t s = hash_key(kx, ky, kz, 0) & t.mask;
+        for (uint32_t probe = 0; probe <= t.mask; ++probe) {
+            const Entry e = t.read_fresh(s);
+            if (e.val == kEmpty) break;
+            if (e.val >= 0 && key_match(e, kx, ky, kz, 0)) {
+                idx = e.val;
+                break;
+            }
+            s = (s + 1) & t.mask;
+        }
+    }
+    if (idx < 0) {
+        bool present = false;
+        const int64_t slot = emplace(t, kx, ky, kz, 0, kPending, &present);
+        if (slot < 0) return;  // another thread of this launch owns it and stamps it
+        const int top = atomicAdd(tt.counter, 1);
+        if (top >= tt.capacity) {
+            atomicSub(tt.counter, 1);
+            *reinterpret_cast<volatile int*>(t.val_ptr((uint32_t)slot)) = kTomb;
+            atomicOr(t.status, ASHB_STATUS_CAPACITY);
+            return;
+        }
+        idx = tt.heap[top];
+        *reinterpret_cast<volatile int*>(t.val_ptr((uint32_t)slot)) = idx;
+    }
+    // the coordinate is recorded for blocks allocated by other means too
+    tt.grid_coords[3 * idx] = kx;
+    tt.grid_coords[3 * idx + 1] = ky;
+    tt.grid_coords[3 * idx + 2] = kz;
+    if (tt.touched_list) {
+        // first toucher of the call appends the block to the compact work list
+        if (atomicExch(&tt.touched[idx], tt.stamp) != tt.stamp) tt.touched_list[atomicAdd(tt.touched_count, 1)] = idx;
+    } else {
+        tt.touched[idx] = tt.stamp;
+    }
+}
+
+// Called by EVERY lane of a warp (`valid` lanes carry a block).  The distinct blocks of the warp are
+// found with a match; then, one distinct block after the other, the lanes of the whole warp share
+// out its neighbourhood -- lane k takes neighbour k -- so the (2 dilation + 1)^3 probes / inserts
+// of a block run side by side instead of one after the other on a single lane.
 __device__ __forceinline__ void touch_neighbourhood(const Table16& t, const TouchTarget& tt, bool valid, int bx,
                                                     int by, int bz) {
+    const int lane = threadIdx.x & 31;
     // a point whose own block is out of bounds contributes nothing (ash/grid.py:134-135)
     if (valid && tt.bounded &&
         (bx < tt.lo.x || by < tt.lo.y || bz < tt.lo.z || bx >= tt.hi.x || by >= tt.hi.y || bz >= tt.hi.z))
         valid = false;
     const unsigned active = __ballot_sync(0xffffffffu, valid);
-    if (!valid) return;
-    const unsigned long long packed = ((unsigned long long)(unsigned)bx * 0x9E3779B97F4A7C15ull) ^
-                                      ((unsigned long long)(unsigned)by << 21) ^
-                                      ((unsigned long long)(unsigned)bz << 42) ^ (unsigned)bz;
-    const unsigned peers = __match_any_sync(active, packed);
-    // `packed` is not injective; lanes that collide without being equal just do their own work
-    const int leader = __ffs(peers) - 1;
-    const int lbx = __shfl_sync(peers, bx, leader), lby = __shfl_sync(peers, by, leader),
-              lbz = __shfl_sync(peers, bz, leader);
-    if ((int)(threadIdx.x & 31) != leader && lbx == bx && lby == by && lbz == bz) return;
-
-    for (int dz = tt.lo_off; dz <= tt.hi_off; ++dz)
-        for (int dy = tt.lo_off; dy <= tt.hi_off; ++dy)
-            for (int dx = tt.lo_off; dx <= tt.hi_off; ++dx) {
-                const int kx = bx + dx, ky = by + dy, kz = bz + dz;
-                if (tt.bounded && (kx < tt.lo.x || ky < tt.lo.y || kz < tt.lo.z || kx >= tt.hi.x || ky >= tt.hi.y ||
-                                   kz >= tt.hi.z))
-                    continue;
-                // fast path: the block exists already (probe at L2: this launch mutates the table)
-                int idx = -1;
-                {
-                    uint32_t s = hash_key(kx, ky, kz, 0) & t.mask;
-                    for (uint32_t probe = 0; probe <= t.mask; ++probe) {
-                        const Entry e = t.read_fresh(s);
-                        if (e.val == kEmpty) break;
-                        if (e.val >= 0 && key_match(e, kx, ky, kz, 0)) {
-                            idx = e.val;
-                            break;
-                        }
-                        s = (s + 1) & t.mask;
-                    }
-                }
-                if (idx < 0) {
-                    bool present = false;
-                    const int64_t slot = emplace(t, kx, ky, kz, 0, kPending, &present);
-                    if (slot < 0) continue;  // another thread of this launch owns it and stamps it
-                    const int top = atomicAdd(tt.counter, 1);
-                    if (top >= tt.capacity) {
-                        atomicSub(tt.counter, 1);
-                        *reinterpret_cast<volatile int*>(t.val_ptr((uint32_t)slot)) = kTomb;
-                        atomicOr(t.status, ASHB_STATUS_CAPACITY);
-                        continue;
-                    }
-                    idx = tt.heap[top];
-                    *reinterpret_cast<volatile int*>(t.val_ptr((uint32_t)slot)) = idx;
-                }
-                // the coordinate is recorded for blocks allocated by other means too
-                tt.grid_coords[3 * idx] = kx;
-                tt.grid_coords[3 * idx + 1] = ky;
-                tt.grid_coords[3 * idx + 2] = kz;
-                if (tt.touched_list) {
-                    // first toucher of the call appends the block to the compact work list
-                    if (atomicExch(&tt.touched[idx], tt.stamp) != tt.stamp)
-                        tt.touched_list[atomicAdd(tt.touched_count, 1)] = idx;
-                } else {
-                    tt.touched[idx] = tt.stamp;
-                }
-            }
+    bool lead = false;
+    if (valid) {
+        const unsigned long long packed = ((unsigned long long)(unsigned)bx * 0x9E3779B97F4A7C15ull) ^
+                                          ((unsigned long long)(unsigned)by << 21) ^
+                                          ((unsigned long long)(unsigned)bz << 42) ^ (unsigned)bz;
+        const unsigned peers = __match_any_sync(active, packed);
+        const int leader = __ffs(peers) - 1;
+        const int lbx = __shfl_sync(peers, bx, leader), lby = __shfl_sync(peers, by, leader),
+                  lbz = __shfl_sync(peers, bz, leader);
+        // `packed` is not injective; lanes that collide without being equal lead their own block
+        lead = lane == leader || lbx != bx || lby != by || lbz != bz;
+    }
+    unsigned leaders = __ballot_sync(0xffffffffu, lead);
+    const int w = tt.hi_off - tt.lo_off + 1, n_nb = w * w * w;
+    while (leaders) {
+        const int from = __ffs(leaders) - 1;
+        leaders &= leaders - 1;
+        const int cx = __shfl_sync(0xffffffffu, bx, from), cy = __shfl_sync(0xffffffffu, by, from),
+                  cz = __shfl_sync(0xffffffffu, bz, from);
+        for (int k = lane; k < n_nb; k += 32)
+            touch_block(t, tt, cx + tt.lo_off + k % w, cy + tt.lo_off + (k / w) % w, cz + tt.lo_off + k / (w * w));
+        __syncwarp();
+    }
 }
 
 // world -> cell -> block as the Python layer does on a CUDA tensor: multiply by the float
