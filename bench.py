@@ -41,8 +41,9 @@ FIND_BYTES = 12 + 16 + 8 + 1                              # key, one slot, index
 # (taken on a reduced case whose tables are still many times L2; traffic per unit carries over)
 BWD_TRAFFIC_PER_QUERY = 1192 + 469
 FWD_TRAFFIC_PER_QUERY = 523 + 65
-FIND_TRAFFIC_PER_QUERY = 73 + 9
-ROWS_TRAFFIC_PER_QUERY = None  # filled from the ncu capture of the row-list kernel once taken
+FIND_TRAFFIC_PER_QUERY = 50 + 8      # with the occupancy filter (captured: 47 + 8 at load factor 0.125; 0.6 instead of 0.56 probes reach DRAM at 0.195)
+FIND_PLAIN_TRAFFIC_PER_QUERY = 73 + 9
+ROWS_TRAFFIC_PER_QUERY = 587 + 615
 
 
 def measured_peak_gbs():
@@ -447,7 +448,16 @@ def measure_tsdf(ash, bw, device, peak, n_frames=100, H=480, W=640):
         for d in frames:
             fusion.fuse_frame(d, counter=counter)
 
-    ms = event_ms(run)
+    ms_per_call = event_ms(run)           # one fuse_frame call per frame (this pass allocates the blocks)
+    first_blocks = grid.engine.size()
+    # the whole sequence as one fuse_dataset call into a fresh grid: both launches of every frame are
+    # enqueued from native code, so the host's per-frame work no longer paces the GPU
+    grid = ash.UnBoundedSparseDenseGrid(3, cap, 5, G, cell_size=cell, device=device)
+    fusion = TSDFFusion(grid, dilation=1)
+    counter.zero_()
+    torch.cuda.synchronize()
+    ms = event_ms(lambda: fusion.fuse_dataset(frames, counter=counter))
+    assert grid.engine.size() == first_blocks
     blocks = grid.engine.size()
     status = grid.engine.backend.status()
     # triangle mesh of the fused volume (sdf = channel 0, weight = channel 4)
@@ -465,6 +475,7 @@ def measure_tsdf(ash, bw, device, peak, n_frames=100, H=480, W=640):
     gbs = bytes_ / (ms * 1e-3) / 1e9
     return {"workload": f"{n_frames} frames {W}x{H}, voxel {cell} m, grid_dim {G}, 5 channels, dilation 1",
             "frames_per_s": round(n_frames / (ms * 1e-3), 1), "ms_per_frame": round(ms / n_frames, 4),
+            "frames_per_s_one_call_per_frame": round(n_frames / (ms_per_call * 1e-3), 1),
             "active_blocks": blocks, "status": status, "cell_updates_per_s": round(updated_cells / (ms * 1e-3) / 1e9, 3),
             "cell_updates_unit": "G cells/s",
             "marching_cubes": {"ms": round(mesh_ms, 3), "vertices": n_vert, "triangles": n_tri,
@@ -618,6 +629,7 @@ def measure_routed(ash, bw, device, dist, rank, world, grid, blocks, n_queries, 
     z = torch.ones(n_queries, D, device=device)
     box, hm, geom = grid._mailbox, grid.engine.backend, grid._routed_geometry()
     where = box.where[:n_queries]
+    # "zero_grad" is the time to ENQUEUE the fill: it runs on a side stream under route / forward / unpack / send_z
     names = ("zero_grad", "route", "barrier1", "forward", "barrier2", "unpack_y", "send_z", "barrier3", "backward",
              "barrier4", "unpack_grad_x")
 
@@ -643,6 +655,7 @@ def measure_routed(ash, bw, device, dist, rank, world, grid, blocks, n_queries, 
         y, masks = __ash.routed_unpack_y(where, n_queries, D, box.layout)
         mark()
         __ash.routed_send_z(where, z, box.layout)
+        grid._wait_for_zero_fill()
         mark()
         grid._barrier()
         mark()
@@ -1258,7 +1271,7 @@ def main():
         line["roofline"]["row_list"] = {
             "kernel": "query_backward_rows_kernel<float,4,false,true>", "bound": "hbm", "achieved": round(rows_gbs, 1),
             "peak": peak, "unit": "GB/s", "frac": round(rows_gbs / peak, 4), "ms_per_launch": round(r_ms, 4),
-            "traffic": N_QUERIES * ROWS_TRAFFIC_PER_QUERY if ROWS_TRAFFIC_PER_QUERY else None,
+            "traffic": N_QUERIES * ROWS_TRAFFIC_PER_QUERY,
             "double_backward": {"kernel": "query_backward_rows_kernel<float,4,true,false>", "ms_per_launch": round(r2_ms, 4),
                                 "frac": round(N_QUERIES * BWDBWD_BYTES / (r2_ms * 1e-3) / 1e9 / peak, 4)},
             "apply_list_ms": round(ra_ms, 4),
@@ -1352,7 +1365,7 @@ def main():
             "kernel": "find_kernel<Table16,3,filter>", "M_finds_per_s": line["hash_find"]["value"], "ms": round(t_find, 4),
             "bound": "hbm", "achieved": round(fa, 1), "peak": peak, "unit": "GB/s", "frac": round(fa / peak, 4),
             "traffic": HASH_KEYS * FIND_TRAFFIC_PER_QUERY, "hit_rate": round(hit, 4),
-            "without_occupancy_filter": {"ms": round(t_find_plain, 4),
+            "without_occupancy_filter": {"ms": round(t_find_plain, 4), "traffic": HASH_KEYS * FIND_PLAIN_TRAFFIC_PER_QUERY,
                                          "M_finds_per_s": round(HASH_KEYS / (t_find_plain * 1e-3) / 1e6, 1),
                                          "frac": round(HASH_KEYS * FIND_BYTES / (t_find_plain * 1e-3) / 1e9 / peak, 4)}}
         del hm, heap, q, uniq

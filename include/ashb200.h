@@ -394,6 +394,28 @@ int ashb_tsdf_integrate(void* embeddings, int64_t n_emb, int G, int64_t D, const
                         int rgb_channel, int weight_channel, unsigned long long* n_integrated_dev,
                         const int32_t* touched_list, const int32_t* touched_count, void* stream);
 
+/* Steps 1 and 2 in one call (TSDFFusion.fuse_frame, demo/rgbd_fusion.py:199-254, as one entry point:
+ * half the host work per frame); arguments as above, scratch provided by the caller. */
+int ashb_tsdf_fuse_frame(ashb_map* map, void* embeddings, int64_t n_emb, int G, int64_t D, const float* depth,
+                         const float* color, int H, int W, const float* intrinsic, const float* world_to_cam,
+                         const float* cam_to_world, float depth_max, double cell_size, const float* origin,
+                         int dilation, const int32_t* bound_lo, const int32_t* bound_hi, float trunc, int sdf_channel,
+                         int rgb_channel, int weight_channel, int32_t* grid_coords, uint32_t* touched, uint32_t stamp,
+                         int32_t* touched_list, int32_t* touched_count, unsigned long long* n_integrated_dev,
+                         void* stream);
+
+/* A sequence of frames of one size in one call (TSDFFusion.fuse_dataset, demo/rgbd_fusion.py:256-262): the two
+ * launches of every frame are enqueued back to back from native code, so the sequence is not limited by the
+ * caller's per-frame host work.  depths / colors: HOST arrays of n_frames device pointers; intrinsics
+ * [n_frames][9], world_to_cams and cam_to_worlds [n_frames][12]: host floats; frame f uses stamp first_stamp + f. */
+int ashb_tsdf_fuse_frames(ashb_map* map, void* embeddings, int64_t n_emb, int G, int64_t D, int n_frames,
+                          const float* const* depths, const float* const* colors, int H, int W,
+                          const float* intrinsics, const float* world_to_cams, const float* cam_to_worlds,
+                          float depth_max, double cell_size, const float* origin, int dilation, const int32_t* bound_lo,
+                          const int32_t* bound_hi, float trunc, int sdf_channel, int rgb_channel, int weight_channel,
+                          int32_t* grid_coords, uint32_t* touched, uint32_t first_stamp, int32_t* touched_list,
+                          int32_t* touched_count, unsigned long long* n_integrated_dev, void* stream);
+
 /* One whole fusion step (allocation + fusion, as the two calls above) that allocates nothing.
  * It has no counterpart in the reference.  It exists for callers that must not allocate device
  * memory while they run: a capture or playback loop that reserved all of its memory up front, a

@@ -125,10 +125,12 @@ def test_ray_near_far_and_sample_vs_oracle(G):
     assert ri0.numel() == 0 and (p0 == 0).all()
 
 
+@pytest.mark.parametrize("whole_sequence", [False, True])
 @pytest.mark.parametrize("H,W", [(120, 160)])
-def test_tsdf_fusion_vs_oracle(H, W):
-    """Three frames fused by the two CUDA launches vs the numpy restatement of fuse_frame:
-    same set of blocks, and per block coordinate the same sdf / rgb / weight (bit-exact
+def test_tsdf_fusion_vs_oracle(H, W, whole_sequence):
+    """Three frames fused by the two CUDA launches -- frame by frame through fuse_frame, or as one
+    native call for the whole sequence through fuse_dataset -- vs the numpy restatement of
+    fuse_frame: same set of blocks, and per block coordinate the same sdf / rgb / weight (bit-exact
     arithmetic contract; compared with a tiny tolerance)."""
     import ash
     from ash.fusion import TSDFFusion
@@ -139,12 +141,20 @@ def test_tsdf_fusion_vs_oracle(H, W):
     ref = otsdf.OracleTSDF(n_emb, G, cell, dil)
     scene = bw.Scene(DEV)
     K = bw.intrinsics(H, W)
+    frames = []
     for pose in bw.camera_poses(3, seed=77):
         E = torch.linalg.inv(pose)  # world -> camera
         depth, color = scene.render(K.to(DEV), pose.float().to(DEV), H, W)
-        datum = ash.DotDict(depth=depth.clone(), depth_scale=1.0, depth_max=depth_max, intrinsic=K, extrinsic=E, rgb=color)
-        fusion.fuse_frame(datum)
+        frames.append(ash.DotDict(depth=depth.clone(), depth_scale=1.0, depth_max=depth_max, intrinsic=K, extrinsic=E,
+                                  rgb=color))
         ref.fuse_frame(depth.cpu().numpy(), color.cpu().numpy(), K.numpy(), E.numpy(), np.linalg.inv(E.numpy()), depth_max)
+    if whole_sequence:
+        counter = torch.zeros(1, dtype=torch.int64, device=DEV)
+        fusion.fuse_dataset(frames, counter=counter)
+        assert int(counter.item()) > 100 and fusion._stamp == 3
+    else:
+        for datum in frames:
+            fusion.fuse_frame(datum)
     assert grid.engine.backend.status() == 0
     keys, idx = grid.engine.items()
     rkeys, ridx = ref.map.items()

@@ -57,6 +57,10 @@ _lib.ashb_tsdf_touch.argtypes = [_vp, _vp, _int, _int, _vp, _vp, _f32, _c.c_doub
                                  _c.c_uint32, _vp, _vp, _vp]
 _lib.ashb_tsdf_integrate.argtypes = [_vp, _i64, _int, _i64, _vp, _vp, _c.c_uint32, _vp, _vp, _int, _int, _vp, _vp,
                                      _f32, _c.c_double, _vp, _f32, _int, _int, _int, _vp, _vp, _vp, _vp]
+_lib.ashb_tsdf_fuse_frame.argtypes = [_vp, _vp, _i64, _int, _i64, _vp, _vp, _int, _int, _vp, _vp, _vp, _f32, _c.c_double, _vp,
+                                      _int, _vp, _vp, _f32, _int, _int, _int, _vp, _vp, _c.c_uint32, _vp, _vp, _vp, _vp]
+_lib.ashb_tsdf_fuse_frames.argtypes = [_vp, _vp, _i64, _int, _i64, _int, _vp, _vp, _int, _int, _vp, _vp, _vp, _f32, _c.c_double,
+                                       _vp, _int, _vp, _vp, _f32, _int, _int, _int, _vp, _vp, _c.c_uint32, _vp, _vp, _vp, _vp]
 _lib.ashb_tsdf_fuse_frame_static.argtypes = [_vp, _vp, _i64, _int, _i64, _vp, _vp, _int, _int, _vp, _vp, _vp, _f32, _c.c_double,
                                              _vp, _int, _vp, _vp, _f32, _int, _int, _int, _vp]
 _lib.ashb_grid_build_neighbor_lut.argtypes = [_vp, _vp, _vp, _i64, _vp]
@@ -577,6 +581,59 @@ def tsdf_integrate(embeddings, grid_dim, grid_coords, touched, stamp, depth, col
             counter.data_ptr() if counter is not None else None,
             touched_list.data_ptr() if touched_list is not None else None,
             touched_count.data_ptr() if touched_count is not None else None, _stream(emb.device)))
+
+
+def tsdf_fuse_frame(hashmap, embeddings, grid_dim, depth, color, K9, E12, Ei12, depth_max, cell_size, origin3, dilation,
+                    trunc, grid_coords, touched, stamp, touched_list, touched_count, lo3=None, hi3=None, counter=None,
+                    sdf_channel=0, rgb_channel=1, weight_channel=4):
+    """``tsdf_touch`` + ``tsdf_integrate`` as ONE native call.  The camera arrays are prepared by the
+    caller as C float arrays (``K9`` intrinsic row major, ``E12`` / ``Ei12`` the top three rows of world ->
+    camera and camera -> world, ``origin3``; ``lo3`` / ``hi3`` C int32[3] or None), so a frame costs
+    one foreign call and no conversions here.  ``depth`` (H, W), ``color`` (H, W, 3): contiguous
+    float32 CUDA tensors."""
+    emb = embeddings
+    H, W = depth.shape
+    if not (emb.is_cuda and emb.dtype == torch.float32 and emb.is_contiguous() and emb.dim() == 3):
+        raise RuntimeError("embeddings must be a contiguous float32 CUDA tensor (blocks, cells, channels)")
+    if not (depth.is_cuda and depth.dtype == torch.float32 and depth.is_contiguous() and color.is_cuda
+            and color.dtype == torch.float32 and color.is_contiguous() and color.shape == (H, W, 3)):
+        raise RuntimeError("depth (H, W) and color (H, W, 3) must be contiguous float32 CUDA tensors")
+    _check(_lib.ashb_tsdf_fuse_frame(
+        hashmap._h, emb.data_ptr(), emb.shape[0], int(grid_dim), emb.shape[2], depth.data_ptr(), color.data_ptr(), H, W,
+        K9, E12, Ei12, float(depth_max), float(cell_size), origin3, int(dilation), lo3, hi3, float(trunc),
+        int(sdf_channel), int(rgb_channel), int(weight_channel), grid_coords.data_ptr(), touched.data_ptr(), int(stamp),
+        touched_list.data_ptr(), touched_count.data_ptr(), counter.data_ptr() if counter is not None else None,
+        _stream(emb.device)))
+
+
+def tsdf_fuse_frames(hashmap, embeddings, grid_dim, depths, colors, K, E, Ei, depth_max, cell_size, origin3, dilation,
+                     trunc, grid_coords, touched, first_stamp, touched_list, touched_count, lo3=None, hi3=None,
+                     counter=None, sdf_channel=0, rgb_channel=1, weight_channel=4):
+    """A sequence of equally sized frames in ONE native call: ``depths`` / ``colors`` lists of contiguous
+    float32 CUDA tensors (H, W) / (H, W, 3); ``K`` (n, 3, 3), ``E`` and ``Ei`` (n, >=3, 4) float64 numpy arrays
+    (intrinsics, world -> camera, camera -> world)."""
+    import numpy as np
+
+    n = len(depths)
+    if n == 0:
+        return
+    emb = embeddings
+    H, W = depths[0].shape
+    for d, c in zip(depths, colors):
+        if not (d.is_cuda and d.dtype == torch.float32 and d.is_contiguous() and d.shape == (H, W) and c.is_cuda
+                and c.dtype == torch.float32 and c.is_contiguous() and c.shape == (H, W, 3)):
+            raise RuntimeError("every depth (H, W) / color (H, W, 3) must be a contiguous float32 CUDA tensor of one size")
+    dp = (_vp * n)(*[d.data_ptr() for d in depths])
+    cp = (_vp * n)(*[c.data_ptr() for c in colors])
+    k = np.ascontiguousarray(np.asarray(K, np.float64).reshape(n, 9), dtype=np.float32)
+    e = np.ascontiguousarray(np.asarray(E, np.float64)[:, :3, :].reshape(n, 12), dtype=np.float32)
+    ei = np.ascontiguousarray(np.asarray(Ei, np.float64)[:, :3, :].reshape(n, 12), dtype=np.float32)
+    _check(_lib.ashb_tsdf_fuse_frames(
+        hashmap._h, emb.data_ptr(), emb.shape[0], int(grid_dim), emb.shape[2], n, dp, cp, H, W, k.ctypes.data,
+        e.ctypes.data, ei.ctypes.data, float(depth_max), float(cell_size), origin3, int(dilation), lo3, hi3, float(trunc),
+        int(sdf_channel), int(rgb_channel), int(weight_channel), grid_coords.data_ptr(), touched.data_ptr(),
+        int(first_stamp), touched_list.data_ptr(), touched_count.data_ptr(),
+        counter.data_ptr() if counter is not None else None, _stream(emb.device)))
 
 
 def tsdf_fuse_frame_static(hashmap, embeddings, grid_dim, depth, color, intrinsic, world_to_cam, cam_to_world,

@@ -108,11 +108,20 @@ class ASHEngine(nn.Module):
         self._size_bound += n_new
         if self._size_bound <= self.capacity:
             return
-        st = self.backend.status()
+        self._report_status(f"Insertion of {n_new} keys")
         self._size_bound = self.backend.size()
+
+    def _report_status(self, what: str) -> None:
+        """Read and clear the native status word: capacity exhausted -> the reference's warning
+        (ash/core.py:206-211); a probe or wait that gave up (the key was NOT stored) -> error.  Called
+        where the host synchronises with the device anyway (a batch that could overflow, size(),
+        items(), state_dict()), so that no such bit stays unseen."""
+        if not hasattr(self.backend, "status"):
+            return
+        st = self.backend.status()
         if st & backend.STATUS_CAPACITY:
             warnings.warn(
-                f"Insertion of {n_new} keys exceeds the hash map capacity {self.capacity}; the keys beyond "
+                f"{what} exceeds the hash map capacity {self.capacity}; the keys beyond "
                 "capacity were dropped. Please resize the hash map or the behavior could be unexpected."
             )
         if st & ~backend.STATUS_CAPACITY:
@@ -167,6 +176,7 @@ class ASHEngine(nn.Module):
 
     def size(self) -> int:
         self._size_bound = self.backend.size()
+        self._report_status("An earlier insertion")
         return self._size_bound
 
     def resize(self, capacity: int, old_external_values: Dict[str, torch.Tensor] = None,
@@ -212,6 +222,7 @@ class ASHEngine(nn.Module):
 
     def items(self) -> Tuple[torch.Tensor, torch.Tensor]:
         """(active_keys int32 (n, dim), active_indices int64 (n,)), order unspecified."""
+        self._report_status("An earlier insertion")
         return self.backend.items()
 
     # ------------------------------------------------------------------ device moves

@@ -467,10 +467,10 @@ class ShardedSparseDenseGrid(UnBoundedSparseDenseGrid):
         self._grad_shard.zero_()
 
 
-def coarse_owner_of(block_coords: torch.Tensor, world_size: int, coarse_shift: int = 2) -> torch.Tensor:
+def coarse_owner_of(block_coords: torch.Tensor, world_size: int, coarse_shift: int = 3) -> torch.Tensor:
     """Owner rank per BLOCK for ``RoutedSparseDenseGrid``: ``owner_of`` applied to the block
-    coordinate shifted right by ``coarse_shift`` bits per axis, so the 4 x 4 x 4 blocks of one coarse
-    cell -- and with them most +x/+y/+z neighbours of a block -- live on one rank."""
+    coordinate shifted right by ``coarse_shift`` bits per axis, so the 8 x 8 x 8 blocks of one coarse
+    cell -- and with them 7 of 8 +x/+y/+z neighbours of a block -- live on one rank."""
     return owner_of(torch.bitwise_right_shift(block_coords.to(torch.int64), coarse_shift).to(torch.int32), world_size)
 
 
@@ -527,6 +527,7 @@ class _RoutedGridQuery(torch.autograd.Function):
         where = box.where[:ctx.n]             # still this batch's: one batch is in flight at a time
         need_grad_x = bool(ctx.needs_input_grad[1])
         backend.routed_send_z(where, z.contiguous(), box.layout)
+        grid._wait_for_zero_fill()            # this shard is clear before any rank may add to it
         grid._barrier()                       # every owner has the incoming gradients of its records
         backend.routed_backward(grid.engine.backend, grid._emb_bases, grid._grad_bases, ctx.geom, box.layout,
                                 ctx.interpolation, need_grad_x)
@@ -574,6 +575,8 @@ class RoutedSparseDenseGrid(UnBoundedSparseDenseGrid):
         self._mailbox = _RoutedMailbox(self.world, self.rank, cap, max_batch, embedding_dim, self.device, group)
         self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._row_of = None
+        self._side_stream = None
+        self._zero_done = None
         self.fused = True
 
     def _allocate_embeddings(self) -> torch.Tensor:
@@ -612,6 +615,7 @@ class RoutedSparseDenseGrid(UnBoundedSparseDenseGrid):
         row_of[idx] = (owner << 26) | local
         self._row_of = row_of.to(torch.int32)          # bit pattern of the uint32 the kernels read (owner < 32)
         self._owned_blocks = idx[owner == self.rank]   # global block indices of this shard's rows, in row order
+        self._n_owned = int(self._owned_blocks.numel())
 
     def owned_blocks(self) -> torch.Tensor:
         """Global block indices of this rank's shard rows 0 .. n_owned - 1."""
@@ -633,4 +637,20 @@ class RoutedSparseDenseGrid(UnBoundedSparseDenseGrid):
 
     @torch.no_grad()
     def zero_grad_shard_(self) -> None:
-        self._grad_shard.zero_()
+        """Clear the gradient rows of the blocks this rank owns (the rest of the shard is never written).
+        The fill runs on a side stream, ordered after everything enqueued so far, and overlaps the
+        forward pass; the backward pass waits for it before any rank may add to this shard."""
+        n = getattr(self, "_n_owned", self._grad_shard.shape[0])
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream(self.device)
+        self._side_stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(self._side_stream):
+            self._grad_shard[:n].zero_()
+            self._zero_done = torch.cuda.Event()
+            self._zero_done.record(self._side_stream)
+
+    def _wait_for_zero_fill(self) -> None:
+        """Order the current stream after the pending gradient zero-fill, if any."""
+        if self._zero_done is not None:
+            torch.cuda.current_stream(self.device).wait_event(self._zero_done)
+            self._zero_done = None

@@ -42,6 +42,7 @@ class TSDFFusion:
         self._list = torch.zeros(grid.num_embeddings, dtype=torch.int32, device=dev)  # blocks touched by the frame
         self._count = torch.zeros(1, dtype=torch.int32, device=dev)
         self._stamp = 0
+        self._c_frame = None   # origin / bounds as C arrays, built on first use
         if isinstance(grid, BoundedSparseDenseGrid):
             self._origin = [float(v) for v in grid.bbox_min.tolist()]
             self._bounds = ([0, 0, 0], [grid.sparse_grid_dim] * 3)
@@ -62,6 +63,24 @@ class TSDFFusion:
         Ei = np.linalg.inv(E)
         self._stamp = self._stamp % 0x7FFFFFFF + 1
         g = self.grid
+        if hasattr(backend, "tsdf_fuse_frame") and depth.is_cuda:
+            # one foreign call per frame: both launches, camera matrices passed as C arrays
+            import ctypes
+
+            f32 = ctypes.c_float
+            color = datum.rgb
+            if depth.dtype != torch.float32 or not depth.is_contiguous():
+                depth = depth.float().contiguous()
+            if color.dtype != torch.float32 or not color.is_contiguous():
+                color = color.float().contiguous()
+            org, lo3, hi3 = self._c_frame_arrays()
+            backend.tsdf_fuse_frame(
+                g.engine.backend, g.embeddings.data, g.grid_dim, depth, color, (f32 * 9)(*K.reshape(-1)[:9]),
+                (f32 * 12)(*E.reshape(-1)[:12]), (f32 * 12)(*Ei.reshape(-1)[:12]), datum.depth_max, g.cell_size, org,
+                self.dilation, self.trunc, self._coords, self._touched, self._stamp, self._list, self._count, lo3, hi3,
+                counter)
+            g.engine._size_bound = g.engine.capacity
+            return
         backend.tsdf_touch(
             g.engine.backend, depth, K, Ei, datum.depth_max, g.cell_size, self._origin, g.grid_dim, self.dilation,
             self._coords, self._touched, self._stamp, *self._bounds, touched_list=self._list,
@@ -73,10 +92,44 @@ class TSDFFusion:
         # the engine's host-side size bound is stale after native insertions
         g.engine._size_bound = g.engine.capacity
 
+    def _c_frame_arrays(self):
+        import ctypes
+
+        if self._c_frame is None:
+            lo, hi = self._bounds
+            f32, i32 = ctypes.c_float, ctypes.c_int32
+            self._c_frame = ((f32 * 3)(*self._origin), (i32 * 3)(*lo) if lo is not None else None,
+                             (i32 * 3)(*hi) if hi is not None else None)
+        return self._c_frame
+
     @torch.no_grad()
-    def fuse_dataset(self, frames) -> None:
-        for datum in frames:
-            self.fuse_frame(datum)
+    def fuse_dataset(self, frames, counter=None) -> None:
+        """Fuse a sequence of frames (demo/rgbd_fusion.py:256-262).  Frames of one size and depth_max on the
+        GPU go to the library as ONE call that enqueues both launches of every frame back to back."""
+        frames = list(frames)
+        g = self.grid
+        same = (len(frames) > 1 and hasattr(backend, "tsdf_fuse_frames") and all(
+            f.depth.is_cuda and f.depth.shape == frames[0].depth.shape and f.depth_max == frames[0].depth_max
+            for f in frames) and self._stamp + len(frames) < 0x7FFFFFFF)
+        if not same:
+            for datum in frames:
+                self.fuse_frame(datum, counter=counter)
+            return
+        depths, colors = [], []
+        for f in frames:
+            f.depth *= f.depth_scale
+            depths.append(f.depth if f.depth.dtype == torch.float32 and f.depth.is_contiguous() else f.depth.float().contiguous())
+            colors.append(f.rgb if f.rgb.dtype == torch.float32 and f.rgb.is_contiguous() else f.rgb.float().contiguous())
+        K = np.stack([_host_matrix(f.intrinsic) for f in frames])
+        E = np.stack([_host_matrix(f.extrinsic) for f in frames])
+        Ei = np.linalg.inv(E)
+        org, lo3, hi3 = self._c_frame_arrays()
+        backend.tsdf_fuse_frames(
+            g.engine.backend, g.embeddings.data, g.grid_dim, depths, colors, K, E, Ei, frames[0].depth_max, g.cell_size,
+            org, self.dilation, self.trunc, self._coords, self._touched, self._stamp + 1, self._list, self._count, lo3,
+            hi3, counter)
+        self._stamp += len(frames)
+        g.engine._size_bound = g.engine.capacity
 
     @torch.no_grad()
     def prune_by_weight_(self, grid_mean_weight_thr: float = 1) -> int:

@@ -333,6 +333,13 @@ __device__ __forceinline__ int lookup(const Table& t, int k0, int k1, int k2, in
     return -1;
 }
 
+// The same for 16-byte-slot tables that are far larger than L2: the occupancy bit of the home slot
+// is read first, and a key whose home slot never held anything is reported absent without a probe.
+__device__ __forceinline__ int lookup_filtered(const Table16& t, int k0, int k1, int k2) {
+    if (t.occupied != nullptr && t.never_used(hash_key(k0, k1, k2, 0) & t.mask)) return -1;
+    return lookup(t, k0, k1, k2, 0);
+}
+
 }  // namespace ashb
 
 // The host-side map object behind the opaque `ashb_map*` of the C ABI.

@@ -93,14 +93,14 @@ __global__ void peer_publish_counts_kernel(PeerLayout L, const int* __restrict__
     counts[L.rank] = (int)(c < L.region_capacity ? c : L.region_capacity);
 }
 
-__global__ void __launch_bounds__(256) peer_answer_kernel(Table16 t, PeerLayout L) {
+__global__ void __launch_bounds__(256) peer_answer_kernel(Table16 t, PeerLayout L, bool filter) {
     const int region = blockIdx.y;  // the rank that asked
     const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const char* mine = static_cast<const char*>(L.bases[L.rank]);
     const int count = __ldcg(reinterpret_cast<const int*>(mine + L.counts_offset) + region);
     if (j >= count || j >= L.region_capacity) return;
     const int4 rec = __ldcg(reinterpret_cast<const int4*>(mine + L.inbox_offset) + (int64_t)region * L.region_capacity + j);
-    const int idx = lookup(t, rec.x, rec.y, rec.z, 0);
+    const int idx = filter ? lookup_filtered(t, rec.x, rec.y, rec.z) : lookup(t, rec.x, rec.y, rec.z, 0);
     const long long answer = idx >= 0 ? (long long)idx * L.world + L.rank : -1ll;
     long long* answers = reinterpret_cast<long long*>(static_cast<char*>(L.bases[region]) + L.answers_offset);
     answers[(int64_t)L.rank * L.region_capacity + j] = answer;   // my region of the asker's answers
@@ -207,7 +207,9 @@ int ashb_peer_find_answer(ashb_map* m, int world, int rank, void* const* peer_ba
     DeviceGuard guard(m->device);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const dim3 grid((unsigned)((region_capacity + 255) / 256), (unsigned)world);
-    peer_answer_kernel<<<grid, 256, 0, st>>>(table16_of(m), L);
+    // as in ashb_map_find: the occupancy filter pays off for tables that do not stay in L2
+    const bool filter = m->occupied != nullptr && m->n_slots * m->slot_bytes >= ((size_t)64 << 20);
+    peer_answer_kernel<<<grid, 256, 0, st>>>(table16_of(m), L, filter);
     ASHB_LAUNCH_CHECK();
     return ASHB_OK;
 }

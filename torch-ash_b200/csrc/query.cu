@@ -454,11 +454,11 @@ __global__ void __launch_bounds__(256, ASHB_BWD_MIN_BLOCKS) query_backward_backw
 // SECOND = false: first-order pass (rows = w_c * z, d/d offset as in query_backward_forward_kernel);
 // SECOND = true: double backward (rows = (grad w_c . ggo) * z, grad_z as in
 // query_backward_backward_kernel; `side` is grad_z [n][D], `ggo` the incoming gradient).
-#ifndef ASHB_ROWS_MIN_BLOCKS
-#define ASHB_ROWS_MIN_BLOCKS 3
-#endif
+// Resident CTAs per SM each variant is built for (register budget): the double backward holds 8 rows
+// and 8 products at once and runs best with room (2), the first-order pass with d/dx at 3, the
+// write-only pass without the row reads at 4.
 template <typename T, int VEC, bool SECOND, bool NEED_GO>
-__global__ void __launch_bounds__(256, ASHB_ROWS_MIN_BLOCKS) query_backward_rows_kernel(
+__global__ void __launch_bounds__(256, SECOND ? 2 : (NEED_GO ? 3 : 4)) query_backward_rows_kernel(
         const T* __restrict__ z, const T* __restrict__ emb, FusedSource src, const T* __restrict__ ggo,
         int64_t* __restrict__ idx_out, T* __restrict__ rows_out, T* __restrict__ side, T go_scale, int64_t n, int D,
         int lane_shift, int interp) {

@@ -8,7 +8,7 @@
 // Sending the position to the rank that holds the block and letting that rank gather, interpolate
 // and scatter in its OWN memory moves 16 + 4 D (+ 4 D + 16 in the backward pass) bytes per query
 // over NVLink instead of ~64 D.  Blocks are assigned to ranks by a hash of their coarse
-// coordinate (block >> 2 per axis), so a block and its +x/+y/+z neighbours mostly share an owner;
+// coordinate (block >> 3 per axis), so a block and its +x/+y/+z neighbours mostly share an owner;
 // the few corner rows that do not are read from, and reduced into, the neighbour's owner directly
 // (plain peer loads and `red.global.add` over NVLink).
 //
@@ -175,7 +175,7 @@ __device__ __forceinline__ bool routed_record(const RoutedLayout& L, int region,
 
 // ---- owner: forward -----------------------------------------------------------------------------
 template <int VEC>
-__global__ void __launch_bounds__(256) routed_forward_kernel(RoutedGrid g, RoutedLayout L, int D, int lane_shift,
+__global__ void __launch_bounds__(256, 5) routed_forward_kernel(RoutedGrid g, RoutedLayout L, int D, int lane_shift,
                                                              int interp) {
     const int region = blockIdx.y;   // the rank that asked
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -272,7 +272,7 @@ __global__ void __launch_bounds__(256) routed_unpack_gx_kernel(RoutedLayout L, c
 
 // ---- owner: backward ----------------------------------------------------------------------------
 template <int VEC, bool NEED_GO>
-__global__ void __launch_bounds__(256) routed_backward_kernel(RoutedGrid g, RoutedLayout L, float go_scale, int D,
+__global__ void __launch_bounds__(256, 3) routed_backward_kernel(RoutedGrid g, RoutedLayout L, float go_scale, int D,
                                                               int lane_shift, int interp) {
     const int region = blockIdx.y;
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;

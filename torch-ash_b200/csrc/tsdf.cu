@@ -92,6 +92,9 @@ __device__ __forceinline__ void touch_block(const Table16& t, const TouchTarget&
         idx = tt.heap[top];
         *reinterpret_cast<volatile int*>(t.val_ptr((uint32_t)slot)) = idx;
     }
+    // many pixels of a frame fall in the same few thousand blocks: whoever finds the block already
+    // stamped by this call has nothing left to do (the first toucher recorded it)
+    if (__ldcg(&tt.touched[idx]) == tt.stamp) return;
     // the coordinate is recorded for blocks allocated by other means too
     tt.grid_coords[3 * idx] = kx;
     tt.grid_coords[3 * idx + 1] = ky;
@@ -420,6 +423,43 @@ static int static_scratch_for_current_device(unsigned char** out) {
         cached[dev] = static_cast<unsigned char*>(p);
     }
     *out = cached[dev];
+    return ASHB_OK;
+}
+
+int ashb_tsdf_fuse_frame(ashb_map* m, void* embeddings, int64_t n_emb, int G, int64_t D, const float* depth,
+                         const float* color, int H, int W, const float* intrinsic, const float* world_to_cam,
+                         const float* cam_to_world, float depth_max, double cell_size, const float* origin,
+                         int dilation, const int32_t* bound_lo, const int32_t* bound_hi, float trunc, int sdf_channel,
+                         int rgb_channel, int weight_channel, int32_t* grid_coords, uint32_t* touched, uint32_t stamp,
+                         int32_t* touched_list, int32_t* touched_count, unsigned long long* n_integrated_dev,
+                         void* stream) {
+    if (int rc = ashb_tsdf_touch(m, depth, H, W, intrinsic, cam_to_world, depth_max, cell_size, origin, G, dilation,
+                                 bound_lo, bound_hi, grid_coords, touched, stamp, touched_list, touched_count, stream))
+        return rc;
+    DeviceGuard guard(m->device);
+    return ashb_tsdf_integrate(embeddings, n_emb, G, D, grid_coords, touched, stamp, depth, color, H, W, intrinsic,
+                               world_to_cam, depth_max, cell_size, origin, trunc, sdf_channel, rgb_channel,
+                               weight_channel, n_integrated_dev, touched_list, touched_count, stream);
+}
+
+int ashb_tsdf_fuse_frames(ashb_map* m, void* embeddings, int64_t n_emb, int G, int64_t D, int n_frames,
+                          const float* const* depths, const float* const* colors, int H, int W,
+                          const float* intrinsics, const float* world_to_cams, const float* cam_to_worlds,
+                          float depth_max, double cell_size, const float* origin, int dilation, const int32_t* bound_lo,
+                          const int32_t* bound_hi, float trunc, int sdf_channel, int rgb_channel, int weight_channel,
+                          int32_t* grid_coords, uint32_t* touched, uint32_t first_stamp, int32_t* touched_list,
+                          int32_t* touched_count, unsigned long long* n_integrated_dev, void* stream) {
+    ASHB_REQUIRE(n_frames >= 0 && (n_frames == 0 || (depths && colors && intrinsics && world_to_cams && cam_to_worlds)),
+                 "null frame tables");
+    ASHB_REQUIRE((uint64_t)first_stamp + (uint64_t)n_frames <= 0x7FFFFFFFull && first_stamp != 0, "stamps would wrap");
+    for (int f = 0; f < n_frames; ++f) {
+        if (int rc = ashb_tsdf_fuse_frame(m, embeddings, n_emb, G, D, depths[f], colors[f], H, W, intrinsics + 9 * f,
+                                          world_to_cams + 12 * f, cam_to_worlds + 12 * f, depth_max, cell_size, origin,
+                                          dilation, bound_lo, bound_hi, trunc, sdf_channel, rgb_channel, weight_channel,
+                                          grid_coords, touched, first_stamp + (uint32_t)f, touched_list, touched_count,
+                                          n_integrated_dev, stream))
+            return rc;
+    }
     return ASHB_OK;
 }
 
