@@ -1315,11 +1315,13 @@ def main():
             "what": "16-byte reads at random 64-byte-aligned places of the 16.4 GB table, one per thread, L2 fetch size "
                     "64 or 128 bytes: the rate at which this GPU's memory serves scattered accesses",
             "G_reads_per_s_fetch64": round(random_reads[64], 2), "G_reads_per_s_fetch128": round(random_reads[128], 2),
-            "forward_frac": round(N_QUERIES * 5 / (f_ms * 1e-3) / 1e9 / random_reads[128], 4),
-            "backward_frac": round(N_QUERIES * 13 / (bp_ms * 1e-3) / 1e9 / random_reads[128], 4),
-            "note": "scattered accesses per query: forward 1 slot + 4 x-adjacent row pairs (128 B each) = 5; backward "
-                    "1 slot + 4 row pairs + 4 gradient row pairs read and written back = 13; frac = accesses/s over "
-                    "the measured random-read rate"}
+            "forward_frac": round(N_QUERIES * 6 / (f_ms * 1e-3) / 1e9 / random_reads[128], 4),
+            "backward_frac": round(N_QUERIES * 12 / (bp_ms * 1e-3) / 1e9 / random_reads[128], 4),
+            "note": "scattered 128-byte lines per query: forward 4 x-adjacent row pairs, each 1 line when the first "
+                    "cell's x is even and 2 otherwise = 6 (the block's slot and neighbour row come from L2); dense "
+                    "backward 6 table lines + 6 gradient lines read (and written back, not counted) = 12; frac = "
+                    "lines/s over the measured random-read rate, which does not change with the bytes per access nor "
+                    "with the number of reads in flight per thread (profiles/hash_kernels_8M_keys.md)"}
         if allreduce_ms is not None:
             line["grad_allreduce_ms"] = round(allreduce_ms, 3)
 

@@ -407,14 +407,19 @@ int ashb_tsdf_fuse_frame(ashb_map* map, void* embeddings, int64_t n_emb, int G, 
 /* A sequence of frames of one size in one call (TSDFFusion.fuse_dataset, demo/rgbd_fusion.py:256-262): the two
  * launches of every frame are enqueued back to back from native code, so the sequence is not limited by the
  * caller's per-frame host work.  depths / colors: HOST arrays of n_frames device pointers; intrinsics
- * [n_frames][9], world_to_cams and cam_to_worlds [n_frames][12]: host floats; frame f uses stamp first_stamp + f. */
+ * [n_frames][9], world_to_cams and cam_to_worlds [n_frames][12]: host floats; frame f uses stamp first_stamp + f.
+ * With double_buffered != 0 (touched_list int32 [2][n_emb], touched_count int32 [2]) the allocation pass of frame
+ * f + 1 runs on an internal side stream while frame f is fused on `stream` (events order the two; `stream` ends
+ * ordered after all of it); the first such call on a device creates that stream and should come outside stream
+ * capture. */
 int ashb_tsdf_fuse_frames(ashb_map* map, void* embeddings, int64_t n_emb, int G, int64_t D, int n_frames,
                           const float* const* depths, const float* const* colors, int H, int W,
                           const float* intrinsics, const float* world_to_cams, const float* cam_to_worlds,
                           float depth_max, double cell_size, const float* origin, int dilation, const int32_t* bound_lo,
                           const int32_t* bound_hi, float trunc, int sdf_channel, int rgb_channel, int weight_channel,
                           int32_t* grid_coords, uint32_t* touched, uint32_t first_stamp, int32_t* touched_list,
-                          int32_t* touched_count, unsigned long long* n_integrated_dev, void* stream);
+                          int32_t* touched_count, int double_buffered, unsigned long long* n_integrated_dev,
+                          void* stream);
 
 /* One whole fusion step (allocation + fusion, as the two calls above) that allocates nothing.
  * It has no counterpart in the reference.  It exists for callers that must not allocate device

@@ -333,3 +333,47 @@ def routed_grid_worker(rank, world, port):
             del routed, ref
     finally:
         dist.destroy_process_group()
+
+
+def row_table_worker(rank, world, port):
+    """Host logic of the routed grid on CPU: after broadcast_state every rank derives the SAME block ->
+    (owner, shard row) table; every active block has exactly one owner and a row of its own there; the
+    blocks of a coarse cell share an owner, so most +x/+y/+z neighbours of a block are co-owned."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import bench_workloads as bw
+        from ash import ASHEngine
+        from ash.distributed import block_row_table, broadcast_state, coarse_owner_of
+
+        cpu = torch.device("cpu")
+        n_blocks, cap = 3000, 3500
+        blocks = bw.block_coords_blob(n_blocks, cpu, n_blobs=3, seed=11)
+        eng = ASHEngine(3, cap, cpu)
+        eng.insert_keys(blocks[torch.randperm(n_blocks, generator=torch.Generator().manual_seed(rank))])  # own order per rank
+        broadcast_state(eng, src=0)
+        coords, idx = eng.items()
+        rows_per_rank = int(-(-cap // world) * 1.25) + 64
+        row_of, per_owner = block_row_table(coords, idx, world, cap, rows_per_rank)
+        gathered = [torch.empty_like(row_of) for _ in range(world)]
+        dist.all_gather(gathered, row_of)
+        assert all(torch.equal(g, gathered[0]) for g in gathered)
+        assert int(per_owner.sum()) == n_blocks and int(per_owner.min()) > 0
+        owner, local = row_of[idx] >> 26, row_of[idx] & ((1 << 26) - 1)
+        assert torch.equal(owner, coarse_owner_of(coords, world))
+        for o in range(world):
+            rows = torch.sort(local[owner == o])[0]
+            assert torch.equal(rows, torch.arange(int(per_owner[o])))      # a shard's rows are 0 .. count-1, each used once
+        # co-ownership of +x neighbours
+        find_idx, ok = eng.find((coords + torch.tensor([1, 0, 0], dtype=torch.int32)).contiguous())
+        same = (row_of[find_idx[ok]] >> 26) == owner[ok]
+        assert float(same.float().mean()) > 0.8
+        with_error = False
+        try:
+            block_row_table(coords, idx, world, cap, 10)
+        except RuntimeError:
+            with_error = True
+        assert with_error, "a shard too small for its owner's blocks must be refused"
+    finally:
+        dist.destroy_process_group()

@@ -24,3 +24,8 @@ def test_partitioned_hash_map_gloo(world):
 
 def test_replicated_grid_gradient_sum_gloo():
     mp.spawn(dist_workers.replicated_grid_worker, args=(2, _free_port(), "gloo", False), nprocs=2, join=True)
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_routed_grid_ownership_table_gloo(world):
+    mp.spawn(dist_workers.row_table_worker, args=(world, _free_port()), nprocs=world, join=True)

@@ -60,7 +60,7 @@ _lib.ashb_tsdf_integrate.argtypes = [_vp, _i64, _int, _i64, _vp, _vp, _c.c_uint3
 _lib.ashb_tsdf_fuse_frame.argtypes = [_vp, _vp, _i64, _int, _i64, _vp, _vp, _int, _int, _vp, _vp, _vp, _f32, _c.c_double, _vp,
                                       _int, _vp, _vp, _f32, _int, _int, _int, _vp, _vp, _c.c_uint32, _vp, _vp, _vp, _vp]
 _lib.ashb_tsdf_fuse_frames.argtypes = [_vp, _vp, _i64, _int, _i64, _int, _vp, _vp, _int, _int, _vp, _vp, _vp, _f32, _c.c_double,
-                                       _vp, _int, _vp, _vp, _f32, _int, _int, _int, _vp, _vp, _c.c_uint32, _vp, _vp, _vp, _vp]
+                                       _vp, _int, _vp, _vp, _f32, _int, _int, _int, _vp, _vp, _c.c_uint32, _vp, _vp, _int, _vp, _vp]
 _lib.ashb_tsdf_fuse_frame_static.argtypes = [_vp, _vp, _i64, _int, _i64, _vp, _vp, _int, _int, _vp, _vp, _vp, _f32, _c.c_double,
                                              _vp, _int, _vp, _vp, _f32, _int, _int, _int, _vp]
 _lib.ashb_grid_build_neighbor_lut.argtypes = [_vp, _vp, _vp, _i64, _vp]
@@ -611,7 +611,9 @@ def tsdf_fuse_frames(hashmap, embeddings, grid_dim, depths, colors, K, E, Ei, de
                      counter=None, sdf_channel=0, rgb_channel=1, weight_channel=4):
     """A sequence of equally sized frames in ONE native call: ``depths`` / ``colors`` lists of contiguous
     float32 CUDA tensors (H, W) / (H, W, 3); ``K`` (n, 3, 3), ``E`` and ``Ei`` (n, >=3, 4) float64 numpy arrays
-    (intrinsics, world -> camera, camera -> world)."""
+    (intrinsics, world -> camera, camera -> world).  When ``touched_list`` holds two lists (2 x num_embeddings
+    entries) and ``touched_count`` two counters, the allocation pass of every frame overlaps the fusion of
+    the frame before it."""
     import numpy as np
 
     n = len(depths)
@@ -633,6 +635,7 @@ def tsdf_fuse_frames(hashmap, embeddings, grid_dim, depths, colors, K, E, Ei, de
         e.ctypes.data, ei.ctypes.data, float(depth_max), float(cell_size), origin3, int(dilation), lo3, hi3, float(trunc),
         int(sdf_channel), int(rgb_channel), int(weight_channel), grid_coords.data_ptr(), touched.data_ptr(),
         int(first_stamp), touched_list.data_ptr(), touched_count.data_ptr(),
+        int(touched_list.numel() >= 2 * emb.shape[0] and touched_count.numel() >= 2),
         counter.data_ptr() if counter is not None else None, _stream(emb.device)))
 
 

@@ -474,6 +474,27 @@ def coarse_owner_of(block_coords: torch.Tensor, world_size: int, coarse_shift: i
     return owner_of(torch.bitwise_right_shift(block_coords.to(torch.int64), coarse_shift).to(torch.int32), world_size)
 
 
+def block_row_table(coords: torch.Tensor, indices: torch.Tensor, world_size: int, num_embeddings: int,
+                    rows_per_rank: int):
+    """Which rank owns which block and where: from the active blocks' coordinates and indices (the same
+    on every rank after ``broadcast_state``) returns ``(row_of int64 (num_embeddings,), per_owner int64
+    (world,))`` with ``row_of[index] = owner << 26 | row in the owner's shard`` (0 for inactive indices)
+    and the number of blocks per owner.  Rows are handed out in ascending index order, so every rank
+    derives the same table."""
+    owner = coarse_owner_of(coords, world_size)
+    order = torch.argsort(indices)
+    indices, owner = indices[order], owner[order]
+    one_hot = torch.nn.functional.one_hot(owner, world_size)
+    local = (torch.cumsum(one_hot, dim=0) - one_hot).gather(1, owner.view(-1, 1)).view(-1)   # rank among its owner's blocks
+    per_owner = one_hot.sum(dim=0)
+    if indices.numel() and int(per_owner.max()) > rows_per_rank:
+        raise RuntimeError(f"an owner holds {int(per_owner.max())} blocks but a shard has {rows_per_rank} rows; "
+                           "raise shard_slack")
+    row_of = torch.zeros(num_embeddings, dtype=torch.int64, device=coords.device)
+    row_of[indices] = (owner << 26) | local
+    return row_of, per_owner
+
+
 class _RoutedMailbox:
     """Symmetric device memory of the routed query: per rank an inbox of positions, an inbox of
     incoming gradients, the result rows and the position gradients coming back (``world`` regions of
@@ -602,19 +623,10 @@ class RoutedSparseDenseGrid(UnBoundedSparseDenseGrid):
         broadcast_state(self.engine, src=src, group=self.group)
         self.construct_grid_neighbor_lut_(radius=1, bidirectional=False)
         coords, idx = self.engine.items()
-        owner = coarse_owner_of(coords, self.world)
-        order = torch.argsort(idx)                                  # by block index: the same order on every rank
-        coords, idx, owner = coords[order], idx[order], owner[order]
-        one_hot = torch.nn.functional.one_hot(owner, self.world)
-        local = (torch.cumsum(one_hot, dim=0) - one_hot).gather(1, owner.view(-1, 1)).view(-1)   # rank among its owner's blocks
-        per_owner = one_hot.sum(dim=0)
-        if int(per_owner.max()) > self._rows_per_rank:
-            raise RuntimeError(f"an owner holds {int(per_owner.max())} blocks but a shard has {self._rows_per_rank} rows; "
-                               "raise shard_slack")
-        row_of = torch.zeros(self.num_embeddings, dtype=torch.int64, device=self.device)
-        row_of[idx] = (owner << 26) | local
+        row_of, _ = block_row_table(coords, idx, self.world, self.num_embeddings, self._rows_per_rank)
         self._row_of = row_of.to(torch.int32)          # bit pattern of the uint32 the kernels read (owner < 32)
-        self._owned_blocks = idx[owner == self.rank]   # global block indices of this shard's rows, in row order
+        mine = torch.sort(idx[coarse_owner_of(coords, self.world) == self.rank])[0]
+        self._owned_blocks = mine                      # global block indices of this shard's rows, in row order
         self._n_owned = int(self._owned_blocks.numel())
 
     def owned_blocks(self) -> torch.Tensor:

@@ -43,6 +43,7 @@ class TSDFFusion:
         self._count = torch.zeros(1, dtype=torch.int32, device=dev)
         self._stamp = 0
         self._c_frame = None   # origin / bounds as C arrays, built on first use
+        self._list2 = self._count2 = None
         if isinstance(grid, BoundedSparseDenseGrid):
             self._origin = [float(v) for v in grid.bbox_min.tolist()]
             self._bounds = ([0, 0, 0], [grid.sparse_grid_dim] * 3)
@@ -124,9 +125,12 @@ class TSDFFusion:
         E = np.stack([_host_matrix(f.extrinsic) for f in frames])
         Ei = np.linalg.inv(E)
         org, lo3, hi3 = self._c_frame_arrays()
+        if self._list2 is None:   # two work lists: the allocation of a frame overlaps the fusion of the one before
+            self._list2 = torch.zeros(2 * g.num_embeddings, dtype=torch.int32, device=g.device)
+            self._count2 = torch.zeros(2, dtype=torch.int32, device=g.device)
         backend.tsdf_fuse_frames(
             g.engine.backend, g.embeddings.data, g.grid_dim, depths, colors, K, E, Ei, frames[0].depth_max, g.cell_size,
-            org, self.dilation, self.trunc, self._coords, self._touched, self._stamp + 1, self._list, self._count, lo3,
+            org, self.dilation, self.trunc, self._coords, self._touched, self._stamp + 1, self._list2, self._count2, lo3,
             hi3, counter)
         self._stamp += len(frames)
         g.engine._size_bound = g.engine.capacity

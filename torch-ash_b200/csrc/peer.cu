@@ -93,17 +93,23 @@ __global__ void peer_publish_counts_kernel(PeerLayout L, const int* __restrict__
     counts[L.rank] = (int)(c < L.region_capacity ? c : L.region_capacity);
 }
 
+// A region holds region_capacity records in the worst case (every key of a batch to one owner) and
+// about 1 / world of that usually, so the kernels below do not launch one CTA per 256 possible
+// records: a fixed grid walks the tiles of 256 records of all regions and skips the empty ones.
 __global__ void __launch_bounds__(256) peer_answer_kernel(Table16 t, PeerLayout L, bool filter) {
-    const int region = blockIdx.y;  // the rank that asked
-    const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const char* mine = static_cast<const char*>(L.bases[L.rank]);
-    const int count = __ldcg(reinterpret_cast<const int*>(mine + L.counts_offset) + region);
-    if (j >= count || j >= L.region_capacity) return;
-    const int4 rec = __ldcg(reinterpret_cast<const int4*>(mine + L.inbox_offset) + (int64_t)region * L.region_capacity + j);
-    const int idx = filter ? lookup_filtered(t, rec.x, rec.y, rec.z) : lookup(t, rec.x, rec.y, rec.z, 0);
-    const long long answer = idx >= 0 ? (long long)idx * L.world + L.rank : -1ll;
-    long long* answers = reinterpret_cast<long long*>(static_cast<char*>(L.bases[region]) + L.answers_offset);
-    answers[(int64_t)L.rank * L.region_capacity + j] = answer;   // my region of the asker's answers
+    const int64_t tiles_per_region = (L.region_capacity + 255) / 256;
+    for (int64_t tile = blockIdx.x; tile < tiles_per_region * L.world; tile += gridDim.x) {
+        const int region = (int)(tile / tiles_per_region);  // the rank that asked
+        const int64_t j = (tile - (int64_t)region * tiles_per_region) * 256 + threadIdx.x;
+        const int count = __ldcg(reinterpret_cast<const int*>(mine + L.counts_offset) + region);
+        if (j >= count || j >= L.region_capacity) continue;
+        const int4 rec = __ldcg(reinterpret_cast<const int4*>(mine + L.inbox_offset) + (int64_t)region * L.region_capacity + j);
+        const int idx = filter ? lookup_filtered(t, rec.x, rec.y, rec.z) : lookup(t, rec.x, rec.y, rec.z, 0);
+        const long long answer = idx >= 0 ? (long long)idx * L.world + L.rank : -1ll;
+        long long* answers = reinterpret_cast<long long*>(static_cast<char*>(L.bases[region]) + L.answers_offset);
+        answers[(int64_t)L.rank * L.region_capacity + j] = answer;   // my region of the asker's answers
+    }
 }
 
 // The asker's side: answer of key i = answers[owner(i)][slot(i)] of its own mailbox.
@@ -128,21 +134,27 @@ __global__ void __launch_bounds__(256) peer_unpack_kernel(PeerLayout L, const in
 template <bool ERASE>
 __global__ void __launch_bounds__(256) peer_update_kernel(Table16 t, PeerLayout L, int32_t* __restrict__ heap,
                                                           int32_t* counter, int32_t capacity) {
-    const int region = blockIdx.y;
-    const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const char* mine = static_cast<const char*>(L.bases[L.rank]);
-    const int count = __ldcg(reinterpret_cast<const int*>(mine + L.counts_offset) + region);
-    const bool live = j < count && j < L.region_capacity;
-    int4 rec = make_int4(0, 0, 0, 0);
-    if (live) rec = __ldcg(reinterpret_cast<const int4*>(mine + L.inbox_offset) + (int64_t)region * L.region_capacity + j);
-    // the whole CTA (256 threads) goes through the stack operations below: one atomic per CTA
-    if (ERASE) {
-        push_freed_index_cta(live ? tombstone_key(t, rec.x, rec.y, rec.z, 0) : -1, heap, counter);
-    } else {
-        bool present = false;
-        const int64_t slot = live ? emplace(t, rec.x, rec.y, rec.z, 0, kPending, &present) : -1;
-        const int idx = pop_index_for_slot_cta(t, slot, heap, counter, capacity);
-        if (idx >= 0) publish_index(t, slot, idx);
+    const int64_t tiles_per_region = (L.region_capacity + 255) / 256;
+    for (int64_t tile = blockIdx.x; tile < tiles_per_region * L.world; tile += gridDim.x) {
+        const int region = (int)(tile / tiles_per_region);
+        const int64_t first = (tile - (int64_t)region * tiles_per_region) * 256;
+        const int count = __ldcg(reinterpret_cast<const int*>(mine + L.counts_offset) + region);
+        if (first >= count) continue;   // the same for every thread of the CTA: an empty tile
+        const int64_t j = first + threadIdx.x;
+        const bool live = j < count && j < L.region_capacity;
+        int4 rec = make_int4(0, 0, 0, 0);
+        if (live) rec = __ldcg(reinterpret_cast<const int4*>(mine + L.inbox_offset) + (int64_t)region * L.region_capacity + j);
+        // the whole CTA (256 threads) goes through the stack operations below: one atomic per CTA
+        if (ERASE) {
+            push_freed_index_cta(live ? tombstone_key(t, rec.x, rec.y, rec.z, 0) : -1, heap, counter);
+        } else {
+            bool present = false;
+            const int64_t slot = live ? emplace(t, rec.x, rec.y, rec.z, 0, kPending, &present) : -1;
+            const int idx = pop_index_for_slot_cta(t, slot, heap, counter, capacity);
+            if (idx >= 0) publish_index(t, slot, idx);
+        }
+        __syncthreads();   // the shared words of the CTA-wide stack operations are reused by the next tile
     }
 }
 
@@ -206,7 +218,7 @@ int ashb_peer_find_answer(ashb_map* m, int world, int rank, void* const* peer_ba
     ASHB_REQUIRE(m->key_dim <= 3, "the peer transport carries keys of 1 to 3 columns");
     DeviceGuard guard(m->device);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const dim3 grid((unsigned)((region_capacity + 255) / 256), (unsigned)world);
+    const unsigned grid = wave_grid(((region_capacity + 255) / 256) * 256 * (int64_t)world, 256, 8);
     // as in ashb_map_find: the occupancy filter pays off for tables that do not stay in L2
     const bool filter = m->occupied != nullptr && m->n_slots * m->slot_bytes >= ((size_t)64 << 20);
     peer_answer_kernel<<<grid, 256, 0, st>>>(table16_of(m), L, filter);
@@ -240,7 +252,7 @@ int ashb_peer_update(ashb_map* m, int erase, int world, int rank, void* const* p
     ASHB_REQUIRE(m->key_dim <= 3, "the peer transport carries keys of 1 to 3 columns");
     DeviceGuard guard(m->device);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const dim3 grid((unsigned)((region_capacity + 255) / 256), (unsigned)world);
+    const unsigned grid = wave_grid(((region_capacity + 255) / 256) * 256 * (int64_t)world, 256, 8);
     if (erase)
         peer_update_kernel<true><<<grid, 256, 0, st>>>(table16_of(m), L, m->heap, m->counter, (int32_t)m->capacity);
     else

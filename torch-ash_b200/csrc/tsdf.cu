@@ -442,25 +442,86 @@ int ashb_tsdf_fuse_frame(ashb_map* m, void* embeddings, int64_t n_emb, int G, in
                                weight_channel, n_integrated_dev, touched_list, touched_count, stream);
 }
 
+// Side stream and events of the two-stage frame pipeline below, one set per device, created on first
+// use and kept for the life of the process.
+struct FramePipeline {
+    cudaStream_t side = nullptr;
+    cudaEvent_t start = nullptr, touched[2] = {nullptr, nullptr}, integrated[2] = {nullptr, nullptr};
+};
+
+static int frame_pipeline_for_current_device(FramePipeline** out) {
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static FramePipeline cached[kMaxDevices];
+    int dev = -1;
+    ASHB_CUDA_TRY(cudaGetDevice(&dev));
+    ASHB_REQUIRE(dev >= 0 && dev < kMaxDevices, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    FramePipeline& p = cached[dev];
+    if (p.side == nullptr) {
+        ASHB_CUDA_TRY(cudaStreamCreateWithFlags(&p.side, cudaStreamNonBlocking));
+        ASHB_CUDA_TRY(cudaEventCreateWithFlags(&p.start, cudaEventDisableTiming));
+        for (int i = 0; i < 2; ++i) {
+            ASHB_CUDA_TRY(cudaEventCreateWithFlags(&p.touched[i], cudaEventDisableTiming));
+            ASHB_CUDA_TRY(cudaEventCreateWithFlags(&p.integrated[i], cudaEventDisableTiming));
+        }
+    }
+    *out = &p;
+    return ASHB_OK;
+}
+
 int ashb_tsdf_fuse_frames(ashb_map* m, void* embeddings, int64_t n_emb, int G, int64_t D, int n_frames,
                           const float* const* depths, const float* const* colors, int H, int W,
                           const float* intrinsics, const float* world_to_cams, const float* cam_to_worlds,
                           float depth_max, double cell_size, const float* origin, int dilation, const int32_t* bound_lo,
                           const int32_t* bound_hi, float trunc, int sdf_channel, int rgb_channel, int weight_channel,
                           int32_t* grid_coords, uint32_t* touched, uint32_t first_stamp, int32_t* touched_list,
-                          int32_t* touched_count, unsigned long long* n_integrated_dev, void* stream) {
+                          int32_t* touched_count, int double_buffered, unsigned long long* n_integrated_dev,
+                          void* stream) {
     ASHB_REQUIRE(n_frames >= 0 && (n_frames == 0 || (depths && colors && intrinsics && world_to_cams && cam_to_worlds)),
                  "null frame tables");
     ASHB_REQUIRE((uint64_t)first_stamp + (uint64_t)n_frames <= 0x7FFFFFFFull && first_stamp != 0, "stamps would wrap");
-    for (int f = 0; f < n_frames; ++f) {
-        if (int rc = ashb_tsdf_fuse_frame(m, embeddings, n_emb, G, D, depths[f], colors[f], H, W, intrinsics + 9 * f,
-                                          world_to_cams + 12 * f, cam_to_worlds + 12 * f, depth_max, cell_size, origin,
-                                          dilation, bound_lo, bound_hi, trunc, sdf_channel, rgb_channel, weight_channel,
-                                          grid_coords, touched, first_stamp + (uint32_t)f, touched_list, touched_count,
-                                          n_integrated_dev, stream))
-            return rc;
+    ASHB_REQUIRE(m != nullptr && m->slots != nullptr, "null or destroyed map");
+    if (!double_buffered || touched_list == nullptr || touched_count == nullptr || n_frames < 2) {
+        for (int f = 0; f < n_frames; ++f) {
+            if (int rc = ashb_tsdf_fuse_frame(m, embeddings, n_emb, G, D, depths[f], colors[f], H, W, intrinsics + 9 * f,
+                                              world_to_cams + 12 * f, cam_to_worlds + 12 * f, depth_max, cell_size,
+                                              origin, dilation, bound_lo, bound_hi, trunc, sdf_channel, rgb_channel,
+                                              weight_channel, grid_coords, touched, first_stamp + (uint32_t)f,
+                                              touched_list, touched_count, n_integrated_dev, stream))
+                return rc;
+        }
+        return ASHB_OK;
     }
-    return ASHB_OK;
+    // Two-stage pipeline: the allocation pass of frame f + 1 (side stream) runs while frame f is fused
+    // (caller's stream).  The allocation pass writes the hash table, the free-index stack, the stamps and
+    // ITS work list (lists and counts alternate between two buffers); the fusion pass of the frame before
+    // reads its own list, the coordinates of blocks that already exist (re-written with the same values at
+    // most) and embedding rows no allocation touches -- so the two only meet through the events below.
+    DeviceGuard guard(m->device);
+    FramePipeline* p = nullptr;
+    if (int rc = frame_pipeline_for_current_device(&p)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    ASHB_CUDA_TRY(cudaEventRecord(p->start, st));
+    ASHB_CUDA_TRY(cudaStreamWaitEvent(p->side, p->start, 0));   // after whatever the caller enqueued before
+    for (int f = 0; f < n_frames; ++f) {
+        const int b = f & 1;
+        if (f >= 2) ASHB_CUDA_TRY(cudaStreamWaitEvent(p->side, p->integrated[b], 0));   // list b is free again
+        if (int rc = ashb_tsdf_touch(m, depths[f], H, W, intrinsics + 9 * f, cam_to_worlds + 12 * f, depth_max, cell_size,
+                                     origin, G, dilation, bound_lo, bound_hi, grid_coords, touched,
+                                     first_stamp + (uint32_t)f, touched_list + (int64_t)b * n_emb, touched_count + b,
+                                     p->side))
+            return rc;
+        ASHB_CUDA_TRY(cudaEventRecord(p->touched[b], p->side));
+        ASHB_CUDA_TRY(cudaStreamWaitEvent(st, p->touched[b], 0));
+        if (int rc = ashb_tsdf_integrate(embeddings, n_emb, G, D, grid_coords, touched, first_stamp + (uint32_t)f,
+                                         depths[f], colors[f], H, W, intrinsics + 9 * f, world_to_cams + 12 * f,
+                                         depth_max, cell_size, origin, trunc, sdf_channel, rgb_channel, weight_channel,
+                                         n_integrated_dev, touched_list + (int64_t)b * n_emb, touched_count + b, st))
+            return rc;
+        ASHB_CUDA_TRY(cudaEventRecord(p->integrated[b], st));
+    }
+    return ASHB_OK;   // the caller's stream has waited for every allocation pass: it is ordered after all the work
 }
 
 int ashb_tsdf_static_max_blocks(void) { return ASHB_TSDF_STATIC_MAX_BLOCKS; }
