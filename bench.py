@@ -1128,8 +1128,8 @@ def main():
             ev.record(stream)
         return xb, ev
 
-    def run_e2e(in_place, pipelined):
-        grid.grad_mode = "in_place" if in_place else "dense"
+    def run_e2e(in_place, pipelined, row_list=False):
+        grid.grad_mode = "row_list" if row_list else ("in_place" if in_place else "dense")
         grid.embeddings.grad = None
         main = torch.cuda.current_stream(device)
         times = []
@@ -1156,6 +1156,8 @@ def main():
             loss_value = loss.item()  # device -> host read of the step's result
             if in_place:
                 grid.zero_grad_rows_(x)  # this step's zero_grad
+            if row_list:
+                grid.apply_row_list_(alpha=-1e-12)  # the optimiser step on the touched rows (plain gradient descent)
         torch.cuda.synchronize()
         sec = (time.perf_counter() - t_begin) / args.steps
         if in_place:
@@ -1167,6 +1169,7 @@ def main():
     e2e_serial_sec = run_e2e(False, False)
     e2e_sec = run_e2e(False, True)
     e2e_ip_sec = run_e2e(True, True)
+    e2e_rl_sec = run_e2e(False, True, row_list=True)
 
     # the whole "forward + backward + double backward" step through the public API (eikonal-style
     # gradient-of-gradient term on the first channel), in both gradient modes, inputs resident
@@ -1279,6 +1282,14 @@ def main():
                     "cell, row) records per query -- coalesced stores, nothing read back, no table-sized buffer; "
                     "apply_list_ms = rows_scatter_add of that list into a dense buffer (what an optimiser step on the "
                     "touched rows costs)"}
+        pair_bytes = N_QUERIES * (FWD_BYTES + BWD_BYTES)
+        line["roofline"]["fwd_plus_bwd"] = {
+            "what": "forward + backward kernels together (the metric's unit of work), algorithmic bytes over the sum of "
+                    "the two launch times",
+            "dense_persistent_gradient": {"ms": round(f_ms + bp_ms, 4),
+                                          "frac": round(pair_bytes / ((f_ms + bp_ms) * 1e-3) / 1e9 / peak, 4)},
+            "row_list_gradient": {"ms": round(f_ms + r_ms, 4),
+                                  "frac": round(pair_bytes / ((f_ms + r_ms) * 1e-3) / 1e9 / peak, 4)}}
         line["roofline"]["api_faithful_step"] = {
             "what": "forward + 16.4 GB zero-fill + backward, bytes incl. the table once", "bytes": step_bytes,
             "achieved": round(step_bytes / (ms_per_step * 1e-3) / 1e9, 1),
@@ -1310,6 +1321,11 @@ def main():
             "ms_per_step": round(e2e_ip_sec * 1e3, 4),
             "note": "as e2e, with grid.grad_mode = 'in_place' and grid.zero_grad_rows_(x) as the step's zero_grad "
                     "(rank-local time)"}
+        line["e2e_row_list_grad"] = {
+            "value": round(world * N_QUERIES / e2e_rl_sec / 1e6, 2), "unit": "M queries/s",
+            "ms_per_step": round(e2e_rl_sec * 1e3, 4),
+            "note": "as e2e, with grid.grad_mode = 'row_list' (sparse gradient, no table-sized buffer) AND a gradient-"
+                    "descent step on the touched rows (grid.apply_row_list_) inside the timed step (rank-local time)"}
         line["zero_row_fraction"] = round(zero_rows, 4)
         line["random_access"] = {
             "what": "16-byte reads at random 64-byte-aligned places of the 16.4 GB table, one per thread, L2 fetch size "

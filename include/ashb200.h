@@ -13,7 +13,11 @@
  *   - every function returns 0 on success or an ASHB_ERR_* code; a text for
  *     the calling thread's last failure is available from
  *     ashb_last_error_string();
- *   - sizes and counts are int64_t; keys are int32 rows of `key_dim` columns.
+ *   - sizes and counts are int64_t; keys are int32 rows of `key_dim` columns;
+ *   - entry points that take an ashb_map select the map's device for the call; those that take only
+ *     buffers (ashb_query_*, ashb_conv_*, ashb_tsdf_integrate, ashb_route_by_owner, ashb_peer_route_keys,
+ *     ashb_peer_unpack_answers, ashb_routed_unpack_*, ashb_routed_send_z, ashb_rows_scatter_add, ...) launch on
+ *     the CURRENT device: the caller makes the buffers' device current first.
  *
  * There is no CPU implementation behind this interface: without a CUDA device
  * every compute entry point fails with ASHB_ERR_CUDA.
@@ -118,7 +122,9 @@ int ashb_map_load_states(ashb_map* map, const int32_t* keys_dev, const int64_t* 
  * (open addressing keeps erased slots occupied so that probe chains stay intact; after heavy
  * insert / erase traffic they lengthen every probe).  Indices, heap and size are unchanged.  The
  * reference has no counterpart: its chained third-party map frees nodes on erase.  Allocates a
- * second table for the duration of the call and synchronises `stream`. */
+ * second table for the duration of the call (cudaMalloc / cudaFree: the table is transiently
+ * doubled, and the call is illegal inside stream capture), synchronises `stream` and frees the old
+ * table: no other stream may still have work queued that probes this map. */
 int ashb_map_rehash(ashb_map* map, void* stream);
 
 /* ---------------------------------------------------------------- grid query

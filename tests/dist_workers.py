@@ -329,6 +329,19 @@ def routed_grid_worker(rank, world, port):
                     assert torch.count_nonzero(routed.embeddings.grad[mine.numel():]) == 0
                 if n > 1000:
                     assert 0.3 < float(mr.float().mean()) < 1.0
+            # the mailbox holds one batch at a time: a backward pass of an OLDER batch is refused, on every rank
+            # alike and before any collective, and the newest batch still goes through
+            routed.zero_grad_shard_()
+            x1 = x.clone().requires_grad_(True)
+            y1, _ = routed(x1, interpolation)
+            y2, _ = routed(x.clone().requires_grad_(True), interpolation)
+            try:
+                y1.sum().backward()
+                raise AssertionError("the backward pass of a superseded batch was accepted")
+            except RuntimeError as err:
+                assert "one batch at a time" in str(err)
+            y2.sum().backward()
+            routed.check_status()
             dist.barrier()
             del routed, ref
     finally:
@@ -355,20 +368,21 @@ def row_table_worker(rank, world, port):
         broadcast_state(eng, src=0)
         coords, idx = eng.items()
         rows_per_rank = int(-(-cap // world) * 1.25) + 64
-        row_of, per_owner = block_row_table(coords, idx, world, cap, rows_per_rank)
+        row_of, per_owner, shift = block_row_table(coords, idx, world, cap, rows_per_rank)
+        assert shift in (0, 1, 2, 3) and int(per_owner.max()) <= 1.08 * n_blocks / world or shift == 0
         gathered = [torch.empty_like(row_of) for _ in range(world)]
         dist.all_gather(gathered, row_of)
         assert all(torch.equal(g, gathered[0]) for g in gathered)
         assert int(per_owner.sum()) == n_blocks and int(per_owner.min()) > 0
         owner, local = row_of[idx] >> 26, row_of[idx] & ((1 << 26) - 1)
-        assert torch.equal(owner, coarse_owner_of(coords, world))
+        assert torch.equal(owner, coarse_owner_of(coords, world, shift))
         for o in range(world):
             rows = torch.sort(local[owner == o])[0]
             assert torch.equal(rows, torch.arange(int(per_owner[o])))      # a shard's rows are 0 .. count-1, each used once
         # co-ownership of +x neighbours
         find_idx, ok = eng.find((coords + torch.tensor([1, 0, 0], dtype=torch.int32)).contiguous())
         same = (row_of[find_idx[ok]] >> 26) == owner[ok]
-        assert float(same.float().mean()) > 0.8
+        assert float(same.float().mean()) > (0.8 if shift >= 2 else 0.3)
         with_error = False
         try:
             block_row_table(coords, idx, world, cap, 10)

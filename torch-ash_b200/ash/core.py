@@ -44,6 +44,7 @@ class ASHEngine(nn.Module):
         # passes half the capacity the table is rebuilt from its live entries, so that long
         # insert / erase histories (fusion with pruning) do not lengthen every probe.
         self._erased_bound = 0
+        self.auto_rehash = True
         self.register_load_state_dict_post_hook(ASHEngine._post_load_state_dict_hook)
 
     # ------------------------------------------------------------------ state
@@ -165,7 +166,11 @@ class ASHEngine(nn.Module):
             return
         self.backend.erase(keys)
         self._erased_bound += keys.shape[0]
-        if self._erased_bound > self.capacity // 2 and hasattr(self.backend, "rehash"):
+        # auto_rehash: rebuild the table once the erased keys may fill half of it (tombstones lengthen every
+        # probe).  The rebuild allocates a second table and waits for the stream, so it cannot run inside
+        # stream capture nor while another stream still probes this map: set auto_rehash = False there and
+        # call backend.rehash() at a point of your choosing.
+        if self.auto_rehash and self._erased_bound > self.capacity // 2 and hasattr(self.backend, "rehash"):
             self.backend.rehash()
             self._erased_bound = 0
 

@@ -217,7 +217,7 @@ class PartitionedHashMap:
         if erase:
             # as ASHEngine.erase: rebuild the table once the erased keys may fill half of it
             self.engine._erased_bound += keys.shape[0]
-            if self.engine._erased_bound > self.engine.capacity // 2:
+            if self.engine.auto_rehash and self.engine._erased_bound > self.engine.capacity // 2:
                 self.engine.backend.rehash()
                 self.engine._erased_bound = 0
 
@@ -469,30 +469,41 @@ class ShardedSparseDenseGrid(UnBoundedSparseDenseGrid):
 
 def coarse_owner_of(block_coords: torch.Tensor, world_size: int, coarse_shift: int = 3) -> torch.Tensor:
     """Owner rank per BLOCK for ``RoutedSparseDenseGrid``: ``owner_of`` applied to the block
-    coordinate shifted right by ``coarse_shift`` bits per axis, so the 8 x 8 x 8 blocks of one coarse
-    cell -- and with them 7 of 8 +x/+y/+z neighbours of a block -- live on one rank."""
+    coordinate shifted right by ``coarse_shift`` bits per axis, so the blocks of one coarse cell (8 x 8 x 8
+    at shift 3) -- and with them most +x/+y/+z neighbours of a block -- live on one rank."""
     return owner_of(torch.bitwise_right_shift(block_coords.to(torch.int64), coarse_shift).to(torch.int32), world_size)
 
 
 def block_row_table(coords: torch.Tensor, indices: torch.Tensor, world_size: int, num_embeddings: int,
-                    rows_per_rank: int):
+                    rows_per_rank: int, coarse_shift: Optional[int] = None, balance: float = 1.08):
     """Which rank owns which block and where: from the active blocks' coordinates and indices (the same
     on every rank after ``broadcast_state``) returns ``(row_of int64 (num_embeddings,), per_owner int64
-    (world,))`` with ``row_of[index] = owner << 26 | row in the owner's shard`` (0 for inactive indices)
-    and the number of blocks per owner.  Rows are handed out in ascending index order, so every rank
-    derives the same table."""
-    owner = coarse_owner_of(coords, world_size)
+    (world,), coarse_shift)`` with ``row_of[index] = owner << 26 | row in the owner's shard`` (0 for
+    inactive indices) and the number of blocks per owner.  Rows are handed out in ascending index
+    order, so every rank derives the same table.
+
+    Ownership is a hash of the block coordinate shifted right by ``coarse_shift`` bits per axis.  Large
+    coarse cells keep neighbouring blocks on one rank but balance badly when there are few of them, so
+    with ``coarse_shift=None`` the largest shift of 3, 2, 1, 0 is taken for which no rank owns more
+    than ``balance`` times the mean (and its blocks fit its shard); the step waits for the slowest rank."""
+    n = indices.numel()
     order = torch.argsort(indices)
-    indices, owner = indices[order], owner[order]
-    one_hot = torch.nn.functional.one_hot(owner, world_size)
+    coords, indices = coords[order], indices[order]
+    shifts = (3, 2, 1, 0) if coarse_shift is None else (coarse_shift,)
+    for shift in shifts:
+        owner = coarse_owner_of(coords, world_size, shift)
+        one_hot = torch.nn.functional.one_hot(owner, world_size)
+        per_owner = one_hot.sum(dim=0)
+        largest = int(per_owner.max()) if n else 0
+        fits = largest <= rows_per_rank
+        if fits and (shift == shifts[-1] or largest <= balance * n / world_size):
+            break
+    else:
+        raise RuntimeError(f"an owner holds {largest} blocks but a shard has {rows_per_rank} rows; raise shard_slack")
     local = (torch.cumsum(one_hot, dim=0) - one_hot).gather(1, owner.view(-1, 1)).view(-1)   # rank among its owner's blocks
-    per_owner = one_hot.sum(dim=0)
-    if indices.numel() and int(per_owner.max()) > rows_per_rank:
-        raise RuntimeError(f"an owner holds {int(per_owner.max())} blocks but a shard has {rows_per_rank} rows; "
-                           "raise shard_slack")
     row_of = torch.zeros(num_embeddings, dtype=torch.int64, device=coords.device)
     row_of[indices] = (owner << 26) | local
-    return row_of, per_owner
+    return row_of, per_owner, shift
 
 
 class _RoutedMailbox:
@@ -537,6 +548,8 @@ class _RoutedGridQuery(torch.autograd.Function):
         backend.routed_forward(grid.engine.backend, grid._emb_bases, geom, box.layout, interpolation)
         grid._barrier()                       # every result row has landed
         y, masks = backend.routed_unpack_y(where, n, grid.embedding_dim, box.layout)
+        grid._batch_serial += 1               # the mailbox now holds THIS batch's records and slots
+        ctx.serial = grid._batch_serial
         ctx.grid, ctx.geom, ctx.interpolation, ctx.n = grid, geom, interpolation, n
         ctx.embeddings = embeddings
         ctx.mark_non_differentiable(masks)
@@ -545,6 +558,9 @@ class _RoutedGridQuery(torch.autograd.Function):
     @staticmethod
     def backward(ctx, z, _grad_masks):
         grid, box = ctx.grid, ctx.grid._mailbox
+        if ctx.serial != grid._batch_serial:
+            raise RuntimeError("RoutedSparseDenseGrid: another batch was queried before this one's backward pass; "
+                               "the mailbox holds one batch at a time (forward, then its backward)")
         where = box.where[:ctx.n]             # still this batch's: one batch is in flight at a time
         need_grad_x = bool(ctx.needs_input_grad[1])
         backend.routed_send_z(where, z.contiguous(), box.layout)
@@ -598,6 +614,7 @@ class RoutedSparseDenseGrid(UnBoundedSparseDenseGrid):
         self._row_of = None
         self._side_stream = None
         self._zero_done = None
+        self._batch_serial = 0
         self.fused = True
 
     def _allocate_embeddings(self) -> torch.Tensor:
@@ -623,9 +640,9 @@ class RoutedSparseDenseGrid(UnBoundedSparseDenseGrid):
         broadcast_state(self.engine, src=src, group=self.group)
         self.construct_grid_neighbor_lut_(radius=1, bidirectional=False)
         coords, idx = self.engine.items()
-        row_of, _ = block_row_table(coords, idx, self.world, self.num_embeddings, self._rows_per_rank)
+        row_of, _, self.coarse_shift = block_row_table(coords, idx, self.world, self.num_embeddings, self._rows_per_rank)
         self._row_of = row_of.to(torch.int32)          # bit pattern of the uint32 the kernels read (owner < 32)
-        mine = torch.sort(idx[coarse_owner_of(coords, self.world) == self.rank])[0]
+        mine = torch.sort(idx[(row_of[idx] >> 26) == self.rank])[0]
         self._owned_blocks = mine                      # global block indices of this shard's rows, in row order
         self._n_owned = int(self._owned_blocks.numel())
 

@@ -8,7 +8,8 @@
 // Sending the position to the rank that holds the block and letting that rank gather, interpolate
 // and scatter in its OWN memory moves 16 + 4 D (+ 4 D + 16 in the backward pass) bytes per query
 // over NVLink instead of ~64 D.  Blocks are assigned to ranks by a hash of their coarse
-// coordinate (block >> 3 per axis), so a block and its +x/+y/+z neighbours mostly share an owner;
+// coordinate (block >> 3 per axis, fewer bits when that balances badly), so a block and its
+// +x/+y/+z neighbours mostly share an owner;
 // the few corner rows that do not are read from, and reduced into, the neighbour's owner directly
 // (plain peer loads and `red.global.add` over NVLink).
 //
