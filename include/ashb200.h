@@ -624,7 +624,8 @@ int ashb_peer_update(ashb_map* map, int erase, int world, int rank, void* const*
  *
  * Mailbox (symmetric memory, one per rank, peer_bases_dev [world]): inbox_x float4 [world][cap]
  * {x, y, z, block index}, counts int32 [world], inbox_z float [world][cap][D], out_y float
- * [world][cap][D], out_gx float4 [world][cap]; all offsets in bytes, multiples of 16 (counts: 4).
+ * [world][cap][D], out_gx float4 [world][cap], inbox_g float4 [world][cap]; all offsets in bytes,
+ * multiples of 16 (counts: 4).
  * Rank r writes only region r of another rank's sections.  world <= 32, region_capacity < 2^26.
  * A step on every rank: route | barrier | forward | barrier | unpack_y | ... | send_z | barrier |
  * backward | barrier | unpack_grad_x, the barriers being collectives the caller enqueues on the
@@ -635,39 +636,57 @@ int ashb_routed_route(ashb_map* map, const float* x, int64_t n, double cell_size
                       const int32_t* nb_lut, const uint32_t* row_of, int64_t n_emb, int64_t D,
                       void* const* peer_bases_dev, int64_t mailbox_bytes, int64_t inbox_x_offset,
                       int64_t counts_offset, int64_t inbox_z_offset, int64_t out_y_offset, int64_t out_gx_offset,
-                      int64_t region_capacity, int world, int rank, int32_t* cursor_dev, int32_t* where_dev,
+                      int64_t inbox_g_offset, int64_t region_capacity, int world, int rank, int32_t* cursor_dev, int32_t* where_dev,
                       uint32_t* status_dev, void* stream);
 /* Owner side: interpolate every record of this rank's inbox (semantics of ashb_grid_query_forward)
  * and store row j of region r into rank r's out_y[rank][j]. */
 int ashb_routed_forward(ashb_map* map, int interp, const void* const* emb_bases_dev, double cell_size,
                         const float* origin, int G, const int32_t* nb_lut, const uint32_t* row_of, int64_t n_emb,
                         int64_t D, void* const* peer_bases_dev, int64_t mailbox_bytes, int64_t inbox_x_offset,
-                        int64_t counts_offset, int64_t inbox_z_offset, int64_t out_y_offset, int64_t out_gx_offset,
+                        int64_t counts_offset, int64_t inbox_z_offset, int64_t out_y_offset, int64_t out_gx_offset, int64_t inbox_g_offset,
                         int64_t region_capacity, int world, int rank, void* stream);
 /* Asker side: y [n][D] and masks uint8 [n] (optional) from this rank's out_y, in query order. */
 int ashb_routed_unpack_y(const int32_t* where_dev, int64_t n, float* y, uint8_t* masks, int64_t D,
                          void* const* peer_bases_dev, int64_t mailbox_bytes, int64_t inbox_x_offset,
-                         int64_t counts_offset, int64_t inbox_z_offset, int64_t out_y_offset, int64_t out_gx_offset,
+                         int64_t counts_offset, int64_t inbox_z_offset, int64_t out_y_offset, int64_t out_gx_offset, int64_t inbox_g_offset,
                          int64_t region_capacity, int world, int rank, void* stream);
 /* Asker side: z [n][D] = dL/dy of every query into its owner's inbox_z, at the slot routing gave it. */
 int ashb_routed_send_z(const int32_t* where_dev, int64_t n, const float* z, int64_t D,
                        void* const* peer_bases_dev, int64_t mailbox_bytes, int64_t inbox_x_offset,
-                       int64_t counts_offset, int64_t inbox_z_offset, int64_t out_y_offset, int64_t out_gx_offset,
+                       int64_t counts_offset, int64_t inbox_z_offset, int64_t out_y_offset, int64_t out_gx_offset, int64_t inbox_g_offset,
                        int64_t region_capacity, int world, int rank, void* stream);
 /* Owner side: semantics of ashb_grid_query_backward for every record: gradient rows ADDED into the
- * owners' gradient shards, dL/dx (times 1 / cell_size) stored into the asker's out_gx unless
+ * owners' gradient shards unless need_grad_embeddings == 0 (the first-order pass of a
+ * gradient-of-gradient loss), dL/dx (times 1 / cell_size) stored into the asker's out_gx unless
  * need_grad_x == 0 (then the embedding rows are not read). */
 int ashb_routed_backward(ashb_map* map, int interp, const void* const* emb_bases_dev, void* const* grad_bases_dev,
-                         int need_grad_x, double cell_size, const float* origin, int G, const int32_t* nb_lut,
+                         int need_grad_x, int need_grad_embeddings, double cell_size, const float* origin, int G, const int32_t* nb_lut,
                          const uint32_t* row_of, int64_t n_emb, int64_t D, void* const* peer_bases_dev,
                          int64_t mailbox_bytes, int64_t inbox_x_offset, int64_t counts_offset,
-                         int64_t inbox_z_offset, int64_t out_y_offset, int64_t out_gx_offset,
+                         int64_t inbox_z_offset, int64_t out_y_offset, int64_t out_gx_offset, int64_t inbox_g_offset,
                          int64_t region_capacity, int world, int rank, void* stream);
 /* Asker side: grad_x [n][3] from this rank's out_gx, zero rows for queries without a block. */
 int ashb_routed_unpack_grad_x(const int32_t* where_dev, int64_t n, float* grad_x, int64_t D,
                               void* const* peer_bases_dev, int64_t mailbox_bytes, int64_t inbox_x_offset,
                               int64_t counts_offset, int64_t inbox_z_offset, int64_t out_y_offset,
-                              int64_t out_gx_offset, int64_t region_capacity, int world, int rank, void* stream);
+                              int64_t out_gx_offset, int64_t inbox_g_offset, int64_t region_capacity, int world, int rank, void* stream);
+
+/* Double backward over the routed table.  Asker side: grad_grad_x [n][3], the gradient arriving at dL/dx,
+ * into every query's owner's inbox_g (send dL/dy again with ashb_routed_send_z first: another pass may have
+ * replaced it).  Owner side: semantics of ashb_grid_query_backward_backward for every record -- second-order
+ * gradient rows ADDED into the owners' gradient shards, the gradient with respect to dL/dy stored into the
+ * asker's out_y (gather it with ashb_routed_unpack_y, masks NULL). */
+int ashb_routed_send_g(const int32_t* where_dev, int64_t n, const float* grad_grad_x, int64_t D,
+                       void* const* peer_bases_dev, int64_t mailbox_bytes, int64_t inbox_x_offset,
+                       int64_t counts_offset, int64_t inbox_z_offset, int64_t out_y_offset, int64_t out_gx_offset,
+                       int64_t inbox_g_offset, int64_t region_capacity, int world, int rank, void* stream);
+int ashb_routed_backward_backward(ashb_map* map, int interp, const void* const* emb_bases_dev,
+                                  void* const* grad_bases_dev, double cell_size, const float* origin, int G,
+                                  const int32_t* nb_lut, const uint32_t* row_of, int64_t n_emb, int64_t D,
+                                  void* const* peer_bases_dev, int64_t mailbox_bytes, int64_t inbox_x_offset,
+                                  int64_t counts_offset, int64_t inbox_z_offset, int64_t out_y_offset,
+                                  int64_t out_gx_offset, int64_t inbox_g_offset, int64_t region_capacity, int world,
+                                  int rank, void* stream);
 
 /* ---------------------------------------------------------------- runtime knobs */
 

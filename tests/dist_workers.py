@@ -270,7 +270,8 @@ def sharded_grid_worker(rank, world, port):
 def routed_grid_worker(rank, world, port):
     """A table sharded over the ranks with the queries routed to the owners answers like a replicated
     table, returns the same gradients for the positions, and leaves in every gradient shard the
-    rows of the summed dense gradient; also when a batch is empty or ragged, and over two steps."""
+    rows of the summed dense gradient; also when a batch is empty or ragged, over two steps, and for a
+    loss on dL/dx (double backward)."""
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     torch.cuda.set_device(rank)
@@ -329,6 +330,41 @@ def routed_grid_worker(rank, world, port):
                     assert torch.count_nonzero(routed.embeddings.grad[mine.numel():]) == 0
                 if n > 1000:
                     assert 0.3 < float(mr.float().mean()) < 1.0
+            # a loss on dL/dx (an eikonal term) next to a loss on y: the first-order pass that forms dL/dx leaves the
+            # shards alone, the second round adds the second-order rows and the first-order rows of the y term
+            w2 = torch.randn(n, D, device=device, generator=g)
+
+            def two_level_loss(grid, xin):
+                yv, _ = grid(xin, interpolation)
+                (gx,) = torch.autograd.grad((yv * w).sum(), xin, create_graph=True)
+                return ((gx.norm(dim=-1) - 1.0) ** 2).sum() * 1e-2 + (yv * w2).sum(), gx
+
+            ref.embeddings.grad = None
+            loss_r, gx_r = two_level_loss(ref, x.clone().requires_grad_(True))
+            loss_r.backward()
+            per_block = ref.embeddings.grad[idx_ref].clone()
+            dist.all_reduce(per_block)
+            routed.zero_grad_shard_()
+            loss_s, gx_s = two_level_loss(routed, x.clone().requires_grad_(True))
+            assert torch.count_nonzero(routed.embeddings.grad) == 0     # forming dL/dx added nothing
+            loss_s.backward()
+            routed.check_status()
+            torch.testing.assert_close(gx_s, gx_r, rtol=1e-4, atol=1e-5 * float(gx_r.abs().max()))
+            torch.testing.assert_close(loss_s, loss_r, rtol=1e-4, atol=1e-4)
+            got, want = routed.embeddings.grad[: mine.numel()], per_block[mine]
+            torch.testing.assert_close(got, want, rtol=1e-4, atol=2e-5 * max(1.0, float(want.abs().max())))
+            assert torch.count_nonzero(routed.embeddings.grad[mine.numel():]) == 0
+            # the gradient with respect to dL/dy comes back through the second round as well
+            zr = w.clone().requires_grad_(True)
+            zs = w.clone().requires_grad_(True)
+            for grid, zz in ((ref, zr), (routed, zs)):
+                if grid is routed:
+                    routed.zero_grad_shard_()
+                xin = x.clone().requires_grad_(True)
+                yv, _ = grid(xin, interpolation)
+                (gx,) = torch.autograd.grad((yv * zz).sum(), xin, create_graph=True)
+                (gx * gx).sum().backward()
+            torch.testing.assert_close(zs.grad, zr.grad, rtol=1e-4, atol=1e-5 * float(zr.grad.abs().max()))
             # the mailbox holds one batch at a time: a backward pass of an OLDER batch is refused, on every rank
             # alike and before any collective, and the newest batch still goes through
             routed.zero_grad_shard_()

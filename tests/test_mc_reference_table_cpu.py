@@ -104,7 +104,7 @@ def test_every_pattern_against_the_reference_table():
     print(f"identical {identical}, same oriented loops / other diagonals {same_loops}, "
           f"different polygons {different}: {differing}")
     assert identical + same_loops + different == 256
-    # the recorded outcome of the comparison (DESIGN.md quotes these numbers)
+    # the recorded outcome of the comparison
     assert (identical, same_loops, different) == EXPECTED, (identical, same_loops, different)
 
 

@@ -109,12 +109,14 @@ _lib.ashb_rows_scatter_add.argtypes = [_int, _vp, _vp, _vp, _i64, _i64, _i64, _i
 _lib.ashb_set_find_filter.argtypes = [_int]
 _lib.ashb_set_erase_cooperative.argtypes = [_int]
 _lib.ashb_measure_random_reads_ilp.argtypes = [_vp, _i64, _i64, _int, _int, _c.c_uint32, _vp, _vp]
-_ROUTED_LAYOUT = [_vp] + [_i64] * 7 + [_int, _int]
+_ROUTED_LAYOUT = [_vp] + [_i64] * 8 + [_int, _int]
 _lib.ashb_routed_route.argtypes = [_vp, _vp, _i64, _c.c_double, _vp, _int, _vp, _vp, _i64, _i64] + _ROUTED_LAYOUT + [_vp] * 4
 _lib.ashb_routed_forward.argtypes = [_vp, _int, _vp, _c.c_double, _vp, _int, _vp, _vp, _i64, _i64] + _ROUTED_LAYOUT + [_vp]
 _lib.ashb_routed_unpack_y.argtypes = [_vp, _i64, _vp, _vp, _i64] + _ROUTED_LAYOUT + [_vp]
 _lib.ashb_routed_send_z.argtypes = [_vp, _i64, _vp, _i64] + _ROUTED_LAYOUT + [_vp]
-_lib.ashb_routed_backward.argtypes = [_vp, _int, _vp, _vp, _int, _c.c_double, _vp, _int, _vp, _vp, _i64, _i64] + _ROUTED_LAYOUT + [_vp]
+_lib.ashb_routed_backward.argtypes = [_vp, _int, _vp, _vp, _int, _int, _c.c_double, _vp, _int, _vp, _vp, _i64, _i64] + _ROUTED_LAYOUT + [_vp]
+_lib.ashb_routed_send_g.argtypes = [_vp, _i64, _vp, _i64] + _ROUTED_LAYOUT + [_vp]
+_lib.ashb_routed_backward_backward.argtypes = [_vp, _int, _vp, _vp, _c.c_double, _vp, _int, _vp, _vp, _i64, _i64] + _ROUTED_LAYOUT + [_vp]
 _lib.ashb_routed_unpack_grad_x.argtypes = [_vp, _i64, _vp, _i64] + _ROUTED_LAYOUT + [_vp]
 _lib.ashb_grid_zero_rows.argtypes = [_vp, _int, _vp, _vp, _c.c_double, _vp, _int, _vp, _vp, _i64, _i64, _i64, _vp]
 
@@ -1309,7 +1311,7 @@ def render_intervals_backward(hashmap, embeddings, nb_lut, cell_size, origin, ra
 
 
 # ---- table sharded over the ranks, queries routed to the owners -----------------------------------
-# ``layout`` = (peer_bases_dev, mailbox_bytes, inbox_x, counts, inbox_z, out_y, out_gx, region_capacity, world, rank);
+# ``layout`` = (peer_bases_dev, mailbox_bytes, inbox_x, counts, inbox_z, out_y, out_gx, inbox_g, region_capacity, world, rank);
 # ``geom`` = (cell_size, origin, grid_dim, nb_lut int32, row_of int32 viewed as uint32, n_emb, D).
 def _routed_geom(geom):
     cell_size, origin, grid_dim, nb_lut, row_of, n_emb, D = geom
@@ -1329,12 +1331,13 @@ def routed_forward(hashmap, emb_bases, geom, layout, interpolation):
                                     _stream(hashmap.device())))
 
 
-def routed_unpack_y(where, n, D, layout):
+def routed_unpack_y(where, n, D, layout, with_masks=True):
     dev = where.device
     y = torch.empty((n, D), dtype=torch.float32, device=dev)
-    masks = torch.empty(n, dtype=torch.bool, device=dev)
+    masks = torch.empty(n, dtype=torch.bool, device=dev) if with_masks else None
     with torch.cuda.device(dev):
-        _check(_lib.ashb_routed_unpack_y(where.data_ptr(), n, y.data_ptr(), masks.data_ptr(), D, *layout, _stream(dev)))
+        _check(_lib.ashb_routed_unpack_y(where.data_ptr(), n, y.data_ptr(), masks.data_ptr() if with_masks else None, D,
+                                         *layout, _stream(dev)))
     return y, masks
 
 
@@ -1344,9 +1347,21 @@ def routed_send_z(where, z, layout):
         _check(_lib.ashb_routed_send_z(where.data_ptr(), z.shape[0], z.data_ptr(), z.shape[1], *layout, _stream(z.device)))
 
 
-def routed_backward(hashmap, emb_bases, grad_bases, geom, layout, interpolation, need_grad_x):
+def routed_backward(hashmap, emb_bases, grad_bases, geom, layout, interpolation, need_grad_x, need_grad_embeddings=True):
     _check(_lib.ashb_routed_backward(hashmap._h, _interp_code(interpolation), emb_bases, grad_bases, int(bool(need_grad_x)),
-                                     *_routed_geom(geom), *layout, _stream(hashmap.device())))
+                                     int(bool(need_grad_embeddings)), *_routed_geom(geom), *layout,
+                                     _stream(hashmap.device())))
+
+
+def routed_send_g(where, grad_grad_x, D, layout):
+    g = _cuda(grad_grad_x, "grad_grad_x", torch.float32)
+    with torch.cuda.device(g.device):
+        _check(_lib.ashb_routed_send_g(where.data_ptr(), g.shape[0], g.data_ptr(), int(D), *layout, _stream(g.device)))
+
+
+def routed_backward_backward(hashmap, emb_bases, grad_bases, geom, layout, interpolation):
+    _check(_lib.ashb_routed_backward_backward(hashmap._h, _interp_code(interpolation), emb_bases, grad_bases,
+                                              *_routed_geom(geom), *layout, _stream(hashmap.device())))
 
 
 def routed_unpack_grad_x(where, n, D, layout):

@@ -522,10 +522,11 @@ class _RoutedMailbox:
         inbox_z = align(counts + world * 4)
         out_y = align(inbox_z + recs * D * 4)
         out_gx = align(out_y + recs * D * 4)
-        total = align(out_gx + recs * 16)
+        inbox_g = align(out_gx + recs * 16)
+        total = align(inbox_g + recs * 16)
         self.buffer = symm.empty(total, dtype=torch.uint8, device=device)
         self.handle = symm.rendezvous(self.buffer, group if group is not None else dist.group.WORLD)
-        self.layout = (self.handle.buffer_ptrs_dev, total, inbox_x, counts, inbox_z, out_y, out_gx, cap, world, rank)
+        self.layout = (self.handle.buffer_ptrs_dev, total, inbox_x, counts, inbox_z, out_y, out_gx, inbox_g, cap, world, rank)
         self.max_batch = int(max_batch)
         self.where = torch.empty(self.max_batch, dtype=torch.int32, device=device)
         self.cursor = torch.zeros(world, dtype=torch.int32, device=device)
@@ -557,20 +558,63 @@ class _RoutedGridQuery(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, z, _grad_masks):
-        grid, box = ctx.grid, ctx.grid._mailbox
-        if ctx.serial != grid._batch_serial:
-            raise RuntimeError("RoutedSparseDenseGrid: another batch was queried before this one's backward pass; "
-                               "the mailbox holds one batch at a time (forward, then its backward)")
-        where = box.where[:ctx.n]             # still this batch's: one batch is in flight at a time
+        from .grid_query import _engine_wants_gradient_of
+
         need_grad_x = bool(ctx.needs_input_grad[1])
-        backend.routed_send_z(where, z.contiguous(), box.layout)
+        # a pass that only asks for d/dx (the first-order pass of an eikonal term) must not add to the shards
+        need_grad_emb = bool(ctx.needs_input_grad[0]) and _engine_wants_gradient_of(ctx.embeddings)
+        grad_x = _RoutedGridQueryBackward.apply(z.contiguous(), ctx.embeddings, ctx.grid, ctx.geom, ctx.interpolation,
+                                                ctx.n, ctx.serial, need_grad_x, need_grad_emb)
+        return None, grad_x, None, None       # the embedding gradient went straight into the owners' shards
+
+
+def _check_batch(grid, serial) -> None:
+    if serial != grid._batch_serial:
+        raise RuntimeError("RoutedSparseDenseGrid: another batch was queried before this one's backward pass; "
+                           "the mailbox holds one batch at a time (forward, then its backward passes)")
+
+
+class _RoutedGridQueryBackward(torch.autograd.Function):
+    """First-order backward of the routed query, itself differentiable w.r.t. the incoming gradient (and,
+    through the owners' gradient shards, the embeddings), so that gradient-of-gradient losses train; the
+    double-backward gradient w.r.t. positions is dropped as in ash/grid_query.py."""
+
+    @staticmethod
+    def forward(ctx, z, embeddings, grid, geom, interpolation, n, serial, need_grad_x, need_grad_emb):
+        _check_batch(grid, serial)
+        box = grid._mailbox
+        where = box.where[:n]                 # still this batch's: one batch is in flight at a time
+        ctx.save_for_backward(z)
+        ctx.grid, ctx.geom, ctx.interpolation, ctx.n, ctx.serial = grid, geom, interpolation, n, serial
+        ctx.set_materialize_grads(False)
+        if not need_grad_x and not need_grad_emb:
+            return None
+        backend.routed_send_z(where, z, box.layout)
         grid._wait_for_zero_fill()            # this shard is clear before any rank may add to it
         grid._barrier()                       # every owner has the incoming gradients of its records
-        backend.routed_backward(grid.engine.backend, grid._emb_bases, grid._grad_bases, ctx.geom, box.layout,
-                                ctx.interpolation, need_grad_x)
-        grid._barrier()                       # gradient rows and dL/dx have landed; the mailbox is free again
-        grad_x = backend.routed_unpack_grad_x(where, ctx.n, grid.embedding_dim, box.layout) if need_grad_x else None
-        return None, grad_x, None, None       # the embedding gradient went straight into the owners' shards
+        backend.routed_backward(grid.engine.backend, grid._emb_bases, grid._grad_bases, geom, box.layout, interpolation,
+                                need_grad_x, need_grad_emb)
+        grid._barrier()                       # gradient rows and dL/dx have landed
+        return backend.routed_unpack_grad_x(where, n, grid.embedding_dim, box.layout) if need_grad_x else None
+
+    @staticmethod
+    def backward(ctx, grad_grad_x):
+        if grad_grad_x is None:
+            return (None,) * 9
+        (z,) = ctx.saved_tensors
+        grid, box = ctx.grid, ctx.grid._mailbox
+        _check_batch(grid, ctx.serial)
+        where = box.where[:ctx.n]
+        # dL/dy goes out again: a first-order pass of the same batch may have replaced it since
+        backend.routed_send_z(where, z, box.layout)
+        backend.routed_send_g(where, grad_grad_x.to(torch.float32).contiguous(), grid.embedding_dim, box.layout)
+        grid._wait_for_zero_fill()
+        grid._barrier()
+        backend.routed_backward_backward(grid.engine.backend, grid._emb_bases, grid._grad_bases, ctx.geom, box.layout,
+                                         ctx.interpolation)
+        grid._barrier()                       # second-order gradient rows and the gradient w.r.t. dL/dy have landed
+        grad_z, _ = backend.routed_unpack_y(where, ctx.n, grid.embedding_dim, box.layout, with_masks=False)
+        return (grad_z,) + (None,) * 8
 
 
 class RoutedSparseDenseGrid(UnBoundedSparseDenseGrid):
@@ -588,7 +632,8 @@ class RoutedSparseDenseGrid(UnBoundedSparseDenseGrid):
 
     The block structure (hash map, neighbour table, block -> (owner, row) table) is replicated: build
     it the same way on every rank, then call ``sync_structure_()``.  One batch is in flight at a time
-    (forward, then its backward); first-order gradients only."""
+    (forward, then its backward passes); all three autograd levels of the reference are provided (a loss
+    on dL/dx trains the embeddings through a double backward round)."""
 
     def __init__(self, in_dim: int, num_embeddings: int, embedding_dim: int, grid_dim: int, cell_size: float = 1.0,
                  device=None, group=None, max_batch: int = 1 << 20, region_slack: float = 1.5, shard_slack: float = 1.25):

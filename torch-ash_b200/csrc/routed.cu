@@ -25,6 +25,9 @@
 //   backward  the owner adds the 8 gradient rows per record into its gradient shard and stores
 //             dL/dx into the asker's buffer
 //   (barrier) the asker gathers dL/dx.
+// The double backward (a loss on dL/dx, e.g. an eikonal term) is one more round of the same kind: the
+// asker sends dL/dy again together with the gradient arriving at dL/dx, the owner adds the second-order
+// gradient rows into its shard and returns the gradient with respect to dL/dy through the result buffer.
 // No kernel waits on another GPU; ordering comes from the collectives between the launches.  Every
 // remote address is base[peer] + offset with offsets checked against the mailbox size on the host
 // and slots re-checked on the device; records that do not fit are dropped and reported.
@@ -43,6 +46,7 @@ struct RoutedLayout {
     int64_t inbox_z;          // float [world][cap][D]
     int64_t out_y;            // float [world][cap][D]: region o = rows computed by owner o, in its inbox order
     int64_t out_gx;           // float4 [world][cap]
+    int64_t inbox_g;          // float4 [world][cap]: gradient arriving at dL/dx (double backward)
     int64_t cap;              // records per region
     int world, rank;
 };
@@ -272,7 +276,7 @@ __global__ void __launch_bounds__(256) routed_unpack_gx_kernel(RoutedLayout L, c
 }
 
 // ---- owner: backward ----------------------------------------------------------------------------
-template <int VEC, bool NEED_GO>
+template <int VEC, bool NEED_GO, bool NEED_GE>
 __global__ void __launch_bounds__(256, 3) routed_backward_kernel(RoutedGrid g, RoutedLayout L, float go_scale, int D,
                                                               int lane_shift, int interp) {
     const int region = blockIdx.y;
@@ -315,7 +319,7 @@ __global__ void __launch_bounds__(256, 3) routed_backward_kernel(RoutedGrid g, R
                     gr.v[k] = w * zv.v[k];
                     if (NEED_GO) dot += e[c].v[k] * zv.v[k];
                 }
-                atomic_add_pack<float, VEC>(routed_out_row(g, base[c]) + ch, gr);
+                if (NEED_GE) atomic_add_pack<float, VEC>(routed_out_row(g, base[c]) + ch, gr);
                 if (NEED_GO) {
                     float wg[3];
                     aw.grad(c, wg);
@@ -335,6 +339,75 @@ __global__ void __launch_bounds__(256, 3) routed_backward_kernel(RoutedGrid g, R
     }
 }
 
+// ---- double backward ------------------------------------------------------------------------------
+// asker: the gradient arriving at dL/dx of every query, into the owner's inbox_g at the query's slot
+__global__ void __launch_bounds__(256) routed_send_g_kernel(RoutedLayout L, const int32_t* __restrict__ where, int64_t n,
+                                                            const float* __restrict__ ggx) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int w = where[i];
+    if (w < 0) return;
+    const int owner = (int)((unsigned)w >> kRowOwnerShift);
+    const int64_t slot = (unsigned)w & kRowLocalMask;
+    float4* inbox = reinterpret_cast<float4*>(static_cast<char*>(L.bases[owner]) + L.inbox_g);
+    inbox[(int64_t)L.rank * L.cap + slot] = make_float4(ggx[3 * i], ggx[3 * i + 1], ggx[3 * i + 2], 0.f);
+}
+
+// owner: semantics of query_backward_backward_kernel for every record; the gradient with respect to
+// dL/dy goes back through the asker's result buffer (out_y), the second-order gradient rows into the shards
+template <int VEC>
+__global__ void __launch_bounds__(256, 3) routed_backward_backward_kernel(RoutedGrid g, RoutedLayout L, float go_scale,
+                                                                       int D, int lane_shift, int interp) {
+    const int region = blockIdx.y;
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t j = tid >> lane_shift;
+    const int lane = (int)(tid & ((1 << lane_shift) - 1));
+    const int ch = lane * VEC;
+    float4 rec;
+    if (ch >= D || !routed_record(L, region, j, &rec)) return;
+    Pack<float, VEC> gz;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) gz.v[k] = 0;
+    const int gi = __float_as_int(rec.w);
+    if (gi >= 0 && gi < g.n_emb) {
+        const float xw[3] = {rec.x, rec.y, rec.z};
+        int blk[3], cell[3];
+        float off[3];
+        split_world_position(xw, g.org, g.inv_cell, g.inv_G, g.G_f, g.G, blk, cell, off);
+        int64_t base[8];
+        bool mine;
+        if (routed_corner_rows(g, gi, cell, D, base, &mine, L.rank)) {
+            AxisWeights<float> aw;
+            aw.init(interp, off);
+            const char* box = static_cast<const char*>(L.bases[L.rank]);
+            const int64_t r = (int64_t)region * L.cap + j;
+            const float4 gg = __ldcg(reinterpret_cast<const float4*>(box + L.inbox_g) + r);
+            const float g3[3] = {gg.x * go_scale, gg.y * go_scale, gg.z * go_scale};
+            using V = typename Vec<float, VEC>::type;
+            Pack<float, VEC> zv;
+            *reinterpret_cast<V*>(zv.v) = __ldcg(reinterpret_cast<const V*>(reinterpret_cast<const float*>(box + L.inbox_z) + r * D + ch));
+            Pack<float, VEC> e[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) e[c] = routed_corner<VEC>(g, base[c], ch, mine);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                float wg[3];
+                aw.grad(c, wg);
+                const float dot = wg[0] * g3[0] + wg[1] * g3[1] + wg[2] * g3[2];
+                Pack<float, VEC> gr;
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) {
+                    gr.v[k] = dot * zv.v[k];
+                    gz.v[k] += dot * e[c].v[k];
+                }
+                atomic_add_pack<float, VEC>(routed_out_row(g, base[c]) + ch, gr);
+            }
+        }
+    }
+    float* out = reinterpret_cast<float*>(static_cast<char*>(L.bases[region]) + L.out_y);
+    store_pack<float, VEC>(out + ((int64_t)L.rank * L.cap + j) * D + ch, gz);
+}
+
 }  // namespace ashb
 
 using namespace ashb;
@@ -346,15 +419,15 @@ int check_routed_layout(const RoutedLayout& L, int64_t mailbox_bytes, int64_t D)
     ASHB_REQUIRE(L.world >= 1 && L.world <= kRoutedMaxWorld && L.rank >= 0 && L.rank < L.world, "bad world / rank");
     ASHB_REQUIRE(L.cap >= 1 && L.cap <= (int64_t)kRowLocalMask, "a region holds 1 to 2^26 - 1 records");
     ASHB_REQUIRE(D >= 1 && D <= 16, "embedding_dim %lld not in 1..16", (long long)D);
-    ASHB_REQUIRE((L.inbox_x | L.inbox_z | L.out_y | L.out_gx) % 16 == 0 && L.counts % 4 == 0 && L.inbox_x >= 0,
+    ASHB_REQUIRE((L.inbox_x | L.inbox_z | L.out_y | L.out_gx | L.inbox_g) % 16 == 0 && L.counts % 4 == 0 && L.inbox_x >= 0,
                  "misaligned mailbox sections");
     const int64_t recs = (int64_t)L.world * L.cap;
-    const int64_t ends[5][2] = {{L.inbox_x, L.inbox_x + recs * 16}, {L.counts, L.counts + (int64_t)L.world * 4},
+    const int64_t ends[6][2] = {{L.inbox_x, L.inbox_x + recs * 16}, {L.counts, L.counts + (int64_t)L.world * 4},
                                 {L.inbox_z, L.inbox_z + recs * D * 4}, {L.out_y, L.out_y + recs * D * 4},
-                                {L.out_gx, L.out_gx + recs * 16}};
-    for (int a = 0; a < 5; ++a) {
+                                {L.out_gx, L.out_gx + recs * 16}, {L.inbox_g, L.inbox_g + recs * 16}};
+    for (int a = 0; a < 6; ++a) {
         ASHB_REQUIRE(ends[a][0] >= 0 && ends[a][1] <= mailbox_bytes, "a mailbox section exceeds the mailbox");
-        for (int b = a + 1; b < 5; ++b)
+        for (int b = a + 1; b < 6; ++b)
             ASHB_REQUIRE(ends[a][1] <= ends[b][0] || ends[b][1] <= ends[a][0], "mailbox sections overlap");
     }
     return ASHB_OK;
@@ -420,12 +493,12 @@ extern "C" {
 
 #define ASHB_ROUTED_LAYOUT_ARGS                                                                                  \
     void *const *peer_bases_dev, int64_t mailbox_bytes, int64_t inbox_x_offset, int64_t counts_offset,           \
-            int64_t inbox_z_offset, int64_t out_y_offset, int64_t out_gx_offset, int64_t region_capacity, int world, \
-            int rank
+            int64_t inbox_z_offset, int64_t out_y_offset, int64_t out_gx_offset, int64_t inbox_g_offset,             \
+            int64_t region_capacity, int world, int rank
 #define ASHB_ROUTED_LAYOUT                                                                                         \
     RoutedLayout {                                                                                                 \
-        peer_bases_dev, inbox_x_offset, counts_offset, inbox_z_offset, out_y_offset, out_gx_offset, region_capacity, \
-                world, rank                                                                                        \
+        peer_bases_dev, inbox_x_offset, counts_offset, inbox_z_offset, out_y_offset, out_gx_offset, inbox_g_offset,  \
+                region_capacity, world, rank                                                                       \
     }
 
 int ashb_routed_route(ashb_map* m, const float* x, int64_t n, double cell_size, const float* origin, int G,
@@ -495,7 +568,7 @@ int ashb_routed_send_z(const int32_t* where_dev, int64_t n, const float* z, int6
 }
 
 int ashb_routed_backward(ashb_map* m, int interp, const void* const* emb_bases_dev, void* const* grad_bases_dev,
-                         int need_grad_x, double cell_size, const float* origin, int G, const int32_t* nb_lut,
+                         int need_grad_x, int need_grad_embeddings, double cell_size, const float* origin, int G, const int32_t* nb_lut,
                          const uint32_t* row_of, int64_t n_emb, int64_t D, ASHB_ROUTED_LAYOUT_ARGS, void* stream) {
     const RoutedLayout L = ASHB_ROUTED_LAYOUT;
     if (int rc = check_routed_layout(L, mailbox_bytes, D)) return rc;
@@ -509,9 +582,12 @@ int ashb_routed_backward(ashb_map* m, int interp, const void* const* emb_bases_d
     const dim3 grid((unsigned)(((region_capacity << sh.lane_shift) + 255) / 256), (unsigned)world);
     const float scale = (float)(1.0 / cell_size);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    ASHB_ROUTED_VEC(sh, if (need_grad_x) {
-        routed_backward_kernel<VEC, true><<<grid, 256, 0, st>>>(g, L, scale, (int)D, sh.lane_shift, interp);
-    } else { routed_backward_kernel<VEC, false><<<grid, 256, 0, st>>>(g, L, scale, (int)D, sh.lane_shift, interp); });
+    ASHB_REQUIRE(need_grad_x || need_grad_embeddings, "nothing to compute");
+    ASHB_ROUTED_VEC(sh, if (need_grad_x && need_grad_embeddings) {
+        routed_backward_kernel<VEC, true, true><<<grid, 256, 0, st>>>(g, L, scale, (int)D, sh.lane_shift, interp);
+    } else if (need_grad_x) {
+        routed_backward_kernel<VEC, true, false><<<grid, 256, 0, st>>>(g, L, scale, (int)D, sh.lane_shift, interp);
+    } else { routed_backward_kernel<VEC, false, true><<<grid, 256, 0, st>>>(g, L, scale, (int)D, sh.lane_shift, interp); });
     ASHB_LAUNCH_CHECK();
     return ASHB_OK;
 }
@@ -524,6 +600,39 @@ int ashb_routed_unpack_grad_x(const int32_t* where_dev, int64_t n, float* grad_x
     ASHB_REQUIRE(n > 0 && where_dev && grad_x, "null buffer or negative count");
     routed_unpack_gx_kernel<<<(unsigned)((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(L, where_dev, n,
                                                                                                         grad_x);
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+int ashb_routed_send_g(const int32_t* where_dev, int64_t n, const float* grad_grad_x, int64_t D, ASHB_ROUTED_LAYOUT_ARGS,
+                       void* stream) {
+    const RoutedLayout L = ASHB_ROUTED_LAYOUT;
+    if (int rc = check_routed_layout(L, mailbox_bytes, D)) return rc;
+    if (n == 0) return ASHB_OK;
+    ASHB_REQUIRE(n > 0 && where_dev && grad_grad_x, "null buffer or negative count");
+    routed_send_g_kernel<<<(unsigned)((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(L, where_dev, n,
+                                                                                                     grad_grad_x);
+    ASHB_LAUNCH_CHECK();
+    return ASHB_OK;
+}
+
+int ashb_routed_backward_backward(ashb_map* m, int interp, const void* const* emb_bases_dev, void* const* grad_bases_dev,
+                                  double cell_size, const float* origin, int G, const int32_t* nb_lut,
+                                  const uint32_t* row_of, int64_t n_emb, int64_t D, ASHB_ROUTED_LAYOUT_ARGS,
+                                  void* stream) {
+    const RoutedLayout L = ASHB_ROUTED_LAYOUT;
+    if (int rc = check_routed_layout(L, mailbox_bytes, D)) return rc;
+    ASHB_REQUIRE(interp == ASHB_LINEAR || interp == ASHB_SMOOTH_STEP, "unknown interpolation code %d", interp);
+    ASHB_REQUIRE(emb_bases_dev != nullptr && grad_bases_dev != nullptr, "null shard table");
+    RoutedGrid g;
+    if (int rc = make_routed_grid(m, nb_lut, row_of, emb_bases_dev, grad_bases_dev, cell_size, origin, G, n_emb, &g))
+        return rc;
+    DeviceGuard guard(m->device);
+    const LaneShape sh = lane_shape(D);
+    const dim3 grid((unsigned)(((region_capacity << sh.lane_shift) + 255) / 256), (unsigned)world);
+    const float scale = (float)(1.0 / cell_size);
+    ASHB_ROUTED_VEC(sh, (routed_backward_backward_kernel<VEC><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+                                g, L, scale, (int)D, sh.lane_shift, interp)));
     ASHB_LAUNCH_CHECK();
     return ASHB_OK;
 }
