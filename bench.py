@@ -460,6 +460,17 @@ def measure_tsdf(ash, bw, device, peak, n_frames=100, H=480, W=640):
     assert grid.engine.size() == first_blocks
     blocks = grid.engine.size()
     status = grid.engine.backend.status()
+    # the same sequence with dilation 2 (the reference's setting for learned depth, demo/rgbd_fusion.py:312):
+    # the stated scene, fully covered, then holds about 200k blocks instead of 130k
+    wide_grid = ash.UnBoundedSparseDenseGrid(3, cap, 5, G, cell_size=cell, device=device)
+    wide = TSDFFusion(wide_grid, dilation=2)
+    wide_counter = torch.zeros(1, dtype=torch.int64, device=device)
+    torch.cuda.synchronize()
+    wide_ms = event_ms(lambda: wide.fuse_dataset(frames, counter=wide_counter))
+    wide_row = {"active_blocks": wide_grid.engine.size(), "frames_per_s": round(n_frames / (wide_ms * 1e-3), 1),
+                "ms_per_frame": round(wide_ms / n_frames, 4), "status": wide_grid.engine.backend.status(),
+                "cell_updates_per_s": round(int(wide_counter.item()) * G**3 / (wide_ms * 1e-3) / 1e9, 3)}
+    del wide, wide_grid
     # triangle mesh of the fused volume (sdf = channel 0, weight = channel 4)
     with torch.no_grad():
         sdf = grid.embeddings[..., 0].contiguous()
@@ -477,7 +488,7 @@ def measure_tsdf(ash, bw, device, peak, n_frames=100, H=480, W=640):
             "frames_per_s": round(n_frames / (ms * 1e-3), 1), "ms_per_frame": round(ms / n_frames, 4),
             "frames_per_s_one_call_per_frame": round(n_frames / (ms_per_call * 1e-3), 1),
             "active_blocks": blocks, "status": status, "cell_updates_per_s": round(updated_cells / (ms * 1e-3) / 1e9, 3),
-            "cell_updates_unit": "G cells/s",
+            "cell_updates_unit": "G cells/s", "dilation_2": wide_row,
             "marching_cubes": {"ms": round(mesh_ms, 3), "vertices": n_vert, "triangles": n_tri,
                                "cubes_per_s": round(blocks * G**3 / (mesh_ms * 1e-3) / 1e9, 3), "cubes_unit": "G cubes/s",
                                "achieved_gbs": round(mesh_bytes / (mesh_ms * 1e-3) / 1e9, 1),
@@ -600,6 +611,21 @@ def measure_sharded_table(ash, bw, device, dist, rank, world, n_blocks, n_querie
             "ms_per_step": round(out[True], 4), "value": round(world * n_queries / (out[True] * 1e-3) / 1e6, 2),
             "unit": "M queries/s (fwd+bwd, gradients complete on their owners)",
             "ms_per_step_embedding_gradient_only": round(out[False], 4)}
+
+
+def run_routed_alone(args, ash, bw, device):
+    """The routed step with every phase, on one GPU as a process group of one rank: the same kernels
+    and mailbox as on N GPUs, every owner being this rank.  One JSON line with the phase times."""
+    import torch.distributed as dist
+
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
+    grid, blocks = build_routed_grid(bw, device, args.blocks, args.queries, 0)
+    res = measure_routed(ash, bw, device, dist, 0, 1, grid, blocks, args.queries, args.steps, args.warmup, with_e2e=False)
+    print(json.dumps({"routed_alone": {"blocks": args.blocks, "queries": args.queries, "ms_per_step": round(res["ms_per_step"], 4),
+                                       "phase_ms": res["phase_ms_rank0"]}}))
+    dist.destroy_process_group()
 
 
 def build_routed_grid(bw, device, n_blocks, max_batch, seed_rank):
@@ -941,6 +967,8 @@ def main():
     ap.add_argument("--hash-keys", type=int, default=HASH_KEYS, help="profiling aid: fewer keys (default 50M)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-extras", action="store_true", help="skip the fusion / convolution / ray sampler side measurements")
+    ap.add_argument("--routed-alone", action="store_true",
+                    help="profiling aid: only the routed multi-GPU step, run on this one GPU as a world of one")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
@@ -966,6 +994,8 @@ def main():
     import ash
     import bench_workloads as bw
 
+    if args.routed_alone:
+        return run_routed_alone(args, ash, bw, device)
     peak, peak_kind = measured_peak_gbs()
     multi = None
     if dist is not None:

@@ -267,6 +267,39 @@ def sharded_grid_worker(rank, world, port):
         dist.destroy_process_group()
 
 
+def split_convolution_worker(rank, world, port, backend, use_cuda):
+    """The convolution with its output blocks divided among the ranks and gathered equals the
+    whole convolution on one rank, for a ragged division and both window sizes."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    if use_cuda:
+        torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank) if use_cuda else torch.device("cpu")
+    dist.init_process_group(backend, rank=rank, world_size=world)
+    try:
+        import ash
+        from ash.distributed import broadcast_state, split_convolution
+
+        G, D = 4, 3
+        grid = ash.SparseDenseGrid(3, 48, D, G, device)
+        r = torch.arange(-1, 2, dtype=torch.int32)
+        blocks = torch.stack(torch.meshgrid(r, r, r, indexing="ij"), -1).view(-1, 3)
+        blocks = torch.cat([blocks, torch.tensor([[4, 0, 0], [5, 0, 0]], dtype=torch.int32)])      # 29 blocks: ragged runs
+        grid.engine.insert_keys(blocks[torch.randperm(29, generator=torch.Generator().manual_seed(rank))].to(device))
+        with torch.no_grad():
+            grid.embeddings.copy_(torch.randn(grid.embeddings.shape, generator=torch.Generator().manual_seed(3 + rank)))
+        broadcast_state(grid, src=0)
+        _, idx = grid.engine.items()
+        for size in (3, 5):
+            w = torch.randn(size, size, size, D, generator=torch.Generator().manual_seed(size)).to(device)
+            whole = grid.convolution(grid.embeddings.detach(), w)
+            split = split_convolution(grid, grid.embeddings.detach(), w)
+            torch.testing.assert_close(split[idx], whole[idx], rtol=0, atol=0)
+            assert float(whole[idx].abs().max()) > 0.1
+    finally:
+        dist.destroy_process_group()
+
+
 def routed_grid_worker(rank, world, port):
     """A table sharded over the ranks with the queries routed to the owners answers like a replicated
     table, returns the same gradients for the positions, and leaves in every gradient shard the

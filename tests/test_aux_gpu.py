@@ -125,9 +125,9 @@ def test_ray_near_far_and_sample_vs_oracle(G):
     assert ri0.numel() == 0 and (p0 == 0).all()
 
 
-@pytest.mark.parametrize("whole_sequence", [False, True])
+@pytest.mark.parametrize("whole_sequence,dil", [(False, 1), (True, 1), (True, 2)])
 @pytest.mark.parametrize("H,W", [(120, 160)])
-def test_tsdf_fusion_vs_oracle(H, W, whole_sequence):
+def test_tsdf_fusion_vs_oracle(H, W, whole_sequence, dil):
     """Three frames fused by the two CUDA launches -- frame by frame through fuse_frame, or as one
     native call for the whole sequence through fuse_dataset -- vs the numpy restatement of
     fuse_frame: same set of blocks, and per block coordinate the same sdf / rgb / weight (bit-exact
@@ -135,7 +135,7 @@ def test_tsdf_fusion_vs_oracle(H, W, whole_sequence):
     import ash
     from ash.fusion import TSDFFusion
 
-    G, cell, dil, depth_max, n_emb = 8, 0.04, 1, 5.0, 6000
+    G, cell, depth_max, n_emb = 8, 0.04, 5.0, 6000 * dil
     grid = ash.UnBoundedSparseDenseGrid(3, n_emb, 5, G, cell_size=cell, device=DEV)
     fusion = TSDFFusion(grid, dil)
     ref = otsdf.OracleTSDF(n_emb, G, cell, dil)

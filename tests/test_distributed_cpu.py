@@ -29,3 +29,8 @@ def test_replicated_grid_gradient_sum_gloo():
 @pytest.mark.parametrize("world", [2, 3])
 def test_routed_grid_ownership_table_gloo(world):
     mp.spawn(dist_workers.row_table_worker, args=(world, _free_port()), nprocs=world, join=True)
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_split_convolution_gloo(world):
+    mp.spawn(dist_workers.split_convolution_worker, args=(world, _free_port(), "gloo", False), nprocs=world, join=True)

@@ -34,3 +34,7 @@ def test_sharded_grid_matches_replicated_grid():
 
 def test_routed_grid_matches_replicated_grid():
     mp.spawn(dist_workers.routed_grid_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
+def test_split_convolution_nccl():
+    mp.spawn(dist_workers.split_convolution_worker, args=(2, _free_port(), "nccl", True), nprocs=2, join=True)

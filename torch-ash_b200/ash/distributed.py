@@ -324,6 +324,30 @@ def allreduce_gradients(module: torch.nn.Module, group=None, sparse_below: float
             blocks[rows] = packed
 
 
+@torch.no_grad()
+def split_convolution(grid, inputs: torch.Tensor, weights: torch.Tensor, group=None) -> torch.Tensor:
+    """``grid.convolution(inputs, weights)`` over a replicated grid with the OUTPUT blocks divided
+    among the ranks: every rank convolves a contiguous run of the active blocks (in ascending index
+    order, so all ranks agree on the runs) and one all-gather of the compact rows completes the result
+    everywhere.  The structure and ``inputs`` must be the same on every rank (``broadcast_state``).
+    The reference is single-GPU (ash/grid.py:476-520 is the op)."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    _, indices = grid.engine.items()
+    blocks = torch.sort(indices.to(torch.int64))[0]
+    n = int(blocks.numel())
+    per = -(-n // world) if n else 0
+    mine = blocks[rank * per:(rank + 1) * per]
+    out = grid.convolution(inputs, weights, output_blocks=mine)
+    if world == 1 or n == 0:
+        return out
+    send = torch.zeros((per,) + tuple(inputs.shape[1:]), dtype=inputs.dtype, device=inputs.device)
+    send[: mine.numel()] = out[mine]
+    gathered = torch.empty((world * per,) + tuple(inputs.shape[1:]), dtype=inputs.dtype, device=inputs.device)
+    dist.all_gather_into_tensor(gathered, send, group=group)
+    out[blocks] = gathered[:n]            # run r of the gathered rows is rank r's run of ``blocks``
+    return out
+
+
 class _ShardedGridQuery(torch.autograd.Function):
     """Query of a table sharded over the ranks: rows read from, and gradient rows added into,
     their owners' memory."""

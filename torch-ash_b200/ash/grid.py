@@ -354,9 +354,12 @@ class SparseDenseGrid(ASHModule):
         weights = self._gaussian_weights(size, sigma).view(size, size, size, 1).repeat(1, 1, 1, channels)
         self.embeddings.copy_(self.convolution(self.embeddings, weights.to(self.embeddings.device)))
 
-    def convolution(self, inputs: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    def convolution(self, inputs: torch.Tensor, weights: torch.Tensor,
+                    output_blocks: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Depth-wise (2R+1)^3 convolution over the sparse-dense structure (ash/grid.py:476-520).
-        ``inputs`` (num_embeddings, G^3, C); ``weights`` (2R+1, 2R+1, 2R+1, C)."""
+        ``inputs`` (num_embeddings, G^3, C); ``weights`` (2R+1, 2R+1, 2R+1, C).  ``output_blocks``
+        (int64 block indices) restricts the work to those output rows -- the others are left
+        unwritten -- which is how ``ash.distributed.split_convolution`` divides it over ranks."""
         assert inputs.is_contiguous() and inputs.shape[:2] == self.embeddings.shape[:2]
         assert weights.is_contiguous() and weights.dim() == 4 and weights.shape[0] % 2 == 1
         radius = weights.shape[0] // 2
@@ -366,6 +369,8 @@ class SparseDenseGrid(ASHModule):
         grid_radius = (radius + self.grid_dim - 1) // self.grid_dim
         _, lut_g2g = self.construct_grid_neighbor_lut(grid_radius, bidirectional=True)
         _, _, grid_indices, cell_indices = self.items()
+        if output_blocks is not None:
+            grid_indices = output_blocks.to(torch.int64).view(-1, 1)
         if (self.tiled_convolution and inputs.is_cuda and inputs.dtype == torch.float32 and 1 <= radius <= self.grid_dim
                 and hasattr(backend, "convolution_forward_tiled")):
             # the per-cell tables of this window are pure arithmetic: one CTA per block works

@@ -38,14 +38,24 @@ __global__ void __launch_bounds__(256) find_kernel(Table t, const int32_t* __res
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     int k0, k1, k2, k3;
-    load_key<DIM>(keys, i, k0, k1, k2, k3);
+    if constexpr (FILTER) {   // the batch and the slots pass through L2 once (first out); the bit map stays
+        const int32_t* p = keys + i * DIM;
+        k0 = __ldcs(p);
+        k1 = DIM > 1 ? __ldcs(p + 1) : 0;
+        k2 = DIM > 2 ? __ldcs(p + 2) : 0;
+        k3 = 0;
+    } else {
+        load_key<DIM>(keys, i, k0, k1, k2, k3);
+    }
     uint32_t s = hash_key(k0, k1, k2, k3) & t.mask;
     int found = -1;
     bool absent = false;
     if constexpr (FILTER) absent = t.never_used(s);
     if (!absent) {
         for (uint32_t probe = 0; probe <= t.mask; ++probe) {
-            const Entry e = t.read_const(s);
+            Entry e;
+            if constexpr (FILTER) e = t.read_const_passing(s);
+            else e = t.read_const(s);
             if (e.val == kEmpty) break;
             if (e.val >= 0 && key_match(e, k0, k1, k2, k3)) {
                 found = e.val;
@@ -54,8 +64,13 @@ __global__ void __launch_bounds__(256) find_kernel(Table t, const int32_t* __res
             s = (s + 1) & t.mask;
         }
     }
-    indices[i] = found >= 0 ? (int64_t)found : 0;
-    masks[i] = (uint8_t)(found >= 0);
+    if constexpr (FILTER) {
+        __stcs(indices + i, found >= 0 ? (int64_t)found : 0);
+        __stcs(masks + i, (uint8_t)(found >= 0));
+    } else {
+        indices[i] = found >= 0 ? (int64_t)found : 0;
+        masks[i] = (uint8_t)(found >= 0);
+    }
 }
 
 // Sub-warp cooperative variant for 16-byte slots: 8 lanes serve one query and read the whole

@@ -64,6 +64,17 @@ struct Table16 {
                      : "l"(slots + s));
         return unpack(u);
     }
+    // The same with the line marked first to leave L2: beside the bit map, which a filtered find
+    // wants to keep there, a slot read once is only passing through.
+    __device__ __forceinline__ Entry read_const_passing(uint32_t s) const {
+        uint4 u;
+        uint64_t policy;
+        asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+        asm volatile("ld.global.nc.L2::cache_hint.L2::64B.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+                     : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w)
+                     : "l"(slots + s), "l"(policy));
+        return unpack(u);
+    }
     // Probe inside a mutating launch: read at L2, where the atomics resolve.
     __device__ __forceinline__ Entry read_fresh(uint32_t s) const {
         uint4 u;
@@ -90,7 +101,11 @@ struct Table16 {
         return true;
     }
     __device__ __forceinline__ bool never_used(uint32_t s) const {
-        return ((__ldg(occupied + (s >> 5)) >> (s & 31)) & 1u) == 0;
+        uint32_t word;   // marked last to leave L2
+        uint64_t policy;
+        asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+        asm volatile("ld.global.nc.L2::cache_hint.u32 %0, [%1], %2;" : "=r"(word) : "l"(occupied + (s >> 5)), "l"(policy));
+        return ((word >> (s & 31)) & 1u) == 0;
     }
     __device__ __forceinline__ int* val_ptr(uint32_t s) const {
         return reinterpret_cast<int*>(slots + s) + 3;
