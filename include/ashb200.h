@@ -578,7 +578,7 @@ int ashb_grid_query_backward_backward_sharded(ashb_map* map, int interp, const f
  * reference).  Every rank has a mailbox of mailbox_bytes, mapped into every other rank;
  * peer_bases_dev is a DEVICE array [world] with the address of every rank's mailbox as seen from
  * this rank.  Sections of a mailbox: inbox (int4 records {k0, k1, k2, position}; world regions of
- * region_capacity <= 2^26 records, region r written by rank r), counts int32 [world], answers int64
+ * region_capacity <= 2^26 records, region r written by rank r), counts int32 [world], answers int32
  * [world][region_capacity] (region o written by owner o, in the order of its inbox region).  A
  * batch has at most answer_capacity keys.  Keys of 1 to 3 columns.
  *   ashb_peer_route_keys   writes every key of the batch into its owner's inbox and publishes the
@@ -586,11 +586,12 @@ int ashb_grid_query_backward_backward_sharded(ashb_map* map, int interp, const f
  *                          (or NULL) receives owner << 26 | slot of every key (-1: dropped);
  *                          records beyond region_capacity are dropped and ASHB_STATUS_CAPACITY is
  *                          or-ed into status_dev.
- *   ashb_peer_find_answer  probes the records of this rank's inbox and stores the answers (global
- *                          index local * world + rank, or -1) into its region of the asker's
- *                          answers section, contiguously in inbox order.
+ *   ashb_peer_find_answer  probes the records of this rank's inbox and stores the answers (the
+ *                          owner's local index, or -1) into its region of the asker's answers
+ *                          section, contiguously in inbox order.
  *   ashb_peer_unpack_answers  the asker's side, after the second barrier: indices int64 [n] (0 for
- *                          a miss) and masks uint8 [n] gathered from its own answers section.
+ *                          a miss; global index = owner's local index * world + owner) and masks uint8
+ *                          [n] gathered from its own answers section.
  * The caller orders the two across the ranks (all route calls complete before any answer call
  * starts, all answer calls complete before the answers are read or the next route call starts),
  * e.g. with a small collective on the same stream between them.  No host synchronisation. */

@@ -98,7 +98,7 @@ class _PeerMailbox:
         inbox_bytes = world * self.max_batch * 16
         counts_offset = (inbox_bytes + 255) // 256 * 256
         answers_offset = counts_offset + 256
-        total = answers_offset + world * self.max_batch * 8
+        total = answers_offset + world * self.max_batch * 4   # the owner's local index per key
         self.buffer = symm.empty(total, dtype=torch.uint8, device=device)
         self.handle = symm.rendezvous(self.buffer, group if group is not None else dist.group.WORLD)
         self.layout = (self.handle.buffer_ptrs_dev, total, 0, counts_offset, answers_offset, self.max_batch,

@@ -4,11 +4,13 @@
 //
 //   route   every key is written straight into its OWNER's inbox as a 16-byte record
 //           {k0, k1, k2, position in the asker's batch}.  Rank r owns region r of every inbox, so
-//           the write position comes from a LOCAL cursor (one atomic per warp and owner) and no
-//           remote atomic is needed; the per-region counts are published to the owners at the end.
+//           the write position comes from a LOCAL cursor (one atomic per CTA and owner) and no
+//           remote atomic is needed; a CTA gathers the records of its 1024 keys per owner in shared
+//           memory and stores each owner's run as one contiguous segment; the per-region counts
+//           are published to the owners at the end.
 //   (stream-ordered barrier across the ranks: a collective on a one-element tensor)
-//   answer  every owner probes the records of its inbox and stores the answers (global index or
-//           -1) straight into the ASKER's answer buffer, region by region in inbox order, so that
+//   answer  every owner probes the records of its inbox and stores the answers (its local index
+//           or -1, 4 bytes) straight into the ASKER's answer buffer, region by region in inbox order, so that
 //           the peer stores of a warp are contiguous (scattered 8-byte peer stores ran at a
 //           fraction of the link rate); the asker remembers, per key, which owner and slot it
 //           used and gathers its answers locally afterwards.
@@ -39,7 +41,7 @@ struct PeerLayout {
     void* const* bases;      // device array [world]: base address of every rank's mailbox as mapped here
     int64_t inbox_offset;    // int4 records, world regions of region_capacity each
     int64_t counts_offset;   // int32 [world]: records in each region
-    int64_t answers_offset;  // int64 [world][region_capacity]: region o = answers of owner o, in inbox order
+    int64_t answers_offset;  // int32 [world][region_capacity]: region o = answers of owner o, in inbox order
     int64_t region_capacity;
     int64_t answer_capacity;
     int world, rank;
@@ -47,42 +49,73 @@ struct PeerLayout {
 
 constexpr int kWhereOwnerShift = 26;  // where[i] = owner << 26 | slot
 
+// One CTA routes a tile of kRouteTile keys.  Its records are first gathered per owner in shared
+// memory and then written out run by run, consecutive threads storing consecutive 16-byte records:
+// a link carries few long segments far better than many short ones (one store per lane to
+// whichever owner its key hashes to was 128 bytes per warp and owner at best).
+constexpr int kRouteKeysPerThread = 4;
+constexpr int kRouteTile = 256 * kRouteKeysPerThread;
+
 template <int DIM>
 __global__ void __launch_bounds__(256) peer_route_kernel(const int32_t* __restrict__ keys, int64_t n, PeerLayout L,
                                                          int* __restrict__ cursor, int32_t* __restrict__ where,
                                                          uint32_t* __restrict__ status) {
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    __shared__ int4 staged[kRouteTile];
+    __shared__ int cta_count[kPeerMaxWorld];   // records of this tile per owner
+    __shared__ int cta_base[kPeerMaxWorld];    // first slot of the tile's run in the owner's region
+    __shared__ int run_start[kPeerMaxWorld + 1];
     const int lane = threadIdx.x & 31;
-    const bool live = i < n;
-    int k0 = 0, k1 = 0, k2 = 0, k3 = 0;
-    if (live) load_key<DIM>(keys, i, k0, k1, k2, k3);
-    // lanes without a key take a negative owner of their own, so that they match nobody
-    const int owner = live ? peer_owner_of(k0, k1, k2, DIM, L.world) : -1 - lane;
-    // slots are reserved per CTA: the warps' per-owner groups meet in shared memory and one global
-    // atomic per (CTA, owner) follows, instead of one per (warp, owner)
-    __shared__ int cta_count[kPeerMaxWorld];
-    __shared__ int cta_base[kPeerMaxWorld];
+    const int64_t tile_first = (int64_t)blockIdx.x * kRouteTile;
     for (int o = threadIdx.x; o < L.world; o += blockDim.x) cta_count[o] = 0;
     __syncthreads();
-    const unsigned peers = __match_any_sync(0xffffffffu, owner);
-    const int leader = __ffs(peers) - 1;
-    int within = 0;
-    if (live && lane == leader) within = atomicAdd(&cta_count[owner], __popc(peers));
-    within = __shfl_sync(0xffffffffu, within, leader);
+    int4 rec[kRouteKeysPerThread];
+    int owner[kRouteKeysPerThread], within[kRouteKeysPerThread];
+#pragma unroll
+    for (int j = 0; j < kRouteKeysPerThread; ++j) {
+        const int64_t i = tile_first + j * 256 + threadIdx.x;
+        const bool live = i < n;
+        int k0 = 0, k1 = 0, k2 = 0, k3 = 0;
+        if (live) load_key<DIM>(keys, i, k0, k1, k2, k3);
+        rec[j] = make_int4(k0, k1, k2, (int)i);
+        // lanes without a key take a negative owner of their own, so that they match nobody
+        owner[j] = live ? peer_owner_of(k0, k1, k2, DIM, L.world) : -1 - lane;
+        const unsigned peers = __match_any_sync(0xffffffffu, owner[j]);
+        const int leader = __ffs(peers) - 1;
+        int base = 0;
+        if (live && lane == leader) base = atomicAdd(&cta_count[owner[j]], __popc(peers));
+        within[j] = __shfl_sync(0xffffffffu, base, leader) + __popc(peers & lanemask_lt());
+    }
     __syncthreads();
+    if (threadIdx.x == 0) {
+        int sum = 0;
+        for (int o = 0; o < L.world; ++o) {
+            run_start[o] = sum;
+            sum += cta_count[o];
+        }
+        run_start[L.world] = sum;
+    }
     for (int o = threadIdx.x; o < L.world; o += blockDim.x)
         cta_base[o] = cta_count[o] ? atomicAdd(&cursor[o], cta_count[o]) : 0;
     __syncthreads();
-    if (!live) return;
-    const int64_t slot = (int64_t)cta_base[owner] + within + __popc(peers & lanemask_lt());
-    if (slot >= L.region_capacity) {
-        atomicOr(status, ASHB_STATUS_CAPACITY);
-        if (where) where[i] = -1;
-        return;
+#pragma unroll
+    for (int j = 0; j < kRouteKeysPerThread; ++j) {
+        const int64_t i = tile_first + j * 256 + threadIdx.x;
+        if (i >= n) continue;
+        staged[run_start[owner[j]] + within[j]] = rec[j];
+        const int64_t slot = (int64_t)cta_base[owner[j]] + within[j];
+        if (slot >= L.region_capacity) atomicOr(status, ASHB_STATUS_CAPACITY);
+        if (where) where[i] = slot < L.region_capacity ? (int)((unsigned)owner[j] << kWhereOwnerShift | (unsigned)slot) : -1;
     }
-    int4* inbox = reinterpret_cast<int4*>(static_cast<char*>(L.bases[owner]) + L.inbox_offset);
-    inbox[(int64_t)L.rank * L.region_capacity + slot] = make_int4(k0, k1, k2, (int)i);
-    if (where) where[i] = (int)((unsigned)owner << kWhereOwnerShift | (unsigned)slot);
+    __syncthreads();
+    const int total = run_start[L.world];
+    for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+        int o = 0;
+        while (idx >= run_start[o + 1]) ++o;   // world <= 32 runs
+        const int64_t slot = (int64_t)cta_base[o] + (idx - run_start[o]);
+        if (slot >= L.region_capacity) continue;   // dropped and reported above
+        int4* inbox = reinterpret_cast<int4*>(static_cast<char*>(L.bases[o]) + L.inbox_offset);
+        inbox[(int64_t)L.rank * L.region_capacity + slot] = staged[idx];
+    }
 }
 
 __global__ void peer_publish_counts_kernel(PeerLayout L, const int* __restrict__ cursor) {
@@ -95,24 +128,52 @@ __global__ void peer_publish_counts_kernel(PeerLayout L, const int* __restrict__
 
 // A region holds region_capacity records in the worst case (every key of a batch to one owner) and
 // about 1 / world of that usually, so the kernels below do not launch one CTA per 256 possible
-// records: a fixed grid walks the tiles of 256 records of all regions and skips the empty ones.
+// records: a fixed grid walks the tiles of 256 records that the regions actually hold.  Every CTA
+// reads the region counts once and numbers the occupied tiles of all regions in one sequence.
+struct PeerTiles {
+    int count[kPeerMaxWorld];          // records per region (clamped to the capacity)
+    int64_t first[kPeerMaxWorld + 1];  // number of the first tile of every region in that sequence
+};
+
+__device__ __forceinline__ void peer_number_tiles(const PeerLayout& L, PeerTiles* tiles) {
+    if (threadIdx.x == 0) {
+        const int* counts = reinterpret_cast<const int*>(static_cast<const char*>(L.bases[L.rank]) + L.counts_offset);
+        int64_t sum = 0;
+        for (int r = 0; r < L.world; ++r) {
+            int64_t c = __ldcg(counts + r);
+            c = c < 0 ? 0 : (c > L.region_capacity ? L.region_capacity : c);
+            tiles->count[r] = (int)c;
+            tiles->first[r] = sum;
+            sum += (c + 255) / 256;
+        }
+        tiles->first[L.world] = sum;
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ int peer_region_of_tile(const PeerTiles& tiles, int64_t tile) {
+    int region = 0;
+    while (tile >= tiles.first[region + 1]) ++region;   // at most world <= 32 steps
+    return region;
+}
+
 __global__ void __launch_bounds__(256) peer_answer_kernel(Table16 t, PeerLayout L, bool filter) {
+    __shared__ PeerTiles tiles;
+    peer_number_tiles(L, &tiles);
     const char* mine = static_cast<const char*>(L.bases[L.rank]);
-    const int64_t tiles_per_region = (L.region_capacity + 255) / 256;
-    for (int64_t tile = blockIdx.x; tile < tiles_per_region * L.world; tile += gridDim.x) {
-        const int region = (int)(tile / tiles_per_region);  // the rank that asked
-        const int64_t j = (tile - (int64_t)region * tiles_per_region) * 256 + threadIdx.x;
-        const int count = __ldcg(reinterpret_cast<const int*>(mine + L.counts_offset) + region);
-        if (j >= count || j >= L.region_capacity) continue;
+    for (int64_t tile = blockIdx.x; tile < tiles.first[L.world]; tile += gridDim.x) {
+        const int region = peer_region_of_tile(tiles, tile);  // the rank that asked
+        const int64_t j = (tile - tiles.first[region]) * 256 + threadIdx.x;
+        if (j >= tiles.count[region]) continue;
         const int4 rec = __ldcg(reinterpret_cast<const int4*>(mine + L.inbox_offset) + (int64_t)region * L.region_capacity + j);
         const int idx = filter ? lookup_filtered(t, rec.x, rec.y, rec.z) : lookup(t, rec.x, rec.y, rec.z, 0);
-        const long long answer = idx >= 0 ? (long long)idx * L.world + L.rank : -1ll;
-        long long* answers = reinterpret_cast<long long*>(static_cast<char*>(L.bases[region]) + L.answers_offset);
-        answers[(int64_t)L.rank * L.region_capacity + j] = answer;   // my region of the asker's answers
+        int32_t* answers = reinterpret_cast<int32_t*>(static_cast<char*>(L.bases[region]) + L.answers_offset);
+        answers[(int64_t)L.rank * L.region_capacity + j] = idx >= 0 ? idx : -1;   // my region of the asker's answers
     }
 }
 
-// The asker's side: answer of key i = answers[owner(i)][slot(i)] of its own mailbox.
+// The asker's side: answer of key i = answers[owner(i)][slot(i)] of its own mailbox; the global index
+// of a key is its owner's local index * world + owner.
 __global__ void __launch_bounds__(256) peer_unpack_kernel(PeerLayout L, const int32_t* __restrict__ where, int64_t n,
                                                           int64_t* __restrict__ indices, uint8_t* __restrict__ masks) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -123,8 +184,10 @@ __global__ void __launch_bounds__(256) peer_unpack_kernel(PeerLayout L, const in
         const int owner = (int)((unsigned)w >> kWhereOwnerShift);
         const int64_t slot = (unsigned)w & ((1u << kWhereOwnerShift) - 1);
         const char* mine = static_cast<const char*>(L.bases[L.rank]);
-        if (owner < L.world && slot < L.region_capacity)
-            answer = __ldcg(reinterpret_cast<const long long*>(mine + L.answers_offset) + (int64_t)owner * L.region_capacity + slot);
+        if (owner < L.world && slot < L.region_capacity) {
+            const int local = __ldcg(reinterpret_cast<const int32_t*>(mine + L.answers_offset) + (int64_t)owner * L.region_capacity + slot);
+            if (local >= 0) answer = (long long)local * L.world + owner;
+        }
     }
     indices[i] = answer >= 0 ? answer : 0;
     masks[i] = (uint8_t)(answer >= 0);
@@ -134,15 +197,13 @@ __global__ void __launch_bounds__(256) peer_unpack_kernel(PeerLayout L, const in
 template <bool ERASE>
 __global__ void __launch_bounds__(256) peer_update_kernel(Table16 t, PeerLayout L, int32_t* __restrict__ heap,
                                                           int32_t* counter, int32_t capacity) {
+    __shared__ PeerTiles tiles;
+    peer_number_tiles(L, &tiles);
     const char* mine = static_cast<const char*>(L.bases[L.rank]);
-    const int64_t tiles_per_region = (L.region_capacity + 255) / 256;
-    for (int64_t tile = blockIdx.x; tile < tiles_per_region * L.world; tile += gridDim.x) {
-        const int region = (int)(tile / tiles_per_region);
-        const int64_t first = (tile - (int64_t)region * tiles_per_region) * 256;
-        const int count = __ldcg(reinterpret_cast<const int*>(mine + L.counts_offset) + region);
-        if (first >= count) continue;   // the same for every thread of the CTA: an empty tile
-        const int64_t j = first + threadIdx.x;
-        const bool live = j < count && j < L.region_capacity;
+    for (int64_t tile = blockIdx.x; tile < tiles.first[L.world]; tile += gridDim.x) {
+        const int region = peer_region_of_tile(tiles, tile);
+        const int64_t j = (tile - tiles.first[region]) * 256 + threadIdx.x;
+        const bool live = j < tiles.count[region];
         int4 rec = make_int4(0, 0, 0, 0);
         if (live) rec = __ldcg(reinterpret_cast<const int4*>(mine + L.inbox_offset) + (int64_t)region * L.region_capacity + j);
         // the whole CTA (256 threads) goes through the stack operations below: one atomic per CTA
@@ -172,7 +233,7 @@ static int check_layout(const PeerLayout& L, int64_t mailbox_bytes) {
                  "misaligned mailbox sections");
     const int64_t inbox_end = L.inbox_offset + (int64_t)L.world * L.region_capacity * 16;
     const int64_t counts_end = L.counts_offset + (int64_t)L.world * 4;
-    const int64_t answers_end = L.answers_offset + (int64_t)L.world * L.region_capacity * 8;
+    const int64_t answers_end = L.answers_offset + (int64_t)L.world * L.region_capacity * 4;
     ASHB_REQUIRE(inbox_end <= L.counts_offset && counts_end <= L.answers_offset && answers_end <= mailbox_bytes,
                  "mailbox sections overlap or exceed the mailbox");
     return ASHB_OK;
@@ -195,7 +256,7 @@ int ashb_peer_route_keys(const int32_t* keys, int64_t n, int key_dim, int world,
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     ASHB_CUDA_TRY(cudaMemsetAsync(cursor_dev, 0, (size_t)world * sizeof(int32_t), st));
     if (n > 0) {
-        const unsigned grid = (unsigned)((n + 255) / 256);
+        const unsigned grid = (unsigned)((n + kRouteTile - 1) / kRouteTile);
         switch (key_dim) {
             case 1: peer_route_kernel<1><<<grid, 256, 0, st>>>(keys, n, L, cursor_dev, where_dev, status_dev); break;
             case 2: peer_route_kernel<2><<<grid, 256, 0, st>>>(keys, n, L, cursor_dev, where_dev, status_dev); break;
