@@ -577,7 +577,7 @@ int ashb_grid_query_backward_backward_sharded(ashb_map* map, int interp, const f
  * find over the key-hash-partitioned map without a data collective (no counterpart in the
  * reference).  Every rank has a mailbox of mailbox_bytes, mapped into every other rank;
  * peer_bases_dev is a DEVICE array [world] with the address of every rank's mailbox as seen from
- * this rank.  Sections of a mailbox: inbox (int4 records {k0, k1, k2, position}; world regions of
+ * this rank.  Sections of a mailbox: inbox (12-byte records {k0, k1, k2}, unused columns zero; world regions of
  * region_capacity <= 2^26 records, region r written by rank r), counts int32 [world], answers int32
  * [world][region_capacity] (region o written by owner o, in the order of its inbox region).  A
  * batch has at most answer_capacity keys.  Keys of 1 to 3 columns.

@@ -95,7 +95,7 @@ class _PeerMailbox:
         import torch.distributed._symmetric_memory as symm
 
         self.world, self.rank, self.max_batch = world, rank, int(max_batch)
-        inbox_bytes = world * self.max_batch * 16
+        inbox_bytes = world * self.max_batch * 12            # {k0, k1, k2} per key
         counts_offset = (inbox_bytes + 255) // 256 * 256
         answers_offset = counts_offset + 256
         total = answers_offset + world * self.max_batch * 4   # the owner's local index per key

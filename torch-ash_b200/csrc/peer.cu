@@ -2,8 +2,8 @@
 // mailbox mapped into every other rank over NVLink).  The reference is single-GPU and has no
 // counterpart.  A find over the partitioned map is two launches per rank and no data collective:
 //
-//   route   every key is written straight into its OWNER's inbox as a 16-byte record
-//           {k0, k1, k2, position in the asker's batch}.  Rank r owns region r of every inbox, so
+//   route   every key is written straight into its OWNER's inbox as a 12-byte record
+//           {k0, k1, k2} (unused columns zero).  Rank r owns region r of every inbox, so
 //           the write position comes from a LOCAL cursor (one atomic per CTA and owner) and no
 //           remote atomic is needed; a CTA gathers the records of its 1024 keys per owner in shared
 //           memory and stores each owner's run as one contiguous segment; the per-region counts
@@ -39,7 +39,7 @@ __device__ __forceinline__ int peer_owner_of(int k0, int k1, int k2, int dim, in
 
 struct PeerLayout {
     void* const* bases;      // device array [world]: base address of every rank's mailbox as mapped here
-    int64_t inbox_offset;    // int4 records, world regions of region_capacity each
+    int64_t inbox_offset;    // int32 [world][region_capacity][3]: 12-byte records, region r written by rank r
     int64_t counts_offset;   // int32 [world]: records in each region
     int64_t answers_offset;  // int32 [world][region_capacity]: region o = answers of owner o, in inbox order
     int64_t region_capacity;
@@ -49,10 +49,20 @@ struct PeerLayout {
 
 constexpr int kWhereOwnerShift = 26;  // where[i] = owner << 26 | slot
 
+struct PeerKey {
+    int x, y, z;
+};
+// Record j of region `region` of this rank's inbox.
+__device__ __forceinline__ PeerKey peer_read_key(const PeerLayout& L, int region, int64_t j) {
+    const int* rec = reinterpret_cast<const int*>(static_cast<const char*>(L.bases[L.rank]) + L.inbox_offset) +
+                     ((int64_t)region * L.region_capacity + j) * 3;
+    return PeerKey{__ldcg(rec), __ldcg(rec + 1), __ldcg(rec + 2)};
+}
+
 // One CTA routes a tile of kRouteTile keys.  Its records are first gathered per owner in shared
-// memory and then written out run by run, consecutive threads storing consecutive 16-byte records:
-// a link carries few long segments far better than many short ones (one store per lane to
-// whichever owner its key hashes to was 128 bytes per warp and owner at best).
+// memory and then written out run by run, consecutive threads storing consecutive 4-byte words of
+// the run's 12-byte records: a link carries few long segments far better than many short ones (one
+// store per lane to whichever owner its key hashes to was 128 bytes per warp and owner at best).
 constexpr int kRouteKeysPerThread = 4;
 constexpr int kRouteTile = 256 * kRouteKeysPerThread;
 
@@ -60,7 +70,8 @@ template <int DIM>
 __global__ void __launch_bounds__(256) peer_route_kernel(const int32_t* __restrict__ keys, int64_t n, PeerLayout L,
                                                          int* __restrict__ cursor, int32_t* __restrict__ where,
                                                          uint32_t* __restrict__ status) {
-    __shared__ int4 staged[kRouteTile];
+    __shared__ int staged[kRouteTile * 3];
+    __shared__ unsigned char staged_owner[kRouteTile];
     __shared__ int cta_count[kPeerMaxWorld];   // records of this tile per owner
     __shared__ int cta_base[kPeerMaxWorld];    // first slot of the tile's run in the owner's region
     __shared__ int run_start[kPeerMaxWorld + 1];
@@ -68,7 +79,7 @@ __global__ void __launch_bounds__(256) peer_route_kernel(const int32_t* __restri
     const int64_t tile_first = (int64_t)blockIdx.x * kRouteTile;
     for (int o = threadIdx.x; o < L.world; o += blockDim.x) cta_count[o] = 0;
     __syncthreads();
-    int4 rec[kRouteKeysPerThread];
+    int rec[kRouteKeysPerThread][3];
     int owner[kRouteKeysPerThread], within[kRouteKeysPerThread];
 #pragma unroll
     for (int j = 0; j < kRouteKeysPerThread; ++j) {
@@ -76,7 +87,9 @@ __global__ void __launch_bounds__(256) peer_route_kernel(const int32_t* __restri
         const bool live = i < n;
         int k0 = 0, k1 = 0, k2 = 0, k3 = 0;
         if (live) load_key<DIM>(keys, i, k0, k1, k2, k3);
-        rec[j] = make_int4(k0, k1, k2, (int)i);
+        rec[j][0] = k0;
+        rec[j][1] = k1;
+        rec[j][2] = k2;
         // lanes without a key take a negative owner of their own, so that they match nobody
         owner[j] = live ? peer_owner_of(k0, k1, k2, DIM, L.world) : -1 - lane;
         const unsigned peers = __match_any_sync(0xffffffffu, owner[j]);
@@ -101,20 +114,24 @@ __global__ void __launch_bounds__(256) peer_route_kernel(const int32_t* __restri
     for (int j = 0; j < kRouteKeysPerThread; ++j) {
         const int64_t i = tile_first + j * 256 + threadIdx.x;
         if (i >= n) continue;
-        staged[run_start[owner[j]] + within[j]] = rec[j];
+        const int at = run_start[owner[j]] + within[j];
+        staged[3 * at] = rec[j][0];
+        staged[3 * at + 1] = rec[j][1];
+        staged[3 * at + 2] = rec[j][2];
+        staged_owner[at] = (unsigned char)owner[j];
         const int64_t slot = (int64_t)cta_base[owner[j]] + within[j];
         if (slot >= L.region_capacity) atomicOr(status, ASHB_STATUS_CAPACITY);
         if (where) where[i] = slot < L.region_capacity ? (int)((unsigned)owner[j] << kWhereOwnerShift | (unsigned)slot) : -1;
     }
     __syncthreads();
-    const int total = run_start[L.world];
-    for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
-        int o = 0;
-        while (idx >= run_start[o + 1]) ++o;   // world <= 32 runs
-        const int64_t slot = (int64_t)cta_base[o] + (idx - run_start[o]);
+    const int total_words = 3 * run_start[L.world];
+    for (int word = threadIdx.x; word < total_words; word += blockDim.x) {
+        const int at = word / 3;
+        const int o = staged_owner[at];
+        const int64_t slot = (int64_t)cta_base[o] + (at - run_start[o]);
         if (slot >= L.region_capacity) continue;   // dropped and reported above
-        int4* inbox = reinterpret_cast<int4*>(static_cast<char*>(L.bases[o]) + L.inbox_offset);
-        inbox[(int64_t)L.rank * L.region_capacity + slot] = staged[idx];
+        int* inbox = reinterpret_cast<int*>(static_cast<char*>(L.bases[o]) + L.inbox_offset);
+        inbox[((int64_t)L.rank * L.region_capacity + slot) * 3 + (word - 3 * at)] = staged[word];
     }
 }
 
@@ -165,7 +182,7 @@ __global__ void __launch_bounds__(256) peer_answer_kernel(Table16 t, PeerLayout 
         const int region = peer_region_of_tile(tiles, tile);  // the rank that asked
         const int64_t j = (tile - tiles.first[region]) * 256 + threadIdx.x;
         if (j >= tiles.count[region]) continue;
-        const int4 rec = __ldcg(reinterpret_cast<const int4*>(mine + L.inbox_offset) + (int64_t)region * L.region_capacity + j);
+        const PeerKey rec = peer_read_key(L, region, j);
         const int idx = filter ? lookup_filtered(t, rec.x, rec.y, rec.z) : lookup(t, rec.x, rec.y, rec.z, 0);
         int32_t* answers = reinterpret_cast<int32_t*>(static_cast<char*>(L.bases[region]) + L.answers_offset);
         answers[(int64_t)L.rank * L.region_capacity + j] = idx >= 0 ? idx : -1;   // my region of the asker's answers
@@ -204,8 +221,8 @@ __global__ void __launch_bounds__(256) peer_update_kernel(Table16 t, PeerLayout 
         const int region = peer_region_of_tile(tiles, tile);
         const int64_t j = (tile - tiles.first[region]) * 256 + threadIdx.x;
         const bool live = j < tiles.count[region];
-        int4 rec = make_int4(0, 0, 0, 0);
-        if (live) rec = __ldcg(reinterpret_cast<const int4*>(mine + L.inbox_offset) + (int64_t)region * L.region_capacity + j);
+        PeerKey rec{0, 0, 0};
+        if (live) rec = peer_read_key(L, region, j);
         // the whole CTA (256 threads) goes through the stack operations below: one atomic per CTA
         if (ERASE) {
             push_freed_index_cta(live ? tombstone_key(t, rec.x, rec.y, rec.z, 0) : -1, heap, counter);
@@ -231,7 +248,7 @@ static int check_layout(const PeerLayout& L, int64_t mailbox_bytes) {
                  "bad capacities (a region holds at most 2^26 records)");
     ASHB_REQUIRE(L.inbox_offset >= 0 && L.inbox_offset % 16 == 0 && L.counts_offset % 4 == 0 && L.answers_offset % 8 == 0,
                  "misaligned mailbox sections");
-    const int64_t inbox_end = L.inbox_offset + (int64_t)L.world * L.region_capacity * 16;
+    const int64_t inbox_end = L.inbox_offset + (int64_t)L.world * L.region_capacity * 12;
     const int64_t counts_end = L.counts_offset + (int64_t)L.world * 4;
     const int64_t answers_end = L.answers_offset + (int64_t)L.world * L.region_capacity * 4;
     ASHB_REQUIRE(inbox_end <= L.counts_offset && counts_end <= L.answers_offset && answers_end <= mailbox_bytes,
