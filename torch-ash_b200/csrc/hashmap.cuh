@@ -351,8 +351,15 @@ __device__ __forceinline__ int lookup(const Table& t, int k0, int k1, int k2, in
 // The same for 16-byte-slot tables that are far larger than L2: the occupancy bit of the home slot
 // is read first, and a key whose home slot never held anything is reported absent without a probe.
 __device__ __forceinline__ int lookup_filtered(const Table16& t, int k0, int k1, int k2) {
-    if (t.occupied != nullptr && t.never_used(hash_key(k0, k1, k2, 0) & t.mask)) return -1;
-    return lookup(t, k0, k1, k2, 0);
+    uint32_t s = hash_key(k0, k1, k2, 0) & t.mask;
+    if (t.occupied != nullptr && t.never_used(s)) return -1;
+    for (uint32_t probe = 0; probe <= t.mask; ++probe) {
+        const Entry e = t.read_const_passing(s);   // the slots pass through L2, the bit map stays
+        if (e.val == kEmpty) return -1;
+        if (e.val >= 0 && key_match(e, k0, k1, k2, 0)) return e.val;
+        s = (s + 1) & t.mask;
+    }
+    return -1;
 }
 
 }  // namespace ashb
