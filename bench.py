@@ -628,12 +628,13 @@ def run_routed_alone(args, ash, bw, device):
     dist.destroy_process_group()
 
 
-def build_routed_grid(bw, device, n_blocks, max_batch, seed_rank):
-    """The microbench table split over the ranks by block (owner = hash of the coarse block
-    coordinate), each rank's shard filled with its own values."""
+def build_routed_grid(bw, device, n_blocks, max_batch, seed_rank, partition="morton"):
+    """The microbench table split over the ranks by block (equal runs of the blocks in Z order, or a
+    hash of the coarse block coordinate), each rank's shard filled with its own values."""
     from ash.distributed import RoutedSparseDenseGrid
 
-    grid = RoutedSparseDenseGrid(3, n_blocks, EMB_DIM, GRID_DIM, cell_size=1.0, device=device, max_batch=max_batch)
+    grid = RoutedSparseDenseGrid(3, n_blocks, EMB_DIM, GRID_DIM, cell_size=1.0, device=device, max_batch=max_batch,
+                                 partition=partition)
     blocks = bw.block_coords_blob(n_blocks, device)
     grid.engine.insert_keys(blocks)
     grid.sync_structure_(src=0)
@@ -1015,6 +1016,14 @@ def main():
         multi["table_bytes_per_gpu"] = rgrid.embeddings.numel() * 4
         del rgrid, rblocks
         torch.cuda.empty_cache()
+        # the same step with ownership by hash of the coarse block coordinate, for comparison
+        rgrid, rblocks = build_routed_grid(bw, device, N_BLOCKS, N_QUERIES, rank, partition="hash")
+        hashed = measure_routed(ash, bw, device, dist, rank, world, rgrid, rblocks, N_QUERIES, min(args.steps, 10), 3,
+                                with_e2e=False)
+        multi["hash_partition"] = {"ms_per_step": round(hashed["ms_per_step"], 4), "coarse_shift": rgrid.coarse_shift,
+                                   "phase_ms_rank0": hashed["phase_ms_rank0"]}
+        del rgrid, rblocks, hashed
+        torch.cuda.empty_cache()
     grid, blocks = build_grid(ash, bw, device, N_BLOCKS)
     if dist is not None:
         # replicas must agree on which row is which block before their gradients can be summed
@@ -1265,8 +1274,8 @@ def main():
                             "backward; gradient shards complete), positions from pinned host memory through a "
                             "double-buffered loader, loss read back; max over ranks"}})
         line["config"]["parallelism"] = (
-            f"table of {N_BLOCKS} blocks split over the {world} ranks by block (owner = hash of the coarse block "
-            "coordinate), 4M queries per rank routed to the owners of their blocks over NVLink peer memory (16-byte "
+            f"table of {N_BLOCKS} blocks split over the {world} ranks by block (equal runs of the blocks in Z order), "
+            "4M queries per rank routed to the owners of their blocks over NVLink peer memory (16-byte "
             "record out, result row back; dL/dy out, dL/dx back), owners gather / scatter in their own HBM; every "
             "gradient shard is complete when the step ends, no all-reduce")
         line["config"]["workload"] = line["config"]["workload"].replace(
@@ -1278,6 +1287,7 @@ def main():
             "phase_ms_rank0": weak["phase_ms_rank0"], "table_bytes_per_gpu": multi["table_bytes_per_gpu"],
             "nvlink_bytes_per_rank_per_step": nv,
             "nvlink_GBs_per_gpu_per_direction_over_the_step": round(nv / (weak["ms_per_step"] * 1e-3) / 1e9, 1),
+            "ownership_by_hash_of_coarse_block": multi["hash_partition"],
             "note": "phases of one step as rank 0 sees them (CUDA events); barrier = one-element NCCL all-reduce, its "
                     "time includes waiting for the slowest rank"}
         line["strong_scaling"] = {

@@ -317,11 +317,12 @@ def routed_grid_worker(rank, world, port):
 
         G, n_blocks, cell = 4, 301, 0.05
         blocks = bw.block_coords_blob(n_blocks, device, n_blobs=3, seed=7)
-        for D, interpolation in ((8, "linear"), (16, "smooth_step"), (3, "linear")):
+        for D, interpolation, partition in ((8, "linear", "morton"), (16, "smooth_step", "hash"), (3, "linear", "morton")):
             full = torch.randn(n_blocks, G**3, D, generator=torch.Generator().manual_seed(1)).to(device)
             ref = ash.UnBoundedSparseDenseGrid(3, n_blocks + 40, D, G, cell_size=cell, device=device)
             ref.engine.insert_keys(blocks[torch.randperm(n_blocks, device=device)])   # an order of its own per rank
-            routed = RoutedSparseDenseGrid(3, n_blocks + 40, D, G, cell_size=cell, device=device, max_batch=8192)
+            routed = RoutedSparseDenseGrid(3, n_blocks + 40, D, G, cell_size=cell, device=device, max_batch=8192,
+                                           partition=partition)
             routed.engine.insert_keys(blocks)
             routed.sync_structure_(src=0)
             idx_ref, _ = ref.engine.find(blocks)
@@ -427,7 +428,8 @@ def row_table_worker(rank, world, port):
     try:
         import bench_workloads as bw
         from ash import ASHEngine
-        from ash.distributed import block_row_table, broadcast_state, coarse_owner_of
+        from ash.distributed import (block_row_table, broadcast_state, coarse_owner_of, morton_code,
+                                     morton_owner_of)
 
         cpu = torch.device("cpu")
         n_blocks, cap = 3000, 3500
@@ -437,21 +439,30 @@ def row_table_worker(rank, world, port):
         broadcast_state(eng, src=0)
         coords, idx = eng.items()
         rows_per_rank = int(-(-cap // world) * 1.25) + 64
-        row_of, per_owner, shift = block_row_table(coords, idx, world, cap, rows_per_rank)
-        assert shift in (0, 1, 2, 3) and int(per_owner.max()) <= 1.08 * n_blocks / world or shift == 0
-        gathered = [torch.empty_like(row_of) for _ in range(world)]
-        dist.all_gather(gathered, row_of)
-        assert all(torch.equal(g, gathered[0]) for g in gathered)
-        assert int(per_owner.sum()) == n_blocks and int(per_owner.min()) > 0
-        owner, local = row_of[idx] >> 26, row_of[idx] & ((1 << 26) - 1)
-        assert torch.equal(owner, coarse_owner_of(coords, world, shift))
-        for o in range(world):
-            rows = torch.sort(local[owner == o])[0]
-            assert torch.equal(rows, torch.arange(int(per_owner[o])))      # a shard's rows are 0 .. count-1, each used once
-        # co-ownership of +x neighbours
-        find_idx, ok = eng.find((coords + torch.tensor([1, 0, 0], dtype=torch.int32)).contiguous())
-        same = (row_of[find_idx[ok]] >> 26) == owner[ok]
-        assert float(same.float().mean()) > (0.8 if shift >= 2 else 0.3)
+        for partition in ("hash", "morton"):
+            row_of, per_owner, shift = block_row_table(coords, idx, world, cap, rows_per_rank, partition=partition)
+            gathered = [torch.empty_like(row_of) for _ in range(world)]
+            dist.all_gather(gathered, row_of)
+            assert all(torch.equal(g, gathered[0]) for g in gathered)
+            assert int(per_owner.sum()) == n_blocks and int(per_owner.min()) > 0
+            owner, local = row_of[idx] >> 26, row_of[idx] & ((1 << 26) - 1)
+            if partition == "hash":
+                assert shift in (0, 1, 2, 3) and int(per_owner.max()) <= 1.08 * n_blocks / world or shift == 0
+                assert torch.equal(owner, coarse_owner_of(coords, world, shift))
+            else:
+                # equal runs of the blocks in Z order: counts equal to within one run's rounding
+                assert shift == -1 and int(per_owner.max()) == -(-n_blocks // world)
+                assert torch.equal(owner, morton_owner_of(coords, world))
+                code = morton_code(coords)
+                for o in range(world - 1):      # the runs do not interleave in that order
+                    assert int(code[owner == o].max()) < int(code[owner == o + 1].min())
+            for o in range(world):
+                rows = torch.sort(local[owner == o])[0]
+                assert torch.equal(rows, torch.arange(int(per_owner[o])))      # a shard's rows are 0 .. count-1, each used once
+            # co-ownership of +x neighbours
+            find_idx, ok = eng.find((coords + torch.tensor([1, 0, 0], dtype=torch.int32)).contiguous())
+            same = (row_of[find_idx[ok]] >> 26) == owner[ok]
+            assert float(same.float().mean()) > (0.9 if partition == "morton" else 0.8 if shift >= 2 else 0.3)
         with_error = False
         try:
             block_row_table(coords, idx, world, cap, 10)

@@ -498,24 +498,62 @@ def coarse_owner_of(block_coords: torch.Tensor, world_size: int, coarse_shift: i
     return owner_of(torch.bitwise_right_shift(block_coords.to(torch.int64), coarse_shift).to(torch.int32), world_size)
 
 
+def morton_code(block_coords: torch.Tensor) -> torch.Tensor:
+    """Z-order code (int64) of int block coordinates (n, 3), taken relative to their minimum: the bits of
+    x, y and z interleaved, 21 bits per axis.  Blocks that are close in space are close in this order."""
+    c = block_coords.to(torch.int64)
+    c = c - c.min(dim=0)[0] if c.shape[0] else c
+    code = torch.zeros(c.shape[0], dtype=torch.int64, device=c.device)
+    for axis in range(3):
+        v = c[:, axis] & 0x1FFFFF
+        v = (v | (v << 32)) & 0x1F00000000FFFF
+        v = (v | (v << 16)) & 0x1F0000FF0000FF
+        v = (v | (v << 8)) & 0x100F00F00F00F00F
+        v = (v | (v << 4)) & 0x10C30C30C30C30C3
+        v = (v | (v << 2)) & 0x1249249249249249
+        code |= v << axis
+    return code
+
+
+def morton_owner_of(block_coords: torch.Tensor, world_size: int) -> torch.Tensor:
+    """Owner rank per BLOCK when the blocks, in Z order, are cut into ``world_size`` runs of equal length:
+    every rank owns a compact region of space (few blocks have a neighbour on another rank) and the same
+    number of blocks to within one."""
+    n = block_coords.shape[0]
+    order = torch.argsort(morton_code(block_coords), stable=True)
+    per = max(1, -(-n // world_size))
+    owner = torch.empty(n, dtype=torch.int64, device=block_coords.device)
+    owner[order] = torch.arange(n, device=block_coords.device) // per
+    return owner
+
+
 def block_row_table(coords: torch.Tensor, indices: torch.Tensor, world_size: int, num_embeddings: int,
-                    rows_per_rank: int, coarse_shift: Optional[int] = None, balance: float = 1.08):
+                    rows_per_rank: int, coarse_shift: Optional[int] = None, balance: float = 1.08,
+                    partition: str = "hash"):
     """Which rank owns which block and where: from the active blocks' coordinates and indices (the same
     on every rank after ``broadcast_state``) returns ``(row_of int64 (num_embeddings,), per_owner int64
     (world,), coarse_shift)`` with ``row_of[index] = owner << 26 | row in the owner's shard`` (0 for
     inactive indices) and the number of blocks per owner.  Rows are handed out in ascending index
     order, so every rank derives the same table.
 
-    Ownership is a hash of the block coordinate shifted right by ``coarse_shift`` bits per axis.  Large
-    coarse cells keep neighbouring blocks on one rank but balance badly when there are few of them, so
-    with ``coarse_shift=None`` the largest shift of 3, 2, 1, 0 is taken for which no rank owns more
-    than ``balance`` times the mean (and its blocks fit its shard); the step waits for the slowest rank."""
+    ``partition="morton"``: equal runs of the blocks in Z order (``morton_owner_of``; the returned shift
+    is -1).  Compact regions, so few corner rows live on another rank, and equal block counts; a batch
+    that concentrates on one region of space loads that region's rank alone.
+    ``partition="hash"``: ownership is a hash of the block coordinate shifted right by ``coarse_shift``
+    bits per axis, which spreads any batch over all ranks.  Large coarse cells keep neighbouring blocks
+    on one rank but balance badly when there are few of them, so with ``coarse_shift=None`` the largest
+    shift of 3, 2, 1, 0 is taken for which no rank owns more than ``balance`` times the mean (and its
+    blocks fit its shard); the step waits for the slowest rank."""
+    if partition not in ("hash", "morton"):
+        raise ValueError(f"unknown partition {partition!r}")
     n = indices.numel()
     order = torch.argsort(indices)
     coords, indices = coords[order], indices[order]
     shifts = (3, 2, 1, 0) if coarse_shift is None else (coarse_shift,)
+    if partition == "morton":
+        shifts = (-1,)
     for shift in shifts:
-        owner = coarse_owner_of(coords, world_size, shift)
+        owner = morton_owner_of(coords, world_size) if partition == "morton" else coarse_owner_of(coords, world_size, shift)
         one_hot = torch.nn.functional.one_hot(owner, world_size)
         per_owner = one_hot.sum(dim=0)
         largest = int(per_owner.max()) if n else 0
@@ -643,7 +681,8 @@ class _RoutedGridQueryBackward(torch.autograd.Function):
 
 class RoutedSparseDenseGrid(UnBoundedSparseDenseGrid):
     """A sparse-dense grid whose table is SPLIT over the ranks of one box, queried by sending every
-    position to the rank that owns its block (``coarse_owner_of``): that rank interpolates in its own
+    position to the rank that owns its block (``block_row_table``: by default equal runs of the blocks in
+    Z order, ``partition="hash"`` for a hash of the coarse block coordinate): that rank interpolates in its own
     memory and sends the result row back; in the backward pass it receives dL/dy, adds the gradient
     rows into ITS gradient shard and returns dL/dx.  A query crosses NVLink as 16 + 4 D bytes each
     way instead of the ~64 D bytes of its rows; there is no gradient all-reduce, and each rank holds
@@ -660,8 +699,10 @@ class RoutedSparseDenseGrid(UnBoundedSparseDenseGrid):
     on dL/dx trains the embeddings through a double backward round)."""
 
     def __init__(self, in_dim: int, num_embeddings: int, embedding_dim: int, grid_dim: int, cell_size: float = 1.0,
-                 device=None, group=None, max_batch: int = 1 << 20, region_slack: float = 1.5, shard_slack: float = 1.25):
+                 device=None, group=None, max_batch: int = 1 << 20, region_slack: float = 1.5, shard_slack: float = 1.25,
+                 partition: str = "morton"):
         self.group = group
+        self.partition = partition
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         assert self.world <= 32, "at most 32 ranks"
@@ -709,7 +750,8 @@ class RoutedSparseDenseGrid(UnBoundedSparseDenseGrid):
         broadcast_state(self.engine, src=src, group=self.group)
         self.construct_grid_neighbor_lut_(radius=1, bidirectional=False)
         coords, idx = self.engine.items()
-        row_of, _, self.coarse_shift = block_row_table(coords, idx, self.world, self.num_embeddings, self._rows_per_rank)
+        row_of, _, self.coarse_shift = block_row_table(coords, idx, self.world, self.num_embeddings, self._rows_per_rank,
+                                                       partition=self.partition)
         self._row_of = row_of.to(torch.int32)          # bit pattern of the uint32 the kernels read (owner < 32)
         mine = torch.sort(idx[(row_of[idx] >> 26) == self.rank])[0]
         self._owned_blocks = mine                      # global block indices of this shard's rows, in row order
