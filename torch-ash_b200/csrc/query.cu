@@ -458,7 +458,7 @@ __global__ void __launch_bounds__(256, ASHB_BWD_MIN_BLOCKS) query_backward_backw
 // and 8 products at once and runs best with room (2), the first-order pass with d/dx at 3, the
 // write-only pass without the row reads at 4.
 template <typename T, int VEC, bool SECOND, bool NEED_GO>
-__global__ void __launch_bounds__(256, SECOND ? 2 : (NEED_GO ? 3 : 4)) query_backward_rows_kernel(
+__global__ void __launch_bounds__(256, SECOND ? 3 : (NEED_GO ? 3 : 4)) query_backward_rows_kernel(
         const T* __restrict__ z, const T* __restrict__ emb, FusedSource src, const T* __restrict__ ggo,
         int64_t* __restrict__ idx_out, T* __restrict__ rows_out, T* __restrict__ side, T go_scale, int64_t n, int D,
         int lane_shift, int interp) {
@@ -469,6 +469,18 @@ __global__ void __launch_bounds__(256, SECOND ? 2 : (NEED_GO ? 3 : 4)) query_bac
     const int ch = lane * VEC;
     const bool live = q < n;
     const bool has_ch = ch < D;
+    // The records of a warp's queries are one contiguous stretch of the list (4 KB of rows when a lane
+    // holds 16 bytes of a row and the lanes cover it exactly), but a lane produces them corner by
+    // corner: 64 bytes here, 64 bytes half a kilobyte on.  So the warp first lays its records out in
+    // shared memory and then copies them out with every store instruction covering 512 contiguous
+    // bytes.  16-byte chunk j of the warp's stretch sits at j ^ ((its query * lanes) & 7): the lanes of
+    // a quarter warp then write different banks, and a row of 8 chunks stays a row for the copy.
+    __shared__ uint4 stage_rows[8][256];
+    __shared__ int64_t stage_idx[8][2][64];
+    const bool staged = sizeof(T) * VEC == 16 && D == lanes * VEC && lanes >= 4;
+    const int warp = threadIdx.x >> 5, warp_lane = threadIdx.x & 31;
+    const int ql = warp_lane >> lane_shift;   // query within the warp
+    const int swizzle = (ql * lanes) & 7;
     T go[3] = {0, 0, 0};
     Pack<T, VEC> gz;
 #pragma unroll
@@ -478,9 +490,26 @@ __global__ void __launch_bounds__(256, SECOND ? 2 : (NEED_GO ? 3 : 4)) query_bac
         float off[3];
         const int gi = src.locate(q, lane, cell, off);
         const bool ok = gi >= 0 && gi < src.n_emb && corner_blocks_cells(src.nb_lut, gi, cell, src.G, src.n_emb, blocks, cells);
+        // the 8 index pairs of the query are shared out over its lanes
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            if ((c & (lanes - 1)) != lane) continue;
+            const int64_t block = ok ? blocks[c] : (int64_t)(q % src.n_emb);
+            const int64_t cell_of = ok ? cells[c] : (int64_t)(c % src.cells_per_grid);
+            if (staged) {
+                stage_idx[warp][0][ql * 8 + c] = block;
+                stage_idx[warp][1][ql * 8 + c] = cell_of;
+            } else {
+                idx_out[q * 8 + c] = block;
+                idx_out[(n + q) * 8 + c] = cell_of;
+            }
+        }
         if (has_ch && !ok) {
 #pragma unroll
-            for (int c = 0; c < 8; ++c) store_pack<T, VEC>(rows_out + (q * 8 + c) * D + ch, gz);
+            for (int c = 0; c < 8; ++c) {
+                if (staged) stage_rows[warp][(((ql * 8 + c) << lane_shift) + lane) ^ swizzle] = make_uint4(0, 0, 0, 0);
+                else store_pack<T, VEC>(rows_out + (q * 8 + c) * D + ch, gz);
+            }
             if (SECOND) store_pack<T, VEC>(side + q * D + ch, gz);
         } else if (has_ch) {
             AxisWeights<T> aw;
@@ -513,7 +542,8 @@ __global__ void __launch_bounds__(256, SECOND ? 2 : (NEED_GO ? 3 : 4)) query_bac
                     if (SECOND) gz.v[k] += w * e[c].v[k];
                     if (!SECOND && NEED_GO) dot += e[c].v[k] * zv.v[k];
                 }
-                store_pack<T, VEC>(out, g);
+                if (staged) stage_rows[warp][(((ql * 8 + c) << lane_shift) + lane) ^ swizzle] = *reinterpret_cast<const uint4*>(g.v);
+                else store_pack<T, VEC>(out, g);
                 out += corner_stride;
                 if (!SECOND && NEED_GO) {
                     go[0] += dot * wg[0];
@@ -523,12 +553,23 @@ __global__ void __launch_bounds__(256, SECOND ? 2 : (NEED_GO ? 3 : 4)) query_bac
             }
             if (SECOND) store_pack<T, VEC>(side + q * D + ch, gz);
         }
-        // the 8 index pairs of the query are shared out over its lanes
+    }
+    if (staged) {
+        __syncwarp();
+        const int64_t q0 = (tid - warp_lane) >> lane_shift;   // the warp's first query
+        if (q0 < n) {
+            uint4* dst = reinterpret_cast<uint4*>(rows_out + q0 * 8 * D);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            if ((c & (lanes - 1)) != lane) continue;
-            idx_out[q * 8 + c] = ok ? blocks[c] : (int64_t)(q % src.n_emb);
-            idx_out[(n + q) * 8 + c] = ok ? cells[c] : (int64_t)(c % src.cells_per_grid);
+            for (int k = 0; k < 8; ++k) {
+                const int j = k * 32 + warp_lane;
+                const int jq = j >> (3 + lane_shift);
+                if (q0 + jq < n) dst[j] = stage_rows[warp][j ^ ((jq * lanes) & 7)];
+            }
+            for (int j = warp_lane; j < (256 >> lane_shift); j += 32) {
+                if (q0 + (j >> 3) >= n) continue;
+                idx_out[q0 * 8 + j] = stage_idx[warp][0][j];
+                idx_out[(n + q0) * 8 + j] = stage_idx[warp][1][j];
+            }
         }
     }
     if (SECOND || !NEED_GO) return;
