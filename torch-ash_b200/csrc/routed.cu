@@ -243,19 +243,63 @@ __global__ void __launch_bounds__(256) routed_unpack_y_kernel(RoutedLayout L, co
     if (lane == 0 && masks) masks[i] = (uint8_t)(w >= 0);
 }
 
+// The asker's dL/dy rows go to the slots its positions took in the owners' inboxes.  A CTA handles the
+// 256 queries one route CTA handled, so those that went to one owner hold consecutive slots there: the
+// CTA orders its queries by (owner, slot) in shared memory and stores the rows in that order, a warp
+// instruction covering up to 512 contiguous bytes of one owner's inbox instead of eight 64-byte pieces
+// in eight places (what a link carries well is long segments).  Nothing depends on the slots really
+// being consecutive: a query whose slot falls outside its owner's run stores its row on its own.
 template <int VEC>
 __global__ void __launch_bounds__(256) routed_send_z_kernel(RoutedLayout L, const int32_t* __restrict__ where, int64_t n,
                                                             const float* __restrict__ z, int D, int lane_shift) {
-    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const int64_t i = tid >> lane_shift;
-    const int ch = (int)(tid & ((1 << lane_shift) - 1)) * VEC;
-    if (i >= n || ch >= D) return;
-    const int w = where[i];
-    if (w < 0) return;
-    const int owner = (int)((unsigned)w >> kRowOwnerShift);
-    const int64_t slot = (unsigned)w & kRowLocalMask;
-    float* inbox = reinterpret_cast<float*>(static_cast<char*>(L.bases[owner]) + L.inbox_z);
-    store_pack<float, VEC>(inbox + ((int64_t)L.rank * L.cap + slot) * D + ch, load_pack<float, VEC>(z + i * D + ch));
+    __shared__ int lowest[kRoutedMaxWorld], count[kRoutedMaxWorld], start[kRoutedMaxWorld + 1];
+    __shared__ short order[256];   // order[p] = the tile's query at position p of the (owner, slot) order
+    const int t = threadIdx.x;
+    const int64_t first = (int64_t)blockIdx.x * 256;
+    for (int o = t; o < L.world; o += blockDim.x) {
+        lowest[o] = 0x7fffffff;
+        count[o] = 0;
+    }
+    order[t] = -1;
+    __syncthreads();
+    const int64_t i = first + t;
+    const int w = i < n ? where[i] : -1;
+    const int owner = w >= 0 ? (int)((unsigned)w >> kRowOwnerShift) : 0;
+    const int slot = w >= 0 ? (int)((unsigned)w & kRowLocalMask) : 0;
+    const bool sends = w >= 0 && owner < L.world && slot < L.cap;
+    if (sends) {
+        atomicMin(&lowest[owner], slot);
+        atomicAdd(&count[owner], 1);
+    }
+    __syncthreads();
+    if (t == 0) {
+        int sum = 0;
+        for (int o = 0; o < L.world; ++o) {
+            start[o] = sum;
+            sum += count[o];
+        }
+        start[L.world] = sum;
+    }
+    __syncthreads();
+    const bool placed = sends && slot - lowest[owner] < count[owner];
+    if (placed) order[start[owner] + slot - lowest[owner]] = (short)t;
+    __syncthreads();
+    const int lanes = 1 << lane_shift;
+    const int ch = (t & (lanes - 1)) * VEC;
+    if (ch < D) {
+        for (int p = t >> lane_shift; p < start[L.world]; p += 256 >> lane_shift) {
+            const int query = order[p];
+            if (query < 0) continue;
+            const int wq = where[first + query];
+            float* inbox = reinterpret_cast<float*>(static_cast<char*>(L.bases[(unsigned)wq >> kRowOwnerShift]) + L.inbox_z);
+            store_pack<float, VEC>(inbox + ((int64_t)L.rank * L.cap + ((unsigned)wq & kRowLocalMask)) * D + ch,
+                                   load_pack<float, VEC>(z + (first + query) * D + ch));
+        }
+    }
+    if (sends && !placed) {
+        float* inbox = reinterpret_cast<float*>(static_cast<char*>(L.bases[owner]) + L.inbox_z) + ((int64_t)L.rank * L.cap + slot) * D;
+        for (int c = 0; c < D; ++c) inbox[c] = z[i * D + c];
+    }
 }
 
 __global__ void __launch_bounds__(256) routed_unpack_gx_kernel(RoutedLayout L, const int32_t* __restrict__ where,
@@ -560,7 +604,7 @@ int ashb_routed_send_z(const int32_t* where_dev, int64_t n, const float* z, int6
     if (n == 0) return ASHB_OK;
     ASHB_REQUIRE(n > 0 && where_dev && z, "null buffer or negative count");
     const LaneShape sh = lane_shape(D, z);
-    const unsigned grid = (unsigned)(((n << sh.lane_shift) + 255) / 256);
+    const unsigned grid = (unsigned)((n + 255) / 256);   // one CTA per 256 queries, whatever the lanes per query
     ASHB_ROUTED_VEC(sh, (routed_send_z_kernel<VEC><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
                                 L, where_dev, n, z, (int)D, sh.lane_shift)));
     ASHB_LAUNCH_CHECK();
