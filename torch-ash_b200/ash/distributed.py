@@ -694,9 +694,12 @@ class RoutedSparseDenseGrid(UnBoundedSparseDenseGrid):
         optimizer.step()              # on this rank's shard
 
     The block structure (hash map, neighbour table, block -> (owner, row) table) is replicated: build
-    it the same way on every rank, then call ``sync_structure_()``.  One batch is in flight at a time
-    (forward, then its backward passes); all three autograd levels of the reference are provided (a loss
-    on dL/dx trains the embeddings through a double backward round)."""
+    it the same way on every rank, then call ``sync_structure_()`` ONCE, when the structure is final:
+    a later call hands the shard rows out afresh and does not move the values with them.  One batch is
+    in flight at a time (forward, then its backward passes); all three autograd levels of the reference
+    are provided (a loss on dL/dx trains the embeddings through a double backward round).  Every pass is
+    a collective round: all ranks must run the same passes in the same order (a rank whose loss does not
+    reach a pass the others run leaves them waiting until the process group's timeout)."""
 
     def __init__(self, in_dim: int, num_embeddings: int, embedding_dim: int, grid_dim: int, cell_size: float = 1.0,
                  device=None, group=None, max_batch: int = 1 << 20, region_slack: float = 1.5, shard_slack: float = 1.25,
