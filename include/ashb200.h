@@ -391,8 +391,10 @@ int ashb_tsdf_touch(ashb_map* map, const float* depth, int H, int W, const float
  * touched[idx] == stamp.  embeddings float32 [n_emb][G^3][D], 5 <= D <= 16, with sdf at
  * sdf_channel, colour at rgb_channel..+2 and the weight at weight_channel (the demo uses
  * 0, 1, 4).  n_integrated_dev: optional device counter incremented once per fused block.
- * With the list of step 1 a few persistent CTAs walk exactly the stamped blocks; without it
- * (NULL, NULL) one CTA per embedding row checks its stamp. */
+ * With the list of step 1 a few persistent CTAs walk exactly the stamped blocks -- and when a
+ * block's rows are a 16-byte aligned multiple of 16 bytes they travel by bulk copies (global ->
+ * shared on an mbarrier, shared -> global), two tiles per CTA, so that loading, arithmetic and
+ * storing overlap; without it (NULL, NULL) one CTA per embedding row checks its stamp. */
 int ashb_tsdf_integrate(void* embeddings, int64_t n_emb, int G, int64_t D, const int32_t* grid_coords,
                         const uint32_t* touched, uint32_t stamp, const float* depth, const float* color,
                         int H, int W, const float* intrinsic, const float* world_to_cam, float depth_max,
@@ -441,6 +443,11 @@ int ashb_tsdf_fuse_frames(ashb_map* map, void* embeddings, int64_t n_emb, int G,
  * so two calls whose work overlaps on the GPU race with each other: issue them on one stream
  * or order them yourself.  No cudaMalloc, cudaFree or other allocating routine is called. */
 int ashb_tsdf_static_max_blocks(void);
+
+/* The bulk-copy path of ashb_tsdf_integrate bounds every wait on a copy; a wait that runs out is
+ * counted (on the current device) and the CTA stops.  *out = that count since the library was
+ * loaded: 0 in any healthy run.  Synchronises with the device. */
+int ashb_tsdf_copy_timeouts(unsigned int* out);
 int ashb_tsdf_fuse_frame_static(ashb_map* map, void* embeddings, int64_t n_emb, int G, int64_t D,
                                 const float* depth, const float* color, int H, int W,
                                 const float* intrinsic, const float* world_to_cam,

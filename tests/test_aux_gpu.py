@@ -156,6 +156,9 @@ def test_tsdf_fusion_vs_oracle(H, W, whole_sequence, dil):
         for datum in frames:
             fusion.fuse_frame(datum)
     assert grid.engine.backend.status() == 0
+    import __ash
+
+    assert __ash.tsdf_copy_timeouts(DEV) == 0      # no bounded wait of the bulk copies ran out
     keys, idx = grid.engine.items()
     rkeys, ridx = ref.map.items()
     keys_np = keys.cpu().numpy()

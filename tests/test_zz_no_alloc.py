@@ -58,6 +58,7 @@ def test_static_scratch_fusion_matches_regular_path():
         np.testing.assert_allclose(e_s, e_r, rtol=1e-6, atol=1e-6)
         assert (e_r[..., 4] > 0).any(), f"call {call}: nothing was fused"
     assert static.engine.backend.status() == 0
+    assert __ash.tsdf_copy_timeouts(DEV) == 0
 
 
 def test_static_scratch_rejects_oversized_grids():

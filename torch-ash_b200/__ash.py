@@ -63,6 +63,7 @@ _lib.ashb_tsdf_fuse_frames.argtypes = [_vp, _vp, _i64, _int, _i64, _int, _vp, _v
                                        _vp, _int, _vp, _vp, _f32, _int, _int, _int, _vp, _vp, _c.c_uint32, _vp, _vp, _int, _vp, _vp]
 _lib.ashb_tsdf_fuse_frame_static.argtypes = [_vp, _vp, _i64, _int, _i64, _vp, _vp, _int, _int, _vp, _vp, _vp, _f32, _c.c_double,
                                              _vp, _int, _vp, _vp, _f32, _int, _int, _int, _vp]
+_lib.ashb_tsdf_copy_timeouts.argtypes = [_vp]
 _lib.ashb_grid_build_neighbor_lut.argtypes = [_vp, _vp, _vp, _i64, _vp]
 _lib.ashb_grid_query_forward.argtypes = [_vp, _int, _int, _vp, _vp, _c.c_double, _vp, _int, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]
 _lib.ashb_grid_query_backward.argtypes = [_vp, _int, _int, _vp, _vp, _vp, _c.c_double, _vp, _int, _vp, _vp, _vp, _vp, _int,
@@ -639,6 +640,16 @@ def tsdf_fuse_frames(hashmap, embeddings, grid_dim, depths, colors, K, E, Ei, de
         int(first_stamp), touched_list.data_ptr(), touched_count.data_ptr(),
         int(touched_list.numel() >= 2 * emb.shape[0] and touched_count.numel() >= 2),
         counter.data_ptr() if counter is not None else None, _stream(emb.device)))
+
+
+def tsdf_copy_timeouts(device=None) -> int:
+    """Waits of the fusion kernel's bulk copies that ran out on ``device`` since the library was loaded
+    (0 in any healthy run).  Synchronises with the device."""
+    out = _c.c_uint(0)
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        _check(_lib.ashb_tsdf_copy_timeouts(_c.byref(out)))
+    return int(out.value)
 
 
 def tsdf_fuse_frame_static(hashmap, embeddings, grid_dim, depth, color, intrinsic, world_to_cam, cam_to_world,

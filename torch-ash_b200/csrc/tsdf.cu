@@ -150,7 +150,7 @@ __device__ __forceinline__ int block_of(float w, float org, float inv_cell, floa
     return (int)floorf(__fmul_rn(__fmul_rn(__fsub_rn(w, org), inv_cell), inv_G));
 }
 
-__global__ void __launch_bounds__(256) tsdf_touch_kernel(Table16 t, TouchTarget tt, const float* __restrict__ depth,
+__global__ void __launch_bounds__(256, 8) tsdf_touch_kernel(Table16 t, TouchTarget tt, const float* __restrict__ depth,
                                                          int H, int W, Camera cam, float depth_max, float inv_cell,
                                                          float3 origin, float inv_G) {
     const int64_t pix = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -188,83 +188,189 @@ __global__ void __launch_bounds__(256) points_touch_kernel(Table16 t, TouchTarge
 }
 
 // ---- integrate ---------------------------------------------------------------------
+struct IntegrateFrame {
+    const float* __restrict__ depth;
+    const float* __restrict__ color;
+    int H, W;
+    Camera cam;
+    float depth_max, cell_size;
+    float3 origin;
+    int G, cells;
+    float trunc;
+    int sdf_ch, rgb_ch, w_ch;
+};
+
+// One observation fused into every cell of block (gx, gy, gz), whose rows sit in `tile` (cells * D floats).
 template <int D>
-__global__ void __launch_bounds__(256) tsdf_integrate_kernel(
-        float* __restrict__ emb, const int32_t* __restrict__ grid_coords, const uint32_t* __restrict__ touched,
-        uint32_t stamp, const float* __restrict__ depth, const float* __restrict__ color, int H, int W, Camera cam,
-        float depth_max, float cell_size, float3 origin, int G, int cells, float trunc, int sdf_ch, int rgb_ch,
-        int w_ch, unsigned long long* n_integrated, int64_t n_emb, const int32_t* __restrict__ touched_list,
-        const int32_t* __restrict__ touched_count) {
-    extern __shared__ float tile[];  // cells * D floats
-    // Work items: the compact list written by the touch kernel (a few persistent CTAs walk it),
-    // or, without a list, every embedding row whose stamp matches (one CTA per row).
-    const int64_t n_items = touched_list ? (int64_t)*touched_count : n_emb;
-    for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
-    const int64_t idx = touched_list ? (int64_t)touched_list[item] : item;
-    if (!touched_list && touched[idx] != stamp) continue;
-    float* block = emb + idx * (int64_t)cells * D;
-    const int n_float = cells * D;
-    // rows are 16-byte aligned when cells * D * 4 is a multiple of 16
-    const bool vec_ok = (n_float & 3) == 0 && (((uintptr_t)block) & 15) == 0;
-    if (vec_ok) {
-        for (int i = threadIdx.x; i < n_float / 4; i += blockDim.x)
-            reinterpret_cast<float4*>(tile)[i] = reinterpret_cast<const float4*>(block)[i];
-    } else {
-        for (int i = threadIdx.x; i < n_float; i += blockDim.x) tile[i] = block[i];
-    }
-    __syncthreads();
-    const int gx = grid_coords[3 * idx], gy = grid_coords[3 * idx + 1], gz = grid_coords[3 * idx + 2];
-    for (int c = threadIdx.x; c < cells; c += blockDim.x) {
+__device__ __forceinline__ void integrate_cells(float* tile, int gx, int gy, int gz, const IntegrateFrame& f) {
+    const int G = f.G;
+    for (int c = threadIdx.x; c < f.cells; c += blockDim.x) {
         const int cx = c % G, cy = (c / G) % G, cz = c / (G * G);
         // cell_to_world: (block * G + cell) * cell_size (+ origin for bounded grids)
-        const float px = __fadd_rn(__fmul_rn((float)(gx * G + cx), cell_size), origin.x);
-        const float py = __fadd_rn(__fmul_rn((float)(gy * G + cy), cell_size), origin.y);
-        const float pz = __fadd_rn(__fmul_rn((float)(gz * G + cz), cell_size), origin.z);
-        const float x = affine3(cam.E, px, py, pz);
-        const float y = affine3(cam.E + 4, px, py, pz);
-        const float z = affine3(cam.E + 8, px, py, pz);
-        const float un = dot3(cam.K, x, y, z);
-        const float vn = dot3(cam.K + 3, x, y, z);
-        const float d = dot3(cam.K + 6, x, y, z);
+        const float px = __fadd_rn(__fmul_rn((float)(gx * G + cx), f.cell_size), f.origin.x);
+        const float py = __fadd_rn(__fmul_rn((float)(gy * G + cy), f.cell_size), f.origin.y);
+        const float pz = __fadd_rn(__fmul_rn((float)(gz * G + cz), f.cell_size), f.origin.z);
+        const float x = affine3(f.cam.E, px, py, pz);
+        const float y = affine3(f.cam.E + 4, px, py, pz);
+        const float z = affine3(f.cam.E + 8, px, py, pz);
+        const float un = dot3(f.cam.K, x, y, z);
+        const float vn = dot3(f.cam.K + 3, x, y, z);
+        const float d = dot3(f.cam.K + 6, x, y, z);
         float w = 0.f, sdf = 0.f, r = 0.f, g = 0.f, b = 0.f;
         if (d > 0.f) {
             const float uf = rintf(__fdiv_rn(un, d)), vf = rintf(__fdiv_rn(vn, d));  // torch.round: half to even
-            if (uf >= 0.f && vf >= 0.f && uf < (float)W && vf < (float)H) {
+            if (uf >= 0.f && vf >= 0.f && uf < (float)f.W && vf < (float)f.H) {
                 const int u = (int)uf, v = (int)vf;
-                const float dr = __ldg(depth + (int64_t)v * W + u);
-                const float* col = color + ((int64_t)v * W + u) * 3;
+                const float dr = __ldg(f.depth + (int64_t)v * f.W + u);
+                const float* col = f.color + ((int64_t)v * f.W + u) * 3;
                 r = __ldg(col), g = __ldg(col + 1), b = __ldg(col + 2);
                 sdf = __fsub_rn(dr, d);
-                if (dr > 0.f && dr < depth_max && sdf >= -trunc) w = 1.f;
-                if (sdf >= trunc) sdf = trunc;
+                if (dr > 0.f && dr < f.depth_max && sdf >= -f.trunc) w = 1.f;
+                if (sdf >= f.trunc) sdf = f.trunc;
             }
         }
         // outside the image or behind the camera the observation has weight 0 and its
         // value does not matter (demo/rgbd_fusion.py:93-108)
         float* cell = tile + c * D;
-        const float w_sum = cell[w_ch];
+        const float w_sum = cell[f.w_ch];
         // demo/rgbd_fusion.py:247-249: mean' = (mean * w_sum + obs * w) / (w_sum + w + 1e-6)
         const float w_new = __fadd_rn(w_sum, w);
         const float den = __fadd_rn(w_new, 1e-6f);
         auto fuse = [&](float mean, float obs) {
             return __fdiv_rn(__fadd_rn(__fmul_rn(mean, w_sum), __fmul_rn(obs, w)), den);
         };
-        cell[sdf_ch] = fuse(cell[sdf_ch], sdf);
-        cell[rgb_ch] = fuse(cell[rgb_ch], r);
-        cell[rgb_ch + 1] = fuse(cell[rgb_ch + 1], g);
-        cell[rgb_ch + 2] = fuse(cell[rgb_ch + 2], b);
-        cell[w_ch] = w_new;
+        cell[f.sdf_ch] = fuse(cell[f.sdf_ch], sdf);
+        cell[f.rgb_ch] = fuse(cell[f.rgb_ch], r);
+        cell[f.rgb_ch + 1] = fuse(cell[f.rgb_ch + 1], g);
+        cell[f.rgb_ch + 2] = fuse(cell[f.rgb_ch + 2], b);
+        cell[f.w_ch] = w_new;
+    }
+}
+
+template <int D>
+__global__ void __launch_bounds__(256, 8) tsdf_integrate_kernel(
+        float* __restrict__ emb, const int32_t* __restrict__ grid_coords, const uint32_t* __restrict__ touched,
+        uint32_t stamp, IntegrateFrame f, unsigned long long* n_integrated, int64_t n_emb,
+        const int32_t* __restrict__ touched_list, const int32_t* __restrict__ touched_count) {
+    extern __shared__ float tile[];  // cells * D floats
+    // Work items: the compact list written by the touch kernel (a few persistent CTAs walk it),
+    // or, without a list, every embedding row whose stamp matches (one CTA per row).
+    const int64_t n_items = touched_list ? (int64_t)*touched_count : n_emb;
+    for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
+        const int64_t idx = touched_list ? (int64_t)touched_list[item] : item;
+        if (!touched_list && touched[idx] != stamp) continue;
+        float* block = emb + idx * (int64_t)f.cells * D;
+        const int n_float = f.cells * D;
+        // rows are 16-byte aligned when cells * D * 4 is a multiple of 16
+        const bool vec_ok = (n_float & 3) == 0 && (((uintptr_t)block) & 15) == 0;
+        if (vec_ok) {
+            for (int i = threadIdx.x; i < n_float / 4; i += blockDim.x)
+                reinterpret_cast<float4*>(tile)[i] = reinterpret_cast<const float4*>(block)[i];
+        } else {
+            for (int i = threadIdx.x; i < n_float; i += blockDim.x) tile[i] = block[i];
+        }
+        __syncthreads();
+        integrate_cells<D>(tile, grid_coords[3 * idx], grid_coords[3 * idx + 1], grid_coords[3 * idx + 2], f);
+        __syncthreads();
+        if (vec_ok) {
+            for (int i = threadIdx.x; i < n_float / 4; i += blockDim.x)
+                reinterpret_cast<float4*>(block)[i] = reinterpret_cast<const float4*>(tile)[i];
+        } else {
+            for (int i = threadIdx.x; i < n_float; i += blockDim.x) block[i] = tile[i];
+        }
+        if (threadIdx.x == 0 && n_integrated) atomicAdd(n_integrated, 1ull);
+        __syncthreads();  // the tile is reused by the next item
+    }
+}
+
+// Number of waits of the bulk-copy variant below that ran out (0 in any healthy run): read with
+// ashb_tsdf_copy_timeouts.
+__device__ unsigned int g_tsdf_copy_timeouts = 0;
+
+__device__ __forceinline__ uint32_t smem_address(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// Waits, with a limit, for phase `parity` of the mbarrier at `bar`; false when the limit ran out.
+__device__ __forceinline__ bool wait_phase(uint32_t bar, uint32_t parity) {
+    for (int spin = 0; spin < (1 << 18); ++spin) {
+        uint32_t done;
+        asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(done)
+                : "r"(bar), "r"(parity)
+                : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+// The same pass over a work list with the block rows moved by the copy engine: a persistent CTA keeps
+// two tiles in shared memory; while it fuses the observation into one, the next block's rows arrive in
+// the other (cp.async.bulk global -> shared, completion on an mbarrier) and the finished tile leaves
+// as one bulk store (shared -> global), so loading, arithmetic and storing overlap instead of taking
+// turns.  A block's rows are one contiguous, 16-byte aligned stretch of cells * D * 4 bytes (a multiple
+// of 16: checked by the host).  Every wait has an iteration limit; a CTA whose wait runs out counts it
+// in g_tsdf_copy_timeouts, waits for its own stores and stops.
+template <int D>
+__global__ void __launch_bounds__(256, 8) tsdf_integrate_bulk_kernel(
+        float* __restrict__ emb, const int32_t* __restrict__ grid_coords, IntegrateFrame f,
+        unsigned long long* n_integrated, const int32_t* __restrict__ touched_list,
+        const int32_t* __restrict__ touched_count) {
+    extern __shared__ __align__(128) float tiles[];  // 2 tiles of cells * D floats
+    __shared__ __align__(8) unsigned long long full[2];
+    const int n_float = f.cells * D;
+    const uint32_t bytes = (uint32_t)n_float * 4u;
+    const int64_t n_items = (int64_t)*touched_count;
+    const bool boss = threadIdx.x == 0;
+    if (boss) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_address(&full[0])) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_address(&full[1])) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (vec_ok) {
-        for (int i = threadIdx.x; i < n_float / 4; i += blockDim.x)
-            reinterpret_cast<float4*>(block)[i] = reinterpret_cast<const float4*>(tile)[i];
-    } else {
-        for (int i = threadIdx.x; i < n_float; i += blockDim.x) block[i] = tile[i];
+    auto fetch = [&](int64_t item, int buf) {   // thread 0 only
+        const float* src = emb + (int64_t)touched_list[item] * n_float;
+        const uint32_t bar = smem_address(&full[buf]);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                             smem_address(tiles + (int64_t)buf * n_float)),
+                     "l"(src), "r"(bytes), "r"(bar)
+                     : "memory");
+    };
+    if (boss && (int64_t)blockIdx.x < n_items) fetch(blockIdx.x, 0);
+    int round = 0;
+    for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x, ++round) {
+        const int buf = round & 1;
+        const int64_t next = item + gridDim.x;
+        if (boss && next < n_items) {
+            // the other tile was handed to a bulk store one round ago: it may be refilled once that store has read it
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            fetch(next, buf ^ 1);
+        }
+        const bool arrived = wait_phase(smem_address(&full[buf]), (uint32_t)(round >> 1) & 1u);
+        if (!__syncthreads_and(arrived)) {
+            if (boss) {
+                atomicAdd(&g_tsdf_copy_timeouts, 1u);
+                // the copy already requested for the next round must not land in a dead CTA's memory
+                if (next < n_items) wait_phase(smem_address(&full[buf ^ 1]), (uint32_t)((round + 1) >> 1) & 1u);
+            }
+            break;
+        }
+        float* tile = tiles + (int64_t)buf * n_float;
+        const int64_t idx = touched_list[item];
+        integrate_cells<D>(tile, grid_coords[3 * idx], grid_coords[3 * idx + 1], grid_coords[3 * idx + 2], f);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tile as written, visible to the copy engine
+        __syncthreads();
+        if (boss) {
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(emb + idx * (int64_t)n_float),
+                         "r"(smem_address(tile)), "r"(bytes)
+                         : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            if (n_integrated) atomicAdd(n_integrated, 1ull);
+        }
     }
-    if (threadIdx.x == 0 && n_integrated) atomicAdd(n_integrated, 1ull);
-    __syncthreads();  // the tile is reused by the next item
-    }
+    if (boss) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // stores complete before the CTA's memory goes
 }
 
 }  // namespace ashb
@@ -372,19 +478,36 @@ int ashb_tsdf_integrate(void* embeddings, int64_t n_emb, int G, int64_t D, const
     const int cells = G * G * G;
     const size_t smem = (size_t)cells * D * sizeof(float);
     ASHB_REQUIRE(smem <= 200 * 1024, "block of %zu bytes does not fit in shared memory", smem);
-    const float3 org = make_float3(origin[0], origin[1], origin[2]);
-    // with a work list: a whole number of waves of persistent CTAs; without: one CTA per row
-    const unsigned launch_ctas =
-            touched_list ? (unsigned)(n_emb < (int64_t)sm_count() * 8 ? n_emb : (int64_t)sm_count() * 8) : (unsigned)n_emb;
+    const IntegrateFrame frame{depth, color, H, W, cam, depth_max, (float)cell_size,
+                               make_float3(origin[0], origin[1], origin[2]), G, cells, trunc, sdf_channel, rgb_channel,
+                               weight_channel};
+    // The copy-engine variant needs a work list, 16-byte aligned rows of a multiple of 16 bytes, and room
+    // for two tiles per CTA; everything else takes the plain kernel.
+    const bool bulk = touched_list != nullptr && smem % 16 == 0 && ((uintptr_t)embeddings & 15) == 0 && 2 * smem <= 96 * 1024;
+    // with a work list: exactly the CTAs that are resident at once walk it (more would queue behind them
+    // as a partly filled second wave); without: one CTA per row
+    // The pass is bound by arithmetic (seven IEEE divisions per cell), which half of an SM's thread slots
+    // already saturate; the other half is left to the allocation pass of the NEXT frame, which runs
+    // beside it on a second stream when a sequence is fused (ashb_tsdf_fuse_frames).
+    constexpr int kIntegrateCtasPerSm = 4;
 #define ASHB_TSDF_LAUNCH(DD)                                                                               \
     case DD: {                                                                                             \
-        if (smem > 48 * 1024)                                                                              \
-            ASHB_CUDA_TRY(cudaFuncSetAttribute(tsdf_integrate_kernel<DD>,                                  \
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));  \
-        tsdf_integrate_kernel<DD><<<launch_ctas, 256, smem, st>>>(                                         \
-                static_cast<float*>(embeddings), grid_coords, touched, stamp, depth, color, H, W, cam,     \
-                depth_max, (float)cell_size, org, G, cells, trunc, sdf_channel, rgb_channel, weight_channel,      \
-                n_integrated_dev, n_emb, touched_list, touched_count);                                     \
+        const size_t dyn = bulk ? 2 * smem : smem;                                                         \
+        const void* fn = bulk ? (const void*)tsdf_integrate_bulk_kernel<DD> : (const void*)tsdf_integrate_kernel<DD>; \
+        if (dyn > 48 * 1024)                                                                               \
+            ASHB_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn)); \
+        int per_sm = 0;                                                                                    \
+        ASHB_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, 256, dyn));               \
+        if (per_sm > kIntegrateCtasPerSm) per_sm = kIntegrateCtasPerSm;                                    \
+        const int64_t resident = (int64_t)sm_count() * (per_sm > 0 ? per_sm : 1);                          \
+        const unsigned launch_ctas = touched_list ? (unsigned)(n_emb < resident ? n_emb : resident) : (unsigned)n_emb; \
+        if (bulk)                                                                                          \
+            tsdf_integrate_bulk_kernel<DD><<<launch_ctas, 256, dyn, st>>>(                                 \
+                    static_cast<float*>(embeddings), grid_coords, frame, n_integrated_dev, touched_list, touched_count); \
+        else                                                                                               \
+            tsdf_integrate_kernel<DD><<<launch_ctas, 256, dyn, st>>>(                                      \
+                    static_cast<float*>(embeddings), grid_coords, touched, stamp, frame, n_integrated_dev, n_emb, \
+                    touched_list, touched_count);                                                          \
     } break;
     switch ((int)D) {
         ASHB_TSDF_LAUNCH(5)
@@ -525,6 +648,12 @@ int ashb_tsdf_fuse_frames(ashb_map* m, void* embeddings, int64_t n_emb, int G, i
 }
 
 int ashb_tsdf_static_max_blocks(void) { return ASHB_TSDF_STATIC_MAX_BLOCKS; }
+
+int ashb_tsdf_copy_timeouts(unsigned int* out) {
+    ASHB_REQUIRE(out != nullptr, "out is null");
+    ASHB_CUDA_TRY(cudaMemcpyFromSymbol(out, g_tsdf_copy_timeouts, sizeof(unsigned int)));
+    return ASHB_OK;
+}
 
 int ashb_tsdf_fuse_frame_static(ashb_map* m, void* embeddings, int64_t n_emb, int G, int64_t D,
                                 const float* depth, const float* color, int H, int W, const float* intrinsic,
