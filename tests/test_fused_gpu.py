@@ -299,6 +299,45 @@ def test_row_list_entry_point_float64_and_second_order():
     assert idx.shape == (2, 0) and rows.shape == (0, 6) and side.shape == (0, 3)
 
 
+@pytest.mark.parametrize("dtype,D", [(torch.float32, 16), (torch.float64, 8), (torch.float64, 16), (torch.float32, 8),
+                                     (torch.float32, 4)])
+def test_row_list_entry_point_row_shapes(dtype, D):
+    """The row-list kernels lay a warp's records out in shared memory before storing them when a lane
+    holds 16 bytes of a row and the lanes cover the row exactly with 4 lanes or more (float32 D = 16;
+    float64 D = 8 with 4 lanes, D = 16 with 8); other shapes (here float32 D = 8 and 4) store directly.  Both, first and
+    second order, on a batch whose size is not a multiple of a warp's queries, with misses, against the
+    dense entry points."""
+    import __ash
+
+    grid, x = _make("unbounded", 4, D, seed=23)
+    x = x[:1003].contiguous()
+    emb = grid.embeddings.detach().to(dtype)
+    origin, cell_size = grid._cell_frame()
+    hm, lut = grid.engine.backend, grid._neighbor_lut32()
+    n = x.shape[0]
+    gen = torch.Generator(device=DEV).manual_seed(5)
+    z = torch.randn(n, D, generator=gen, device=DEV, dtype=dtype)
+    ggx = torch.randn(n, 3, generator=gen, device=DEV, dtype=dtype)
+    tol = 1e-12 if dtype == torch.float64 else 2e-5
+    _, masks, bidx = __ash.grid_query_forward(hm, emb, x, cell_size, origin, 4, lut, "linear")
+    assert 0.2 < float(masks.float().mean()) < 0.95
+    ge, gx = __ash.grid_query_backward(hm, z, emb, x, cell_size, origin, 4, lut, bidx, "linear")
+    idx, rows, gx_r = __ash.grid_query_backward_rows(hm, z, emb, x, cell_size, origin, 4, lut, bidx, "linear")
+    assert idx.shape == (2, 8 * n) and rows.shape == (8 * n, D)
+    assert int(idx[0].min()) >= 0 and int(idx[0].max()) < emb.shape[0] and int(idx[1].max()) < emb.shape[1]
+    buf = torch.zeros_like(emb)
+    __ash.rows_scatter_add(buf, idx, rows)
+    torch.testing.assert_close(buf, ge, rtol=tol, atol=tol * float(ge.abs().max()))
+    assert torch.equal(gx, gx_r)
+    gz, ge2 = __ash.grid_query_backward_backward(hm, ggx, z, emb, x, cell_size, origin, 4, lut, bidx, "linear")
+    idx, rows, gz_r = __ash.grid_query_backward_rows(hm, z, emb, x, cell_size, origin, 4, lut, bidx, "linear",
+                                                     grad_grad_x=ggx)
+    buf.zero_()
+    __ash.rows_scatter_add(buf, idx, rows)
+    torch.testing.assert_close(buf, ge2, rtol=tol, atol=tol * float(ge2.abs().max()))
+    assert torch.equal(gz, gz_r)
+
+
 def test_zero_grad_rows_clears_exactly_what_a_batch_added():
     grid, x = _make("unbounded", 8, 16, seed=21)
     grid.grad_mode = "in_place"
