@@ -718,7 +718,14 @@ def measure_routed(ash, bw, device, dist, rank, world, grid, blocks, n_queries, 
         for k, a, b in zip(names, marks[:-1], marks[1:]):
             phases[k].append(a.elapsed_time(b))
     phase_ms = {k: round(statistics.mean(v), 4) for k, v in phases.items()}
-    out = {"ms_per_step": ms, "phase_ms_rank0": phase_ms, "queries_per_rank": n_queries,
+    # the slowest and the fastest rank per phase (a barrier's time is mostly the wait for the slowest)
+    mine = torch.tensor([phase_ms[k] for k in names], device=device, dtype=torch.float64)
+    slowest, fastest = mine.clone(), mine.clone()
+    dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
+    dist.all_reduce(fastest, op=dist.ReduceOp.MIN)
+    phase_spread = {k: [round(float(lo), 4), round(float(hi), 4)] for k, lo, hi in zip(names, fastest, slowest)}
+    out = {"ms_per_step": ms, "phase_ms_rank0": phase_ms, "phase_ms_min_max_over_ranks": phase_spread,
+           "queries_per_rank": n_queries,
            "nvlink_bytes_per_rank_per_step": int(n_queries * (world - 1) / world * (16 + 4 * D + 4 * D + 16))}
     if with_e2e:
         x_host = [x.cpu().pin_memory() for x in xs]
@@ -1284,7 +1291,8 @@ def main():
         line["config"]["parity"] = multi["parity"]
         nv = weak["nvlink_bytes_per_rank_per_step"]
         line["multi_gpu_step"] = {
-            "phase_ms_rank0": weak["phase_ms_rank0"], "table_bytes_per_gpu": multi["table_bytes_per_gpu"],
+            "phase_ms_rank0": weak["phase_ms_rank0"], "phase_ms_min_max_over_ranks": weak["phase_ms_min_max_over_ranks"],
+            "table_bytes_per_gpu": multi["table_bytes_per_gpu"],
             "nvlink_bytes_per_rank_per_step": nv,
             "nvlink_GBs_per_gpu_per_direction_over_the_step": round(nv / (weak["ms_per_step"] * 1e-3) / 1e9, 1),
             "ownership_by_hash_of_coarse_block": multi["hash_partition"],
